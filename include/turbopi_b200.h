@@ -1,0 +1,150 @@
+/*
+ * turbopi_b200 -- C ABI of the B200 (sm_100a) kernels behind TurboPi's quantized
+ * Pi0.5 inference plugins.
+ *
+ * Conventions for every entry point:
+ *   - all tensor pointers are caller-owned DEVICE memory, row-major, 16-byte aligned;
+ *   - the call only enqueues work on `stream` (no allocation, no synchronisation,
+ *     no global mutable state), so it may be captured in a CUDA graph and is safe
+ *     to call concurrently on different streams;
+ *   - the device is the calling thread's current device;
+ *   - `tpb200_*` functions return TPB200_OK or a negative tpb200_status; arguments
+ *     are validated on the host before anything is launched;
+ *   - functions that carry the reference's own names and signatures return void
+ *     as theirs do and report a bad argument through tpb200_last_error().
+ *
+ * File/line citations name the reference interface each entry point replaces
+ * (paths inside the TurboPi repository).
+ */
+#ifndef TURBOPI_B200_H_
+#define TURBOPI_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* tpb200_stream_t; /* == cudaStream_t */
+
+typedef enum {
+    TPB200_OK = 0,
+    TPB200_ERR_NULL = -1,      /* a required pointer is NULL */
+    TPB200_ERR_SHAPE = -2,     /* a dimension is out of the supported range */
+    TPB200_ERR_ALIGN = -3,     /* a pointer or row pitch is not 16-byte aligned */
+    TPB200_ERR_ENUM = -4,      /* unknown dtype / layout / activation / flag */
+    TPB200_ERR_CUDA = -5,      /* the CUDA runtime refused the launch */
+    TPB200_ERR_WORKSPACE = -6, /* workspace missing or too small */
+    TPB200_ERR_DEVICE = -7     /* a kernel gave up on a bounded wait (tpb200_device_error) */
+} tpb200_status;
+
+/* element types; values match the reference's DataType enum
+ * (openpi/nvfp4_packed_plugin/src/nvfp4_packed_kernel.cu:411-415) */
+enum { TPB200_F32 = 0, TPB200_F16 = 1, TPB200_BF16 = 2 };
+
+/* fused activations; values match the reference's ActivationType
+ * (openpi/nvfp4_packed_plugin/src/nvfp4_packed_plugin.h:44-48) */
+enum { TPB200_ACT_NONE = 0, TPB200_ACT_GELU = 1, TPB200_ACT_SILU = 2 };
+
+/* block-scale encodings */
+enum { TPB200_SCALE_F32 = 0, TPB200_SCALE_E4M3 = 1, TPB200_SCALE_F16 = 2, TPB200_SCALE_BF16 = 3 };
+
+/* INT4 weight layouts */
+enum {
+    TPB200_INT4_KBLOCK = 0,  /* (K/32, N, 4) int32 + (K/32, N) fp16 scales: W4A16Packer's order,
+                                openpi/src/openpi/utils/w4a16_packer.py:129-174 */
+    TPB200_INT4_ROWMAJOR = 1 /* (N, K/8) int32 + (N, K/group) scales, 8 codes per word along K */
+};
+
+/* launch flags */
+enum {
+    TPB200_FLAG_NONE = 0,
+    TPB200_FLAG_PDL = 1 /* launch with programmatic stream serialisation: the kernel prefetches its
+                           weights while the previous kernel in the stream is still running, and
+                           waits for that kernel before it reads activations or writes outputs */
+};
+
+int tpb200_version(void);
+const char* tpb200_status_string(int status);
+/* last non-OK status produced on this host thread by a void-returning entry point (and clears it) */
+int tpb200_last_error(void);
+/* code recorded by a kernel whose bounded wait ran out on the current device, 0 if none; synchronises
+ * the device.  `clear` != 0 resets the word. */
+int tpb200_device_error(int clear);
+
+/* ---------------------------------------------------------------------------------------------
+ * W4A16 INT4 GEMV/GEMM for decode shapes (M <= 16).
+ *   out[m, n] = sum_k x[m, k] * (q[n, k] - 8) * scale[n, k / group] (+ bias[n])
+ * q are unsigned 4-bit codes (zero point 8), code i of a word at bits 4i.
+ * Replaces torch.ops.openpi.w4a16_gemv / the TVM gemv_vec128 kernel
+ * (openpi/src/openpi/ops/w4a16_gemv.py:56-102,244-294) for layout KBLOCK, group 32, fp16
+ * activations, fp32 output, M == 1; ROWMAJOR with group 128 is the benchmark layout.
+ * scales are fp16 (TPB200_SCALE_F16) or bf16.  fp32 accumulation.
+ * ------------------------------------------------------------------------------------------- */
+int tpb200_w4a16_gemv(const void* x, int x_dtype, const void* weight_packed, const void* scales,
+                      int scale_dtype, const void* bias, int bias_dtype, void* out, int out_dtype, int M,
+                      int N, int K, int group_size, int layout, int flags, tpb200_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * NVFP4 weight-only GEMV/GEMM for decode shapes (M <= 16).
+ *   out[m, n] = act(global_scale * sum_k x[m,k] * xs[m,k/block] * E2M1[code[n,k]] * ws[n,k/block] + bias[n])
+ * weight_packed [N, K/2] bytes (even k in the low nibble), weight_scales [N, K/block] fp32 or E4M3,
+ * block in {16, 32}; x_scales optional ([M, K/block], dtype of x).
+ * Replaces nvfp4_gemv_v6 / nvfp4_gemv_w4a16 / nvfp4_gemv
+ * (openpi/nvfp4_packed_plugin/src/nvfp4_gemv_v5.cu:430-476,
+ *  openpi/nvfp4_packed_plugin/src/nvfp4_packed_torch.cu:173-290).
+ * ------------------------------------------------------------------------------------------- */
+int tpb200_nvfp4_gemv(const void* x, int x_dtype, const void* x_scales, const void* weight_packed,
+                      const void* weight_scales, int scale_dtype, int block_size, float global_scale,
+                      const void* bias, int bias_dtype, void* out, int out_dtype, int M, int N, int K,
+                      int activation, int flags, tpb200_stream_t stream);
+
+/* One launch over several independent NVFP4 GEMVs that share M, dtypes, block format and activation
+ * (q/k/v, gate/up, or a whole stack of layers in a benchmark).  `count` <= TPB200_MAX_GROUP. */
+#define TPB200_MAX_GROUP 64
+typedef struct {
+    const void* x;             /* [M, K] */
+    const void* weight_packed; /* [N, K/2] */
+    const void* weight_scales; /* [N, K/block] */
+    const void* bias;          /* [N] or NULL */
+    void* out;                 /* [M, N] */
+    int N;
+    int K;
+    float global_scale;
+    int reserved;
+} tpb200_gemv_problem;
+
+int tpb200_nvfp4_gemv_grouped(const tpb200_gemv_problem* problems, int count, int x_dtype, int scale_dtype,
+                              int block_size, int bias_dtype, int out_dtype, int M, int activation,
+                              int flags, tpb200_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Entry points with the reference's names and signatures (TensorRT-plugin / test ABI).
+ * ------------------------------------------------------------------------------------------- */
+
+/* openpi/nvfp4_packed_plugin/src/nvfp4_packed_plugin.h:50-64: block 32, scales in the dtype
+ * named by data_type, scale_A may be NULL (weight-only). */
+void nvfp4_gemv_forward(const void* activation, const void* weight_packed, const void* scale_A,
+                        const void* scale_W, const void* bias, void* output, int M, int N, int K,
+                        int activation_type, int data_type, tpb200_stream_t stream);
+size_t nvfp4_gemv_workspace_size(int M, int N, int K);
+
+/* openpi/w4a16_plugin/src/w4a16_gemm_plugin.h:61-81: signed int4 (two's complement nibbles, even k
+ * in the low nibble) [N, K/2], bf16 scales/zeros [N, K/group]. */
+void quantizeWeightToINT4(const void* input_bf16, int8_t* output_packed, void* scales_bf16, void* zeros_bf16,
+                          int N, int K, int group_size, tpb200_stream_t stream);
+void dequantizeINT4ToBF16(const int8_t* input_packed, const void* scales_bf16, const void* zeros_bf16,
+                          void* output_bf16, int N, int K, int group_size, tpb200_stream_t stream);
+
+/* openpi/w4a8_plugin/src/w4a8_gemm_plugin.h:58-73: bf16 -> E4M3 values + E4M3 scale per 16 along K;
+ * bf16 [N, K] weight -> e2m1 packed TRANSPOSED [K/2, N] + E4M3 scales [K/16, N]. */
+void quantizeActivationToFP8(const void* input_bf16, void* output_fp8, void* scales_fp8, int M, int K,
+                             tpb200_stream_t stream);
+void quantizeWeightToNVFP4(const void* input_bf16, uint8_t* output_packed, void* scales_fp8, int N, int K,
+                           tpb200_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TURBOPI_B200_H_ */

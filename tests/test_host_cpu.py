@@ -1,0 +1,104 @@
+"""Host-side logic on CPU: packers against the oracle and the golden vectors, the
+C-ABI library's exports, and argument validation (no compute without a GPU)."""
+import ctypes
+import re
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import formats, int4, nvfp4
+from turbopi_b200 import _lib, nvfp4_packed, w4a16
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def test_library_exports_every_declared_symbol():
+    header = (ROOT / "include" / "turbopi_b200.h").read_text()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    declared = set(re.findall(r"\b(tpb200_\w+|nvfp4_gemv_\w+|quantize\w+|dequantize\w+|w4a16Gemm\w+|w4a8Gemm\w+|"
+                              r"getW4A\w+)\s*\(", header))
+    declared -= {"tpb200_status", "tpb200_stream_t", "tpb200_gemv_problem"}
+    assert declared, "no declarations found"
+    lib = ctypes.CDLL(str(_lib.LIB_PATH))
+    for name in sorted(declared):
+        assert hasattr(lib, name), f"{name} declared in include/turbopi_b200.h but not exported"
+    assert declared == set(_lib.SIGNATURES), (declared ^ set(_lib.SIGNATURES))
+    assert _lib.load().tpb200_version() >= 100
+
+
+def test_argument_validation_happens_on_the_host():
+    lib = _lib.load()
+    # NULL pointers, bad shapes, bad enums: rejected before any CUDA call
+    assert lib.tpb200_nvfp4_gemv(None, 2, None, None, None, 1, 16, 1.0, None, 0, None, 2, 1, 64, 64, 0, 0, None) == -1
+    assert lib.tpb200_nvfp4_gemv(16, 2, None, 16, 16, 1, 16, 1.0, None, 0, 16, 2, 17, 64, 64, 0, 0, None) == -2
+    assert lib.tpb200_nvfp4_gemv(16, 2, None, 16, 16, 1, 16, 1.0, None, 0, 16, 2, 1, 64, 48, 0, 0, None) == -2
+    assert lib.tpb200_nvfp4_gemv(16, 7, None, 16, 16, 1, 16, 1.0, None, 0, 16, 2, 1, 64, 64, 0, 0, None) == -4
+    assert lib.tpb200_nvfp4_gemv(16, 2, None, 8, 16, 1, 16, 1.0, None, 0, 16, 2, 1, 64, 64, 0, 0, None) == -3
+    assert lib.tpb200_w4a16_gemv(16, 1, 16, 16, 2, None, 0, 16, 0, 1, 64, 64, 32, 9, 0, None) == -4
+    assert lib.tpb200_w4a16_gemv(16, 1, 16, 16, 2, None, 0, 16, 0, 1, 64, 64, 64, 0, 0, None) == -2
+    lib.quantizeWeightToINT4(None, None, None, None, 4, 128, 128, None)
+    assert lib.tpb200_last_error() == -1 and lib.tpb200_last_error() == 0
+    assert b"NULL" in lib.tpb200_status_string(-1)
+
+
+def test_ops_refuse_cpu_tensors():
+    from turbopi_b200 import ops
+    x = torch.zeros(1, 64, dtype=torch.float16)
+    with pytest.raises(_lib.TurboPiError):
+        ops.w4a16_gemv(x, torch.zeros(2, 8, 4, dtype=torch.int32), torch.zeros(2, 8, dtype=torch.float16))
+    with pytest.raises(_lib.TurboPiError):
+        ops.nvfp4_gemv_v6(torch.zeros(1, 64), torch.zeros(8, 32, dtype=torch.uint8), torch.zeros(8, 2), None, 1, 8, 64, 0)
+
+
+def test_int4_packers_match_oracle_and_golden(golden):
+    g = golden("int4_packers")
+    w = torch.from_numpy(g["weight"])
+    fast = w4a16.W4A16PackerFast().pack(w)
+    assert fast.weight_packed.dtype == torch.int32 and fast.scales.dtype == torch.float16
+    assert np.array_equal(fast.weight_packed.numpy(), g["fast_packed"].astype(np.int32))
+    assert np.array_equal(fast.scales.numpy().view(np.uint16), g["fast_scales"].view(np.uint16))
+    basic = w4a16.W4A16Packer().pack(w)
+    assert np.array_equal(basic.weight_packed.numpy(), g["basic_packed"])
+    assert np.array_equal(basic.scales.numpy().view(np.uint16), g["basic_scales"].view(np.uint16))
+    assert np.array_equal(w4a16.W4A16Packer().unpack(basic).numpy(), g["basic_unpacked"])
+    words, scales = w4a16.W4A16PackerFast().pack_rowmajor(w, 128)
+    ow, os_ = int4.pack_fast(g["weight"], 128, "rowmajor")
+    assert np.array_equal(words.numpy(), ow) and np.array_equal(scales.numpy().view(np.uint16), os_.view(np.uint16))
+
+
+def test_int4_state_dict_roundtrip_and_autopack():
+    torch.manual_seed(0)
+    lin = torch.nn.Linear(64, 24, bias=True)
+    q = w4a16.W4A16Linear.from_linear(lin)
+    sd = q.state_dict()
+    assert set(sd) == {"weight_packed", "scales", "bias"}
+    q2 = w4a16.W4A16Linear(64, 24, bias=True)
+    q2.load_state_dict(sd)
+    assert torch.equal(q2.weight_packed, q.weight_packed) and torch.equal(q2.scales, q.scales)
+    q3 = w4a16.W4A16Linear(64, 24, bias=True)
+    q3.load_state_dict({"weight": lin.weight.data, "bias": lin.bias.data})      # unpacked weight: quantised on load
+    assert torch.equal(q3.weight_packed, q.weight_packed)
+    assert q.weight.dtype == torch.float16 and q.weight.shape == (24, 64)
+    assert (q.weight.float() - lin.weight).abs().max() < lin.weight.abs().max() / 7
+
+
+def test_nvfp4_packers_match_oracle_and_golden(golden):
+    g = golden("nvfp4_packed")
+    w = torch.from_numpy(g["weight"])
+    q, s = nvfp4_packed.quantize_to_nvfp4(w, 32)
+    assert np.array_equal(q.numpy(), g["quantized"]) and np.array_equal(s.numpy(), g["scales"])
+    p = nvfp4_packed.pack_nvfp4(q)
+    assert np.array_equal(p.numpy(), g["packed"])
+    assert np.array_equal(nvfp4_packed.unpack_nvfp4(p, 40, 128).numpy(), g["unpacked"])
+    rng = np.random.default_rng(5)
+    w2 = (rng.normal(size=(32, 256)) * 0.02).astype(np.float32)
+    w2[3, :16] = 0
+    pk, sc, gs = nvfp4_packed.quantize_nvfp4_two_level(torch.from_numpy(w2), 16)
+    opk, osc, ogs = nvfp4.quantize_two_level(w2, 16)
+    assert gs == float(ogs)
+    assert np.array_equal(sc.numpy(), osc)
+    assert np.array_equal(pk.numpy(), opk)
+    deq = nvfp4.dequantize(opk, osc, 16, ogs, scale_is_e4m3=True)
+    assert np.abs(deq - w2).max() < np.abs(w2).max() * 0.3

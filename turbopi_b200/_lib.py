@@ -1,0 +1,81 @@
+"""ctypes binding of libturbopi_b200.so (the C ABI declared in include/turbopi_b200.h).
+
+There is no fallback: if the library is missing or a call returns a non-zero
+status, an exception is raised.
+"""
+import ctypes
+from ctypes import c_char_p, c_float, c_int, c_size_t, c_void_p
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "lib" / "libturbopi_b200.so"
+
+F32, F16, BF16 = 0, 1, 2
+ACT_NONE, ACT_GELU, ACT_SILU = 0, 1, 2
+SCALE_F32, SCALE_E4M3, SCALE_F16, SCALE_BF16 = 0, 1, 2, 3
+INT4_KBLOCK, INT4_ROWMAJOR = 0, 1
+FLAG_NONE, FLAG_PDL = 0, 1
+MAX_GROUP = 64
+
+ACTIVATIONS = {"none": ACT_NONE, "gelu": ACT_GELU, "silu": ACT_SILU}
+
+
+class TurboPiError(RuntimeError):
+    pass
+
+
+class GemvProblem(ctypes.Structure):
+    _fields_ = [("x", c_void_p), ("weight_packed", c_void_p), ("weight_scales", c_void_p), ("bias", c_void_p),
+                ("out", c_void_p), ("N", c_int), ("K", c_int), ("global_scale", c_float), ("reserved", c_int)]
+
+
+# name -> (restype, argtypes); every symbol include/turbopi_b200.h declares
+SIGNATURES = {
+    "tpb200_version": (c_int, []),
+    "tpb200_status_string": (c_char_p, [c_int]),
+    "tpb200_last_error": (c_int, []),
+    "tpb200_device_error": (c_int, [c_int]),
+    "tpb200_w4a16_gemv": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int,
+                                  c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "tpb200_nvfp4_gemv": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p,
+                                  c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "tpb200_nvfp4_gemv_grouped": (c_int, [ctypes.POINTER(GemvProblem), c_int, c_int, c_int, c_int, c_int, c_int,
+                                          c_int, c_int, c_int, c_void_p]),
+    "nvfp4_gemv_forward": (None, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                  c_int, c_int, c_void_p]),
+    "nvfp4_gemv_workspace_size": (c_size_t, [c_int, c_int, c_int]),
+    "quantizeWeightToINT4": (None, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "dequantizeINT4ToBF16": (None, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "quantizeActivationToFP8": (None, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "quantizeWeightToNVFP4": (None, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
+}
+
+_lib = None
+
+
+def load():
+    """Load the shared library once and attach signatures."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise TurboPiError(
+            f"{LIB_PATH} is missing: build it with `python -m turbopi_b200.build` "
+            "(there is no CPU or PyTorch fallback for these kernels)")
+    lib = ctypes.CDLL(str(LIB_PATH))
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)      # AttributeError if the library does not export it
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def check(status, what):
+    if status != 0:
+        msg = load().tpb200_status_string(status).decode()
+        raise TurboPiError(f"{what}: {msg} (status {status})")
+
+
+def check_void(what):
+    """After a void-returning (reference-signature) entry point."""
+    check(load().tpb200_last_error(), what)

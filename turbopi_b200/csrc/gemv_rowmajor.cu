@@ -1,0 +1,553 @@
+// Decode-shaped (M <= 16) 4-bit weight-only GEMV for row-major packed weights
+// ([N, K/2] bytes): NVFP4 (e2m1 + block scales) and unsigned INT4 (zero point 8 +
+// group scales).
+//
+// HBM-bound design for B200:
+//   * persistent CTAs walk a list of row tiles; a tile (R consecutive rows = one
+//     contiguous byte range of the weight matrix, plus its scale rows) is fetched
+//     by ONE thread with 1-D bulk async copies into a 4-stage shared-memory ring
+//     and signalled through an mbarrier, so the bytes in flight per SM do not
+//     depend on registers or occupancy;
+//   * the first tiles are requested BEFORE griddepcontrol.wait, so under
+//     programmatic dependent launch the weight stream of kernel i+1 overlaps the
+//     tail of kernel i (weights never depend on the previous kernel);
+//   * activations live in registers as fp16 pairs; each lane owns fixed 32-wide K
+//     slices, reads its 16 bytes of codes per row with one conflict-free LDS.128,
+//     decodes in registers (cvt.rn.f16x2.e2m1x2 / magic-number int4), multiplies
+//     in packed fp16 over 4 products, then accumulates in fp32 with the block
+//     scale; rows are reduced with warp shuffles, K-parts (split K across warps
+//     for long rows) through shared memory in a fixed order (deterministic).
+#include <algorithm>
+#include <atomic>
+
+#include "common.cuh"
+
+namespace tpb {
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = 8;
+constexpr int kStages = 4;
+constexpr int kWStage = 16384;     // weight bytes per stage
+constexpr int kSStage = 4096;      // scale bytes per stage
+constexpr int kMaxTileRows = 64;
+constexpr int kMaxPartials = 256;  // rows * K-parts per tile
+
+enum { kFmtE2M1 = 0, kFmtU4 = 1 };
+// how the scales of one 32-code chunk are found
+enum {
+    kScE4M3B16 = 0,  // two E4M3 bytes per chunk
+    kScE4M3B32 = 1,  // one E4M3 byte per chunk
+    kScF32B16 = 2,   // two floats per chunk
+    kScF32B32 = 3,   // one float per chunk
+    kScF16Group = 4, // fp16, one per `group` codes (group % 32 == 0)
+    kScBF16Group = 5 // bf16, same
+};
+
+struct ProblemDev {
+    const uint8_t* w;
+    const uint8_t* scales;
+    const void* x;
+    const void* x_scales;
+    const void* bias;
+    void* out;
+    int N;
+    int K;
+    float global_scale;
+    int tile_begin;      // index of this problem's first tile in the launch-wide list
+    int rows_per_tile;   // multiple of (8 / kparts)
+    int kparts;          // warps along K: 1, 2, 4 or 8
+    int scale_row_bytes;
+    int scales_by_tma;   // 1: scale rows ride in the stage buffer, 0: read from global
+};
+
+template <int MAXP>
+struct GemvParams {
+    int num_problems;
+    int total_tiles;
+    int M;
+    int x_dtype;
+    int bias_dtype;
+    int out_dtype;
+    int activation;
+    int group;  // codes per scale
+    ProblemDev prob[MAXP];
+};
+
+__device__ __forceinline__ __half to_half_sat(float v) {
+    return __float2half_rn(fminf(fmaxf(v, -65504.0f), 65504.0f));
+}
+
+// Load the 32 activations of chunk j of row m into fp16 pairs ordered the way the
+// decoder of FMT produces weight pairs.
+template <int FMT>
+__device__ __forceinline__ void load_x_chunk(__half2 (&xr)[16], const void* x, const void* xs, int x_dtype,
+                                             size_t row_off, int j, int group, bool valid) {
+    float v[32];
+    if (!valid) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) xr[i] = __float2half2_rn(0.0f);
+        return;
+    }
+    const size_t e0 = row_off + static_cast<size_t>(j) * 32;
+    if (x_dtype == TPB200_F32) {
+        const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(x) + e0);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            float4 t = __ldg(p + i);
+            v[4 * i] = t.x; v[4 * i + 1] = t.y; v[4 * i + 2] = t.z; v[4 * i + 3] = t.w;
+        }
+    } else {
+        const uint4* p = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(x) + e0);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            uint4 t = __ldg(p + i);
+            const uint32_t u[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                float2 f;
+                if (x_dtype == TPB200_F16) {
+                    f = __half22float2(*reinterpret_cast<const __half2*>(&u[q]));
+                } else {
+                    f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u[q]));
+                }
+                v[8 * i + 2 * q] = f.x;
+                v[8 * i + 2 * q + 1] = f.y;
+            }
+        }
+    }
+    if (xs != nullptr) {  // per-block activation scales, dtype of x
+        const size_t per_row = row_off / group;  // row_off = m*K, K % group == 0
+        if (group == 16) {
+            float s0 = load_as_float(xs, x_dtype, per_row + 2 * static_cast<size_t>(j));
+            float s1 = load_as_float(xs, x_dtype, per_row + 2 * static_cast<size_t>(j) + 1);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) { v[i] *= s0; v[16 + i] *= s1; }
+        } else {
+            float s0 = load_as_float(xs, x_dtype, per_row + (static_cast<size_t>(j) * 32) / group);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] *= s0;
+        }
+    }
+    if (FMT == kFmtE2M1) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) xr[i] = __halves2half2(to_half_sat(v[2 * i]), to_half_sat(v[2 * i + 1]));
+    } else {
+#pragma unroll
+        for (int wd = 0; wd < 4; ++wd) {
+#pragma unroll
+            for (int p = 0; p < 4; ++p) {
+                xr[wd * 4 + p] = __halves2half2(to_half_sat(v[8 * wd + p]), to_half_sat(v[8 * wd + p + 4]));
+            }
+        }
+    }
+}
+
+template <int SCALE_MODE>
+__device__ __forceinline__ void load_chunk_scales(const uint8_t* sc_row, int j, int group, float& s0, float& s1) {
+    if (SCALE_MODE == kScE4M3B16) {
+        float2 f = decode_e4m3x2(*reinterpret_cast<const uint16_t*>(sc_row + 2 * j));
+        s0 = f.x; s1 = f.y;
+    } else if (SCALE_MODE == kScE4M3B32) {
+        s0 = s1 = decode_e4m3(sc_row[j]);
+    } else if (SCALE_MODE == kScF32B16) {
+        float2 f = *reinterpret_cast<const float2*>(sc_row + 8 * j);
+        s0 = f.x; s1 = f.y;
+    } else if (SCALE_MODE == kScF32B32) {
+        s0 = s1 = *reinterpret_cast<const float*>(sc_row + 4 * j);
+    } else if (SCALE_MODE == kScF16Group) {
+        s0 = s1 = __half2float(reinterpret_cast<const __half*>(sc_row)[(j * 32) / group]);
+    } else {
+        s0 = s1 = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(sc_row)[(j * 32) / group]);
+    }
+}
+
+// sum over 16 codes (two words) of code * x, packed fp16 products in two chains of
+// four, widened to fp32 at the end
+__device__ __forceinline__ float dot16(const __half2 (&ha)[4], const __half2 (&hb)[4], const __half2* x) {
+    __half2 a = __hmul2(ha[0], x[0]);
+    __half2 b = __hmul2(hb[0], x[4]);
+    a = __hfma2(ha[1], x[1], a);
+    b = __hfma2(hb[1], x[5], b);
+    a = __hfma2(ha[2], x[2], a);
+    b = __hfma2(hb[2], x[6], b);
+    a = __hfma2(ha[3], x[3], a);
+    b = __hfma2(hb[3], x[7], b);
+    float2 fa = __half22float2(a);
+    float2 fb = __half22float2(b);
+    return (fa.x + fa.y) + (fb.x + fb.y);
+}
+
+template <int FMT, int SCALE_MODE, int M_TILE, int CPL, int MAXP>
+__global__ void __launch_bounds__(kThreads, 2) gemv_rowmajor_kernel(const __grid_constant__ GemvParams<MAXP> P) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint8_t* wst = smem;
+    uint8_t* sst = smem + kStages * kWStage;
+    float* part = reinterpret_cast<float*>(sst + kStages * kSStage);
+    uint64_t* full = reinterpret_cast<uint64_t*>(part + 2 * kMaxPartials * M_TILE);
+    int* abort_flag = reinterpret_cast<int*>(full + kStages);
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const int total_tiles = P.total_tiles;
+    const int m0 = blockIdx.y * M_TILE;
+    const int group = P.group;
+
+    if (tid == 0) {
+#pragma unroll
+        for (int s = 0; s < kStages; ++s) mbar_init(&full[s], 1);
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    __syncthreads();
+
+    // Producer (thread 0): request tile number `it` of this CTA.
+    auto issue = [&](int it) {
+        const int tile = blockIdx.x + it * gridDim.x;
+        if (tile >= total_tiles) return;
+        int p = 0;
+        while (p + 1 < P.num_problems && tile >= P.prob[p + 1].tile_begin) ++p;
+        const ProblemDev& pr = P.prob[p];
+        const int row0 = (tile - pr.tile_begin) * pr.rows_per_tile;
+        const int rows = min(pr.rows_per_tile, pr.N - row0);
+        const int row_bytes = pr.K >> 1;
+        const int s = it % kStages;
+        const uint32_t wbytes = static_cast<uint32_t>(rows) * row_bytes;
+        const uint32_t sbytes = pr.scales_by_tma ? static_cast<uint32_t>(rows) * pr.scale_row_bytes : 0u;
+        mbar_expect_tx(&full[s], wbytes + sbytes);
+        bulk_copy_g2s(wst + s * kWStage, pr.w + static_cast<size_t>(row0) * row_bytes, wbytes, &full[s]);
+        if (sbytes) {
+            bulk_copy_g2s(sst + s * kSStage, pr.scales + static_cast<size_t>(row0) * pr.scale_row_bytes, sbytes,
+                          &full[s]);
+        }
+    };
+    if (tid == 0) {
+#pragma unroll
+        for (int it = 0; it < kStages; ++it) issue(it);
+    }
+    // Weights are in flight; let the next kernel start its own prefetch, then wait
+    // for whatever produced our activations (and last read our output buffer).
+    pdl_launch_dependents();
+    pdl_wait_prior_grids();
+
+    __half2 xr[M_TILE][CPL][16];
+    int p = 0, cur_p = -1;
+    int KP = 1, kp = 0, rw = 0, RW = kWarps, nchunks = 0;
+
+    for (int it = 0;; ++it) {
+        const int tile = blockIdx.x + it * gridDim.x;
+        if (tile >= total_tiles) break;
+        while (p + 1 < P.num_problems && tile >= P.prob[p + 1].tile_begin) ++p;
+        const ProblemDev& pr = P.prob[p];
+        if (p != cur_p) {
+            cur_p = p;
+            KP = pr.kparts;
+            RW = kWarps / KP;
+            kp = warp % KP;
+            rw = warp / KP;
+            nchunks = pr.K >> 5;
+#pragma unroll
+            for (int m = 0; m < M_TILE; ++m) {
+#pragma unroll
+                for (int c = 0; c < CPL; ++c) {
+                    const int j = (kp * CPL + c) * 32 + lane;
+                    load_x_chunk<FMT>(xr[m][c], pr.x, pr.x_scales, P.x_dtype,
+                                      static_cast<size_t>(m0 + m) * pr.K, j, group,
+                                      (j < nchunks) && (m0 + m < P.M));
+                }
+            }
+        }
+        const int row0 = (tile - pr.tile_begin) * pr.rows_per_tile;
+        const int rows = min(pr.rows_per_tile, pr.N - row0);
+        const int row_bytes = pr.K >> 1;
+        const int s = it % kStages;
+        if (!mbar_wait_bounded(&full[s], (it / kStages) & 1)) {
+            record_error(kErrGemvFullBarrierTimeout);
+            *abort_flag = 1;
+        }
+        const uint8_t* wt = wst + s * kWStage;
+        const uint8_t* sc = pr.scales_by_tma ? (sst + s * kSStage)
+                                             : (pr.scales + static_cast<size_t>(row0) * pr.scale_row_bytes);
+        float* pt = part + (it & 1) * kMaxPartials * M_TILE;
+
+        for (int r = rw; r < rows; r += RW) {
+            float acc[M_TILE];
+#pragma unroll
+            for (int m = 0; m < M_TILE; ++m) acc[m] = 0.0f;
+#pragma unroll
+            for (int c = 0; c < CPL; ++c) {
+                const int j = (kp * CPL + c) * 32 + lane;
+                if (j < nchunks) {
+                    const uint4 w = *reinterpret_cast<const uint4*>(wt + r * row_bytes + j * 16);
+                    float s0, s1;
+                    load_chunk_scales<SCALE_MODE>(sc + static_cast<size_t>(r) * pr.scale_row_bytes, j, group, s0, s1);
+                    __half2 h0[4], h1[4], h2[4], h3[4];
+                    if (FMT == kFmtE2M1) {
+                        decode_e2m1x8(w.x, h0); decode_e2m1x8(w.y, h1);
+                        decode_e2m1x8(w.z, h2); decode_e2m1x8(w.w, h3);
+                    } else {
+                        decode_u4x8_minus8(w.x, h0); decode_u4x8_minus8(w.y, h1);
+                        decode_u4x8_minus8(w.z, h2); decode_u4x8_minus8(w.w, h3);
+                    }
+#pragma unroll
+                    for (int m = 0; m < M_TILE; ++m) {
+                        const float d0 = dot16(h0, h1, &xr[m][c][0]);
+                        const float d1 = dot16(h2, h3, &xr[m][c][8]);
+                        acc[m] = fmaf(d0, s0, acc[m]);
+                        acc[m] = fmaf(d1, s1, acc[m]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int m = 0; m < M_TILE; ++m) acc[m] = warp_sum(acc[m]);
+            if (lane == 0) {
+#pragma unroll
+                for (int m = 0; m < M_TILE; ++m) pt[(r * KP + kp) * M_TILE + m] = acc[m];
+            }
+        }
+        __syncthreads();  // partial sums visible; every thread is done with stage s
+        if (*abort_flag) break;
+        if (tid == 0) issue(it + kStages);
+        if (tid < rows * M_TILE) {
+            const int m = tid / rows;
+            const int r = tid - m * rows;
+            if (m0 + m < P.M) {
+                float v = 0.0f;
+                for (int q = 0; q < KP; ++q) v += pt[(r * KP + q) * M_TILE + m];
+                v *= pr.global_scale;
+                if (pr.bias != nullptr) v += load_as_float(pr.bias, P.bias_dtype, row0 + r);
+                v = apply_activation(v, P.activation);
+                store_from_float(pr.out, P.out_dtype, static_cast<size_t>(m0 + m) * pr.N + row0 + r, v);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+struct HostProblem {
+    const void* x;
+    const void* x_scales;
+    const void* w;
+    const void* scales;
+    const void* bias;
+    void* out;
+    int N, K;
+    float global_scale;
+};
+
+struct Plan {
+    int m_tile, cpl, kparts;
+};
+
+// Choose the M tile, K-parts and chunk columns per lane for the LARGEST K of the launch
+// (M_TILE * CPL <= 4 keeps the activation registers within 64).
+bool make_plan(int M, int maxK, Plan& plan) {
+    int m_tile = M >= 3 ? 4 : M;
+    const int nchunks = maxK / 32;
+    while (m_tile >= 1) {
+        const int cplmax = 4 / m_tile;
+        int kparts = 1;
+        while ((nchunks + 32 * kparts - 1) / (32 * kparts) > cplmax && kparts < 8) kparts *= 2;
+        const int need = (nchunks + 32 * kparts - 1) / (32 * kparts);
+        if (need <= cplmax) {
+            plan.m_tile = m_tile;
+            plan.cpl = need <= 1 ? 1 : (need <= 2 ? 2 : 4);
+            plan.kparts = kparts;
+            return true;
+        }
+        m_tile /= 2;
+    }
+    return false;
+}
+
+template <int FMT, int SCALE_MODE, int M_TILE, int CPL, int MAXP>
+int launch_instance(const GemvParams<MAXP>& P, int grid_x, int grid_y, int flags, cudaStream_t stream) {
+    auto kernel = gemv_rowmajor_kernel<FMT, SCALE_MODE, M_TILE, CPL, MAXP>;
+    const size_t smem = kStages * (kWStage + kSStage) + 2 * kMaxPartials * M_TILE * sizeof(float) +
+                        kStages * sizeof(uint64_t) + 16;
+    static std::atomic<uint64_t> configured{0};  // bit d: attribute set on device d
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return TPB200_ERR_CUDA;
+    const uint64_t bit = 1ull << (dev & 63);
+    if (!(configured.load(std::memory_order_relaxed) & bit)) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
+            cudaSuccess) {
+            return TPB200_ERR_CUDA;
+        }
+        configured.fetch_or(bit, std::memory_order_relaxed);
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid_x, grid_y, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    if (flags & TPB200_FLAG_PDL) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    if (cudaLaunchKernelEx(&cfg, kernel, P) != cudaSuccess) return TPB200_ERR_CUDA;
+    return TPB200_OK;
+}
+
+template <int FMT, int SCALE_MODE, int MAXP>
+int dispatch_tiles(const GemvParams<MAXP>& P, const Plan& plan, int grid_x, int grid_y, int flags,
+                   cudaStream_t stream) {
+#define TPB_CASE(MT, C)                              \
+    if (plan.m_tile == MT && plan.cpl == C)          \
+        return launch_instance<FMT, SCALE_MODE, MT, C, MAXP>(P, grid_x, grid_y, flags, stream);
+    TPB_CASE(1, 1) TPB_CASE(1, 2) TPB_CASE(1, 4) TPB_CASE(2, 1) TPB_CASE(2, 2) TPB_CASE(4, 1)
+#undef TPB_CASE
+    return TPB200_ERR_SHAPE;
+}
+
+template <int MAXP>
+int run_gemv(int fmt, const HostProblem* probs, int count, int x_dtype, int scale_dtype, int group,
+             int bias_dtype, int out_dtype, int M, int activation, int flags, cudaStream_t stream) {
+    TPB_REQUIRE(probs != nullptr, TPB200_ERR_NULL);
+    TPB_REQUIRE(count >= 1 && count <= MAXP, TPB200_ERR_SHAPE);
+    TPB_REQUIRE(M >= 1 && M <= 16, TPB200_ERR_SHAPE);
+    TPB_REQUIRE(tpb_valid_dtype(x_dtype) && tpb_valid_dtype(out_dtype) && tpb_valid_dtype(bias_dtype),
+                TPB200_ERR_ENUM);
+    TPB_REQUIRE(activation >= TPB200_ACT_NONE && activation <= TPB200_ACT_SILU, TPB200_ERR_ENUM);
+    TPB_REQUIRE((flags & ~TPB200_FLAG_PDL) == 0, TPB200_ERR_ENUM);
+    int scale_mode, scale_bytes;
+    if (fmt == kFmtE2M1) {
+        TPB_REQUIRE(group == 16 || group == 32, TPB200_ERR_SHAPE);
+        if (scale_dtype == TPB200_SCALE_E4M3) {
+            scale_mode = group == 16 ? kScE4M3B16 : kScE4M3B32;
+            scale_bytes = 1;
+        } else if (scale_dtype == TPB200_SCALE_F32) {
+            scale_mode = group == 16 ? kScF32B16 : kScF32B32;
+            scale_bytes = 4;
+        } else {
+            return TPB200_ERR_ENUM;
+        }
+    } else {
+        TPB_REQUIRE(group >= 32 && group % 32 == 0, TPB200_ERR_SHAPE);
+        if (scale_dtype == TPB200_SCALE_F16) scale_mode = kScF16Group;
+        else if (scale_dtype == TPB200_SCALE_BF16) scale_mode = kScBF16Group;
+        else return TPB200_ERR_ENUM;
+        scale_bytes = 2;
+    }
+
+    int maxK = 0;
+    for (int i = 0; i < count; ++i) {
+        const HostProblem& h = probs[i];
+        TPB_REQUIRE(h.x && h.w && h.scales && h.out, TPB200_ERR_NULL);
+        TPB_REQUIRE(h.N >= 1 && h.K >= 32 && h.K % 32 == 0 && h.K % group == 0, TPB200_ERR_SHAPE);
+        TPB_REQUIRE(tpb_aligned16(h.x) && tpb_aligned16(h.w) && tpb_aligned16(h.scales) && tpb_aligned16(h.out),
+                    TPB200_ERR_ALIGN);
+        maxK = std::max(maxK, h.K);
+    }
+    Plan plan;
+    TPB_REQUIRE(make_plan(M, maxK, plan), TPB200_ERR_SHAPE);
+
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+        return TPB200_ERR_CUDA;
+    }
+
+    GemvParams<MAXP> P;
+    P.num_problems = count;
+    P.M = M;
+    P.x_dtype = x_dtype;
+    P.bias_dtype = bias_dtype;
+    P.out_dtype = out_dtype;
+    P.activation = activation;
+    P.group = group;
+    int tiles = 0;
+    for (int i = 0; i < count; ++i) {
+        const HostProblem& h = probs[i];
+        ProblemDev& d = P.prob[i];
+        d.w = static_cast<const uint8_t*>(h.w);
+        d.scales = static_cast<const uint8_t*>(h.scales);
+        d.x = h.x;
+        d.x_scales = h.x_scales;
+        d.bias = h.bias;
+        d.out = h.out;
+        d.N = h.N;
+        d.K = h.K;
+        d.global_scale = h.global_scale;
+        // K-parts for THIS problem under the launch-wide CPL
+        const int nchunks = h.K / 32;
+        int kparts = 1;
+        while ((nchunks + 32 * kparts - 1) / (32 * kparts) > plan.cpl && kparts < 8) kparts *= 2;
+        d.kparts = kparts;
+        const int rw = kWarps / kparts;
+        const int row_bytes = h.K / 2;
+        d.scale_row_bytes = (h.K / group) * scale_bytes;
+        int rmax = std::min({kMaxTileRows, kWStage / row_bytes, kMaxPartials / kparts});
+        rmax = std::max(rw, rmax / rw * rw);
+        TPB_REQUIRE(rmax * row_bytes <= kWStage, TPB200_ERR_SHAPE);
+        // aim for at least two tiles per SM so that every SM streams, but keep tiles >= one row per warp
+        int target = (h.N / (2 * sms)) / rw * rw;
+        int R = std::min(rmax, std::max(rw, target));
+        d.scales_by_tma = (d.scale_row_bytes % 16 == 0) && (R * d.scale_row_bytes <= kSStage) ? 1 : 0;
+        d.rows_per_tile = R;
+        d.tile_begin = tiles;
+        tiles += (h.N + R - 1) / R;
+    }
+    P.total_tiles = tiles;
+    const int grid_x = std::min(tiles, 2 * sms);
+    const int grid_y = (M + plan.m_tile - 1) / plan.m_tile;
+
+#define TPB_MODE(F, S) \
+    if (fmt == F && scale_mode == S) return dispatch_tiles<F, S, MAXP>(P, plan, grid_x, grid_y, flags, stream);
+    TPB_MODE(kFmtE2M1, kScE4M3B16)
+    TPB_MODE(kFmtE2M1, kScF32B32)
+    if (MAXP == 1) {
+        TPB_MODE(kFmtE2M1, kScE4M3B32)
+        TPB_MODE(kFmtE2M1, kScF32B16)
+        TPB_MODE(kFmtU4, kScF16Group)
+        TPB_MODE(kFmtU4, kScBF16Group)
+    }
+#undef TPB_MODE
+    return TPB200_ERR_ENUM;
+}
+
+}  // namespace
+
+int gemv_rowmajor_single(int fmt_is_u4, const void* x, int x_dtype, const void* x_scales, const void* w,
+                         const void* scales, int scale_dtype, int group, float global_scale, const void* bias,
+                         int bias_dtype, void* out, int out_dtype, int M, int N, int K, int activation, int flags,
+                         cudaStream_t stream) {
+    HostProblem h{x, x_scales, w, scales, bias, out, N, K, global_scale};
+    return run_gemv<1>(fmt_is_u4 ? kFmtU4 : kFmtE2M1, &h, 1, x_dtype, scale_dtype, group, bias_dtype, out_dtype, M,
+                       activation, flags, stream);
+}
+
+int device_error_gemv_rowmajor(int clear) { return read_device_error(clear); }
+
+}  // namespace tpb
+
+extern "C" int tpb200_nvfp4_gemv(const void* x, int x_dtype, const void* x_scales, const void* weight_packed,
+                                 const void* weight_scales, int scale_dtype, int block_size, float global_scale,
+                                 const void* bias, int bias_dtype, void* out, int out_dtype, int M, int N, int K,
+                                 int activation, int flags, tpb200_stream_t stream) {
+    return tpb::gemv_rowmajor_single(0, x, x_dtype, x_scales, weight_packed, weight_scales, scale_dtype, block_size,
+                                     global_scale, bias, bias_dtype, out, out_dtype, M, N, K, activation, flags,
+                                     reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int tpb200_nvfp4_gemv_grouped(const tpb200_gemv_problem* problems, int count, int x_dtype,
+                                         int scale_dtype, int block_size, int bias_dtype, int out_dtype, int M,
+                                         int activation, int flags, tpb200_stream_t stream) {
+    TPB_REQUIRE(problems != nullptr, TPB200_ERR_NULL);
+    TPB_REQUIRE(count >= 1 && count <= TPB200_MAX_GROUP, TPB200_ERR_SHAPE);
+    tpb::HostProblem h[TPB200_MAX_GROUP];
+    for (int i = 0; i < count; ++i) {
+        h[i] = tpb::HostProblem{problems[i].x, nullptr, problems[i].weight_packed, problems[i].weight_scales,
+                                problems[i].bias, problems[i].out, problems[i].N, problems[i].K,
+                                problems[i].global_scale};
+    }
+    return tpb::run_gemv<TPB200_MAX_GROUP>(tpb::kFmtE2M1, h, count, x_dtype, scale_dtype, block_size, bias_dtype,
+                                           out_dtype, M, activation, flags, reinterpret_cast<cudaStream_t>(stream));
+}

@@ -1,0 +1,279 @@
+// Quantiser / dequantiser kernels behind the plugin ABI:
+//   quantizeWeightToINT4, dequantizeINT4ToBF16   (w4a16 plugin)
+//   quantizeActivationToFP8, quantizeWeightToNVFP4 (w4a8 plugin)
+// All are streaming, HBM-bound element-wise passes: one thread owns one scale block,
+// reads it with 128-bit loads and writes packed results with the widest store the
+// output layout allows.
+#include "common.cuh"
+
+namespace tpb {
+namespace {
+
+__device__ __forceinline__ void unpack_bf16x8(const uint4& v, float (&f)[8]) {
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float2 t = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u[i]));
+        f[2 * i] = t.x;
+        f[2 * i + 1] = t.y;
+    }
+}
+
+// index of the nearest e2m1 magnitude {0,.5,1,1.5,2,3,4,6}; an exact midpoint goes to the
+// lower magnitude, as a strict-less-than scan over the table does
+__device__ __forceinline__ uint32_t e2m1_index(float a) {
+    return (a > 0.25f) + (a > 0.75f) + (a > 1.25f) + (a > 1.75f) + (a > 2.5f) + (a > 3.5f) + (a > 5.0f);
+}
+
+// ------------------------------------------------------------------ INT4, one warp per (row, group)
+__global__ void int4_quantize_kernel(const __nv_bfloat16* __restrict__ in, int8_t* __restrict__ packed,
+                                     __nv_bfloat16* __restrict__ scales, __nv_bfloat16* __restrict__ zeros, int N,
+                                     int K, int group) {
+    const int groups_per_row = K / group;
+    const long long gid = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (gid >= static_cast<long long>(N) * groups_per_row) return;
+    const int n = static_cast<int>(gid / groups_per_row);
+    const int g = static_cast<int>(gid % groups_per_row);
+    const __nv_bfloat16* src = in + static_cast<size_t>(n) * K + static_cast<size_t>(g) * group;
+    float amax = 0.0f;
+    for (int i = lane * 2; i < group; i += 64) {
+        float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + i));
+        amax = fmaxf(amax, fmaxf(fabsf(v.x), fabsf(v.y)));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float scale = amax / 7.0f + 1e-12f;
+    if (lane == 0) {
+        scales[gid] = __float2bfloat16_rn(scale);
+        if (zeros != nullptr) zeros[gid] = __float2bfloat16_rn(0.0f);
+    }
+    int8_t* dst = packed + (static_cast<size_t>(n) * K + static_cast<size_t>(g) * group) / 2;
+    for (int i = lane * 2; i < group; i += 64) {
+        float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + i));
+        const int q0 = static_cast<int>(fmaxf(-8.0f, fminf(7.0f, roundf(__fdiv_rn(v.x, scale)))));
+        const int q1 = static_cast<int>(fmaxf(-8.0f, fminf(7.0f, roundf(__fdiv_rn(v.y, scale)))));
+        dst[i >> 1] = static_cast<int8_t>((q0 & 0xF) | ((q1 & 0xF) << 4));
+    }
+}
+
+// one thread per 8 outputs (4 packed bytes)
+__global__ void int4_dequantize_kernel(const int8_t* __restrict__ packed, const __nv_bfloat16* __restrict__ scales,
+                                       const __nv_bfloat16* __restrict__ zeros, __nv_bfloat16* __restrict__ out,
+                                       int N, int K, int group) {
+    const long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const long long total = static_cast<long long>(N) * K / 8;
+    if (t >= total) return;
+    const long long e = t * 8;
+    const int n = static_cast<int>(e / K);
+    const int k = static_cast<int>(e % K);
+    const uint32_t w = *reinterpret_cast<const uint32_t*>(packed + e / 2);
+    const size_t sidx = static_cast<size_t>(n) * (K / group) + k / group;   // group % 8 == 0
+    const float s = __bfloat162float(scales[sidx]);
+    const float z = zeros != nullptr ? __bfloat162float(zeros[sidx]) : 0.0f;
+    uint32_t o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int q0 = (static_cast<int>(w << (28 - 8 * i))) >> 28;       // sign-extended low nibble of byte i
+        const int q1 = (static_cast<int>(w << (24 - 8 * i))) >> 28;       // high nibble
+        __nv_bfloat162 v = __floats2bfloat162_rn(fmaf(static_cast<float>(q0), s, z), fmaf(static_cast<float>(q1), s, z));
+        o[i] = *reinterpret_cast<uint32_t*>(&v);
+    }
+    *reinterpret_cast<uint4*>(out + e) = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// ------------------------------------------------------------------ FP8 activations, one thread per 16-block
+__global__ void fp8_quantize_act_kernel(const __nv_bfloat16* __restrict__ in, uint8_t* __restrict__ out,
+                                        uint8_t* __restrict__ scales, long long nblocks) {
+    const long long b = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (b >= nblocks) return;
+    const uint4* src = reinterpret_cast<const uint4*>(in + b * 16);
+    float f[16];
+    {
+        float lo[8], hi[8];
+        unpack_bf16x8(__ldg(src), lo);
+        unpack_bf16x8(__ldg(src + 1), hi);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { f[i] = lo[i]; f[8 + i] = hi[i]; }
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(f[i]));
+    const float scale = amax / 448.0f + 1e-12f;
+    scales[b] = encode_e4m3(scale);
+    uint32_t o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint32_t word = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            float v = __fdiv_rn(f[4 * i + j], scale);
+            v = fminf(fmaxf(v, -448.0f), 448.0f);
+            word |= static_cast<uint32_t>(encode_e4m3(v)) << (8 * j);
+        }
+        o[i] = word;
+    }
+    *reinterpret_cast<uint4*>(out + b * 16) = make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// ------------------------------------------------------------------ NVFP4 weights, transposed output
+// thread t -> (block kb = t / N, column n = t % N): consecutive threads write consecutive bytes of the
+// [K/2, N] and [K/16, N] outputs
+__global__ void nvfp4_quantize_weight_t_kernel(const __nv_bfloat16* __restrict__ in, uint8_t* __restrict__ packed_t,
+                                               uint8_t* __restrict__ scales_t, int N, int K) {
+    const long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const long long total = static_cast<long long>(N) * (K / 16);
+    if (t >= total) return;
+    const int kb = static_cast<int>(t / N);
+    const int n = static_cast<int>(t % N);
+    const uint4* src = reinterpret_cast<const uint4*>(in + static_cast<size_t>(n) * K + static_cast<size_t>(kb) * 16);
+    float f[16];
+    {
+        float lo[8], hi[8];
+        unpack_bf16x8(__ldg(src), lo);
+        unpack_bf16x8(__ldg(src + 1), hi);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) { f[i] = lo[i]; f[8 + i] = hi[i]; }
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(f[i]));
+    const float scale = amax / 6.0f + 1e-12f;
+    scales_t[static_cast<size_t>(kb) * N + n] = encode_e4m3(scale);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float a = __fdiv_rn(f[2 * i], scale);
+        const float b = __fdiv_rn(f[2 * i + 1], scale);
+        const uint32_t ca = e2m1_index(fabsf(a)) | (a < 0.0f ? 8u : 0u);
+        const uint32_t cb = e2m1_index(fabsf(b)) | (b < 0.0f ? 8u : 0u);
+        packed_t[(static_cast<size_t>(kb) * 8 + i) * N + n] = static_cast<uint8_t>(ca | (cb << 4));
+    }
+}
+
+thread_local int t_last_error = TPB200_OK;
+
+}  // namespace
+
+void set_last_error(int status) {
+    if (status != TPB200_OK) t_last_error = status;
+}
+
+int gemv_rowmajor_single(int fmt_is_u4, const void* x, int x_dtype, const void* x_scales, const void* w,
+                         const void* scales, int scale_dtype, int group, float global_scale, const void* bias,
+                         int bias_dtype, void* out, int out_dtype, int M, int N, int K, int activation, int flags,
+                         cudaStream_t stream);
+int device_error_gemv_rowmajor(int clear);
+int device_error_w4a16_kblock(int clear);
+
+}  // namespace tpb
+
+extern "C" {
+
+int tpb200_version(void) { return 100; }
+
+const char* tpb200_status_string(int status) {
+    switch (status) {
+        case TPB200_OK: return "ok";
+        case TPB200_ERR_NULL: return "a required pointer is NULL";
+        case TPB200_ERR_SHAPE: return "a dimension is out of the supported range";
+        case TPB200_ERR_ALIGN: return "a pointer or row pitch is not 16-byte aligned";
+        case TPB200_ERR_ENUM: return "unknown dtype, layout, activation or flag";
+        case TPB200_ERR_CUDA: return "the CUDA runtime refused the launch";
+        case TPB200_ERR_WORKSPACE: return "workspace missing or too small";
+        case TPB200_ERR_DEVICE: return "a kernel gave up on a bounded wait";
+        default: return "unknown status";
+    }
+}
+
+int tpb200_last_error(void) {
+    const int e = tpb::t_last_error;
+    tpb::t_last_error = TPB200_OK;
+    return e;
+}
+
+int tpb200_device_error(int clear) {
+    if (cudaDeviceSynchronize() != cudaSuccess) return TPB200_ERR_CUDA;
+    int (*const readers[])(int) = {tpb::device_error_gemv_rowmajor, tpb::device_error_w4a16_kblock};
+    int first = 0;
+    for (auto r : readers) {
+        const int v = r(clear);
+        if (v != 0 && first == 0) first = v;
+    }
+    return first;
+}
+
+void quantizeWeightToINT4(const void* input_bf16, int8_t* output_packed, void* scales_bf16, void* zeros_bf16, int N,
+                          int K, int group_size, tpb200_stream_t stream) {
+    if (!input_bf16 || !output_packed || !scales_bf16) return tpb::set_last_error(TPB200_ERR_NULL);
+    if (N < 1 || K < 2 || group_size < 2 || group_size % 2 != 0 || K % group_size != 0)
+        return tpb::set_last_error(TPB200_ERR_SHAPE);
+    const long long warps = static_cast<long long>(N) * (K / group_size);
+    const int threads = 256;
+    const long long blocks = (warps * 32 + threads - 1) / threads;
+    tpb::int4_quantize_kernel<<<static_cast<unsigned>(blocks), threads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(input_bf16), output_packed, static_cast<__nv_bfloat16*>(scales_bf16),
+        static_cast<__nv_bfloat16*>(zeros_bf16), N, K, group_size);
+    tpb::set_last_error(tpb_launch_status());
+}
+
+void dequantizeINT4ToBF16(const int8_t* input_packed, const void* scales_bf16, const void* zeros_bf16,
+                          void* output_bf16, int N, int K, int group_size, tpb200_stream_t stream) {
+    if (!input_packed || !scales_bf16 || !output_bf16) return tpb::set_last_error(TPB200_ERR_NULL);
+    if (N < 1 || K < 8 || K % 8 != 0 || group_size % 8 != 0 || K % group_size != 0)
+        return tpb::set_last_error(TPB200_ERR_SHAPE);
+    if (!tpb_aligned16(output_bf16) || (reinterpret_cast<uintptr_t>(input_packed) & 3u))
+        return tpb::set_last_error(TPB200_ERR_ALIGN);
+    const long long total = static_cast<long long>(N) * K / 8;
+    const int threads = 256;
+    tpb::int4_dequantize_kernel<<<static_cast<unsigned>((total + threads - 1) / threads), threads, 0,
+                                  reinterpret_cast<cudaStream_t>(stream)>>>(
+        input_packed, static_cast<const __nv_bfloat16*>(scales_bf16), static_cast<const __nv_bfloat16*>(zeros_bf16),
+        static_cast<__nv_bfloat16*>(output_bf16), N, K, group_size);
+    tpb::set_last_error(tpb_launch_status());
+}
+
+void quantizeActivationToFP8(const void* input_bf16, void* output_fp8, void* scales_fp8, int M, int K,
+                             tpb200_stream_t stream) {
+    if (!input_bf16 || !output_fp8 || !scales_fp8) return tpb::set_last_error(TPB200_ERR_NULL);
+    if (M < 1 || K < 16 || K % 16 != 0) return tpb::set_last_error(TPB200_ERR_SHAPE);
+    if (!tpb_aligned16(input_bf16) || !tpb_aligned16(output_fp8)) return tpb::set_last_error(TPB200_ERR_ALIGN);
+    const long long nblocks = static_cast<long long>(M) * (K / 16);
+    const int threads = 256;
+    tpb::fp8_quantize_act_kernel<<<static_cast<unsigned>((nblocks + threads - 1) / threads), threads, 0,
+                                   reinterpret_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(input_bf16), static_cast<uint8_t*>(output_fp8),
+        static_cast<uint8_t*>(scales_fp8), nblocks);
+    tpb::set_last_error(tpb_launch_status());
+}
+
+void quantizeWeightToNVFP4(const void* input_bf16, uint8_t* output_packed, void* scales_fp8, int N, int K,
+                           tpb200_stream_t stream) {
+    if (!input_bf16 || !output_packed || !scales_fp8) return tpb::set_last_error(TPB200_ERR_NULL);
+    if (N < 1 || K < 16 || K % 16 != 0) return tpb::set_last_error(TPB200_ERR_SHAPE);
+    if (!tpb_aligned16(input_bf16)) return tpb::set_last_error(TPB200_ERR_ALIGN);
+    const long long total = static_cast<long long>(N) * (K / 16);
+    const int threads = 256;
+    tpb::nvfp4_quantize_weight_t_kernel<<<static_cast<unsigned>((total + threads - 1) / threads), threads, 0,
+                                          reinterpret_cast<cudaStream_t>(stream)>>>(
+        static_cast<const __nv_bfloat16*>(input_bf16), output_packed, static_cast<uint8_t*>(scales_fp8), N, K);
+    tpb::set_last_error(tpb_launch_status());
+}
+
+// openpi/nvfp4_packed_plugin/src/nvfp4_packed_kernel.cu:419-504: block 32, every tensor in `data_type`,
+// activation scales optional, bias + activation fused (the reference fuses them for fp32 only; here
+// for every dtype).
+void nvfp4_gemv_forward(const void* activation, const void* weight_packed, const void* scale_A, const void* scale_W,
+                        const void* bias, void* output, int M, int N, int K, int activation_type, int data_type,
+                        tpb200_stream_t stream) {
+    // scales arrive in the tensor dtype; the kernel takes fp32 or E4M3 block scales, so only fp32 scale
+    // tensors are accepted here (the reference's python always passes fp32 scales)
+    if (data_type != TPB200_F32) return tpb::set_last_error(TPB200_ERR_ENUM);
+    const int st = tpb::gemv_rowmajor_single(0, activation, data_type, scale_A, weight_packed, scale_W,
+                                             TPB200_SCALE_F32, 32, 1.0f, bias, data_type, output, data_type, M, N, K,
+                                             activation_type, TPB200_FLAG_NONE, reinterpret_cast<cudaStream_t>(stream));
+    tpb::set_last_error(st);
+}
+
+size_t nvfp4_gemv_workspace_size(int, int, int) { return 0; }
+
+}  // extern "C"

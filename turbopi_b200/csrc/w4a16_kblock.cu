@@ -1,0 +1,268 @@
+// W4A16 INT4 GEMV for the reference packer's block-interleaved layout:
+// weights (K/32, N, 4) int32 -- the 16 bytes of output n's 32-code block qb sit at
+// ((qb * N) + n) * 16 -- and fp16 scales (K/32, N).
+//
+// In this layout consecutive outputs are contiguous for a fixed K block, so a lane
+// owns an OUTPUT (no shuffle reduction): a CTA takes 64 outputs, streams their K
+// blocks through a 4-stage shared-memory ring (16 K-blocks x 64 outputs x 16 B per
+// stage, one bulk async copy per K-block row), and four thread groups split each
+// stage's K blocks; their partial sums meet in shared memory in a fixed order.
+// Activations are staged once per CTA in shared memory as fp16 pairs in the order
+// the int4 decoder emits (k, k+4) and are read as warp-wide broadcasts.
+#include <algorithm>
+#include <atomic>
+
+#include "common.cuh"
+
+namespace tpb {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kNT = 64;       // outputs per tile
+constexpr int kQT = 16;       // K blocks per stage
+constexpr int kStages = 4;
+constexpr int kParts = kThreads / kNT;  // 4 thread groups along K
+constexpr int kWStage = kQT * kNT * 16;
+constexpr int kSStage = kQT * kNT * 2;
+
+struct KBlockParams {
+    const uint8_t* w;
+    const __half* scales;
+    const void* x;
+    const void* bias;
+    void* out;
+    int M, N, K;
+    int x_dtype, bias_dtype, out_dtype;
+    int scales_by_tma;
+};
+
+template <int M_TILE>
+__global__ void __launch_bounds__(kThreads, 2) w4a16_kblock_kernel(const __grid_constant__ KBlockParams P) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint8_t* wst = smem;
+    uint8_t* sst = wst + kStages * kWStage;
+    float* part = reinterpret_cast<float*>(sst + kStages * kSStage);             // [kParts][M_TILE][kNT]
+    uint64_t* full = reinterpret_cast<uint64_t*>(part + kParts * M_TILE * kNT);
+    int* abort_flag = reinterpret_cast<int*>(full + kStages);
+    __half2* xs = reinterpret_cast<__half2*>(abort_flag + 4);                    // [M_TILE][K/2]
+
+    const int tid = threadIdx.x;
+    const int nl = tid % kNT;
+    const int part_id = tid / kNT;
+    const int N = P.N, K = P.K;
+    const int nqb = K >> 5;
+    const int steps = (nqb + kQT - 1) / kQT;           // stage-steps per output tile
+    const int ntiles = (N + kNT - 1) / kNT;
+    const int m0 = blockIdx.y * M_TILE;
+    // this CTA's work list: (tile, step) pairs in order, numbered `it`
+    const int my_tiles = (ntiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) /
+                         static_cast<int>(gridDim.x);
+    const int my_its = my_tiles * steps;
+
+    if (tid == 0) {
+        for (int s = 0; s < kStages; ++s) mbar_init(&full[s], 1);
+        *abort_flag = 0;
+        fence_mbar_init();
+    }
+    __syncthreads();
+
+    auto issue = [&](int it) {
+        if (it >= my_its) return;
+        const int tile = blockIdx.x + (it / steps) * gridDim.x;
+        const int step = it % steps;
+        const int n0 = tile * kNT;
+        const int nv = min(kNT, N - n0);
+        const int q0 = step * kQT;
+        const int qv = min(kQT, nqb - q0);
+        const int s = it % kStages;
+        const uint32_t wb = static_cast<uint32_t>(nv) * 16u;
+        const uint32_t sb = P.scales_by_tma ? static_cast<uint32_t>(nv) * 2u : 0u;
+        mbar_expect_tx(&full[s], static_cast<uint32_t>(qv) * (wb + sb));
+        for (int q = 0; q < qv; ++q) {
+            const size_t e = static_cast<size_t>(q0 + q) * N + n0;
+            bulk_copy_g2s(wst + s * kWStage + q * (kNT * 16), P.w + e * 16, wb, &full[s]);
+            if (sb) bulk_copy_g2s(sst + s * kSStage + q * (kNT * 2), P.scales + e, sb, &full[s]);
+        }
+    };
+    if (tid == 0) {
+        for (int it = 0; it < kStages; ++it) issue(it);
+    }
+    pdl_launch_dependents();
+    pdl_wait_prior_grids();
+
+    // stage activations: xs[m][qb*16 + wd*4 + p] = (x[32qb + 8wd + p], x[32qb + 8wd + p + 4])
+    for (int i = tid; i < M_TILE * (K >> 1); i += kThreads) {
+        const int m = i / (K >> 1);
+        const int e = i - m * (K >> 1);
+        const int k = (e >> 2) * 8 + (e & 3);
+        float a = 0.0f, b = 0.0f;
+        if (m0 + m < P.M) {
+            a = load_as_float(P.x, P.x_dtype, static_cast<size_t>(m0 + m) * K + k);
+            b = load_as_float(P.x, P.x_dtype, static_cast<size_t>(m0 + m) * K + k + 4);
+        }
+        a = fminf(fmaxf(a, -65504.0f), 65504.0f);
+        b = fminf(fmaxf(b, -65504.0f), 65504.0f);
+        xs[i] = __floats2half2_rn(a, b);
+    }
+    __syncthreads();
+
+    float acc[M_TILE];
+#pragma unroll
+    for (int m = 0; m < M_TILE; ++m) acc[m] = 0.0f;
+
+    for (int it = 0; it < my_its; ++it) {
+        const int tile = blockIdx.x + (it / steps) * gridDim.x;
+        const int step = it % steps;
+        const int n0 = tile * kNT;
+        const int nv = min(kNT, N - n0);
+        const int q0 = step * kQT;
+        const int qv = min(kQT, nqb - q0);
+        const int s = it % kStages;
+        if (!mbar_wait_bounded(&full[s], (it / kStages) & 1)) {
+            record_error(kErrGemvFullBarrierTimeout);
+            *abort_flag = 1;
+        }
+        if (nl < nv) {
+            for (int q = part_id; q < qv; q += kParts) {
+                const uint4 w = *reinterpret_cast<const uint4*>(wst + s * kWStage + q * (kNT * 16) + nl * 16);
+                float sc;
+                if (P.scales_by_tma) {
+                    sc = __half2float(*reinterpret_cast<const __half*>(sst + s * kSStage + q * (kNT * 2) + nl * 2));
+                } else {
+                    sc = __half2float(P.scales[static_cast<size_t>(q0 + q) * N + n0 + nl]);
+                }
+                __half2 h[4][4];
+                decode_u4x8_minus8(w.x, h[0]);
+                decode_u4x8_minus8(w.y, h[1]);
+                decode_u4x8_minus8(w.z, h[2]);
+                decode_u4x8_minus8(w.w, h[3]);
+#pragma unroll
+                for (int m = 0; m < M_TILE; ++m) {
+                    const uint4* xp = reinterpret_cast<const uint4*>(xs + m * (K >> 1) + (q0 + q) * 16);
+                    float d = 0.0f;
+#pragma unroll
+                    for (int wd = 0; wd < 4; ++wd) {
+                        const uint4 xv = xp[wd];  // warp-wide broadcast
+                        const __half2* x2 = reinterpret_cast<const __half2*>(&xv);
+                        __half2 a = __hmul2(h[wd][0], x2[0]);
+                        a = __hfma2(h[wd][1], x2[1], a);
+                        a = __hfma2(h[wd][2], x2[2], a);
+                        a = __hfma2(h[wd][3], x2[3], a);
+                        const float2 f = __half22float2(a);
+                        d += f.x + f.y;
+                    }
+                    acc[m] = fmaf(d, sc, acc[m]);
+                }
+            }
+        }
+        const bool last_step = (step == steps - 1);
+        if (last_step) {
+#pragma unroll
+            for (int m = 0; m < M_TILE; ++m) {
+                part[(part_id * M_TILE + m) * kNT + nl] = acc[m];
+                acc[m] = 0.0f;
+            }
+        }
+        __syncthreads();  // stage s free; partial sums visible on the last step
+        if (*abort_flag) break;
+        if (tid == 0) issue(it + kStages);
+        if (last_step) {
+            if (tid < M_TILE * kNT) {
+                const int m = tid / kNT;
+                const int n = tid % kNT;
+                if (n < nv && m0 + m < P.M) {
+                    float v = 0.0f;
+#pragma unroll
+                    for (int q = 0; q < kParts; ++q) v += part[(q * M_TILE + m) * kNT + n];
+                    if (P.bias != nullptr) v += load_as_float(P.bias, P.bias_dtype, n0 + n);
+                    store_from_float(P.out, P.out_dtype, static_cast<size_t>(m0 + m) * N + n0 + n, v);
+                }
+            }
+            __syncthreads();  // `part` is rewritten by the next tile's last step
+        }
+    }
+}
+
+template <int M_TILE>
+int launch(const KBlockParams& P, int grid_x, int grid_y, int flags, cudaStream_t stream) {
+    auto kernel = w4a16_kblock_kernel<M_TILE>;
+    const size_t smem = kStages * (kWStage + kSStage) + kParts * M_TILE * kNT * sizeof(float) +
+                        kStages * sizeof(uint64_t) + 16 + static_cast<size_t>(M_TILE) * (P.K / 2) * sizeof(__half2);
+    if (smem > 200 * 1024) return TPB200_ERR_SHAPE;
+    // the attribute is raised to the largest request seen on each device
+    static std::atomic<int> configured[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return TPB200_ERR_CUDA;
+    if (configured[dev & 63].load(std::memory_order_relaxed) < static_cast<int>(smem)) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
+            cudaSuccess) {
+            return TPB200_ERR_CUDA;
+        }
+        configured[dev & 63].store(static_cast<int>(smem), std::memory_order_relaxed);
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid_x, grid_y, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    if (flags & TPB200_FLAG_PDL) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    if (cudaLaunchKernelEx(&cfg, kernel, P) != cudaSuccess) return TPB200_ERR_CUDA;
+    return TPB200_OK;
+}
+
+}  // namespace
+
+int gemv_rowmajor_single(int fmt_is_u4, const void* x, int x_dtype, const void* x_scales, const void* w,
+                         const void* scales, int scale_dtype, int group, float global_scale, const void* bias,
+                         int bias_dtype, void* out, int out_dtype, int M, int N, int K, int activation, int flags,
+                         cudaStream_t stream);
+
+int device_error_w4a16_kblock(int clear) { return read_device_error(clear); }
+
+}  // namespace tpb
+
+extern "C" int tpb200_w4a16_gemv(const void* x, int x_dtype, const void* weight_packed, const void* scales,
+                                 int scale_dtype, const void* bias, int bias_dtype, void* out, int out_dtype, int M,
+                                 int N, int K, int group_size, int layout, int flags, tpb200_stream_t stream_) {
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    if (layout == TPB200_INT4_ROWMAJOR) {
+        return tpb::gemv_rowmajor_single(1, x, x_dtype, nullptr, weight_packed, scales, scale_dtype, group_size, 1.0f,
+                                         bias, bias_dtype, out, out_dtype, M, N, K, TPB200_ACT_NONE, flags, stream);
+    }
+    TPB_REQUIRE(layout == TPB200_INT4_KBLOCK, TPB200_ERR_ENUM);
+    TPB_REQUIRE(x && weight_packed && scales && out, TPB200_ERR_NULL);
+    TPB_REQUIRE(M >= 1 && M <= 16 && N >= 1 && K >= 32 && K % 32 == 0, TPB200_ERR_SHAPE);
+    TPB_REQUIRE(group_size == 32, TPB200_ERR_SHAPE);
+    TPB_REQUIRE(scale_dtype == TPB200_SCALE_F16, TPB200_ERR_ENUM);
+    TPB_REQUIRE(tpb_valid_dtype(x_dtype) && tpb_valid_dtype(out_dtype) && tpb_valid_dtype(bias_dtype), TPB200_ERR_ENUM);
+    TPB_REQUIRE((flags & ~TPB200_FLAG_PDL) == 0, TPB200_ERR_ENUM);
+    TPB_REQUIRE(tpb_aligned16(x) && tpb_aligned16(weight_packed) && tpb_aligned16(scales) && tpb_aligned16(out),
+                TPB200_ERR_ALIGN);
+    tpb::KBlockParams P;
+    P.w = static_cast<const uint8_t*>(weight_packed);
+    P.scales = static_cast<const __half*>(scales);
+    P.x = x;
+    P.bias = bias;
+    P.out = out;
+    P.M = M; P.N = N; P.K = K;
+    P.x_dtype = x_dtype; P.bias_dtype = bias_dtype; P.out_dtype = out_dtype;
+    P.scales_by_tma = (N % 8 == 0) ? 1 : 0;
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+        return TPB200_ERR_CUDA;
+    }
+    const int ntiles = (N + tpb::kNT - 1) / tpb::kNT;
+    const int grid_x = std::min(ntiles, 2 * sms);
+    const int m_tile = M >= 3 ? 4 : M;
+    const int grid_y = (M + m_tile - 1) / m_tile;
+    if (m_tile == 1) return tpb::launch<1>(P, grid_x, grid_y, flags, stream);
+    if (m_tile == 2) return tpb::launch<2>(P, grid_x, grid_y, flags, stream);
+    return tpb::launch<4>(P, grid_x, grid_y, flags, stream);
+}

@@ -1,0 +1,224 @@
+"""Tensor-level wrappers over the C ABI.
+
+The functions keep the names, argument order and return conventions of the
+reference's pybind / torch.library surfaces:
+
+  w4a16_gemv(input, weight_packed, scales)            openpi/src/openpi/ops/w4a16_gemv.py:244-294
+  nvfp4_gemv_v6 / nvfp4_gemv_w4a16 / nvfp4_gemv       openpi/nvfp4_packed_plugin/src/nvfp4_gemv_v5.cu:566-602,
+                                                       openpi/nvfp4_packed_plugin/src/nvfp4_packed_torch.cu:296-319
+
+and add the B200-native forms (bf16 in/out, E4M3 block-16 scales, grouped launch).
+Every tensor must live on a CUDA device; nothing here computes on the CPU.
+"""
+import ctypes
+
+import torch
+
+from . import _lib
+from ._lib import (ACT_NONE, BF16, F16, F32, FLAG_NONE, FLAG_PDL, INT4_KBLOCK, INT4_ROWMAJOR, SCALE_E4M3,
+                   SCALE_F16, SCALE_BF16, SCALE_F32, TurboPiError)
+
+_DTYPES = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
+
+
+def _dt(t):
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise TurboPiError(f"unsupported dtype {t.dtype}") from None
+
+
+def _cuda(*tensors):
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise TurboPiError("turbopi_b200 kernels need CUDA tensors (there is no CPU path)")
+
+
+def _ptr(t):
+    return 0 if t is None else t.data_ptr()
+
+
+def _stream(t):
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _scale_kind(scales):
+    if scales.dtype == torch.float32:
+        return SCALE_F32
+    if scales.dtype in (torch.uint8, torch.float8_e4m3fn):
+        return SCALE_E4M3
+    if scales.dtype == torch.float16:
+        return SCALE_F16
+    if scales.dtype == torch.bfloat16:
+        return SCALE_BF16
+    raise TurboPiError(f"unsupported scale dtype {scales.dtype}")
+
+
+# ------------------------------------------------------------------------------------- INT4
+def w4a16_gemv_out(input, weight_packed, scales, out, bias=None, group_size=32, layout=INT4_KBLOCK, pdl=False):
+    """out[M, N] = input[M, K] @ dequant(W)^T (+ bias); M <= 16.  Writes into `out`."""
+    _cuda(input, weight_packed, scales, out, bias)
+    M, K = input.shape
+    N = out.shape[1]
+    with torch.cuda.device(input.device):
+        st = _lib.load().tpb200_w4a16_gemv(
+            _ptr(input), _dt(input), _ptr(weight_packed), _ptr(scales), _scale_kind(scales), _ptr(bias),
+            _dt(bias) if bias is not None else F32, _ptr(out), _dt(out), M, N, K, group_size, layout,
+            FLAG_PDL if pdl else FLAG_NONE, _stream(input))
+    _lib.check(st, "tpb200_w4a16_gemv")
+    return out
+
+
+def w4a16_gemv(input, weight_packed, scales):
+    """Same contract as torch.ops.openpi.w4a16_gemv: input (1, K) fp16 CUDA, weight_packed
+    (K/32, N, 4) int32, scales (K/32, N) fp16; returns (1, N) float32.  Raises ValueError
+    for more than one row, as the reference does."""
+    if not input.is_cuda:
+        raise TurboPiError("Input must be on CUDA")
+    if input.size(0) > 1:
+        raise ValueError("W4A16 GEMV only supports seq_len=1. Use F.linear for seq_len > 1.")
+    nb, N, four = weight_packed.shape
+    if four != 4 or input.shape[1] != nb * 32:
+        raise TurboPiError(f"shape mismatch: input {tuple(input.shape)}, weight_packed {tuple(weight_packed.shape)}")
+    out = torch.empty((input.size(0), N), dtype=torch.float32, device=input.device)
+    return w4a16_gemv_out(input.contiguous(), weight_packed.contiguous(), scales.contiguous(), out)
+
+
+# ------------------------------------------------------------------------------------- NVFP4
+def nvfp4_gemv_out(x, weight_packed, weight_scales, out, bias=None, activation=ACT_NONE, block_size=32,
+                   global_scale=1.0, x_scales=None, pdl=False):
+    """out[M, N] = act(gs * x @ dequant(W)^T + bias); M <= 16.  Writes into `out`."""
+    _cuda(x, weight_packed, weight_scales, out, bias, x_scales)
+    M, K = x.shape
+    N = out.shape[1]
+    with torch.cuda.device(x.device):
+        st = _lib.load().tpb200_nvfp4_gemv(
+            _ptr(x), _dt(x), _ptr(x_scales), _ptr(weight_packed), _ptr(weight_scales), _scale_kind(weight_scales),
+            block_size, float(global_scale), _ptr(bias), _dt(bias) if bias is not None else F32, _ptr(out),
+            _dt(out), M, N, K, int(activation), FLAG_PDL if pdl else FLAG_NONE, _stream(x))
+    _lib.check(st, "tpb200_nvfp4_gemv")
+    return out
+
+
+def _nvfp4_gemv_ref_signature(activation, weight_packed, scale_W, bias, M, N, K, activation_type, scale_A=None):
+    activation = activation.to(torch.float32).contiguous()
+    weight_packed = weight_packed.contiguous()
+    scale_W = scale_W.to(torch.float32).contiguous()
+    if bias is not None and bias.numel() > 0:
+        bias = bias.to(torch.float32).contiguous()
+    else:
+        bias = None
+    if scale_A is not None:
+        scale_A = scale_A.to(torch.float32).contiguous()
+    if tuple(activation.shape) != (M, K) or tuple(weight_packed.shape) != (N, K // 2):
+        raise TurboPiError("nvfp4_gemv: tensor shapes do not match M, N, K")
+    out = torch.empty((M, N), dtype=torch.float32, device=activation.device)
+    for m0 in range(0, M, 16):                       # the kernel takes up to 16 rows per launch
+        m1 = min(M, m0 + 16)
+        nvfp4_gemv_out(activation[m0:m1], weight_packed, scale_W, out[m0:m1], bias, activation_type, 32, 1.0,
+                       None if scale_A is None else scale_A[m0:m1])
+    return out
+
+
+def nvfp4_gemv_v6(activation, weight_packed, scale_W, bias, M, N, K, activation_type):
+    """nvfp4_gemv_v6(activation, weight_packed uint8[N,K/2], scale_W f32[N,K/32], bias|None, M, N, K, act)
+    -> f32[M, N]  (openpi/nvfp4_packed_plugin/src/nvfp4_gemv_v5.cu:430-476)."""
+    return _nvfp4_gemv_ref_signature(activation, weight_packed, scale_W, bias, M, N, K, activation_type)
+
+
+nvfp4_gemv_w4a16 = nvfp4_gemv_v6  # openpi/nvfp4_packed_plugin/src/nvfp4_packed_torch.cu:232-290
+
+
+def nvfp4_gemv(activation, weight_packed, scale_A, scale_W, bias, M, N, K, activation_type):
+    """W4A4-style variant with per-block activation scales
+    (openpi/nvfp4_packed_plugin/src/nvfp4_packed_torch.cu:173-230)."""
+    return _nvfp4_gemv_ref_signature(activation, weight_packed, scale_W, bias, M, N, K, activation_type, scale_A)
+
+
+class GroupedGemv:
+    """A fixed list of independent NVFP4 GEMVs launched as ONE kernel.  The problem table is
+    built once (host memory only); `launch()` enqueues the kernel on the current stream."""
+
+    def __init__(self, problems, block_size, activation=ACT_NONE, pdl=False):
+        # problems: list of dicts with x, weight_packed, weight_scales, out, optional bias, global_scale
+        if not 1 <= len(problems) <= _lib.MAX_GROUP:
+            raise TurboPiError(f"1..{_lib.MAX_GROUP} problems per grouped launch")
+        p0 = problems[0]
+        self._keep = problems
+        self.M = p0["x"].shape[0]
+        self.x_dtype = _dt(p0["x"])
+        self.out_dtype = _dt(p0["out"])
+        self.scale_kind = _scale_kind(p0["weight_scales"])
+        self.bias_dtype = _dt(p0["bias"]) if p0.get("bias") is not None else F32
+        self.block_size = block_size
+        self.activation = int(activation)
+        self.flags = FLAG_PDL if pdl else FLAG_NONE
+        self.device = p0["x"].device
+        arr = (_lib.GemvProblem * len(problems))()
+        for i, p in enumerate(problems):
+            _cuda(p["x"], p["weight_packed"], p["weight_scales"], p["out"], p.get("bias"))
+            N, Kh = p["weight_packed"].shape
+            arr[i] = _lib.GemvProblem(_ptr(p["x"]), _ptr(p["weight_packed"]), _ptr(p["weight_scales"]),
+                                      _ptr(p.get("bias")), _ptr(p["out"]), N, Kh * 2,
+                                      float(p.get("global_scale", 1.0)), 0)
+        self._arr = arr
+
+    def launch(self):
+        with torch.cuda.device(self.device):
+            st = _lib.load().tpb200_nvfp4_gemv_grouped(
+                self._arr, len(self._arr), self.x_dtype, self.scale_kind, self.block_size, self.bias_dtype,
+                self.out_dtype, self.M, self.activation, self.flags,
+                torch.cuda.current_stream(self.device).cuda_stream)
+        _lib.check(st, "tpb200_nvfp4_gemv_grouped")
+
+
+# ------------------------------------------------------------------------------------- plugin quantisers
+def quantize_weight_to_int4(weight_bf16, group_size=128):
+    """quantizeWeightToINT4: bf16 [N, K] -> (int8 [N, K/2], bf16 scales [N, K/g], bf16 zeros)."""
+    _cuda(weight_bf16)
+    w = weight_bf16.to(torch.bfloat16).contiguous()
+    N, K = w.shape
+    packed = torch.empty((N, K // 2), dtype=torch.int8, device=w.device)
+    scales = torch.empty((N, K // group_size), dtype=torch.bfloat16, device=w.device)
+    zeros = torch.empty_like(scales)
+    with torch.cuda.device(w.device):
+        _lib.load().quantizeWeightToINT4(_ptr(w), _ptr(packed), _ptr(scales), _ptr(zeros), N, K, group_size, _stream(w))
+    _lib.check_void("quantizeWeightToINT4")
+    return packed, scales, zeros
+
+
+def dequantize_int4_to_bf16(packed, scales, zeros, group_size=128):
+    _cuda(packed, scales, zeros)
+    N, Kh = packed.shape
+    out = torch.empty((N, Kh * 2), dtype=torch.bfloat16, device=packed.device)
+    with torch.cuda.device(packed.device):
+        _lib.load().dequantizeINT4ToBF16(_ptr(packed), _ptr(scales), _ptr(zeros), _ptr(out), N, Kh * 2, group_size,
+                                         _stream(packed))
+    _lib.check_void("dequantizeINT4ToBF16")
+    return out
+
+
+def quantize_activation_to_fp8(x_bf16):
+    """quantizeActivationToFP8: bf16 [M, K] -> (E4M3 bytes [M, K], E4M3 scale bytes [M, K/16])."""
+    _cuda(x_bf16)
+    x = x_bf16.to(torch.bfloat16).contiguous()
+    M, K = x.shape
+    out = torch.empty((M, K), dtype=torch.uint8, device=x.device)
+    scales = torch.empty((M, K // 16), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        _lib.load().quantizeActivationToFP8(_ptr(x), _ptr(out), _ptr(scales), M, K, _stream(x))
+    _lib.check_void("quantizeActivationToFP8")
+    return out, scales
+
+
+def quantize_weight_to_nvfp4(weight_bf16):
+    """quantizeWeightToNVFP4: bf16 [N, K] -> (packed [K/2, N] uint8, E4M3 scale bytes [K/16, N])."""
+    _cuda(weight_bf16)
+    w = weight_bf16.to(torch.bfloat16).contiguous()
+    N, K = w.shape
+    packed = torch.empty((K // 2, N), dtype=torch.uint8, device=w.device)
+    scales = torch.empty((K // 16, N), dtype=torch.uint8, device=w.device)
+    with torch.cuda.device(w.device):
+        _lib.load().quantizeWeightToNVFP4(_ptr(w), _ptr(packed), _ptr(scales), N, K, _stream(w))
+    _lib.check_void("quantizeWeightToNVFP4")
+    return packed, scales
