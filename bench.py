@@ -1,0 +1,453 @@
+#!/usr/bin/env python3
+"""Benchmark of the quantized Pi0.5 decode hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (seeded synthetic, stands in for real checkpoints): the NVFP4 weight-only GEMV
+(M = 1) over the 54 MLP matrices of the Gemma-300M action expert -- 18 layers x
+(gate 1024->4096, up 1024->4096, down 4096->1024), e2m1 codes uniform over the 16 codes,
+2 per byte, E4M3 scale per 16 K-elements = blockamax/6 of an N(0, 0.02) matrix over an fp32
+global scale, bf16 activations N(0,1), bf16 outputs.  A step is one pass over all 54
+matrices.  Four independent weight sets (4 x 128 MB) are rotated from step to step, so
+every step streams its weights from HBM, never from the 126 MB L2.
+
+`value` times the pass with inputs resident in HBM (one grouped launch per step);
+`e2e` times the same pass through the Python API with HOST activations and results
+(pinned H2D / D2H copies inside the timed region).  N > 1 runs one independent replica per
+GPU (no collective on the data path); the barrier and max-over-ranks use NCCL.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+LAYERS = 18
+HIDDEN, INTER = 1024, 4096
+SHAPES = [(INTER, HIDDEN), (INTER, HIDDEN), (HIDDEN, INTER)]      # (N, K): gate, up, down
+BLOCK = 16
+NSETS = 4
+METRIC = "nvfp4_gemv_hbm_gbps"
+UNIT = "GB/s"
+
+
+def algorithmic_bytes(N, K, M=1):
+    """codes + E4M3 block scales + fp32 global scale + bf16 activations + bf16 outputs."""
+    return N * K // 2 + N * K // BLOCK + 4 + M * K * 2 + M * N * 2
+
+
+STEP_BYTES = LAYERS * sum(algorithmic_bytes(n, k) for n, k in SHAPES)
+
+
+def measured_peak_gbs():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+# ------------------------------------------------------------------------------------------ synthetic weights
+def make_weight_set(seed, device):
+    """54 problems: packed codes, E4M3 scale bytes, global scale -- generated on the device."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    mats = []
+    for layer in range(LAYERS):
+        for (N, K) in SHAPES:
+            base = torch.randn(N, K, generator=g, device=device) * 0.02
+            gs = float(base.abs().max() / (6.0 * 448.0))
+            bmax = base.reshape(N, K // BLOCK, BLOCK).abs().amax(dim=2)
+            scales = (bmax / 6.0 / gs).clamp(max=448.0).to(torch.float8_e4m3fn).view(torch.uint8)
+            packed = torch.randint(0, 256, (N, K // 2), generator=g, device=device, dtype=torch.uint8)
+            mats.append((packed, scales, gs, N, K))
+    return mats
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons of one GPU, sampled in the background."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.rows = []
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def stop(self, t0, t1):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        rows = [r for (t, r) in self.rows if t0 - 0.05 <= t <= t1 + 0.15] or [r for (_, r) in self.rows]
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            try:
+                sm.append(float(r[0])); mx.append(float(r[1]))
+            except Exception:
+                continue
+            for n, v in zip(names, r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def dist_setup(n_gpus):
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return rank, world, local
+
+
+def barrier_sync(world):
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(ms, world, device):
+    if world == 1:
+        return ms
+    import torch.distributed as dist
+    t = torch.tensor([ms], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+# ------------------------------------------------------------------------------------------ our arm
+def run_ours(args):
+    from turbopi_b200 import _lib, ops
+    rank, world, local = dist_setup(args.gpus)
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    _lib.load()
+
+    x = {K: torch.randn(1, K, device=device, generator=torch.Generator(device=device).manual_seed(7)).to(torch.bfloat16)
+         for K in (HIDDEN, INTER)}
+    sets, groups, outs = [], [], []
+    for s in range(NSETS):
+        mats = make_weight_set(100 + s, device)
+        o = [torch.empty((1, N), dtype=torch.bfloat16, device=device) for (_, _, _, N, _) in mats]
+        probs = [dict(x=x[K], weight_packed=p, weight_scales=sc, out=oo, global_scale=gs)
+                 for (p, sc, gs, N, K), oo in zip(mats, o)]
+        sets.append(mats)
+        outs.append(o)
+        groups.append(ops.GroupedGemv(probs, BLOCK))
+    stream = torch.cuda.current_stream(device)
+
+    def step(i):
+        groups[i % NSETS].launch()
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    t_wall0 = time.time()
+    # warm-up: W steps, extended to ~0.4 s of GPU work so the clock sampler sees the kernel under load
+    w = 0
+    t_w = time.time()
+    while w < args.warmup or (not args.no_clock_warmup and (time.time() - t_w) < 0.4):
+        step(w)
+        w += 1
+        if w % 64 == 0:
+            torch.cuda.synchronize()
+    barrier_sync(world)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for i in range(args.steps):
+        step(i)
+    e1.record(stream)
+    barrier_sync(world)
+    ms = max_over_ranks(e0.elapsed_time(e1), world, device)
+    launches = args.steps
+    per_launch_s = (e0.elapsed_time(e1) / 1e3) / launches
+
+    # ---- end to end: host activations in, host results out, through the Python API --------------------
+    hx = {K: x[K].cpu().pin_memory() for K in x}
+    out_flat = [torch.cat([o.reshape(-1) for o in outs[s]]) for s in range(NSETS)]   # contiguous result buffers
+    # re-point the problems at slices of one result buffer per set so the step's result is one D2H copy
+    e2e_groups = []
+    for s in range(NSETS):
+        off, probs = 0, []
+        for (p, sc, gs, N, K) in sets[s]:
+            probs.append(dict(x=x[K], weight_packed=p, weight_scales=sc, out=out_flat[s][off:off + N].view(1, N),
+                              global_scale=gs))
+            off += N
+        e2e_groups.append(ops.GroupedGemv(probs, BLOCK))
+    h_out = torch.empty_like(out_flat[0], device="cpu").pin_memory()
+    h2d = sum(t.numel() * t.element_size() for t in hx.values())
+    d2h = h_out.numel() * h_out.element_size()
+
+    def e2e_step(i):
+        for K in x:
+            x[K].copy_(hx[K], non_blocking=True)
+        e2e_groups[i % NSETS].launch()
+        h_out.copy_(out_flat[i % NSETS], non_blocking=True)
+        stream.synchronize()                      # the caller has its result on the host
+
+    for i in range(max(3, min(args.warmup, 20))):
+        e2e_step(i)
+    barrier_sync(world)
+    e2e_steps = args.steps
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record(stream)
+    for i in range(e2e_steps):
+        e2e_step(i)
+    f1.record(stream)
+    barrier_sync(world)
+    e2e_ms = max_over_ranks(f0.elapsed_time(f1), world, device)
+    t_wall1 = time.time()
+    clocks = sampler.stop(t_wall0, t_wall1) if sampler else None
+
+    extras = {}
+    if rank == 0 and not args.no_extras:
+        extras = run_extras(device, sets, x)
+    dev_err = _lib.load().tpb200_device_error(0)
+
+    if rank == 0:
+        peak, peak_kind = measured_peak_gbs()
+        total_bytes = STEP_BYTES * args.steps * world
+        value = total_bytes / (ms / 1e3) / 1e9
+        achieved = STEP_BYTES / per_launch_s / 1e9
+        traffic = None
+        tf = ROOT / "profiles" / "traffic.json"
+        if tf.exists():
+            try:
+                traffic = json.loads(tf.read_text()).get("nvfp4_gemv_grouped_54_bytes_per_launch")
+            except Exception:
+                traffic = None
+        cpu = cpu_baseline_sample() if world == 1 else None
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f16 products / f32 accumulate", "data": "synthetic",
+            "config": {"workload": "NVFP4 weight-only GEMV, M=1, Gemma-300M action-expert MLP, 18 layers x "
+                                   "(gate,up 1024->4096; down 4096->1024) = 54 matrices per step, E4M3 block-16 "
+                                   "scales + fp32 global scale, bf16 in/out",
+                       "launch": "one grouped launch per step (tpb200_nvfp4_gemv_grouped)",
+                       "l2": f"{NSETS} weight sets of {STEP_BYTES / 1e6:.1f} MB rotated per step (> 126 MB L2)",
+                       "parallelism": f"{world} independent replica(s), no collective",
+                       "warmup_note": "warm-up extended to >= 0.4 s so clocks are sampled under load"},
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                         "frac": achieved / peak, "traffic": traffic, "peak_kind": f"of {peak_kind}",
+                         "algorithmic_bytes_per_launch": STEP_BYTES, "nominal_peak": 8000.0,
+                         "frac_of_nominal": achieved / 8000.0},
+            "cpu_baseline": cpu,
+            "e2e": {"value": STEP_BYTES * e2e_steps * world / (e2e_ms / 1e3) / 1e9, "unit": UNIT,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / e2e_steps},
+            "gpu_launches": launches,
+            "clocks": clocks,
+            "device_error": dev_err,
+            "extras": extras,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+def time_launches(fn, iters, warm=20):
+    stream = torch.cuda.current_stream()
+    for i in range(warm):
+        fn(i)
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record(stream)
+    for i in range(iters):
+        fn(i)
+    b.record(stream)
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / iters * 1e-3
+
+
+def run_extras(device, sets, x):
+    """Per-configuration figures that explain the headline: single launches per shape and M,
+    the dependent chain under programmatic dependent launch in a CUDA graph, and the INT4
+    W4A16 GEMV of the reference's own benchmark shape."""
+    from turbopi_b200 import ops
+    ex = {}
+    # (a) one launch per matrix, rotating through all 216 matrices (> L2), M in {1, 4, 16}
+    flat = [m for s in sets for m in s]
+    for M in (1, 4, 16):
+        xm = {K: torch.randn(M, K, device=device).to(torch.bfloat16) for K in (HIDDEN, INTER)}
+        om = {N: torch.empty((M, N), dtype=torch.bfloat16, device=device) for N in (HIDDEN, INTER)}
+        for (Nsel, Ksel, name) in ((INTER, HIDDEN, "gateup_1024x4096"), (HIDDEN, INTER, "down_4096x1024")):
+            ms_ = [m for m in flat if m[3] == Nsel]
+
+            def fn(i, ms_=ms_, xm=xm, om=om, Nsel=Nsel, Ksel=Ksel):
+                p, sc, gs, N, K = ms_[i % len(ms_)]
+                ops.nvfp4_gemv_out(xm[Ksel], p, sc, om[Nsel], block_size=BLOCK, global_scale=gs)
+            t = time_launches(fn, 400)
+            ex[f"single_launch_M{M}_{name}"] = {"us": t * 1e6, "gbps": algorithmic_bytes(Nsel, Ksel, M) / t / 1e9}
+    # (b) the 54 GEMVs as 54 launches with programmatic dependent launch, captured in one CUDA graph per set
+    graphs = []
+    side = torch.cuda.Stream(device=device)
+    outs = [torch.empty((1, N), dtype=torch.bfloat16, device=device) for (_, _, _, N, _) in sets[0]]
+    for pdl in (False, True):
+        gl = []
+        for s in range(NSETS):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                for (p, sc, gs, N, K), o in zip(sets[s], outs):     # warm the launch path on the side stream
+                    ops.nvfp4_gemv_out(x[K], p, sc, o, block_size=BLOCK, global_scale=gs, pdl=pdl)
+            torch.cuda.synchronize()
+            with torch.cuda.graph(g, stream=side):
+                for (p, sc, gs, N, K), o in zip(sets[s], outs):
+                    ops.nvfp4_gemv_out(x[K], p, sc, o, block_size=BLOCK, global_scale=gs, pdl=pdl)
+            gl.append(g)
+        t = time_launches(lambda i, gl=gl: gl[i % NSETS].replay(), 200)
+        ex["graph_54_launches_pdl" if pdl else "graph_54_launches"] = {
+            "us_per_step": t * 1e6, "gbps": STEP_BYTES / t / 1e9, "us_per_launch": t * 1e6 / 54}
+        graphs.append(gl)
+    # (c) W4A16 INT4 GEMV, N=16384 K=2048 g=128 row-major, bf16; 16 rotating weight buffers (277 MB)
+    N, K, G = 16384, 2048, 128
+    ws = [torch.randint(-2 ** 31, 2 ** 31 - 1, (N, K // 8), device=device, dtype=torch.int32) for _ in range(16)]
+    sc = [(torch.rand(N, K // G, device=device) * 0.015 + 0.005).to(torch.float16) for _ in range(16)]
+    xi = torch.randn(1, K, device=device).to(torch.bfloat16)
+    oi = torch.empty((1, N), dtype=torch.bfloat16, device=device)
+    nbytes = N * K // 2 + N * (K // G) * 2 + K * 2 + N * 2
+    t = time_launches(lambda i: ops.w4a16_gemv_out(xi, ws[i % 16], sc[i % 16], oi, group_size=G, layout=1), 400)
+    ex["w4a16_int4_rowmajor_g128_16384x2048"] = {"us": t * 1e6, "gbps": nbytes / t / 1e9, "bytes": nbytes}
+    # reference layout (K/32, N, 4) g=32, fp16 in / fp32 out
+    wk = [torch.randint(-2 ** 31, 2 ** 31 - 1, (K // 32, N, 4), device=device, dtype=torch.int32) for _ in range(16)]
+    sk = [(torch.rand(K // 32, N, device=device) * 0.015 + 0.005).to(torch.float16) for _ in range(16)]
+    xh = torch.randn(1, K, device=device).to(torch.float16)
+    of = torch.empty((1, N), dtype=torch.float32, device=device)
+    nbytes = N * K // 2 + N * (K // 32) * 2 + K * 2 + N * 4
+    t = time_launches(lambda i: ops.w4a16_gemv_out(xh, wk[i % 16], sk[i % 16], of, group_size=32, layout=0), 400)
+    ex["w4a16_int4_kblock_g32_16384x2048"] = {"us": t * 1e6, "gbps": nbytes / t / 1e9, "bytes": nbytes}
+    # (d) NVFP4 GEMV at the Gemma-2B shapes (18.9 MB each), 12 rotating buffers
+    for (N, K, name) in ((16384, 2048, "gemma2b_gateup_2048x16384"), (2048, 16384, "gemma2b_down_16384x2048")):
+        wp = [torch.randint(0, 256, (N, K // 2), device=device, dtype=torch.uint8) for _ in range(12)]
+        sp = [torch.randint(40, 120, (N, K // 16), device=device, dtype=torch.uint8) for _ in range(12)]
+        xb = torch.randn(1, K, device=device).to(torch.bfloat16)
+        ob = torch.empty((1, N), dtype=torch.bfloat16, device=device)
+        t = time_launches(lambda i: ops.nvfp4_gemv_out(xb, wp[i % 12], sp[i % 12], ob, block_size=16,
+                                                       global_scale=1e-3), 400)
+        ex[f"nvfp4_single_launch_{name}"] = {"us": t * 1e6, "gbps": algorithmic_bytes(N, K) / t / 1e9}
+    return ex
+
+
+# ------------------------------------------------------------------------------------------ CPU arms
+def _cpu_layer(seed):
+    g = torch.Generator().manual_seed(seed)
+    mats = []
+    for (N, K) in SHAPES:
+        base = torch.randn(N, K, generator=g) * 0.02
+        gs = float(base.abs().max() / (6.0 * 448.0))
+        bmax = base.reshape(N, K // BLOCK, BLOCK).abs().amax(dim=2)
+        scales = (bmax / 6.0 / gs).to(torch.float8_e4m3fn).float() * gs          # pre-expanded to fp32
+        packed = torch.randint(0, 256, (N, K // 2), generator=g, dtype=torch.uint8)
+        mats.append((packed, scales, N, K))
+    return mats
+
+
+def cpu_time_layers(n_layers, reps):
+    """Reference CPU path (dequantise every call + F.linear, fp32) over `n_layers` layers."""
+    from oracle import cpu_baseline
+    torch.set_num_threads(os.cpu_count() or 1)
+    layers = [_cpu_layer(1000 + i) for i in range(n_layers)]
+    xs = {K: torch.randn(1, K) for K in (HIDDEN, INTER)}
+    times = []
+    for r in range(reps):
+        t0 = time.perf_counter()
+        for mats in layers:
+            for (p, s, N, K) in mats:
+                cpu_baseline.nvfp4_forward_dequant_gemm(xs[K], p, s, BLOCK)
+        times.append(time.perf_counter() - t0)
+    return times
+
+
+def cpu_baseline_sample():
+    """~10-20 s of the reference CPU path on the host cores of this box: all 18 layers (the 54
+    matrices of one step) per repetition."""
+    n_layers = LAYERS
+    cpu_time_layers(n_layers, 1)
+    times = cpu_time_layers(n_layers, 8)
+    t = float(np.median(times))
+    bytes_ = n_layers * sum(algorithmic_bytes(n, k) for n, k in SHAPES)
+    return {"value": bytes_ / t / 1e9, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
+            "sample": f"{n_layers} of 18 layers ({3 * n_layers} matrices = one full step), median of 8 repetitions; torch CPU restatement of "
+                      "NVFP4PackedLinear._forward_dequant_gemm (dequantise per call + F.linear, fp32), "
+                      f"torch threads = {torch.get_num_threads()}",
+            "seconds_per_sample": t}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    n_layers = 2
+    bytes_ = n_layers * sum(algorithmic_bytes(n, k) for n, k in SHAPES)
+    cpu_time_layers(n_layers, max(1, min(args.warmup, 3)))
+    steps = args.steps
+    budget_s = 150.0
+    times = []
+    t_start = time.perf_counter()
+    for i in range(steps):
+        times += cpu_time_layers(n_layers, 1)
+        if time.perf_counter() - t_start > budget_s:
+            break
+    done = len(times)
+    total = float(sum(times))
+    value = bytes_ * done / total / 1e9
+    cpu = {"value": value, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
+           "sample": f"each step = {n_layers} of 18 layers (6 matrices) of the same workload; torch CPU restatement "
+                     "of NVFP4PackedLinear._forward_dequant_gemm, all host threads"}
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": int(args.gpus),
+            "steps": done, "steps_requested": steps, "warmup": args.warmup, "ms_per_step": total / done * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "NVFP4 weight-only GEMV, M=1, Gemma-300M action-expert MLP (bounded sample: "
+                                   f"{n_layers} layers per step)", "parallelism": "host CPU, rank 0 only"},
+            "cpu_baseline": cpu,
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=50)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extras", action="store_true", help="skip the per-configuration side measurements")
+    ap.add_argument("--no-clock-warmup", action="store_true",
+                    help="do exactly W warm-up steps (profiling runs); by default warm-up lasts >= 0.4 s")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU fallback")
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
