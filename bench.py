@@ -180,11 +180,13 @@ def run_ours(args):
             torch.cuda.synchronize()
     barrier_sync(world)
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.profiler.start()       # `ncu --profile-from-start off` captures the timed region only
     e0.record(stream)
     for i in range(args.steps):
         step(i)
     e1.record(stream)
     barrier_sync(world)
+    torch.cuda.profiler.stop()
     ms = max_over_ranks(e0.elapsed_time(e1), world, device)
     launches = args.steps
     per_launch_s = (e0.elapsed_time(e1) / 1e3) / launches
@@ -274,8 +276,34 @@ def run_ours(args):
 
 
 def time_launches(fn, iters, warm=20):
+    """Seconds per launch of fn(i) with the launches captured in ONE CUDA graph (rotating through
+    `iters` argument sets), so the figure is device time per launch, not Python call overhead."""
     stream = torch.cuda.current_stream()
-    for i in range(warm):
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for i in range(min(warm, iters)):
+            fn(i)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=side):
+        for i in range(iters):
+            fn(i)
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    reps = 5
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record(stream)
+    for _ in range(reps):
+        g.replay()
+    b.record(stream)
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / (iters * reps) * 1e-3
+
+
+def time_replays(fn, iters):
+    stream = torch.cuda.current_stream()
+    for i in range(8):
         fn(i)
     torch.cuda.synchronize()
     a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -304,7 +332,7 @@ def run_extras(device, sets, x):
             def fn(i, ms_=ms_, xm=xm, om=om, Nsel=Nsel, Ksel=Ksel):
                 p, sc, gs, N, K = ms_[i % len(ms_)]
                 ops.nvfp4_gemv_out(xm[Ksel], p, sc, om[Nsel], block_size=BLOCK, global_scale=gs)
-            t = time_launches(fn, 400)
+            t = time_launches(fn, 216)
             ex[f"single_launch_M{M}_{name}"] = {"us": t * 1e6, "gbps": algorithmic_bytes(Nsel, Ksel, M) / t / 1e9}
     # (b) the 54 GEMVs as 54 launches with programmatic dependent launch, captured in one CUDA graph per set
     graphs = []
@@ -322,7 +350,7 @@ def run_extras(device, sets, x):
                 for (p, sc, gs, N, K), o in zip(sets[s], outs):
                     ops.nvfp4_gemv_out(x[K], p, sc, o, block_size=BLOCK, global_scale=gs, pdl=pdl)
             gl.append(g)
-        t = time_launches(lambda i, gl=gl: gl[i % NSETS].replay(), 200)
+        t = time_replays(lambda i, gl=gl: gl[i % NSETS].replay(), 200)
         ex["graph_54_launches_pdl" if pdl else "graph_54_launches"] = {
             "us_per_step": t * 1e6, "gbps": STEP_BYTES / t / 1e9, "us_per_launch": t * 1e6 / 54}
         graphs.append(gl)
@@ -333,7 +361,7 @@ def run_extras(device, sets, x):
     xi = torch.randn(1, K, device=device).to(torch.bfloat16)
     oi = torch.empty((1, N), dtype=torch.bfloat16, device=device)
     nbytes = N * K // 2 + N * (K // G) * 2 + K * 2 + N * 2
-    t = time_launches(lambda i: ops.w4a16_gemv_out(xi, ws[i % 16], sc[i % 16], oi, group_size=G, layout=1), 400)
+    t = time_launches(lambda i: ops.w4a16_gemv_out(xi, ws[i % 16], sc[i % 16], oi, group_size=G, layout=1), 64)
     ex["w4a16_int4_rowmajor_g128_16384x2048"] = {"us": t * 1e6, "gbps": nbytes / t / 1e9, "bytes": nbytes}
     # reference layout (K/32, N, 4) g=32, fp16 in / fp32 out
     wk = [torch.randint(-2 ** 31, 2 ** 31 - 1, (K // 32, N, 4), device=device, dtype=torch.int32) for _ in range(16)]
@@ -341,7 +369,7 @@ def run_extras(device, sets, x):
     xh = torch.randn(1, K, device=device).to(torch.float16)
     of = torch.empty((1, N), dtype=torch.float32, device=device)
     nbytes = N * K // 2 + N * (K // 32) * 2 + K * 2 + N * 4
-    t = time_launches(lambda i: ops.w4a16_gemv_out(xh, wk[i % 16], sk[i % 16], of, group_size=32, layout=0), 400)
+    t = time_launches(lambda i: ops.w4a16_gemv_out(xh, wk[i % 16], sk[i % 16], of, group_size=32, layout=0), 64)
     ex["w4a16_int4_kblock_g32_16384x2048"] = {"us": t * 1e6, "gbps": nbytes / t / 1e9, "bytes": nbytes}
     # (d) NVFP4 GEMV at the Gemma-2B shapes (18.9 MB each), 12 rotating buffers
     for (N, K, name) in ((16384, 2048, "gemma2b_gateup_2048x16384"), (2048, 16384, "gemma2b_down_16384x2048")):
@@ -350,7 +378,7 @@ def run_extras(device, sets, x):
         xb = torch.randn(1, K, device=device).to(torch.bfloat16)
         ob = torch.empty((1, N), dtype=torch.bfloat16, device=device)
         t = time_launches(lambda i: ops.nvfp4_gemv_out(xb, wp[i % 12], sp[i % 12], ob, block_size=16,
-                                                       global_scale=1e-3), 400)
+                                                       global_scale=1e-3), 48)
         ex[f"nvfp4_single_launch_{name}"] = {"us": t * 1e6, "gbps": algorithmic_bytes(N, K) / t / 1e9}
     return ex
 

@@ -264,6 +264,7 @@ def test_grouped_launch_and_pdl_chain_match_single_launches(cuda_device):
         assert torch.equal(a, b)
 
 
+@torch.no_grad()
 def test_modules_forward_through_kernels(cuda_device):
     from turbopi_b200 import nvfp4_packed, w4a16
     torch.manual_seed(3)

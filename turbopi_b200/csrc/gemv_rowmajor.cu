@@ -83,7 +83,7 @@ __device__ __forceinline__ __half to_half_sat(float v) {
 // decoder of FMT produces weight pairs.
 template <int FMT>
 __device__ __forceinline__ void load_x_chunk(__half2 (&xr)[16], const void* x, const void* xs, int x_dtype,
-                                             size_t row_off, int j, int group, bool valid) {
+                                             size_t row_off, int j, int group, bool valid, float prescale) {
     float v[32];
     if (!valid) {
 #pragma unroll
@@ -130,6 +130,10 @@ __device__ __forceinline__ void load_x_chunk(__half2 (&xr)[16], const void* x, c
             for (int i = 0; i < 32; ++i) v[i] *= s0;
         }
     }
+    if (prescale != 1.0f) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] *= prescale;
+    }
     if (FMT == kFmtE2M1) {
 #pragma unroll
         for (int i = 0; i < 16; ++i) xr[i] = __halves2half2(to_half_sat(v[2 * i]), to_half_sat(v[2 * i + 1]));
@@ -163,9 +167,9 @@ __device__ __forceinline__ void load_chunk_scales(const uint8_t* sc_row, int j, 
     }
 }
 
-// sum over 16 codes (two words) of code * x, packed fp16 products in two chains of
-// four, widened to fp32 at the end
-__device__ __forceinline__ float dot16(const __half2 (&ha)[4], const __half2 (&hb)[4], const __half2* x) {
+// sum over 16 codes (two words) of code * x as a packed fp16 pair (even/odd lanes of the
+// pairing still separate): two chains of four products, added at the end
+__device__ __forceinline__ __half2 dot16h(const __half2 (&ha)[4], const __half2 (&hb)[4], const __half2* x) {
     __half2 a = __hmul2(ha[0], x[0]);
     __half2 b = __hmul2(hb[0], x[4]);
     a = __hfma2(ha[1], x[1], a);
@@ -174,9 +178,54 @@ __device__ __forceinline__ float dot16(const __half2 (&ha)[4], const __half2 (&h
     b = __hfma2(hb[2], x[6], b);
     a = __hfma2(ha[3], x[3], a);
     b = __hfma2(hb[3], x[7], b);
-    float2 fa = __half22float2(a);
-    float2 fb = __half22float2(b);
-    return (fa.x + fa.y) + (fb.x + fb.y);
+    return __hadd2(a, b);
+}
+
+__device__ __forceinline__ float hsum2(__half2 v) {
+    const float2 f = __half22float2(v);
+    return f.x + f.y;
+}
+
+// E4M3 block scales are exact in fp16, so the two 16-code sums of a chunk are scaled and added
+// in packed fp16 and widened once.  To keep sum * scale (scale up to 448) inside fp16 range the
+// activations of these modes are stored pre-multiplied by 2^-8 (kXPrescale) and the result is
+// multiplied back in the epilogue.
+constexpr float kXPrescale = 1.0f / 256.0f;
+template <int SCALE_MODE>
+__host__ __device__ constexpr bool scales_in_half() { return SCALE_MODE == kScE4M3B16 || SCALE_MODE == kScE4M3B32; }
+
+template <int SCALE_MODE>
+__device__ __forceinline__ void load_chunk_scales_h2(const uint8_t* sc_row, int j, __half2& s0, __half2& s1) {
+    uint32_t r;
+    if (SCALE_MODE == kScE4M3B16) {
+        const uint16_t v = *reinterpret_cast<const uint16_t*>(sc_row + 2 * j);
+        asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(r) : "h"(v));
+    } else {
+        const uint16_t v = static_cast<uint16_t>(sc_row[j]) * 0x0101u;
+        asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(r) : "h"(v));
+    }
+    const __half2 h = *reinterpret_cast<__half2*>(&r);
+    s0 = __low2half2(h);
+    s1 = __high2half2(h);
+}
+
+// Sum four per-lane values over the warp at once: after the call lane 8*i (i = 0..3) holds the
+// warp total of v[i].  6 shuffles instead of 20.
+__device__ __forceinline__ float warp_sum4(const float (&v)[4], int lane) {
+    const bool b4 = (lane & 16) != 0, b3 = (lane & 8) != 0;
+    float k0 = b4 ? v[2] : v[0];
+    float k1 = b4 ? v[3] : v[1];
+    const float s0 = b4 ? v[0] : v[2];
+    const float s1 = b4 ? v[1] : v[3];
+    k0 += __shfl_xor_sync(0xffffffffu, s0, 16);
+    k1 += __shfl_xor_sync(0xffffffffu, s1, 16);
+    float k = b3 ? k1 : k0;
+    const float sx = b3 ? k0 : k1;
+    k += __shfl_xor_sync(0xffffffffu, sx, 8);
+    k += __shfl_xor_sync(0xffffffffu, k, 4);
+    k += __shfl_xor_sync(0xffffffffu, k, 2);
+    k += __shfl_xor_sync(0xffffffffu, k, 1);
+    return k;
 }
 
 template <int FMT, int SCALE_MODE, int M_TILE, int CPL, int MAXP>
@@ -203,13 +252,19 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_rowmajor_kernel(const __grid
     }
     __syncthreads();
 
-    // Producer (thread 0): request tile number `it` of this CTA.
+    // This CTA owns the contiguous tile range [tile_lo, tile_hi): consecutive tiles belong to the
+    // same matrix, so the activation registers are reloaded only when the range crosses into
+    // the next problem.
+    const int tile_lo = static_cast<int>(static_cast<long long>(blockIdx.x) * total_tiles / gridDim.x);
+    const int tile_hi = static_cast<int>(static_cast<long long>(blockIdx.x + 1) * total_tiles / gridDim.x);
+
+    // Producer (thread 0): request tile number `it` of this CTA.  `ip` follows the problem index.
+    int ip = 0;
     auto issue = [&](int it) {
-        const int tile = blockIdx.x + it * gridDim.x;
-        if (tile >= total_tiles) return;
-        int p = 0;
-        while (p + 1 < P.num_problems && tile >= P.prob[p + 1].tile_begin) ++p;
-        const ProblemDev& pr = P.prob[p];
+        const int tile = tile_lo + it;
+        if (tile >= tile_hi) return;
+        while (ip + 1 < P.num_problems && tile >= P.prob[ip + 1].tile_begin) ++ip;
+        const ProblemDev& pr = P.prob[ip];
         const int row0 = (tile - pr.tile_begin) * pr.rows_per_tile;
         const int rows = min(pr.rows_per_tile, pr.N - row0);
         const int row_bytes = pr.K >> 1;
@@ -237,8 +292,8 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_rowmajor_kernel(const __grid
     int KP = 1, kp = 0, rw = 0, RW = kWarps, nchunks = 0;
 
     for (int it = 0;; ++it) {
-        const int tile = blockIdx.x + it * gridDim.x;
-        if (tile >= total_tiles) break;
+        const int tile = tile_lo + it;
+        if (tile >= tile_hi) break;
         while (p + 1 < P.num_problems && tile >= P.prob[p + 1].tile_begin) ++p;
         const ProblemDev& pr = P.prob[p];
         if (p != cur_p) {
@@ -255,7 +310,8 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_rowmajor_kernel(const __grid
                     const int j = (kp * CPL + c) * 32 + lane;
                     load_x_chunk<FMT>(xr[m][c], pr.x, pr.x_scales, P.x_dtype,
                                       static_cast<size_t>(m0 + m) * pr.K, j, group,
-                                      (j < nchunks) && (m0 + m < P.M));
+                                      (j < nchunks) && (m0 + m < P.M),
+                                      scales_in_half<SCALE_MODE>() ? kXPrescale : 1.0f);
                 }
             }
         }
@@ -272,39 +328,58 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_rowmajor_kernel(const __grid
                                              : (pr.scales + static_cast<size_t>(row0) * pr.scale_row_bytes);
         float* pt = part + (it & 1) * kMaxPartials * M_TILE;
 
-        for (int r = rw; r < rows; r += RW) {
-            float acc[M_TILE];
+        // Each warp takes its rows (rw, rw + RW, ...) in groups of RG = 4 / M_TILE, so that the four
+        // (row, m) sums of a group are reduced over the warp together.
+        constexpr int RG = 4 / M_TILE;
+        for (int rbase = rw; rbase < rows; rbase += RW * RG) {
+            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // index g * M_TILE + m
 #pragma unroll
-            for (int m = 0; m < M_TILE; ++m) acc[m] = 0.0f;
+            for (int g = 0; g < RG; ++g) {
+                const int r = rbase + g * RW;
+                if (r < rows) {
 #pragma unroll
-            for (int c = 0; c < CPL; ++c) {
-                const int j = (kp * CPL + c) * 32 + lane;
-                if (j < nchunks) {
-                    const uint4 w = *reinterpret_cast<const uint4*>(wt + r * row_bytes + j * 16);
-                    float s0, s1;
-                    load_chunk_scales<SCALE_MODE>(sc + static_cast<size_t>(r) * pr.scale_row_bytes, j, group, s0, s1);
-                    __half2 h0[4], h1[4], h2[4], h3[4];
-                    if (FMT == kFmtE2M1) {
-                        decode_e2m1x8(w.x, h0); decode_e2m1x8(w.y, h1);
-                        decode_e2m1x8(w.z, h2); decode_e2m1x8(w.w, h3);
-                    } else {
-                        decode_u4x8_minus8(w.x, h0); decode_u4x8_minus8(w.y, h1);
-                        decode_u4x8_minus8(w.z, h2); decode_u4x8_minus8(w.w, h3);
-                    }
+                    for (int c = 0; c < CPL; ++c) {
+                        const int j = (kp * CPL + c) * 32 + lane;
+                        if (j < nchunks) {
+                            const uint4 w = *reinterpret_cast<const uint4*>(wt + r * row_bytes + j * 16);
+                            const uint8_t* sc_row = sc + static_cast<size_t>(r) * pr.scale_row_bytes;
+                            __half2 h0[4], h1[4], h2[4], h3[4];
+                            if (FMT == kFmtE2M1) {
+                                decode_e2m1x8(w.x, h0); decode_e2m1x8(w.y, h1);
+                                decode_e2m1x8(w.z, h2); decode_e2m1x8(w.w, h3);
+                            } else {
+                                decode_u4x8_minus8(w.x, h0); decode_u4x8_minus8(w.y, h1);
+                                decode_u4x8_minus8(w.z, h2); decode_u4x8_minus8(w.w, h3);
+                            }
+                            if (scales_in_half<SCALE_MODE>()) {
+                                __half2 s0, s1;
+                                load_chunk_scales_h2<SCALE_MODE>(sc_row, j, s0, s1);
 #pragma unroll
-                    for (int m = 0; m < M_TILE; ++m) {
-                        const float d0 = dot16(h0, h1, &xr[m][c][0]);
-                        const float d1 = dot16(h2, h3, &xr[m][c][8]);
-                        acc[m] = fmaf(d0, s0, acc[m]);
-                        acc[m] = fmaf(d1, s1, acc[m]);
+                                for (int m = 0; m < M_TILE; ++m) {
+                                    const __half2 d0 = dot16h(h0, h1, &xr[m][c][0]);
+                                    const __half2 d1 = dot16h(h2, h3, &xr[m][c][8]);
+                                    acc[g * M_TILE + m] += hsum2(__hfma2(d0, s0, __hmul2(d1, s1)));
+                                }
+                            } else {
+                                float s0, s1;
+                                load_chunk_scales<SCALE_MODE>(sc_row, j, group, s0, s1);
+#pragma unroll
+                                for (int m = 0; m < M_TILE; ++m) {
+                                    const float d0 = hsum2(dot16h(h0, h1, &xr[m][c][0]));
+                                    const float d1 = hsum2(dot16h(h2, h3, &xr[m][c][8]));
+                                    acc[g * M_TILE + m] = fmaf(d0, s0, acc[g * M_TILE + m]);
+                                    acc[g * M_TILE + m] = fmaf(d1, s1, acc[g * M_TILE + m]);
+                                }
+                            }
+                        }
                     }
                 }
             }
-#pragma unroll
-            for (int m = 0; m < M_TILE; ++m) acc[m] = warp_sum(acc[m]);
-            if (lane == 0) {
-#pragma unroll
-                for (int m = 0; m < M_TILE; ++m) pt[(r * KP + kp) * M_TILE + m] = acc[m];
+            const float total = warp_sum4(acc, lane);
+            if ((lane & 7) == 0) {
+                const int idx = lane >> 3;
+                const int r = rbase + (idx / M_TILE) * RW;
+                if (r < rows) pt[(r * KP + kp) * M_TILE + (idx % M_TILE)] = total;
             }
         }
         __syncthreads();  // partial sums visible; every thread is done with stage s
@@ -316,7 +391,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_rowmajor_kernel(const __grid
             if (m0 + m < P.M) {
                 float v = 0.0f;
                 for (int q = 0; q < KP; ++q) v += pt[(r * KP + q) * M_TILE + m];
-                v *= pr.global_scale;
+                v *= scales_in_half<SCALE_MODE>() ? pr.global_scale * (1.0f / kXPrescale) : pr.global_scale;
                 if (pr.bias != nullptr) v += load_as_float(pr.bias, P.bias_dtype, row0 + r);
                 v = apply_activation(v, P.activation);
                 store_from_float(pr.out, P.out_dtype, static_cast<size_t>(m0 + m) * pr.N + row0 + r, v);
@@ -463,6 +538,10 @@ int run_gemv(int fmt, const HostProblem* probs, int count, int x_dtype, int scal
     P.out_dtype = out_dtype;
     P.activation = activation;
     P.group = group;
+    long long weight_bytes = 0;
+    for (int i = 0; i < count; ++i) weight_bytes += static_cast<long long>(probs[i].N) * (probs[i].K / 2);
+    const long long target_tile_bytes =
+        std::min<long long>(kWStage, std::max<long long>(4096, weight_bytes / (16LL * sms)));
     int tiles = 0;
     for (int i = 0; i < count; ++i) {
         const HostProblem& h = probs[i];
@@ -487,9 +566,10 @@ int run_gemv(int fmt, const HostProblem* probs, int count, int x_dtype, int scal
         int rmax = std::min({kMaxTileRows, kWStage / row_bytes, kMaxPartials / kparts});
         rmax = std::max(rw, rmax / rw * rw);
         TPB_REQUIRE(rmax * row_bytes <= kWStage, TPB200_ERR_SHAPE);
-        // aim for at least two tiles per SM so that every SM streams, but keep tiles >= one row per warp
-        int target = (h.N / (2 * sms)) / rw * rw;
-        int R = std::min(rmax, std::max(rw, target));
+        // tile bytes: the whole launch split into ~8 tiles per CTA (2 CTAs per SM), within 4..16 KB,
+        // and at least one row per row-warp
+        const int target_rows = static_cast<int>(target_tile_bytes / row_bytes) / rw * rw;
+        int R = std::min(rmax, std::max(rw, target_rows));
         d.scales_by_tma = (d.scale_row_bytes % 16 == 0) && (R * d.scale_row_bytes <= kSStage) ? 1 : 0;
         d.rows_per_tile = R;
         d.tile_begin = tiles;

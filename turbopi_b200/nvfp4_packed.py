@@ -123,7 +123,7 @@ class NVFP4PackedLinear(nn.Module):
                 raise ValueError(f"unknown format {fmt!r}")
             if linear.bias is not None:
                 layer.bias.copy_(linear.bias)
-        return layer
+        return layer.to(linear.weight.device)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         batch_shape = x.shape[:-1]
