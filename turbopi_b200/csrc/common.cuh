@@ -23,6 +23,7 @@ static __device__ int g_device_error = 0;
 enum DeviceErrorCode : int {
     kErrNone = 0,
     kErrGemvFullBarrierTimeout = 101,
+    kErrGemvEmptyBarrierTimeout = 102,
     kErrGemmTmaBarrierTimeout = 201,
     kErrGemmMmaBarrierTimeout = 202,
     kErrGemmEpilogueBarrierTimeout = 203,

@@ -228,6 +228,59 @@ __device__ __forceinline__ float warp_sum4(const float (&v)[4], int lane) {
     return k;
 }
 
+// Per-lane partial sums of one group of RG = 4 / M_TILE rows (rbase, rbase + RW, ...) over the
+// lane's chunk columns of K-part `kp`: acc[g * M_TILE + m].
+template <int FMT, int SCALE_MODE, int M_TILE, int CPL>
+__device__ __forceinline__ void accumulate_row_group(float (&acc)[4], const __half2 (&xr)[M_TILE][CPL][16],
+                                                     const uint8_t* wt, const uint8_t* sc, int row_bytes,
+                                                     int scale_row_bytes, int rbase, int RW, int rows, int kp,
+                                                     int lane, int nchunks, int group) {
+    constexpr int RG = 4 / M_TILE;
+    acc[0] = acc[1] = acc[2] = acc[3] = 0.0f;
+#pragma unroll
+    for (int g = 0; g < RG; ++g) {
+        const int r = rbase + g * RW;
+        if (r < rows) {
+#pragma unroll
+            for (int c = 0; c < CPL; ++c) {
+                const int j = (kp * CPL + c) * 32 + lane;
+                if (j < nchunks) {
+                    const uint4 w = *reinterpret_cast<const uint4*>(wt + r * row_bytes + j * 16);
+                    const uint8_t* sc_row = sc + static_cast<size_t>(r) * scale_row_bytes;
+                    __half2 h0[4], h1[4], h2[4], h3[4];
+                    if (FMT == kFmtE2M1) {
+                        decode_e2m1x8(w.x, h0); decode_e2m1x8(w.y, h1);
+                        decode_e2m1x8(w.z, h2); decode_e2m1x8(w.w, h3);
+                    } else {
+                        decode_u4x8_minus8(w.x, h0); decode_u4x8_minus8(w.y, h1);
+                        decode_u4x8_minus8(w.z, h2); decode_u4x8_minus8(w.w, h3);
+                    }
+                    if (scales_in_half<SCALE_MODE>()) {
+                        __half2 s0, s1;
+                        load_chunk_scales_h2<SCALE_MODE>(sc_row, j, s0, s1);
+#pragma unroll
+                        for (int m = 0; m < M_TILE; ++m) {
+                            const __half2 d0 = dot16h(h0, h1, &xr[m][c][0]);
+                            const __half2 d1 = dot16h(h2, h3, &xr[m][c][8]);
+                            acc[g * M_TILE + m] += hsum2(__hfma2(d0, s0, __hmul2(d1, s1)));
+                        }
+                    } else {
+                        float s0, s1;
+                        load_chunk_scales<SCALE_MODE>(sc_row, j, group, s0, s1);
+#pragma unroll
+                        for (int m = 0; m < M_TILE; ++m) {
+                            const float d0 = hsum2(dot16h(h0, h1, &xr[m][c][0]));
+                            const float d1 = hsum2(dot16h(h2, h3, &xr[m][c][8]));
+                            acc[g * M_TILE + m] = fmaf(d0, s0, acc[g * M_TILE + m]);
+                            acc[g * M_TILE + m] = fmaf(d1, s1, acc[g * M_TILE + m]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+}
+
 template <int FMT, int SCALE_MODE, int M_TILE, int CPL, int MAXP>
 __global__ void __launch_bounds__(kThreads, 2) gemv_rowmajor_kernel(const __grid_constant__ GemvParams<MAXP> P) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -332,49 +385,9 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_rowmajor_kernel(const __grid
         // (row, m) sums of a group are reduced over the warp together.
         constexpr int RG = 4 / M_TILE;
         for (int rbase = rw; rbase < rows; rbase += RW * RG) {
-            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // index g * M_TILE + m
-#pragma unroll
-            for (int g = 0; g < RG; ++g) {
-                const int r = rbase + g * RW;
-                if (r < rows) {
-#pragma unroll
-                    for (int c = 0; c < CPL; ++c) {
-                        const int j = (kp * CPL + c) * 32 + lane;
-                        if (j < nchunks) {
-                            const uint4 w = *reinterpret_cast<const uint4*>(wt + r * row_bytes + j * 16);
-                            const uint8_t* sc_row = sc + static_cast<size_t>(r) * pr.scale_row_bytes;
-                            __half2 h0[4], h1[4], h2[4], h3[4];
-                            if (FMT == kFmtE2M1) {
-                                decode_e2m1x8(w.x, h0); decode_e2m1x8(w.y, h1);
-                                decode_e2m1x8(w.z, h2); decode_e2m1x8(w.w, h3);
-                            } else {
-                                decode_u4x8_minus8(w.x, h0); decode_u4x8_minus8(w.y, h1);
-                                decode_u4x8_minus8(w.z, h2); decode_u4x8_minus8(w.w, h3);
-                            }
-                            if (scales_in_half<SCALE_MODE>()) {
-                                __half2 s0, s1;
-                                load_chunk_scales_h2<SCALE_MODE>(sc_row, j, s0, s1);
-#pragma unroll
-                                for (int m = 0; m < M_TILE; ++m) {
-                                    const __half2 d0 = dot16h(h0, h1, &xr[m][c][0]);
-                                    const __half2 d1 = dot16h(h2, h3, &xr[m][c][8]);
-                                    acc[g * M_TILE + m] += hsum2(__hfma2(d0, s0, __hmul2(d1, s1)));
-                                }
-                            } else {
-                                float s0, s1;
-                                load_chunk_scales<SCALE_MODE>(sc_row, j, group, s0, s1);
-#pragma unroll
-                                for (int m = 0; m < M_TILE; ++m) {
-                                    const float d0 = hsum2(dot16h(h0, h1, &xr[m][c][0]));
-                                    const float d1 = hsum2(dot16h(h2, h3, &xr[m][c][8]));
-                                    acc[g * M_TILE + m] = fmaf(d0, s0, acc[g * M_TILE + m]);
-                                    acc[g * M_TILE + m] = fmaf(d1, s1, acc[g * M_TILE + m]);
-                                }
-                            }
-                        }
-                    }
-                }
-            }
+            float acc[4];
+            accumulate_row_group<FMT, SCALE_MODE, M_TILE, CPL>(acc, xr, wt, sc, row_bytes, pr.scale_row_bytes, rbase, RW,
+                                                               rows, kp, lane, nchunks, group);
             const float total = warp_sum4(acc, lane);
             if ((lane & 7) == 0) {
                 const int idx = lane >> 3;
@@ -397,6 +410,129 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_rowmajor_kernel(const __grid
                 store_from_float(pr.out, P.out_dtype, static_cast<size_t>(m0 + m) * pr.N + row0 + r, v);
             }
         }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// Warp-specialised variant for launches in which no row is split across warps (every problem has
+// kparts == 1, i.e. K <= 1024 * CPL): eight consumer warps and one producer warp per CTA, and no
+// CTA-wide barrier in the tile loop.  The producer lane refills a stage as soon as all eight
+// consumer warps have released it (an `empty` mbarrier per stage), so warps drift apart freely;
+// each warp reduces and stores its own rows.
+// ---------------------------------------------------------------------------------------------
+constexpr int kWsThreads = kThreads + 32;
+
+template <int FMT, int SCALE_MODE, int M_TILE, int CPL, int MAXP>
+__global__ void __launch_bounds__(kWsThreads, 2) gemv_rowmajor_ws_kernel(const __grid_constant__ GemvParams<MAXP> P) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint8_t* wst = smem;
+    uint8_t* sst = smem + kStages * kWStage;
+    uint64_t* full = reinterpret_cast<uint64_t*>(sst + kStages * kSStage);
+    uint64_t* empty = full + kStages;
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const int total_tiles = P.total_tiles;
+    const int m0 = blockIdx.y * M_TILE;
+    const int group = P.group;
+    const int tile_lo = static_cast<int>(static_cast<long long>(blockIdx.x) * total_tiles / gridDim.x);
+    const int tile_hi = static_cast<int>(static_cast<long long>(blockIdx.x + 1) * total_tiles / gridDim.x);
+
+    if (tid == 0) {
+#pragma unroll
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], kWarps);
+        }
+        fence_mbar_init();
+    }
+    __syncthreads();
+    pdl_launch_dependents();
+
+    if (warp == kWarps) {
+        // ---------------- producer: one lane streams this CTA's tiles through the ring ----------------
+        if (lane == 0) {
+            int ip = 0;
+            for (int it = 0; tile_lo + it < tile_hi; ++it) {
+                const int tile = tile_lo + it;
+                const int s = it % kStages;
+                if (it >= kStages && !mbar_wait_bounded(&empty[s], ((it / kStages) - 1) & 1)) {
+                    record_error(kErrGemvEmptyBarrierTimeout);
+                    break;
+                }
+                while (ip + 1 < P.num_problems && tile >= P.prob[ip + 1].tile_begin) ++ip;
+                const ProblemDev& pr = P.prob[ip];
+                const int row0 = (tile - pr.tile_begin) * pr.rows_per_tile;
+                const int rows = min(pr.rows_per_tile, pr.N - row0);
+                const int row_bytes = pr.K >> 1;
+                const uint32_t wbytes = static_cast<uint32_t>(rows) * row_bytes;
+                const uint32_t sbytes = pr.scales_by_tma ? static_cast<uint32_t>(rows) * pr.scale_row_bytes : 0u;
+                mbar_expect_tx(&full[s], wbytes + sbytes);
+                bulk_copy_g2s(wst + s * kWStage, pr.w + static_cast<size_t>(row0) * row_bytes, wbytes, &full[s]);
+                if (sbytes) {
+                    bulk_copy_g2s(sst + s * kSStage, pr.scales + static_cast<size_t>(row0) * pr.scale_row_bytes,
+                                  sbytes, &full[s]);
+                }
+            }
+        }
+        return;
+    }
+
+    // ---------------- consumers ----------------
+    pdl_wait_prior_grids();  // activations and the output buffer belong to earlier kernels until here
+    __half2 xr[M_TILE][CPL][16];
+    int p = 0, cur_p = -1, nchunks = 0;
+    constexpr int RG = 4 / M_TILE;
+    for (int it = 0; tile_lo + it < tile_hi; ++it) {
+        const int tile = tile_lo + it;
+        while (p + 1 < P.num_problems && tile >= P.prob[p + 1].tile_begin) ++p;
+        const ProblemDev& pr = P.prob[p];
+        if (p != cur_p) {
+            cur_p = p;
+            nchunks = pr.K >> 5;
+#pragma unroll
+            for (int m = 0; m < M_TILE; ++m) {
+#pragma unroll
+                for (int c = 0; c < CPL; ++c) {
+                    const int j = c * 32 + lane;
+                    load_x_chunk<FMT>(xr[m][c], pr.x, pr.x_scales, P.x_dtype, static_cast<size_t>(m0 + m) * pr.K, j,
+                                      group, (j < nchunks) && (m0 + m < P.M),
+                                      scales_in_half<SCALE_MODE>() ? kXPrescale : 1.0f);
+                }
+            }
+        }
+        const int row0 = (tile - pr.tile_begin) * pr.rows_per_tile;
+        const int rows = min(pr.rows_per_tile, pr.N - row0);
+        const int row_bytes = pr.K >> 1;
+        const int s = it % kStages;
+        if (!mbar_wait_bounded(&full[s], (it / kStages) & 1)) {
+            record_error(kErrGemvFullBarrierTimeout);
+            break;
+        }
+        const uint8_t* wt = wst + s * kWStage;
+        const uint8_t* sc = pr.scales_by_tma ? (sst + s * kSStage)
+                                             : (pr.scales + static_cast<size_t>(row0) * pr.scale_row_bytes);
+        const float out_scale = scales_in_half<SCALE_MODE>() ? pr.global_scale * (1.0f / kXPrescale) : pr.global_scale;
+        for (int rbase = warp; rbase < rows; rbase += kWarps * RG) {
+            float acc[4];
+            accumulate_row_group<FMT, SCALE_MODE, M_TILE, CPL>(acc, xr, wt, sc, row_bytes, pr.scale_row_bytes, rbase,
+                                                               kWarps, rows, 0, lane, nchunks, group);
+            float v = warp_sum4(acc, lane);
+            if ((lane & 7) == 0) {
+                const int idx = lane >> 3;
+                const int r = rbase + (idx / M_TILE) * kWarps;
+                const int m = idx % M_TILE;
+                if (r < rows && m0 + m < P.M) {
+                    v *= out_scale;
+                    if (pr.bias != nullptr) v += load_as_float(pr.bias, P.bias_dtype, row0 + r);
+                    v = apply_activation(v, P.activation);
+                    store_from_float(pr.out, P.out_dtype, static_cast<size_t>(m0 + m) * pr.N + row0 + r, v);
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);  // this warp is done reading stage s
     }
 }
 
@@ -439,15 +575,12 @@ bool make_plan(int M, int maxK, Plan& plan) {
     return false;
 }
 
-template <int FMT, int SCALE_MODE, int M_TILE, int CPL, int MAXP>
-int launch_instance(const GemvParams<MAXP>& P, int grid_x, int grid_y, int flags, cudaStream_t stream) {
-    auto kernel = gemv_rowmajor_kernel<FMT, SCALE_MODE, M_TILE, CPL, MAXP>;
-    const size_t smem = kStages * (kWStage + kSStage) + 2 * kMaxPartials * M_TILE * sizeof(float) +
-                        kStages * sizeof(uint64_t) + 16;
-    static std::atomic<uint64_t> configured{0};  // bit d: attribute set on device d
+template <typename Kernel, typename Params>
+int launch_kernel(Kernel kernel, const Params& P, int threads, size_t smem, std::atomic<uint64_t>& configured,
+                  int grid_x, int grid_y, int flags, cudaStream_t stream) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return TPB200_ERR_CUDA;
-    const uint64_t bit = 1ull << (dev & 63);
+    const uint64_t bit = 1ull << (dev & 63);  // bit d: attribute set on device d
     if (!(configured.load(std::memory_order_relaxed) & bit)) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
             cudaSuccess) {
@@ -457,7 +590,7 @@ int launch_instance(const GemvParams<MAXP>& P, int grid_x, int grid_y, int flags
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid_x, grid_y, 1);
-    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.blockDim = dim3(threads, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -471,12 +604,28 @@ int launch_instance(const GemvParams<MAXP>& P, int grid_x, int grid_y, int flags
     return TPB200_OK;
 }
 
+template <int FMT, int SCALE_MODE, int M_TILE, int CPL, int MAXP>
+int launch_instance(const GemvParams<MAXP>& P, bool warp_specialised, int grid_x, int grid_y, int flags,
+                    cudaStream_t stream) {
+    if (warp_specialised) {
+        static std::atomic<uint64_t> configured_ws{0};
+        const size_t smem = kStages * (kWStage + kSStage) + 2 * kStages * sizeof(uint64_t);
+        return launch_kernel(gemv_rowmajor_ws_kernel<FMT, SCALE_MODE, M_TILE, CPL, MAXP>, P, kWsThreads, smem,
+                             configured_ws, grid_x, grid_y, flags, stream);
+    }
+    static std::atomic<uint64_t> configured{0};
+    const size_t smem = kStages * (kWStage + kSStage) + 2 * kMaxPartials * M_TILE * sizeof(float) +
+                        kStages * sizeof(uint64_t) + 16;
+    return launch_kernel(gemv_rowmajor_kernel<FMT, SCALE_MODE, M_TILE, CPL, MAXP>, P, kThreads, smem, configured,
+                         grid_x, grid_y, flags, stream);
+}
+
 template <int FMT, int SCALE_MODE, int MAXP>
-int dispatch_tiles(const GemvParams<MAXP>& P, const Plan& plan, int grid_x, int grid_y, int flags,
+int dispatch_tiles(const GemvParams<MAXP>& P, const Plan& plan, bool ws, int grid_x, int grid_y, int flags,
                    cudaStream_t stream) {
 #define TPB_CASE(MT, C)                              \
     if (plan.m_tile == MT && plan.cpl == C)          \
-        return launch_instance<FMT, SCALE_MODE, MT, C, MAXP>(P, grid_x, grid_y, flags, stream);
+        return launch_instance<FMT, SCALE_MODE, MT, C, MAXP>(P, ws, grid_x, grid_y, flags, stream);
     TPB_CASE(1, 1) TPB_CASE(1, 2) TPB_CASE(1, 4) TPB_CASE(2, 1) TPB_CASE(2, 2) TPB_CASE(4, 1)
 #undef TPB_CASE
     return TPB200_ERR_SHAPE;
@@ -576,11 +725,13 @@ int run_gemv(int fmt, const HostProblem* probs, int count, int x_dtype, int scal
         tiles += (h.N + R - 1) / R;
     }
     P.total_tiles = tiles;
+    bool ws = true;  // no row split across warps anywhere in the launch -> warp-specialised kernel
+    for (int i = 0; i < count; ++i) ws = ws && (P.prob[i].kparts == 1);
     const int grid_x = std::min(tiles, 2 * sms);
     const int grid_y = (M + plan.m_tile - 1) / plan.m_tile;
 
 #define TPB_MODE(F, S) \
-    if (fmt == F && scale_mode == S) return dispatch_tiles<F, S, MAXP>(P, plan, grid_x, grid_y, flags, stream);
+    if (fmt == F && scale_mode == S) return dispatch_tiles<F, S, MAXP>(P, plan, ws, grid_x, grid_y, flags, stream);
     TPB_MODE(kFmtE2M1, kScE4M3B16)
     TPB_MODE(kFmtE2M1, kScF32B32)
     if (MAXP == 1) {
