@@ -120,6 +120,26 @@ int tpb200_nvfp4_gemv_grouped(const tpb200_gemv_problem* problems, int count, in
                               int flags, tpb200_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * NVFP4 x NVFP4 block-scaled GEMM on tcgen05 tensor cores (prefix shapes, any M):
+ *   out[M, N] = act(alpha * sum_k (a[m,k] sfa[m,k/16]) * (b[n,k] sfb[n,k/16]) + bias[n])
+ * a_packed [M, a_pitch] / b_packed [N, b_pitch] bytes: e2m1 codes two per byte (even k low), pitches
+ * multiples of 16 bytes; a_sf / b_sf: UE4M3 scales per 16 along K in 512-byte atoms of 128 rows x
+ * 4 K-blocks (byte (r%32)*16 + (r/32)*4 + kb inside an atom), atoms ordered [row tile][K atom] with
+ * K padded to a multiple of 256 -- tpb200_nvfp4_sf_bytes() gives the buffer size, padding scales
+ * must be 0.  N % 8 == 0, K % 16 == 0.  bf16 or fp32 output with leading dimension ldo.
+ * Replaces nvfp4_gemm.gemm / gemm_prepared / reorder_scales
+ * (openpi/src/openpi/models_pytorch/nvfp4_extension/nvfp4_gemm.cu:216-304,330-429,451-549).
+ * tpb200_nvfp4_quantize_act produces the A operand from bf16/fp16/fp32 activations with the
+ * reference's per-block recipe (openpi/src/openpi/models_pytorch/nvfp4_mlp.py:88-173,606-608).
+ * ------------------------------------------------------------------------------------------- */
+size_t tpb200_nvfp4_sf_bytes(int rows, int K);
+int tpb200_nvfp4_quantize_act(const void* x, int x_dtype, int ldx, void* packed, int packed_pitch,
+                              void* sf_swizzled, int M, int K, tpb200_stream_t stream);
+int tpb200_nvfp4_gemm(const void* a_packed, int a_pitch, const void* a_sf, const void* b_packed, int b_pitch,
+                      const void* b_sf, float alpha, const void* bias_f32, int activation, void* out,
+                      int out_dtype, int ldo, int M, int N, int K, int flags, tpb200_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Entry points with the reference's names and signatures (TensorRT-plugin / test ABI).
  * ------------------------------------------------------------------------------------------- */
 

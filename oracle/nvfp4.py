@@ -273,7 +273,7 @@ def linear_sim(x, w_q, w_scales, block_size=BLOCK_SIZE, bias=None, quantize_act=
     return y
 
 
-def swizzle_scales_128x4(scales_bytes):
+def swizzle_scales_128x4(scales_bytes, kb_multiple=4):
     """Scale-factor bytes (rows, kblocks) -> the 128-row x 4-k-block interleaved atom
     order described in openpi/src/openpi/models_pytorch/nvfp4_mlp.py:224-288: rows
     padded to 128, k-blocks to 4; tile order (k-tile outer... see below), inside a
@@ -281,11 +281,12 @@ def swizzle_scales_128x4(scales_bytes):
     (r % 32) * 16 + (r // 32) * 4 + kb.
 
     Tiles are laid out row-tile major, k-tile minor (each tile 512 bytes), which
-    is the order the tcgen05 scale-factor copy consumes them in."""
+    is the order the tcgen05 scale-factor copy consumes them in.  `kb_multiple`
+    pads the k-blocks (16 for the GEMM, whose K stage is 256 elements)."""
     s = np.asarray(scales_bytes, dtype=np.uint8)
     R, KB = s.shape
     Rp = (R + 127) // 128 * 128
-    Kp = (KB + 3) // 4 * 4
+    Kp = (KB + kb_multiple - 1) // kb_multiple * kb_multiple
     pad = np.zeros((Rp, Kp), dtype=np.uint8)
     pad[:R, :KB] = s
     t = pad.reshape(Rp // 128, 4, 32, Kp // 4, 4)      # [rt, r//32, r%32, kt, kb]

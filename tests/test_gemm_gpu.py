@@ -1,0 +1,97 @@
+"""Parity of the tcgen05 NVFP4 x NVFP4 GEMM and its activation quantiser with the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import cosine, rel_err
+from oracle import formats, nvfp4
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev(a, device, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a)).to(device)
+    return t if dtype is None else t.to(dtype)
+
+
+def _pack_padded(codes_packed, pitch):
+    R, Kh = codes_packed.shape
+    out = np.zeros((R, pitch), dtype=np.uint8)
+    out[:, :Kh] = codes_packed
+    return out
+
+
+def _operand(rng, rows, K, scale):
+    """Random block-16 NVFP4 operand: (packed codes, UE4M3 scale bytes, dequantised float64)."""
+    vals = (rng.normal(size=(rows, K)) * scale).astype(np.float32)
+    q, s = nvfp4.quantize_to_nvfp4(vals, 16)
+    sb = formats.e4m3_encode(s)
+    packed = nvfp4.pack_nvfp4(q)
+    deq = nvfp4.dequantize(packed, sb, 16, 1.0, scale_is_e4m3=True).astype(np.float64)
+    return packed, sb, deq
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 256), (128, 128, 64), (1, 8, 16), (200, 264, 1024), (712, 2048, 2048),
+                                   (512, 1152, 4304), (512, 4304, 1152), (37, 4096, 1024), (712, 384, 16384)])
+def test_gemm_matches_oracle(cuda_device, M, N, K):
+    from turbopi_b200 import _lib, ops
+    rng = np.random.default_rng(M + N + K)
+    ap, asf, ad = _operand(rng, M, K, 1.0)
+    bp, bsf, bd = _operand(rng, N, K, 0.5)
+    pitch = ops.packed_pitch(K)
+    a = _dev(_pack_padded(ap, pitch), cuda_device)
+    b = _dev(_pack_padded(bp, pitch), cuda_device)
+    a_sf = _dev(nvfp4.swizzle_scales_128x4(asf, 16), cuda_device)
+    b_sf = _dev(nvfp4.swizzle_scales_128x4(bsf, 16), cuda_device)
+    assert a_sf.numel() == ops.nvfp4_sf_bytes(M, K) and b_sf.numel() == ops.nvfp4_sf_bytes(N, K)
+    assert np.array_equal(ops.swizzle_scales(_dev(bsf, cuda_device)).cpu().numpy(), b_sf.cpu().numpy())
+    bias = rng.normal(size=(N,)).astype(np.float32)
+    buf = torch.full((M + 2, N), -777.0, dtype=torch.float32, device=cuda_device)
+    out = ops.nvfp4_gemm(a, a_sf, b, b_sf, M, N, K, alpha=0.125, bias=_dev(bias, cuda_device), out=buf[1:M + 1])
+    ref = 0.125 * (ad @ bd.T) + bias
+    y = out.cpu().numpy()
+    assert _lib.load().tpb200_device_error(0) == 0
+    assert rel_err(y, ref) <= 2e-5, rel_err(y, ref)      # products of e2m1 x E4M3 are exact; only fp32 summation order
+    assert (buf[0] == -777.0).all() and (buf[-1] == -777.0).all()
+    yb = ops.nvfp4_gemm(a, a_sf, b, b_sf, M, N, K, alpha=0.125, activation=1, out_dtype=torch.bfloat16)
+    refb = nvfp4.gelu_tanh(0.125 * (ad @ bd.T))
+    assert rel_err(yb.float().cpu().numpy(), refb) <= 1e-2 and cosine(yb.float().cpu().numpy(), refb) >= 0.999
+
+
+@pytest.mark.parametrize("M,K", [(712, 2048), (5, 16), (130, 4304), (512, 1152)])
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float32])
+def test_activation_quantiser_bit_exact(cuda_device, M, K, dt):
+    """Codes and scale bytes equal the reference recipe (quantize_to_nvfp4_sim without MSE search,
+    block 16; scales rounded to E4M3) bit for bit, including zero blocks, ties and the +-2688 clamp."""
+    from turbopi_b200 import ops
+    rng = np.random.default_rng(M * K)
+    x = (rng.normal(size=(M, K)) * rng.choice([0.01, 1.0, 30.0], size=(M, 1))).astype(np.float32)
+    x[0, :16] = 0.0
+    x[min(1, M - 1), :16] = [6, 5, 3.5, 2.5, 1.75, 1.25, 0.75, 0.25, -6, -5, -3.5, -2.5, -1.75, -1.25, -0.75, -0.25]
+    x[min(2, M - 1), 0] = 1e5
+    xt = _dev(x, cuda_device, dt)
+    xr = xt.float().cpu().numpy()
+    packed, sf = ops.nvfp4_quantize_act(xt)
+    lim = np.float32(2688.0)
+    q, s = nvfp4.quantize_to_nvfp4_sim(np.clip(xr, -lim, lim), 16, use_mse_search=False)
+    ref_packed = nvfp4.pack_nvfp4_data(q)
+    assert np.array_equal(packed.cpu().numpy()[:, :K // 2], ref_packed)
+    ref_sf = nvfp4.swizzle_scales_128x4(formats.e4m3_encode(s), 16)
+    assert np.array_equal(sf.cpu().numpy(), ref_sf)
+
+
+def test_quantise_then_gemm_matches_reference_simulation(cuda_device):
+    """The full W4A4 path against NVFP4Linear._forward_simulation restated in the oracle."""
+    from turbopi_b200 import ops
+    rng = np.random.default_rng(99)
+    M, N, K = 300, 512, 2048
+    w = (rng.normal(size=(N, K)) * 0.02).astype(np.float32)
+    x = formats.round_to_bf16(rng.normal(size=(M, K)).astype(np.float32))
+    wq, ws = nvfp4.quantize_to_nvfp4_sim(w, 16, use_mse_search=False)
+    ws_b = formats.e4m3_encode(ws * np.float32(256.0))          # keep small weight scales inside E4M3's range
+    b = _dev(_pack_padded(nvfp4.pack_nvfp4_data(wq), ops.packed_pitch(K)), cuda_device)
+    b_sf = _dev(nvfp4.swizzle_scales_128x4(ws_b, 16), cuda_device)
+    a, a_sf = ops.nvfp4_quantize_act(_dev(x, cuda_device, torch.bfloat16))
+    y = ops.nvfp4_gemm(a, a_sf, b, b_sf, M, N, K, alpha=1.0 / 256.0, out_dtype=torch.float32)
+    ref = nvfp4.linear_sim(x, wq, formats.e4m3_decode(ws_b) / np.float32(256.0), 16)
+    assert rel_err(y.cpu().numpy(), ref) <= 1e-4

@@ -40,6 +40,10 @@ SIGNATURES = {
                                   c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "tpb200_nvfp4_gemv_grouped": (c_int, [ctypes.POINTER(GemvProblem), c_int, c_int, c_int, c_int, c_int, c_int,
                                           c_int, c_int, c_int, c_void_p]),
+    "tpb200_nvfp4_sf_bytes": (c_size_t, [c_int, c_int]),
+    "tpb200_nvfp4_quantize_act": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]),
+    "tpb200_nvfp4_gemm": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_float, c_void_p, c_int,
+                                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "nvfp4_gemv_forward": (None, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                   c_int, c_int, c_void_p]),
     "nvfp4_gemv_workspace_size": (c_size_t, [c_int, c_int, c_int]),

@@ -1,0 +1,426 @@
+// NVFP4 x NVFP4 block-scaled GEMM on the 5th-generation tensor cores:
+//   out[M, N] = act(alpha * sum_k (a[m,k] * sfa[m,k/16]) * (b[n,k] * sfb[n,k/16]) + bias[n])
+// a, b: e2m1 codes, two per byte (even k in the low nibble), K-major; sfa, sfb: UE4M3 per 16
+// along K, stored in 512-byte atoms of 128 rows x 4 K-blocks (byte (r%32)*16 + (r/32)*4 + kb),
+// atoms ordered [row tile][K atom].
+//
+// One persistent CTA per SM, warp-specialised:
+//   warp 0     TMA producer: per 256-wide K stage one 128B-swizzled box of A (128 rows) and of
+//              B (128 rows) plus the two 2 KB scale slabs (plain bulk copies), 5-stage ring;
+//   warp 1     allocates tensor memory; one lane copies the stage's scale atoms shared->tensor
+//              memory (tcgen05.cp) and issues 4 tcgen05.mma kind::mxf4nvf4 (K = 64 each) into
+//              one of two 128x128 fp32 accumulators, committing the stage back to the producer;
+//   warps 2-5  epilogue: tcgen05.ld 32 columns at a time, alpha / bias / GELU, convert, 16-byte
+//              stores; the accumulator is handed back as soon as it has been read.
+// No multicast, no cluster; every wait is bounded and reports through the device error word.
+#include <algorithm>
+#include <atomic>
+
+#include "tcgen05.cuh"
+
+namespace tpb {
+namespace {
+
+constexpr int kBM = 128;
+constexpr int kBN = 128;
+constexpr int kBKBytes = 128;            // 256 e2m1 codes per row per stage
+constexpr int kStages = 5;
+constexpr int kATile = kBM * kBKBytes;   // 16 KB
+constexpr int kBTile = kBN * kBKBytes;   // 16 KB
+constexpr int kSfSlab = 4 * 512;         // 4 K-atoms of one 128-row tile
+constexpr int kStageBytes = kATile + kBTile + 2 * kSfSlab;
+constexpr int kThreads = 192;
+constexpr int kTmemCols = 512;
+constexpr int kAccCols = kBN;            // fp32 accumulator columns per buffer
+constexpr uint32_t kSfaCol = 2 * kAccCols;
+constexpr uint32_t kSfbCol = kSfaCol + 16;
+
+struct alignas(64) GemmParams {
+    CUtensorMap map_a;
+    CUtensorMap map_b;
+    const uint8_t* sfa;
+    const uint8_t* sfb;
+    const float* bias;
+    void* out;
+    int M, N, K;
+    int ldo;
+    int out_dtype;
+    int activation;
+    float alpha;
+    int k_stages;   // ceil(K / 256)
+    int m_blocks, n_blocks;
+};
+
+struct SharedControl {
+    uint64_t full[kStages];
+    uint64_t empty[kStages];
+    uint64_t acc_full[2];
+    uint64_t acc_empty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+__global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_constant__ GemmParams P) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    SharedControl* ctl = reinterpret_cast<SharedControl*>(smem + kStages * kStageBytes);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int total_tiles = P.m_blocks * P.n_blocks;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&ctl->full[s], 1);
+            mbar_init(&ctl->empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&ctl->acc_full[b], 1);
+            mbar_init(&ctl->acc_empty[b], 4);
+        }
+        ctl->abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tc::tmem_alloc(&ctl->tmem_base, kTmemCols);
+        tc::tmem_relinquish();
+    }
+    tc::fence_before_thread_sync();
+    __syncthreads();
+    tc::fence_after_thread_sync();
+    const uint32_t tmem_base = ctl->tmem_base;
+    volatile int* abort_flag = &ctl->abort_flag;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            tc::prefetch_tensormap(&P.map_a);
+            tc::prefetch_tensormap(&P.map_b);
+            const int sf_row_stride = P.k_stages * kSfSlab;   // bytes per 128-row tile of scales
+            int it = 0;
+            for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
+                const int m_blk = tile % P.m_blocks;
+                const int n_blk = tile / P.m_blocks;
+                for (int ks = 0; ks < P.k_stages; ++ks, ++it) {
+                    const int s = it % kStages;
+                    if (it >= kStages && !mbar_wait_bounded(&ctl->empty[s], ((it / kStages) - 1) & 1)) {
+                        record_error(kErrGemmEmptyBarrierTimeout);
+                        *abort_flag = 1;
+                        break;
+                    }
+                    uint8_t* st = smem + s * kStageBytes;
+                    mbar_expect_tx(&ctl->full[s], kStageBytes);
+                    tc::tma_load_2d(st, &P.map_a, ks * kBKBytes, m_blk * kBM, &ctl->full[s]);
+                    tc::tma_load_2d(st + kATile, &P.map_b, ks * kBKBytes, n_blk * kBN, &ctl->full[s]);
+                    bulk_copy_g2s(st + kATile + kBTile,
+                                  P.sfa + static_cast<size_t>(m_blk) * sf_row_stride + static_cast<size_t>(ks) * kSfSlab,
+                                  kSfSlab, &ctl->full[s]);
+                    bulk_copy_g2s(st + kATile + kBTile + kSfSlab,
+                                  P.sfb + static_cast<size_t>(n_blk) * sf_row_stride + static_cast<size_t>(ks) * kSfSlab,
+                                  kSfSlab, &ctl->full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = tc::make_idesc_mxf4nvf4(kBN);
+            int it = 0, tile_iter = 0;
+            for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++tile_iter) {
+                const int buf = tile_iter & 1;
+                if (tile_iter >= 2 && !mbar_wait_bounded(&ctl->acc_empty[buf], ((tile_iter >> 1) - 1) & 1)) {
+                    record_error(kErrGemmEpilogueBarrierTimeout);
+                    *abort_flag = 1;
+                    break;
+                }
+                tc::fence_after_thread_sync();
+                const uint32_t tmem_acc = tmem_base + buf * kAccCols;
+                for (int ks = 0; ks < P.k_stages; ++ks, ++it) {
+                    const int s = it % kStages;
+                    if (!mbar_wait_bounded(&ctl->full[s], (it / kStages) & 1)) {
+                        record_error(kErrGemmTmaBarrierTimeout);
+                        *abort_flag = 1;
+                        break;
+                    }
+                    tc::fence_after_thread_sync();
+                    const uint32_t st = smem_u32(smem + s * kStageBytes);
+                    const uint32_t sfa_s = st + kATile + kBTile;
+                    const uint32_t sfb_s = sfa_s + kSfSlab;
+#pragma unroll
+                    for (int a = 0; a < 4; ++a) {
+                        tc::cp_sf_32x128b(tmem_base + kSfaCol + 4 * a, tc::make_sf_desc(sfa_s + a * 512));
+                        tc::cp_sf_32x128b(tmem_base + kSfbCol + 4 * a, tc::make_sf_desc(sfb_s + a * 512));
+                    }
+#pragma unroll
+                    for (int a = 0; a < 4; ++a) {
+                        tc::mma_mxf4nvf4(tmem_acc, tc::make_kmajor_sw128_desc(st, a * 32),
+                                         tc::make_kmajor_sw128_desc(st + kATile, a * 32), idesc,
+                                         tmem_base + kSfaCol + 4 * a, tmem_base + kSfbCol + 4 * a, (ks | a) != 0);
+                    }
+                    tc::commit(&ctl->empty[s]);   // stage s may be refilled once these MMAs have read it
+                }
+                tc::commit(&ctl->acc_full[buf]);  // accumulator complete
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2..5)
+        const int q = warp & 3;                       // tensor-memory lane quarter this warp may read
+        int tile_iter = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++tile_iter) {
+            const int m_blk = tile % P.m_blocks;
+            const int n_blk = tile / P.m_blocks;
+            const int buf = tile_iter & 1;
+            if (!mbar_wait_bounded(&ctl->acc_full[buf], (tile_iter >> 1) & 1)) {
+                record_error(kErrGemmMmaBarrierTimeout);
+                *abort_flag = 1;
+                break;
+            }
+            tc::fence_after_thread_sync();
+            const int m = m_blk * kBM + q * 32 + lane;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * kAccCols;
+#pragma unroll 1
+            for (int c = 0; c < kBN / 32; ++c) {
+                uint32_t r[32];
+                tc::tmem_ld_32x32b_x32(taddr + c * 32, r);
+                tc::tmem_ld_wait();
+                if (c == kBN / 32 - 1) {
+                    // everything this warp needs from the accumulator is in registers
+                    tc::fence_before_thread_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&ctl->acc_empty[buf]);
+                }
+                const int n0 = n_blk * kBN + c * 32;
+                if (m < P.M) {
+                    float v[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        float f = __uint_as_float(r[i]) * P.alpha;
+                        if (P.bias != nullptr && n0 + i < P.N) f += __ldg(P.bias + n0 + i);
+                        v[i] = apply_activation(f, P.activation);
+                    }
+                    if (P.out_dtype == TPB200_BF16) {
+                        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(P.out) + static_cast<size_t>(m) * P.ldo + n0;
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            if (n0 + g * 8 + 8 <= P.N) {
+                                uint32_t w[4];
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    __nv_bfloat162 b2 = __floats2bfloat162_rn(v[g * 8 + 2 * i], v[g * 8 + 2 * i + 1]);
+                                    w[i] = *reinterpret_cast<uint32_t*>(&b2);
+                                }
+                                *reinterpret_cast<uint4*>(dst + g * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                            }
+                        }
+                    } else {
+                        float* dst = static_cast<float*>(P.out) + static_cast<size_t>(m) * P.ldo + n0;
+#pragma unroll
+                        for (int g = 0; g < 8; ++g) {
+                            if (n0 + g * 4 + 4 <= P.N) {
+                                *reinterpret_cast<float4*>(dst + g * 4) =
+                                    make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    tc::fence_before_thread_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc::fence_after_thread_sync();
+        tc::tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Activation quantiser: x [M, K] -> e2m1 codes [M, pitch] + UE4M3 scales in the atom layout.
+// One thread per 16-element block over the PADDED scale domain, so padding scales are zeroed.
+// Codes follow the reference's simulation quantiser
+// (openpi/src/openpi/models_pytorch/nvfp4_mlp.py:88-173 with use_mse_search=False):
+//   sf = max(blockmax, 1e-12) / 6;  scaled = x / max(sf * 6, 1e-12) * 6, clamped to +-6;
+//   nearest e2m1 magnitude (ties to the lower); a value that rounds to 0 is stored as +0.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t e2m1_index(float a) {
+    return (a > 0.25f) + (a > 0.75f) + (a > 1.25f) + (a > 1.75f) + (a > 2.5f) + (a > 3.5f) + (a > 5.0f);
+}
+
+__global__ void nvfp4_quantize_act_kernel(const void* __restrict__ x, int x_dtype, int ldx, uint8_t* __restrict__ packed,
+                                          int pitch, uint8_t* __restrict__ sf, int M, int K, int rows_pad,
+                                          int kb_pad) {
+    const long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (t >= static_cast<long long>(rows_pad) * kb_pad) return;
+    const int row = static_cast<int>(t / kb_pad);
+    const int kb = static_cast<int>(t % kb_pad);
+    const size_t sf_off = (static_cast<size_t>(row >> 7) * (kb_pad >> 2) + (kb >> 2)) * 512 + (row & 31) * 16 +
+                          ((row >> 5) & 3) * 4 + (kb & 3);
+    if (row >= M || kb * 16 >= K) {
+        sf[sf_off] = 0;
+        return;
+    }
+    float v[16];
+    const size_t e0 = static_cast<size_t>(row) * ldx + static_cast<size_t>(kb) * 16;
+    if (x_dtype == TPB200_F32) {
+        const float4* p = reinterpret_cast<const float4*>(static_cast<const float*>(x) + e0);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float4 f = __ldg(p + i);
+            v[4 * i] = f.x; v[4 * i + 1] = f.y; v[4 * i + 2] = f.z; v[4 * i + 3] = f.w;
+        }
+    } else {
+        const uint4* p = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(x) + e0);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            uint4 u = __ldg(p + i);
+            const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float2 f = x_dtype == TPB200_F16 ? __half22float2(*reinterpret_cast<const __half2*>(&w[j]))
+                                                 : __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
+                v[8 * i + 2 * j] = f.x;
+                v[8 * i + 2 * j + 1] = f.y;
+            }
+        }
+    }
+    const float lim = 2688.0f;   // 448 * 6: keeps the block scale inside E4M3 (nvfp4_mlp.py:606-608)
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        v[i] = fminf(fmaxf(v[i], -lim), lim);
+        amax = fmaxf(amax, fabsf(v[i]));
+    }
+    const float sfv = __fdiv_rn(fmaxf(amax, 1e-12f), 6.0f);
+    const float denom = fmaxf(__fmul_rn(sfv, 6.0f), 1e-12f);
+    sf[sf_off] = encode_e4m3(sfv);
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        float s = __fmul_rn(__fdiv_rn(v[i], denom), 6.0f);
+        s = fminf(fmaxf(s, -6.0f), 6.0f);
+        const uint32_t idx = e2m1_index(fabsf(s));
+        const uint32_t code = (s < 0.0f && idx != 0) ? (idx | 8u) : idx;
+        if (i < 8) lo |= code << (4 * i);
+        else hi |= code << (4 * (i - 8));
+    }
+    *reinterpret_cast<uint2*>(packed + static_cast<size_t>(row) * pitch + kb * 8) = make_uint2(lo, hi);
+}
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn get_encode_fn() {
+    static std::atomic<EncodeFn> cached{nullptr};
+    EncodeFn fn = cached.load(std::memory_order_acquire);
+    if (fn != nullptr) return fn;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess || p == nullptr) {
+        return nullptr;
+    }
+    fn = reinterpret_cast<EncodeFn>(p);
+    cached.store(fn, std::memory_order_release);
+    return fn;
+}
+
+}  // namespace
+
+bool make_tensor_map_bytes_sw128(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_t rows,
+                                 uint64_t pitch_bytes, uint32_t box_rows) {
+    EncodeFn fn = get_encode_fn();
+    if (fn == nullptr) return false;
+    const cuuint64_t dims[2] = {row_bytes, rows};
+    const cuuint64_t strides[1] = {pitch_bytes};
+    const cuuint32_t box[2] = {128, box_rows};
+    const cuuint32_t elem_strides[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, elem_strides,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int device_error_nvfp4_gemm(int clear) { return read_device_error(clear); }
+
+}  // namespace tpb
+
+extern "C" size_t tpb200_nvfp4_sf_bytes(int rows, int K) {
+    if (rows < 1 || K < 16) return 0;
+    const size_t row_tiles = (static_cast<size_t>(rows) + 127) / 128;
+    const size_t k_stages = (static_cast<size_t>(K) + 255) / 256;
+    return row_tiles * k_stages * tpb::kSfSlab;
+}
+
+extern "C" int tpb200_nvfp4_quantize_act(const void* x, int x_dtype, int ldx, void* packed, int packed_pitch,
+                                         void* sf_swizzled, int M, int K, tpb200_stream_t stream) {
+    TPB_REQUIRE(x && packed && sf_swizzled, TPB200_ERR_NULL);
+    TPB_REQUIRE(M >= 1 && K >= 16 && K % 16 == 0 && ldx >= K, TPB200_ERR_SHAPE);
+    TPB_REQUIRE(tpb_valid_dtype(x_dtype), TPB200_ERR_ENUM);
+    TPB_REQUIRE(packed_pitch >= K / 2 && packed_pitch % 16 == 0, TPB200_ERR_ALIGN);
+    TPB_REQUIRE(tpb_aligned16(x) && tpb_aligned16(packed) && tpb_aligned16(sf_swizzled), TPB200_ERR_ALIGN);
+    TPB_REQUIRE((static_cast<long long>(ldx) * tpb_dtype_size(x_dtype)) % 16 == 0, TPB200_ERR_ALIGN);
+    const int rows_pad = (M + 127) / 128 * 128;
+    const int kb_pad = (K + 255) / 256 * 16;
+    const long long total = static_cast<long long>(rows_pad) * kb_pad;
+    const int threads = 256;
+    tpb::nvfp4_quantize_act_kernel<<<static_cast<unsigned>((total + threads - 1) / threads), threads, 0,
+                                     reinterpret_cast<cudaStream_t>(stream)>>>(
+        x, x_dtype, ldx, static_cast<uint8_t*>(packed), packed_pitch, static_cast<uint8_t*>(sf_swizzled), M, K,
+        rows_pad, kb_pad);
+    return tpb_launch_status();
+}
+
+extern "C" int tpb200_nvfp4_gemm(const void* a_packed, int a_pitch, const void* a_sf, const void* b_packed,
+                                 int b_pitch, const void* b_sf, float alpha, const void* bias_f32, int activation,
+                                 void* out, int out_dtype, int ldo, int M, int N, int K, int flags,
+                                 tpb200_stream_t stream) {
+    TPB_REQUIRE(a_packed && a_sf && b_packed && b_sf && out, TPB200_ERR_NULL);
+    TPB_REQUIRE(M >= 1 && N >= 8 && N % 8 == 0 && K >= 16 && K % 16 == 0 && ldo >= N, TPB200_ERR_SHAPE);
+    TPB_REQUIRE(out_dtype == TPB200_BF16 || out_dtype == TPB200_F32, TPB200_ERR_ENUM);
+    TPB_REQUIRE(activation == TPB200_ACT_NONE || activation == TPB200_ACT_GELU || activation == TPB200_ACT_SILU,
+                TPB200_ERR_ENUM);
+    TPB_REQUIRE(flags == TPB200_FLAG_NONE, TPB200_ERR_ENUM);
+    TPB_REQUIRE(a_pitch >= K / 2 && b_pitch >= K / 2 && a_pitch % 16 == 0 && b_pitch % 16 == 0, TPB200_ERR_ALIGN);
+    TPB_REQUIRE(tpb_aligned16(a_packed) && tpb_aligned16(b_packed) && tpb_aligned16(a_sf) && tpb_aligned16(b_sf) &&
+                    tpb_aligned16(out),
+                TPB200_ERR_ALIGN);
+    TPB_REQUIRE((static_cast<long long>(ldo) * tpb_dtype_size(out_dtype)) % 16 == 0, TPB200_ERR_ALIGN);
+
+    tpb::GemmParams P;
+    if (!tpb::make_tensor_map_bytes_sw128(&P.map_a, a_packed, static_cast<uint64_t>(K) / 2, M, a_pitch, tpb::kBM) ||
+        !tpb::make_tensor_map_bytes_sw128(&P.map_b, b_packed, static_cast<uint64_t>(K) / 2, N, b_pitch, tpb::kBN)) {
+        return TPB200_ERR_CUDA;
+    }
+    P.sfa = static_cast<const uint8_t*>(a_sf);
+    P.sfb = static_cast<const uint8_t*>(b_sf);
+    P.bias = static_cast<const float*>(bias_f32);
+    P.out = out;
+    P.M = M; P.N = N; P.K = K;
+    P.ldo = ldo;
+    P.out_dtype = out_dtype;
+    P.activation = activation;
+    P.alpha = alpha;
+    P.k_stages = (K + 255) / 256;
+    P.m_blocks = (M + tpb::kBM - 1) / tpb::kBM;
+    P.n_blocks = (N + tpb::kBN - 1) / tpb::kBN;
+
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+        return TPB200_ERR_CUDA;
+    }
+    const size_t smem = tpb::kStages * tpb::kStageBytes + sizeof(tpb::SharedControl) + 1024;
+    static std::atomic<uint64_t> configured{0};
+    const uint64_t bit = 1ull << (dev & 63);
+    if (!(configured.load(std::memory_order_relaxed) & bit)) {
+        if (cudaFuncSetAttribute(tpb::nvfp4_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(smem)) != cudaSuccess) {
+            return TPB200_ERR_CUDA;
+        }
+        configured.fetch_or(bit, std::memory_order_relaxed);
+    }
+    const int grid = std::min(P.m_blocks * P.n_blocks, sms);
+    tpb::nvfp4_gemm_kernel<<<grid, tpb::kThreads, smem, reinterpret_cast<cudaStream_t>(stream)>>>(P);
+    return tpb_launch_status();
+}

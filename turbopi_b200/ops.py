@@ -222,3 +222,58 @@ def quantize_weight_to_nvfp4(weight_bf16):
         _lib.load().quantizeWeightToNVFP4(_ptr(w), _ptr(packed), _ptr(scales), N, K, _stream(w))
     _lib.check_void("quantizeWeightToNVFP4")
     return packed, scales
+
+
+# ------------------------------------------------------------------------------------- NVFP4 tensor-core GEMM
+def nvfp4_sf_bytes(rows, K):
+    return int(_lib.load().tpb200_nvfp4_sf_bytes(int(rows), int(K)))
+
+
+def packed_pitch(K):
+    """Row pitch in bytes of a packed e2m1 matrix: K/2 rounded up to 16 bytes."""
+    return (K // 2 + 15) // 16 * 16
+
+
+def swizzle_scales(sf_bytes):
+    """UE4M3 scale bytes [rows, K/16] -> the GEMM's atom layout (flat uint8): rows padded to 128,
+    K-blocks to 16, atoms of 128 rows x 4 blocks ordered [row tile][K atom], byte
+    (r % 32) * 16 + (r // 32) * 4 + kb inside an atom.  Pure index shuffle (host-side weight prep)."""
+    R, KB = sf_bytes.shape
+    Rp, Kp = (R + 127) // 128 * 128, (KB + 15) // 16 * 16
+    pad = torch.zeros((Rp, Kp), dtype=torch.uint8, device=sf_bytes.device)
+    pad[:R, :KB] = sf_bytes
+    t = pad.reshape(Rp // 128, 4, 32, Kp // 4, 4).permute(0, 3, 2, 1, 4)
+    return t.contiguous().reshape(-1)
+
+
+def nvfp4_quantize_act(x, packed=None, sf=None):
+    """x [M, K] (bf16/fp16/fp32, CUDA) -> (packed [M, pitch] uint8, swizzled UE4M3 scales)."""
+    _cuda(x)
+    M, K = x.shape
+    x = x.contiguous()
+    pitch = packed_pitch(K)
+    if packed is None:
+        packed = torch.empty((M, pitch), dtype=torch.uint8, device=x.device)
+    if sf is None:
+        sf = torch.empty(nvfp4_sf_bytes(M, K), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        st = _lib.load().tpb200_nvfp4_quantize_act(_ptr(x), _dt(x), K, _ptr(packed), pitch, _ptr(sf), M, K, _stream(x))
+    _lib.check(st, "tpb200_nvfp4_quantize_act")
+    return packed, sf
+
+
+def nvfp4_gemm(a_packed, a_sf, b_packed, b_sf, M, N, K, alpha=1.0, bias=None, activation=ACT_NONE, out=None,
+               out_dtype=torch.bfloat16):
+    """out[M, N] = act(alpha * A @ B^T + bias) with A, B packed e2m1 + swizzled UE4M3 scales."""
+    _cuda(a_packed, a_sf, b_packed, b_sf, bias, out)
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a_packed.device)
+    if bias is not None:
+        bias = bias.float().contiguous()
+    with torch.cuda.device(a_packed.device):
+        st = _lib.load().tpb200_nvfp4_gemm(
+            _ptr(a_packed), a_packed.stride(0), _ptr(a_sf), _ptr(b_packed), b_packed.stride(0), _ptr(b_sf),
+            float(alpha), _ptr(bias), int(activation), _ptr(out), _dt(out), out.stride(0), M, N, K, FLAG_NONE,
+            _stream(a_packed))
+    _lib.check(st, "tpb200_nvfp4_gemm")
+    return out
