@@ -380,6 +380,24 @@ def run_extras(device, sets, x):
         t = time_launches(lambda i: ops.nvfp4_gemv_out(xb, wp[i % 12], sp[i % 12], ob, block_size=16,
                                                        global_scale=1e-3), 48)
         ex[f"nvfp4_single_launch_{name}"] = {"us": t * 1e6, "gbps": algorithmic_bytes(N, K) / t / 1e9}
+    # (e) prefix NVFP4 x NVFP4 GEMMs on tcgen05 (e2m1 activations and weights, UE4M3 block-16 scales)
+    for (M, N, K, name) in ((712, 16384, 2048, "gemma2b_gateup_M712"), (712, 2048, 16384, "gemma2b_down_M712"),
+                            (512, 4304, 1152, "siglip_fc1_M512"), (512, 1152, 4304, "siglip_fc2_M512")):
+        pitch = ops.packed_pitch(K)
+        nb = 4
+        a = torch.randint(0, 256, (M, pitch), device=device, dtype=torch.uint8)
+        a_sf = torch.randint(40, 120, (ops.nvfp4_sf_bytes(M, K),), device=device, dtype=torch.uint8)
+        bs = [torch.randint(0, 256, (N, pitch), device=device, dtype=torch.uint8) for _ in range(nb)]
+        b_sf = [torch.randint(40, 120, (ops.nvfp4_sf_bytes(N, K),), device=device, dtype=torch.uint8) for _ in range(nb)]
+        o = torch.empty((M, N), dtype=torch.bfloat16, device=device)
+        t = time_launches(lambda i: ops.nvfp4_gemm(a, a_sf, bs[i % nb], b_sf[i % nb], M, N, K, alpha=1e-4, out=o), 16)
+        flops = 2.0 * M * N * K
+        bytes_ = M * K // 2 + M * K // 16 + N * K // 2 + N * K // 16 + M * N * 2
+        ex[f"nvfp4_gemm_{name}"] = {"us": t * 1e6, "tflops": flops / t / 1e12, "gbps": bytes_ / t / 1e9}
+        xq = torch.randn(M, K, device=device).to(torch.bfloat16)
+        pk, sf = ops.nvfp4_quantize_act(xq)
+        t = time_launches(lambda i: ops.nvfp4_quantize_act(xq, pk, sf), 16)
+        ex[f"nvfp4_quantize_act_{M}x{K}"] = {"us": t * 1e6, "gbps": (M * K * 2 + M * K // 2 + M * K // 16) / t / 1e9}
     return ex
 
 

@@ -93,5 +93,33 @@ def test_quantise_then_gemm_matches_reference_simulation(cuda_device):
     b_sf = _dev(nvfp4.swizzle_scales_128x4(ws_b, 16), cuda_device)
     a, a_sf = ops.nvfp4_quantize_act(_dev(x, cuda_device, torch.bfloat16))
     y = ops.nvfp4_gemm(a, a_sf, b, b_sf, M, N, K, alpha=1.0 / 256.0, out_dtype=torch.float32)
-    ref = nvfp4.linear_sim(x, wq, formats.e4m3_decode(ws_b) / np.float32(256.0), 16)
+    lim = np.float32(2688.0)
+    xq, xs = nvfp4.quantize_to_nvfp4_sim(np.clip(x, -lim, lim), 16, use_mse_search=False)
+    xd = nvfp4.dequantize_nvfp4_sim(xq, xs, 16, use_fp8_scales=True).astype(np.float64)
+    wd = (wq.reshape(N, -1, 16) * (formats.e4m3_decode(ws_b) / np.float32(256.0))[:, :, None]).reshape(N, K)
+    ref = xd @ wd.astype(np.float64).T
     assert rel_err(y.cpu().numpy(), ref) <= 1e-4
+
+
+@torch.no_grad()
+def test_nvfp4_linear_module_matches_reference_golden(cuda_device, golden):
+    """NVFP4Linear (block 32, MSE-searched weight scales, E4M3-rounded scales on both sides) against the
+    output of the reference's own simulation forward on its own quantised tensors."""
+    from turbopi_b200 import nvfp4_linear
+    g = golden("nvfp4_sim")
+    lin = torch.nn.Linear(128, 48, bias=False)
+    lin.weight.copy_(torch.from_numpy(g["weight"]))
+    layer = nvfp4_linear.NVFP4Linear.from_linear(lin.to(cuda_device), block_size=32, keep_sim_weights=True)
+    assert np.array_equal(layer.weight_q.cpu().numpy(), g["wq_mse"])
+    assert np.array_equal(layer.weight_scales.cpu().numpy(), g["ws_mse"])
+    assert np.array_equal(layer.weight_packed.cpu().numpy()[:, :64], g["w_packed"])
+    # activations: the reference example quantises x per 32; the kernel's native block is 16, so compare
+    # against the oracle's simulation at block 16 for x and the golden block-32 weights
+    x = torch.from_numpy(g["x"]).to(cuda_device)
+    y = layer(x).float().cpu().numpy()
+    xq, xs = nvfp4.quantize_to_nvfp4_sim(g["x"], 16, use_mse_search=False)
+    xd = nvfp4.dequantize_nvfp4_sim(xq, xs, 16, use_fp8_scales=True).astype(np.float64)
+    ref = xd @ g["w_dequant_fp8"].astype(np.float64).T
+    assert rel_err(y, ref) <= 1e-4
+    # and it stays close to the reference's block-32 activation result
+    assert cosine(y, g["y"]) >= 0.99

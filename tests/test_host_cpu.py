@@ -102,3 +102,19 @@ def test_nvfp4_packers_match_oracle_and_golden(golden):
     assert np.array_equal(pk.numpy(), opk)
     deq = nvfp4.dequantize(opk, osc, 16, ogs, scale_is_e4m3=True)
     assert np.abs(deq - w2).max() < np.abs(w2).max() * 0.3
+
+
+def test_nvfp4_sim_quantiser_matches_golden(golden):
+    from turbopi_b200 import nvfp4_linear
+    g = golden("nvfp4_sim")
+    w = torch.from_numpy(g["weight"])
+    q, s = nvfp4_linear.quantize_to_nvfp4_sim(w, 32, use_mse_search=True)
+    assert np.array_equal(q.numpy(), g["wq_mse"]) and np.array_equal(s.numpy(), g["ws_mse"])
+    q2, s2 = nvfp4_linear.quantize_to_nvfp4_sim(w, 32, use_mse_search=False)
+    assert np.array_equal(q2.numpy(), g["wq_minmax"]) and np.array_equal(s2.numpy(), g["ws_minmax"])
+    d = nvfp4_linear.dequantize_nvfp4_sim(q, s, 32, use_fp8_scales=True)
+    assert np.array_equal(d.numpy(), g["w_dequant_fp8"])
+    assert np.array_equal(nvfp4_linear.pack_nvfp4_data(q).numpy(), g["w_packed"])
+    sw = nvfp4_linear.prepare_scales(s, 32).numpy()
+    ref = nvfp4.swizzle_scales_128x4(np.repeat(formats.e4m3_encode(g["ws_mse"]), 2, axis=1), 16)
+    assert np.array_equal(sw, ref)
