@@ -139,6 +139,31 @@ int tpb200_nvfp4_gemm(const void* a_packed, int a_pitch, const void* a_sf, const
                       const void* b_sf, float alpha, const void* bias_f32, int activation, void* out,
                       int out_dtype, int ldo, int M, int N, int K, int flags, tpb200_stream_t stream);
 
+/* Extended form.  Adds (a) weight-only semantics on the tensor-core path: the A operand may be given as
+ * `a_pieces` residual pieces of a bf16 activation matrix (tpb200_nvfp4_quantize_act_pieces: piece p of row
+ * m at packed row p * a_piece_rows + m, a_piece_rows a multiple of 128, per-row power-of-two pre-scale
+ * undone through a_row_scale), which the kernel sums in its accumulator; and (b) the fused QKV epilogue
+ * that replaces fused_qkv_fp4 for prefix shapes (openpi/kv_fuse_plugin/src/fused_qkv_fp4.cu:382-467 plus
+ * the RoPE + cache fill of openpi/src/openpi/models_pytorch/pi0_pytorch.py:455-473): B = [Wq; Wk; Wv]
+ * with head_dim 256 and one KV head, rows tile-permuted (tile 2*head+half = head rows [64*half, 64*half+64)
+ * then the same +128), rotary embedding applied to Q and K in bf16, Q written to qkv_q_out, K (post-RoPE)
+ * and V rows written to qkv_k_rows / qkv_v_rows + m * 256 (pointers to the cache row of the first token). */
+typedef struct {
+    const void* a_packed; int a_pitch; const void* a_sf;
+    int a_pieces; int a_piece_rows; const float* a_row_scale;
+    const void* b_packed; int b_pitch; const void* b_sf;
+    float alpha; const float* bias; int activation;
+    void* out; int out_dtype; int ldo;
+    int M, N, K;
+    void* qkv_q_out; int qkv_ldq; int qkv_q_dim;
+    void* qkv_k_rows; void* qkv_v_rows;
+    const int* qkv_positions; const void* qkv_rope_cos; const void* qkv_rope_sin; /* bf16 [positions, 128] */
+} tpb200_nvfp4_gemm_args;
+int tpb200_nvfp4_gemm_ex(const tpb200_nvfp4_gemm_args* args, tpb200_stream_t stream);
+int tpb200_nvfp4_quantize_act_pieces(const void* x, int x_dtype, int ldx, void* packed, int packed_pitch,
+                                     void* sf_swizzled, float* row_scale, int M, int K, int pieces,
+                                     int piece_rows, tpb200_stream_t stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Entry points with the reference's names and signatures (TensorRT-plugin / test ABI).
  * ------------------------------------------------------------------------------------------- */

@@ -109,7 +109,8 @@ def test_nvfp4_linear_module_matches_reference_golden(cuda_device, golden):
     g = golden("nvfp4_sim")
     lin = torch.nn.Linear(128, 48, bias=False)
     lin.weight.copy_(torch.from_numpy(g["weight"]))
-    layer = nvfp4_linear.NVFP4Linear.from_linear(lin.to(cuda_device), block_size=32, keep_sim_weights=True)
+    # quantise on the CPU (where the golden vectors were made), then move the packed layer to the GPU
+    layer = nvfp4_linear.NVFP4Linear.from_linear(lin, block_size=32, keep_sim_weights=True).to(cuda_device)
     assert np.array_equal(layer.weight_q.cpu().numpy(), g["wq_mse"])
     assert np.array_equal(layer.weight_scales.cpu().numpy(), g["ws_mse"])
     assert np.array_equal(layer.weight_packed.cpu().numpy()[:, :64], g["w_packed"])
@@ -123,3 +124,64 @@ def test_nvfp4_linear_module_matches_reference_golden(cuda_device, golden):
     assert rel_err(y, ref) <= 1e-4
     # and it stays close to the reference's block-32 activation result
     assert cosine(y, g["y"]) >= 0.99
+
+
+@pytest.mark.parametrize("pieces,tol", [(1, 0.12), (2, 2.5e-2), (3, 4e-3), (4, 3e-3)])
+def test_weight_only_semantics_through_residual_pieces(cuda_device, pieces, tol):
+    """bf16 activations x NVFP4 weights on the tensor cores: the error against the dequantise-then-matmul
+    reference falls with the number of residual pieces; three pieces are inside the 1e-2 bound."""
+    from turbopi_b200 import ops
+    rng = np.random.default_rng(5)
+    M, N, K = 200, 384, 2048
+    w = (rng.normal(size=(N, K)) * 0.02).astype(np.float32)
+    packed, sbytes, g = nvfp4.quantize_two_level(w, 16)
+    x = formats.round_to_bf16((rng.normal(size=(M, K)) * rng.choice([0.05, 1.0, 20.0], size=(M, 1))).astype(np.float32))
+    x[3] = 0.0
+    b = _dev(_pack_padded(packed, ops.packed_pitch(K)), cuda_device)
+    b_sf = _dev(nvfp4.swizzle_scales_128x4(sbytes, 16), cuda_device)
+    y = ops.nvfp4_gemm_w4a16(_dev(x, cuda_device, torch.bfloat16), b, b_sf, N, alpha=float(g), pieces=pieces,
+                             out_dtype=torch.float32).cpu().numpy()
+    ref = nvfp4.gemv_dequant_matmul(x, packed, sbytes, None, 0, 16, float(g), True)
+    assert np.isfinite(y).all() and (y[3] == 0).all()
+    # every row against its own scale: rows differ by 400x in magnitude
+    err = np.abs(y - ref).max(axis=1) / np.maximum(np.abs(ref).max(axis=1), 1e-30)
+    assert err.max() <= tol, err.max()
+
+
+def test_fused_qkv_rope_kv_append_prefix(cuda_device):
+    """Benchmark configuration 3: hidden 2048, 8 query heads, 1 KV head, head_dim 256, 712 prefix tokens,
+    positions 0..711, bf16 cache [18, 2, 1024, 256] pre-filled with a sentinel."""
+    from oracle import kv_fuse
+    from turbopi_b200 import _lib, ops
+    rng = np.random.default_rng(12)
+    S, H, QD = 712, 2048, 2048
+    layer, pos0 = 7, 0
+    x = formats.round_to_bf16(rng.normal(size=(S, H)).astype(np.float32))
+    w = (rng.normal(size=(QD + 512, H)) * 0.02).astype(np.float32)
+    packed, sbytes, g = nvfp4.quantize_two_level(w, 16)
+    wd = nvfp4.dequantize(packed, sbytes, 16, float(g), True)
+    perm = ops.qkv_tile_permutation(QD).numpy()
+    b = _dev(_pack_padded(packed[perm], ops.packed_pitch(H)), cuda_device)
+    b_sf = _dev(nvfp4.swizzle_scales_128x4(sbytes[perm], 16), cuda_device)
+    cache = torch.full((18, 2, 1024, 256), -3.0, dtype=torch.bfloat16, device=cuda_device)
+    positions = torch.arange(S, dtype=torch.int32, device=cuda_device)
+    cos, sin = ops.rope_tables(1024, device=cuda_device)
+    q = ops.fused_qkv_rope_append(_dev(x, cuda_device, torch.bfloat16), b, b_sf, QD, cache[layer, 0, pos0:],
+                                  cache[layer, 1, pos0:], positions, cos, sin, alpha=float(g))
+    assert _lib.load().tpb200_device_error(0) == 0
+    ref_cache = np.full((18, 2, 1024, 256), -3.0, dtype=np.float32)
+    q_ref, _ = kv_fuse.fused_qkv_rope_append(x, wd[:QD], wd[QD:QD + 256], wd[QD + 256:], ref_cache, layer,
+                                             np.arange(S), pos0)
+    # the rotary tables are the model's, bit for bit
+    oc, os_ = kv_fuse.rope_cos_sin(np.arange(1024), 256, 10000.0)
+    assert np.array_equal(cos.float().cpu().numpy(), oc[:, :128]) and np.array_equal(sin.float().cpu().numpy(), os_[:, :128])
+    got = cache.float().cpu().numpy()
+    # cache index writes: exactly rows pos0..pos0+S-1 of `layer` changed, nothing else
+    touched = np.zeros((18, 2, 1024), dtype=bool)
+    touched[layer, :, pos0:pos0 + S] = True
+    assert (got[~touched] == -3.0).all()
+    assert (got[touched] != -3.0).any(axis=-1).all()
+    for name, y, r in (("q", q.float().cpu().numpy(), q_ref), ("k", got[layer, 0, :S], ref_cache[layer, 0, :S]),
+                       ("v", got[layer, 1, :S], ref_cache[layer, 1, :S])):
+        assert rel_err(y, r) <= 1e-2, (name, rel_err(y, r))
+        assert cosine(y, r) >= 0.999, (name, cosine(y, r))

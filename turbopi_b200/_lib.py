@@ -28,6 +28,18 @@ class GemvProblem(ctypes.Structure):
                 ("out", c_void_p), ("N", c_int), ("K", c_int), ("global_scale", c_float), ("reserved", c_int)]
 
 
+class GemmArgs(ctypes.Structure):
+    _fields_ = [("a_packed", c_void_p), ("a_pitch", c_int), ("a_sf", c_void_p),
+                ("a_pieces", c_int), ("a_piece_rows", c_int), ("a_row_scale", c_void_p),
+                ("b_packed", c_void_p), ("b_pitch", c_int), ("b_sf", c_void_p),
+                ("alpha", c_float), ("bias", c_void_p), ("activation", c_int),
+                ("out", c_void_p), ("out_dtype", c_int), ("ldo", c_int),
+                ("M", c_int), ("N", c_int), ("K", c_int),
+                ("qkv_q_out", c_void_p), ("qkv_ldq", c_int), ("qkv_q_dim", c_int),
+                ("qkv_k_rows", c_void_p), ("qkv_v_rows", c_void_p),
+                ("qkv_positions", c_void_p), ("qkv_rope_cos", c_void_p), ("qkv_rope_sin", c_void_p)]
+
+
 # name -> (restype, argtypes); every symbol include/turbopi_b200.h declares
 SIGNATURES = {
     "tpb200_version": (c_int, []),
@@ -44,6 +56,9 @@ SIGNATURES = {
     "tpb200_nvfp4_quantize_act": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]),
     "tpb200_nvfp4_gemm": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_float, c_void_p, c_int,
                                   c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "tpb200_nvfp4_gemm_ex": (c_int, [ctypes.POINTER(GemmArgs), c_void_p]),
+    "tpb200_nvfp4_quantize_act_pieces": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int,
+                                                 c_int, c_int, c_int, c_void_p]),
     "nvfp4_gemv_forward": (None, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                   c_int, c_int, c_void_p]),
     "nvfp4_gemv_workspace_size": (c_size_t, [c_int, c_int, c_int]),

@@ -49,7 +49,26 @@ struct alignas(64) GemmParams {
     float alpha;
     int k_stages;   // ceil(K / 256)
     int m_blocks, n_blocks;
+    // A operand given as `a_pieces` residual pieces stacked along rows (piece p at row p * a_piece_rows):
+    // the K loop runs over all pieces against the same B tiles, summing them in the accumulator
+    int a_pieces;
+    int a_piece_rows;
+    const float* row_scale;  // optional per-row multiplier of the result (undoes the activation pre-scale)
+    // fused QKV epilogue (epilogue == kEpiQkvRope): rotary embedding on the Q and K heads, K/V rows
+    // appended to the cache.  B rows are stored tile-permuted: tile t = 2 * head + half holds
+    // head rows [64*half, 64*half + 64) followed by their rotation partners (+128).
+    int epilogue;
+    int q_dim;                 // number of Q outputs (heads * 256); then 256 K and 256 V outputs
+    void* q_out;               // bf16 [M, ldq]
+    int ldq;
+    void* k_rows;              // bf16 cache rows: row (cache_pos0 + m) * 256
+    void* v_rows;
+    const int* positions;      // [M] index into the rotary tables
+    const __nv_bfloat16* rope_cos;   // [positions, 128]
+    const __nv_bfloat16* rope_sin;
 };
+
+enum { kEpiPlain = 0, kEpiQkvRope = 1 };
 
 struct SharedControl {
     uint64_t full[kStages];
@@ -101,7 +120,10 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
             for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
                 const int m_blk = tile % P.m_blocks;
                 const int n_blk = tile / P.m_blocks;
-                for (int ks = 0; ks < P.k_stages; ++ks, ++it) {
+                for (int vs = 0; vs < P.a_pieces * P.k_stages; ++vs, ++it) {
+                    const int piece = vs / P.k_stages;
+                    const int ks = vs - piece * P.k_stages;
+                    const int a_row_tile = piece * (P.a_piece_rows >> 7) + m_blk;
                     const int s = it % kStages;
                     if (it >= kStages && !mbar_wait_bounded(&ctl->empty[s], ((it / kStages) - 1) & 1)) {
                         record_error(kErrGemmEmptyBarrierTimeout);
@@ -110,10 +132,10 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
                     }
                     uint8_t* st = smem + s * kStageBytes;
                     mbar_expect_tx(&ctl->full[s], kStageBytes);
-                    tc::tma_load_2d(st, &P.map_a, ks * kBKBytes, m_blk * kBM, &ctl->full[s]);
+                    tc::tma_load_2d(st, &P.map_a, ks * kBKBytes, a_row_tile * kBM, &ctl->full[s]);
                     tc::tma_load_2d(st + kATile, &P.map_b, ks * kBKBytes, n_blk * kBN, &ctl->full[s]);
                     bulk_copy_g2s(st + kATile + kBTile,
-                                  P.sfa + static_cast<size_t>(m_blk) * sf_row_stride + static_cast<size_t>(ks) * kSfSlab,
+                                  P.sfa + static_cast<size_t>(a_row_tile) * sf_row_stride + static_cast<size_t>(ks) * kSfSlab,
                                   kSfSlab, &ctl->full[s]);
                     bulk_copy_g2s(st + kATile + kBTile + kSfSlab,
                                   P.sfb + static_cast<size_t>(n_blk) * sf_row_stride + static_cast<size_t>(ks) * kSfSlab,
@@ -135,7 +157,7 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
                 }
                 tc::fence_after_thread_sync();
                 const uint32_t tmem_acc = tmem_base + buf * kAccCols;
-                for (int ks = 0; ks < P.k_stages; ++ks, ++it) {
+                for (int ks = 0; ks < P.a_pieces * P.k_stages; ++ks, ++it) {
                     const int s = it % kStages;
                     if (!mbar_wait_bounded(&ctl->full[s], (it / kStages) & 1)) {
                         record_error(kErrGemmTmaBarrierTimeout);
@@ -178,48 +200,119 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
             tc::fence_after_thread_sync();
             const int m = m_blk * kBM + q * 32 + lane;
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * kAccCols;
+            const float rs = (P.row_scale != nullptr && m < P.M) ? P.alpha * __ldg(P.row_scale + m) : P.alpha;
+            if (P.epilogue == kEpiPlain) {
 #pragma unroll 1
-            for (int c = 0; c < kBN / 32; ++c) {
-                uint32_t r[32];
-                tc::tmem_ld_32x32b_x32(taddr + c * 32, r);
-                tc::tmem_ld_wait();
-                if (c == kBN / 32 - 1) {
-                    // everything this warp needs from the accumulator is in registers
-                    tc::fence_before_thread_sync();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&ctl->acc_empty[buf]);
-                }
-                const int n0 = n_blk * kBN + c * 32;
-                if (m < P.M) {
-                    float v[32];
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        float f = __uint_as_float(r[i]) * P.alpha;
-                        if (P.bias != nullptr && n0 + i < P.N) f += __ldg(P.bias + n0 + i);
-                        v[i] = apply_activation(f, P.activation);
+                for (int c = 0; c < kBN / 32; ++c) {
+                    uint32_t r[32];
+                    tc::tmem_ld_32x32b_x32(taddr + c * 32, r);
+                    tc::tmem_ld_wait();
+                    if (c == kBN / 32 - 1) {
+                        // everything this warp needs from the accumulator is in registers
+                        tc::fence_before_thread_sync();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&ctl->acc_empty[buf]);
                     }
-                    if (P.out_dtype == TPB200_BF16) {
-                        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(P.out) + static_cast<size_t>(m) * P.ldo + n0;
+                    const int n0 = n_blk * kBN + c * 32;
+                    if (m < P.M) {
+                        float v[32];
 #pragma unroll
-                        for (int g = 0; g < 4; ++g) {
-                            if (n0 + g * 8 + 8 <= P.N) {
-                                uint32_t w[4];
+                        for (int i = 0; i < 32; ++i) {
+                            float f = __uint_as_float(r[i]) * rs;
+                            if (P.bias != nullptr && n0 + i < P.N) f += __ldg(P.bias + n0 + i);
+                            v[i] = apply_activation(f, P.activation);
+                        }
+                        if (P.out_dtype == TPB200_BF16) {
+                            __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(P.out) + static_cast<size_t>(m) * P.ldo + n0;
 #pragma unroll
-                                for (int i = 0; i < 4; ++i) {
-                                    __nv_bfloat162 b2 = __floats2bfloat162_rn(v[g * 8 + 2 * i], v[g * 8 + 2 * i + 1]);
-                                    w[i] = *reinterpret_cast<uint32_t*>(&b2);
+                            for (int g = 0; g < 4; ++g) {
+                                if (n0 + g * 8 + 8 <= P.N) {
+                                    uint32_t w[4];
+#pragma unroll
+                                    for (int i = 0; i < 4; ++i) {
+                                        __nv_bfloat162 b2 = __floats2bfloat162_rn(v[g * 8 + 2 * i], v[g * 8 + 2 * i + 1]);
+                                        w[i] = *reinterpret_cast<uint32_t*>(&b2);
+                                    }
+                                    *reinterpret_cast<uint4*>(dst + g * 8) = make_uint4(w[0], w[1], w[2], w[3]);
                                 }
-                                *reinterpret_cast<uint4*>(dst + g * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+                            }
+                        } else {
+                            float* dst = static_cast<float*>(P.out) + static_cast<size_t>(m) * P.ldo + n0;
+#pragma unroll
+                            for (int g = 0; g < 8; ++g) {
+                                if (n0 + g * 4 + 4 <= P.N) {
+                                    *reinterpret_cast<float4*>(dst + g * 4) =
+                                        make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+                                }
                             }
                         }
-                    } else {
-                        float* dst = static_cast<float*>(P.out) + static_cast<size_t>(m) * P.ldo + n0;
+                    }
+                }
+            } else {
+                // Fused QKV: tile columns [0,64) are head offsets i0..i0+63, columns [64,128) their
+                // rotation partners i + 128.  bf16 arithmetic as torch does it: q, cos, sin in bf16,
+                // each product and the sum rounded to bf16.
+                const int head = n_blk >> 1;
+                const int i0 = (n_blk & 1) * 64;
+                const int n_heads_q = P.q_dim >> 8;
+                const bool is_v = head == n_heads_q + 1;
+                const int pos = (m < P.M) ? __ldg(P.positions + m) : 0;
+#pragma unroll 1
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t lo[32], hi[32];
+                    tc::tmem_ld_32x32b_x32(taddr + c * 32, lo);
+                    tc::tmem_ld_32x32b_x32(taddr + 64 + c * 32, hi);
+                    tc::tmem_ld_wait();
+                    if (c == 1) {
+                        tc::fence_before_thread_sync();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&ctl->acc_empty[buf]);
+                    }
+                    if (m < P.M) {
+                        const int i = i0 + c * 32;   // head offset of lo[0]
+                        uint32_t olo[16], ohi[16];
+                        const uint4* cs = reinterpret_cast<const uint4*>(P.rope_cos + static_cast<size_t>(pos) * 128 + i);
+                        const uint4* sn = reinterpret_cast<const uint4*>(P.rope_sin + static_cast<size_t>(pos) * 128 + i);
 #pragma unroll
-                        for (int g = 0; g < 8; ++g) {
-                            if (n0 + g * 4 + 4 <= P.N) {
-                                *reinterpret_cast<float4*>(dst + g * 4) =
-                                    make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+                        for (int g = 0; g < 4; ++g) {
+                            uint4 cv = make_uint4(0, 0, 0, 0), sv = make_uint4(0, 0, 0, 0);
+                            if (!is_v) { cv = __ldg(cs + g); sv = __ldg(sn + g); }
+                            const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w};
+                            const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                const int e = g * 8 + 2 * j;
+                                __nv_bfloat162 a = __floats2bfloat162_rn(__uint_as_float(lo[e]) * rs,
+                                                                         __uint_as_float(lo[e + 1]) * rs);
+                                __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(hi[e]) * rs,
+                                                                         __uint_as_float(hi[e + 1]) * rs);
+                                if (!is_v) {
+                                    const __nv_bfloat162 co = *reinterpret_cast<const __nv_bfloat162*>(&cw[j]);
+                                    const __nv_bfloat162 si = *reinterpret_cast<const __nv_bfloat162*>(&sw[j]);
+                                    // first half: x*cos + (-x_partner)*sin ; second half: x_partner*cos + x*sin
+                                    const __nv_bfloat162 ra = __hadd2(__hmul2(a, co), __hmul2(__hneg2(b), si));
+                                    const __nv_bfloat162 rb = __hadd2(__hmul2(b, co), __hmul2(a, si));
+                                    a = ra;
+                                    b = rb;
+                                }
+                                olo[g * 4 + j] = *reinterpret_cast<uint32_t*>(&a);
+                                ohi[g * 4 + j] = *reinterpret_cast<uint32_t*>(&b);
                             }
+                        }
+                        __nv_bfloat16* dst;
+                        if (head < n_heads_q) {
+                            dst = static_cast<__nv_bfloat16*>(P.q_out) + static_cast<size_t>(m) * P.ldq + head * 256 + i;
+                        } else if (!is_v) {
+                            dst = static_cast<__nv_bfloat16*>(P.k_rows) + static_cast<size_t>(m) * 256 + i;
+                        } else {
+                            dst = static_cast<__nv_bfloat16*>(P.v_rows) + static_cast<size_t>(m) * 256 + i;
+                        }
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            *reinterpret_cast<uint4*>(dst + g * 8) =
+                                make_uint4(olo[g * 4], olo[g * 4 + 1], olo[g * 4 + 2], olo[g * 4 + 3]);
+                            *reinterpret_cast<uint4*>(dst + 128 + g * 8) =
+                                make_uint4(ohi[g * 4], ohi[g * 4 + 1], ohi[g * 4 + 2], ohi[g * 4 + 3]);
                         }
                     }
                 }
@@ -307,6 +400,93 @@ __global__ void nvfp4_quantize_act_kernel(const void* __restrict__ x, int x_dtyp
     *reinterpret_cast<uint2*>(packed + static_cast<size_t>(row) * pitch + kb * 8) = make_uint2(lo, hi);
 }
 
+// ------------------------------------------------------------------------------------------
+// Residual-piece activation quantiser: keeps (almost) the full precision of bf16 activations in
+// e2m1 operands, so that weight-only semantics run on the block-scaled tensor-core path.
+//   row pre-scale: x' = x * 2^e with max|x'| in [1024, 2048)   (row_scale[m] = 2^-e)
+//   piece 0 quantises x', piece p quantises what pieces 0..p-1 left over, each per 16-block with
+//   its own UE4M3 scale (rounded UP so that nothing clips):  x' ~= sum_p q_p * s_p.
+// One CTA per row; piece p of row m goes to packed row p * piece_rows + m.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ float e4m3_round_up(float v, uint8_t& code) {
+    code = encode_e4m3(v);
+    float d = decode_e4m3(code);
+    if (d < v && code < 0x7E) {
+        code += 1;               // next representable value (codes are monotonic for positive values)
+        d = decode_e4m3(code);
+    }
+    return d;
+}
+
+__global__ void __launch_bounds__(256) nvfp4_quantize_pieces_kernel(const void* __restrict__ x, int x_dtype, int ldx,
+                                                                    uint8_t* __restrict__ packed, int pitch,
+                                                                    uint8_t* __restrict__ sf, float* __restrict__ row_scale,
+                                                                    int M, int K, int pieces, int piece_rows,
+                                                                    int kb_pad) {
+    const int row = blockIdx.x;
+    const int nblk = K >> 4;
+    __shared__ float red[8];
+    float amax = 0.0f;
+    for (int i = threadIdx.x; i < K; i += blockDim.x) {
+        amax = fmaxf(amax, fabsf(load_as_float(x, x_dtype, static_cast<size_t>(row) * ldx + i)));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = red[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) amax = fmaxf(amax, red[i]);
+    int e = 0;
+    if (amax > 0.0f && amax < 3.0e38f) {
+        int ex;
+        frexpf(amax, &ex);        // amax = f * 2^ex, f in [0.5, 1)
+        e = 11 - ex;              // amax * 2^e in [1024, 2048)
+    }
+    const float pre = ldexpf(1.0f, e);
+    if (threadIdx.x == 0) row_scale[row] = ldexpf(1.0f, -e);
+
+    for (int kb = threadIdx.x; kb < kb_pad; kb += blockDim.x) {
+        float r[16];
+        const bool valid = kb < nblk;
+        if (valid) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                r[i] = load_as_float(x, x_dtype, static_cast<size_t>(row) * ldx + kb * 16 + i) * pre;
+            }
+        }
+        for (int p = 0; p < pieces; ++p) {
+            const int prow = p * piece_rows + row;
+            const size_t sf_off = (static_cast<size_t>(prow >> 7) * (kb_pad >> 2) + (kb >> 2)) * 512 + (prow & 31) * 16 +
+                                  ((prow >> 5) & 3) * 4 + (kb & 3);
+            if (!valid) {
+                sf[sf_off] = 0;
+                continue;
+            }
+            float bmax = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) bmax = fmaxf(bmax, fabsf(r[i]));
+            uint8_t code;
+            const float s = e4m3_round_up(bmax * (1.0f / 6.0f), code);
+            sf[sf_off] = code;
+            const float inv = s > 0.0f ? 1.0f / s : 0.0f;
+            uint32_t lo = 0, hi = 0;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const float a = fminf(fabsf(r[i]) * inv, 6.0f);
+                const uint32_t idx = e2m1_index(a);
+                const float mag = idx < 4 ? 0.5f * idx : (idx == 4 ? 2.0f : (idx == 5 ? 3.0f : (idx == 6 ? 4.0f : 6.0f)));
+                const bool neg = r[i] < 0.0f;
+                const uint32_t c = (neg && idx != 0) ? (idx | 8u) : idx;
+                r[i] -= (neg ? -mag : mag) * s;          // what this piece leaves for the next one
+                if (i < 8) lo |= c << (4 * i);
+                else hi |= c << (4 * (i - 8));
+            }
+            *reinterpret_cast<uint2*>(packed + static_cast<size_t>(prow) * pitch + kb * 8) = make_uint2(lo, hi);
+        }
+    }
+}
+
 using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                               const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -371,39 +551,86 @@ extern "C" int tpb200_nvfp4_quantize_act(const void* x, int x_dtype, int ldx, vo
     return tpb_launch_status();
 }
 
-extern "C" int tpb200_nvfp4_gemm(const void* a_packed, int a_pitch, const void* a_sf, const void* b_packed,
-                                 int b_pitch, const void* b_sf, float alpha, const void* bias_f32, int activation,
-                                 void* out, int out_dtype, int ldo, int M, int N, int K, int flags,
-                                 tpb200_stream_t stream) {
-    TPB_REQUIRE(a_packed && a_sf && b_packed && b_sf && out, TPB200_ERR_NULL);
-    TPB_REQUIRE(M >= 1 && N >= 8 && N % 8 == 0 && K >= 16 && K % 16 == 0 && ldo >= N, TPB200_ERR_SHAPE);
-    TPB_REQUIRE(out_dtype == TPB200_BF16 || out_dtype == TPB200_F32, TPB200_ERR_ENUM);
-    TPB_REQUIRE(activation == TPB200_ACT_NONE || activation == TPB200_ACT_GELU || activation == TPB200_ACT_SILU,
-                TPB200_ERR_ENUM);
-    TPB_REQUIRE(flags == TPB200_FLAG_NONE, TPB200_ERR_ENUM);
-    TPB_REQUIRE(a_pitch >= K / 2 && b_pitch >= K / 2 && a_pitch % 16 == 0 && b_pitch % 16 == 0, TPB200_ERR_ALIGN);
-    TPB_REQUIRE(tpb_aligned16(a_packed) && tpb_aligned16(b_packed) && tpb_aligned16(a_sf) && tpb_aligned16(b_sf) &&
-                    tpb_aligned16(out),
+extern "C" int tpb200_nvfp4_quantize_act_pieces(const void* x, int x_dtype, int ldx, void* packed, int packed_pitch,
+                                                void* sf_swizzled, float* row_scale, int M, int K, int pieces,
+                                                int piece_rows, tpb200_stream_t stream) {
+    TPB_REQUIRE(x && packed && sf_swizzled && row_scale, TPB200_ERR_NULL);
+    TPB_REQUIRE(M >= 1 && K >= 16 && K % 16 == 0 && ldx >= K, TPB200_ERR_SHAPE);
+    TPB_REQUIRE(pieces >= 1 && pieces <= 4 && piece_rows >= M, TPB200_ERR_SHAPE);
+    TPB_REQUIRE(pieces == 1 || piece_rows % 16 == 0, TPB200_ERR_SHAPE);
+    TPB_REQUIRE(tpb_valid_dtype(x_dtype), TPB200_ERR_ENUM);
+    TPB_REQUIRE(packed_pitch >= K / 2 && packed_pitch % 16 == 0, TPB200_ERR_ALIGN);
+    TPB_REQUIRE(tpb_aligned16(packed) && tpb_aligned16(sf_swizzled), TPB200_ERR_ALIGN);
+    const int kb_pad = (K + 255) / 256 * 16;
+    tpb::nvfp4_quantize_pieces_kernel<<<M, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        x, x_dtype, ldx, static_cast<uint8_t*>(packed), packed_pitch, static_cast<uint8_t*>(sf_swizzled), row_scale, M,
+        K, pieces, piece_rows, kb_pad);
+    return tpb_launch_status();
+}
+
+extern "C" int tpb200_nvfp4_gemm_ex(const tpb200_nvfp4_gemm_args* a, tpb200_stream_t stream) {
+    TPB_REQUIRE(a != nullptr, TPB200_ERR_NULL);
+    const int M = a->M, N = a->N, K = a->K;
+    TPB_REQUIRE(a->a_packed && a->a_sf && a->b_packed && a->b_sf, TPB200_ERR_NULL);
+    TPB_REQUIRE(M >= 1 && N >= 8 && N % 8 == 0 && K >= 16 && K % 16 == 0, TPB200_ERR_SHAPE);
+    TPB_REQUIRE(a->activation >= TPB200_ACT_NONE && a->activation <= TPB200_ACT_SILU, TPB200_ERR_ENUM);
+    TPB_REQUIRE(a->a_pitch >= K / 2 && a->b_pitch >= K / 2 && a->a_pitch % 16 == 0 && a->b_pitch % 16 == 0,
                 TPB200_ERR_ALIGN);
-    TPB_REQUIRE((static_cast<long long>(ldo) * tpb_dtype_size(out_dtype)) % 16 == 0, TPB200_ERR_ALIGN);
+    TPB_REQUIRE(tpb_aligned16(a->a_packed) && tpb_aligned16(a->b_packed) && tpb_aligned16(a->a_sf) &&
+                    tpb_aligned16(a->b_sf),
+                TPB200_ERR_ALIGN);
+    const int pieces = a->a_pieces <= 0 ? 1 : a->a_pieces;
+    TPB_REQUIRE(pieces <= 4, TPB200_ERR_SHAPE);
+    TPB_REQUIRE(pieces == 1 || (a->a_piece_rows >= M && a->a_piece_rows % 128 == 0), TPB200_ERR_SHAPE);
+    const bool qkv = a->qkv_q_out != nullptr;
+    if (qkv) {
+        TPB_REQUIRE(a->qkv_k_rows && a->qkv_v_rows && a->qkv_positions && a->qkv_rope_cos && a->qkv_rope_sin,
+                    TPB200_ERR_NULL);
+        TPB_REQUIRE(a->qkv_q_dim >= 256 && a->qkv_q_dim % 256 == 0 && N == a->qkv_q_dim + 512 && a->qkv_ldq >= a->qkv_q_dim,
+                    TPB200_ERR_SHAPE);
+        TPB_REQUIRE(tpb_aligned16(a->qkv_q_out) && tpb_aligned16(a->qkv_k_rows) && tpb_aligned16(a->qkv_v_rows) &&
+                        tpb_aligned16(a->qkv_rope_cos) && tpb_aligned16(a->qkv_rope_sin) && a->qkv_ldq % 8 == 0,
+                    TPB200_ERR_ALIGN);
+    } else {
+        TPB_REQUIRE(a->out != nullptr, TPB200_ERR_NULL);
+        TPB_REQUIRE(a->out_dtype == TPB200_BF16 || a->out_dtype == TPB200_F32, TPB200_ERR_ENUM);
+        TPB_REQUIRE(a->ldo >= N, TPB200_ERR_SHAPE);
+        TPB_REQUIRE(tpb_aligned16(a->out) && (static_cast<long long>(a->ldo) * tpb_dtype_size(a->out_dtype)) % 16 == 0,
+                    TPB200_ERR_ALIGN);
+    }
 
     tpb::GemmParams P;
-    if (!tpb::make_tensor_map_bytes_sw128(&P.map_a, a_packed, static_cast<uint64_t>(K) / 2, M, a_pitch, tpb::kBM) ||
-        !tpb::make_tensor_map_bytes_sw128(&P.map_b, b_packed, static_cast<uint64_t>(K) / 2, N, b_pitch, tpb::kBN)) {
+    const uint64_t a_rows = pieces == 1 ? static_cast<uint64_t>(M) : static_cast<uint64_t>(pieces) * a->a_piece_rows;
+    if (!tpb::make_tensor_map_bytes_sw128(&P.map_a, a->a_packed, static_cast<uint64_t>(K) / 2, a_rows, a->a_pitch,
+                                          tpb::kBM) ||
+        !tpb::make_tensor_map_bytes_sw128(&P.map_b, a->b_packed, static_cast<uint64_t>(K) / 2, N, a->b_pitch,
+                                          tpb::kBN)) {
         return TPB200_ERR_CUDA;
     }
-    P.sfa = static_cast<const uint8_t*>(a_sf);
-    P.sfb = static_cast<const uint8_t*>(b_sf);
-    P.bias = static_cast<const float*>(bias_f32);
-    P.out = out;
+    P.sfa = static_cast<const uint8_t*>(a->a_sf);
+    P.sfb = static_cast<const uint8_t*>(a->b_sf);
+    P.bias = a->bias;
+    P.out = a->out;
     P.M = M; P.N = N; P.K = K;
-    P.ldo = ldo;
-    P.out_dtype = out_dtype;
-    P.activation = activation;
-    P.alpha = alpha;
+    P.ldo = a->ldo;
+    P.out_dtype = a->out_dtype;
+    P.activation = a->activation;
+    P.alpha = a->alpha;
     P.k_stages = (K + 255) / 256;
     P.m_blocks = (M + tpb::kBM - 1) / tpb::kBM;
     P.n_blocks = (N + tpb::kBN - 1) / tpb::kBN;
+    P.a_pieces = pieces;
+    P.a_piece_rows = pieces == 1 ? 0 : a->a_piece_rows;
+    P.row_scale = a->a_row_scale;
+    P.epilogue = qkv ? tpb::kEpiQkvRope : tpb::kEpiPlain;
+    P.q_dim = a->qkv_q_dim;
+    P.q_out = a->qkv_q_out;
+    P.ldq = a->qkv_ldq;
+    P.k_rows = a->qkv_k_rows;
+    P.v_rows = a->qkv_v_rows;
+    P.positions = a->qkv_positions;
+    P.rope_cos = static_cast<const __nv_bfloat16*>(a->qkv_rope_cos);
+    P.rope_sin = static_cast<const __nv_bfloat16*>(a->qkv_rope_sin);
 
     int dev = 0, sms = 0;
     if (cudaGetDevice(&dev) != cudaSuccess ||
@@ -423,4 +650,18 @@ extern "C" int tpb200_nvfp4_gemm(const void* a_packed, int a_pitch, const void* 
     const int grid = std::min(P.m_blocks * P.n_blocks, sms);
     tpb::nvfp4_gemm_kernel<<<grid, tpb::kThreads, smem, reinterpret_cast<cudaStream_t>(stream)>>>(P);
     return tpb_launch_status();
+}
+
+extern "C" int tpb200_nvfp4_gemm(const void* a_packed, int a_pitch, const void* a_sf, const void* b_packed,
+                                 int b_pitch, const void* b_sf, float alpha, const void* bias_f32, int activation,
+                                 void* out, int out_dtype, int ldo, int M, int N, int K, int flags,
+                                 tpb200_stream_t stream) {
+    TPB_REQUIRE(flags == TPB200_FLAG_NONE, TPB200_ERR_ENUM);
+    tpb200_nvfp4_gemm_args a = {};
+    a.a_packed = a_packed; a.a_pitch = a_pitch; a.a_sf = a_sf; a.a_pieces = 1;
+    a.b_packed = b_packed; a.b_pitch = b_pitch; a.b_sf = b_sf;
+    a.alpha = alpha; a.bias = static_cast<const float*>(bias_f32); a.activation = activation;
+    a.out = out; a.out_dtype = out_dtype; a.ldo = ldo;
+    a.M = M; a.N = N; a.K = K;
+    return tpb200_nvfp4_gemm_ex(&a, stream);
 }

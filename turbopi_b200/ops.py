@@ -277,3 +277,94 @@ def nvfp4_gemm(a_packed, a_sf, b_packed, b_sf, M, N, K, alpha=1.0, bias=None, ac
             _stream(a_packed))
     _lib.check(st, "tpb200_nvfp4_gemm")
     return out
+
+
+def nvfp4_quantize_act_pieces(x, pieces=3):
+    """bf16/fp16/fp32 x [M, K] -> `pieces` residual e2m1 operands stacked along rows (piece p of row m at
+    row p * piece_rows + m), their swizzled UE4M3 scales, and the per-row multiplier that undoes the
+    power-of-two pre-scale.  Returns (packed, sf, row_scale, piece_rows)."""
+    _cuda(x)
+    M, K = x.shape
+    x = x.contiguous()
+    pitch = packed_pitch(K)
+    piece_rows = (M + 127) // 128 * 128
+    packed = torch.empty((pieces * piece_rows, pitch), dtype=torch.uint8, device=x.device)
+    sf = torch.empty(nvfp4_sf_bytes(pieces * piece_rows, K), dtype=torch.uint8, device=x.device)
+    row_scale = torch.empty((M,), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        st = _lib.load().tpb200_nvfp4_quantize_act_pieces(_ptr(x), _dt(x), K, _ptr(packed), pitch, _ptr(sf),
+                                                          _ptr(row_scale), M, K, pieces, piece_rows, _stream(x))
+    _lib.check(st, "tpb200_nvfp4_quantize_act_pieces")
+    return packed, sf, row_scale, piece_rows
+
+
+def _gemm_ex(args, device):
+    with torch.cuda.device(device):
+        st = _lib.load().tpb200_nvfp4_gemm_ex(ctypes.byref(args), torch.cuda.current_stream(device).cuda_stream)
+    _lib.check(st, "tpb200_nvfp4_gemm_ex")
+
+
+def nvfp4_gemm_w4a16(x, b_packed, b_sf, N, alpha=1.0, bias=None, activation=ACT_NONE, pieces=3, out=None,
+                     out_dtype=torch.bfloat16):
+    """Weight-only semantics on the tensor-core path: out = act(alpha * x @ dequant(W)^T + bias) with the
+    bf16 activations carried as `pieces` residual e2m1 operands (3 pieces keep ~bf16 precision)."""
+    M, K = x.shape
+    a, a_sf, row_scale, piece_rows = nvfp4_quantize_act_pieces(x, pieces)
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    if bias is not None:
+        bias = bias.float().contiguous()
+    args = _lib.GemmArgs(a_packed=_ptr(a), a_pitch=a.stride(0), a_sf=_ptr(a_sf), a_pieces=pieces,
+                         a_piece_rows=piece_rows, a_row_scale=_ptr(row_scale), b_packed=_ptr(b_packed),
+                         b_pitch=b_packed.stride(0), b_sf=_ptr(b_sf), alpha=float(alpha), bias=_ptr(bias),
+                         activation=int(activation), out=_ptr(out), out_dtype=_dt(out), ldo=out.stride(0),
+                         M=M, N=N, K=K)
+    _gemm_ex(args, x.device)
+    return out
+
+
+def qkv_tile_permutation(q_dim, head_dim=256):
+    """Row order of the stacked [Wq; Wk; Wv] the fused-QKV kernel expects: every 128-row tile holds 64
+    rows of one head's first half followed by their rotate-half partners (+ head_dim / 2)."""
+    if head_dim != 256:
+        raise TurboPiError("the fused QKV kernel is built for head_dim 256")
+    heads = q_dim // 256 + 2
+    idx = []
+    for h in range(heads):
+        for half in range(2):
+            base = h * 256 + half * 64
+            idx += list(range(base, base + 64)) + list(range(base + 128, base + 192))
+    return torch.tensor(idx, dtype=torch.long)
+
+
+def rope_tables(num_positions, head_dim=256, theta=10000.0, device="cuda"):
+    """cos / sin tables [positions, head_dim / 2] in bf16, computed the way the model does:
+    inv_freq in fp32 rounded to bf16, pos * inv_freq in fp32, cos / sin rounded to bf16."""
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim))
+    inv = inv.to(torch.bfloat16).float()
+    f = torch.arange(num_positions, dtype=torch.float32)[:, None] * inv[None, :]
+    return f.cos().to(torch.bfloat16).to(device).contiguous(), f.sin().to(torch.bfloat16).to(device).contiguous()
+
+
+def fused_qkv_rope_append(x, w_packed, w_sf, q_dim, k_rows, v_rows, positions, rope_cos, rope_sin, alpha=1.0,
+                          pieces=3, q_out=None):
+    """q = RoPE(x Wq^T), cache K rows <- RoPE(x Wk^T), cache V rows <- x Wv^T in ONE kernel.
+    x [M, H] bf16; w_packed / w_sf: tile-permuted stacked [Wq; Wk; Wv] (qkv_tile_permutation) in NVFP4;
+    k_rows / v_rows: views of the cache whose row 0 is the first token's row, row stride 256 (bf16);
+    positions int32 [M].  Returns q [M, q_dim] bf16."""
+    _cuda(x, w_packed, w_sf, k_rows, v_rows, positions, rope_cos, rope_sin)
+    M, K = x.shape
+    N = q_dim + 512
+    if k_rows.stride(0) != 256 or v_rows.stride(0) != 256 or k_rows.dtype != torch.bfloat16:
+        raise TurboPiError("cache rows must be bf16 with a row stride of 256 elements")
+    a, a_sf, row_scale, piece_rows = nvfp4_quantize_act_pieces(x, pieces)
+    if q_out is None:
+        q_out = torch.empty((M, q_dim), dtype=torch.bfloat16, device=x.device)
+    args = _lib.GemmArgs(a_packed=_ptr(a), a_pitch=a.stride(0), a_sf=_ptr(a_sf), a_pieces=pieces,
+                         a_piece_rows=piece_rows, a_row_scale=_ptr(row_scale), b_packed=_ptr(w_packed),
+                         b_pitch=w_packed.stride(0), b_sf=_ptr(w_sf), alpha=float(alpha), M=M, N=N, K=K,
+                         qkv_q_out=_ptr(q_out), qkv_ldq=q_out.stride(0), qkv_q_dim=q_dim, qkv_k_rows=_ptr(k_rows),
+                         qkv_v_rows=_ptr(v_rows), qkv_positions=_ptr(positions), qkv_rope_cos=_ptr(rope_cos),
+                         qkv_rope_sin=_ptr(rope_sin))
+    _gemm_ex(args, x.device)
+    return q_out
