@@ -76,7 +76,7 @@ def apply_rope_bf16(x, cos, sin):
 
 
 def fused_qkv_rope_append(x, w_q, w_k, w_v, cache, layer, positions, cache_pos0,
-                          num_heads=8, num_kv_heads=1, head_dim=256, theta=10000.0):
+                          num_heads=8, num_kv_heads=1, head_dim=256, theta=10000.0, cos_sin=None):
     """Prefix-shaped fused projection: the computation of
     `compute_prefix_kv_cache` for one layer's attention inputs
     (openpi/src/openpi/models_pytorch/pi0_pytorch.py:455-473): q/k/v = x W^T rounded
@@ -92,7 +92,7 @@ def fused_qkv_rope_append(x, w_q, w_k, w_v, cache, layer, positions, cache_pos0,
     q = xb @ np.asarray(w_q, dtype=np.float64).T
     k = xb @ np.asarray(w_k, dtype=np.float64).T
     v = xb @ np.asarray(w_v, dtype=np.float64).T
-    cos, sin = rope_cos_sin(positions, head_dim, theta)
+    cos, sin = cos_sin if cos_sin is not None else rope_cos_sin(positions, head_dim, theta)
     qb = round_to_bf16(q.astype(np.float32)).reshape(S, num_heads, head_dim)
     kb = round_to_bf16(k.astype(np.float32)).reshape(S, num_kv_heads, head_dim)
     vb = round_to_bf16(v.astype(np.float32)).reshape(S, num_kv_heads, head_dim)
