@@ -36,6 +36,9 @@ HIDDEN, INTER = 1024, 4096
 SHAPES = [(INTER, HIDDEN), (INTER, HIDDEN), (HIDDEN, INTER)]      # (N, K): gate, up, down
 BLOCK = 16
 NSETS = 4
+# dram__bytes_read.sum + dram__bytes_write.sum of one grouped launch over this workload, from the ncu
+# capture summarised in profiles/gemv_rowmajor_grouped54.md (127.46 MB read + 3.97 MB written)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 131436544
 METRIC = "nvfp4_gemv_hbm_gbps"
 UNIT = "GB/s"
 
@@ -238,13 +241,7 @@ def run_ours(args):
         total_bytes = STEP_BYTES * args.steps * world
         value = total_bytes / (ms / 1e3) / 1e9
         achieved = STEP_BYTES / per_launch_s / 1e9
-        traffic = None
-        tf = ROOT / "profiles" / "traffic.json"
-        if tf.exists():
-            try:
-                traffic = json.loads(tf.read_text()).get("nvfp4_gemv_grouped_54_bytes_per_launch")
-            except Exception:
-                traffic = None
+        traffic = NCU_TRAFFIC_BYTES_PER_LAUNCH
         cpu = cpu_baseline_sample() if world == 1 else None
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,

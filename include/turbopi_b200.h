@@ -165,6 +165,32 @@ int tpb200_nvfp4_quantize_act_pieces(const void* x, int x_dtype, int ldx, void* 
                                      int piece_rows, tpb200_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * NVFP4 weight-only GEMV for decode shapes (M <= 16) on the tensor cores: same result as
+ * tpb200_nvfp4_gemv (E4M3 block-16 scales + global scale), no per-weight work on the SM.  Weights are
+ * given PRE-TILED: [row tile of 128][K stage of 256][128 rows][128 B] with the 16-byte chunk c of row r
+ * stored at chunk c ^ (r & 7) (N padded to 128, K to 256 with zero codes), scales in the GEMM's atom
+ * layout.  Activations are first turned into `pieces` residual e2m1 operands in the same tiled image by
+ * tpb200_nvfp4_quantize_act_tc (x_tiled: ceil(K/256) * 16*pieces*128 bytes, x_sf: ceil(K/256) * 2048
+ * bytes, x_row_scale: 16 floats).  Row tiles whose K range is split across CTAs are combined through
+ * `workspace` (size from tpb200_nvfp4_gemv_tc_workspace_size; the caller zeroes it ONCE after
+ * allocation, the kernel leaves its counters at zero).  Launches that share a workspace must not
+ * overlap.  No counterpart in the reference (its GEMVs are CUDA-core kernels).
+ * ------------------------------------------------------------------------------------------- */
+typedef struct {
+    const void* w_tiled; const void* w_sf;
+    const void* x_tiled; const void* x_sf; const float* x_row_scale;
+    const void* bias; void* out;
+    int N; int K; int ldo; /* 0 = N */
+    float global_scale;
+} tpb200_gemv_tc_problem;
+size_t tpb200_nvfp4_gemv_tc_workspace_size(const tpb200_gemv_tc_problem* problems, int count);
+int tpb200_nvfp4_quantize_act_tc(const void* x, int x_dtype, int ldx, void* x_tiled, void* x_sf, float* row_scale,
+                                 int M, int K, int pieces, int flags, tpb200_stream_t stream);
+int tpb200_nvfp4_gemv_tc(const tpb200_gemv_tc_problem* problems, int count, int M, int pieces, int bias_dtype,
+                         int out_dtype, int activation, void* workspace, size_t workspace_bytes, int flags,
+                         tpb200_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Entry points with the reference's names and signatures (TensorRT-plugin / test ABI).
  * ------------------------------------------------------------------------------------------- */
 

@@ -1,0 +1,83 @@
+"""Parity of the tensor-core NVFP4 GEMV (weights as the MMA's 128-row operand, residual-piece
+activations, split-K through scratch) with the CPU oracle and with the CUDA-core GEMV."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import cosine, rel_err
+from oracle import formats, nvfp4
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev(a, device, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a)).to(device)
+    return t if dtype is None else t.to(dtype)
+
+
+def _weights(rng, N, K):
+    base = (rng.normal(size=(N, K)) * 0.02).astype(np.float32)
+    _, sbytes, g = nvfp4.quantize_two_level(base, 16)
+    packed = rng.integers(0, 256, size=(N, K // 2), dtype=np.uint8)
+    return packed, sbytes, float(g)
+
+
+def test_weight_tiling_is_the_swizzled_image(cuda_device):
+    from turbopi_b200 import ops
+    rng = np.random.default_rng(1)
+    N, K = 200, 1024 + 512
+    packed = rng.integers(0, 256, size=(N, K // 2), dtype=np.uint8)
+    tiled = ops.tile_weights_for_tc(torch.from_numpy(packed), N, K).numpy().reshape(2, 6, 128, 8, 16)
+    for (n, kbyte) in [(0, 0), (1, 17), (129, 300), (199, 767), (77, 640)]:
+        rt, r = divmod(n, 128)
+        ks, within = divmod(kbyte, 128)
+        c, b = divmod(within, 16)
+        assert tiled[rt, ks, r, c ^ (r & 7), b] == packed[n, kbyte]
+    assert tiled[1, :, 72:, :, :].sum() == 0          # padded rows are zero codes
+
+
+@pytest.mark.parametrize("M", [1, 4, 16])
+@pytest.mark.parametrize("N,K", [(4096, 1024), (1024, 4096), (16384, 2048), (2048, 16384), (200, 272), (2560, 2048)])
+def test_tc_gemv_matches_oracle(cuda_device, M, N, K):
+    from turbopi_b200 import _lib, ops
+    rng = np.random.default_rng(M + N + K)
+    packed, sbytes, g = _weights(rng, N, K)
+    x = formats.round_to_bf16((rng.normal(size=(M, K)) * rng.choice([0.1, 1.0, 10.0], size=(M, 1))).astype(np.float32))
+    bias = rng.normal(size=(N,)).astype(np.float32)
+    buf = torch.full((M + 32, N), -5.0, dtype=torch.float32, device=cuda_device)
+    out = buf[16:16 + M]
+    tc = ops.TcGemv([dict(x=_dev(x, cuda_device, torch.bfloat16), weight_packed=_dev(packed, cuda_device),
+                          weight_scales=_dev(sbytes, cuda_device), global_scale=g, out=out,
+                          bias=_dev(bias, cuda_device))], pieces=3)
+    tc.launch()
+    tc.launch()                       # the counters are back at zero: a second launch gives the same bytes
+    y1 = out.cpu().numpy().copy()
+    tc.launch()
+    assert np.array_equal(out.cpu().numpy(), y1)
+    assert _lib.load().tpb200_device_error(0) == 0
+    ref = nvfp4.gemv_dequant_matmul(x, packed, sbytes, bias, 0, 16, g, True)
+    err = np.abs(y1 - ref).max(axis=1) / np.abs(ref).max(axis=1)
+    assert err.max() <= 1e-2, err.max()
+    assert cosine(y1, ref) >= 0.999
+    assert (buf[:16] == -5.0).all() and (buf[16 + M:] == -5.0).all()
+    assert int(tc.workspace[:4096].view(torch.int32).abs().sum()) == 0 or N * K < 1 << 20   # counters reset
+
+
+def test_tc_grouped_matches_cuda_core_gemv(cuda_device):
+    from turbopi_b200 import ops
+    rng = np.random.default_rng(3)
+    shapes = [(4096, 1024), (4096, 1024), (1024, 4096)] * 2
+    xs = {K: _dev(formats.round_to_bf16(rng.normal(size=(1, K)).astype(np.float32)), cuda_device, torch.bfloat16)
+          for K in (1024, 4096)}
+    probs, refs = [], []
+    for N, K in shapes:
+        packed, sbytes, g = _weights(rng, N, K)
+        p = dict(x=xs[K], weight_packed=_dev(packed, cuda_device), weight_scales=_dev(sbytes, cuda_device),
+                 global_scale=g, out=torch.zeros((1, N), dtype=torch.bfloat16, device=cuda_device))
+        probs.append(p)
+        o = torch.empty((1, N), dtype=torch.bfloat16, device=cuda_device)
+        ops.nvfp4_gemv_out(p["x"], p["weight_packed"], p["weight_scales"], o, block_size=16, global_scale=g)
+        refs.append(o)
+    ops.TcGemv(probs, pieces=3, activation=0).launch()
+    for p, o in zip(probs, refs):
+        assert rel_err(p["out"].float().cpu().numpy(), o.float().cpu().numpy()) <= 1e-2

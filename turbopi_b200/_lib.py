@@ -40,6 +40,12 @@ class GemmArgs(ctypes.Structure):
                 ("qkv_positions", c_void_p), ("qkv_rope_cos", c_void_p), ("qkv_rope_sin", c_void_p)]
 
 
+class GemvTcProblem(ctypes.Structure):
+    _fields_ = [("w_tiled", c_void_p), ("w_sf", c_void_p), ("x_tiled", c_void_p), ("x_sf", c_void_p),
+                ("x_row_scale", c_void_p), ("bias", c_void_p), ("out", c_void_p),
+                ("N", c_int), ("K", c_int), ("ldo", c_int), ("global_scale", c_float)]
+
+
 # name -> (restype, argtypes); every symbol include/turbopi_b200.h declares
 SIGNATURES = {
     "tpb200_version": (c_int, []),
@@ -59,6 +65,11 @@ SIGNATURES = {
     "tpb200_nvfp4_gemm_ex": (c_int, [ctypes.POINTER(GemmArgs), c_void_p]),
     "tpb200_nvfp4_quantize_act_pieces": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int,
                                                  c_int, c_int, c_int, c_void_p]),
+    "tpb200_nvfp4_gemv_tc_workspace_size": (c_size_t, [ctypes.POINTER(GemvTcProblem), c_int]),
+    "tpb200_nvfp4_quantize_act_tc": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                             c_int, c_void_p]),
+    "tpb200_nvfp4_gemv_tc": (c_int, [ctypes.POINTER(GemvTcProblem), c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                     c_size_t, c_int, c_void_p]),
     "nvfp4_gemv_forward": (None, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                   c_int, c_int, c_void_p]),
     "nvfp4_gemv_workspace_size": (c_size_t, [c_int, c_int, c_int]),

@@ -1,0 +1,601 @@
+// Decode-shaped (M <= 16 tokens) NVFP4 weight-only GEMV on the tensor cores.
+//
+// The CUDA-core GEMV is bound by instruction issue (decode + FMA per weight); here the SM does
+// no per-weight work at all.  The roles of a GEMM are swapped: a 128-row slab of the WEIGHT
+// matrix is the A operand of tcgen05.mma kind::mxf4nvf4, the activations are the B operand.
+// bf16 activations keep their precision as residual e2m1 pieces (see nvfp4_gemm.cu) stacked
+// along N: piece p of token t is B row 16 p + t, so one MMA (N = 16 * pieces) per 64-wide K
+// atom handles all pieces and the epilogue adds the pieces' columns.
+//
+// Both operands are stored PRE-TILED in the shared-memory image of the 128-byte swizzle
+// ([row tile][K stage][128 rows][128 B], 16-byte chunk c of row r at chunk c ^ (r & 7)), so a
+// stage is four plain 1-D bulk copies (weights 16 KB, weight scales 2 KB, activation tile,
+// activation scales 2 KB) -- no tensor maps, any number of problems per launch.
+//
+// Work unit = (problem, row tile, K split).  CTAs own contiguous unit ranges.  A tile whose K
+// range is split writes per-split partial sums (only the valid tokens) to caller-provided
+// scratch; the CTA that arrives last on the tile's counter adds them in split order
+// (deterministic), applies the epilogue and resets the counter.  Nothing ever waits on another
+// CTA.
+#include <algorithm>
+#include <atomic>
+
+#include "tcgen05.cuh"
+
+namespace tpb {
+namespace {
+
+constexpr int kStages = 6;
+constexpr int kWTile = 128 * 128;     // weight tile bytes per stage
+constexpr int kSfSlab = 2048;         // 4 scale atoms
+constexpr int kMaxNB = 64;            // 16 tokens x 4 pieces
+constexpr int kStageBytes = kWTile + kSfSlab + kMaxNB * 128 + kSfSlab;
+constexpr int kThreads = 192;
+constexpr int kTmemCols = 256;
+constexpr uint32_t kSfaCol = 2 * kMaxNB;       // after two accumulators of up to 64 columns
+constexpr uint32_t kSfbCol = kSfaCol + 16;
+constexpr int kMaxProblems = TPB200_MAX_GROUP;
+
+struct TcProblem {
+    const uint8_t* w_tiled;     // [row_tiles][k_stages][16384]
+    const uint8_t* w_sf;        // [row_tiles][k_stages][2048]
+    const uint8_t* x_tiled;     // [k_stages][NB * 128]
+    const uint8_t* x_sf;        // [k_stages][2048]
+    const float* row_scale;     // [M]
+    const void* bias;
+    void* out;
+    int N, K;
+    int ldo;
+    float global_scale;
+    int k_stages;
+    int row_tiles;
+    int splits;                 // K splits per row tile
+    int stages_per_split;
+    int unit_begin;
+    int scratch_off;            // float offset of this problem's partials [splits][16][row_tiles*128]
+    int counter_off;            // int offset of this problem's per-tile counters
+};
+
+struct TcParams {
+    int num_problems;
+    int total_units;
+    int M;
+    int pieces;
+    int bias_dtype, out_dtype, activation;
+    float* scratch;
+    int* counters;
+    TcProblem prob[kMaxProblems];
+};
+
+struct SharedControl {
+    uint64_t full[kStages];
+    uint64_t empty[kStages];
+    uint64_t acc_full[2];
+    uint64_t acc_empty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+    int ticket;
+};
+
+__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+
+struct Unit {
+    int p, rt, split, ks0, ks1;
+};
+
+__device__ __forceinline__ Unit decode_unit(const TcParams& P, int u, int& p_hint) {
+    while (p_hint + 1 < P.num_problems && u >= P.prob[p_hint + 1].unit_begin) ++p_hint;
+    const TcProblem& pr = P.prob[p_hint];
+    const int local = u - pr.unit_begin;
+    Unit un;
+    un.p = p_hint;
+    un.rt = local / pr.splits;
+    un.split = local - un.rt * pr.splits;
+    un.ks0 = un.split * pr.stages_per_split;
+    un.ks1 = min(pr.k_stages, un.ks0 + pr.stages_per_split);
+    return un;
+}
+
+__global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid_constant__ TcParams P) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    SharedControl* ctl = reinterpret_cast<SharedControl*>(smem + kStages * kStageBytes);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int NB = 16 * P.pieces;
+    const int unit_lo = static_cast<int>(static_cast<long long>(blockIdx.x) * P.total_units / gridDim.x);
+    const int unit_hi = static_cast<int>(static_cast<long long>(blockIdx.x + 1) * P.total_units / gridDim.x);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&ctl->full[s], 1);
+            mbar_init(&ctl->empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&ctl->acc_full[b], 1);
+            mbar_init(&ctl->acc_empty[b], 4);
+        }
+        ctl->abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 1) {
+        tc::tmem_alloc(&ctl->tmem_base, kTmemCols);
+        tc::tmem_relinquish();
+    }
+    tc::fence_before_thread_sync();
+    __syncthreads();
+    tc::fence_after_thread_sync();
+    const uint32_t tmem_base = ctl->tmem_base;
+    volatile int* abort_flag = &ctl->abort_flag;
+    pdl_launch_dependents();
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ producer: four bulk copies per stage.
+        // Weights never depend on the previous kernel, so they are requested before griddepcontrol.wait
+        // would matter; activations are produced by the previous kernel, so this lane waits first.
+        if (lane == 0) {
+            const uint32_t xbytes = static_cast<uint32_t>(NB) * 128u;
+            // prologue: the weight halves of the first stages go out before griddepcontrol.wait
+            int pre = 0;
+            {
+                int ph = 0;
+                for (int u = unit_lo; u < unit_hi && pre < kStages; ++u) {
+                    const Unit un = decode_unit(P, u, ph);
+                    const TcProblem& pr = P.prob[un.p];
+                    for (int ks = un.ks0; ks < un.ks1 && pre < kStages; ++ks, ++pre) {
+                        uint8_t* st = smem + pre * kStageBytes;
+                        const size_t tile = static_cast<size_t>(un.rt) * pr.k_stages + ks;
+                        mbar_expect_tx(&ctl->full[pre], kWTile + kSfSlab + xbytes + kSfSlab);
+                        bulk_copy_g2s(st, pr.w_tiled + tile * kWTile, kWTile, &ctl->full[pre]);
+                        bulk_copy_g2s(st + kWTile, pr.w_sf + tile * kSfSlab, kSfSlab, &ctl->full[pre]);
+                    }
+                }
+            }
+            pdl_wait_prior_grids();   // the activation tiles are written by the previous kernel
+            int it = 0, ph = 0;
+            for (int u = unit_lo; u < unit_hi && !*abort_flag; ++u) {
+                const Unit un = decode_unit(P, u, ph);
+                const TcProblem& pr = P.prob[un.p];
+                for (int ks = un.ks0; ks < un.ks1; ++ks, ++it) {
+                    const int s = it % kStages;
+                    uint8_t* st = smem + s * kStageBytes;
+                    const size_t tile = static_cast<size_t>(un.rt) * pr.k_stages + ks;
+                    if (it >= pre) {
+                        if (it >= kStages && !mbar_wait_bounded(&ctl->empty[s], ((it / kStages) - 1) & 1)) {
+                            record_error(kErrGemmEmptyBarrierTimeout);
+                            *abort_flag = 1;
+                            break;
+                        }
+                        mbar_expect_tx(&ctl->full[s], kWTile + kSfSlab + xbytes + kSfSlab);
+                        bulk_copy_g2s(st, pr.w_tiled + tile * kWTile, kWTile, &ctl->full[s]);
+                        bulk_copy_g2s(st + kWTile, pr.w_sf + tile * kSfSlab, kSfSlab, &ctl->full[s]);
+                    }
+                    bulk_copy_g2s(st + kWTile + kSfSlab, pr.x_tiled + static_cast<size_t>(ks) * xbytes, xbytes,
+                                  &ctl->full[s]);
+                    bulk_copy_g2s(st + kWTile + kSfSlab + kMaxNB * 128, pr.x_sf + static_cast<size_t>(ks) * kSfSlab,
+                                  kSfSlab, &ctl->full[s]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = tc::make_idesc_mxf4nvf4(NB);
+            int it = 0, unit_iter = 0, ph = 0;
+            for (int u = unit_lo; u < unit_hi && !*abort_flag; ++u, ++unit_iter) {
+                const Unit un = decode_unit(P, u, ph);
+                const int buf = unit_iter & 1;
+                if (unit_iter >= 2 && !mbar_wait_bounded(&ctl->acc_empty[buf], ((unit_iter >> 1) - 1) & 1)) {
+                    record_error(kErrGemmEpilogueBarrierTimeout);
+                    *abort_flag = 1;
+                    break;
+                }
+                tc::fence_after_thread_sync();
+                const uint32_t tmem_acc = tmem_base + buf * kMaxNB;
+                for (int ks = un.ks0; ks < un.ks1; ++ks, ++it) {
+                    const int s = it % kStages;
+                    if (!mbar_wait_bounded(&ctl->full[s], (it / kStages) & 1)) {
+                        record_error(kErrGemmTmaBarrierTimeout);
+                        *abort_flag = 1;
+                        break;
+                    }
+                    tc::fence_after_thread_sync();
+                    const uint32_t st = smem_u32(smem + s * kStageBytes);
+                    const uint32_t sfa_s = st + kWTile;
+                    const uint32_t xt_s = sfa_s + kSfSlab;
+                    const uint32_t sfb_s = xt_s + kMaxNB * 128;
+#pragma unroll
+                    for (int a = 0; a < 4; ++a) {
+                        tc::cp_sf_32x128b(tmem_base + kSfaCol + 4 * a, tc::make_sf_desc(sfa_s + a * 512));
+                        tc::cp_sf_32x128b(tmem_base + kSfbCol + 4 * a, tc::make_sf_desc(sfb_s + a * 512));
+                    }
+#pragma unroll
+                    for (int a = 0; a < 4; ++a) {
+                        tc::mma_mxf4nvf4(tmem_acc, tc::make_kmajor_sw128_desc(st, a * 32),
+                                         tc::make_kmajor_sw128_desc(xt_s, a * 32), idesc, tmem_base + kSfaCol + 4 * a,
+                                         tmem_base + kSfbCol + 4 * a, (ks > un.ks0) || (a != 0));
+                    }
+                    tc::commit(&ctl->empty[s]);
+                }
+                tc::commit(&ctl->acc_full[buf]);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (warps 2..5, 128 threads)
+        const int q = warp & 3;
+        const int et = q * 32 + lane;            // 0..127: the weight row inside the tile
+        int unit_iter = 0, ph = 0;
+        pdl_wait_prior_grids();                   // the output buffer may still be read by the previous kernel
+        for (int u = unit_lo; u < unit_hi && !*abort_flag; ++u, ++unit_iter) {
+            const Unit un = decode_unit(P, u, ph);
+            const TcProblem& pr = P.prob[un.p];
+            const int buf = unit_iter & 1;
+            if (!mbar_wait_bounded(&ctl->acc_full[buf], (unit_iter >> 1) & 1)) {
+                record_error(kErrGemmMmaBarrierTimeout);
+                *abort_flag = 1;
+                break;
+            }
+            tc::fence_after_thread_sync();
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * kMaxNB;
+            float v[16];
+#pragma unroll
+            for (int t = 0; t < 16; ++t) v[t] = 0.0f;
+            for (int pc = 0; pc < P.pieces; ++pc) {
+                uint32_t r[16];
+                tmem_ld_32x32b_x16(taddr + pc * 16, r);
+                tc::tmem_ld_wait();
+#pragma unroll
+                for (int t = 0; t < 16; ++t) v[t] += __uint_as_float(r[t]);
+            }
+            tc::fence_before_thread_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&ctl->acc_empty[buf]);
+
+            const int n = un.rt * 128 + et;
+            const int n_pad = pr.row_tiles * 128;
+            bool finalize = true;
+            if (pr.splits > 1) {
+                float* part = P.scratch + pr.scratch_off;
+#pragma unroll
+                for (int t = 0; t < 16; ++t) {
+                    if (t < P.M) part[(static_cast<size_t>(un.split) * 16 + t) * n_pad + n] = v[t];
+                }
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (et == 0) ctl->ticket = atomicAdd(P.counters + pr.counter_off + un.rt, 1);
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                finalize = (ctl->ticket == pr.splits - 1);
+                if (finalize) {
+                    __threadfence();
+#pragma unroll
+                    for (int t = 0; t < 16; ++t) {
+                        if (t < P.M) {
+                            float acc = 0.0f;
+                            for (int sp = 0; sp < pr.splits; ++sp) {
+                                acc += __ldcg(part + (static_cast<size_t>(sp) * 16 + t) * n_pad + n);
+                            }
+                            v[t] = acc;
+                        }
+                    }
+                    if (et == 0) P.counters[pr.counter_off + un.rt] = 0;   // ready for the next launch
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");              // ticket slot free for the next unit
+            }
+            if (finalize && n < pr.N) {
+#pragma unroll
+                for (int t = 0; t < 16; ++t) {
+                    if (t < P.M) {
+                        float f = v[t] * pr.global_scale * __ldg(pr.row_scale + t);
+                        if (pr.bias != nullptr) f += load_as_float(pr.bias, P.bias_dtype, n);
+                        f = apply_activation(f, P.activation);
+                        store_from_float(pr.out, P.out_dtype, static_cast<size_t>(t) * pr.ldo + n, f);
+                    }
+                }
+            }
+        }
+    }
+
+    tc::fence_before_thread_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc::fence_after_thread_sync();
+        tc::tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Activation pieces in the tiled image: one CTA per token row t < 16 (rows >= M are zeroed).
+// Same arithmetic as nvfp4_quantize_pieces_kernel in nvfp4_gemm.cu.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t e2m1_index(float a) {
+    return (a > 0.25f) + (a > 0.75f) + (a > 1.25f) + (a > 1.75f) + (a > 2.5f) + (a > 3.5f) + (a > 5.0f);
+}
+
+__device__ __forceinline__ float e4m3_round_up(float v, uint8_t& code) {
+    code = encode_e4m3(v);
+    float d = decode_e4m3(code);
+    if (d < v && code < 0x7E) {
+        code += 1;
+        d = decode_e4m3(code);
+    }
+    return d;
+}
+
+__global__ void __launch_bounds__(256) quantize_pieces_tiled_kernel(const void* __restrict__ x, int x_dtype, int ldx,
+                                                                    uint8_t* __restrict__ x_tiled,
+                                                                    uint8_t* __restrict__ x_sf,
+                                                                    float* __restrict__ row_scale, int M, int K,
+                                                                    int pieces) {
+    pdl_launch_dependents();
+    pdl_wait_prior_grids();
+    const int t = blockIdx.x;                 // 0..15
+    const int NB = 16 * pieces;
+    const int nblk = K >> 4;
+    const int kb_pad = (K + 255) / 256 * 16;
+    __shared__ float red[8];
+    float amax = 0.0f;
+    if (t < M) {
+        for (int i = threadIdx.x; i < K; i += blockDim.x) {
+            amax = fmaxf(amax, fabsf(load_as_float(x, x_dtype, static_cast<size_t>(t) * ldx + i)));
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = red[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) amax = fmaxf(amax, red[i]);
+    int e = 0;
+    if (amax > 0.0f && amax < 3.0e38f) {
+        int ex;
+        frexpf(amax, &ex);
+        e = 11 - ex;
+    }
+    const float pre = ldexpf(1.0f, e);
+    if (threadIdx.x == 0 && t < M) row_scale[t] = ldexpf(1.0f, -e);
+
+    for (int kb = threadIdx.x; kb < kb_pad; kb += blockDim.x) {
+        float r[16];
+        const bool valid = (t < M) && (kb < nblk);
+        if (valid) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                r[i] = load_as_float(x, x_dtype, static_cast<size_t>(t) * ldx + kb * 16 + i) * pre;
+            }
+        }
+        const int ks = kb >> 4;
+        const int c = (kb & 15) >> 1;            // 16-byte chunk of the 128-byte row
+        for (int p = 0; p < pieces; ++p) {
+            const int prow = p * 16 + t;
+            uint8_t* dst = x_tiled + static_cast<size_t>(ks) * (NB * 128) + prow * 128 + ((c ^ (prow & 7)) << 4) +
+                           (kb & 1) * 8;
+            const size_t sf_off = static_cast<size_t>(ks) * 2048 + ((kb >> 2) & 3) * 512 + (prow & 31) * 16 +
+                                  ((prow >> 5) & 3) * 4 + (kb & 3);
+            if (!valid) {
+                x_sf[sf_off] = 0;
+                *reinterpret_cast<uint2*>(dst) = make_uint2(0u, 0u);
+                continue;
+            }
+            float bmax = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) bmax = fmaxf(bmax, fabsf(r[i]));
+            uint8_t code;
+            const float s = e4m3_round_up(bmax * (1.0f / 6.0f), code);
+            x_sf[sf_off] = code;
+            const float inv = s > 0.0f ? 1.0f / s : 0.0f;
+            uint32_t lo = 0, hi = 0;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const float a = fminf(fabsf(r[i]) * inv, 6.0f);
+                const uint32_t idx = e2m1_index(a);
+                const float mag = idx < 4 ? 0.5f * idx : (idx == 4 ? 2.0f : (idx == 5 ? 3.0f : (idx == 6 ? 4.0f : 6.0f)));
+                const bool neg = r[i] < 0.0f;
+                const uint32_t cc = (neg && idx != 0) ? (idx | 8u) : idx;
+                r[i] -= (neg ? -mag : mag) * s;
+                if (i < 8) lo |= cc << (4 * i);
+                else hi |= cc << (4 * (i - 8));
+            }
+            *reinterpret_cast<uint2*>(dst) = make_uint2(lo, hi);
+        }
+    }
+}
+
+}  // namespace
+
+int device_error_gemv_tc(int clear) { return read_device_error(clear); }
+
+}  // namespace tpb
+
+// ---------------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+struct TcPlan {
+    int splits[TPB200_MAX_GROUP];
+    int stages_per_split[TPB200_MAX_GROUP];
+    size_t scratch_floats;
+    size_t counters;
+    int total_units;
+};
+
+// shared by the workspace query and the launch so that both see the same layout
+int make_plan(const tpb200_gemv_tc_problem* probs, int count, int sms, TcPlan& plan) {
+    long long total_stages = 0;
+    for (int i = 0; i < count; ++i) {
+        if (probs[i].N < 1 || probs[i].K < 16 || probs[i].K % 16 != 0) return TPB200_ERR_SHAPE;
+        const long long row_tiles = (probs[i].N + 127) / 128;
+        total_stages += row_tiles * ((probs[i].K + 255) / 256);
+    }
+    // aim for ~4 units per SM, units of 1..8 stages
+    const int target = static_cast<int>(std::min<long long>(8, std::max<long long>(1, total_stages / (4LL * sms))));
+    plan.scratch_floats = 0;
+    plan.counters = 0;
+    plan.total_units = 0;
+    for (int i = 0; i < count; ++i) {
+        const int row_tiles = (probs[i].N + 127) / 128;
+        const int k_stages = (probs[i].K + 255) / 256;
+        int splits = (k_stages + target - 1) / target;
+        const int sps = (k_stages + splits - 1) / splits;
+        splits = (k_stages + sps - 1) / sps;
+        plan.splits[i] = splits;
+        plan.stages_per_split[i] = sps;
+        if (splits > 1) {
+            plan.scratch_floats += static_cast<size_t>(splits) * 16 * row_tiles * 128;
+            plan.counters += row_tiles;
+        }
+        plan.total_units += row_tiles * splits;
+    }
+    return TPB200_OK;
+}
+
+int device_sms(int& sms) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+        return TPB200_ERR_CUDA;
+    }
+    return TPB200_OK;
+}
+
+}  // namespace
+
+extern "C" size_t tpb200_nvfp4_gemv_tc_workspace_size(const tpb200_gemv_tc_problem* problems, int count) {
+    if (problems == nullptr || count < 1 || count > TPB200_MAX_GROUP) return 0;
+    int sms = 0;
+    if (device_sms(sms) != TPB200_OK) return 0;
+    TcPlan plan;
+    if (make_plan(problems, count, sms, plan) != TPB200_OK) return 0;
+    // counters first (zero-initialised by the caller once), then the partial sums
+    return (plan.counters * sizeof(int) + 255) / 256 * 256 + plan.scratch_floats * sizeof(float) + 256;
+}
+
+extern "C" int tpb200_nvfp4_quantize_act_tc(const void* x, int x_dtype, int ldx, void* x_tiled, void* x_sf,
+                                            float* row_scale, int M, int K, int pieces, int flags,
+                                            tpb200_stream_t stream) {
+    TPB_REQUIRE(x && x_tiled && x_sf && row_scale, TPB200_ERR_NULL);
+    TPB_REQUIRE(M >= 1 && M <= 16 && K >= 16 && K % 16 == 0 && ldx >= K, TPB200_ERR_SHAPE);
+    TPB_REQUIRE(pieces >= 1 && pieces <= 4, TPB200_ERR_SHAPE);
+    TPB_REQUIRE(tpb_valid_dtype(x_dtype), TPB200_ERR_ENUM);
+    TPB_REQUIRE((flags & ~TPB200_FLAG_PDL) == 0, TPB200_ERR_ENUM);
+    TPB_REQUIRE(tpb_aligned16(x_tiled) && tpb_aligned16(x_sf), TPB200_ERR_ALIGN);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(16, 1, 1);
+    cfg.blockDim = dim3(256, 1, 1);
+    cfg.stream = reinterpret_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    if (flags & TPB200_FLAG_PDL) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    if (cudaLaunchKernelEx(&cfg, tpb::quantize_pieces_tiled_kernel, x, x_dtype, ldx, static_cast<uint8_t*>(x_tiled),
+                           static_cast<uint8_t*>(x_sf), row_scale, M, K, pieces) != cudaSuccess) {
+        return TPB200_ERR_CUDA;
+    }
+    return TPB200_OK;
+}
+
+extern "C" int tpb200_nvfp4_gemv_tc(const tpb200_gemv_tc_problem* problems, int count, int M, int pieces,
+                                    int bias_dtype, int out_dtype, int activation, void* workspace,
+                                    size_t workspace_bytes, int flags, tpb200_stream_t stream) {
+    TPB_REQUIRE(problems != nullptr, TPB200_ERR_NULL);
+    TPB_REQUIRE(count >= 1 && count <= TPB200_MAX_GROUP, TPB200_ERR_SHAPE);
+    TPB_REQUIRE(M >= 1 && M <= 16 && pieces >= 1 && pieces <= 4, TPB200_ERR_SHAPE);
+    TPB_REQUIRE(tpb_valid_dtype(bias_dtype) && tpb_valid_dtype(out_dtype), TPB200_ERR_ENUM);
+    TPB_REQUIRE(activation >= TPB200_ACT_NONE && activation <= TPB200_ACT_SILU, TPB200_ERR_ENUM);
+    TPB_REQUIRE((flags & ~TPB200_FLAG_PDL) == 0, TPB200_ERR_ENUM);
+    int sms = 0;
+    if (device_sms(sms) != TPB200_OK) return TPB200_ERR_CUDA;
+    TcPlan plan;
+    const int st = make_plan(problems, count, sms, plan);
+    if (st != TPB200_OK) return st;
+    const size_t counter_bytes = (plan.counters * sizeof(int) + 255) / 256 * 256;
+    if (plan.scratch_floats > 0) {
+        TPB_REQUIRE(workspace != nullptr, TPB200_ERR_WORKSPACE);
+        TPB_REQUIRE(workspace_bytes >= counter_bytes + plan.scratch_floats * sizeof(float), TPB200_ERR_WORKSPACE);
+        TPB_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255u) == 0, TPB200_ERR_ALIGN);
+    }
+
+    tpb::TcParams P;
+    P.num_problems = count;
+    P.total_units = plan.total_units;
+    P.M = M;
+    P.pieces = pieces;
+    P.bias_dtype = bias_dtype;
+    P.out_dtype = out_dtype;
+    P.activation = activation;
+    P.counters = static_cast<int*>(workspace);
+    P.scratch = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + counter_bytes);
+    int units = 0, coff = 0;
+    size_t soff = 0;
+    for (int i = 0; i < count; ++i) {
+        const tpb200_gemv_tc_problem& h = problems[i];
+        TPB_REQUIRE(h.w_tiled && h.w_sf && h.x_tiled && h.x_sf && h.x_row_scale && h.out, TPB200_ERR_NULL);
+        TPB_REQUIRE(tpb_aligned16(h.w_tiled) && tpb_aligned16(h.w_sf) && tpb_aligned16(h.x_tiled) && tpb_aligned16(h.x_sf),
+                    TPB200_ERR_ALIGN);
+        TPB_REQUIRE(h.ldo == 0 || h.ldo >= h.N, TPB200_ERR_SHAPE);
+        tpb::TcProblem& d = P.prob[i];
+        d.w_tiled = static_cast<const uint8_t*>(h.w_tiled);
+        d.w_sf = static_cast<const uint8_t*>(h.w_sf);
+        d.x_tiled = static_cast<const uint8_t*>(h.x_tiled);
+        d.x_sf = static_cast<const uint8_t*>(h.x_sf);
+        d.row_scale = h.x_row_scale;
+        d.bias = h.bias;
+        d.out = h.out;
+        d.N = h.N;
+        d.K = h.K;
+        d.ldo = h.ldo == 0 ? h.N : h.ldo;
+        d.global_scale = h.global_scale;
+        d.k_stages = (h.K + 255) / 256;
+        d.row_tiles = (h.N + 127) / 128;
+        d.splits = plan.splits[i];
+        d.stages_per_split = plan.stages_per_split[i];
+        d.unit_begin = units;
+        d.scratch_off = static_cast<int>(soff);
+        d.counter_off = coff;
+        units += d.row_tiles * d.splits;
+        if (d.splits > 1) {
+            soff += static_cast<size_t>(d.splits) * 16 * d.row_tiles * 128;
+            coff += d.row_tiles;
+        }
+    }
+
+    const size_t smem = tpb::kStages * tpb::kStageBytes + sizeof(tpb::SharedControl) + 1024;
+    static std::atomic<uint64_t> configured{0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const uint64_t bit = 1ull << (dev & 63);
+    if (!(configured.load(std::memory_order_relaxed) & bit)) {
+        if (cudaFuncSetAttribute(tpb::nvfp4_gemv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(smem)) != cudaSuccess) {
+            return TPB200_ERR_CUDA;
+        }
+        configured.fetch_or(bit, std::memory_order_relaxed);
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(std::min(plan.total_units, sms), 1, 1);
+    cfg.blockDim = dim3(tpb::kThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = reinterpret_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    if (flags & TPB200_FLAG_PDL) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    if (cudaLaunchKernelEx(&cfg, tpb::nvfp4_gemv_tc_kernel, P) != cudaSuccess) return TPB200_ERR_CUDA;
+    return TPB200_OK;
+}

@@ -368,3 +368,85 @@ def fused_qkv_rope_append(x, w_packed, w_sf, q_dim, k_rows, v_rows, positions, r
                          qkv_rope_sin=_ptr(rope_sin))
     _gemm_ex(args, x.device)
     return q_out
+
+
+# ------------------------------------------------------------------------------------- tensor-core GEMV
+def tile_weights_for_tc(packed, N, K):
+    """Packed e2m1 weights [N, >= K/2] -> the pre-tiled image the tensor-core GEMV streams:
+    [row tile of 128][K stage of 256][128 rows][128 B], 16-byte chunk c of row r at c ^ (r & 7);
+    N padded to 128 and K to 256 with zero codes.  Pure index shuffle (weight prep, any device)."""
+    rt, ks = (N + 127) // 128, (K + 255) // 256
+    pad = torch.zeros((rt * 128, ks * 128), dtype=torch.uint8, device=packed.device)
+    pad[:N, :K // 2] = packed[:, :K // 2]
+    t = pad.reshape(rt, 128, ks, 8, 16)
+    r = torch.arange(128, device=packed.device)
+    c = torch.arange(8, device=packed.device)
+    src = (c[None, :] ^ (r[:, None] & 7))                        # dest chunk c' holds source chunk c' ^ (r & 7)
+    idx = src[None, :, None, :, None].expand(rt, 128, ks, 8, 16)
+    t = torch.gather(t, 3, idx)
+    return t.permute(0, 2, 1, 3, 4).contiguous().reshape(-1)
+
+
+class TcGemv:
+    """NVFP4 weight-only GEMV(s) for M <= 16 tokens on the tensor cores.  Built once from a list of
+    problems (dicts: weight_packed [N, K/2] uint8, weight_scales [N, K/16] E4M3 bytes, global_scale,
+    x [M, K], out [M, N], optional bias); weights are re-tiled at construction.  `launch()` quantises
+    every distinct activation tensor into residual pieces and enqueues ONE GEMV kernel."""
+
+    def __init__(self, problems, pieces=3, activation=ACT_NONE, pdl=False):
+        if not 1 <= len(problems) <= _lib.MAX_GROUP:
+            raise TurboPiError(f"1..{_lib.MAX_GROUP} problems per launch")
+        p0 = problems[0]
+        self.device = p0["x"].device
+        self.M = p0["x"].shape[0]
+        self.pieces = pieces
+        self.activation = int(activation)
+        self.flags = FLAG_PDL if pdl else FLAG_NONE
+        self.out_dtype = _dt(p0["out"])
+        self.bias_dtype = _dt(p0["bias"]) if p0.get("bias") is not None else F32
+        self._keep = []
+        self._acts = {}           # id(x) -> (x, tiled, sf, row_scale, K)
+        arr = (_lib.GemvTcProblem * len(problems))()
+        for i, p in enumerate(problems):
+            x, w, ws, out = p["x"], p["weight_packed"], p["weight_scales"], p["out"]
+            _cuda(x, w, ws, out, p.get("bias"))
+            N, K = w.shape[0], x.shape[1]
+            if "w_tiled" in p:
+                w_tiled, w_sf = p["w_tiled"], p["w_sf"]
+            else:
+                w_tiled, w_sf = tile_weights_for_tc(w, N, K), swizzle_scales(ws.view(torch.uint8))
+            key = x.data_ptr()
+            if key not in self._acts:
+                ks = (K + 255) // 256
+                self._acts[key] = (x, torch.empty(ks * 16 * pieces * 128, dtype=torch.uint8, device=self.device),
+                                   torch.empty(ks * 2048, dtype=torch.uint8, device=self.device),
+                                   torch.empty(16, dtype=torch.float32, device=self.device), K)
+            _, xt, xsf, rs, _ = self._acts[key]
+            self._keep.append((w_tiled, w_sf, out, p.get("bias")))
+            arr[i] = _lib.GemvTcProblem(_ptr(w_tiled), _ptr(w_sf), _ptr(xt), _ptr(xsf), _ptr(rs), _ptr(p.get("bias")),
+                                        _ptr(out), N, K, out.stride(0), float(p.get("global_scale", 1.0)))
+        self._arr = arr
+        with torch.cuda.device(self.device):
+            nbytes = int(_lib.load().tpb200_nvfp4_gemv_tc_workspace_size(arr, len(arr)))
+        self.workspace = torch.zeros(max(nbytes, 256), dtype=torch.uint8, device=self.device)
+
+    def quantize(self):
+        lib = _lib.load()
+        with torch.cuda.device(self.device):
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+            for (x, xt, xsf, rs, K) in self._acts.values():
+                st = lib.tpb200_nvfp4_quantize_act_tc(_ptr(x), _dt(x), x.stride(0), _ptr(xt), _ptr(xsf), _ptr(rs),
+                                                      self.M, K, self.pieces, self.flags, stream)
+                _lib.check(st, "tpb200_nvfp4_quantize_act_tc")
+
+    def gemv(self):
+        with torch.cuda.device(self.device):
+            st = _lib.load().tpb200_nvfp4_gemv_tc(self._arr, len(self._arr), self.M, self.pieces, self.bias_dtype,
+                                                  self.out_dtype, self.activation, _ptr(self.workspace),
+                                                  self.workspace.numel(), self.flags,
+                                                  torch.cuda.current_stream(self.device).cuda_stream)
+        _lib.check(st, "tpb200_nvfp4_gemv_tc")
+
+    def launch(self):
+        self.quantize()
+        self.gemv()
