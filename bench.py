@@ -167,9 +167,42 @@ def run_ours(args):
         outs.append(o)
         groups.append(ops.GroupedGemv(probs, BLOCK))
     stream = torch.cuda.current_stream(device)
+    tcs = None
+    if args.path == "tc":
+        # tensor-core GEMV: a step = re-quantise the two activation vectors into residual pieces
+        # (2 small launches) + ONE grouped GEMV launch over the 54 matrices
+        tcs = []
+        for s in range(NSETS):
+            probs = [dict(x=x[K], weight_packed=p, weight_scales=sc, global_scale=gs, out=oo)
+                     for (p, sc, gs, N, K), oo in zip(sets[s], outs[s])]
+            tcs.append(ops.TcGemv(probs, pieces=3))
+
+    def launch_step(i):
+        if tcs is not None:
+            tcs[i % NSETS].launch()
+        else:
+            groups[i % NSETS].launch()
+
+    step_graphs = None
+    if not args.no_graph:
+        # one CUDA graph per weight set: a step is a single graph launch on the host side
+        side = torch.cuda.Stream(device=device)
+        with torch.cuda.stream(side):
+            for s in range(NSETS):
+                launch_step(s)
+        torch.cuda.synchronize()
+        step_graphs = []
+        for s in range(NSETS):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                launch_step(s)
+            step_graphs.append(g)
 
     def step(i):
-        groups[i % NSETS].launch()
+        if step_graphs is not None:
+            step_graphs[i % NSETS].replay()
+        else:
+            launch_step(i)
 
     sampler = ClockSampler(local) if rank == 0 else None
     t_wall0 = time.time()
@@ -191,8 +224,8 @@ def run_ours(args):
     barrier_sync(world)
     torch.cuda.profiler.stop()
     ms = max_over_ranks(e0.elapsed_time(e1), world, device)
-    launches = args.steps
-    per_launch_s = (e0.elapsed_time(e1) / 1e3) / launches
+    launches = args.steps * (3 if tcs is not None else 1)
+    per_launch_s = (e0.elapsed_time(e1) / 1e3) / args.steps   # the GEMV launch; the quantisers ride in its shadow
 
     # ---- end to end: host activations in, host results out, through the Python API --------------------
     hx = {K: x[K].cpu().pin_memory() for K in x}
@@ -250,8 +283,11 @@ def run_ours(args):
             "config": {"workload": "NVFP4 weight-only GEMV, M=1, Gemma-300M action-expert MLP, 18 layers x "
                                    "(gate,up 1024->4096; down 4096->1024) = 54 matrices per step, E4M3 block-16 "
                                    "scales + fp32 global scale, bf16 in/out",
-                       "launch": "one grouped launch per step (tpb200_nvfp4_gemv_grouped)",
+                       "launch": ("one grouped launch per step (tpb200_nvfp4_gemv_grouped)" if tcs is None else
+                                  "activation-piece quantiser x2 + one grouped tensor-core launch per step "
+                                  "(tpb200_nvfp4_gemv_tc)"),
                        "l2": f"{NSETS} weight sets of {STEP_BYTES / 1e6:.1f} MB rotated per step (> 126 MB L2)",
+                       "graph": "each step replays one CUDA graph" if step_graphs is not None else "direct launches",
                        "parallelism": f"{world} independent replica(s), no collective",
                        "warmup_note": "warm-up extended to >= 0.4 s so clocks are sampled under load"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
@@ -377,6 +413,24 @@ def run_extras(device, sets, x):
         t = time_launches(lambda i: ops.nvfp4_gemv_out(xb, wp[i % 12], sp[i % 12], ob, block_size=16,
                                                        global_scale=1e-3), 48)
         ex[f"nvfp4_single_launch_{name}"] = {"us": t * 1e6, "gbps": algorithmic_bytes(N, K) / t / 1e9}
+    # (f) the same 54-matrix pass on the tensor-core GEMV (activation pieces + one grouped launch)
+    tcs = []
+    for sidx in range(NSETS):
+        probs = [dict(x=x[K], weight_packed=p, weight_scales=sc, global_scale=gs,
+                      out=torch.empty((1, N), dtype=torch.bfloat16, device=device)) for (p, sc, gs, N, K) in sets[sidx]]
+        tcs.append(ops.TcGemv(probs, pieces=3))
+    t = time_replays(lambda i: tcs[i % NSETS].launch(), 400)
+    ex["tc_grouped_54_quantize_plus_gemv"] = {"us_per_step": t * 1e6, "gbps": STEP_BYTES / t / 1e9}
+    t = time_replays(lambda i: tcs[i % NSETS].gemv(), 400)
+    ex["tc_grouped_54_gemv_only"] = {"us_per_step": t * 1e6, "gbps": STEP_BYTES / t / 1e9}
+    for (Nsel, Ksel, name) in ((INTER, HIDDEN, "gateup_1024x4096"), (HIDDEN, INTER, "down_4096x1024")):
+        ms_ = [m for m in flat if m[3] == Nsel][:24]
+        singles = [ops.TcGemv([dict(x=x[Ksel], weight_packed=p, weight_scales=sc, global_scale=gs,
+                                    out=torch.empty((1, N), dtype=torch.bfloat16, device=device))], pieces=3)
+                   for (p, sc, gs, N, K) in ms_]
+        t = time_launches(lambda i: singles[i % len(singles)].gemv(), 48)
+        ex[f"tc_single_launch_M1_{name}"] = {"us": t * 1e6, "gbps": algorithmic_bytes(Nsel, Ksel) / t / 1e9}
+    del tcs
     # (e) prefix NVFP4 x NVFP4 GEMMs on tcgen05 (e2m1 activations and weights, UE4M3 block-16 scales)
     for (M, N, K, name) in ((712, 16384, 2048, "gemma2b_gateup_M712"), (712, 2048, 16384, "gemma2b_down_M712"),
                             (512, 4304, 1152, "siglip_fc1_M512"), (512, 1152, 4304, "siglip_fc2_M512")):
@@ -480,6 +534,9 @@ def main():
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--path", default="cuda", choices=["cuda", "tc"],
+                    help="GEMV kernel: CUDA-core decode (cuda) or tensor-core (tc)")
+    ap.add_argument("--no-graph", action="store_true", help="launch the step's kernels directly instead of one CUDA graph")
     ap.add_argument("--no-extras", action="store_true", help="skip the per-configuration side measurements")
     ap.add_argument("--no-clock-warmup", action="store_true",
                     help="do exactly W warm-up steps (profiling runs); by default warm-up lasts >= 0.4 s")

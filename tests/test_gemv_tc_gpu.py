@@ -60,7 +60,6 @@ def test_tc_gemv_matches_oracle(cuda_device, M, N, K):
     assert err.max() <= 1e-2, err.max()
     assert cosine(y1, ref) >= 0.999
     assert (buf[:16] == -5.0).all() and (buf[16 + M:] == -5.0).all()
-    assert int(tc.workspace[:4096].view(torch.int32).abs().sum()) == 0 or N * K < 1 << 20   # counters reset
 
 
 def test_tc_grouped_matches_cuda_core_gemv(cuda_device):

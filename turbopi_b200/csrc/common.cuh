@@ -164,6 +164,61 @@ __device__ __forceinline__ uint8_t encode_e4m3(float v) {
     return static_cast<uint8_t>(r & 0xFF);
 }
 
+// two floats -> one byte of e2m1 codes (lo in the low nibble), round-to-nearest-even, saturating at 6
+__device__ __forceinline__ uint32_t encode_e2m1x2(float lo, float hi) {
+    uint16_t r;
+    asm("{\n"
+        " .reg .b8 t;\n"
+        " cvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\n"
+        " cvt.u16.u8 %0, t;\n"
+        "}\n"
+        : "=h"(r)
+        : "f"(hi), "f"(lo));
+    return r;
+}
+
+// one byte of e2m1 codes -> (value of low nibble, value of high nibble)
+__device__ __forceinline__ float2 decode_e2m1x2(uint32_t byte) {
+    uint32_t r;
+    const uint16_t b = static_cast<uint16_t>(byte);
+    asm("{\n"
+        " .reg .b8 lo, hi;\n"
+        " mov.b16 {lo, hi}, %1;\n"
+        " cvt.rn.f16x2.e2m1x2 %0, lo;\n"
+        "}\n"
+        : "=r"(r)
+        : "h"(b));
+    return __half22float2(*reinterpret_cast<__half2*>(&r));
+}
+
+// One residual piece of a 16-element block: chooses the UE4M3 scale (rounded up so nothing clips),
+// returns the 16 codes in (lo, hi) and leaves in r what the piece could not represent.
+__device__ __forceinline__ uint8_t quantize_block16_piece(float (&r)[16], uint32_t& lo, uint32_t& hi) {
+    float bmax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) bmax = fmaxf(bmax, fabsf(r[i]));
+    const float want = bmax * (1.0f / 6.0f);
+    uint8_t code = encode_e4m3(want);
+    float s = decode_e4m3(code);
+    if (s < want && code < 0x7E) {   // next representable scale up (positive codes are monotonic)
+        code += 1;
+        s = decode_e4m3(code);
+    }
+    const float inv = s > 0.0f ? 1.0f / s : 0.0f;
+    lo = 0;
+    hi = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const uint32_t byte = encode_e2m1x2(r[2 * i] * inv, r[2 * i + 1] * inv);
+        const float2 q = decode_e2m1x2(byte);
+        r[2 * i] = fmaf(-q.x, s, r[2 * i]);
+        r[2 * i + 1] = fmaf(-q.y, s, r[2 * i + 1]);
+        if (i < 4) lo |= byte << (8 * i);
+        else hi |= byte << (8 * (i - 4));
+    }
+    return code;
+}
+
 // ---------------------------------------------------------------------------
 // Scalars of a run-time dtype
 // ---------------------------------------------------------------------------
@@ -180,6 +235,33 @@ __device__ __forceinline__ void store_from_float(void* p, int dtype, size_t i, f
         static_cast<__half*>(p)[i] = __float2half_rn(v);
     } else {
         static_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
+    }
+}
+
+// 16 consecutive elements (16-element aligned) of a run-time dtype as floats, with 128-bit loads
+__device__ __forceinline__ void load16_as_float(const void* p, int dtype, size_t e0, float (&v)[16]) {
+    if (dtype == TPB200_F32) {
+        const float4* q = reinterpret_cast<const float4*>(static_cast<const float*>(p) + e0);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const float4 f = __ldg(q + i);
+            v[4 * i] = f.x; v[4 * i + 1] = f.y; v[4 * i + 2] = f.z; v[4 * i + 3] = f.w;
+        }
+    } else {
+        const uint4* q = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p) + e0);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const uint4 u = __ldg(q + i);
+            const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = dtype == TPB200_F16
+                                     ? __half22float2(*reinterpret_cast<const __half2*>(&w[j]))
+                                     : __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
+                v[8 * i + 2 * j] = f.x;
+                v[8 * i + 2 * j + 1] = f.y;
+            }
+        }
     }
 }
 

@@ -320,16 +320,6 @@ __device__ __forceinline__ uint32_t e2m1_index(float a) {
     return (a > 0.25f) + (a > 0.75f) + (a > 1.25f) + (a > 1.75f) + (a > 2.5f) + (a > 3.5f) + (a > 5.0f);
 }
 
-__device__ __forceinline__ float e4m3_round_up(float v, uint8_t& code) {
-    code = encode_e4m3(v);
-    float d = decode_e4m3(code);
-    if (d < v && code < 0x7E) {
-        code += 1;
-        d = decode_e4m3(code);
-    }
-    return d;
-}
-
 __global__ void __launch_bounds__(256) quantize_pieces_tiled_kernel(const void* __restrict__ x, int x_dtype, int ldx,
                                                                     uint8_t* __restrict__ x_tiled,
                                                                     uint8_t* __restrict__ x_sf,
@@ -344,8 +334,11 @@ __global__ void __launch_bounds__(256) quantize_pieces_tiled_kernel(const void* 
     __shared__ float red[8];
     float amax = 0.0f;
     if (t < M) {
-        for (int i = threadIdx.x; i < K; i += blockDim.x) {
-            amax = fmaxf(amax, fabsf(load_as_float(x, x_dtype, static_cast<size_t>(t) * ldx + i)));
+        for (int kb = threadIdx.x; kb < nblk; kb += blockDim.x) {
+            float r[16];
+            load16_as_float(x, x_dtype, static_cast<size_t>(t) * ldx + kb * 16, r);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(r[i]));
         }
     }
 #pragma unroll
@@ -368,10 +361,9 @@ __global__ void __launch_bounds__(256) quantize_pieces_tiled_kernel(const void* 
         float r[16];
         const bool valid = (t < M) && (kb < nblk);
         if (valid) {
+            load16_as_float(x, x_dtype, static_cast<size_t>(t) * ldx + kb * 16, r);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                r[i] = load_as_float(x, x_dtype, static_cast<size_t>(t) * ldx + kb * 16 + i) * pre;
-            }
+            for (int i = 0; i < 16; ++i) r[i] *= pre;
         }
         const int ks = kb >> 4;
         const int c = (kb & 15) >> 1;            // 16-byte chunk of the 128-byte row
@@ -386,25 +378,8 @@ __global__ void __launch_bounds__(256) quantize_pieces_tiled_kernel(const void* 
                 *reinterpret_cast<uint2*>(dst) = make_uint2(0u, 0u);
                 continue;
             }
-            float bmax = 0.0f;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) bmax = fmaxf(bmax, fabsf(r[i]));
-            uint8_t code;
-            const float s = e4m3_round_up(bmax * (1.0f / 6.0f), code);
-            x_sf[sf_off] = code;
-            const float inv = s > 0.0f ? 1.0f / s : 0.0f;
-            uint32_t lo = 0, hi = 0;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const float a = fminf(fabsf(r[i]) * inv, 6.0f);
-                const uint32_t idx = e2m1_index(a);
-                const float mag = idx < 4 ? 0.5f * idx : (idx == 4 ? 2.0f : (idx == 5 ? 3.0f : (idx == 6 ? 4.0f : 6.0f)));
-                const bool neg = r[i] < 0.0f;
-                const uint32_t cc = (neg && idx != 0) ? (idx | 8u) : idx;
-                r[i] -= (neg ? -mag : mag) * s;
-                if (i < 8) lo |= cc << (4 * i);
-                else hi |= cc << (4 * (i - 8));
-            }
+            uint32_t lo, hi;
+            x_sf[sf_off] = quantize_block16_piece(r, lo, hi);
             *reinterpret_cast<uint2*>(dst) = make_uint2(lo, hi);
         }
     }
@@ -437,8 +412,10 @@ int make_plan(const tpb200_gemv_tc_problem* probs, int count, int sms, TcPlan& p
         const long long row_tiles = (probs[i].N + 127) / 128;
         total_stages += row_tiles * ((probs[i].K + 255) / 256);
     }
-    // aim for ~4 units per SM, units of 1..8 stages
-    const int target = static_cast<int>(std::min<long long>(8, std::max<long long>(1, total_stages / (4LL * sms))));
+    // aim for ~4 units per SM, units of 1..8 stages, and never longer than the shortest problem's K so
+    // that the units of a mixed launch carry (nearly) the same number of stages: CTAs own equal COUNTS
+    int target = static_cast<int>(std::min<long long>(8, std::max<long long>(1, total_stages / (4LL * sms))));
+    for (int i = 0; i < count; ++i) target = std::min(target, (probs[i].K + 255) / 256);
     plan.scratch_floats = 0;
     plan.counters = 0;
     plan.total_units = 0;
@@ -488,7 +465,8 @@ extern "C" int tpb200_nvfp4_quantize_act_tc(const void* x, int x_dtype, int ldx,
     TPB_REQUIRE(pieces >= 1 && pieces <= 4, TPB200_ERR_SHAPE);
     TPB_REQUIRE(tpb_valid_dtype(x_dtype), TPB200_ERR_ENUM);
     TPB_REQUIRE((flags & ~TPB200_FLAG_PDL) == 0, TPB200_ERR_ENUM);
-    TPB_REQUIRE(tpb_aligned16(x_tiled) && tpb_aligned16(x_sf), TPB200_ERR_ALIGN);
+    TPB_REQUIRE(tpb_aligned16(x) && tpb_aligned16(x_tiled) && tpb_aligned16(x_sf), TPB200_ERR_ALIGN);
+    TPB_REQUIRE((static_cast<long long>(ldx) * tpb_dtype_size(x_dtype)) % 16 == 0, TPB200_ERR_ALIGN);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(16, 1, 1);
     cfg.blockDim = dim3(256, 1, 1);

@@ -408,16 +408,6 @@ __global__ void nvfp4_quantize_act_kernel(const void* __restrict__ x, int x_dtyp
 //   its own UE4M3 scale (rounded UP so that nothing clips):  x' ~= sum_p q_p * s_p.
 // One CTA per row; piece p of row m goes to packed row p * piece_rows + m.
 // ------------------------------------------------------------------------------------------
-__device__ __forceinline__ float e4m3_round_up(float v, uint8_t& code) {
-    code = encode_e4m3(v);
-    float d = decode_e4m3(code);
-    if (d < v && code < 0x7E) {
-        code += 1;               // next representable value (codes are monotonic for positive values)
-        d = decode_e4m3(code);
-    }
-    return d;
-}
-
 __global__ void __launch_bounds__(256) nvfp4_quantize_pieces_kernel(const void* __restrict__ x, int x_dtype, int ldx,
                                                                     uint8_t* __restrict__ packed, int pitch,
                                                                     uint8_t* __restrict__ sf, float* __restrict__ row_scale,
@@ -427,8 +417,11 @@ __global__ void __launch_bounds__(256) nvfp4_quantize_pieces_kernel(const void* 
     const int nblk = K >> 4;
     __shared__ float red[8];
     float amax = 0.0f;
-    for (int i = threadIdx.x; i < K; i += blockDim.x) {
-        amax = fmaxf(amax, fabsf(load_as_float(x, x_dtype, static_cast<size_t>(row) * ldx + i)));
+    for (int kb = threadIdx.x; kb < nblk; kb += blockDim.x) {
+        float r[16];
+        load16_as_float(x, x_dtype, static_cast<size_t>(row) * ldx + kb * 16, r);
+#pragma unroll
+        for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(r[i]));
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
@@ -450,10 +443,9 @@ __global__ void __launch_bounds__(256) nvfp4_quantize_pieces_kernel(const void* 
         float r[16];
         const bool valid = kb < nblk;
         if (valid) {
+            load16_as_float(x, x_dtype, static_cast<size_t>(row) * ldx + kb * 16, r);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                r[i] = load_as_float(x, x_dtype, static_cast<size_t>(row) * ldx + kb * 16 + i) * pre;
-            }
+            for (int i = 0; i < 16; ++i) r[i] *= pre;
         }
         for (int p = 0; p < pieces; ++p) {
             const int prow = p * piece_rows + row;
@@ -463,25 +455,8 @@ __global__ void __launch_bounds__(256) nvfp4_quantize_pieces_kernel(const void* 
                 sf[sf_off] = 0;
                 continue;
             }
-            float bmax = 0.0f;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) bmax = fmaxf(bmax, fabsf(r[i]));
-            uint8_t code;
-            const float s = e4m3_round_up(bmax * (1.0f / 6.0f), code);
-            sf[sf_off] = code;
-            const float inv = s > 0.0f ? 1.0f / s : 0.0f;
-            uint32_t lo = 0, hi = 0;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const float a = fminf(fabsf(r[i]) * inv, 6.0f);
-                const uint32_t idx = e2m1_index(a);
-                const float mag = idx < 4 ? 0.5f * idx : (idx == 4 ? 2.0f : (idx == 5 ? 3.0f : (idx == 6 ? 4.0f : 6.0f)));
-                const bool neg = r[i] < 0.0f;
-                const uint32_t c = (neg && idx != 0) ? (idx | 8u) : idx;
-                r[i] -= (neg ? -mag : mag) * s;          // what this piece leaves for the next one
-                if (i < 8) lo |= c << (4 * i);
-                else hi |= c << (4 * (i - 8));
-            }
+            uint32_t lo, hi;
+            sf[sf_off] = quantize_block16_piece(r, lo, hi);
             *reinterpret_cast<uint2*>(packed + static_cast<size_t>(prow) * pitch + kb * 8) = make_uint2(lo, hi);
         }
     }
@@ -560,7 +535,8 @@ extern "C" int tpb200_nvfp4_quantize_act_pieces(const void* x, int x_dtype, int 
     TPB_REQUIRE(pieces == 1 || piece_rows % 16 == 0, TPB200_ERR_SHAPE);
     TPB_REQUIRE(tpb_valid_dtype(x_dtype), TPB200_ERR_ENUM);
     TPB_REQUIRE(packed_pitch >= K / 2 && packed_pitch % 16 == 0, TPB200_ERR_ALIGN);
-    TPB_REQUIRE(tpb_aligned16(packed) && tpb_aligned16(sf_swizzled), TPB200_ERR_ALIGN);
+    TPB_REQUIRE(tpb_aligned16(x) && tpb_aligned16(packed) && tpb_aligned16(sf_swizzled), TPB200_ERR_ALIGN);
+    TPB_REQUIRE((static_cast<long long>(ldx) * tpb_dtype_size(x_dtype)) % 16 == 0, TPB200_ERR_ALIGN);
     const int kb_pad = (K + 255) / 256 * 16;
     tpb::nvfp4_quantize_pieces_kernel<<<M, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
         x, x_dtype, ldx, static_cast<uint8_t*>(packed), packed_pitch, static_cast<uint8_t*>(sf_swizzled), row_scale, M,
