@@ -191,6 +191,28 @@ int tpb200_nvfp4_gemv_tc(const tpb200_gemv_tc_problem* problems, int count, int 
                          tpb200_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Row-wise glue between two linears, fused with the activation quantiser of the tensor-core GEMM:
+ *   h = res_in + x * gate (optional)  ->  RMSNorm (1 + w0) | adaptive RMSNorm (1 + w0) + w1 | LayerNorm w0, w1
+ *   or  GELU_tanh(x[:, :K]) * x[:, K:2K]
+ * with the roundings of the PyTorch modules (GemmaRMSNorm, _gated_residual, GemmaMLP:
+ * openpi/src/openpi/models_pytorch/transformers_replace/models/gemma/modeling_gemma.py:49-129,212-230),
+ * written as residual e2m1 pieces + swizzled UE4M3 scales + row multipliers (the A operand of
+ * tpb200_nvfp4_gemm_ex), optionally also as bf16 (y_out) and as the updated residual stream (h_out).
+ * All tensors bf16, K % 16 == 0, K <= 16384.
+ * ------------------------------------------------------------------------------------------- */
+enum { TPB200_ROW_NONE = 0, TPB200_ROW_RMSNORM = 1, TPB200_ROW_ADARMS = 2, TPB200_ROW_LAYERNORM = 3,
+       TPB200_ROW_GELU_MUL = 4 };
+typedef struct {
+    int mode; int M; int K;
+    const void* x; int ldx;
+    const void* res_in; const void* gate; void* h_out;
+    const void* w0; const void* w1; float eps;
+    void* y_out;
+    void* packed; int pitch; void* sf; float* row_scale; int pieces; int piece_rows;
+} tpb200_rowop_args;
+int tpb200_row_transform_quantize(const tpb200_rowop_args* args, tpb200_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Entry points with the reference's names and signatures (TensorRT-plugin / test ABI).
  * ------------------------------------------------------------------------------------------- */
 

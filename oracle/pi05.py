@@ -1,0 +1,142 @@
+"""CPU oracle of the Pi0.5-shaped inference: torch fp32 arithmetic with the bf16 roundings of the
+reference's bf16 model.  Test infrastructure; see oracle/__init__.py.
+
+Follows `PI0Pytorch.sample_actions` (openpi/src/openpi/models_pytorch/pi0_pytorch.py:876-937):
+embed_prefix (:215-264), compute_prefix_kv_cache (:406-522), denoise_step_with_cache (:524-654),
+embed_suffix (:266-345); GemmaRMSNorm / adaptive RMSNorm / _gated_residual / GemmaMLP
+(transformers_replace/models/gemma/modeling_gemma.py:49-129,212-230); RoPE (:132-197);
+SigLIP encoder layer (transformers_replace/models/siglip/modeling_siglip.py:212-231,420-432).
+Weights are plain float32 matrices (already dequantised) in a dict; see tests/test_pi05_gpu.py.
+"""
+import math
+
+import torch
+import torch.nn.functional as F
+
+
+def r(x):
+    """round to bf16, keep float32 storage"""
+    return x.to(torch.bfloat16).float()
+
+
+def linear(x, w, b=None, act=None, out_fp32=False):
+    y = r(x) @ w.t()
+    if b is not None:
+        y = y + b
+    if act == "gelu":
+        y = F.gelu(y, approximate="tanh")
+    elif act == "silu":
+        y = F.silu(y)
+    return y if out_fp32 else r(y)
+
+
+def rms(x, eps):
+    return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps)
+
+
+def rope(x, cos, sin):
+    """x [L, H, D]; cos, sin [L, D/2] (bf16 values); bf16 product-by-product as torch does."""
+    h = x.shape[-1] // 2
+    c = torch.cat([cos, cos], -1)[:, None, :]
+    s = torch.cat([sin, sin], -1)[:, None, :]
+    rot = torch.cat([-x[..., h:], x[..., :h]], -1)
+    return r(r(x * c) + r(rot * s))
+
+
+def attention(q, k, v, heads):
+    """q [L, H*D], k/v [S, D] (one KV head)."""
+    L, D = q.shape[0], k.shape[1]
+    qh = q.view(L, heads, D).transpose(0, 1)
+    o = F.scaled_dot_product_attention(qh[None], k[None, None].expand(1, heads, -1, -1), v[None, None].expand(1, heads, -1, -1))
+    return r(o[0].transpose(0, 1).reshape(L, heads * D))
+
+
+def vision_tower(w, images_u8, cfg):
+    n = cfg["image_size"] // cfg["patch"]
+    NI, vw = images_u8.shape[0], cfg["vision_width"]
+    img = images_u8.float() / 127.5 - 1.0
+    pt = img.view(NI, n, cfg["patch"], n, cfg["patch"], 3).permute(0, 1, 3, 5, 2, 4).reshape(NI * n * n, -1)
+    pk = pt.shape[1]
+    h = linear(pt, w["patch_embed"][:, :pk], w["patch_embed_b"])
+    h = r(h.view(NI, n * n, vw) + w["pos_emb"]).view(-1, vw)
+    heads = cfg["vision_heads"]
+    hd = vw // heads
+    for L in w["vision"]:
+        x = r(F.layer_norm(h, (vw,), L["ln1_w"], L["ln1_b"], cfg["eps"]))
+        qkv = linear(x, L["qkv"], L["qkv_b"]).view(NI, n * n, 3, heads, hd).permute(2, 0, 3, 1, 4)
+        o = F.scaled_dot_product_attention(qkv[0], qkv[1], qkv[2])
+        o = r(o.transpose(1, 2).reshape(-1, vw))
+        h = r(h + linear(o, L["out"], L["out_b"]))
+        x = r(F.layer_norm(h, (vw,), L["ln2_w"], L["ln2_b"], cfg["eps"]))
+        h = r(h + linear(linear(x, L["fc1"], L["fc1_b"], "gelu"), L["fc2"], L["fc2_b"]))
+    x = r(F.layer_norm(h, (vw,), w["post_ln_w"], w["post_ln_b"], cfg["eps"]))
+    return linear(x, w["projector"], w["projector_b"])
+
+
+def prefix_pass(w, img_tokens, tokens, cfg, cos, sin):
+    """Returns the per-layer (K post-RoPE, V) rows, each [S, 256]."""
+    width, qd, hd = cfg["width"], cfg["q_dim"], cfg["head_dim"]
+    h = torch.cat([img_tokens, r(w["embed_tokens"][tokens] * math.sqrt(width))], 0)
+    S = h.shape[0]
+    kv = []
+    for L in w["prefix"]:
+        x = r(rms(h, cfg["eps"]) * (1.0 + L["in_norm"]))
+        qkv = linear(x, L["qkv"])
+        q = rope(qkv[:, :qd].view(S, -1, hd), cos[:S], sin[:S]).reshape(S, qd)
+        k = rope(qkv[:, qd:qd + hd].view(S, 1, hd), cos[:S], sin[:S]).reshape(S, hd)
+        v = qkv[:, qd + hd:]
+        kv.append((k, v))
+        h = r(h + linear(attention(q, k, v, cfg["heads"]), L["o"]))
+        x = r(rms(h, cfg["eps"]) * (1.0 + L["post_norm"]))
+        gu = linear(x, L["gate_up"])
+        I = gu.shape[1] // 2
+        act = r(r(F.gelu(gu[:, :I], approximate="tanh")) * gu[:, I:])
+        h = r(h + linear(act, L["down"]))
+    return kv
+
+
+def sinusoidal(t, dim, min_period=4e-3, max_period=4.0):
+    frac = torch.linspace(0.0, 1.0, dim // 2, dtype=torch.float64)
+    period = min_period * (max_period / min_period) ** frac
+    ang = (1.0 / period * 2 * math.pi)[None, :] * t.to(torch.float64)[:, None]
+    return torch.cat([torch.sin(ang), torch.cos(ang)], 1)
+
+
+def denoise(w, kv, noise, num_steps, cfg, cos, sin):
+    ew, qd, hd, A = cfg["expert_width"], cfg["q_dim"], cfg["head_dim"], noise.shape[0]
+    S = kv[0][0].shape[0]
+    dt = -1.0 / num_steps
+    x_t = noise.clone().float()
+    for i in range(num_steps):
+        t = torch.tensor([1.0 + i * dt], dtype=torch.float32)
+        emb = r(sinusoidal(t, ew).float())
+        cond = linear(linear(emb, w["time_mlp_in"], w["time_mlp_in_b"], "silu"), w["time_mlp_out"], w["time_mlp_out_b"], "silu")
+        mod = linear(cond, w["ada_dense"], w["ada_dense_b"]).view(-1, 3, ew)       # [n_norms, (scale, shift, gate), ew]
+        h = linear(r(x_t), w["action_in"], w["action_in_b"])
+        for l, L in enumerate(w["expert"]):
+            m_in, m_post = mod[2 * l], mod[2 * l + 1]
+            x = r(rms(h, cfg["eps"]) * (1.0 + m_in[0]) + m_in[1])
+            qkv = linear(x, L["qkv"])
+            pos_c, pos_s = cos[S:S + A], sin[S:S + A]
+            q = rope(qkv[:, :qd].view(A, -1, hd), pos_c, pos_s).reshape(A, qd)
+            k = rope(qkv[:, qd:qd + hd].view(A, 1, hd), pos_c, pos_s).reshape(A, hd)
+            v = qkv[:, qd + hd:]
+            kf, vf = torch.cat([kv[l][0], k], 0), torch.cat([kv[l][1], v], 0)
+            o = linear(attention(q, kf, vf, cfg["heads"]), L["o"])
+            h = r(h + r(o * m_in[2]))
+            x = r(rms(h, cfg["eps"]) * (1.0 + m_post[0]) + m_post[1])
+            gu = linear(x, L["gate_up"])
+            I = gu.shape[1] // 2
+            act = r(r(F.gelu(gu[:, :I], approximate="tanh")) * gu[:, I:])
+            h = r(h + r(linear(act, L["down"]) * m_post[2]))
+        m_f = mod[2 * len(w["expert"])]
+        x = r(rms(h, cfg["eps"]) * (1.0 + m_f[0]) + m_f[1])
+        v_t = linear(x, w["action_out"], w["action_out_b"], out_fp32=True)
+        x_t = x_t + dt * v_t
+    return x_t
+
+
+def sample_actions(w, images_u8, tokens, noise, num_steps, cfg, cos, sin):
+    img_tokens = vision_tower(w, images_u8, cfg)
+    kv = prefix_pass(w, img_tokens, tokens, cfg, cos, sin)
+    return denoise(w, kv, noise, num_steps, cfg, cos, sin), kv

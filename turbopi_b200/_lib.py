@@ -46,6 +46,16 @@ class GemvTcProblem(ctypes.Structure):
                 ("N", c_int), ("K", c_int), ("ldo", c_int), ("global_scale", c_float)]
 
 
+class RowOpArgs(ctypes.Structure):
+    _fields_ = [("mode", c_int), ("M", c_int), ("K", c_int), ("x", c_void_p), ("ldx", c_int),
+                ("res_in", c_void_p), ("gate", c_void_p), ("h_out", c_void_p),
+                ("w0", c_void_p), ("w1", c_void_p), ("eps", c_float), ("y_out", c_void_p),
+                ("packed", c_void_p), ("pitch", c_int), ("sf", c_void_p), ("row_scale", c_void_p),
+                ("pieces", c_int), ("piece_rows", c_int)]
+
+
+ROW_NONE, ROW_RMSNORM, ROW_ADARMS, ROW_LAYERNORM, ROW_GELU_MUL = 0, 1, 2, 3, 4
+
 # name -> (restype, argtypes); every symbol include/turbopi_b200.h declares
 SIGNATURES = {
     "tpb200_version": (c_int, []),
@@ -70,6 +80,7 @@ SIGNATURES = {
                                              c_int, c_void_p]),
     "tpb200_nvfp4_gemv_tc": (c_int, [ctypes.POINTER(GemvTcProblem), c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                      c_size_t, c_int, c_void_p]),
+    "tpb200_row_transform_quantize": (c_int, [ctypes.POINTER(RowOpArgs), c_void_p]),
     "nvfp4_gemv_forward": (None, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                   c_int, c_int, c_void_p]),
     "nvfp4_gemv_workspace_size": (c_size_t, [c_int, c_int, c_int]),
