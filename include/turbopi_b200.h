@@ -112,7 +112,7 @@ typedef struct {
     int N;
     int K;
     float global_scale;
-    int reserved;
+    int out_stride;            /* elements between output rows; 0 = N */
 } tpb200_gemv_problem;
 
 int tpb200_nvfp4_gemv_grouped(const tpb200_gemv_problem* problems, int count, int x_dtype, int scale_dtype,
@@ -230,8 +230,22 @@ void quantizeWeightToINT4(const void* input_bf16, int8_t* output_packed, void* s
 void dequantizeINT4ToBF16(const int8_t* input_packed, const void* scales_bf16, const void* zeros_bf16,
                           void* output_bf16, int N, int K, int group_size, tpb200_stream_t stream);
 
-/* openpi/w4a8_plugin/src/w4a8_gemm_plugin.h:58-73: bf16 -> E4M3 values + E4M3 scale per 16 along K;
+/* openpi/w4a16_plugin/src/w4a16_gemm_plugin.h:41-59: out bf16 [M,N] = alpha * act bf16 [M,K] @ dequant(W)^T + beta * out,
+ * W signed int4 [N, K/2], bf16 scales and optional zero points [N, K/128] (q * scale + zero).  Any M (the
+ * decode kernel runs 16 rows per launch).  The workspace is only used with zero points or beta != 0. */
+void w4a16GemmForward(const void* activation, const void* weight_packed, const void* weight_scale,
+                      const void* weight_zero, void* output, int M, int N, int K, float alpha, float beta,
+                      void* workspace, size_t workspaceSize, tpb200_stream_t stream);
+size_t getW4A16GemmWorkspaceSize(int M, int N, int K);
+
+/* openpi/w4a8_plugin/src/w4a8_gemm_plugin.h:39-73: out bf16 [M,N] = alpha * (fp8 act * act scale) @ (e2m1 * w scale),
+ * weights and their scales stored transposed ([K/2, N], [K/16, N]); N % 8 == 0; the workspace (size from
+ * getW4A8GemmWorkspaceSize) holds the re-laid-out operands.  bf16 -> E4M3 values + E4M3 scale per 16 along K;
  * bf16 [N, K] weight -> e2m1 packed TRANSPOSED [K/2, N] + E4M3 scales [K/16, N]. */
+void w4a8GemmForward(const void* activation_fp8, const void* activation_scale, const void* weight_packed,
+                     const void* weight_scale, void* output_bf16, int M, int N, int K, float alpha, void* workspace,
+                     size_t workspaceSize, tpb200_stream_t stream);
+size_t getW4A8GemmWorkspaceSize(int M, int N, int K);
 void quantizeActivationToFP8(const void* input_bf16, void* output_fp8, void* scales_fp8, int M, int K,
                              tpb200_stream_t stream);
 void quantizeWeightToNVFP4(const void* input_bf16, uint8_t* output_packed, void* scales_fp8, int N, int K,

@@ -305,3 +305,27 @@ def test_modules_forward_through_kernels(cuda_device):
 def test_no_kernel_gave_up_on_a_wait(cuda_device):
     from turbopi_b200 import _lib
     assert _lib.load().tpb200_device_error(0) == 0
+
+
+def test_kv_fuse_module_matches_reference_golden(cuda_device, golden):
+    """FusedQKVProjection on the reference's own quantised weights: Q and the cache rows against the output
+    of its fallback path; every other cache row keeps the sentinel bit for bit."""
+    from turbopi_b200 import kv_fuse
+    g = golden("kv_fuse")
+    mod = kv_fuse.FusedQKVProjection(64, 2, 1, 32, max_seq_len=6)
+    for n in ("q", "k", "v"):
+        setattr(mod, f"W{n}_packed", _dev(g[f"W{n}_packed"], cuda_device))
+        setattr(mod, f"scale_W{n}", _dev(g[f"scale_W{n}"], cuda_device))
+    # the packer is the reference's, bit for bit (sign from the input: code 8 appears)
+    pk, sc = kv_fuse.quantize_to_fp4(torch.from_numpy(g["Wk"]), 32)
+    assert np.array_equal(pk.numpy(), g["Wk_packed"]) and np.array_equal(sc.numpy(), g["scale_Wk"])
+    Kc = torch.full((3, 6, 1, 32), -7.0, device=cuda_device)
+    Vc = torch.full((3, 6, 1, 32), -7.0, device=cuda_device)
+    pos = int(g["cache_pos"])
+    Q, Kc2, Vc2 = mod(_dev(g["x"], cuda_device), Kc, Vc, pos)
+    assert Kc2 is Kc and Vc2 is Vc                                  # updated in place
+    _check(Q.cpu().numpy(), g["Q"])
+    _check(Kc[:, pos].cpu().numpy(), g["K_cache"][:, pos])
+    _check(Vc[:, pos].cpu().numpy(), g["V_cache"][:, pos])
+    other = [i for i in range(6) if i != pos]
+    assert (Kc[:, other] == -7.0).all() and (Vc[:, other] == -7.0).all()

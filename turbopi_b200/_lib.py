@@ -25,7 +25,7 @@ class TurboPiError(RuntimeError):
 
 class GemvProblem(ctypes.Structure):
     _fields_ = [("x", c_void_p), ("weight_packed", c_void_p), ("weight_scales", c_void_p), ("bias", c_void_p),
-                ("out", c_void_p), ("N", c_int), ("K", c_int), ("global_scale", c_float), ("reserved", c_int)]
+                ("out", c_void_p), ("N", c_int), ("K", c_int), ("global_scale", c_float), ("out_stride", c_int)]
 
 
 class GemmArgs(ctypes.Structure):
@@ -84,6 +84,12 @@ SIGNATURES = {
     "nvfp4_gemv_forward": (None, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                   c_int, c_int, c_void_p]),
     "nvfp4_gemv_workspace_size": (c_size_t, [c_int, c_int, c_int]),
+    "w4a16GemmForward": (None, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_float,
+                                c_void_p, c_size_t, c_void_p]),
+    "getW4A16GemmWorkspaceSize": (c_size_t, [c_int, c_int, c_int]),
+    "w4a8GemmForward": (None, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p,
+                               c_size_t, c_void_p]),
+    "getW4A8GemmWorkspaceSize": (c_size_t, [c_int, c_int, c_int]),
     "quantizeWeightToINT4": (None, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "dequantizeINT4ToBF16": (None, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "quantizeActivationToFP8": (None, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),

@@ -54,6 +54,7 @@ struct ProblemDev {
     void* out;
     int N;
     int K;
+    int ldo;             // output row stride in elements
     float global_scale;
     int tile_begin;      // index of this problem's first tile in the launch-wide list
     int rows_per_tile;   // multiple of (8 / kparts)
@@ -72,6 +73,7 @@ struct GemvParams {
     int out_dtype;
     int activation;
     int group;  // codes per scale
+    uint32_t u4_xor;  // 0x88888888 turns two's-complement int4 nibbles into the offset-8 codes the decoder expects
     ProblemDev prob[MAXP];
 };
 
@@ -234,7 +236,7 @@ template <int FMT, int SCALE_MODE, int M_TILE, int CPL>
 __device__ __forceinline__ void accumulate_row_group(float (&acc)[4], const __half2 (&xr)[M_TILE][CPL][16],
                                                      const uint8_t* wt, const uint8_t* sc, int row_bytes,
                                                      int scale_row_bytes, int rbase, int RW, int rows, int kp,
-                                                     int lane, int nchunks, int group) {
+                                                     int lane, int nchunks, int group, uint32_t u4_xor) {
     constexpr int RG = 4 / M_TILE;
     acc[0] = acc[1] = acc[2] = acc[3] = 0.0f;
 #pragma unroll
@@ -252,8 +254,8 @@ __device__ __forceinline__ void accumulate_row_group(float (&acc)[4], const __ha
                         decode_e2m1x8(w.x, h0); decode_e2m1x8(w.y, h1);
                         decode_e2m1x8(w.z, h2); decode_e2m1x8(w.w, h3);
                     } else {
-                        decode_u4x8_minus8(w.x, h0); decode_u4x8_minus8(w.y, h1);
-                        decode_u4x8_minus8(w.z, h2); decode_u4x8_minus8(w.w, h3);
+                        decode_u4x8_minus8(w.x ^ u4_xor, h0); decode_u4x8_minus8(w.y ^ u4_xor, h1);
+                        decode_u4x8_minus8(w.z ^ u4_xor, h2); decode_u4x8_minus8(w.w ^ u4_xor, h3);
                     }
                     if (scales_in_half<SCALE_MODE>()) {
                         __half2 s0, s1;
@@ -387,7 +389,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_rowmajor_kernel(const __grid
         for (int rbase = rw; rbase < rows; rbase += RW * RG) {
             float acc[4];
             accumulate_row_group<FMT, SCALE_MODE, M_TILE, CPL>(acc, xr, wt, sc, row_bytes, pr.scale_row_bytes, rbase, RW,
-                                                               rows, kp, lane, nchunks, group);
+                                                               rows, kp, lane, nchunks, group, P.u4_xor);
             const float total = warp_sum4(acc, lane);
             if ((lane & 7) == 0) {
                 const int idx = lane >> 3;
@@ -407,7 +409,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_rowmajor_kernel(const __grid
                 v *= scales_in_half<SCALE_MODE>() ? pr.global_scale * (1.0f / kXPrescale) : pr.global_scale;
                 if (pr.bias != nullptr) v += load_as_float(pr.bias, P.bias_dtype, row0 + r);
                 v = apply_activation(v, P.activation);
-                store_from_float(pr.out, P.out_dtype, static_cast<size_t>(m0 + m) * pr.N + row0 + r, v);
+                store_from_float(pr.out, P.out_dtype, static_cast<size_t>(m0 + m) * pr.ldo + row0 + r, v);
             }
         }
     }
@@ -517,7 +519,7 @@ __global__ void __launch_bounds__(kWsThreads, 2) gemv_rowmajor_ws_kernel(const _
         for (int rbase = warp; rbase < rows; rbase += kWarps * RG) {
             float acc[4];
             accumulate_row_group<FMT, SCALE_MODE, M_TILE, CPL>(acc, xr, wt, sc, row_bytes, pr.scale_row_bytes, rbase,
-                                                               kWarps, rows, 0, lane, nchunks, group);
+                                                               kWarps, rows, 0, lane, nchunks, group, P.u4_xor);
             float v = warp_sum4(acc, lane);
             if ((lane & 7) == 0) {
                 const int idx = lane >> 3;
@@ -527,7 +529,7 @@ __global__ void __launch_bounds__(kWsThreads, 2) gemv_rowmajor_ws_kernel(const _
                     v *= out_scale;
                     if (pr.bias != nullptr) v += load_as_float(pr.bias, P.bias_dtype, row0 + r);
                     v = apply_activation(v, P.activation);
-                    store_from_float(pr.out, P.out_dtype, static_cast<size_t>(m0 + m) * pr.N + row0 + r, v);
+                    store_from_float(pr.out, P.out_dtype, static_cast<size_t>(m0 + m) * pr.ldo + row0 + r, v);
                 }
             }
         }
@@ -548,6 +550,7 @@ struct HostProblem {
     void* out;
     int N, K;
     float global_scale;
+    int ldo = 0;   // 0: rows of `out` are N apart
 };
 
 struct Plan {
@@ -632,8 +635,9 @@ int dispatch_tiles(const GemvParams<MAXP>& P, const Plan& plan, bool ws, int gri
 }
 
 template <int MAXP>
-int run_gemv(int fmt, const HostProblem* probs, int count, int x_dtype, int scale_dtype, int group,
+int run_gemv(int fmt_in, const HostProblem* probs, int count, int x_dtype, int scale_dtype, int group,
              int bias_dtype, int out_dtype, int M, int activation, int flags, cudaStream_t stream) {
+    const int fmt = fmt_in == 2 ? kFmtU4 : fmt_in;   // 2 = signed (two's complement) int4
     TPB_REQUIRE(probs != nullptr, TPB200_ERR_NULL);
     TPB_REQUIRE(count >= 1 && count <= MAXP, TPB200_ERR_SHAPE);
     TPB_REQUIRE(M >= 1 && M <= 16, TPB200_ERR_SHAPE);
@@ -666,6 +670,7 @@ int run_gemv(int fmt, const HostProblem* probs, int count, int x_dtype, int scal
         const HostProblem& h = probs[i];
         TPB_REQUIRE(h.x && h.w && h.scales && h.out, TPB200_ERR_NULL);
         TPB_REQUIRE(h.N >= 1 && h.K >= 32 && h.K % 32 == 0 && h.K % group == 0, TPB200_ERR_SHAPE);
+        TPB_REQUIRE(h.ldo == 0 || h.ldo >= h.N, TPB200_ERR_SHAPE);
         TPB_REQUIRE(tpb_aligned16(h.x) && tpb_aligned16(h.w) && tpb_aligned16(h.scales) && tpb_aligned16(h.out),
                     TPB200_ERR_ALIGN);
         maxK = std::max(maxK, h.K);
@@ -687,6 +692,7 @@ int run_gemv(int fmt, const HostProblem* probs, int count, int x_dtype, int scal
     P.out_dtype = out_dtype;
     P.activation = activation;
     P.group = group;
+    P.u4_xor = fmt_in == 2 ? 0x88888888u : 0u;
     long long weight_bytes = 0;
     for (int i = 0; i < count; ++i) weight_bytes += static_cast<long long>(probs[i].N) * (probs[i].K / 2);
     const long long target_tile_bytes =
@@ -703,6 +709,7 @@ int run_gemv(int fmt, const HostProblem* probs, int count, int x_dtype, int scal
         d.out = h.out;
         d.N = h.N;
         d.K = h.K;
+        d.ldo = h.ldo > 0 ? h.ldo : h.N;
         d.global_scale = h.global_scale;
         // K-parts for THIS problem under the launch-wide CPL
         const int nchunks = h.K / 32;
@@ -751,7 +758,7 @@ int gemv_rowmajor_single(int fmt_is_u4, const void* x, int x_dtype, const void* 
                          int bias_dtype, void* out, int out_dtype, int M, int N, int K, int activation, int flags,
                          cudaStream_t stream) {
     HostProblem h{x, x_scales, w, scales, bias, out, N, K, global_scale};
-    return run_gemv<1>(fmt_is_u4 ? kFmtU4 : kFmtE2M1, &h, 1, x_dtype, scale_dtype, group, bias_dtype, out_dtype, M,
+    return run_gemv<1>(fmt_is_u4 == 2 ? 2 : (fmt_is_u4 ? kFmtU4 : kFmtE2M1), &h, 1, x_dtype, scale_dtype, group, bias_dtype, out_dtype, M,
                        activation, flags, stream);
 }
 
@@ -777,7 +784,7 @@ extern "C" int tpb200_nvfp4_gemv_grouped(const tpb200_gemv_problem* problems, in
     for (int i = 0; i < count; ++i) {
         h[i] = tpb::HostProblem{problems[i].x, nullptr, problems[i].weight_packed, problems[i].weight_scales,
                                 problems[i].bias, problems[i].out, problems[i].N, problems[i].K,
-                                problems[i].global_scale};
+                                problems[i].global_scale, problems[i].out_stride};
     }
     return tpb::run_gemv<TPB200_MAX_GROUP>(tpb::kFmtE2M1, h, count, x_dtype, scale_dtype, block_size, bias_dtype,
                                            out_dtype, M, activation, flags, reinterpret_cast<cudaStream_t>(stream));

@@ -160,7 +160,7 @@ class GroupedGemv:
             N, Kh = p["weight_packed"].shape
             arr[i] = _lib.GemvProblem(_ptr(p["x"]), _ptr(p["weight_packed"]), _ptr(p["weight_scales"]),
                                       _ptr(p.get("bias")), _ptr(p["out"]), N, Kh * 2,
-                                      float(p.get("global_scale", 1.0)), 0)
+                                      float(p.get("global_scale", 1.0)), p["out"].stride(0))
         self._arr = arr
 
     def launch(self):
