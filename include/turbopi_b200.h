@@ -190,6 +190,16 @@ int tpb200_nvfp4_gemv_tc(const tpb200_gemv_tc_problem* problems, int count, int 
                          int out_dtype, int activation, void* workspace, size_t workspace_bytes, int flags,
                          tpb200_stream_t stream);
 
+/* tpb200_nvfp4_gemv_tc for callers that cannot allocate device memory (no counterpart in the reference).
+ * The split-K scratch is a 16 MiB array built into the library (tpb200_nvfp4_gemv_tc_static_capacity());
+ * launches whose plan needs more are refused with TPB200_ERR_WORKSPACE.  The call allocates nothing.
+ * The first call on a device looks up the array's device address; make that first call outside of any
+ * stream capture.  All calls on a device share the one array: two calls that may run at the same time
+ * on the GPU (different streams, different threads) race on it and must be serialised by the caller. */
+size_t tpb200_nvfp4_gemv_tc_static_capacity(void);
+int tpb200_nvfp4_gemv_tc_static(const tpb200_gemv_tc_problem* problems, int count, int M, int pieces,
+                                int bias_dtype, int out_dtype, int activation, int flags, tpb200_stream_t stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Row-wise glue between two linears, fused with the activation quantiser of the tensor-core GEMM:
  *   h = res_in + x * gate (optional)  ->  RMSNorm (1 + w0) | adaptive RMSNorm (1 + w0) + w1 | LayerNorm w0, w1

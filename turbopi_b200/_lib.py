@@ -81,6 +81,9 @@ SIGNATURES = {
     "tpb200_nvfp4_gemv_tc": (c_int, [ctypes.POINTER(GemvTcProblem), c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                      c_size_t, c_int, c_void_p]),
     "tpb200_row_transform_quantize": (c_int, [ctypes.POINTER(RowOpArgs), c_void_p]),
+    "tpb200_nvfp4_gemv_tc_static_capacity": (c_size_t, []),
+    "tpb200_nvfp4_gemv_tc_static": (c_int, [ctypes.POINTER(GemvTcProblem), c_int, c_int, c_int, c_int, c_int, c_int,
+                                            c_int, c_void_p]),
     "nvfp4_gemv_forward": (None, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                   c_int, c_int, c_void_p]),
     "nvfp4_gemv_workspace_size": (c_size_t, [c_int, c_int, c_int]),

@@ -577,3 +577,68 @@ extern "C" int tpb200_nvfp4_gemv_tc(const tpb200_gemv_tc_problem* problems, int 
     if (cudaLaunchKernelEx(&cfg, tpb::nvfp4_gemv_tc_kernel, P) != cudaSuccess) return TPB200_ERR_CUDA;
     return TPB200_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// The same GEMV for callers that are not able to allocate device memory.
+//
+// tpb200_nvfp4_gemv_tc needs a workspace for its split-K partial sums and tile counters.  Some
+// callers have nowhere to get one from: a TensorRT plugin whose enqueue() was not granted a
+// workspace, a robot-control loop that must not touch the allocator once it is running, host code
+// that is handed raw pointers and no allocator of the framework that owns them.  For them the
+// scratch lives in the library image itself, in the array below.  Every GPU that loads the library
+// carries these 16 MiB until the process exits.
+//
+// Host code must not hand `g_static_scratch` to a kernel directly: in host code that name is only a
+// stand-in for the symbol, not a device address.  The address is looked up once per device with
+// cudaGetSymbolAddress while that device is current.
+// ---------------------------------------------------------------------------------------------
+namespace {
+
+constexpr size_t kStaticScratchBytes = 16u << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// device-side address of g_static_scratch per device ordinal, filled on first use
+std::atomic<void*> g_static_scratch_addr[64];
+
+int static_scratch_address(void** out) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return TPB200_ERR_CUDA;
+    void* p = g_static_scratch_addr[dev].load(std::memory_order_acquire);
+    if (p == nullptr) {
+        if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr) return TPB200_ERR_CUDA;
+        g_static_scratch_addr[dev].store(p, std::memory_order_release);
+    }
+    *out = p;
+    return TPB200_OK;
+}
+
+}  // namespace
+
+extern "C" size_t tpb200_nvfp4_gemv_tc_static_capacity(void) { return kStaticScratchBytes; }
+
+extern "C" int tpb200_nvfp4_gemv_tc_static(const tpb200_gemv_tc_problem* problems, int count, int M, int pieces,
+                                           int bias_dtype, int out_dtype, int activation, int flags,
+                                           tpb200_stream_t stream) {
+    TPB_REQUIRE(problems != nullptr, TPB200_ERR_NULL);
+    TPB_REQUIRE(count >= 1 && count <= TPB200_MAX_GROUP, TPB200_ERR_SHAPE);
+    int sms = 0;
+    if (device_sms(sms) != TPB200_OK) return TPB200_ERR_CUDA;
+    TcPlan plan;
+    const int st = make_plan(problems, count, sms, plan);
+    if (st != TPB200_OK) return st;
+    const size_t counter_bytes = (plan.counters * sizeof(int) + 255) / 256 * 256;
+    const size_t need = counter_bytes + plan.scratch_floats * sizeof(float);
+    // larger problems than the built-in scratch can hold are refused, never truncated
+    TPB_REQUIRE(need <= kStaticScratchBytes, TPB200_ERR_WORKSPACE);
+    void* scratch = nullptr;
+    const int sa = static_scratch_address(&scratch);
+    if (sa != TPB200_OK) return sa;
+    // The array keeps whatever the previous call left.  Only the tile counters have to start at
+    // zero; the partial sums are always written before they are read.
+    if (counter_bytes > 0 &&
+        cudaMemsetAsync(scratch, 0, counter_bytes, reinterpret_cast<cudaStream_t>(stream)) != cudaSuccess) {
+        return TPB200_ERR_CUDA;
+    }
+    return tpb200_nvfp4_gemv_tc(problems, count, M, pieces, bias_dtype, out_dtype, activation, scratch,
+                                kStaticScratchBytes, flags, stream);
+}

@@ -447,6 +447,15 @@ class TcGemv:
                                                   torch.cuda.current_stream(self.device).cuda_stream)
         _lib.check(st, "tpb200_nvfp4_gemv_tc")
 
+    def gemv_static(self):
+        """The GEMV through the entry point that uses the library's built-in scratch instead of
+        `self.workspace` (for hosts that cannot allocate device memory)."""
+        with torch.cuda.device(self.device):
+            st = _lib.load().tpb200_nvfp4_gemv_tc_static(self._arr, len(self._arr), self.M, self.pieces,
+                                                         self.bias_dtype, self.out_dtype, self.activation, self.flags,
+                                                         torch.cuda.current_stream(self.device).cuda_stream)
+        _lib.check(st, "tpb200_nvfp4_gemv_tc_static")
+
     def launch(self):
         self.quantize()
         self.gemv()
