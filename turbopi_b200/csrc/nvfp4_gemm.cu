@@ -1,20 +1,24 @@
 // NVFP4 x NVFP4 block-scaled GEMM on the 5th-generation tensor cores:
-//   out[M, N] = act(alpha * sum_k (a[m,k] * sfa[m,k/16]) * (b[n,k] * sfb[n,k/16]) + bias[n])
-// a, b: e2m1 codes, two per byte (even k in the low nibble), K-major; sfa, sfb: UE4M3 per 16
+//   out[M, N] = act(alpha * rowscale[m] * sum_p sum_k (a_p[m,k] * sfa_p[m,k/16]) * (b[n,k] * sfb[n,k/16]) + bias[n])
+// a_p, b: e2m1 codes, two per byte (even k in the low nibble), K-major; sfa, sfb: UE4M3 per 16
 // along K, stored in 512-byte atoms of 128 rows x 4 K-blocks (byte (r%32)*16 + (r/32)*4 + kb),
-// atoms ordered [row tile][K atom].
+// atoms ordered [row tile][K atom].  The A operand may consist of up to four residual pieces
+// (weight-only semantics for bf16 activations); all pieces of a K stage are multiplied against
+// ONE resident B tile.
 //
 // One persistent CTA per SM, warp-specialised:
-//   warp 0     TMA producer: per 256-wide K stage one 128B-swizzled box of A (128 rows) and of
-//              B (128 rows) plus the two 2 KB scale slabs (plain bulk copies), 5-stage ring;
+//   warp 0     TMA producer: per 256-wide K stage one 128B-swizzled box of B (128 rows), one per
+//              A piece, and their 2 KB scale slabs (plain bulk copies), ring of 2..5 stages;
 //   warp 1     allocates tensor memory; one lane copies the stage's scale atoms shared->tensor
-//              memory (tcgen05.cp) and issues 4 tcgen05.mma kind::mxf4nvf4 (K = 64 each) into
-//              one of two 128x128 fp32 accumulators, committing the stage back to the producer;
-//   warps 2-5  epilogue: tcgen05.ld 32 columns at a time, alpha / bias / GELU, convert, 16-byte
-//              stores; the accumulator is handed back as soon as it has been read.
+//              memory (tcgen05.cp) and issues 4 tcgen05.mma kind::mxf4nvf4 (K = 64 each) per piece
+//              into one of two 128x128 fp32 accumulators, committing the stage back to the producer;
+//   warps 2-5  epilogue: tcgen05.ld, alpha / row scale / bias / activation (or rotary embedding for
+//              the fused QKV form), conversion, 128B-swizzled staging in shared memory and TMA
+//              tile stores (full-line writes, clipped at the matrix edge by the tensor map).
 // No multicast, no cluster; every wait is bounded and reports through the device error word.
 #include <algorithm>
 #include <atomic>
+#include <cstdlib>
 
 #include "tcgen05.cuh"
 
@@ -24,33 +28,41 @@ namespace {
 constexpr int kBM = 128;
 constexpr int kBN = 128;
 constexpr int kBKBytes = 128;            // 256 e2m1 codes per row per stage
-constexpr int kStages = 5;
-constexpr int kATile = kBM * kBKBytes;   // 16 KB
-constexpr int kBTile = kBN * kBKBytes;   // 16 KB
+constexpr int kMaxStages = 5;
+constexpr int kMaxPieces = 4;
+constexpr int kTile = 128 * kBKBytes;    // 16 KB operand tile
 constexpr int kSfSlab = 4 * 512;         // 4 K-atoms of one 128-row tile
-constexpr int kStageBytes = kATile + kBTile + 2 * kSfSlab;
+constexpr int kOutBuf = 128 * 128;       // one staged output box: 128 rows x 128 bytes
 constexpr int kThreads = 192;
 constexpr int kTmemCols = 512;
 constexpr int kAccCols = kBN;            // fp32 accumulator columns per buffer
-constexpr uint32_t kSfaCol = 2 * kAccCols;
-constexpr uint32_t kSfbCol = kSfaCol + 16;
+constexpr uint32_t kSfbCol = 2 * kAccCols;
+constexpr uint32_t kSfaCol = kSfbCol + 16;   // 16 columns per piece
+constexpr int kSmemBudget = 227 * 1024 - 2048;
+
+__host__ __device__ constexpr int stage_bytes(int pieces) { return (1 + pieces) * (kTile + kSfSlab); }
+__host__ __device__ constexpr int num_stages(int pieces) {
+    return (kSmemBudget - 2 * kOutBuf) / stage_bytes(pieces) < kMaxStages
+               ? (kSmemBudget - 2 * kOutBuf) / stage_bytes(pieces)
+               : kMaxStages;
+}
 
 struct alignas(64) GemmParams {
     CUtensorMap map_a;
     CUtensorMap map_b;
+    CUtensorMap map_out;       // plain epilogue: out; fused QKV: q_out
+    CUtensorMap map_k;         // fused QKV: K cache rows
+    CUtensorMap map_v;         // fused QKV: V cache rows
     const uint8_t* sfa;
     const uint8_t* sfb;
     const float* bias;
-    void* out;
     int M, N, K;
-    int ldo;
     int out_dtype;
     int activation;
     float alpha;
     int k_stages;   // ceil(K / 256)
     int m_blocks, n_blocks;
-    // A operand given as `a_pieces` residual pieces stacked along rows (piece p at row p * a_piece_rows):
-    // the K loop runs over all pieces against the same B tiles, summing them in the accumulator
+    // A operand given as `a_pieces` residual pieces stacked along rows (piece p at row p * a_piece_rows)
     int a_pieces;
     int a_piece_rows;
     const float* row_scale;  // optional per-row multiplier of the result (undoes the activation pre-scale)
@@ -59,37 +71,69 @@ struct alignas(64) GemmParams {
     // head rows [64*half, 64*half + 64) followed by their rotation partners (+128).
     int epilogue;
     int q_dim;                 // number of Q outputs (heads * 256); then 256 K and 256 V outputs
-    void* q_out;               // bf16 [M, ldq]
-    int ldq;
-    void* k_rows;              // bf16 cache rows: row (cache_pos0 + m) * 256
-    void* v_rows;
     const int* positions;      // [M] index into the rotary tables
     const __nv_bfloat16* rope_cos;   // [positions, 128]
     const __nv_bfloat16* rope_sin;
+    int debug;   // development switches (TPB200_GEMM_DEBUG): 1 = no stores, 2 = no accumulator reads, 4 = no MMA
 };
 
 enum { kEpiPlain = 0, kEpiQkvRope = 1 };
 
 struct SharedControl {
-    uint64_t full[kStages];
-    uint64_t empty[kStages];
+    uint64_t full[kMaxStages];
+    uint64_t empty[kMaxStages];
     uint64_t acc_full[2];
     uint64_t acc_empty[2];
     uint32_t tmem_base;
     int abort_flag;
 };
 
+// epilogue activations with the hardware approximations (results are rounded to bf16 anyway)
+__device__ __forceinline__ float gelu_tanh_fast(float x) {
+    const float inner = 0.7978845608028654f * (x + 0.044715f * x * x * x);
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(inner));
+    return 0.5f * x * (1.0f + t);
+}
+__device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* smem_src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
+                 "r"(smem_u32(smem_src)), "r"(x), "r"(y)
+                 : "memory");
+}
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read() {
+    asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void bulk_wait_group_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// 16-byte chunk c of row r in a staged 128-byte-row box (the layout a 128B-swizzled TMA store reads)
+__device__ __forceinline__ uint8_t* staged_chunk(uint8_t* buf, int r, int c) {
+    return buf + r * 128 + ((c ^ (r & 7)) << 4);
+}
+
 __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_constant__ GemmParams P) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    SharedControl* ctl = reinterpret_cast<SharedControl*>(smem + kStages * kStageBytes);
+    const int pieces = P.a_pieces;
+    const int nstages = num_stages(pieces);
+    const int stage_sz = stage_bytes(pieces);
+    // stage layout: [B tile][A tile x pieces][SFB slab][SFA slab x pieces]
+    const int off_a = kTile;
+    const int off_sfb = (1 + pieces) * kTile;
+    const int off_sfa = off_sfb + kSfSlab;
+    uint8_t* out_stage = smem + nstages * stage_sz;                       // 2 x 16 KB, 1024-byte aligned
+    SharedControl* ctl = reinterpret_cast<SharedControl*>(out_stage + 2 * kOutBuf);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int total_tiles = P.m_blocks * P.n_blocks;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) {
+        for (int s = 0; s < kMaxStages; ++s) {
             mbar_init(&ctl->full[s], 1);
             mbar_init(&ctl->empty[s], 1);
         }
@@ -120,26 +164,27 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
             for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
                 const int m_blk = tile % P.m_blocks;
                 const int n_blk = tile / P.m_blocks;
-                for (int vs = 0; vs < P.a_pieces * P.k_stages; ++vs, ++it) {
-                    const int piece = vs / P.k_stages;
-                    const int ks = vs - piece * P.k_stages;
-                    const int a_row_tile = piece * (P.a_piece_rows >> 7) + m_blk;
-                    const int s = it % kStages;
-                    if (it >= kStages && !mbar_wait_bounded(&ctl->empty[s], ((it / kStages) - 1) & 1)) {
+                for (int ks = 0; ks < P.k_stages; ++ks, ++it) {
+                    const int s = it % nstages;
+                    if (it >= nstages && !mbar_wait_bounded(&ctl->empty[s], ((it / nstages) - 1) & 1)) {
                         record_error(kErrGemmEmptyBarrierTimeout);
                         *abort_flag = 1;
                         break;
                     }
-                    uint8_t* st = smem + s * kStageBytes;
-                    mbar_expect_tx(&ctl->full[s], kStageBytes);
-                    tc::tma_load_2d(st, &P.map_a, ks * kBKBytes, a_row_tile * kBM, &ctl->full[s]);
-                    tc::tma_load_2d(st + kATile, &P.map_b, ks * kBKBytes, n_blk * kBN, &ctl->full[s]);
-                    bulk_copy_g2s(st + kATile + kBTile,
-                                  P.sfa + static_cast<size_t>(a_row_tile) * sf_row_stride + static_cast<size_t>(ks) * kSfSlab,
-                                  kSfSlab, &ctl->full[s]);
-                    bulk_copy_g2s(st + kATile + kBTile + kSfSlab,
+                    uint8_t* st = smem + s * stage_sz;
+                    mbar_expect_tx(&ctl->full[s], stage_sz);
+                    tc::tma_load_2d(st, &P.map_b, ks * kBKBytes, n_blk * kBN, &ctl->full[s]);
+                    bulk_copy_g2s(st + off_sfb,
                                   P.sfb + static_cast<size_t>(n_blk) * sf_row_stride + static_cast<size_t>(ks) * kSfSlab,
                                   kSfSlab, &ctl->full[s]);
+                    for (int p = 0; p < pieces; ++p) {
+                        const int a_row_tile = p * (P.a_piece_rows >> 7) + m_blk;
+                        tc::tma_load_2d(st + off_a + p * kTile, &P.map_a, ks * kBKBytes, a_row_tile * kBM, &ctl->full[s]);
+                        bulk_copy_g2s(st + off_sfa + p * kSfSlab,
+                                      P.sfa + static_cast<size_t>(a_row_tile) * sf_row_stride +
+                                          static_cast<size_t>(ks) * kSfSlab,
+                                      kSfSlab, &ctl->full[s]);
+                    }
                 }
             }
         }
@@ -157,27 +202,33 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
                 }
                 tc::fence_after_thread_sync();
                 const uint32_t tmem_acc = tmem_base + buf * kAccCols;
-                for (int ks = 0; ks < P.a_pieces * P.k_stages; ++ks, ++it) {
-                    const int s = it % kStages;
-                    if (!mbar_wait_bounded(&ctl->full[s], (it / kStages) & 1)) {
+                for (int ks = 0; ks < P.k_stages; ++ks, ++it) {
+                    const int s = it % nstages;
+                    if (!mbar_wait_bounded(&ctl->full[s], (it / nstages) & 1)) {
                         record_error(kErrGemmTmaBarrierTimeout);
                         *abort_flag = 1;
                         break;
                     }
                     tc::fence_after_thread_sync();
-                    const uint32_t st = smem_u32(smem + s * kStageBytes);
-                    const uint32_t sfa_s = st + kATile + kBTile;
-                    const uint32_t sfb_s = sfa_s + kSfSlab;
+                    const uint32_t st = smem_u32(smem + s * stage_sz);
 #pragma unroll
                     for (int a = 0; a < 4; ++a) {
-                        tc::cp_sf_32x128b(tmem_base + kSfaCol + 4 * a, tc::make_sf_desc(sfa_s + a * 512));
-                        tc::cp_sf_32x128b(tmem_base + kSfbCol + 4 * a, tc::make_sf_desc(sfb_s + a * 512));
+                        tc::cp_sf_32x128b(tmem_base + kSfbCol + 4 * a, tc::make_sf_desc(st + off_sfb + a * 512));
                     }
+                    for (int p = 0; p < pieces; ++p) {
 #pragma unroll
-                    for (int a = 0; a < 4; ++a) {
-                        tc::mma_mxf4nvf4(tmem_acc, tc::make_kmajor_sw128_desc(st, a * 32),
-                                         tc::make_kmajor_sw128_desc(st + kATile, a * 32), idesc,
-                                         tmem_base + kSfaCol + 4 * a, tmem_base + kSfbCol + 4 * a, (ks | a) != 0);
+                        for (int a = 0; a < 4; ++a) {
+                            tc::cp_sf_32x128b(tmem_base + kSfaCol + 16 * p + 4 * a,
+                                              tc::make_sf_desc(st + off_sfa + p * kSfSlab + a * 512));
+                        }
+#pragma unroll
+                        for (int a = 0; a < 4; ++a) {
+                            if (P.debug & 4) break;
+                            tc::mma_mxf4nvf4(tmem_acc, tc::make_kmajor_sw128_desc(st + off_a + p * kTile, a * 32),
+                                             tc::make_kmajor_sw128_desc(st, a * 32), idesc,
+                                             tmem_base + kSfaCol + 16 * p + 4 * a, tmem_base + kSfbCol + 4 * a,
+                                             (ks | p | a) != 0);
+                        }
                     }
                     tc::commit(&ctl->empty[s]);   // stage s may be refilled once these MMAs have read it
                 }
@@ -185,9 +236,12 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
             }
         }
     } else {
-        // ------------------------------------------------------------ epilogue (warps 2..5)
+        // ------------------------------------------------------------ epilogue (warps 2..5, 128 threads)
         const int q = warp & 3;                       // tensor-memory lane quarter this warp may read
+        const int row = q * 32 + lane;                // row of the tile this thread owns
+        const bool issuer = (threadIdx.x == 64);      // first epilogue thread issues the TMA stores
         int tile_iter = 0;
+        uint32_t nstore = 0;                          // staged boxes so far (buffer = nstore & 1)
         for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++tile_iter) {
             const int m_blk = tile % P.m_blocks;
             const int n_blk = tile / P.m_blocks;
@@ -198,65 +252,101 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
                 break;
             }
             tc::fence_after_thread_sync();
-            const int m = m_blk * kBM + q * 32 + lane;
+            const int m = m_blk * kBM + row;
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * kAccCols;
             const float rs = (P.row_scale != nullptr && m < P.M) ? P.alpha * __ldg(P.row_scale + m) : P.alpha;
+            if (P.debug & 2) {
+                tc::fence_before_thread_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&ctl->acc_empty[buf]);
+                continue;
+            }
             if (P.epilogue == kEpiPlain) {
+                // boxes of 128 bytes per row: 64 bf16 or 32 fp32 columns
+                const int cols_per_box = P.out_dtype == TPB200_BF16 ? 64 : 32;
+                const int nboxes = kBN / cols_per_box;
 #pragma unroll 1
-                for (int c = 0; c < kBN / 32; ++c) {
-                    uint32_t r[32];
-                    tc::tmem_ld_32x32b_x32(taddr + c * 32, r);
-                    tc::tmem_ld_wait();
-                    if (c == kBN / 32 - 1) {
-                        // everything this warp needs from the accumulator is in registers
+                for (int bx = 0; bx < nboxes; ++bx, ++nstore) {
+                    uint8_t* ob = out_stage + (nstore & 1) * kOutBuf;
+                    if (issuer) bulk_wait_group_read<1>();    // the store that last used this buffer has read it
+                    epilogue_barrier();
+                    const int n0 = n_blk * kBN + bx * cols_per_box;
+#pragma unroll 1
+                    for (int c = 0; c < cols_per_box / 32; ++c) {
+                        uint32_t r[32];
+                        if (!(P.debug & 16)) {
+                            tc::tmem_ld_32x32b_x32(taddr + bx * cols_per_box + c * 32, r);
+                            tc::tmem_ld_wait();
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) r[i] = i + row;
+                        }
+                        if (P.debug & 8) {
+                            if (r[5] == 0x7fc12345u) record_error(999);
+                            continue;
+                        }
+                        float v[32];
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * rs;
+                        if (P.bias != nullptr) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) {
+                                if (n0 + c * 32 + i < P.N) v[i] += __ldg(P.bias + n0 + c * 32 + i);
+                            }
+                        }
+                        // one uniform branch per chunk: the transcendental code stays out of the plain path
+                        if (P.activation == TPB200_ACT_GELU) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) v[i] = gelu_tanh_fast(v[i]);
+                        } else if (P.activation == TPB200_ACT_SILU) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) v[i] = silu_fast(v[i]);
+                        }
+                        if (P.out_dtype == TPB200_BF16) {
+#pragma unroll
+                            for (int g = 0; g < 4; ++g) {
+                                uint32_t w[4];
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    __nv_bfloat162 b2 = __floats2bfloat162_rn(v[g * 8 + 2 * i], v[g * 8 + 2 * i + 1]);
+                                    w[i] = *reinterpret_cast<uint32_t*>(&b2);
+                                }
+                                *reinterpret_cast<uint4*>(staged_chunk(ob, row, c * 4 + g)) = make_uint4(w[0], w[1], w[2], w[3]);
+                            }
+                        } else {
+#pragma unroll
+                            for (int g = 0; g < 8; ++g) {
+                                *reinterpret_cast<float4*>(staged_chunk(ob, row, g)) =
+                                    make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+                            }
+                        }
+                    }
+                    if (bx == nboxes - 1) {
+                        // everything this warp needs from the accumulator is in registers / shared memory
                         tc::fence_before_thread_sync();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&ctl->acc_empty[buf]);
                     }
-                    const int n0 = n_blk * kBN + c * 32;
-                    if (m < P.M) {
-                        float v[32];
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) {
-                            float f = __uint_as_float(r[i]) * rs;
-                            if (P.bias != nullptr && n0 + i < P.N) f += __ldg(P.bias + n0 + i);
-                            v[i] = apply_activation(f, P.activation);
-                        }
-                        if (P.out_dtype == TPB200_BF16) {
-                            __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(P.out) + static_cast<size_t>(m) * P.ldo + n0;
-#pragma unroll
-                            for (int g = 0; g < 4; ++g) {
-                                if (n0 + g * 8 + 8 <= P.N) {
-                                    uint32_t w[4];
-#pragma unroll
-                                    for (int i = 0; i < 4; ++i) {
-                                        __nv_bfloat162 b2 = __floats2bfloat162_rn(v[g * 8 + 2 * i], v[g * 8 + 2 * i + 1]);
-                                        w[i] = *reinterpret_cast<uint32_t*>(&b2);
-                                    }
-                                    *reinterpret_cast<uint4*>(dst + g * 8) = make_uint4(w[0], w[1], w[2], w[3]);
-                                }
-                            }
-                        } else {
-                            float* dst = static_cast<float*>(P.out) + static_cast<size_t>(m) * P.ldo + n0;
-#pragma unroll
-                            for (int g = 0; g < 8; ++g) {
-                                if (n0 + g * 4 + 4 <= P.N) {
-                                    *reinterpret_cast<float4*>(dst + g * 4) =
-                                        make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
-                                }
-                            }
-                        }
+                    fence_proxy_async_smem();
+                    epilogue_barrier();
+                    if (issuer) {
+                        if (!(P.debug & 1)) tma_store_2d(&P.map_out, ob, n0, m_blk * kBM);
+                        bulk_commit_group();
                     }
                 }
             } else {
                 // Fused QKV: tile columns [0,64) are head offsets i0..i0+63, columns [64,128) their
                 // rotation partners i + 128.  bf16 arithmetic as torch does it: q, cos, sin in bf16,
-                // each product and the sum rounded to bf16.
+                // each product and the sum rounded to bf16.  Two boxes of 64 columns: lo and hi.
                 const int head = n_blk >> 1;
                 const int i0 = (n_blk & 1) * 64;
                 const int n_heads_q = P.q_dim >> 8;
                 const bool is_v = head == n_heads_q + 1;
                 const int pos = (m < P.M) ? __ldg(P.positions + m) : 0;
+                uint8_t* ob_lo = out_stage;
+                uint8_t* ob_hi = out_stage + kOutBuf;
+                if (issuer) bulk_wait_group_read<0>();
+                epilogue_barrier();
 #pragma unroll 1
                 for (int c = 0; c < 2; ++c) {
                     uint32_t lo[32], hi[32];
@@ -268,56 +358,52 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&ctl->acc_empty[buf]);
                     }
-                    if (m < P.M) {
-                        const int i = i0 + c * 32;   // head offset of lo[0]
-                        uint32_t olo[16], ohi[16];
-                        const uint4* cs = reinterpret_cast<const uint4*>(P.rope_cos + static_cast<size_t>(pos) * 128 + i);
-                        const uint4* sn = reinterpret_cast<const uint4*>(P.rope_sin + static_cast<size_t>(pos) * 128 + i);
+                    const int i = i0 + c * 32;   // head offset of lo[0]
+                    const uint4* cs = reinterpret_cast<const uint4*>(P.rope_cos + static_cast<size_t>(pos) * 128 + i);
+                    const uint4* sn = reinterpret_cast<const uint4*>(P.rope_sin + static_cast<size_t>(pos) * 128 + i);
 #pragma unroll
-                        for (int g = 0; g < 4; ++g) {
-                            uint4 cv = make_uint4(0, 0, 0, 0), sv = make_uint4(0, 0, 0, 0);
-                            if (!is_v) { cv = __ldg(cs + g); sv = __ldg(sn + g); }
-                            const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w};
-                            const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
+                    for (int g = 0; g < 4; ++g) {
+                        uint4 cv = make_uint4(0, 0, 0, 0), sv = make_uint4(0, 0, 0, 0);
+                        if (!is_v) { cv = __ldg(cs + g); sv = __ldg(sn + g); }
+                        const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w};
+                        const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
+                        uint32_t olo[4], ohi[4];
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                const int e = g * 8 + 2 * j;
-                                __nv_bfloat162 a = __floats2bfloat162_rn(__uint_as_float(lo[e]) * rs,
-                                                                         __uint_as_float(lo[e + 1]) * rs);
-                                __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(hi[e]) * rs,
-                                                                         __uint_as_float(hi[e + 1]) * rs);
-                                if (!is_v) {
-                                    const __nv_bfloat162 co = *reinterpret_cast<const __nv_bfloat162*>(&cw[j]);
-                                    const __nv_bfloat162 si = *reinterpret_cast<const __nv_bfloat162*>(&sw[j]);
-                                    // first half: x*cos + (-x_partner)*sin ; second half: x_partner*cos + x*sin
-                                    const __nv_bfloat162 ra = __hadd2(__hmul2(a, co), __hmul2(__hneg2(b), si));
-                                    const __nv_bfloat162 rb = __hadd2(__hmul2(b, co), __hmul2(a, si));
-                                    a = ra;
-                                    b = rb;
-                                }
-                                olo[g * 4 + j] = *reinterpret_cast<uint32_t*>(&a);
-                                ohi[g * 4 + j] = *reinterpret_cast<uint32_t*>(&b);
+                        for (int j = 0; j < 4; ++j) {
+                            const int e = g * 8 + 2 * j;
+                            __nv_bfloat162 a = __floats2bfloat162_rn(__uint_as_float(lo[e]) * rs, __uint_as_float(lo[e + 1]) * rs);
+                            __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(hi[e]) * rs, __uint_as_float(hi[e + 1]) * rs);
+                            if (!is_v) {
+                                const __nv_bfloat162 co = *reinterpret_cast<const __nv_bfloat162*>(&cw[j]);
+                                const __nv_bfloat162 si = *reinterpret_cast<const __nv_bfloat162*>(&sw[j]);
+                                // first half: x*cos + (-x_partner)*sin ; second half: x_partner*cos + x*sin
+                                const __nv_bfloat162 ra = __hadd2(__hmul2(a, co), __hmul2(__hneg2(b), si));
+                                const __nv_bfloat162 rb = __hadd2(__hmul2(b, co), __hmul2(a, si));
+                                a = ra;
+                                b = rb;
                             }
+                            olo[j] = *reinterpret_cast<uint32_t*>(&a);
+                            ohi[j] = *reinterpret_cast<uint32_t*>(&b);
                         }
-                        __nv_bfloat16* dst;
-                        if (head < n_heads_q) {
-                            dst = static_cast<__nv_bfloat16*>(P.q_out) + static_cast<size_t>(m) * P.ldq + head * 256 + i;
-                        } else if (!is_v) {
-                            dst = static_cast<__nv_bfloat16*>(P.k_rows) + static_cast<size_t>(m) * 256 + i;
-                        } else {
-                            dst = static_cast<__nv_bfloat16*>(P.v_rows) + static_cast<size_t>(m) * 256 + i;
-                        }
-#pragma unroll
-                        for (int g = 0; g < 4; ++g) {
-                            *reinterpret_cast<uint4*>(dst + g * 8) =
-                                make_uint4(olo[g * 4], olo[g * 4 + 1], olo[g * 4 + 2], olo[g * 4 + 3]);
-                            *reinterpret_cast<uint4*>(dst + 128 + g * 8) =
-                                make_uint4(ohi[g * 4], ohi[g * 4 + 1], ohi[g * 4 + 2], ohi[g * 4 + 3]);
-                        }
+                        *reinterpret_cast<uint4*>(staged_chunk(ob_lo, row, c * 4 + g)) = make_uint4(olo[0], olo[1], olo[2], olo[3]);
+                        *reinterpret_cast<uint4*>(staged_chunk(ob_hi, row, c * 4 + g)) = make_uint4(ohi[0], ohi[1], ohi[2], ohi[3]);
                     }
                 }
+                fence_proxy_async_smem();
+                epilogue_barrier();
+                if (issuer) {
+                    if (!(P.debug & 1)) {
+                        const CUtensorMap* map = head < n_heads_q ? &P.map_out : (is_v ? &P.map_v : &P.map_k);
+                        const int x0 = head < n_heads_q ? head * 256 + i0 : i0;
+                        tma_store_2d(map, ob_lo, x0, m_blk * kBM);
+                        tma_store_2d(map, ob_hi, x0 + 128, m_blk * kBM);
+                    }
+                    bulk_commit_group();
+                }
+                nstore += 2;
             }
         }
+        if (issuer) bulk_wait_group_all();   // every output tile has landed before the CTA goes away
     }
 
     tc::fence_before_thread_sync();
@@ -496,6 +582,21 @@ bool make_tensor_map_bytes_sw128(CUtensorMap* map, const void* base, uint64_t ro
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Output matrix [rows, cols] of bf16 / fp32 elements, box = 128 rows x 128 bytes, 128-byte swizzle.
+bool make_tensor_map_out_sw128(CUtensorMap* map, void* base, int dtype, uint64_t cols, uint64_t rows,
+                               uint64_t pitch_bytes) {
+    EncodeFn fn = get_encode_fn();
+    if (fn == nullptr) return false;
+    const bool bf = dtype == TPB200_BF16;
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {pitch_bytes};
+    const cuuint32_t box[2] = {bf ? 64u : 32u, 128u};
+    const cuuint32_t elem_strides[2] = {1, 1};
+    return fn(map, bf ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, base, dims, strides, box,
+              elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 int device_error_nvfp4_gemm(int clear) { return read_device_error(clear); }
 
 }  // namespace tpb
@@ -583,13 +684,26 @@ extern "C" int tpb200_nvfp4_gemm_ex(const tpb200_nvfp4_gemm_args* a, tpb200_stre
                                           tpb::kBN)) {
         return TPB200_ERR_CUDA;
     }
+    if (qkv) {
+        if (!tpb::make_tensor_map_out_sw128(&P.map_out, a->qkv_q_out, TPB200_BF16, a->qkv_q_dim, M,
+                                            static_cast<uint64_t>(a->qkv_ldq) * 2) ||
+            !tpb::make_tensor_map_out_sw128(&P.map_k, a->qkv_k_rows, TPB200_BF16, 256, M, 512) ||
+            !tpb::make_tensor_map_out_sw128(&P.map_v, a->qkv_v_rows, TPB200_BF16, 256, M, 512)) {
+            return TPB200_ERR_CUDA;
+        }
+    } else {
+        if (!tpb::make_tensor_map_out_sw128(&P.map_out, a->out, a->out_dtype, N, M,
+                                            static_cast<uint64_t>(a->ldo) * tpb_dtype_size(a->out_dtype))) {
+            return TPB200_ERR_CUDA;
+        }
+        P.map_k = P.map_out;
+        P.map_v = P.map_out;
+    }
     P.sfa = static_cast<const uint8_t*>(a->a_sf);
     P.sfb = static_cast<const uint8_t*>(a->b_sf);
     P.bias = a->bias;
-    P.out = a->out;
     P.M = M; P.N = N; P.K = K;
-    P.ldo = a->ldo;
-    P.out_dtype = a->out_dtype;
+    P.out_dtype = qkv ? TPB200_BF16 : a->out_dtype;
     P.activation = a->activation;
     P.alpha = a->alpha;
     P.k_stages = (K + 255) / 256;
@@ -600,25 +714,25 @@ extern "C" int tpb200_nvfp4_gemm_ex(const tpb200_nvfp4_gemm_args* a, tpb200_stre
     P.row_scale = a->a_row_scale;
     P.epilogue = qkv ? tpb::kEpiQkvRope : tpb::kEpiPlain;
     P.q_dim = a->qkv_q_dim;
-    P.q_out = a->qkv_q_out;
-    P.ldq = a->qkv_ldq;
-    P.k_rows = a->qkv_k_rows;
-    P.v_rows = a->qkv_v_rows;
     P.positions = a->qkv_positions;
     P.rope_cos = static_cast<const __nv_bfloat16*>(a->qkv_rope_cos);
     P.rope_sin = static_cast<const __nv_bfloat16*>(a->qkv_rope_sin);
+    {
+        const char* dbg = getenv("TPB200_GEMM_DEBUG");
+        P.debug = dbg != nullptr ? atoi(dbg) : 0;
+    }
 
     int dev = 0, sms = 0;
     if (cudaGetDevice(&dev) != cudaSuccess ||
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
         return TPB200_ERR_CUDA;
     }
-    const size_t smem = tpb::kStages * tpb::kStageBytes + sizeof(tpb::SharedControl) + 1024;
+    const size_t smem = tpb::num_stages(pieces) * tpb::stage_bytes(pieces) + 2 * tpb::kOutBuf + sizeof(tpb::SharedControl) + 1024;
     static std::atomic<uint64_t> configured{0};
     const uint64_t bit = 1ull << (dev & 63);
     if (!(configured.load(std::memory_order_relaxed) & bit)) {
         if (cudaFuncSetAttribute(tpb::nvfp4_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 static_cast<int>(smem)) != cudaSuccess) {
+                                 227 * 1024) != cudaSuccess) {
             return TPB200_ERR_CUDA;
         }
         configured.fetch_or(bit, std::memory_order_relaxed);
