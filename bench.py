@@ -119,40 +119,12 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def dist_setup(n_gpus):
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if world > 1:
-        import torch.distributed as dist
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        torch.cuda.set_device(local)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    return rank, world, local
-
-
-def barrier_sync(world):
-    if world > 1:
-        import torch.distributed as dist
-        dist.barrier()
-    torch.cuda.synchronize()
-
-
-def max_over_ranks(ms, world, device):
-    if world == 1:
-        return ms
-    import torch.distributed as dist
-    t = torch.tensor([ms], dtype=torch.float64, device=device)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return float(t.item())
-
-
 # ------------------------------------------------------------------------------------------ our arm
 def run_ours(args):
     from turbopi_b200 import _lib, ops
-    rank, world, local = dist_setup(args.gpus)
-    device = torch.device("cuda", local)
-    torch.cuda.set_device(device)
+    from turbopi_b200.replicas import ReplicaGroup
+    group = ReplicaGroup.from_env("nccl")
+    rank, world, local, device = group.rank, group.world, group.local_rank, group.device
     _lib.load()
 
     x = {K: torch.randn(1, K, device=device, generator=torch.Generator(device=device).manual_seed(7)).to(torch.bfloat16)
@@ -214,16 +186,16 @@ def run_ours(args):
         w += 1
         if w % 64 == 0:
             torch.cuda.synchronize()
-    barrier_sync(world)
+    group.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.profiler.start()       # `ncu --profile-from-start off` captures the timed region only
     e0.record(stream)
     for i in range(args.steps):
         step(i)
     e1.record(stream)
-    barrier_sync(world)
+    group.barrier()
     torch.cuda.profiler.stop()
-    ms = max_over_ranks(e0.elapsed_time(e1), world, device)
+    ms = group.max_over_ranks(e0.elapsed_time(e1))
     launches = args.steps * (3 if tcs is not None else 1)
     per_launch_s = (e0.elapsed_time(e1) / 1e3) / args.steps   # the GEMV launch; the quantisers ride in its shadow
 
@@ -252,15 +224,15 @@ def run_ours(args):
 
     for i in range(max(3, min(args.warmup, 20))):
         e2e_step(i)
-    barrier_sync(world)
+    group.barrier()
     e2e_steps = args.steps
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     f0.record(stream)
     for i in range(e2e_steps):
         e2e_step(i)
     f1.record(stream)
-    barrier_sync(world)
-    e2e_ms = max_over_ranks(f0.elapsed_time(f1), world, device)
+    group.barrier()
+    e2e_ms = group.max_over_ranks(f0.elapsed_time(f1))
     t_wall1 = time.time()
     clocks = sampler.stop(t_wall0, t_wall1) if sampler else None
 
@@ -303,9 +275,7 @@ def run_ours(args):
             "extras": extras,
         }
         print(json.dumps(line))
-    if world > 1:
-        import torch.distributed as dist
-        dist.destroy_process_group()
+    group.close()
 
 
 def time_launches(fn, iters, warm=20):

@@ -158,7 +158,29 @@ typedef struct {
     void* qkv_q_out; int qkv_ldq; int qkv_q_dim;
     void* qkv_k_rows; void* qkv_v_rows;
     const int* qkv_positions; const void* qkv_rope_cos; const void* qkv_rope_sin; /* bf16 [positions, 128] */
+    /* Optional split-K scratch.  Shapes with fewer 128 x 128 output tiles than SMs split their K range over
+     * several CTAs per tile when a workspace of at least tpb200_nvfp4_gemm_workspace_size() bytes is given
+     * (a smaller one limits the split; NULL = never split).  Zero it ONCE after allocation: the kernel
+     * leaves its counters at zero.  Launches that share a workspace must not overlap.  The partial sums
+     * are added in a fixed order, so results do not depend on timing. */
+    void* workspace; size_t workspace_bytes;
+    /* Operand format.  TPB200_OPERANDS_ROWMAJOR (0): as described above.  TPB200_OPERANDS_TILED: a_packed and
+     * b_packed point at pre-tiled images that carry their scales (a_sf, b_sf, pitches and a_piece_rows are
+     * ignored), which the kernel streams in large contiguous requests into 128 x 256 output tiles -- the
+     * fast path.  B image (tpb200_nvfp4_tile_weights makes it from the row-major operand, once per weight):
+     * blocks [ceil(N/256)][ceil(K/256)] of 36864 bytes = 256 rows x 128 B of codes, 16-byte chunk c of row r
+     * at chunk c ^ (r & 7), then the 2048-byte scale slabs (4 atoms) of rows 0..127 and 128..255.  A image
+     * (tpb200_row_transform_quantize with TPB200_OPERANDS_TILED writes it): blocks [ceil(M/128)][ceil(K/256)]
+     * of a_pieces * 18432 bytes = one 128-row code tile per piece in the same chunk pattern, then one scale
+     * slab per piece; a_pieces <= 3.  Padding rows / K must hold zero scales. */
+    int layout;
 } tpb200_nvfp4_gemm_args;
+enum { TPB200_OPERANDS_ROWMAJOR = 0, TPB200_OPERANDS_TILED = 1 };
+size_t tpb200_nvfp4_gemm_workspace_size(int M, int N, int K, int a_pieces, int layout);
+size_t tpb200_nvfp4_tiled_a_bytes(int M, int K, int pieces);
+size_t tpb200_nvfp4_tiled_b_bytes(int N, int K);
+int tpb200_nvfp4_tile_weights(const void* b_packed, int b_pitch, const void* b_sf, void* image, int N, int K,
+                              tpb200_stream_t stream);
 int tpb200_nvfp4_gemm_ex(const tpb200_nvfp4_gemm_args* args, tpb200_stream_t stream);
 int tpb200_nvfp4_quantize_act_pieces(const void* x, int x_dtype, int ldx, void* packed, int packed_pitch,
                                      void* sf_swizzled, float* row_scale, int M, int K, int pieces,
@@ -219,6 +241,7 @@ typedef struct {
     const void* w0; const void* w1; float eps;
     void* y_out;
     void* packed; int pitch; void* sf; float* row_scale; int pieces; int piece_rows;
+    int layout;   /* TPB200_OPERANDS_TILED: `packed` is the GEMM's tiled A image (pitch, sf, piece_rows unused) */
 } tpb200_rowop_args;
 int tpb200_row_transform_quantize(const tpb200_rowop_args* args, tpb200_stream_t stream);
 

@@ -189,3 +189,160 @@ def test_fused_qkv_rope_kv_append_prefix(cuda_device):
                        ("v", got[layer, 1, :S], ref_cache[layer, 1, :S])):
         assert rel_err(y, r) <= 1e-2, (name, rel_err(y, r))
         assert cosine(y, r) >= 0.999, (name, cosine(y, r))
+
+
+@pytest.mark.parametrize("M,N,K,act", [(50, 1024, 2048, 0), (50, 2048, 4096, 1), (300, 1152, 4608, 2), (17, 136, 2048, 0),
+                                       (129, 520, 8192, 0)])
+def test_split_k_through_workspace_matches_unsplit_and_oracle(cuda_device, M, N, K, act):
+    """Few-tile shapes split their K range over several CTAs when a workspace is given: same result as
+    the unsplit launch (up to fp32 summation order), twice in a row on one workspace (the kernel leaves
+    its counters at zero), bias and activation applied once by the reducing CTA."""
+    from turbopi_b200 import _lib, ops
+    rng = np.random.default_rng(31)
+    w = (rng.normal(size=(N, K)) * 0.02).astype(np.float32)
+    packed, sbytes, g = nvfp4.quantize_two_level(w, 16)
+    x = formats.round_to_bf16(rng.normal(size=(M, K)).astype(np.float32))
+    bias = rng.normal(size=(N,)).astype(np.float32)
+    b = _dev(_pack_padded(packed, ops.packed_pitch(K)), cuda_device)
+    b_sf = _dev(nvfp4.swizzle_scales_128x4(sbytes, 16), cuda_device)
+    xd, bd = _dev(x, cuda_device, torch.bfloat16), _dev(bias, cuda_device)
+    need = ops.nvfp4_gemm_workspace_size(M, N, K, 3)
+    assert need > 0, "shape expected to split"
+    ws = ops.gemm_workspace(cuda_device, need)
+    base = ops.nvfp4_gemm_w4a16(xd, b, b_sf, N, alpha=float(g), bias=bd, activation=act, out_dtype=torch.float32)
+    y1 = ops.nvfp4_gemm_w4a16(xd, b, b_sf, N, alpha=float(g), bias=bd, activation=act, out_dtype=torch.float32,
+                              workspace=ws)
+    y2 = ops.nvfp4_gemm_w4a16(xd, b, b_sf, N, alpha=float(g), bias=bd, activation=act, out_dtype=torch.float32,
+                              workspace=ws)
+    assert _lib.load().tpb200_device_error(0) == 0
+    assert torch.equal(y1, y2)
+    assert (ws[:16384].view(torch.int32) == 0).all()
+    scale = base.abs().max().item()
+    assert (y1 - base).abs().max().item() <= 2e-5 * scale
+    pre = nvfp4.gemv_dequant_matmul(x, packed, sbytes, None, 0, 16, float(g), True) + bias
+    if act == 1:
+        ref = 0.5 * pre * (1 + np.tanh(0.7978845608028654 * (pre + 0.044715 * pre ** 3)))
+    elif act == 2:
+        ref = pre / (1 + np.exp(-pre))
+    else:
+        ref = pre
+    assert rel_err(y1.cpu().numpy(), ref) <= 1e-2
+
+
+def test_fused_qkv_split_k_matches_unsplit(cuda_device):
+    """The action expert's per-step shape (50 tokens): fused QKV + RoPE + cache rows with the K range
+    split over CTAs gives the same bf16 values as the unsplit launch."""
+    from turbopi_b200 import ops
+    rng = np.random.default_rng(13)
+    S, H, QD = 50, 1024, 2048
+    x = _dev(formats.round_to_bf16(rng.normal(size=(S, H)).astype(np.float32)), cuda_device, torch.bfloat16)
+    w = (rng.normal(size=(QD + 512, H)) * 0.02).astype(np.float32)
+    packed, sbytes, g = nvfp4.quantize_two_level(w, 16)
+    perm = ops.qkv_tile_permutation(QD).numpy()
+    b = _dev(_pack_padded(packed[perm], ops.packed_pitch(H)), cuda_device)
+    b_sf = _dev(nvfp4.swizzle_scales_128x4(sbytes[perm], 16), cuda_device)
+    positions = torch.arange(712, 712 + S, dtype=torch.int32, device=cuda_device)
+    cos, sin = ops.rope_tables(1024, device=cuda_device)
+    outs = []
+    for ws in (None, ops.gemm_workspace(cuda_device)):
+        cache = torch.full((2, 1024, 256), -3.0, dtype=torch.bfloat16, device=cuda_device)
+        q = ops.fused_qkv_rope_append(x, b, b_sf, QD, cache[0, 712:], cache[1, 712:], positions, cos, sin,
+                                      alpha=float(g), workspace=ws)
+        outs.append((q.float(), cache.float()))
+    assert ops.nvfp4_gemm_workspace_size(S, QD + 512, H, 3) > 0
+    for a, c in zip(outs[0], outs[1]):
+        # fp32 summation order differs, so a bf16 rounding may flip for a few elements
+        assert (a == c).float().mean().item() > 0.99
+        assert (a - c).abs().max().item() <= 2 ** -7 * a.abs().max().item()
+    assert (outs[1][1][:, :712] == -3.0).all() and (outs[1][1][:, 762:] == -3.0).all()
+
+
+# ---------------------------------------------------------------------------- tiled operand images
+@pytest.mark.parametrize("M,N,K,act,split", [(128, 256, 256, 0, False), (200, 384, 2048, 1, False),
+                                             (712, 2048, 2048, 0, False), (50, 1024, 4096, 2, True),
+                                             (300, 1152, 1152, 0, True), (5, 8, 16, 0, False),
+                                             (130, 4304, 1152, 1, False), (712, 2048, 16384, 0, True)])
+def test_tiled_operands_match_oracle_and_rowmajor(cuda_device, M, N, K, act, split):
+    """The fast path (pre-tiled operand images, 128 x 256 output tiles, bulk-copy producer) against the
+    dequantise-then-matmul oracle and against the row-major form of the same kernel."""
+    from turbopi_b200 import _lib, ops
+    rng = np.random.default_rng(41)
+    w = (rng.normal(size=(N, K)) * 0.02).astype(np.float32)
+    packed, sbytes, g = nvfp4.quantize_two_level(w, 16)
+    x = formats.round_to_bf16((rng.normal(size=(M, K)) * rng.choice([0.05, 1.0, 20.0], size=(M, 1))).astype(np.float32))
+    bias = rng.normal(size=(N,)).astype(np.float32)
+    b = _dev(_pack_padded(packed, ops.packed_pitch(K)), cuda_device)
+    b_sf = _dev(nvfp4.swizzle_scales_128x4(sbytes, 16), cuda_device)
+    image = ops.tile_weights(b, b_sf, N, K)
+    xd, bd = _dev(x, cuda_device, torch.bfloat16), _dev(bias, cuda_device)
+    ws = ops.gemm_workspace(cuda_device) if split else None
+    if split:
+        assert ops.nvfp4_gemm_workspace_size(M, N, K, 3, ops.OPERANDS_TILED) > 0
+    y = ops.nvfp4_gemm_w4a16_tiled(xd, image, N, alpha=float(g), bias=bd, activation=act, out_dtype=torch.float32,
+                                   workspace=ws)
+    y2 = ops.nvfp4_gemm_w4a16_tiled(xd, image, N, alpha=float(g), bias=bd, activation=act, out_dtype=torch.float32,
+                                    workspace=ws)
+    base = ops.nvfp4_gemm_w4a16(xd, b, b_sf, N, alpha=float(g), bias=bd, activation=act, out_dtype=torch.float32)
+    assert _lib.load().tpb200_device_error(0) == 0
+    assert torch.equal(y, y2)
+    assert (y - base).abs().max().item() <= 2e-5 * base.abs().max().item()
+    pre = nvfp4.gemv_dequant_matmul(x, packed, sbytes, None, 0, 16, float(g), True) + bias
+    if act == 1:
+        ref = 0.5 * pre * (1 + np.tanh(0.7978845608028654 * (pre + 0.044715 * pre ** 3)))
+    elif act == 2:
+        ref = pre / (1 + np.exp(-pre))
+    else:
+        ref = pre
+    got = y.cpu().numpy()
+    err = np.abs(got - ref).max(axis=1) / np.maximum(np.abs(ref).max(axis=1), 1e-30)
+    assert err.max() <= 5e-3, err.max()
+
+
+def test_tiled_bf16_output_leaves_neighbours_untouched(cuda_device):
+    """bf16 output into a view of a larger buffer: only the [M, N] window changes (tile stores are clipped
+    by the tensor map at ragged edges: M = 130 rows, N = 328 columns)."""
+    from turbopi_b200 import ops
+    rng = np.random.default_rng(43)
+    M, N, K = 130, 328, 512
+    w = (rng.normal(size=(N, K)) * 0.02).astype(np.float32)
+    packed, sbytes, g = nvfp4.quantize_two_level(w, 16)
+    x = formats.round_to_bf16(rng.normal(size=(M, K)).astype(np.float32))
+    image = ops.tile_weights(_dev(_pack_padded(packed, ops.packed_pitch(K)), cuda_device),
+                             _dev(nvfp4.swizzle_scales_128x4(sbytes, 16), cuda_device), N, K)
+    canvas = torch.full((M + 3, 512), 7.0, dtype=torch.bfloat16, device=cuda_device)
+    out = canvas[2:M + 2, 8:8 + N]
+    ops.nvfp4_gemm_w4a16_tiled(_dev(x, cuda_device, torch.bfloat16), image, N, alpha=float(g), out=out)
+    ref = nvfp4.gemv_dequant_matmul(x, packed, sbytes, None, 0, 16, float(g), True)
+    assert rel_err(out.float().cpu().numpy(), ref) <= 1e-2
+    mask = torch.ones_like(canvas, dtype=torch.bool)
+    mask[2:M + 2, 8:8 + N] = False
+    assert (canvas[mask] == 7.0).all()
+
+
+def test_fused_qkv_tiled_matches_rowmajor(cuda_device):
+    """Fused QKV + RoPE + cache rows through the tiled images: same bf16 results as the row-major form
+    (prefix shape, 712 tokens; and the expert's 50-token shape with split K)."""
+    from turbopi_b200 import ops
+    rng = np.random.default_rng(17)
+    QD = 2048
+    for S, H, pos0, ws in ((712, 2048, 0, None), (50, 1024, 712, "ws")):
+        x = _dev(formats.round_to_bf16(rng.normal(size=(S, H)).astype(np.float32)), cuda_device, torch.bfloat16)
+        w = (rng.normal(size=(QD + 512, H)) * 0.02).astype(np.float32)
+        packed, sbytes, g = nvfp4.quantize_two_level(w, 16)
+        perm = ops.qkv_tile_permutation(QD).numpy()
+        b = _dev(_pack_padded(packed[perm], ops.packed_pitch(H)), cuda_device)
+        b_sf = _dev(nvfp4.swizzle_scales_128x4(sbytes[perm], 16), cuda_device)
+        image = ops.tile_weights(b, b_sf, QD + 512, H)
+        positions = torch.arange(pos0, pos0 + S, dtype=torch.int32, device=cuda_device)
+        cos, sin = ops.rope_tables(1024, device=cuda_device)
+        outs = []
+        for tiled in (False, True):
+            cache = torch.full((2, 1024, 256), -3.0, dtype=torch.bfloat16, device=cuda_device)
+            q = ops.fused_qkv_rope_append(x, image if tiled else b, None if tiled else b_sf, QD, cache[0, pos0:],
+                                          cache[1, pos0:], positions, cos, sin, alpha=float(g),
+                                          workspace=ops.gemm_workspace(cuda_device) if (ws and tiled) else None)
+            outs.append((q.float(), cache.float()))
+        for a, c in zip(outs[0], outs[1]):
+            assert (a == c).float().mean().item() > 0.99
+            assert (a - c).abs().max().item() <= 2 ** -7 * a.abs().max().item()
+        assert (outs[1][1][:, :pos0] == -3.0).all() and (outs[1][1][:, pos0 + S:] == -3.0).all()

@@ -37,7 +37,8 @@ class GemmArgs(ctypes.Structure):
                 ("M", c_int), ("N", c_int), ("K", c_int),
                 ("qkv_q_out", c_void_p), ("qkv_ldq", c_int), ("qkv_q_dim", c_int),
                 ("qkv_k_rows", c_void_p), ("qkv_v_rows", c_void_p),
-                ("qkv_positions", c_void_p), ("qkv_rope_cos", c_void_p), ("qkv_rope_sin", c_void_p)]
+                ("qkv_positions", c_void_p), ("qkv_rope_cos", c_void_p), ("qkv_rope_sin", c_void_p),
+                ("workspace", c_void_p), ("workspace_bytes", c_size_t), ("layout", c_int)]
 
 
 class GemvTcProblem(ctypes.Structure):
@@ -51,7 +52,7 @@ class RowOpArgs(ctypes.Structure):
                 ("res_in", c_void_p), ("gate", c_void_p), ("h_out", c_void_p),
                 ("w0", c_void_p), ("w1", c_void_p), ("eps", c_float), ("y_out", c_void_p),
                 ("packed", c_void_p), ("pitch", c_int), ("sf", c_void_p), ("row_scale", c_void_p),
-                ("pieces", c_int), ("piece_rows", c_int)]
+                ("pieces", c_int), ("piece_rows", c_int), ("layout", c_int)]
 
 
 ROW_NONE, ROW_RMSNORM, ROW_ADARMS, ROW_LAYERNORM, ROW_GELU_MUL = 0, 1, 2, 3, 4
@@ -69,6 +70,10 @@ SIGNATURES = {
     "tpb200_nvfp4_gemv_grouped": (c_int, [ctypes.POINTER(GemvProblem), c_int, c_int, c_int, c_int, c_int, c_int,
                                           c_int, c_int, c_int, c_void_p]),
     "tpb200_nvfp4_sf_bytes": (c_size_t, [c_int, c_int]),
+    "tpb200_nvfp4_gemm_workspace_size": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
+    "tpb200_nvfp4_tiled_a_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "tpb200_nvfp4_tiled_b_bytes": (c_size_t, [c_int, c_int]),
+    "tpb200_nvfp4_tile_weights": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "tpb200_nvfp4_quantize_act": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]),
     "tpb200_nvfp4_gemm": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_float, c_void_p, c_int,
                                   c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),

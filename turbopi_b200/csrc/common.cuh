@@ -28,6 +28,7 @@ enum DeviceErrorCode : int {
     kErrGemmMmaBarrierTimeout = 202,
     kErrGemmEpilogueBarrierTimeout = 203,
     kErrGemmEmptyBarrierTimeout = 204,
+    kErrGemmSplitTimeout = 205,
 };
 
 __device__ __forceinline__ void record_error(int code) { atomicCAS(&g_device_error, 0, code); }

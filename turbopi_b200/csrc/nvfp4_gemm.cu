@@ -16,6 +16,16 @@
 //              the fused QKV form), conversion, 128B-swizzled staging in shared memory and TMA
 //              tile stores (full-line writes, clipped at the matrix edge by the tensor map).
 // No multicast, no cluster; every wait is bounded and reports through the device error word.
+//
+// Two operand formats.  Row-major (the reference's): tiles of 128 x 128 outputs, operands fetched with
+// tiled TMA boxes.  Tiled images (kTiled): both operands pre-arranged so that everything one K stage
+// needs from an operand is ONE contiguous block -- B block (n_blk, ks) = 256 rows x 128 B of codes in
+// the 128B-swizzle pattern + their two scale slabs (36 KB), A block (m_blk, ks) = the code tiles of all
+// pieces + their scale slabs (18 KB per piece) -- fetched with two plain bulk copies per stage into
+// tiles of 128 x 256 outputs.  An SM takes in roughly 0.3 us per copy request whatever its size (the
+// measured rate grows from ~25 GB/s with 8 KB requests to ~100 GB/s with 32 KB+), and this kernel is
+// bound by exactly that intake, so the tiled form both halves the bytes per flop (B shared by twice
+// the columns) and moves them in requests of 36-54 KB instead of 2-16 KB.
 #include <algorithm>
 #include <atomic>
 #include <cstdlib>
@@ -26,7 +36,6 @@ namespace tpb {
 namespace {
 
 constexpr int kBM = 128;
-constexpr int kBN = 128;
 constexpr int kBKBytes = 128;            // 256 e2m1 codes per row per stage
 constexpr int kMaxStages = 5;
 constexpr int kMaxPieces = 4;
@@ -35,15 +44,18 @@ constexpr int kSfSlab = 4 * 512;         // 4 K-atoms of one 128-row tile
 constexpr int kOutBuf = 128 * 128;       // one staged output box: 128 rows x 128 bytes
 constexpr int kThreads = 192;
 constexpr int kTmemCols = 512;
-constexpr int kAccCols = kBN;            // fp32 accumulator columns per buffer
-constexpr uint32_t kSfbCol = 2 * kAccCols;
-constexpr uint32_t kSfaCol = kSfbCol + 16;   // 16 columns per piece
+// tensor memory: columns [0, 256) hold two 128-column accumulators (row-major form) or one of 256
+// columns (tiled form); then the B scales (4 columns per K atom and 128 rows) and 16 columns per A piece
+constexpr uint32_t kSfbCol = 256;
+constexpr uint32_t kSfaCol = kSfbCol + 32;
 constexpr int kSmemBudget = 227 * 1024 - 2048;
+constexpr int kBlock = kTile + kSfSlab;  // codes + scales of 128 rows for one K stage (18 KB)
 
-__host__ __device__ constexpr int stage_bytes(int pieces) { return (1 + pieces) * (kTile + kSfSlab); }
-__host__ __device__ constexpr int num_stages(int pieces) {
-    return (kSmemBudget - 2 * kOutBuf) / stage_bytes(pieces) < kMaxStages
-               ? (kSmemBudget - 2 * kOutBuf) / stage_bytes(pieces)
+__host__ __device__ constexpr int tile_n(bool tiled) { return tiled ? 256 : 128; }
+__host__ __device__ constexpr int stage_bytes(int pieces, bool tiled) { return ((tiled ? 2 : 1) + pieces) * kBlock; }
+__host__ __device__ constexpr int num_stages(int pieces, bool tiled) {
+    return (kSmemBudget - 2 * kOutBuf) / stage_bytes(pieces, tiled) < kMaxStages
+               ? (kSmemBudget - 2 * kOutBuf) / stage_bytes(pieces, tiled)
                : kMaxStages;
 }
 
@@ -55,6 +67,8 @@ struct alignas(64) GemmParams {
     CUtensorMap map_v;         // fused QKV: V cache rows
     const uint8_t* sfa;
     const uint8_t* sfb;
+    const uint8_t* a_image;    // tiled form: blocks [m_blk][ks] of pieces * 18 KB
+    const uint8_t* b_image;    // tiled form: blocks [n_blk][ks] of 36 KB
     const float* bias;
     int M, N, K;
     int out_dtype;
@@ -74,8 +88,20 @@ struct alignas(64) GemmParams {
     const int* positions;      // [M] index into the rotary tables
     const __nv_bfloat16* rope_cos;   // [positions, 128]
     const __nv_bfloat16* rope_sin;
-    int debug;   // development switches (TPB200_GEMM_DEBUG): 1 = no stores, 2 = no accumulator reads, 4 = no MMA
+    // split-K: work item w = tile * splits + split covers K stages [split * stages_per_split, ...);
+    // partial accumulators go through `scratch` ([item][column / 4][row] float4); once all CTAs of a
+    // tile have parked theirs, each finishes a slice of the tile's rows.
+    int splits;
+    int stages_per_split;
+    float* scratch;
+    unsigned int* counters;    // [2][kCounterSlots]: CTAs that parked their sums, CTAs that finished their slice
+    // plain pointers for the split-K path's vector stores
+    void* out;                 // plain: out; fused QKV: q_out
+    int ldo;                   // elements
+    __nv_bfloat16* k_rows;
+    __nv_bfloat16* v_rows;
 };
+constexpr int kCounterSlots = 2048;
 
 enum { kEpiPlain = 0, kEpiQkvRope = 1 };
 
@@ -115,22 +141,89 @@ __device__ __forceinline__ uint8_t* staged_chunk(uint8_t* buf, int r, int c) {
     return buf + r * 128 + ((c ^ (r & 7)) << 4);
 }
 
+// alpha / row scale, bias and activation on 32 consecutive outputs starting at column n
+__device__ __forceinline__ void finish_plain32(float* v, float rs, const float* bias, int n, int N, int activation) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] *= rs;
+    if (bias != nullptr) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            if (n + i < N) v[i] += __ldg(bias + n + i);
+        }
+    }
+    // one uniform branch per chunk: the transcendental code stays out of the plain path
+    if (activation == TPB200_ACT_GELU) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = gelu_tanh_fast(v[i]);
+    } else if (activation == TPB200_ACT_SILU) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = silu_fast(v[i]);
+    }
+}
+
+__device__ __forceinline__ void pack_bf16x32(const float* v, uint32_t* w) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        __nv_bfloat162 b2 = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        w[i] = *reinterpret_cast<uint32_t*>(&b2);
+    }
+}
+
+// Rotary embedding on 32 head offsets (lo) and their partners 128 further on (hi), in bf16 as torch
+// does it: x, cos, sin in bf16, each product and the sum rounded to bf16.  V heads pass through.
+__device__ __forceinline__ void rope_pair32(const float* lo, const float* hi, float rs, const __nv_bfloat16* cos_row,
+                                            const __nv_bfloat16* sin_row, bool is_v, uint32_t* olo, uint32_t* ohi) {
+    const uint4* cs = reinterpret_cast<const uint4*>(cos_row);
+    const uint4* sn = reinterpret_cast<const uint4*>(sin_row);
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+        uint4 cv = make_uint4(0, 0, 0, 0), sv = make_uint4(0, 0, 0, 0);
+        if (!is_v) { cv = __ldg(cs + g); sv = __ldg(sn + g); }
+        const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w};
+        const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int e = g * 8 + 2 * j;
+            __nv_bfloat162 a = __floats2bfloat162_rn(lo[e] * rs, lo[e + 1] * rs);
+            __nv_bfloat162 b = __floats2bfloat162_rn(hi[e] * rs, hi[e + 1] * rs);
+            if (!is_v) {
+                const __nv_bfloat162 co = *reinterpret_cast<const __nv_bfloat162*>(&cw[j]);
+                const __nv_bfloat162 si = *reinterpret_cast<const __nv_bfloat162*>(&sw[j]);
+                // first half: x*cos + (-x_partner)*sin ; second half: x_partner*cos + x*sin
+                const __nv_bfloat162 ra = __hadd2(__hmul2(a, co), __hmul2(__hneg2(b), si));
+                const __nv_bfloat162 rb = __hadd2(__hmul2(b, co), __hmul2(a, si));
+                a = ra;
+                b = rb;
+            }
+            olo[g * 4 + j] = *reinterpret_cast<uint32_t*>(&a);
+            ohi[g * 4 + j] = *reinterpret_cast<uint32_t*>(&b);
+        }
+    }
+}
+
+template <bool kTiled>
 __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_constant__ GemmParams P) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    constexpr int kBN = tile_n(kTiled);
+    constexpr int kSubTiles = kBN / 128;          // 128-column halves of an output tile
+    constexpr int kAccBufs = kTiled ? 1 : 2;
+    constexpr int kItemFloat4 = 128 * kBN / 4;    // one parked partial accumulator
     const int pieces = P.a_pieces;
-    const int nstages = num_stages(pieces);
-    const int stage_sz = stage_bytes(pieces);
-    // stage layout: [B tile][A tile x pieces][SFB slab][SFA slab x pieces]
-    const int off_a = kTile;
-    const int off_sfb = (1 + pieces) * kTile;
-    const int off_sfa = off_sfb + kSfSlab;
+    const int nstages = num_stages(pieces, kTiled);
+    const int stage_sz = stage_bytes(pieces, kTiled);
+    // stage layout, row-major form: [B tile][A tile x pieces][SFB slab][SFA slab x pieces]
+    //               tiled form:     [B 256 rows][SFB slab x 2][A tile x pieces][SFA slab x pieces]
+    const int off_a = kTiled ? 2 * kBlock : kTile;
+    const int off_sfb = kTiled ? 2 * kTile : (1 + pieces) * kTile;
+    const int off_sfa = kTiled ? 2 * kBlock + pieces * kTile : off_sfb + kSfSlab;
     uint8_t* out_stage = smem + nstages * stage_sz;                       // 2 x 16 KB, 1024-byte aligned
     SharedControl* ctl = reinterpret_cast<SharedControl*>(out_stage + 2 * kOutBuf);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int total_tiles = P.m_blocks * P.n_blocks;
+    const int splits = P.splits;
+    const int total_items = P.m_blocks * P.n_blocks * splits;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kMaxStages; ++s) {
@@ -139,7 +232,7 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&ctl->acc_full[b], 1);
-            mbar_init(&ctl->acc_empty[b], 4);
+            mbar_init(&ctl->acc_empty[b], 4);   // one arrival per epilogue warp
         }
         ctl->abort_flag = 0;
         fence_mbar_init();
@@ -157,14 +250,19 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            tc::prefetch_tensormap(&P.map_a);
-            tc::prefetch_tensormap(&P.map_b);
+            if (!kTiled) {
+                tc::prefetch_tensormap(&P.map_a);
+                tc::prefetch_tensormap(&P.map_b);
+            }
             const int sf_row_stride = P.k_stages * kSfSlab;   // bytes per 128-row tile of scales
             int it = 0;
-            for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x) {
+            for (int w = blockIdx.x; w < total_items && !*abort_flag; w += gridDim.x) {
+                const int tile = w / splits;
+                const int ks0 = (w - tile * splits) * P.stages_per_split;
+                const int ks1 = min(P.k_stages, ks0 + P.stages_per_split);
                 const int m_blk = tile % P.m_blocks;
                 const int n_blk = tile / P.m_blocks;
-                for (int ks = 0; ks < P.k_stages; ++ks, ++it) {
+                for (int ks = ks0; ks < ks1; ++ks, ++it) {
                     const int s = it % nstages;
                     if (it >= nstages && !mbar_wait_bounded(&ctl->empty[s], ((it / nstages) - 1) & 1)) {
                         record_error(kErrGemmEmptyBarrierTimeout);
@@ -173,6 +271,14 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
                     }
                     uint8_t* st = smem + s * stage_sz;
                     mbar_expect_tx(&ctl->full[s], stage_sz);
+                    if (kTiled) {
+                        bulk_copy_g2s(st, P.b_image + (static_cast<size_t>(n_blk) * P.k_stages + ks) * (2 * kBlock),
+                                      2 * kBlock, &ctl->full[s]);
+                        bulk_copy_g2s(st + off_a,
+                                      P.a_image + (static_cast<size_t>(m_blk) * P.k_stages + ks) * (pieces * kBlock),
+                                      pieces * kBlock, &ctl->full[s]);
+                        continue;
+                    }
                     tc::tma_load_2d(st, &P.map_b, ks * kBKBytes, n_blk * kBN, &ctl->full[s]);
                     bulk_copy_g2s(st + off_sfb,
                                   P.sfb + static_cast<size_t>(n_blk) * sf_row_stride + static_cast<size_t>(ks) * kSfSlab,
@@ -193,16 +299,19 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
         if (lane == 0) {
             constexpr uint32_t idesc = tc::make_idesc_mxf4nvf4(kBN);
             int it = 0, tile_iter = 0;
-            for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++tile_iter) {
-                const int buf = tile_iter & 1;
-                if (tile_iter >= 2 && !mbar_wait_bounded(&ctl->acc_empty[buf], ((tile_iter >> 1) - 1) & 1)) {
+            for (int w = blockIdx.x; w < total_items && !*abort_flag; w += gridDim.x, ++tile_iter) {
+                const int ks0 = (w % splits) * P.stages_per_split;
+                const int ks1 = min(P.k_stages, ks0 + P.stages_per_split);
+                const int buf = tile_iter % kAccBufs;
+                const int use = tile_iter / kAccBufs;
+                if (use >= 1 && !mbar_wait_bounded(&ctl->acc_empty[buf], (use - 1) & 1)) {
                     record_error(kErrGemmEpilogueBarrierTimeout);
                     *abort_flag = 1;
                     break;
                 }
                 tc::fence_after_thread_sync();
-                const uint32_t tmem_acc = tmem_base + buf * kAccCols;
-                for (int ks = 0; ks < P.k_stages; ++ks, ++it) {
+                const uint32_t tmem_acc = tmem_base + buf * 128;
+                for (int ks = ks0; ks < ks1; ++ks, ++it) {
                     const int s = it % nstages;
                     if (!mbar_wait_bounded(&ctl->full[s], (it / nstages) & 1)) {
                         record_error(kErrGemmTmaBarrierTimeout);
@@ -211,9 +320,14 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
                     }
                     tc::fence_after_thread_sync();
                     const uint32_t st = smem_u32(smem + s * stage_sz);
+                    // B scales of K atom a sit in kSubTiles * 4 consecutive columns (4 per 128 rows)
 #pragma unroll
                     for (int a = 0; a < 4; ++a) {
-                        tc::cp_sf_32x128b(tmem_base + kSfbCol + 4 * a, tc::make_sf_desc(st + off_sfb + a * 512));
+#pragma unroll
+                        for (int h = 0; h < kSubTiles; ++h) {
+                            tc::cp_sf_32x128b(tmem_base + kSfbCol + 4 * (kSubTiles * a + h),
+                                              tc::make_sf_desc(st + off_sfb + h * kSfSlab + a * 512));
+                        }
                     }
                     for (int p = 0; p < pieces; ++p) {
 #pragma unroll
@@ -223,11 +337,11 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
                         }
 #pragma unroll
                         for (int a = 0; a < 4; ++a) {
-                            if (P.debug & 4) break;
                             tc::mma_mxf4nvf4(tmem_acc, tc::make_kmajor_sw128_desc(st + off_a + p * kTile, a * 32),
                                              tc::make_kmajor_sw128_desc(st, a * 32), idesc,
-                                             tmem_base + kSfaCol + 16 * p + 4 * a, tmem_base + kSfbCol + 4 * a,
-                                             (ks | p | a) != 0);
+                                             tmem_base + kSfaCol + 16 * p + 4 * a,
+                                             tmem_base + kSfbCol + 4 * kSubTiles * a,
+                                             ((ks - ks0) | p | a) != 0);
                         }
                     }
                     tc::commit(&ctl->empty[s]);   // stage s may be refilled once these MMAs have read it
@@ -239,28 +353,163 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
         // ------------------------------------------------------------ epilogue (warps 2..5, 128 threads)
         const int q = warp & 3;                       // tensor-memory lane quarter this warp may read
         const int row = q * 32 + lane;                // row of the tile this thread owns
-        const bool issuer = (threadIdx.x == 64);      // first epilogue thread issues the TMA stores
+        const int etid = threadIdx.x - 64;            // 0..127
+        const bool issuer = (etid == 0);              // first epilogue thread issues the TMA stores
+        const int n_heads_q = P.q_dim >> 8;
         int tile_iter = 0;
         uint32_t nstore = 0;                          // staged boxes so far (buffer = nstore & 1)
-        for (int tile = blockIdx.x; tile < total_tiles && !*abort_flag; tile += gridDim.x, ++tile_iter) {
+        for (int w = blockIdx.x; w < total_items && !*abort_flag; w += gridDim.x, ++tile_iter) {
+            const int tile = w / splits;
             const int m_blk = tile % P.m_blocks;
             const int n_blk = tile / P.m_blocks;
-            const int buf = tile_iter & 1;
-            if (!mbar_wait_bounded(&ctl->acc_full[buf], (tile_iter >> 1) & 1)) {
+            const int buf = tile_iter % kAccBufs;
+            if (!mbar_wait_bounded(&ctl->acc_full[buf], (tile_iter / kAccBufs) & 1)) {
                 record_error(kErrGemmMmaBarrierTimeout);
                 *abort_flag = 1;
                 break;
             }
             tc::fence_after_thread_sync();
             const int m = m_blk * kBM + row;
-            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * kAccCols;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * 128;
             const float rs = (P.row_scale != nullptr && m < P.M) ? P.alpha * __ldg(P.row_scale + m) : P.alpha;
-            if (P.debug & 2) {
+
+            if (splits > 1) {
+                // ---- split K: every CTA of the tile parks its partial sums, waits until all of them
+                // have, then finishes its own slice of the tile's rows (sum in split order, epilogue
+                // arithmetic, plain vector stores).  All CTAs of the launch are resident (grid <= SMs,
+                // one CTA per SM) and nobody waits before parking, so the wait cannot deadlock; it is
+                // bounded all the same.
+                const int rows_valid = min(kBM, P.M - m_blk * kBM);
+                float4* scratch4 = reinterpret_cast<float4*>(P.scratch);
+                if (q * 32 < rows_valid) {     // whole warps only: the tensor-memory load is warp-collective
+                    float4* dst = scratch4 + static_cast<size_t>(w) * kItemFloat4 + row;
+#pragma unroll 1
+                    for (int c = 0; c < kBN / 32; ++c) {
+                        uint32_t r[32];
+                        tc::tmem_ld_32x32b_x32(taddr + c * 32, r);
+                        tc::tmem_ld_wait();
+                        if (row < rows_valid) {
+#pragma unroll
+                            for (int g = 0; g < 8; ++g) {
+                                dst[(c * 8 + g) * 128] =
+                                    make_float4(__uint_as_float(r[4 * g]), __uint_as_float(r[4 * g + 1]),
+                                                __uint_as_float(r[4 * g + 2]), __uint_as_float(r[4 * g + 3]));
+                            }
+                        }
+                    }
+                }
                 tc::fence_before_thread_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&ctl->acc_empty[buf]);
+                __threadfence();
+                epilogue_barrier();
+                if (issuer) {
+                    atomicAdd(P.counters + tile, 1u);
+                    const long long t0 = clock64();
+                    while (true) {
+                        unsigned int seen;
+                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(P.counters + tile) : "memory");
+                        if (seen >= static_cast<unsigned int>(splits)) break;
+                        if (clock64() - t0 > 2000000000LL) {
+                            record_error(kErrGemmSplitTimeout);
+                            *abort_flag = 1;
+                            break;
+                        }
+                    }
+                }
+                epilogue_barrier();
+                if (*abort_flag) break;
+                __threadfence();
+                const int split = w - tile * splits;
+                const int per = (rows_valid + splits - 1) / splits;
+                const int r0 = split * per;
+                const int nrows = max(0, min(rows_valid, r0 + per) - r0);
+                const float4* part = scratch4 + static_cast<size_t>(tile) * splits * kItemFloat4;
+                auto sum32 = [&](int r, int col, float* v) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = 0.0f;
+                    for (int sp = 0; sp < splits; ++sp) {
+                        const float4* src = part + static_cast<size_t>(sp) * kItemFloat4 + (col >> 2) * 128 + r;
+#pragma unroll
+                        for (int g = 0; g < 8; ++g) {
+                            const float4 t = __ldcg(src + g * 128);
+                            v[4 * g] += t.x; v[4 * g + 1] += t.y; v[4 * g + 2] += t.z; v[4 * g + 3] += t.w;
+                        }
+                    }
+                };
+                if (P.epilogue == kEpiPlain) {
+                    const int units = nrows * (kBN / 32);
+                    for (int u = etid; u < units; u += 128) {
+                        const int r = r0 + u % nrows;
+                        const int c = u / nrows;
+                        const int n = n_blk * kBN + c * 32;
+                        if (n >= P.N) continue;
+                        const int mm = m_blk * kBM + r;
+                        float v[32];
+                        sum32(r, c * 32, v);
+                        finish_plain32(v, P.row_scale != nullptr ? P.alpha * __ldg(P.row_scale + mm) : P.alpha, P.bias, n,
+                                       P.N, P.activation);
+                        if (P.out_dtype == TPB200_BF16) {
+                            uint32_t pk[16];
+                            pack_bf16x32(v, pk);
+                            uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(P.out) +
+                                                                  static_cast<size_t>(mm) * P.ldo + n);
+#pragma unroll
+                            for (int g = 0; g < 4; ++g) {
+                                if (n + 8 * g < P.N) dst[g] = make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
+                            }
+                        } else {
+                            float4* dst = reinterpret_cast<float4*>(static_cast<float*>(P.out) +
+                                                                    static_cast<size_t>(mm) * P.ldo + n);
+#pragma unroll
+                            for (int g = 0; g < 8; ++g) {
+                                if (n + 4 * g < P.N) dst[g] = make_float4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+                            }
+                        }
+                    }
+                } else {
+                    const int units = nrows * (kBN / 64);
+                    for (int u = etid; u < units; u += 128) {
+                        const int r = r0 + u % nrows;
+                        const int cu = u / nrows;                  // (128-column half, 32-column chunk)
+                        const int sub = cu >> 1, c = cu & 1;
+                        const int n128 = n_blk * kSubTiles + sub;
+                        const int head = n128 >> 1;
+                        const int i = (n128 & 1) * 64 + c * 32;    // head offset of the first lo column
+                        const bool is_v = head == n_heads_q + 1;
+                        const int mm = m_blk * kBM + r;
+                        float lo[32], hi[32];
+                        sum32(r, sub * 128 + c * 32, lo);
+                        sum32(r, sub * 128 + 64 + c * 32, hi);
+                        const int pos = __ldg(P.positions + mm);
+                        uint32_t olo[16], ohi[16];
+                        rope_pair32(lo, hi, P.row_scale != nullptr ? P.alpha * __ldg(P.row_scale + mm) : P.alpha,
+                                    P.rope_cos + static_cast<size_t>(pos) * 128 + i,
+                                    P.rope_sin + static_cast<size_t>(pos) * 128 + i, is_v, olo, ohi);
+                        __nv_bfloat16* base = head < n_heads_q
+                                                  ? static_cast<__nv_bfloat16*>(P.out) + static_cast<size_t>(mm) * P.ldo + head * 256
+                                                  : (is_v ? P.v_rows : P.k_rows) + static_cast<size_t>(mm) * 256;
+                        uint4* dlo = reinterpret_cast<uint4*>(base + i);
+                        uint4* dhi = reinterpret_cast<uint4*>(base + i + 128);
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            dlo[g] = make_uint4(olo[4 * g], olo[4 * g + 1], olo[4 * g + 2], olo[4 * g + 3]);
+                            dhi[g] = make_uint4(ohi[4 * g], ohi[4 * g + 1], ohi[4 * g + 2], ohi[4 * g + 3]);
+                        }
+                    }
+                }
+                // the last CTA to leave the tile puts both counters back to zero for the next launch
+                epilogue_barrier();
+                if (issuer) {
+                    const unsigned int t = atomicAdd(P.counters + kCounterSlots + tile, 1u);
+                    if (t == static_cast<unsigned int>(splits - 1)) {
+                        P.counters[tile] = 0;
+                        P.counters[kCounterSlots + tile] = 0;
+                    }
+                }
                 continue;
             }
+
             if (P.epilogue == kEpiPlain) {
                 // boxes of 128 bytes per row: 64 bf16 or 32 fp32 columns
                 const int cols_per_box = P.out_dtype == TPB200_BF16 ? 64 : 32;
@@ -273,45 +522,20 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
                     const int n0 = n_blk * kBN + bx * cols_per_box;
 #pragma unroll 1
                     for (int c = 0; c < cols_per_box / 32; ++c) {
-                        uint32_t r[32];
-                        if (!(P.debug & 16)) {
-                            tc::tmem_ld_32x32b_x32(taddr + bx * cols_per_box + c * 32, r);
-                            tc::tmem_ld_wait();
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) r[i] = i + row;
-                        }
-                        if (P.debug & 8) {
-                            if (r[5] == 0x7fc12345u) record_error(999);
-                            continue;
-                        }
+                        uint32_t raw[32];
+                        tc::tmem_ld_32x32b_x32(taddr + bx * cols_per_box + c * 32, raw);
+                        tc::tmem_ld_wait();
                         float v[32];
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * rs;
-                        if (P.bias != nullptr) {
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) {
-                                if (n0 + c * 32 + i < P.N) v[i] += __ldg(P.bias + n0 + c * 32 + i);
-                            }
-                        }
-                        // one uniform branch per chunk: the transcendental code stays out of the plain path
-                        if (P.activation == TPB200_ACT_GELU) {
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) v[i] = gelu_tanh_fast(v[i]);
-                        } else if (P.activation == TPB200_ACT_SILU) {
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) v[i] = silu_fast(v[i]);
-                        }
+                        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[i]);
+                        finish_plain32(v, rs, P.bias, n0 + c * 32, P.N, P.activation);
                         if (P.out_dtype == TPB200_BF16) {
+                            uint32_t pk[16];
+                            pack_bf16x32(v, pk);
 #pragma unroll
                             for (int g = 0; g < 4; ++g) {
-                                uint32_t w[4];
-#pragma unroll
-                                for (int i = 0; i < 4; ++i) {
-                                    __nv_bfloat162 b2 = __floats2bfloat162_rn(v[g * 8 + 2 * i], v[g * 8 + 2 * i + 1]);
-                                    w[i] = *reinterpret_cast<uint32_t*>(&b2);
-                                }
-                                *reinterpret_cast<uint4*>(staged_chunk(ob, row, c * 4 + g)) = make_uint4(w[0], w[1], w[2], w[3]);
+                                *reinterpret_cast<uint4*>(staged_chunk(ob, row, c * 4 + g)) =
+                                    make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
                             }
                         } else {
 #pragma unroll
@@ -330,77 +554,64 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
                     fence_proxy_async_smem();
                     epilogue_barrier();
                     if (issuer) {
-                        if (!(P.debug & 1)) tma_store_2d(&P.map_out, ob, n0, m_blk * kBM);
+                        if (n0 < P.N) tma_store_2d(&P.map_out, ob, n0, m_blk * kBM);
                         bulk_commit_group();
                     }
                 }
             } else {
                 // Fused QKV: tile columns [0,64) are head offsets i0..i0+63, columns [64,128) their
-                // rotation partners i + 128.  bf16 arithmetic as torch does it: q, cos, sin in bf16,
-                // each product and the sum rounded to bf16.  Two boxes of 64 columns: lo and hi.
-                const int head = n_blk >> 1;
-                const int i0 = (n_blk & 1) * 64;
-                const int n_heads_q = P.q_dim >> 8;
-                const bool is_v = head == n_heads_q + 1;
+                // rotation partners i + 128.  Two boxes of 64 columns per 128-column half: lo and hi.
                 const int pos = (m < P.M) ? __ldg(P.positions + m) : 0;
                 uint8_t* ob_lo = out_stage;
                 uint8_t* ob_hi = out_stage + kOutBuf;
-                if (issuer) bulk_wait_group_read<0>();
-                epilogue_barrier();
 #pragma unroll 1
-                for (int c = 0; c < 2; ++c) {
-                    uint32_t lo[32], hi[32];
-                    tc::tmem_ld_32x32b_x32(taddr + c * 32, lo);
-                    tc::tmem_ld_32x32b_x32(taddr + 64 + c * 32, hi);
-                    tc::tmem_ld_wait();
-                    if (c == 1) {
-                        tc::fence_before_thread_sync();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(&ctl->acc_empty[buf]);
-                    }
-                    const int i = i0 + c * 32;   // head offset of lo[0]
-                    const uint4* cs = reinterpret_cast<const uint4*>(P.rope_cos + static_cast<size_t>(pos) * 128 + i);
-                    const uint4* sn = reinterpret_cast<const uint4*>(P.rope_sin + static_cast<size_t>(pos) * 128 + i);
-#pragma unroll
-                    for (int g = 0; g < 4; ++g) {
-                        uint4 cv = make_uint4(0, 0, 0, 0), sv = make_uint4(0, 0, 0, 0);
-                        if (!is_v) { cv = __ldg(cs + g); sv = __ldg(sn + g); }
-                        const uint32_t cw[4] = {cv.x, cv.y, cv.z, cv.w};
-                        const uint32_t sw[4] = {sv.x, sv.y, sv.z, sv.w};
-                        uint32_t olo[4], ohi[4];
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const int e = g * 8 + 2 * j;
-                            __nv_bfloat162 a = __floats2bfloat162_rn(__uint_as_float(lo[e]) * rs, __uint_as_float(lo[e + 1]) * rs);
-                            __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(hi[e]) * rs, __uint_as_float(hi[e + 1]) * rs);
-                            if (!is_v) {
-                                const __nv_bfloat162 co = *reinterpret_cast<const __nv_bfloat162*>(&cw[j]);
-                                const __nv_bfloat162 si = *reinterpret_cast<const __nv_bfloat162*>(&sw[j]);
-                                // first half: x*cos + (-x_partner)*sin ; second half: x_partner*cos + x*sin
-                                const __nv_bfloat162 ra = __hadd2(__hmul2(a, co), __hmul2(__hneg2(b), si));
-                                const __nv_bfloat162 rb = __hadd2(__hmul2(b, co), __hmul2(a, si));
-                                a = ra;
-                                b = rb;
-                            }
-                            olo[j] = *reinterpret_cast<uint32_t*>(&a);
-                            ohi[j] = *reinterpret_cast<uint32_t*>(&b);
+                for (int sub = 0; sub < kSubTiles; ++sub) {
+                    const int n128 = n_blk * kSubTiles + sub;     // 128-row tile of the permuted weight
+                    const int head = n128 >> 1;
+                    const int i0 = (n128 & 1) * 64;
+                    const bool is_v = head == n_heads_q + 1;
+                    if (issuer) bulk_wait_group_read<0>();
+                    epilogue_barrier();
+#pragma unroll 1
+                    for (int c = 0; c < 2; ++c) {
+                        uint32_t rl[32], rh[32];
+                        tc::tmem_ld_32x32b_x32(taddr + sub * 128 + c * 32, rl);
+                        tc::tmem_ld_32x32b_x32(taddr + sub * 128 + 64 + c * 32, rh);
+                        tc::tmem_ld_wait();
+                        if (c == 1 && sub == kSubTiles - 1) {
+                            tc::fence_before_thread_sync();
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(&ctl->acc_empty[buf]);
                         }
-                        *reinterpret_cast<uint4*>(staged_chunk(ob_lo, row, c * 4 + g)) = make_uint4(olo[0], olo[1], olo[2], olo[3]);
-                        *reinterpret_cast<uint4*>(staged_chunk(ob_hi, row, c * 4 + g)) = make_uint4(ohi[0], ohi[1], ohi[2], ohi[3]);
+                        float lo[32], hi[32];
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            lo[i] = __uint_as_float(rl[i]);
+                            hi[i] = __uint_as_float(rh[i]);
+                        }
+                        const int i = i0 + c * 32;   // head offset of lo[0]
+                        uint32_t olo[16], ohi[16];
+                        rope_pair32(lo, hi, rs, P.rope_cos + static_cast<size_t>(pos) * 128 + i,
+                                    P.rope_sin + static_cast<size_t>(pos) * 128 + i, is_v, olo, ohi);
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            *reinterpret_cast<uint4*>(staged_chunk(ob_lo, row, c * 4 + g)) =
+                                make_uint4(olo[4 * g], olo[4 * g + 1], olo[4 * g + 2], olo[4 * g + 3]);
+                            *reinterpret_cast<uint4*>(staged_chunk(ob_hi, row, c * 4 + g)) =
+                                make_uint4(ohi[4 * g], ohi[4 * g + 1], ohi[4 * g + 2], ohi[4 * g + 3]);
+                        }
                     }
-                }
-                fence_proxy_async_smem();
-                epilogue_barrier();
-                if (issuer) {
-                    if (!(P.debug & 1)) {
+                    fence_proxy_async_smem();
+                    epilogue_barrier();
+                    if (issuer) {
                         const CUtensorMap* map = head < n_heads_q ? &P.map_out : (is_v ? &P.map_v : &P.map_k);
                         const int x0 = head < n_heads_q ? head * 256 + i0 : i0;
                         tma_store_2d(map, ob_lo, x0, m_blk * kBM);
                         tma_store_2d(map, ob_hi, x0 + 128, m_blk * kBM);
+                        bulk_commit_group();
                     }
-                    bulk_commit_group();
+                    nstore += 2;
                 }
-                nstore += 2;
             }
         }
         if (issuer) bulk_wait_group_all();   // every output tile has landed before the CTA goes away
@@ -412,6 +623,53 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
         tc::fence_after_thread_sync();
         tc::tmem_dealloc(tmem_base, kTmemCols);
     }
+}
+
+// ------------------------------------------------------------------------------------------
+// Weight preparation for the tiled form: row-major codes [N, pitch] + atom-layout scales -> B image.
+// Block (n_blk, ks) of 36 KB: 256 rows x 128 B with 16-byte chunk c of row r stored at c ^ (r & 7),
+// then the 2 KB scale slabs of rows [0, 128) and [128, 256).  Rows >= N and K beyond the matrix are
+// zero codes with zero scales.  One thread per 16-byte chunk of the image.
+// ------------------------------------------------------------------------------------------
+__global__ void tile_weights_kernel(const uint8_t* __restrict__ packed, int pitch, const uint8_t* __restrict__ sf,
+                                    uint8_t* __restrict__ image, int N, int K, int k_stages, long long chunks) {
+    const long long t = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (t >= chunks) return;
+    constexpr int kChunksPerBlock = 2 * kBlock / 16;
+    const long long blk = t / kChunksPerBlock;
+    const int ci = static_cast<int>(t % kChunksPerBlock);
+    const int n_blk = static_cast<int>(blk / k_stages);
+    const int ks = static_cast<int>(blk % k_stages);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (ci < 2 * kTile / 16) {
+        const int r = ci >> 3;                 // row of the 256-row block
+        const int c = (ci & 7) ^ (r & 7);      // source chunk that lands in this slot
+        const int n = n_blk * 256 + r;
+        const int byte0 = ks * 128 + c * 16;
+        if (n < N && byte0 < K / 2) {
+            v = *reinterpret_cast<const uint4*>(packed + static_cast<size_t>(n) * pitch + byte0);
+            // a chunk that straddles K / 2 (K % 32 != 0) keeps only its valid bytes
+            const int valid = K / 2 - byte0;
+            if (valid < 16) {
+                uint32_t w[4] = {v.x, v.y, v.z, v.w};
+                for (int i = 0; i < 4; ++i) {
+                    const int rem = valid - 4 * i;
+                    if (rem <= 0) w[i] = 0;
+                    else if (rem < 4) w[i] &= (1u << (8 * rem)) - 1u;
+                }
+                v = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        }
+    } else {
+        const int si = ci - 2 * kTile / 16;    // 16-byte chunk of the two scale slabs
+        const int h = si / (kSfSlab / 16);
+        const int off = (si % (kSfSlab / 16)) * 16;
+        const int row_tile = n_blk * 2 + h;
+        if (row_tile * 128 < N) {
+            v = *reinterpret_cast<const uint4*>(sf + (static_cast<size_t>(row_tile) * k_stages + ks) * kSfSlab + off);
+        }
+    }
+    *reinterpret_cast<uint4*>(image + static_cast<size_t>(t) * 16) = v;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -599,6 +857,35 @@ bool make_tensor_map_out_sw128(CUtensorMap* map, void* base, int dtype, uint64_t
 
 int device_error_nvfp4_gemm(int clear) { return read_device_error(clear); }
 
+// Split-K plan.  A launch with fewer tiles than SMs leaves SMs idle and makes each busy one walk the
+// whole K range; splitting K over `splits` CTAs per tile trades that for one pass of the partial sums
+// through L2.  The cost model (microseconds, fitted to B200 timings of this kernel) only has to rank
+// the candidates.
+constexpr size_t kCounterBytes = 16384;            // 4096 tile counters in front of the partial sums
+struct SplitPlan { int splits; int stages_per_split; size_t bytes; };
+
+SplitPlan plan_splits(int tiles, int k_stages, int pieces, bool tiled, int sms, size_t workspace_bytes) {
+    SplitPlan best{1, k_stages, 0};
+    if (2 * tiles > sms || tiles > kCounterSlots || k_stages < 2) return best;
+    const size_t item_bytes = static_cast<size_t>(128) * tile_n(tiled) * 4;   // one partial accumulator
+    // a stage costs its bytes over what one SM takes in with two stages in flight (KB per microsecond);
+    // a split launch adds parking the sums, the wait for the slowest CTA and the slice pass
+    const float t_stage = stage_bytes(pieces, tiled) / 1024.0f / (tiled ? 50.0f : 60.0f);
+    float best_cost = k_stages * t_stage;
+    for (int s = 2; s <= std::min(k_stages, sms / tiles); ++s) {    // one wave: every CTA is resident
+        const int sps = (k_stages + s - 1) / s;
+        const int s_eff = (k_stages + sps - 1) / sps;
+        const size_t bytes = kCounterBytes + static_cast<size_t>(tiles) * s_eff * item_bytes;
+        if (bytes > workspace_bytes) continue;
+        const float c = sps * t_stage + 2.5f;
+        if (c < best_cost * 0.95f) {
+            best_cost = c;
+            best = SplitPlan{s_eff, sps, bytes};
+        }
+    }
+    return best;
+}
+
 }  // namespace tpb
 
 extern "C" size_t tpb200_nvfp4_sf_bytes(int rows, int K) {
@@ -645,20 +932,66 @@ extern "C" int tpb200_nvfp4_quantize_act_pieces(const void* x, int x_dtype, int 
     return tpb_launch_status();
 }
 
+extern "C" size_t tpb200_nvfp4_tiled_a_bytes(int M, int K, int pieces) {
+    if (M < 1 || K < 16 || pieces < 1 || pieces > 3) return 0;
+    return static_cast<size_t>((M + 127) / 128) * ((K + 255) / 256) * pieces * tpb::kBlock;
+}
+
+extern "C" size_t tpb200_nvfp4_tiled_b_bytes(int N, int K) {
+    if (N < 1 || K < 16) return 0;
+    return static_cast<size_t>((N + 255) / 256) * ((K + 255) / 256) * 2 * tpb::kBlock;
+}
+
+extern "C" int tpb200_nvfp4_tile_weights(const void* packed, int pitch, const void* sf_swizzled, void* image, int N,
+                                         int K, tpb200_stream_t stream) {
+    TPB_REQUIRE(packed && sf_swizzled && image, TPB200_ERR_NULL);
+    TPB_REQUIRE(N >= 1 && K >= 16 && K % 16 == 0, TPB200_ERR_SHAPE);
+    TPB_REQUIRE(pitch >= K / 2 && pitch % 16 == 0 && tpb_aligned16(packed) && tpb_aligned16(sf_swizzled) &&
+                    tpb_aligned16(image),
+                TPB200_ERR_ALIGN);
+    const int k_stages = (K + 255) / 256;
+    const int n_blocks = (N + 255) / 256;
+    const long long chunks = static_cast<long long>(n_blocks) * k_stages * (2 * tpb::kBlock / 16);
+    tpb::tile_weights_kernel<<<static_cast<unsigned>((chunks + 255) / 256), 256, 0,
+                               reinterpret_cast<cudaStream_t>(stream)>>>(
+        static_cast<const uint8_t*>(packed), pitch, static_cast<const uint8_t*>(sf_swizzled),
+        static_cast<uint8_t*>(image), N, K, k_stages, chunks);
+    return tpb_launch_status();
+}
+
+extern "C" size_t tpb200_nvfp4_gemm_workspace_size(int M, int N, int K, int a_pieces, int layout) {
+    if (M < 1 || N < 1 || K < 16) return 0;
+    const bool tiled = layout == TPB200_OPERANDS_TILED;
+    const int bn = tpb::tile_n(tiled);
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+        return 0;
+    }
+    const int tiles = ((M + tpb::kBM - 1) / tpb::kBM) * ((N + bn - 1) / bn);
+    return tpb::plan_splits(tiles, (K + 255) / 256, a_pieces <= 0 ? 1 : a_pieces, tiled, sms, ~size_t(0)).bytes;
+}
+
 extern "C" int tpb200_nvfp4_gemm_ex(const tpb200_nvfp4_gemm_args* a, tpb200_stream_t stream) {
     TPB_REQUIRE(a != nullptr, TPB200_ERR_NULL);
     const int M = a->M, N = a->N, K = a->K;
-    TPB_REQUIRE(a->a_packed && a->a_sf && a->b_packed && a->b_sf, TPB200_ERR_NULL);
+    TPB_REQUIRE(a->layout == TPB200_OPERANDS_ROWMAJOR || a->layout == TPB200_OPERANDS_TILED, TPB200_ERR_ENUM);
+    const bool tiled = a->layout == TPB200_OPERANDS_TILED;
+    TPB_REQUIRE(a->a_packed && a->b_packed, TPB200_ERR_NULL);
     TPB_REQUIRE(M >= 1 && N >= 8 && N % 8 == 0 && K >= 16 && K % 16 == 0, TPB200_ERR_SHAPE);
     TPB_REQUIRE(a->activation >= TPB200_ACT_NONE && a->activation <= TPB200_ACT_SILU, TPB200_ERR_ENUM);
-    TPB_REQUIRE(a->a_pitch >= K / 2 && a->b_pitch >= K / 2 && a->a_pitch % 16 == 0 && a->b_pitch % 16 == 0,
-                TPB200_ERR_ALIGN);
-    TPB_REQUIRE(tpb_aligned16(a->a_packed) && tpb_aligned16(a->b_packed) && tpb_aligned16(a->a_sf) &&
-                    tpb_aligned16(a->b_sf),
-                TPB200_ERR_ALIGN);
     const int pieces = a->a_pieces <= 0 ? 1 : a->a_pieces;
-    TPB_REQUIRE(pieces <= 4, TPB200_ERR_SHAPE);
-    TPB_REQUIRE(pieces == 1 || (a->a_piece_rows >= M && a->a_piece_rows % 128 == 0), TPB200_ERR_SHAPE);
+    TPB_REQUIRE(tpb_aligned16(a->a_packed) && tpb_aligned16(a->b_packed), TPB200_ERR_ALIGN);
+    if (tiled) {
+        TPB_REQUIRE(pieces <= 3, TPB200_ERR_SHAPE);
+    } else {
+        TPB_REQUIRE(a->a_sf && a->b_sf, TPB200_ERR_NULL);
+        TPB_REQUIRE(a->a_pitch >= K / 2 && a->b_pitch >= K / 2 && a->a_pitch % 16 == 0 && a->b_pitch % 16 == 0,
+                    TPB200_ERR_ALIGN);
+        TPB_REQUIRE(tpb_aligned16(a->a_sf) && tpb_aligned16(a->b_sf), TPB200_ERR_ALIGN);
+        TPB_REQUIRE(pieces <= 4, TPB200_ERR_SHAPE);
+        TPB_REQUIRE(pieces == 1 || (a->a_piece_rows >= M && a->a_piece_rows % 128 == 0), TPB200_ERR_SHAPE);
+    }
     const bool qkv = a->qkv_q_out != nullptr;
     if (qkv) {
         TPB_REQUIRE(a->qkv_k_rows && a->qkv_v_rows && a->qkv_positions && a->qkv_rope_cos && a->qkv_rope_sin,
@@ -678,12 +1011,14 @@ extern "C" int tpb200_nvfp4_gemm_ex(const tpb200_nvfp4_gemm_args* a, tpb200_stre
 
     tpb::GemmParams P;
     const uint64_t a_rows = pieces == 1 ? static_cast<uint64_t>(M) : static_cast<uint64_t>(pieces) * a->a_piece_rows;
-    if (!tpb::make_tensor_map_bytes_sw128(&P.map_a, a->a_packed, static_cast<uint64_t>(K) / 2, a_rows, a->a_pitch,
-                                          tpb::kBM) ||
-        !tpb::make_tensor_map_bytes_sw128(&P.map_b, a->b_packed, static_cast<uint64_t>(K) / 2, N, a->b_pitch,
-                                          tpb::kBN)) {
+    if (!tiled &&
+        (!tpb::make_tensor_map_bytes_sw128(&P.map_a, a->a_packed, static_cast<uint64_t>(K) / 2, a_rows, a->a_pitch,
+                                           tpb::kBM) ||
+         !tpb::make_tensor_map_bytes_sw128(&P.map_b, a->b_packed, static_cast<uint64_t>(K) / 2, N, a->b_pitch, 128))) {
         return TPB200_ERR_CUDA;
     }
+    P.a_image = static_cast<const uint8_t*>(a->a_packed);
+    P.b_image = static_cast<const uint8_t*>(a->b_packed);
     if (qkv) {
         if (!tpb::make_tensor_map_out_sw128(&P.map_out, a->qkv_q_out, TPB200_BF16, a->qkv_q_dim, M,
                                             static_cast<uint64_t>(a->qkv_ldq) * 2) ||
@@ -708,7 +1043,7 @@ extern "C" int tpb200_nvfp4_gemm_ex(const tpb200_nvfp4_gemm_args* a, tpb200_stre
     P.alpha = a->alpha;
     P.k_stages = (K + 255) / 256;
     P.m_blocks = (M + tpb::kBM - 1) / tpb::kBM;
-    P.n_blocks = (N + tpb::kBN - 1) / tpb::kBN;
+    P.n_blocks = (N + tpb::tile_n(tiled) - 1) / tpb::tile_n(tiled);
     P.a_pieces = pieces;
     P.a_piece_rows = pieces == 1 ? 0 : a->a_piece_rows;
     P.row_scale = a->a_row_scale;
@@ -717,28 +1052,45 @@ extern "C" int tpb200_nvfp4_gemm_ex(const tpb200_nvfp4_gemm_args* a, tpb200_stre
     P.positions = a->qkv_positions;
     P.rope_cos = static_cast<const __nv_bfloat16*>(a->qkv_rope_cos);
     P.rope_sin = static_cast<const __nv_bfloat16*>(a->qkv_rope_sin);
-    {
-        const char* dbg = getenv("TPB200_GEMM_DEBUG");
-        P.debug = dbg != nullptr ? atoi(dbg) : 0;
-    }
 
     int dev = 0, sms = 0;
     if (cudaGetDevice(&dev) != cudaSuccess ||
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
         return TPB200_ERR_CUDA;
     }
-    const size_t smem = tpb::num_stages(pieces) * tpb::stage_bytes(pieces) + 2 * tpb::kOutBuf + sizeof(tpb::SharedControl) + 1024;
+    const size_t smem = tpb::num_stages(pieces, tiled) * tpb::stage_bytes(pieces, tiled) + 2 * tpb::kOutBuf +
+                        sizeof(tpb::SharedControl) + 1024;
     static std::atomic<uint64_t> configured{0};
     const uint64_t bit = 1ull << (dev & 63);
     if (!(configured.load(std::memory_order_relaxed) & bit)) {
-        if (cudaFuncSetAttribute(tpb::nvfp4_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(tpb::nvfp4_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 227 * 1024) != cudaSuccess ||
+            cudaFuncSetAttribute(tpb::nvfp4_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  227 * 1024) != cudaSuccess) {
             return TPB200_ERR_CUDA;
         }
         configured.fetch_or(bit, std::memory_order_relaxed);
     }
-    const int grid = std::min(P.m_blocks * P.n_blocks, sms);
-    tpb::nvfp4_gemm_kernel<<<grid, tpb::kThreads, smem, reinterpret_cast<cudaStream_t>(stream)>>>(P);
+    const int tiles = P.m_blocks * P.n_blocks;
+    tpb::SplitPlan plan{1, P.k_stages, 0};
+    if (a->workspace != nullptr) {
+        TPB_REQUIRE(tpb_aligned16(a->workspace), TPB200_ERR_ALIGN);
+        plan = tpb::plan_splits(tiles, P.k_stages, pieces, tiled, sms, a->workspace_bytes);
+    }
+    P.splits = plan.splits;
+    P.stages_per_split = plan.stages_per_split;
+    P.counters = static_cast<unsigned int*>(a->workspace);
+    P.out = qkv ? a->qkv_q_out : a->out;
+    P.ldo = qkv ? a->qkv_ldq : a->ldo;
+    P.k_rows = static_cast<__nv_bfloat16*>(a->qkv_k_rows);
+    P.v_rows = static_cast<__nv_bfloat16*>(a->qkv_v_rows);
+    P.scratch = reinterpret_cast<float*>(static_cast<uint8_t*>(a->workspace) + tpb::kCounterBytes);
+    const int grid = std::min(tiles * plan.splits, sms);
+    if (tiled) {
+        tpb::nvfp4_gemm_kernel<true><<<grid, tpb::kThreads, smem, reinterpret_cast<cudaStream_t>(stream)>>>(P);
+    } else {
+        tpb::nvfp4_gemm_kernel<false><<<grid, tpb::kThreads, smem, reinterpret_cast<cudaStream_t>(stream)>>>(P);
+    }
     return tpb_launch_status();
 }
 

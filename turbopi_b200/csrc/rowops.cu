@@ -36,6 +36,7 @@ struct RowOpParams {
     uint8_t* sf;                   // swizzled scales of pieces * piece_rows rows
     float* row_scale;              // [M]
     int pieces, piece_rows, kb_pad;
+    int tiled;                     // packed = tiled A image of the GEMM: blocks [m / 128][k / 256] of pieces * 18 KB
 };
 
 __device__ __forceinline__ float block_sum(float v, float* red) {
@@ -167,16 +168,30 @@ __global__ void __launch_bounds__(kThreads) row_transform_quantize_kernel(const 
             for (int i = 0; i < 16; ++i) r[i] = row[kb * 16 + i] * pre;
         }
         for (int p = 0; p < P.pieces; ++p) {
-            const int prow = p * P.piece_rows + m;
-            const size_t sf_off = (static_cast<size_t>(prow >> 7) * (P.kb_pad >> 2) + (kb >> 2)) * 512 +
-                                  (prow & 31) * 16 + ((prow >> 5) & 3) * 4 + (kb & 3);
+            uint8_t* sf_dst;
+            uint8_t* code_dst;
+            if (P.tiled) {
+                // block (m / 128, kb / 16): [piece][128 rows][128 B, 16-byte chunks XOR-swizzled by row & 7],
+                // then [piece][4 atoms of 512 B]
+                const int rr = m & 127;
+                const int j = kb & 15;
+                uint8_t* blk = P.packed + (static_cast<size_t>(m >> 7) * (P.kb_pad >> 4) + (kb >> 4)) *
+                                              (static_cast<size_t>(P.pieces) * 18432);
+                code_dst = blk + p * 16384 + rr * 128 + ((((j >> 1) ^ (rr & 7))) << 4) + (j & 1) * 8;
+                sf_dst = blk + P.pieces * 16384 + p * 2048 + (j >> 2) * 512 + (rr & 31) * 16 + (rr >> 5) * 4 + (j & 3);
+            } else {
+                const int prow = p * P.piece_rows + m;
+                sf_dst = P.sf + (static_cast<size_t>(prow >> 7) * (P.kb_pad >> 2) + (kb >> 2)) * 512 +
+                         (prow & 31) * 16 + ((prow >> 5) & 3) * 4 + (kb & 3);
+                code_dst = P.packed + static_cast<size_t>(prow) * P.pitch + kb * 8;
+            }
             if (!valid) {
-                P.sf[sf_off] = 0;
+                *sf_dst = 0;
                 continue;
             }
             uint32_t lo, hi;
-            P.sf[sf_off] = quantize_block16_piece(r, lo, hi);
-            *reinterpret_cast<uint2*>(P.packed + static_cast<size_t>(prow) * P.pitch + kb * 8) = make_uint2(lo, hi);
+            *sf_dst = quantize_block16_piece(r, lo, hi);
+            *reinterpret_cast<uint2*>(code_dst) = make_uint2(lo, hi);
         }
     }
 }
@@ -194,7 +209,12 @@ extern "C" int tpb200_row_transform_quantize(const tpb200_rowop_args* a, tpb200_
         TPB_REQUIRE(a->w0 != nullptr && a->w1 != nullptr, TPB200_ERR_NULL);
     }
     TPB_REQUIRE(a->packed != nullptr || a->y_out != nullptr || a->h_out != nullptr, TPB200_ERR_NULL);
-    if (a->packed != nullptr) {
+    TPB_REQUIRE(a->layout == TPB200_OPERANDS_ROWMAJOR || a->layout == TPB200_OPERANDS_TILED, TPB200_ERR_ENUM);
+    if (a->packed != nullptr && a->layout == TPB200_OPERANDS_TILED) {
+        TPB_REQUIRE(a->row_scale != nullptr, TPB200_ERR_NULL);
+        TPB_REQUIRE(a->pieces >= 1 && a->pieces <= 3, TPB200_ERR_SHAPE);
+        TPB_REQUIRE(tpb_aligned16(a->packed), TPB200_ERR_ALIGN);
+    } else if (a->packed != nullptr) {
         TPB_REQUIRE(a->sf != nullptr && a->row_scale != nullptr, TPB200_ERR_NULL);
         TPB_REQUIRE(a->pieces >= 1 && a->pieces <= 4 && a->piece_rows >= a->M, TPB200_ERR_SHAPE);
         TPB_REQUIRE(a->pitch >= a->K / 2 && a->pitch % 16 == 0 && tpb_aligned16(a->packed) && tpb_aligned16(a->sf),
@@ -220,6 +240,7 @@ extern "C" int tpb200_row_transform_quantize(const tpb200_rowop_args* a, tpb200_
     P.pieces = a->pieces;
     P.piece_rows = a->piece_rows;
     P.kb_pad = (a->K + 255) / 256 * 16;
+    P.tiled = a->layout == TPB200_OPERANDS_TILED;
     const size_t smem = static_cast<size_t>(a->K) * sizeof(float);
     if (smem > 48 * 1024) {
         if (cudaFuncSetAttribute(tpb::row_transform_quantize_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,

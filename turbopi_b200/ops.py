@@ -298,14 +298,28 @@ def nvfp4_quantize_act_pieces(x, pieces=3):
     return packed, sf, row_scale, piece_rows
 
 
-def _gemm_ex(args, device):
+def gemm_workspace(device, nbytes=32 << 20):
+    """Zeroed split-K scratch for the tensor-core GEMM.  One buffer serves any number of launches that
+    run one after another on a stream; launches that may overlap need a buffer each."""
+    return torch.zeros(nbytes, dtype=torch.uint8, device=device)
+
+
+def nvfp4_gemm_workspace_size(M, N, K, pieces=1, layout=0):
+    return int(_lib.load().tpb200_nvfp4_gemm_workspace_size(M, N, K, pieces, layout))
+
+
+def _gemm_ex(args, device, workspace=None):
+    if workspace is not None:
+        _cuda(workspace)
+        args.workspace = _ptr(workspace)
+        args.workspace_bytes = workspace.numel() * workspace.element_size()
     with torch.cuda.device(device):
         st = _lib.load().tpb200_nvfp4_gemm_ex(ctypes.byref(args), torch.cuda.current_stream(device).cuda_stream)
     _lib.check(st, "tpb200_nvfp4_gemm_ex")
 
 
 def nvfp4_gemm_w4a16(x, b_packed, b_sf, N, alpha=1.0, bias=None, activation=ACT_NONE, pieces=3, out=None,
-                     out_dtype=torch.bfloat16):
+                     out_dtype=torch.bfloat16, workspace=None):
     """Weight-only semantics on the tensor-core path: out = act(alpha * x @ dequant(W)^T + bias) with the
     bf16 activations carried as `pieces` residual e2m1 operands (3 pieces keep ~bf16 precision)."""
     M, K = x.shape
@@ -319,7 +333,7 @@ def nvfp4_gemm_w4a16(x, b_packed, b_sf, N, alpha=1.0, bias=None, activation=ACT_
                          b_pitch=b_packed.stride(0), b_sf=_ptr(b_sf), alpha=float(alpha), bias=_ptr(bias),
                          activation=int(activation), out=_ptr(out), out_dtype=_dt(out), ldo=out.stride(0),
                          M=M, N=N, K=K)
-    _gemm_ex(args, x.device)
+    _gemm_ex(args, x.device, workspace)
     return out
 
 
@@ -347,7 +361,7 @@ def rope_tables(num_positions, head_dim=256, theta=10000.0, device="cuda"):
 
 
 def fused_qkv_rope_append(x, w_packed, w_sf, q_dim, k_rows, v_rows, positions, rope_cos, rope_sin, alpha=1.0,
-                          pieces=3, q_out=None):
+                          pieces=3, q_out=None, workspace=None):
     """q = RoPE(x Wq^T), cache K rows <- RoPE(x Wk^T), cache V rows <- x Wv^T in ONE kernel.
     x [M, H] bf16; w_packed / w_sf: tile-permuted stacked [Wq; Wk; Wv] (qkv_tile_permutation) in NVFP4;
     k_rows / v_rows: views of the cache whose row 0 is the first token's row, row stride 256 (bf16);
@@ -357,17 +371,100 @@ def fused_qkv_rope_append(x, w_packed, w_sf, q_dim, k_rows, v_rows, positions, r
     N = q_dim + 512
     if k_rows.stride(0) != 256 or v_rows.stride(0) != 256 or k_rows.dtype != torch.bfloat16:
         raise TurboPiError("cache rows must be bf16 with a row stride of 256 elements")
-    a, a_sf, row_scale, piece_rows = nvfp4_quantize_act_pieces(x, pieces)
     if q_out is None:
         q_out = torch.empty((M, q_dim), dtype=torch.bfloat16, device=x.device)
-    args = _lib.GemmArgs(a_packed=_ptr(a), a_pitch=a.stride(0), a_sf=_ptr(a_sf), a_pieces=pieces,
-                         a_piece_rows=piece_rows, a_row_scale=_ptr(row_scale), b_packed=_ptr(w_packed),
-                         b_pitch=w_packed.stride(0), b_sf=_ptr(w_sf), alpha=float(alpha), M=M, N=N, K=K,
-                         qkv_q_out=_ptr(q_out), qkv_ldq=q_out.stride(0), qkv_q_dim=q_dim, qkv_k_rows=_ptr(k_rows),
-                         qkv_v_rows=_ptr(v_rows), qkv_positions=_ptr(positions), qkv_rope_cos=_ptr(rope_cos),
-                         qkv_rope_sin=_ptr(rope_sin))
-    _gemm_ex(args, x.device)
+    if w_sf is None:
+        # w_packed is the tiled image of the permuted weight (tile_weights)
+        q = QuantBuf(M, K, pieces, x.device, tiled=True)
+        rowop(_lib.ROW_NONE, x.contiguous(), K, q)
+        args = _lib.GemmArgs(a_packed=_ptr(q.packed), a_pieces=pieces, a_row_scale=_ptr(q.row_scale),
+                             b_packed=_ptr(w_packed), layout=1)
+    else:
+        a, a_sf, row_scale, piece_rows = nvfp4_quantize_act_pieces(x, pieces)
+        args = _lib.GemmArgs(a_packed=_ptr(a), a_pitch=a.stride(0), a_sf=_ptr(a_sf), a_pieces=pieces,
+                             a_piece_rows=piece_rows, a_row_scale=_ptr(row_scale), b_packed=_ptr(w_packed),
+                             b_pitch=w_packed.stride(0), b_sf=_ptr(w_sf))
+    args.alpha, args.M, args.N, args.K = float(alpha), M, N, K
+    args.qkv_q_out, args.qkv_ldq, args.qkv_q_dim = _ptr(q_out), q_out.stride(0), q_dim
+    args.qkv_k_rows, args.qkv_v_rows, args.qkv_positions = _ptr(k_rows), _ptr(v_rows), _ptr(positions)
+    args.qkv_rope_cos, args.qkv_rope_sin = _ptr(rope_cos), _ptr(rope_sin)
+    _gemm_ex(args, x.device, workspace)
     return q_out
+
+
+# ------------------------------------------------------------------------- tiled operands for the GEMM
+OPERANDS_ROWMAJOR, OPERANDS_TILED = 0, 1
+
+
+def tile_weights(b_packed, b_sf, N, K):
+    """Row-major GEMM B operand (codes [N, pitch] + swizzled scales) -> the tiled image of the fast path:
+    blocks [ceil(N/256)][ceil(K/256)] of 36 KB that carry codes and scales of 256 rows for one K stage."""
+    _cuda(b_packed, b_sf)
+    image = torch.empty(int(_lib.load().tpb200_nvfp4_tiled_b_bytes(N, K)), dtype=torch.uint8, device=b_packed.device)
+    with torch.cuda.device(b_packed.device):
+        st = _lib.load().tpb200_nvfp4_tile_weights(_ptr(b_packed), b_packed.stride(0), _ptr(b_sf), _ptr(image), N, K,
+                                                   _stream(b_packed))
+    _lib.check(st, "tpb200_nvfp4_tile_weights")
+    return image
+
+
+class QuantBuf:
+    """Pre-allocated A operand of the GEMM for an [M, K] activation: residual pieces + scales + row
+    multipliers, as the tiled image (default) or the row-major operand.  Allocated zeroed: padding rows
+    and padding K keep zero scales because the quantiser never writes them."""
+
+    def __init__(self, M, K, pieces, device, tiled=True):
+        self.M, self.K, self.pieces, self.tiled = M, K, pieces, tiled
+        self.piece_rows = (M + 127) // 128 * 128
+        self.row_scale = torch.ones((M,), dtype=torch.float32, device=device)
+        if tiled:
+            self.pitch = 0
+            self.packed = torch.zeros(int(_lib.load().tpb200_nvfp4_tiled_a_bytes(M, K, pieces)), dtype=torch.uint8,
+                                      device=device)
+            self.sf = None
+        else:
+            self.pitch = packed_pitch(K)
+            self.packed = torch.zeros((pieces * self.piece_rows, self.pitch), dtype=torch.uint8, device=device)
+            self.sf = torch.zeros(nvfp4_sf_bytes(pieces * self.piece_rows, K), dtype=torch.uint8, device=device)
+
+    @property
+    def layout(self):
+        return OPERANDS_TILED if self.tiled else OPERANDS_ROWMAJOR
+
+
+def rowop(mode, x, K, q=None, res_in=None, gate=None, h_out=None, w0=None, w1=None, eps=1e-6, y_out=None, M=None):
+    """tpb200_row_transform_quantize: optional gated residual, a norm (or GELU(gate) * up), an optional
+    bf16 copy, and the residual-piece quantisation into `q` (a QuantBuf)."""
+    M = x.shape[0] if M is None else M
+    p = _ptr
+    a = _lib.RowOpArgs(mode=mode, M=M, K=K, x=p(x), ldx=x.stride(0), res_in=p(res_in), gate=p(gate), h_out=p(h_out),
+                       w0=p(w0), w1=p(w1), eps=float(eps), y_out=p(y_out),
+                       packed=p(q.packed) if q is not None else 0, pitch=q.pitch if q is not None else 0,
+                       sf=p(q.sf) if q is not None else 0, row_scale=p(q.row_scale) if q is not None else 0,
+                       pieces=q.pieces if q is not None else 0, piece_rows=q.piece_rows if q is not None else 0,
+                       layout=q.layout if q is not None else 0)
+    with torch.cuda.device(x.device):
+        st = _lib.load().tpb200_row_transform_quantize(ctypes.byref(a), torch.cuda.current_stream(x.device).cuda_stream)
+    _lib.check(st, "tpb200_row_transform_quantize")
+
+
+def nvfp4_gemm_w4a16_tiled(x, b_image, N, alpha=1.0, bias=None, activation=ACT_NONE, pieces=3, out=None,
+                           out_dtype=torch.bfloat16, workspace=None):
+    """nvfp4_gemm_w4a16 on the tiled operand images: x bf16 [M, K] is quantised straight into the A image
+    (tpb200_row_transform_quantize), b_image comes from tile_weights()."""
+    _cuda(x, b_image, bias, out)
+    M, K = x.shape
+    q = QuantBuf(M, K, pieces, x.device, tiled=True)
+    rowop(_lib.ROW_NONE, x.contiguous(), K, q)
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    if bias is not None:
+        bias = bias.float().contiguous()
+    args = _lib.GemmArgs(a_packed=_ptr(q.packed), a_pieces=pieces, a_row_scale=_ptr(q.row_scale),
+                         b_packed=_ptr(b_image), alpha=float(alpha), bias=_ptr(bias), activation=int(activation),
+                         out=_ptr(out), out_dtype=_dt(out), ldo=out.stride(0), M=M, N=N, K=K, layout=OPERANDS_TILED)
+    _gemm_ex(args, x.device, workspace)
+    return out
 
 
 # ------------------------------------------------------------------------------------- tensor-core GEMV

@@ -66,29 +66,7 @@ class Pi05Config:
         return self.heads * self.head_dim
 
 
-class QuantBuf:
-    """Pre-allocated A operand of the GEMM for an [M, K] activation: residual pieces + scales + row multipliers."""
-
-    def __init__(self, M, K, pieces, device):
-        self.M, self.K, self.pieces = M, K, pieces
-        self.piece_rows = (M + 127) // 128 * 128
-        self.pitch = ops.packed_pitch(K)
-        self.packed = torch.zeros((pieces * self.piece_rows, self.pitch), dtype=torch.uint8, device=device)
-        self.sf = torch.zeros(ops.nvfp4_sf_bytes(pieces * self.piece_rows, K), dtype=torch.uint8, device=device)
-        self.row_scale = torch.ones((M,), dtype=torch.float32, device=device)
-
-
-def rowop(mode, x, K, q=None, res_in=None, gate=None, h_out=None, w0=None, w1=None, eps=1e-6, y_out=None, M=None):
-    M = x.shape[0] if M is None else M
-    p = ops._ptr
-    a = _lib.RowOpArgs(mode=mode, M=M, K=K, x=p(x), ldx=x.stride(0), res_in=p(res_in), gate=p(gate), h_out=p(h_out),
-                       w0=p(w0), w1=p(w1), eps=float(eps), y_out=p(y_out),
-                       packed=p(q.packed) if q is not None else 0, pitch=q.pitch if q is not None else 0,
-                       sf=p(q.sf) if q is not None else 0, row_scale=p(q.row_scale) if q is not None else 0,
-                       pieces=q.pieces if q is not None else 0, piece_rows=q.piece_rows if q is not None else 0)
-    with torch.cuda.device(x.device):
-        st = _lib.load().tpb200_row_transform_quantize(ctypes.byref(a), torch.cuda.current_stream(x.device).cuda_stream)
-    _lib.check(st, "tpb200_row_transform_quantize")
+QuantBuf, rowop = ops.QuantBuf, ops.rowop
 
 
 class TcLinear:
@@ -106,30 +84,38 @@ class TcLinear:
         pitch = ops.packed_pitch(K)
         b = torch.zeros((N, pitch), dtype=torch.uint8, device=weight.device)
         b[:, :K // 2] = packed
-        self.b = b
-        self.b_sf = ops.swizzle_scales(scales.contiguous())
+        # the GEMM streams the tiled image; the row-major operand is only its source
+        self.b = ops.tile_weights(b, ops.swizzle_scales(scales.contiguous()), N, K)
         self.bias = None if bias is None else bias.float().contiguous()
+
+    # split-K scratch shared by every linear of a device (the model runs them one after another)
+    _workspaces = {}
+
+    @classmethod
+    def workspace(cls, device):
+        key = str(device)
+        if key not in cls._workspaces:
+            cls._workspaces[key] = ops.gemm_workspace(device)
+        return cls._workspaces[key]
 
     def __call__(self, q, out, activation=ACT_NONE, M=None):
         M = q.M if M is None else M
         p = ops._ptr
-        args = _lib.GemmArgs(a_packed=p(q.packed), a_pitch=q.pitch, a_sf=p(q.sf), a_pieces=q.pieces,
-                             a_piece_rows=q.piece_rows, a_row_scale=p(q.row_scale), b_packed=p(self.b),
-                             b_pitch=self.b.stride(0), b_sf=p(self.b_sf), alpha=float(self.g), bias=p(self.bias),
-                             activation=int(activation), out=p(out), out_dtype=ops._dt(out), ldo=out.stride(0),
-                             M=M, N=self.N, K=self.K)
-        ops._gemm_ex(args, out.device)
+        args = _lib.GemmArgs(a_packed=p(q.packed), a_pieces=q.pieces, a_row_scale=p(q.row_scale), b_packed=p(self.b),
+                             alpha=float(self.g), bias=p(self.bias), activation=int(activation), out=p(out),
+                             out_dtype=ops._dt(out), ldo=out.stride(0), M=M, N=self.N, K=self.K,
+                             layout=ops.OPERANDS_TILED)
+        ops._gemm_ex(args, out.device, self.workspace(out.device))
         return out
 
     def qkv(self, q, q_out, k_rows, v_rows, positions, cos, sin, q_dim, M=None):
         M = q.M if M is None else M
         p = ops._ptr
-        args = _lib.GemmArgs(a_packed=p(q.packed), a_pitch=q.pitch, a_sf=p(q.sf), a_pieces=q.pieces,
-                             a_piece_rows=q.piece_rows, a_row_scale=p(q.row_scale), b_packed=p(self.b),
-                             b_pitch=self.b.stride(0), b_sf=p(self.b_sf), alpha=float(self.g), M=M, N=self.N, K=self.K,
+        args = _lib.GemmArgs(a_packed=p(q.packed), a_pieces=q.pieces, a_row_scale=p(q.row_scale), b_packed=p(self.b),
+                             alpha=float(self.g), M=M, N=self.N, K=self.K, layout=ops.OPERANDS_TILED,
                              qkv_q_out=p(q_out), qkv_ldq=q_out.stride(0), qkv_q_dim=q_dim, qkv_k_rows=p(k_rows),
                              qkv_v_rows=p(v_rows), qkv_positions=p(positions), qkv_rope_cos=p(cos), qkv_rope_sin=p(sin))
-        ops._gemm_ex(args, q_out.device)
+        ops._gemm_ex(args, q_out.device, self.workspace(q_out.device))
         return q_out
 
 
