@@ -45,7 +45,11 @@ enum { TPB200_F32 = 0, TPB200_F16 = 1, TPB200_BF16 = 2 };
 
 /* fused activations; values match the reference's ActivationType
  * (openpi/nvfp4_packed_plugin/src/nvfp4_packed_plugin.h:44-48) */
-enum { TPB200_ACT_NONE = 0, TPB200_ACT_GELU = 1, TPB200_ACT_SILU = 2 };
+/* TPB200_ACT_GEGLU (tensor-core GEMM with tiled operands only): B stacks a gate and an up projection,
+ * every 256-row block = 128 gate rows followed by the 128 matching up rows; the output has N / 2
+ * columns, out[m, j] = bf16(gelu_tanh(bf16(gate_j))) * bf16(up_j)  (GemmaMLP,
+ * openpi/src/openpi/models_pytorch/transformers_replace/models/gemma/modeling_gemma.py:212-230). */
+enum { TPB200_ACT_NONE = 0, TPB200_ACT_GELU = 1, TPB200_ACT_SILU = 2, TPB200_ACT_GEGLU = 3 };
 
 /* block-scale encodings */
 enum { TPB200_SCALE_F32 = 0, TPB200_SCALE_E4M3 = 1, TPB200_SCALE_F16 = 2, TPB200_SCALE_BF16 = 3 };

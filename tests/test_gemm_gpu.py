@@ -346,3 +346,34 @@ def test_fused_qkv_tiled_matches_rowmajor(cuda_device):
             assert (a == c).float().mean().item() > 0.99
             assert (a - c).abs().max().item() <= 2 ** -7 * a.abs().max().item()
         assert (outs[1][1][:, :pos0] == -3.0).all() and (outs[1][1][:, pos0 + S:] == -3.0).all()
+
+
+@pytest.mark.parametrize("M,inter,K,split", [(712, 1024, 2048, False), (50, 512, 1024, True), (130, 384, 512, False)])
+def test_gated_gelu_epilogue_matches_module_arithmetic(cuda_device, M, inter, K, split):
+    """gate_up projection with GELU(gate) * up in the epilogue (tiled operands, 128 gate rows + 128 up rows
+    per weight block): out = bf16(bf16(gelu_tanh(bf16(x Wg^T))) * bf16(x Wu^T)), N / 2 columns."""
+    from turbopi_b200 import _lib, ops
+    rng = np.random.default_rng(51)
+    w = (rng.normal(size=(2 * inter, K)) * 0.03).astype(np.float32)
+    packed, sbytes, g = nvfp4.quantize_two_level(w, 16)
+    x = formats.round_to_bf16(rng.normal(size=(M, K)).astype(np.float32))
+    perm = ops.geglu_row_permutation(inter).numpy()
+    image = ops.tile_weights(_dev(_pack_padded(packed[perm], ops.packed_pitch(K)), cuda_device),
+                             _dev(nvfp4.swizzle_scales_128x4(sbytes[perm], 16), cuda_device), 2 * inter, K)
+    ws = ops.gemm_workspace(cuda_device) if split else None
+    if split:
+        assert ops.nvfp4_gemm_workspace_size(M, 2 * inter, K, 3, ops.OPERANDS_TILED) > 0
+    canvas = torch.full((M + 2, inter + 16), 7.0, dtype=torch.bfloat16, device=cuda_device)
+    out = canvas[1:M + 1, 8:8 + inter]
+    ops.nvfp4_gemm_w4a16_tiled(_dev(x, cuda_device, torch.bfloat16), image, 2 * inter, alpha=float(g),
+                               activation=_lib.ACT_GEGLU, out=out, workspace=ws)
+    assert _lib.load().tpb200_device_error(0) == 0
+    pre = nvfp4.gemv_dequant_matmul(x, packed, sbytes, None, 0, 16, float(g), True)
+    gate, up = formats.round_to_bf16(pre[:, :inter].astype(np.float32)), formats.round_to_bf16(pre[:, inter:].astype(np.float32))
+    act = formats.round_to_bf16((0.5 * gate * (1 + np.tanh(0.7978845608028654 * (gate + 0.044715 * gate ** 3)))).astype(np.float32))
+    ref = formats.round_to_bf16(act * up)
+    got = out.float().cpu().numpy()
+    assert rel_err(got, ref) <= 1e-2 and cosine(got, ref) >= 0.999
+    mask = torch.ones_like(canvas, dtype=torch.bool)
+    mask[1:M + 1, 8:8 + inter] = False
+    assert (canvas[mask] == 7.0).all()

@@ -10,7 +10,7 @@ from pathlib import Path
 LIB_PATH = Path(__file__).resolve().parent / "lib" / "libturbopi_b200.so"
 
 F32, F16, BF16 = 0, 1, 2
-ACT_NONE, ACT_GELU, ACT_SILU = 0, 1, 2
+ACT_NONE, ACT_GELU, ACT_SILU, ACT_GEGLU = 0, 1, 2, 3
 SCALE_F32, SCALE_E4M3, SCALE_F16, SCALE_BF16 = 0, 1, 2, 3
 INT4_KBLOCK, INT4_ROWMAJOR = 0, 1
 FLAG_NONE, FLAG_PDL = 0, 1

@@ -116,10 +116,9 @@ struct SharedControl {
 
 // epilogue activations with the hardware approximations (results are rounded to bf16 anyway)
 __device__ __forceinline__ float gelu_tanh_fast(float x) {
-    const float inner = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-    float t;
-    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(inner));
-    return 0.5f * x * (1.0f + t);
+    // 0.5 x (1 + tanh z) == x * sigmoid(2 z); this form has no cancellation for negative x
+    const float z2 = 1.5957691216057308f * (x + 0.044715f * x * x * x);
+    return __fdividef(x, 1.0f + __expf(-z2));
 }
 __device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
@@ -158,6 +157,18 @@ __device__ __forceinline__ void finish_plain32(float* v, float rs, const float* 
     } else if (activation == TPB200_ACT_SILU) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = silu_fast(v[i]);
+    }
+}
+
+// Gated GELU on 32 gate / up accumulator pairs, with the roundings of the module it replaces
+// (GemmaMLP: down(act(gate(x)) * up(x)) on bf16 tensors): both projections rounded to bf16, the
+// activation rounded to bf16, the product rounded by the store.
+__device__ __forceinline__ void finish_geglu32(float* g, const float* u, float rs) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        const float gb = __bfloat162float(__float2bfloat16_rn(g[i] * rs));
+        const float ub = __bfloat162float(__float2bfloat16_rn(u[i] * rs));
+        g[i] = __bfloat162float(__float2bfloat16_rn(gelu_tanh_fast(gb))) * ub;
     }
 }
 
@@ -438,17 +449,26 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
                     }
                 };
                 if (P.epilogue == kEpiPlain) {
-                    const int units = nrows * (kBN / 32);
+                    const bool geglu = kTiled && P.activation == TPB200_ACT_GEGLU;
+                    const int out_cols = geglu ? 128 : kBN;          // output columns of this tile
+                    const int n_out = geglu ? P.N >> 1 : P.N;
+                    const int units = nrows * (out_cols / 32);
                     for (int u = etid; u < units; u += 128) {
                         const int r = r0 + u % nrows;
                         const int c = u / nrows;
-                        const int n = n_blk * kBN + c * 32;
-                        if (n >= P.N) continue;
+                        const int n = n_blk * out_cols + c * 32;
+                        if (n >= n_out) continue;
                         const int mm = m_blk * kBM + r;
+                        const float rs_mm = P.row_scale != nullptr ? P.alpha * __ldg(P.row_scale + mm) : P.alpha;
                         float v[32];
                         sum32(r, c * 32, v);
-                        finish_plain32(v, P.row_scale != nullptr ? P.alpha * __ldg(P.row_scale + mm) : P.alpha, P.bias, n,
-                                       P.N, P.activation);
+                        if (geglu) {
+                            float up[32];
+                            sum32(r, 128 + c * 32, up);
+                            finish_geglu32(v, up, rs_mm);
+                        } else {
+                            finish_plain32(v, rs_mm, P.bias, n, P.N, P.activation);
+                        }
                         if (P.out_dtype == TPB200_BF16) {
                             uint32_t pk[16];
                             pack_bf16x32(v, pk);
@@ -456,14 +476,14 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
                                                                   static_cast<size_t>(mm) * P.ldo + n);
 #pragma unroll
                             for (int g = 0; g < 4; ++g) {
-                                if (n + 8 * g < P.N) dst[g] = make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
+                                if (n + 8 * g < n_out) dst[g] = make_uint4(pk[4 * g], pk[4 * g + 1], pk[4 * g + 2], pk[4 * g + 3]);
                             }
                         } else {
                             float4* dst = reinterpret_cast<float4*>(static_cast<float*>(P.out) +
                                                                     static_cast<size_t>(mm) * P.ldo + n);
 #pragma unroll
                             for (int g = 0; g < 8; ++g) {
-                                if (n + 4 * g < P.N) dst[g] = make_float4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+                                if (n + 4 * g < n_out) dst[g] = make_float4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
                             }
                         }
                     }
@@ -512,14 +532,19 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
 
             if (P.epilogue == kEpiPlain) {
                 // boxes of 128 bytes per row: 64 bf16 or 32 fp32 columns
+                // gated GELU (tiled form): tile columns [0, 128) are gate outputs, [128, 256) the matching
+                // up outputs; the tile yields 128 output columns
+                const bool geglu = kTiled && P.activation == TPB200_ACT_GEGLU;
+                const int out_cols = geglu ? 128 : kBN;
+                const int n_out = geglu ? P.N >> 1 : P.N;
                 const int cols_per_box = P.out_dtype == TPB200_BF16 ? 64 : 32;
-                const int nboxes = kBN / cols_per_box;
+                const int nboxes = out_cols / cols_per_box;
 #pragma unroll 1
                 for (int bx = 0; bx < nboxes; ++bx, ++nstore) {
                     uint8_t* ob = out_stage + (nstore & 1) * kOutBuf;
                     if (issuer) bulk_wait_group_read<1>();    // the store that last used this buffer has read it
                     epilogue_barrier();
-                    const int n0 = n_blk * kBN + bx * cols_per_box;
+                    const int n0 = n_blk * out_cols + bx * cols_per_box;
 #pragma unroll 1
                     for (int c = 0; c < cols_per_box / 32; ++c) {
                         uint32_t raw[32];
@@ -528,7 +553,16 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
                         float v[32];
 #pragma unroll
                         for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[i]);
-                        finish_plain32(v, rs, P.bias, n0 + c * 32, P.N, P.activation);
+                        if (geglu) {
+                            tc::tmem_ld_32x32b_x32(taddr + 128 + bx * cols_per_box + c * 32, raw);
+                            tc::tmem_ld_wait();
+                            float up[32];
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) up[i] = __uint_as_float(raw[i]);
+                            finish_geglu32(v, up, rs);
+                        } else {
+                            finish_plain32(v, rs, P.bias, n0 + c * 32, P.N, P.activation);
+                        }
                         if (P.out_dtype == TPB200_BF16) {
                             uint32_t pk[16];
                             pack_bf16x32(v, pk);
@@ -554,7 +588,7 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
                     fence_proxy_async_smem();
                     epilogue_barrier();
                     if (issuer) {
-                        if (n0 < P.N) tma_store_2d(&P.map_out, ob, n0, m_blk * kBM);
+                        if (n0 < n_out) tma_store_2d(&P.map_out, ob, n0, m_blk * kBM);
                         bulk_commit_group();
                     }
                 }
@@ -979,7 +1013,13 @@ extern "C" int tpb200_nvfp4_gemm_ex(const tpb200_nvfp4_gemm_args* a, tpb200_stre
     const bool tiled = a->layout == TPB200_OPERANDS_TILED;
     TPB_REQUIRE(a->a_packed && a->b_packed, TPB200_ERR_NULL);
     TPB_REQUIRE(M >= 1 && N >= 8 && N % 8 == 0 && K >= 16 && K % 16 == 0, TPB200_ERR_SHAPE);
-    TPB_REQUIRE(a->activation >= TPB200_ACT_NONE && a->activation <= TPB200_ACT_SILU, TPB200_ERR_ENUM);
+    TPB_REQUIRE(a->activation >= TPB200_ACT_NONE && a->activation <= TPB200_ACT_GEGLU, TPB200_ERR_ENUM);
+    const bool geglu = a->activation == TPB200_ACT_GEGLU;
+    if (geglu) {
+        TPB_REQUIRE(a->layout == TPB200_OPERANDS_TILED && a->qkv_q_out == nullptr && a->bias == nullptr, TPB200_ERR_ENUM);
+        TPB_REQUIRE(N % 256 == 0, TPB200_ERR_SHAPE);
+    }
+    const int n_out = geglu ? N / 2 : N;
     const int pieces = a->a_pieces <= 0 ? 1 : a->a_pieces;
     TPB_REQUIRE(tpb_aligned16(a->a_packed) && tpb_aligned16(a->b_packed), TPB200_ERR_ALIGN);
     if (tiled) {
@@ -1004,7 +1044,7 @@ extern "C" int tpb200_nvfp4_gemm_ex(const tpb200_nvfp4_gemm_args* a, tpb200_stre
     } else {
         TPB_REQUIRE(a->out != nullptr, TPB200_ERR_NULL);
         TPB_REQUIRE(a->out_dtype == TPB200_BF16 || a->out_dtype == TPB200_F32, TPB200_ERR_ENUM);
-        TPB_REQUIRE(a->ldo >= N, TPB200_ERR_SHAPE);
+        TPB_REQUIRE(a->ldo >= n_out, TPB200_ERR_SHAPE);
         TPB_REQUIRE(tpb_aligned16(a->out) && (static_cast<long long>(a->ldo) * tpb_dtype_size(a->out_dtype)) % 16 == 0,
                     TPB200_ERR_ALIGN);
     }
@@ -1027,7 +1067,7 @@ extern "C" int tpb200_nvfp4_gemm_ex(const tpb200_nvfp4_gemm_args* a, tpb200_stre
             return TPB200_ERR_CUDA;
         }
     } else {
-        if (!tpb::make_tensor_map_out_sw128(&P.map_out, a->out, a->out_dtype, N, M,
+        if (!tpb::make_tensor_map_out_sw128(&P.map_out, a->out, a->out_dtype, n_out, M,
                                             static_cast<uint64_t>(a->ldo) * tpb_dtype_size(a->out_dtype))) {
             return TPB200_ERR_CUDA;
         }

@@ -7,13 +7,15 @@
 // 212-230), and writes the result straight in the GEMM's operand format: residual e2m1 pieces +
 // UE4M3 block scales + the per-row power-of-two multiplier (see nvfp4_gemm.cu).  A bf16 copy of
 // the transformed row and the updated residual stream are written only when asked for.
-// One CTA per row; the transformed row is staged in shared memory (K <= 16384).
+// One CTA per row; every thread keeps its 16-element blocks in registers (K <= 16384).
+#include <algorithm>
+
 #include "common.cuh"
 
 namespace tpb {
 namespace {
 
-constexpr int kThreads = 256;
+constexpr int kThreads = 1024;   // one 16-element block per thread: K <= 16384
 constexpr int kMaxK = 16384;
 
 struct RowOpParams {
@@ -39,6 +41,7 @@ struct RowOpParams {
     int tiled;                     // packed = tiled A image of the GEMM: blocks [m / 128][k / 256] of pieces * 18 KB
 };
 
+// Block-wide reductions for any multiple of 32 threads up to 256.
 __device__ __forceinline__ float block_sum(float v, float* red) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -46,8 +49,7 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
     __syncthreads();
     float t = 0.0f;
-#pragma unroll
-    for (int i = 0; i < kThreads / 32; ++i) t += red[i];
+    for (int i = 0; i < (blockDim.x >> 5); ++i) t += red[i];
     return t;
 }
 
@@ -58,98 +60,167 @@ __device__ __forceinline__ float block_max(float v, float* red) {
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
     __syncthreads();
     float t = 0.0f;
-#pragma unroll
-    for (int i = 0; i < kThreads / 32; ++i) t = fmaxf(t, red[i]);
+    for (int i = 0; i < (blockDim.x >> 5); ++i) t = fmaxf(t, red[i]);
     return t;
 }
 
 __device__ __forceinline__ float bf16r(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
+// GELU (tanh form) as x * sigmoid(2 z), z = sqrt(2/pi) (x + 0.044715 x^3): the same function as
+// 0.5 x (1 + tanh z) without the cancellation in 1 + tanh z for negative x, so the hardware exp and
+// divide keep ~1e-6 relative accuracy everywhere.
+__device__ __forceinline__ float gelu_tanh_hw(float x) {
+    const float z2 = 1.5957691216057308f * (x + 0.044715f * x * x * x);
+    return __fdividef(x, 1.0f + __expf(-z2));
+}
+
+__device__ __forceinline__ void load16_bf16(const __nv_bfloat16* p, float (&v)[16]) {
+    const uint4* q = reinterpret_cast<const uint4*>(p);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const uint4 u = __ldg(q + i);
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
+            v[8 * i + 2 * j] = f.x;
+            v[8 * i + 2 * j + 1] = f.y;
+        }
+    }
+}
+
+__device__ __forceinline__ void store16_bf16(__nv_bfloat16* p, const float (&v)[16]) {
+    uint32_t w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        __nv_bfloat162 b = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        w[i] = *reinterpret_cast<uint32_t*>(&b);
+    }
+    uint4* q = reinterpret_cast<uint4*>(p);
+    q[0] = make_uint4(w[0], w[1], w[2], w[3]);
+    q[1] = make_uint4(w[4], w[5], w[6], w[7]);
+}
+
+// One CTA per row, one thread per 16-element block (32 .. 1024 threads): the block stays in registers
+// from the global load to the code store; the only shared memory is the scratch of the block-wide
+// reductions.
 __global__ void __launch_bounds__(kThreads) row_transform_quantize_kernel(const __grid_constant__ RowOpParams P) {
-    extern __shared__ __align__(16) uint8_t smem[];
-    float* row = reinterpret_cast<float*>(smem);            // K floats: the row being transformed
+    constexpr int NB = 1;
     __shared__ float red[kThreads / 32];
     const int m = blockIdx.x;
     const int K = P.K;
+    const int T = blockDim.x;
     const int tid = threadIdx.x;
+    const int nblk = K >> 4;
+    float v[NB][16];
 
     // ---- load (+ residual) ------------------------------------------------------------------
-    if (P.mode == TPB200_ROW_GELU_MUL) {
-        const __nv_bfloat16* g = P.x + static_cast<size_t>(m) * P.ldx;
-        const __nv_bfloat16* u = g + K;
-        for (int k = tid * 2; k < K; k += kThreads * 2) {
-            const float2 gv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(g + k));
-            const float2 uv = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(u + k));
-            row[k] = bf16r(bf16r(gelu_tanh(gv.x)) * uv.x);
-            row[k + 1] = bf16r(bf16r(gelu_tanh(gv.y)) * uv.y);
+#pragma unroll
+    for (int j = 0; j < NB; ++j) {
+        const int kb = tid + j * T;
+        if (kb >= nblk) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[j][i] = 0.0f;
+            continue;
         }
-    } else {
-        const __nv_bfloat16* xr = P.x + static_cast<size_t>(m) * P.ldx;
-        for (int k = tid * 2; k < K; k += kThreads * 2) {
-            float2 v = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(xr + k));
+        const int k = kb << 4;
+        if (P.mode == TPB200_ROW_GELU_MUL) {
+            float g[16], u[16];
+            load16_bf16(P.x + static_cast<size_t>(m) * P.ldx + k, g);
+            load16_bf16(P.x + static_cast<size_t>(m) * P.ldx + K + k, u);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[j][i] = bf16r(bf16r(gelu_tanh_hw(g[i])) * u[i]);
+        } else {
+            load16_bf16(P.x + static_cast<size_t>(m) * P.ldx + k, v[j]);
             if (P.res_in != nullptr) {
-                const float2 h = __bfloat1622float2(
-                    *reinterpret_cast<const __nv_bfloat162*>(P.res_in + static_cast<size_t>(m) * K + k));
+                float h[16];
+                load16_bf16(P.res_in + static_cast<size_t>(m) * K + k, h);
                 if (P.gate != nullptr) {
-                    const float2 gt = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(P.gate + k));
-                    v.x = bf16r(v.x * gt.x);
-                    v.y = bf16r(v.y * gt.y);
+                    float gt[16];
+                    load16_bf16(P.gate + k, gt);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) v[j][i] = bf16r(v[j][i] * gt[i]);
                 }
-                v.x = bf16r(h.x + v.x);
-                v.y = bf16r(h.y + v.y);
-                if (P.h_out != nullptr) {
-                    *reinterpret_cast<__nv_bfloat162*>(P.h_out + static_cast<size_t>(m) * K + k) =
-                        __floats2bfloat162_rn(v.x, v.y);
-                }
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[j][i] = bf16r(h[i] + v[j][i]);
+                if (P.h_out != nullptr) store16_bf16(P.h_out + static_cast<size_t>(m) * K + k, v[j]);
             }
-            row[k] = v.x;
-            row[k + 1] = v.y;
         }
     }
-    __syncthreads();
 
     // ---- normalise ---------------------------------------------------------------------------
     if (P.mode == TPB200_ROW_RMSNORM || P.mode == TPB200_ROW_ADARMS) {
         float ss = 0.0f;
-        for (int k = tid; k < K; k += kThreads) ss += row[k] * row[k];
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) ss += v[j][i] * v[j][i];
+        }
         ss = block_sum(ss, red);
         const float r = rsqrtf(ss / static_cast<float>(K) + P.eps);
-        for (int k = tid; k < K; k += kThreads) {
-            float v = row[k] * r;
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+            const int kb = tid + j * T;
+            if (kb >= nblk) continue;
+            float w0[16];
+            load16_bf16(P.w0 + (kb << 4), w0);
             if (P.mode == TPB200_ROW_RMSNORM) {
-                v = v * (1.0f + __bfloat162float(P.w0[k]));
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[j][i] = bf16r(v[j][i] * r * (1.0f + w0[i]));
             } else {
-                v = v * (1.0f + __bfloat162float(P.w0[k])) + __bfloat162float(P.w1[k]);
+                float w1[16];
+                load16_bf16(P.w1 + (kb << 4), w1);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[j][i] = bf16r(v[j][i] * r * (1.0f + w0[i]) + w1[i]);
             }
-            row[k] = bf16r(v);
         }
     } else if (P.mode == TPB200_ROW_LAYERNORM) {
-        float s = 0.0f;
-        for (int k = tid; k < K; k += kThreads) s += row[k];
-        const float mean = block_sum(s, red) / static_cast<float>(K);
+        float sm = 0.0f;
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) sm += v[j][i];
+        }
+        const float mean = block_sum(sm, red) / static_cast<float>(K);
         float ss = 0.0f;
-        for (int k = tid; k < K; k += kThreads) {
-            const float d = row[k] - mean;
-            ss += d * d;
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+            if (tid + j * T >= nblk) continue;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const float d = v[j][i] - mean;
+                ss += d * d;
+            }
         }
         const float r = rsqrtf(block_sum(ss, red) / static_cast<float>(K) + P.eps);
-        for (int k = tid; k < K; k += kThreads) {
-            row[k] = bf16r((row[k] - mean) * r * __bfloat162float(P.w0[k]) + __bfloat162float(P.w1[k]));
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+            const int kb = tid + j * T;
+            if (kb >= nblk) continue;
+            float w0[16], w1[16];
+            load16_bf16(P.w0 + (kb << 4), w0);
+            load16_bf16(P.w1 + (kb << 4), w1);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[j][i] = bf16r((v[j][i] - mean) * r * w0[i] + w1[i]);
         }
     }
-    __syncthreads();
 
     if (P.y_out != nullptr) {
-        for (int k = tid * 2; k < K; k += kThreads * 2) {
-            *reinterpret_cast<__nv_bfloat162*>(P.y_out + static_cast<size_t>(m) * K + k) =
-                __floats2bfloat162_rn(row[k], row[k + 1]);
+#pragma unroll
+        for (int j = 0; j < NB; ++j) {
+            const int kb = tid + j * T;
+            if (kb < nblk) store16_bf16(P.y_out + static_cast<size_t>(m) * K + (kb << 4), v[j]);
         }
     }
     if (P.packed == nullptr) return;
 
     // ---- residual-piece quantisation (same arithmetic as nvfp4_quantize_pieces_kernel) --------
     float amax = 0.0f;
-    for (int k = tid; k < K; k += kThreads) amax = fmaxf(amax, fabsf(row[k]));
+#pragma unroll
+    for (int j = 0; j < NB; ++j) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[j][i]));
+    }
     amax = block_max(amax, red);
     int e = 0;
     if (amax > 0.0f && amax < 3.0e38f) {
@@ -159,14 +230,13 @@ __global__ void __launch_bounds__(kThreads) row_transform_quantize_kernel(const 
     }
     const float pre = ldexpf(1.0f, e);
     if (tid == 0) P.row_scale[m] = ldexpf(1.0f, -e);
-    const int nblk = K >> 4;
-    for (int kb = tid; kb < P.kb_pad; kb += kThreads) {
-        float r[16];
-        const bool valid = kb < nblk;
-        if (valid) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) r[i] = row[kb * 16 + i] * pre;
-        }
+    for (int j = 0; j < NB; ++j) {
+        const int kb = tid + j * T;
+        if (kb >= P.kb_pad) continue;
+        const bool valid = kb < nblk;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[j][i] *= pre;
         for (int p = 0; p < P.pieces; ++p) {
             uint8_t* sf_dst;
             uint8_t* code_dst;
@@ -174,11 +244,11 @@ __global__ void __launch_bounds__(kThreads) row_transform_quantize_kernel(const 
                 // block (m / 128, kb / 16): [piece][128 rows][128 B, 16-byte chunks XOR-swizzled by row & 7],
                 // then [piece][4 atoms of 512 B]
                 const int rr = m & 127;
-                const int j = kb & 15;
+                const int jj = kb & 15;
                 uint8_t* blk = P.packed + (static_cast<size_t>(m >> 7) * (P.kb_pad >> 4) + (kb >> 4)) *
                                               (static_cast<size_t>(P.pieces) * 18432);
-                code_dst = blk + p * 16384 + rr * 128 + ((((j >> 1) ^ (rr & 7))) << 4) + (j & 1) * 8;
-                sf_dst = blk + P.pieces * 16384 + p * 2048 + (j >> 2) * 512 + (rr & 31) * 16 + (rr >> 5) * 4 + (j & 3);
+                code_dst = blk + p * 16384 + rr * 128 + ((((jj >> 1) ^ (rr & 7))) << 4) + (jj & 1) * 8;
+                sf_dst = blk + P.pieces * 16384 + p * 2048 + (jj >> 2) * 512 + (rr & 31) * 16 + (rr >> 5) * 4 + (jj & 3);
             } else {
                 const int prow = p * P.piece_rows + m;
                 sf_dst = P.sf + (static_cast<size_t>(prow >> 7) * (P.kb_pad >> 2) + (kb >> 2)) * 512 +
@@ -190,7 +260,7 @@ __global__ void __launch_bounds__(kThreads) row_transform_quantize_kernel(const 
                 continue;
             }
             uint32_t lo, hi;
-            *sf_dst = quantize_block16_piece(r, lo, hi);
+            *sf_dst = quantize_block16_piece(v[j], lo, hi);
             *reinterpret_cast<uint2*>(code_dst) = make_uint2(lo, hi);
         }
     }
@@ -203,7 +273,10 @@ extern "C" int tpb200_row_transform_quantize(const tpb200_rowop_args* a, tpb200_
     TPB_REQUIRE(a != nullptr && a->x != nullptr, TPB200_ERR_NULL);
     TPB_REQUIRE(a->mode >= TPB200_ROW_NONE && a->mode <= TPB200_ROW_GELU_MUL, TPB200_ERR_ENUM);
     TPB_REQUIRE(a->M >= 1 && a->K >= 16 && a->K % 16 == 0 && a->K <= tpb::kMaxK, TPB200_ERR_SHAPE);
-    TPB_REQUIRE(a->ldx >= (a->mode == TPB200_ROW_GELU_MUL ? 2 * a->K : a->K) && a->ldx % 2 == 0, TPB200_ERR_SHAPE);
+    TPB_REQUIRE(a->ldx >= (a->mode == TPB200_ROW_GELU_MUL ? 2 * a->K : a->K) && a->ldx % 8 == 0, TPB200_ERR_SHAPE);
+    TPB_REQUIRE(tpb_aligned16(a->x) && tpb_aligned16(a->res_in) && tpb_aligned16(a->gate) && tpb_aligned16(a->h_out) &&
+                    tpb_aligned16(a->w0) && tpb_aligned16(a->w1) && tpb_aligned16(a->y_out),
+                TPB200_ERR_ALIGN);
     if (a->mode == TPB200_ROW_RMSNORM) TPB_REQUIRE(a->w0 != nullptr, TPB200_ERR_NULL);
     if (a->mode == TPB200_ROW_ADARMS || a->mode == TPB200_ROW_LAYERNORM) {
         TPB_REQUIRE(a->w0 != nullptr && a->w1 != nullptr, TPB200_ERR_NULL);
@@ -241,13 +314,7 @@ extern "C" int tpb200_row_transform_quantize(const tpb200_rowop_args* a, tpb200_
     P.piece_rows = a->piece_rows;
     P.kb_pad = (a->K + 255) / 256 * 16;
     P.tiled = a->layout == TPB200_OPERANDS_TILED;
-    const size_t smem = static_cast<size_t>(a->K) * sizeof(float);
-    if (smem > 48 * 1024) {
-        if (cudaFuncSetAttribute(tpb::row_transform_quantize_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 tpb::kMaxK * static_cast<int>(sizeof(float))) != cudaSuccess) {
-            return TPB200_ERR_CUDA;
-        }
-    }
-    tpb::row_transform_quantize_kernel<<<a->M, tpb::kThreads, smem, reinterpret_cast<cudaStream_t>(stream)>>>(P);
+    const int threads = std::min(tpb::kThreads, (P.kb_pad + 31) / 32 * 32);
+    tpb::row_transform_quantize_kernel<<<a->M, threads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(P);
     return tpb_launch_status();
 }

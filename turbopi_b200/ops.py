@@ -351,6 +351,17 @@ def qkv_tile_permutation(q_dim, head_dim=256):
     return torch.tensor(idx, dtype=torch.long)
 
 
+def geglu_row_permutation(inter):
+    """Row order of a stacked [W_gate; W_up] ([2 * inter, K]) for the gated-GELU epilogue: every 256-row
+    block holds 128 gate rows followed by the 128 matching up rows."""
+    if inter % 128:
+        raise TurboPiError("the gated-GELU epilogue needs an intermediate size that is a multiple of 128")
+    t = torch.arange(inter // 128)[:, None, None] * 128
+    r = torch.arange(128)[None, None, :]
+    half = torch.tensor([0, inter])[None, :, None]
+    return (t + half + r).reshape(-1)
+
+
 def rope_tables(num_positions, head_dim=256, theta=10000.0, device="cuda"):
     """cos / sin tables [positions, head_dim / 2] in bf16, computed the way the model does:
     inv_freq in fp32 rounded to bf16, pos * inv_freq in fp32, cos / sin rounded to bf16."""
@@ -457,7 +468,7 @@ def nvfp4_gemm_w4a16_tiled(x, b_image, N, alpha=1.0, bias=None, activation=ACT_N
     q = QuantBuf(M, K, pieces, x.device, tiled=True)
     rowop(_lib.ROW_NONE, x.contiguous(), K, q)
     if out is None:
-        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        out = torch.empty((M, N // 2 if activation == _lib.ACT_GEGLU else N), dtype=out_dtype, device=x.device)
     if bias is not None:
         bias = bias.float().contiguous()
     args = _lib.GemmArgs(a_packed=_ptr(q.packed), a_pieces=pieces, a_row_scale=_ptr(q.row_scale),

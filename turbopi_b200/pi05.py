@@ -290,6 +290,8 @@ class Pi05:
             L["o"](b["q_pattn"], b["py"])
             rowop(_lib.ROW_RMSNORM, b["py"], c.width, b["q_p"], res_in=b["ph"], h_out=b["ph"], w0=L["post_norm"],
                   eps=c.eps)
+            # GELU(gate) * up rides in the row kernel: in the GEMM's epilogue (ACT_GEGLU) it would sit between
+            # the accumulator reads of a 128 x 256 tile and hold up the next tile's MMAs
             L["gate_up"](b["q_p"], b["p_gu"])
             rowop(_lib.ROW_GELU_MUL, b["p_gu"], c.mlp, b["q_pmlp"])
             L["down"](b["q_pmlp"], b["py"])
