@@ -419,6 +419,54 @@ def run_extras(device, sets, x):
         pk, sf = ops.nvfp4_quantize_act(xq)
         t = time_launches(lambda i: ops.nvfp4_quantize_act(xq, pk, sf), 16)
         ex[f"nvfp4_quantize_act_{M}x{K}"] = {"us": t * 1e6, "gbps": (M * K * 2 + M * K // 2 + M * K // 16) / t / 1e9}
+    # (g) the model's linears as they run in the pipeline: bf16 activations -> 3 residual e2m1 pieces in the
+    # tiled A image (row kernel), NVFP4 weights as tiled images, 128 x 256 output tiles (benchmark config 4
+    # with weight-only semantics; `tflops` counts the useful 2 M N K once, not the 3 pieces)
+    from turbopi_b200 import _lib as tlib
+    from turbopi_b200.pi05 import TcLinear
+    for (M, N, K, name) in ((712, 32768, 2048, "gemma2b_gate_up_M712"), (712, 2048, 16384, "gemma2b_down_M712"),
+                            (712, 2560, 2048, "gemma2b_qkv_M712"), (512, 4304, 1152, "siglip_fc1_M512"),
+                            (512, 1152, 4304, "siglip_fc2_M512"), (50, 8192, 1024, "expert_gate_up_M50"),
+                            (50, 1024, 4096, "expert_down_M50")):
+        q = ops.QuantBuf(M, K, 3, device)
+        xq = torch.randn(M, K, device=device).to(torch.bfloat16)
+        lins = [TcLinear(torch.randn(N, K, device=device) * 0.02) for _ in range(2)]
+        o = torch.empty((M, N), dtype=torch.bfloat16, device=device)
+        ops.rowop(tlib.ROW_NONE, xq, K, q)
+        t = time_launches(lambda i: lins[i % 2](q, o), 16)
+        tq = time_launches(lambda i: ops.rowop(tlib.ROW_NONE, xq, K, q), 16)
+        ex[f"w4a16_tc_linear_{name}"] = {"gemm_us": t * 1e6, "quantise_us": tq * 1e6,
+                                         "tflops": 2.0 * M * N * K / t / 1e12,
+                                         "tensor_tflops": 3 * 2.0 * M * N * K / t / 1e12}
+        del lins
+    # (h) the whole Pi0.5-shaped inference (SigLIP-So400m/14 on 2 images, 712-token Gemma-2B prefix with the
+    # fused QKV + RoPE + KV-cache append, Gemma-300M action expert, Euler steps) as ONE CUDA graph:
+    # pinned host images / tokens / noise in, actions back on the host, random-init weights
+    from turbopi_b200.pi05 import Pi05, Pi05Config
+    cfg = Pi05Config()
+    model = Pi05(cfg, device, seed=0)
+    gen = torch.Generator().manual_seed(1)
+    images = torch.randint(0, 256, (cfg.num_images, cfg.image_size, cfg.image_size, 3), generator=gen,
+                           dtype=torch.uint8).pin_memory()
+    tokens = torch.randint(0, cfg.vocab, (cfg.text_len,), generator=gen).pin_memory()
+    noise = torch.randn(cfg.action_horizon, cfg.action_dim, generator=gen).pin_memory()
+    host_out = torch.empty(cfg.action_horizon, cfg.action_dim).pin_memory()
+    for steps in (1, 3, 10):
+        with torch.no_grad():
+            model.infer(images, tokens, noise, steps)          # captures the graph for this step count
+            torch.cuda.synchronize()
+            ts = []
+            for _ in range(10):
+                t0 = time.perf_counter()
+                host_out.copy_(model.infer(images, tokens, noise, steps), non_blocking=True)
+                torch.cuda.synchronize()
+                ts.append((time.perf_counter() - t0) * 1e3)
+        ts.sort()
+        ex[f"pi05_e2e_{steps}_steps"] = {"ms_median": ts[len(ts) // 2], "ms_best": ts[0], "hz": 1e3 / ts[len(ts) // 2],
+                                         "finite": bool(torch.isfinite(host_out).all())}
+    ex["pi05_e2e_note"] = ("host wall clock around H2D inputs + one graph replay + D2H actions; reference on Jetson Thor "
+                           "(its published figures, other hardware): 83.5 ms / 1 step, 102.8 ms / 3 steps, 171.4 ms / 10 steps")
+    del model
     return ex
 
 
