@@ -192,26 +192,33 @@ int tpb200_nvfp4_quantize_act_pieces(const void* x, int x_dtype, int ldx, void* 
 
 /* ---------------------------------------------------------------------------------------------
  * NVFP4 weight-only GEMV for decode shapes (M <= 16) on the tensor cores: same result as
- * tpb200_nvfp4_gemv (E4M3 block-16 scales + global scale), no per-weight work on the SM.  Weights are
- * given PRE-TILED: [row tile of 128][K stage of 256][128 rows][128 B] with the 16-byte chunk c of row r
- * stored at chunk c ^ (r & 7) (N padded to 128, K to 256 with zero codes), scales in the GEMM's atom
- * layout.  Activations are first turned into `pieces` residual e2m1 operands in the same tiled image by
- * tpb200_nvfp4_quantize_act_tc (x_tiled: ceil(K/256) * 16*pieces*128 bytes, x_sf: ceil(K/256) * 2048
- * bytes, x_row_scale: 16 floats).  Row tiles whose K range is split across CTAs are combined through
- * `workspace` (size from tpb200_nvfp4_gemv_tc_workspace_size; the caller zeroes it ONCE after
- * allocation, the kernel leaves its counters at zero).  Launches that share a workspace must not
- * overlap.  No counterpart in the reference (its GEMVs are CUDA-core kernels).
+ * tpb200_nvfp4_gemv (E4M3 block-16 scales + global scale), no per-weight work on the SM.
+ * w_image is the tensor-core GEMM's tiled B image (tpb200_nvfp4_tile_weights; blocks
+ * [ceil(N/256)][ceil(K/256)] of 36864 bytes), so one copy of a weight serves prefill and decode.
+ * Activations are first turned into `pieces` residual e2m1 operands by tpb200_nvfp4_quantize_act_tc:
+ * x_image = ceil(K/256) blocks of 16*pieces*128 code bytes (row 16 p + t = piece p of token t, 16-byte
+ * chunk c of row r at c ^ (r & 7)) followed by their 2048-byte scale slab
+ * (tpb200_nvfp4_gemv_tc_x_image_bytes), x_row_scale: 16 floats.  Row tiles whose K range is split
+ * across CTAs are combined through `workspace` (size from tpb200_nvfp4_gemv_tc_workspace_size; the
+ * caller zeroes it ONCE after allocation, the kernel leaves its counters at zero).  Launches that share
+ * a workspace must not overlap.  No counterpart in the reference (its GEMVs are CUDA-core kernels).
  * ------------------------------------------------------------------------------------------- */
 typedef struct {
-    const void* w_tiled; const void* w_sf;
-    const void* x_tiled; const void* x_sf; const float* x_row_scale;
+    const void* w_image;
+    const void* x_image; const float* x_row_scale;
     const void* bias; void* out;
     int N; int K; int ldo; /* 0 = N */
     float global_scale;
 } tpb200_gemv_tc_problem;
 size_t tpb200_nvfp4_gemv_tc_workspace_size(const tpb200_gemv_tc_problem* problems, int count);
-int tpb200_nvfp4_quantize_act_tc(const void* x, int x_dtype, int ldx, void* x_tiled, void* x_sf, float* row_scale,
-                                 int M, int K, int pieces, int flags, tpb200_stream_t stream);
+size_t tpb200_nvfp4_gemv_tc_x_image_bytes(int K, int pieces);
+int tpb200_nvfp4_quantize_act_tc(const void* x, int x_dtype, int ldx, void* x_image, float* row_scale, int M, int K,
+                                 int pieces, int flags, tpb200_stream_t stream);
+/* several activation tensors (different K) of one step in ONE launch */
+#define TPB200_MAX_ACTS 8
+typedef struct { const void* x; int ldx; int K; void* x_image; float* x_row_scale; } tpb200_act_tc;
+int tpb200_nvfp4_quantize_acts_tc(const tpb200_act_tc* acts, int count, int x_dtype, int M, int pieces, int flags,
+                                  tpb200_stream_t stream);
 int tpb200_nvfp4_gemv_tc(const tpb200_gemv_tc_problem* problems, int count, int M, int pieces, int bias_dtype,
                          int out_dtype, int activation, void* workspace, size_t workspace_bytes, int flags,
                          tpb200_stream_t stream);

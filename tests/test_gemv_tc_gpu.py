@@ -23,17 +23,27 @@ def _weights(rng, N, K):
 
 
 def test_weight_tiling_is_the_swizzled_image(cuda_device):
+    """tile_weights: block (n // 256, k_stage) of 36864 bytes = 256 rows x 128 B with 16-byte chunk c of row
+    r at c ^ (r & 7), then the scale slabs of rows 0..127 and 128..255; padding rows are zero."""
     from turbopi_b200 import ops
     rng = np.random.default_rng(1)
-    N, K = 200, 1024 + 512
+    N, K = 328, 1024 + 512
     packed = rng.integers(0, 256, size=(N, K // 2), dtype=np.uint8)
-    tiled = ops.tile_weights_for_tc(torch.from_numpy(packed), N, K).numpy().reshape(2, 6, 128, 8, 16)
-    for (n, kbyte) in [(0, 0), (1, 17), (129, 300), (199, 767), (77, 640)]:
-        rt, r = divmod(n, 128)
+    sbytes = rng.integers(1, 120, size=(N, K // 16), dtype=np.uint8)
+    sf = nvfp4.swizzle_scales_128x4(sbytes, 16)
+    image = ops.tile_weights(_dev(packed, cuda_device), _dev(sf, cuda_device), N, K).cpu().numpy().reshape(2, 6, 36864)
+    codes = image[:, :, :32768].reshape(2, 6, 256, 8, 16)
+    slabs = image[:, :, 32768:].reshape(2, 6, 2, 4, 32, 4, 4)      # [half][K atom][r % 32][r // 32][k block]
+    for (n, kbyte) in [(0, 0), (1, 17), (129, 300), (327, 767), (77, 640), (300, 5)]:
+        nb, r = divmod(n, 256)
         ks, within = divmod(kbyte, 128)
         c, b = divmod(within, 16)
-        assert tiled[rt, ks, r, c ^ (r & 7), b] == packed[n, kbyte]
-    assert tiled[1, :, 72:, :, :].sum() == 0          # padded rows are zero codes
+        assert codes[nb, ks, r, c ^ (r & 7), b] == packed[n, kbyte]
+        kb = kbyte // 8                                  # 16-element block index
+        rr = r % 128
+        assert slabs[nb, ks, r // 128, (kb % 16) // 4, rr % 32, rr // 32, kb % 4] == sbytes[n, kb]
+    assert codes[1, :, 72:, :, :].sum() == 0          # padded rows are zero codes
+    assert slabs[1, :, 1].sum() == 0                   # ... with zero scales
 
 
 @pytest.mark.parametrize("M", [1, 4, 16])

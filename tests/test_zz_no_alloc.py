@@ -48,9 +48,9 @@ def test_static_scratch_entry_refuses_what_does_not_fit(cuda_device):
     """A plan that needs more than the built-in 16 MiB is rejected on the host, nothing is launched."""
     from turbopi_b200 import _lib
     lib = _lib.load()
-    # one 128-row tile per 128 outputs and 64 K-splits of 16 token rows: 262144 x 16384 needs far more than 16 MiB;
+    # 1024 row tiles, 8 K-splits of 16 token rows each: 262144 x 16384 needs far more than 16 MiB;
     # the pointers are never dereferenced because the size check comes first
     arr = (_lib.GemvTcProblem * 1)()
-    arr[0] = _lib.GemvTcProblem(256, 256, 256, 256, 256, 0, 256, 262144, 16384, 0, 1.0)
+    arr[0] = _lib.GemvTcProblem(256, 256, 256, 0, 256, 262144, 16384, 0, 1.0)
     st = lib.tpb200_nvfp4_gemv_tc_static(arr, 1, 1, 3, 0, 2, 0, 0, None)
     assert st == -6 and b"workspace" in lib.tpb200_status_string(st)

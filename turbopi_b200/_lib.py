@@ -42,9 +42,13 @@ class GemmArgs(ctypes.Structure):
 
 
 class GemvTcProblem(ctypes.Structure):
-    _fields_ = [("w_tiled", c_void_p), ("w_sf", c_void_p), ("x_tiled", c_void_p), ("x_sf", c_void_p),
+    _fields_ = [("w_image", c_void_p), ("x_image", c_void_p),
                 ("x_row_scale", c_void_p), ("bias", c_void_p), ("out", c_void_p),
                 ("N", c_int), ("K", c_int), ("ldo", c_int), ("global_scale", c_float)]
+
+
+class ActTc(ctypes.Structure):
+    _fields_ = [("x", c_void_p), ("ldx", c_int), ("K", c_int), ("x_image", c_void_p), ("x_row_scale", c_void_p)]
 
 
 class RowOpArgs(ctypes.Structure):
@@ -81,8 +85,10 @@ SIGNATURES = {
     "tpb200_nvfp4_quantize_act_pieces": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int,
                                                  c_int, c_int, c_int, c_void_p]),
     "tpb200_nvfp4_gemv_tc_workspace_size": (c_size_t, [ctypes.POINTER(GemvTcProblem), c_int]),
-    "tpb200_nvfp4_quantize_act_tc": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                                             c_int, c_void_p]),
+    "tpb200_nvfp4_gemv_tc_x_image_bytes": (c_size_t, [c_int, c_int]),
+    "tpb200_nvfp4_quantize_act_tc": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                             c_void_p]),
+    "tpb200_nvfp4_quantize_acts_tc": (c_int, [ctypes.POINTER(ActTc), c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "tpb200_nvfp4_gemv_tc": (c_int, [ctypes.POINTER(GemvTcProblem), c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                      c_size_t, c_int, c_void_p]),
     "tpb200_row_transform_quantize": (c_int, [ctypes.POINTER(RowOpArgs), c_void_p]),

@@ -7,12 +7,23 @@
 // along N: piece p of token t is B row 16 p + t, so one MMA (N = 16 * pieces) per 64-wide K
 // atom handles all pieces and the epilogue adds the pieces' columns.
 //
-// Both operands are stored PRE-TILED in the shared-memory image of the 128-byte swizzle
-// ([row tile][K stage][128 rows][128 B], 16-byte chunk c of row r at chunk c ^ (r & 7)), so a
-// stage is four plain 1-D bulk copies (weights 16 KB, weight scales 2 KB, activation tile,
-// activation scales 2 KB) -- no tensor maps, any number of problems per launch.
+// Both operands are stored PRE-TILED in the shared-memory image of the 128-byte swizzle, scales
+// included, so that a stage is TWO plain 1-D bulk copies -- no tensor maps, any number of problems
+// per launch:
+//   weights      the tensor-core GEMM's B image (tpb200_nvfp4_tile_weights): block (n_blk, ks) of
+//                36 KB = 256 rows x 128 B of codes (16-byte chunk c of row r at c ^ (r & 7)) + the two
+//                2 KB scale slabs; one image serves the prefill GEMM and this decode GEMV;
+//   activations  block ks = 16 * pieces rows x 128 B of codes in the same pattern + one 2 KB scale slab.
+// A stage (36 KB of weights + <= 10 KB of activations) feeds two MMAs per 64-wide K atom (weight rows
+// 0..127 and 128..255, two accumulators) against the same activation operand.
 //
-// Work unit = (problem, row tile, K split).  CTAs own contiguous unit ranges.  A tile whose K
+// One lane issues the two bulk copies of a stage; a ring of four stages (176 KB) keeps the stream
+// going.  (Streaming alone is not the limit: a ring of 36-48 KB bulk copies reads HBM at 7.1 TB/s
+// over 148 SMs when nothing consumes the data, and four warps of 16-byte cp.async copies do no
+// better.  What this kernel adds per stage -- scale copies and MMAs between `full` and `empty`,
+// and the fenced hand-over of split-K partial sums -- is what keeps it at ~3 TB/s.)
+//
+// Work unit = (problem, 256-row tile, K split).  CTAs own contiguous unit ranges.  A tile whose K
 // range is split writes per-split partial sums (only the valid tokens) to caller-provided
 // scratch; the CTA that arrives last on the tile's counter adds them in split order
 // (deterministic), applies the epilogue and resets the counter.  Nothing ever waits on another
@@ -25,22 +36,27 @@
 namespace tpb {
 namespace {
 
-constexpr int kStages = 6;
-constexpr int kWTile = 128 * 128;     // weight tile bytes per stage
+constexpr int kMaxStages = 6;
+constexpr int kWTile = 128 * 128;     // codes of 128 weight rows for one K stage
 constexpr int kSfSlab = 2048;         // 4 scale atoms
+constexpr int kWBlock = 2 * (kWTile + kSfSlab);   // 256 rows: [codes 32 KB][slab rows 0..127][slab rows 128..255]
 constexpr int kMaxNB = 64;            // 16 tokens x 4 pieces
-constexpr int kStageBytes = kWTile + kSfSlab + kMaxNB * 128 + kSfSlab;
+// a stage holds one weight block and one activation block (16 * pieces rows + scale slab); the ring
+// takes as many stages as fit: 5 for up to 3 pieces, 4 for 4
+__host__ __device__ constexpr int stage_bytes(int pieces) { return kWBlock + 16 * pieces * 128 + kSfSlab; }
+__host__ __device__ constexpr int num_stages(int pieces) {
+    return (227 * 1024 - 2048) / stage_bytes(pieces) < kMaxStages ? (227 * 1024 - 2048) / stage_bytes(pieces) : kMaxStages;
+}
 constexpr int kThreads = 192;
-constexpr int kTmemCols = 256;
-constexpr uint32_t kSfaCol = 2 * kMaxNB;       // after two accumulators of up to 64 columns
-constexpr uint32_t kSfbCol = kSfaCol + 16;
+constexpr int kTmemCols = 512;
+// tensor memory: accumulator (buffer b, row half h) at column b * 128 + h * 64, then the scales
+constexpr uint32_t kSfaCol = 256;              // weights: 16 columns per row half
+constexpr uint32_t kSfbCol = kSfaCol + 32;     // activations
 constexpr int kMaxProblems = TPB200_MAX_GROUP;
 
 struct TcProblem {
-    const uint8_t* w_tiled;     // [row_tiles][k_stages][16384]
-    const uint8_t* w_sf;        // [row_tiles][k_stages][2048]
-    const uint8_t* x_tiled;     // [k_stages][NB * 128]
-    const uint8_t* x_sf;        // [k_stages][2048]
+    const uint8_t* w_image;     // [row_tiles of 256][k_stages][36864]
+    const uint8_t* x_image;     // [k_stages][NB * 128 + 2048]
     const float* row_scale;     // [M]
     const void* bias;
     void* out;
@@ -68,8 +84,8 @@ struct TcParams {
 };
 
 struct SharedControl {
-    uint64_t full[kStages];
-    uint64_t empty[kStages];
+    uint64_t full[kMaxStages];
+    uint64_t empty[kMaxStages];
     uint64_t acc_full[2];
     uint64_t acc_empty[2];
     uint32_t tmem_base;
@@ -107,6 +123,8 @@ __device__ __forceinline__ Unit decode_unit(const TcParams& P, int u, int& p_hin
 __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid_constant__ TcParams P) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int kStages = num_stages(P.pieces);
+    const int kStageBytes = stage_bytes(P.pieces);
     SharedControl* ctl = reinterpret_cast<SharedControl*>(smem + kStages * kStageBytes);
 
     const int warp = threadIdx.x >> 5;
@@ -116,7 +134,7 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
     const int unit_hi = static_cast<int>(static_cast<long long>(blockIdx.x + 1) * P.total_units / gridDim.x);
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) {
+        for (int s = 0; s < kMaxStages; ++s) {
             mbar_init(&ctl->full[s], 1);
             mbar_init(&ctl->empty[s], 1);
         }
@@ -139,11 +157,11 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
     pdl_launch_dependents();
 
     if (warp == 0) {
-        // ------------------------------------------------------------ producer: four bulk copies per stage.
+        // ------------------------------------------------------------ producer: two bulk copies per stage.
         // Weights never depend on the previous kernel, so they are requested before griddepcontrol.wait
         // would matter; activations are produced by the previous kernel, so this lane waits first.
         if (lane == 0) {
-            const uint32_t xbytes = static_cast<uint32_t>(NB) * 128u;
+            const uint32_t xbytes = static_cast<uint32_t>(NB) * 128u + kSfSlab;
             // prologue: the weight halves of the first stages go out before griddepcontrol.wait
             int pre = 0;
             {
@@ -153,14 +171,13 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
                     const TcProblem& pr = P.prob[un.p];
                     for (int ks = un.ks0; ks < un.ks1 && pre < kStages; ++ks, ++pre) {
                         uint8_t* st = smem + pre * kStageBytes;
-                        const size_t tile = static_cast<size_t>(un.rt) * pr.k_stages + ks;
-                        mbar_expect_tx(&ctl->full[pre], kWTile + kSfSlab + xbytes + kSfSlab);
-                        bulk_copy_g2s(st, pr.w_tiled + tile * kWTile, kWTile, &ctl->full[pre]);
-                        bulk_copy_g2s(st + kWTile, pr.w_sf + tile * kSfSlab, kSfSlab, &ctl->full[pre]);
+                        const size_t blk = static_cast<size_t>(un.rt) * pr.k_stages + ks;
+                        mbar_expect_tx(&ctl->full[pre], kWBlock + xbytes);
+                        bulk_copy_g2s(st, pr.w_image + blk * kWBlock, kWBlock, &ctl->full[pre]);
                     }
                 }
             }
-            pdl_wait_prior_grids();   // the activation tiles are written by the previous kernel
+            pdl_wait_prior_grids();   // the activation image is written by the previous kernel
             int it = 0, ph = 0;
             for (int u = unit_lo; u < unit_hi && !*abort_flag; ++u) {
                 const Unit un = decode_unit(P, u, ph);
@@ -168,21 +185,17 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
                 for (int ks = un.ks0; ks < un.ks1; ++ks, ++it) {
                     const int s = it % kStages;
                     uint8_t* st = smem + s * kStageBytes;
-                    const size_t tile = static_cast<size_t>(un.rt) * pr.k_stages + ks;
+                    const size_t blk = static_cast<size_t>(un.rt) * pr.k_stages + ks;
                     if (it >= pre) {
                         if (it >= kStages && !mbar_wait_bounded(&ctl->empty[s], ((it / kStages) - 1) & 1)) {
                             record_error(kErrGemmEmptyBarrierTimeout);
                             *abort_flag = 1;
                             break;
                         }
-                        mbar_expect_tx(&ctl->full[s], kWTile + kSfSlab + xbytes + kSfSlab);
-                        bulk_copy_g2s(st, pr.w_tiled + tile * kWTile, kWTile, &ctl->full[s]);
-                        bulk_copy_g2s(st + kWTile, pr.w_sf + tile * kSfSlab, kSfSlab, &ctl->full[s]);
+                        mbar_expect_tx(&ctl->full[s], kWBlock + xbytes);
+                        bulk_copy_g2s(st, pr.w_image + blk * kWBlock, kWBlock, &ctl->full[s]);
                     }
-                    bulk_copy_g2s(st + kWTile + kSfSlab, pr.x_tiled + static_cast<size_t>(ks) * xbytes, xbytes,
-                                  &ctl->full[s]);
-                    bulk_copy_g2s(st + kWTile + kSfSlab + kMaxNB * 128, pr.x_sf + static_cast<size_t>(ks) * kSfSlab,
-                                  kSfSlab, &ctl->full[s]);
+                    bulk_copy_g2s(st + kWBlock, pr.x_image + static_cast<size_t>(ks) * xbytes, xbytes, &ctl->full[s]);
                 }
             }
         }
@@ -200,7 +213,7 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
                     break;
                 }
                 tc::fence_after_thread_sync();
-                const uint32_t tmem_acc = tmem_base + buf * kMaxNB;
+                const uint32_t tmem_acc = tmem_base + buf * 128;
                 for (int ks = un.ks0; ks < un.ks1; ++ks, ++it) {
                     const int s = it % kStages;
                     if (!mbar_wait_bounded(&ctl->full[s], (it / kStages) & 1)) {
@@ -210,19 +223,24 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
                     }
                     tc::fence_after_thread_sync();
                     const uint32_t st = smem_u32(smem + s * kStageBytes);
-                    const uint32_t sfa_s = st + kWTile;
-                    const uint32_t xt_s = sfa_s + kSfSlab;
-                    const uint32_t sfb_s = xt_s + kMaxNB * 128;
+                    const uint32_t sfa_s = st + 2 * kWTile;          // two slabs: rows 0..127, 128..255
+                    const uint32_t xt_s = st + kWBlock;
+                    const uint32_t sfb_s = xt_s + NB * 128;
 #pragma unroll
                     for (int a = 0; a < 4; ++a) {
                         tc::cp_sf_32x128b(tmem_base + kSfaCol + 4 * a, tc::make_sf_desc(sfa_s + a * 512));
+                        tc::cp_sf_32x128b(tmem_base + kSfaCol + 16 + 4 * a, tc::make_sf_desc(sfa_s + kSfSlab + a * 512));
                         tc::cp_sf_32x128b(tmem_base + kSfbCol + 4 * a, tc::make_sf_desc(sfb_s + a * 512));
                     }
 #pragma unroll
                     for (int a = 0; a < 4; ++a) {
-                        tc::mma_mxf4nvf4(tmem_acc, tc::make_kmajor_sw128_desc(st, a * 32),
-                                         tc::make_kmajor_sw128_desc(xt_s, a * 32), idesc, tmem_base + kSfaCol + 4 * a,
-                                         tmem_base + kSfbCol + 4 * a, (ks > un.ks0) || (a != 0));
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            tc::mma_mxf4nvf4(tmem_acc + h * kMaxNB, tc::make_kmajor_sw128_desc(st + h * kWTile, a * 32),
+                                             tc::make_kmajor_sw128_desc(xt_s, a * 32), idesc,
+                                             tmem_base + kSfaCol + 16 * h + 4 * a, tmem_base + kSfbCol + 4 * a,
+                                             (ks > un.ks0) || (a != 0));
+                        }
                     }
                     tc::commit(&ctl->empty[s]);
                 }
@@ -245,29 +263,35 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
                 break;
             }
             tc::fence_after_thread_sync();
-            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * kMaxNB;
-            float v[16];
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * 128;
+            float v[2][16];
 #pragma unroll
-            for (int t = 0; t < 16; ++t) v[t] = 0.0f;
-            for (int pc = 0; pc < P.pieces; ++pc) {
-                uint32_t r[16];
-                tmem_ld_32x32b_x16(taddr + pc * 16, r);
-                tc::tmem_ld_wait();
+            for (int h = 0; h < 2; ++h) {
 #pragma unroll
-                for (int t = 0; t < 16; ++t) v[t] += __uint_as_float(r[t]);
+                for (int t = 0; t < 16; ++t) v[h][t] = 0.0f;
+                for (int pc = 0; pc < P.pieces; ++pc) {
+                    uint32_t r[16];
+                    tmem_ld_32x32b_x16(taddr + h * kMaxNB + pc * 16, r);
+                    tc::tmem_ld_wait();
+#pragma unroll
+                    for (int t = 0; t < 16; ++t) v[h][t] += __uint_as_float(r[t]);
+                }
             }
             tc::fence_before_thread_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&ctl->acc_empty[buf]);
 
-            const int n = un.rt * 128 + et;
-            const int n_pad = pr.row_tiles * 128;
+            const int n_pad = pr.row_tiles * 256;
             bool finalize = true;
             if (pr.splits > 1) {
                 float* part = P.scratch + pr.scratch_off;
 #pragma unroll
-                for (int t = 0; t < 16; ++t) {
-                    if (t < P.M) part[(static_cast<size_t>(un.split) * 16 + t) * n_pad + n] = v[t];
+                for (int h = 0; h < 2; ++h) {
+                    const int n = un.rt * 256 + h * 128 + et;
+#pragma unroll
+                    for (int t = 0; t < 16; ++t) {
+                        if (t < P.M) part[(static_cast<size_t>(un.split) * 16 + t) * n_pad + n] = v[h][t];
+                    }
                 }
                 __threadfence();
                 asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -277,27 +301,36 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
                 if (finalize) {
                     __threadfence();
 #pragma unroll
-                    for (int t = 0; t < 16; ++t) {
-                        if (t < P.M) {
-                            float acc = 0.0f;
-                            for (int sp = 0; sp < pr.splits; ++sp) {
-                                acc += __ldcg(part + (static_cast<size_t>(sp) * 16 + t) * n_pad + n);
+                    for (int h = 0; h < 2; ++h) {
+                        const int n = un.rt * 256 + h * 128 + et;
+#pragma unroll
+                        for (int t = 0; t < 16; ++t) {
+                            if (t < P.M) {
+                                float acc = 0.0f;
+                                for (int sp = 0; sp < pr.splits; ++sp) {
+                                    acc += __ldcg(part + (static_cast<size_t>(sp) * 16 + t) * n_pad + n);
+                                }
+                                v[h][t] = acc;
                             }
-                            v[t] = acc;
                         }
                     }
                     if (et == 0) P.counters[pr.counter_off + un.rt] = 0;   // ready for the next launch
                 }
                 asm volatile("bar.sync 1, 128;" ::: "memory");              // ticket slot free for the next unit
             }
-            if (finalize && n < pr.N) {
+            if (finalize) {
 #pragma unroll
-                for (int t = 0; t < 16; ++t) {
-                    if (t < P.M) {
-                        float f = v[t] * pr.global_scale * __ldg(pr.row_scale + t);
-                        if (pr.bias != nullptr) f += load_as_float(pr.bias, P.bias_dtype, n);
-                        f = apply_activation(f, P.activation);
-                        store_from_float(pr.out, P.out_dtype, static_cast<size_t>(t) * pr.ldo + n, f);
+                for (int h = 0; h < 2; ++h) {
+                    const int n = un.rt * 256 + h * 128 + et;
+                    if (n >= pr.N) continue;
+#pragma unroll
+                    for (int t = 0; t < 16; ++t) {
+                        if (t < P.M) {
+                            float f = v[h][t] * pr.global_scale * __ldg(pr.row_scale + t);
+                            if (pr.bias != nullptr) f += load_as_float(pr.bias, P.bias_dtype, n);
+                            f = apply_activation(f, P.activation);
+                            store_from_float(pr.out, P.out_dtype, static_cast<size_t>(t) * pr.ldo + n, f);
+                        }
                     }
                 }
             }
@@ -320,14 +353,25 @@ __device__ __forceinline__ uint32_t e2m1_index(float a) {
     return (a > 0.25f) + (a > 0.75f) + (a > 1.25f) + (a > 1.75f) + (a > 2.5f) + (a > 3.5f) + (a > 5.0f);
 }
 
-__global__ void __launch_bounds__(256) quantize_pieces_tiled_kernel(const void* __restrict__ x, int x_dtype, int ldx,
-                                                                    uint8_t* __restrict__ x_tiled,
-                                                                    uint8_t* __restrict__ x_sf,
-                                                                    float* __restrict__ row_scale, int M, int K,
-                                                                    int pieces) {
+struct QuantActs {
+    int count;
+    const void* x[TPB200_MAX_ACTS];
+    int ldx[TPB200_MAX_ACTS];
+    int K[TPB200_MAX_ACTS];
+    uint8_t* image[TPB200_MAX_ACTS];
+    float* row_scale[TPB200_MAX_ACTS];
+};
+
+__global__ void __launch_bounds__(256) quantize_pieces_tiled_kernel(const __grid_constant__ QuantActs A, int x_dtype,
+                                                                    int M, int pieces) {
     pdl_launch_dependents();
     pdl_wait_prior_grids();
     const int t = blockIdx.x;                 // 0..15
+    const void* __restrict__ x = A.x[blockIdx.y];
+    const int ldx = A.ldx[blockIdx.y];
+    const int K = A.K[blockIdx.y];
+    uint8_t* __restrict__ x_image = A.image[blockIdx.y];
+    float* __restrict__ row_scale = A.row_scale[blockIdx.y];
     const int NB = 16 * pieces;
     const int nblk = K >> 4;
     const int kb_pad = (K + 255) / 256 * 16;
@@ -369,17 +413,16 @@ __global__ void __launch_bounds__(256) quantize_pieces_tiled_kernel(const void* 
         const int c = (kb & 15) >> 1;            // 16-byte chunk of the 128-byte row
         for (int p = 0; p < pieces; ++p) {
             const int prow = p * 16 + t;
-            uint8_t* dst = x_tiled + static_cast<size_t>(ks) * (NB * 128) + prow * 128 + ((c ^ (prow & 7)) << 4) +
-                           (kb & 1) * 8;
-            const size_t sf_off = static_cast<size_t>(ks) * 2048 + ((kb >> 2) & 3) * 512 + (prow & 31) * 16 +
-                                  ((prow >> 5) & 3) * 4 + (kb & 3);
+            uint8_t* blk = x_image + static_cast<size_t>(ks) * (NB * 128 + 2048);
+            uint8_t* dst = blk + prow * 128 + ((c ^ (prow & 7)) << 4) + (kb & 1) * 8;
+            uint8_t* sf_dst = blk + NB * 128 + ((kb >> 2) & 3) * 512 + (prow & 31) * 16 + ((prow >> 5) & 3) * 4 + (kb & 3);
             if (!valid) {
-                x_sf[sf_off] = 0;
+                *sf_dst = 0;
                 *reinterpret_cast<uint2*>(dst) = make_uint2(0u, 0u);
                 continue;
             }
             uint32_t lo, hi;
-            x_sf[sf_off] = quantize_block16_piece(r, lo, hi);
+            *sf_dst = quantize_block16_piece(r, lo, hi);
             *reinterpret_cast<uint2*>(dst) = make_uint2(lo, hi);
         }
     }
@@ -409,7 +452,7 @@ int make_plan(const tpb200_gemv_tc_problem* probs, int count, int sms, TcPlan& p
     long long total_stages = 0;
     for (int i = 0; i < count; ++i) {
         if (probs[i].N < 1 || probs[i].K < 16 || probs[i].K % 16 != 0) return TPB200_ERR_SHAPE;
-        const long long row_tiles = (probs[i].N + 127) / 128;
+        const long long row_tiles = (probs[i].N + 255) / 256;
         total_stages += row_tiles * ((probs[i].K + 255) / 256);
     }
     // aim for ~4 units per SM, units of 1..8 stages, and never longer than the shortest problem's K so
@@ -420,7 +463,7 @@ int make_plan(const tpb200_gemv_tc_problem* probs, int count, int sms, TcPlan& p
     plan.counters = 0;
     plan.total_units = 0;
     for (int i = 0; i < count; ++i) {
-        const int row_tiles = (probs[i].N + 127) / 128;
+        const int row_tiles = (probs[i].N + 255) / 256;
         const int k_stages = (probs[i].K + 255) / 256;
         int splits = (k_stages + target - 1) / target;
         const int sps = (k_stages + splits - 1) / splits;
@@ -428,7 +471,7 @@ int make_plan(const tpb200_gemv_tc_problem* probs, int count, int sms, TcPlan& p
         plan.splits[i] = splits;
         plan.stages_per_split[i] = sps;
         if (splits > 1) {
-            plan.scratch_floats += static_cast<size_t>(splits) * 16 * row_tiles * 128;
+            plan.scratch_floats += static_cast<size_t>(splits) * 16 * row_tiles * 256;
             plan.counters += row_tiles;
         }
         plan.total_units += row_tiles * splits;
@@ -457,18 +500,46 @@ extern "C" size_t tpb200_nvfp4_gemv_tc_workspace_size(const tpb200_gemv_tc_probl
     return (plan.counters * sizeof(int) + 255) / 256 * 256 + plan.scratch_floats * sizeof(float) + 256;
 }
 
-extern "C" int tpb200_nvfp4_quantize_act_tc(const void* x, int x_dtype, int ldx, void* x_tiled, void* x_sf,
-                                            float* row_scale, int M, int K, int pieces, int flags,
-                                            tpb200_stream_t stream) {
-    TPB_REQUIRE(x && x_tiled && x_sf && row_scale, TPB200_ERR_NULL);
-    TPB_REQUIRE(M >= 1 && M <= 16 && K >= 16 && K % 16 == 0 && ldx >= K, TPB200_ERR_SHAPE);
-    TPB_REQUIRE(pieces >= 1 && pieces <= 4, TPB200_ERR_SHAPE);
+extern "C" size_t tpb200_nvfp4_gemv_tc_x_image_bytes(int K, int pieces) {
+    if (K < 16 || pieces < 1 || pieces > 4) return 0;
+    return static_cast<size_t>((K + 255) / 256) * (16 * pieces * 128 + 2048);
+}
+
+extern "C" int tpb200_nvfp4_quantize_acts_tc(const tpb200_act_tc* acts, int count, int x_dtype, int M, int pieces,
+                                             int flags, tpb200_stream_t stream) {
+    TPB_REQUIRE(acts != nullptr, TPB200_ERR_NULL);
+    TPB_REQUIRE(count >= 1 && count <= TPB200_MAX_ACTS, TPB200_ERR_SHAPE);
+    TPB_REQUIRE(M >= 1 && M <= 16 && pieces >= 1 && pieces <= 4, TPB200_ERR_SHAPE);
     TPB_REQUIRE(tpb_valid_dtype(x_dtype), TPB200_ERR_ENUM);
     TPB_REQUIRE((flags & ~TPB200_FLAG_PDL) == 0, TPB200_ERR_ENUM);
-    TPB_REQUIRE(tpb_aligned16(x) && tpb_aligned16(x_tiled) && tpb_aligned16(x_sf), TPB200_ERR_ALIGN);
-    TPB_REQUIRE((static_cast<long long>(ldx) * tpb_dtype_size(x_dtype)) % 16 == 0, TPB200_ERR_ALIGN);
+    tpb::QuantActs A;
+    A.count = count;
+    for (int i = 0; i < count; ++i) {
+        const tpb200_act_tc& h = acts[i];
+        TPB_REQUIRE(h.x && h.x_image && h.x_row_scale, TPB200_ERR_NULL);
+        TPB_REQUIRE(h.K >= 16 && h.K % 16 == 0 && h.ldx >= h.K, TPB200_ERR_SHAPE);
+        TPB_REQUIRE(tpb_aligned16(h.x) && tpb_aligned16(h.x_image), TPB200_ERR_ALIGN);
+        TPB_REQUIRE((static_cast<long long>(h.ldx) * tpb_dtype_size(x_dtype)) % 16 == 0, TPB200_ERR_ALIGN);
+        A.x[i] = h.x;
+        A.ldx[i] = h.ldx;
+        A.K[i] = h.K;
+        A.image[i] = static_cast<uint8_t*>(h.x_image);
+        A.row_scale[i] = h.x_row_scale;
+    }
+    // same shared-memory carve-out as the GEMV that follows, so the SMs do not reconfigure in between
+    static std::atomic<uint64_t> configured{0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return TPB200_ERR_CUDA;
+    const uint64_t bit = 1ull << (dev & 63);
+    if (!(configured.load(std::memory_order_relaxed) & bit)) {
+        if (cudaFuncSetAttribute(tpb::quantize_pieces_tiled_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                 cudaSharedmemCarveoutMaxShared) != cudaSuccess) {
+            return TPB200_ERR_CUDA;
+        }
+        configured.fetch_or(bit, std::memory_order_relaxed);
+    }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(16, 1, 1);
+    cfg.gridDim = dim3(16, count, 1);
     cfg.blockDim = dim3(256, 1, 1);
     cfg.stream = reinterpret_cast<cudaStream_t>(stream);
     cudaLaunchAttribute attr[1];
@@ -478,11 +549,16 @@ extern "C" int tpb200_nvfp4_quantize_act_tc(const void* x, int x_dtype, int ldx,
         cfg.attrs = attr;
         cfg.numAttrs = 1;
     }
-    if (cudaLaunchKernelEx(&cfg, tpb::quantize_pieces_tiled_kernel, x, x_dtype, ldx, static_cast<uint8_t*>(x_tiled),
-                           static_cast<uint8_t*>(x_sf), row_scale, M, K, pieces) != cudaSuccess) {
+    if (cudaLaunchKernelEx(&cfg, tpb::quantize_pieces_tiled_kernel, A, x_dtype, M, pieces) != cudaSuccess) {
         return TPB200_ERR_CUDA;
     }
     return TPB200_OK;
+}
+
+extern "C" int tpb200_nvfp4_quantize_act_tc(const void* x, int x_dtype, int ldx, void* x_image, float* row_scale, int M,
+                                            int K, int pieces, int flags, tpb200_stream_t stream) {
+    tpb200_act_tc a = {x, ldx, K, x_image, row_scale};
+    return tpb200_nvfp4_quantize_acts_tc(&a, 1, x_dtype, M, pieces, flags, stream);
 }
 
 extern "C" int tpb200_nvfp4_gemv_tc(const tpb200_gemv_tc_problem* problems, int count, int M, int pieces,
@@ -520,15 +596,12 @@ extern "C" int tpb200_nvfp4_gemv_tc(const tpb200_gemv_tc_problem* problems, int 
     size_t soff = 0;
     for (int i = 0; i < count; ++i) {
         const tpb200_gemv_tc_problem& h = problems[i];
-        TPB_REQUIRE(h.w_tiled && h.w_sf && h.x_tiled && h.x_sf && h.x_row_scale && h.out, TPB200_ERR_NULL);
-        TPB_REQUIRE(tpb_aligned16(h.w_tiled) && tpb_aligned16(h.w_sf) && tpb_aligned16(h.x_tiled) && tpb_aligned16(h.x_sf),
-                    TPB200_ERR_ALIGN);
+        TPB_REQUIRE(h.w_image && h.x_image && h.x_row_scale && h.out, TPB200_ERR_NULL);
+        TPB_REQUIRE(tpb_aligned16(h.w_image) && tpb_aligned16(h.x_image), TPB200_ERR_ALIGN);
         TPB_REQUIRE(h.ldo == 0 || h.ldo >= h.N, TPB200_ERR_SHAPE);
         tpb::TcProblem& d = P.prob[i];
-        d.w_tiled = static_cast<const uint8_t*>(h.w_tiled);
-        d.w_sf = static_cast<const uint8_t*>(h.w_sf);
-        d.x_tiled = static_cast<const uint8_t*>(h.x_tiled);
-        d.x_sf = static_cast<const uint8_t*>(h.x_sf);
+        d.w_image = static_cast<const uint8_t*>(h.w_image);
+        d.x_image = static_cast<const uint8_t*>(h.x_image);
         d.row_scale = h.x_row_scale;
         d.bias = h.bias;
         d.out = h.out;
@@ -537,7 +610,7 @@ extern "C" int tpb200_nvfp4_gemv_tc(const tpb200_gemv_tc_problem* problems, int 
         d.ldo = h.ldo == 0 ? h.N : h.ldo;
         d.global_scale = h.global_scale;
         d.k_stages = (h.K + 255) / 256;
-        d.row_tiles = (h.N + 127) / 128;
+        d.row_tiles = (h.N + 255) / 256;
         d.splits = plan.splits[i];
         d.stages_per_split = plan.stages_per_split[i];
         d.unit_begin = units;
@@ -545,19 +618,19 @@ extern "C" int tpb200_nvfp4_gemv_tc(const tpb200_gemv_tc_problem* problems, int 
         d.counter_off = coff;
         units += d.row_tiles * d.splits;
         if (d.splits > 1) {
-            soff += static_cast<size_t>(d.splits) * 16 * d.row_tiles * 128;
+            soff += static_cast<size_t>(d.splits) * 16 * d.row_tiles * 256;
             coff += d.row_tiles;
         }
     }
 
-    const size_t smem = tpb::kStages * tpb::kStageBytes + sizeof(tpb::SharedControl) + 1024;
+    const size_t smem = tpb::num_stages(pieces) * tpb::stage_bytes(pieces) + sizeof(tpb::SharedControl) + 1024;
     static std::atomic<uint64_t> configured{0};
     int dev = 0;
     cudaGetDevice(&dev);
     const uint64_t bit = 1ull << (dev & 63);
     if (!(configured.load(std::memory_order_relaxed) & bit)) {
         if (cudaFuncSetAttribute(tpb::nvfp4_gemv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 static_cast<int>(smem)) != cudaSuccess) {
+                                 227 * 1024) != cudaSuccess) {
             return TPB200_ERR_CUDA;
         }
         configured.fetch_or(bit, std::memory_order_relaxed);

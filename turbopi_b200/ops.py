@@ -479,26 +479,11 @@ def nvfp4_gemm_w4a16_tiled(x, b_image, N, alpha=1.0, bias=None, activation=ACT_N
 
 
 # ------------------------------------------------------------------------------------- tensor-core GEMV
-def tile_weights_for_tc(packed, N, K):
-    """Packed e2m1 weights [N, >= K/2] -> the pre-tiled image the tensor-core GEMV streams:
-    [row tile of 128][K stage of 256][128 rows][128 B], 16-byte chunk c of row r at c ^ (r & 7);
-    N padded to 128 and K to 256 with zero codes.  Pure index shuffle (weight prep, any device)."""
-    rt, ks = (N + 127) // 128, (K + 255) // 256
-    pad = torch.zeros((rt * 128, ks * 128), dtype=torch.uint8, device=packed.device)
-    pad[:N, :K // 2] = packed[:, :K // 2]
-    t = pad.reshape(rt, 128, ks, 8, 16)
-    r = torch.arange(128, device=packed.device)
-    c = torch.arange(8, device=packed.device)
-    src = (c[None, :] ^ (r[:, None] & 7))                        # dest chunk c' holds source chunk c' ^ (r & 7)
-    idx = src[None, :, None, :, None].expand(rt, 128, ks, 8, 16)
-    t = torch.gather(t, 3, idx)
-    return t.permute(0, 2, 1, 3, 4).contiguous().reshape(-1)
-
-
 class TcGemv:
     """NVFP4 weight-only GEMV(s) for M <= 16 tokens on the tensor cores.  Built once from a list of
     problems (dicts: weight_packed [N, K/2] uint8, weight_scales [N, K/16] E4M3 bytes, global_scale,
-    x [M, K], out [M, N], optional bias); weights are re-tiled at construction.  `launch()` quantises
+    x [M, K], out [M, N], optional bias; or `w_image` = the tiled weight image of tile_weights(), the
+    same one the tensor-core GEMM streams); weights are tiled at construction.  `launch()` quantises
     every distinct activation tensor into residual pieces and enqueues ONE GEMV kernel."""
 
     def __init__(self, problems, pieces=3, activation=ACT_NONE, pdl=False):
@@ -513,25 +498,30 @@ class TcGemv:
         self.out_dtype = _dt(p0["out"])
         self.bias_dtype = _dt(p0["bias"]) if p0.get("bias") is not None else F32
         self._keep = []
-        self._acts = {}           # id(x) -> (x, tiled, sf, row_scale, K)
+        self._acts = {}           # id(x) -> (x, image, row_scale, K)
         arr = (_lib.GemvTcProblem * len(problems))()
         for i, p in enumerate(problems):
-            x, w, ws, out = p["x"], p["weight_packed"], p["weight_scales"], p["out"]
-            _cuda(x, w, ws, out, p.get("bias"))
-            N, K = w.shape[0], x.shape[1]
-            if "w_tiled" in p:
-                w_tiled, w_sf = p["w_tiled"], p["w_sf"]
+            x, out = p["x"], p["out"]
+            _cuda(x, out, p.get("bias"))
+            K = x.shape[1]
+            if "w_image" in p:
+                w_image, N = p["w_image"], out.shape[1]
+                _cuda(w_image)
             else:
-                w_tiled, w_sf = tile_weights_for_tc(w, N, K), swizzle_scales(ws.view(torch.uint8))
+                w, ws = p["weight_packed"], p["weight_scales"]
+                _cuda(w, ws)
+                N = w.shape[0]
+                b = torch.zeros((N, packed_pitch(K)), dtype=torch.uint8, device=self.device)
+                b[:, :K // 2] = w[:, :K // 2]
+                w_image = tile_weights(b, swizzle_scales(ws.view(torch.uint8)), N, K)
             key = x.data_ptr()
             if key not in self._acts:
-                ks = (K + 255) // 256
-                self._acts[key] = (x, torch.empty(ks * 16 * pieces * 128, dtype=torch.uint8, device=self.device),
-                                   torch.empty(ks * 2048, dtype=torch.uint8, device=self.device),
+                nbytes = int(_lib.load().tpb200_nvfp4_gemv_tc_x_image_bytes(K, pieces))
+                self._acts[key] = (x, torch.empty(nbytes, dtype=torch.uint8, device=self.device),
                                    torch.empty(16, dtype=torch.float32, device=self.device), K)
-            _, xt, xsf, rs, _ = self._acts[key]
-            self._keep.append((w_tiled, w_sf, out, p.get("bias")))
-            arr[i] = _lib.GemvTcProblem(_ptr(w_tiled), _ptr(w_sf), _ptr(xt), _ptr(xsf), _ptr(rs), _ptr(p.get("bias")),
+            _, xi, rs, _ = self._acts[key]
+            self._keep.append((w_image, out, p.get("bias")))
+            arr[i] = _lib.GemvTcProblem(_ptr(w_image), _ptr(xi), _ptr(rs), _ptr(p.get("bias")),
                                         _ptr(out), N, K, out.stride(0), float(p.get("global_scale", 1.0)))
         self._arr = arr
         with torch.cuda.device(self.device):
@@ -542,10 +532,14 @@ class TcGemv:
         lib = _lib.load()
         with torch.cuda.device(self.device):
             stream = torch.cuda.current_stream(self.device).cuda_stream
-            for (x, xt, xsf, rs, K) in self._acts.values():
-                st = lib.tpb200_nvfp4_quantize_act_tc(_ptr(x), _dt(x), x.stride(0), _ptr(xt), _ptr(xsf), _ptr(rs),
-                                                      self.M, K, self.pieces, self.flags, stream)
-                _lib.check(st, "tpb200_nvfp4_quantize_act_tc")
+            acts = list(self._acts.values())
+            for i in range(0, len(acts), 8):          # up to 8 activation tensors per launch
+                chunk = acts[i:i + 8]
+                arr = (_lib.ActTc * len(chunk))(*[_lib.ActTc(_ptr(x), x.stride(0), K, _ptr(xi), _ptr(rs))
+                                                  for (x, xi, rs, K) in chunk])
+                st = lib.tpb200_nvfp4_quantize_acts_tc(arr, len(chunk), _dt(chunk[0][0]), self.M, self.pieces,
+                                                       self.flags, stream)
+                _lib.check(st, "tpb200_nvfp4_quantize_acts_tc")
 
     def gemv(self):
         with torch.cuda.device(self.device):
