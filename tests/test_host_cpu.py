@@ -118,3 +118,18 @@ def test_nvfp4_sim_quantiser_matches_golden(golden):
     sw = nvfp4_linear.prepare_scales(s, 32).numpy()
     ref = nvfp4.swizzle_scales_128x4(np.repeat(formats.e4m3_encode(g["ws_mse"]), 2, axis=1), 16)
     assert np.array_equal(sw, ref)
+
+
+def test_weight_row_permutations_are_permutations():
+    """The fused-QKV and gated-GELU epilogues rely on the weight rows being re-ordered; both orders must be
+    permutations with the documented block structure."""
+    import torch
+    from turbopi_b200 import ops
+    p = ops.qkv_tile_permutation(2048)
+    assert sorted(p.tolist()) == list(range(2048 + 512))
+    t = p.reshape(-1, 128)                               # every 128-row tile: 64 rows, then the same + 128
+    assert (t[:, 64:] == t[:, :64] + 128).all()
+    g = ops.geglu_row_permutation(1024)
+    assert sorted(g.tolist()) == list(range(2048))
+    b = g.reshape(-1, 2, 128)                            # every 256-row block: 128 gate rows, their up rows
+    assert (b[:, 1] == b[:, 0] + 1024).all() and (b[:, 0, 0] == torch.arange(8) * 128).all()

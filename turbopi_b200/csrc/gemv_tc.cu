@@ -23,11 +23,14 @@
 // better.  What this kernel adds per stage -- scale copies and MMAs between `full` and `empty`,
 // and the fenced hand-over of split-K partial sums -- is what keeps it at ~3 TB/s.)
 //
-// Work unit = (problem, 256-row tile, K split).  CTAs own contiguous unit ranges.  A tile whose K
-// range is split writes per-split partial sums (only the valid tokens) to caller-provided
-// scratch; the CTA that arrives last on the tile's counter adds them in split order
-// (deterministic), applies the epilogue and resets the counter.  Nothing ever waits on another
-// CTA.
+// Work unit = (problem, 256-row tile, K split); all units carry (nearly) the same number of stages
+// and every CTA owns a contiguous range of equally many.  Consecutive units of one tile inside a
+// CTA's range form a GROUP that is accumulated in tensor memory as one K range, so only the tiles cut
+// by a range boundary are shared between CTAs: each of their groups writes its partial sums (only the
+// valid tokens) to caller-provided scratch, and the CTA that arrives last on the tile's counter adds
+// them in K order (deterministic), applies the epilogue and resets the counter.  Nothing ever waits
+// on another CTA.  (Handing over partial sums costs a device-wide fence, ~2.5 us per hand-over; with
+// one per unit the CTAs that drew down-projection units finished 17 us after the others.)
 #include <algorithm>
 #include <atomic>
 
@@ -120,6 +123,26 @@ __device__ __forceinline__ Unit decode_unit(const TcParams& P, int u, int& p_hin
     return un;
 }
 
+// The group that starts at unit u: the units of u's tile from u to the end of the tile or of the CTA's range.
+struct Group {
+    int p, rt, split0, split1, ks0, ks1, next;
+};
+
+__device__ __forceinline__ Group decode_group(const TcParams& P, int u, int unit_hi, int& p_hint) {
+    const Unit un = decode_unit(P, u, p_hint);
+    const TcProblem& pr = P.prob[un.p];
+    const int tile_end = pr.unit_begin + (un.rt + 1) * pr.splits;
+    Group g;
+    g.p = un.p;
+    g.rt = un.rt;
+    g.split0 = un.split;
+    g.next = min(unit_hi, tile_end);
+    g.split1 = un.split + (g.next - u) - 1;
+    g.ks0 = un.ks0;
+    g.ks1 = min(pr.k_stages, (g.split1 + 1) * pr.stages_per_split);
+    return g;
+}
+
 __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid_constant__ TcParams P) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -157,44 +180,67 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
     pdl_launch_dependents();
 
     if (warp == 0) {
-        // ------------------------------------------------------------ producer: two bulk copies per stage.
-        // Weights never depend on the previous kernel, so they are requested before griddepcontrol.wait
-        // would matter; activations are produced by the previous kernel, so this lane waits first.
-        if (lane == 0) {
-            const uint32_t xbytes = static_cast<uint32_t>(NB) * 128u + kSfSlab;
-            // prologue: the weight halves of the first stages go out before griddepcontrol.wait
-            int pre = 0;
-            {
-                int ph = 0;
-                for (int u = unit_lo; u < unit_hi && pre < kStages; ++u) {
-                    const Unit un = decode_unit(P, u, ph);
-                    const TcProblem& pr = P.prob[un.p];
-                    for (int ks = un.ks0; ks < un.ks1 && pre < kStages; ++ks, ++pre) {
-                        uint8_t* st = smem + pre * kStageBytes;
-                        const size_t blk = static_cast<size_t>(un.rt) * pr.k_stages + ks;
-                        mbar_expect_tx(&ctl->full[pre], kWBlock + xbytes);
-                        bulk_copy_g2s(st, pr.w_image + blk * kWBlock, kWBlock, &ctl->full[pre]);
+        // ------------------------------------------------------------ producer (whole warp): lane 0 owns the
+        // barrier hand-shakes, lanes 0..3 each copy a quarter of the stage's weight block and lane 4 the
+        // activation block.  (A thread that issues a bulk copy is held for ~0.3 us whatever the size; requests
+        // issued side by side from several lanes overlap that.)  Weights never depend on the previous kernel,
+        // so the first stages' weight blocks are requested before griddepcontrol.wait; the activation image
+        // is written by the previous kernel.
+        const uint32_t xbytes = static_cast<uint32_t>(NB) * 128u + kSfSlab;
+        constexpr uint32_t kQuarter = kWBlock / 4;
+        int pre = 0;
+        {
+            int ph = 0;
+            for (int u = unit_lo; u < unit_hi && pre < kStages; ++u) {
+                const Unit un = decode_unit(P, u, ph);
+                const TcProblem& pr = P.prob[un.p];
+                for (int ks = un.ks0; ks < un.ks1 && pre < kStages; ++ks, ++pre) {
+                    uint8_t* st = smem + pre * kStageBytes;
+                    const size_t blk = static_cast<size_t>(un.rt) * pr.k_stages + ks;
+                    if (lane == 0) mbar_expect_tx(&ctl->full[pre], kWBlock + xbytes);
+                    __syncwarp();
+                    if (lane < 4) {
+                        bulk_copy_g2s(st + lane * kQuarter, pr.w_image + blk * kWBlock + lane * kQuarter, kQuarter,
+                                      &ctl->full[pre]);
                     }
                 }
             }
-            pdl_wait_prior_grids();   // the activation image is written by the previous kernel
-            int it = 0, ph = 0;
-            for (int u = unit_lo; u < unit_hi && !*abort_flag; ++u) {
-                const Unit un = decode_unit(P, u, ph);
-                const TcProblem& pr = P.prob[un.p];
-                for (int ks = un.ks0; ks < un.ks1; ++ks, ++it) {
-                    const int s = it % kStages;
-                    uint8_t* st = smem + s * kStageBytes;
-                    const size_t blk = static_cast<size_t>(un.rt) * pr.k_stages + ks;
-                    if (it >= pre) {
+        }
+        pdl_wait_prior_grids();
+        int it = 0, ph = 0;
+        bool stop = false;
+        for (int u = unit_lo; u < unit_hi && !stop; ++u) {
+            const Unit un = decode_unit(P, u, ph);
+            const TcProblem& pr = P.prob[un.p];
+            for (int ks = un.ks0; ks < un.ks1; ++ks, ++it) {
+                const int s = it % kStages;
+                uint8_t* st = smem + s * kStageBytes;
+                const size_t blk = static_cast<size_t>(un.rt) * pr.k_stages + ks;
+                int bad = 0;
+                if (lane == 0) {
+                    if (*abort_flag) {
+                        bad = 1;
+                    } else if (it >= pre) {
                         if (it >= kStages && !mbar_wait_bounded(&ctl->empty[s], ((it / kStages) - 1) & 1)) {
                             record_error(kErrGemmEmptyBarrierTimeout);
                             *abort_flag = 1;
-                            break;
+                            bad = 1;
+                        } else {
+                            mbar_expect_tx(&ctl->full[s], kWBlock + xbytes);
                         }
-                        mbar_expect_tx(&ctl->full[s], kWBlock + xbytes);
-                        bulk_copy_g2s(st, pr.w_image + blk * kWBlock, kWBlock, &ctl->full[s]);
                     }
+                }
+                bad = __shfl_sync(0xffffffffu, bad, 0);
+                if (bad) {
+                    stop = true;
+                    break;
+                }
+                if (lane < 4) {
+                    if (it >= pre) {
+                        bulk_copy_g2s(st + lane * kQuarter, pr.w_image + blk * kWBlock + lane * kQuarter, kQuarter,
+                                      &ctl->full[s]);
+                    }
+                } else if (lane == 4) {
                     bulk_copy_g2s(st + kWBlock, pr.x_image + static_cast<size_t>(ks) * xbytes, xbytes, &ctl->full[s]);
                 }
             }
@@ -203,9 +249,19 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             const uint32_t idesc = tc::make_idesc_mxf4nvf4(NB);
-            int it = 0, unit_iter = 0, ph = 0;
-            for (int u = unit_lo; u < unit_hi && !*abort_flag; ++u, ++unit_iter) {
-                const Unit un = decode_unit(P, u, ph);
+            // descriptor words: (stage address >> 4) + constants; see tcgen05.cuh
+            const uint32_t base16 = smem_u32(smem) >> 4;
+            const uint32_t stage16 = static_cast<uint32_t>(kStageBytes) >> 4;
+            const uint32_t off_sfb16 = static_cast<uint32_t>(kWBlock + NB * 128) >> 4;
+            const uint32_t t_sfa = tmem_base + kSfaCol;
+            const uint32_t t_sfb = tmem_base + kSfbCol;
+            int s = 0;
+            uint32_t full_phase = 0;
+            uint32_t lo0 = base16;
+            int unit_iter = 0, ph = 0;
+            for (int u = unit_lo; u < unit_hi && !*abort_flag; ++unit_iter) {
+                const Group un = decode_group(P, u, unit_hi, ph);
+                u = un.next;
                 const int buf = unit_iter & 1;
                 if (unit_iter >= 2 && !mbar_wait_bounded(&ctl->acc_empty[buf], ((unit_iter >> 1) - 1) & 1)) {
                     record_error(kErrGemmEpilogueBarrierTimeout);
@@ -214,35 +270,41 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
                 }
                 tc::fence_after_thread_sync();
                 const uint32_t tmem_acc = tmem_base + buf * 128;
-                for (int ks = un.ks0; ks < un.ks1; ++ks, ++it) {
-                    const int s = it % kStages;
-                    if (!mbar_wait_bounded(&ctl->full[s], (it / kStages) & 1)) {
+                uint32_t accumulate = 0;
+                for (int ks = un.ks0; ks < un.ks1; ++ks) {
+                    if (!mbar_wait_bounded(&ctl->full[s], full_phase)) {
                         record_error(kErrGemmTmaBarrierTimeout);
                         *abort_flag = 1;
                         break;
                     }
                     tc::fence_after_thread_sync();
-                    const uint32_t st = smem_u32(smem + s * kStageBytes);
-                    const uint32_t sfa_s = st + 2 * kWTile;          // two slabs: rows 0..127, 128..255
-                    const uint32_t xt_s = st + kWBlock;
-                    const uint32_t sfb_s = xt_s + NB * 128;
+                    // stage: [codes rows 0..127][codes rows 128..255][slab 0..127][slab 128..255][x codes][x slab]
 #pragma unroll
                     for (int a = 0; a < 4; ++a) {
-                        tc::cp_sf_32x128b(tmem_base + kSfaCol + 4 * a, tc::make_sf_desc(sfa_s + a * 512));
-                        tc::cp_sf_32x128b(tmem_base + kSfaCol + 16 + 4 * a, tc::make_sf_desc(sfa_s + kSfSlab + a * 512));
-                        tc::cp_sf_32x128b(tmem_base + kSfbCol + 4 * a, tc::make_sf_desc(sfb_s + a * 512));
+                        tc::cp_sf_32x128b(t_sfa + 4 * a, tc::desc_from_words(lo0 + ((2 * kWTile + a * 512) >> 4), tc::kDescHiSfAtom));
+                        tc::cp_sf_32x128b(t_sfa + 16 + 4 * a,
+                                          tc::desc_from_words(lo0 + ((2 * kWTile + kSfSlab + a * 512) >> 4), tc::kDescHiSfAtom));
+                        tc::cp_sf_32x128b(t_sfb + 4 * a, tc::desc_from_words(lo0 + off_sfb16 + ((a * 512) >> 4), tc::kDescHiSfAtom));
                     }
 #pragma unroll
                     for (int a = 0; a < 4; ++a) {
+                        const uint64_t xdesc = tc::desc_from_words(lo0 + ((kWBlock + a * 32) >> 4), tc::kDescHiKmajorSw128);
 #pragma unroll
                         for (int h = 0; h < 2; ++h) {
-                            tc::mma_mxf4nvf4(tmem_acc + h * kMaxNB, tc::make_kmajor_sw128_desc(st + h * kWTile, a * 32),
-                                             tc::make_kmajor_sw128_desc(xt_s, a * 32), idesc,
-                                             tmem_base + kSfaCol + 16 * h + 4 * a, tmem_base + kSfbCol + 4 * a,
-                                             (ks > un.ks0) || (a != 0));
+                            tc::mma_mxf4nvf4(tmem_acc + h * kMaxNB,
+                                             tc::desc_from_words(lo0 + ((h * kWTile + a * 32) >> 4), tc::kDescHiKmajorSw128),
+                                             xdesc, idesc, t_sfa + 16 * h + 4 * a, t_sfb + 4 * a, a == 0 ? accumulate : 1u);
                         }
                     }
+                    accumulate = 1;
                     tc::commit(&ctl->empty[s]);
+                    if (++s == kStages) {
+                        s = 0;
+                        full_phase ^= 1;
+                        lo0 = base16;
+                    } else {
+                        lo0 += stage16;
+                    }
                 }
                 tc::commit(&ctl->acc_full[buf]);
             }
@@ -253,8 +315,9 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
         const int et = q * 32 + lane;            // 0..127: the weight row inside the tile
         int unit_iter = 0, ph = 0;
         pdl_wait_prior_grids();                   // the output buffer may still be read by the previous kernel
-        for (int u = unit_lo; u < unit_hi && !*abort_flag; ++u, ++unit_iter) {
-            const Unit un = decode_unit(P, u, ph);
+        for (int u = unit_lo; u < unit_hi && !*abort_flag; ++unit_iter) {
+            const Group un = decode_group(P, u, unit_hi, ph);
+            u = un.next;
             const TcProblem& pr = P.prob[un.p];
             const int buf = unit_iter & 1;
             if (!mbar_wait_bounded(&ctl->acc_full[buf], (unit_iter >> 1) & 1)) {
@@ -283,21 +346,31 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
 
             const int n_pad = pr.row_tiles * 256;
             bool finalize = true;
-            if (pr.splits > 1) {
+            if (un.split0 != 0 || un.split1 != pr.splits - 1) {
+                // this group covers only part of the tile's K range: hand its sums over.  The tile's groups
+                // start at its first unit and wherever a CTA's range begins inside it.
+                const int t0 = pr.unit_begin + un.rt * pr.splits;
+                const long long total = P.total_units;
+                const int grid = gridDim.x;
+                const int b_first = static_cast<int>((static_cast<long long>(t0) * grid) / total) + 1;
+                int ngroups = 1;
+                for (int b = b_first; b < grid && static_cast<int>(b * total / grid) < t0 + pr.splits; ++b) {
+                    if (static_cast<int>(b * total / grid) > t0) ++ngroups;
+                }
                 float* part = P.scratch + pr.scratch_off;
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     const int n = un.rt * 256 + h * 128 + et;
 #pragma unroll
                     for (int t = 0; t < 16; ++t) {
-                        if (t < P.M) part[(static_cast<size_t>(un.split) * 16 + t) * n_pad + n] = v[h][t];
+                        if (t < P.M) part[(static_cast<size_t>(un.split0) * 16 + t) * n_pad + n] = v[h][t];
                     }
                 }
                 __threadfence();
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (et == 0) ctl->ticket = atomicAdd(P.counters + pr.counter_off + un.rt, 1);
                 asm volatile("bar.sync 1, 128;" ::: "memory");
-                finalize = (ctl->ticket == pr.splits - 1);
+                finalize = (ctl->ticket == ngroups - 1);
                 if (finalize) {
                     __threadfence();
 #pragma unroll
@@ -306,9 +379,10 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
 #pragma unroll
                         for (int t = 0; t < 16; ++t) {
                             if (t < P.M) {
-                                float acc = 0.0f;
-                                for (int sp = 0; sp < pr.splits; ++sp) {
-                                    acc += __ldcg(part + (static_cast<size_t>(sp) * 16 + t) * n_pad + n);
+                                float acc = __ldcg(part + static_cast<size_t>(t) * n_pad + n);       // group at split 0
+                                for (int b = b_first; b < grid && static_cast<int>(b * total / grid) < t0 + pr.splits; ++b) {
+                                    const int sp = static_cast<int>(b * total / grid) - t0;
+                                    if (sp > 0) acc += __ldcg(part + (static_cast<size_t>(sp) * 16 + t) * n_pad + n);
                                 }
                                 v[h][t] = acc;
                             }
@@ -525,18 +599,6 @@ extern "C" int tpb200_nvfp4_quantize_acts_tc(const tpb200_act_tc* acts, int coun
         A.K[i] = h.K;
         A.image[i] = static_cast<uint8_t*>(h.x_image);
         A.row_scale[i] = h.x_row_scale;
-    }
-    // same shared-memory carve-out as the GEMV that follows, so the SMs do not reconfigure in between
-    static std::atomic<uint64_t> configured{0};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return TPB200_ERR_CUDA;
-    const uint64_t bit = 1ull << (dev & 63);
-    if (!(configured.load(std::memory_order_relaxed) & bit)) {
-        if (cudaFuncSetAttribute(tpb::quantize_pieces_tiled_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                 cudaSharedmemCarveoutMaxShared) != cudaSuccess) {
-            return TPB200_ERR_CUDA;
-        }
-        configured.fetch_or(bit, std::memory_order_relaxed);
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(16, count, 1);

@@ -259,49 +259,76 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
     volatile int* abort_flag = &ctl->abort_flag;
 
     if (warp == 0) {
-        // ------------------------------------------------------------ TMA producer
-        if (lane == 0) {
-            if (!kTiled) {
-                tc::prefetch_tensormap(&P.map_a);
-                tc::prefetch_tensormap(&P.map_b);
-            }
-            const int sf_row_stride = P.k_stages * kSfSlab;   // bytes per 128-row tile of scales
-            int it = 0;
-            for (int w = blockIdx.x; w < total_items && !*abort_flag; w += gridDim.x) {
-                const int tile = w / splits;
-                const int ks0 = (w - tile * splits) * P.stages_per_split;
-                const int ks1 = min(P.k_stages, ks0 + P.stages_per_split);
-                const int m_blk = tile % P.m_blocks;
-                const int n_blk = tile / P.m_blocks;
-                for (int ks = ks0; ks < ks1; ++ks, ++it) {
-                    const int s = it % nstages;
-                    if (it >= nstages && !mbar_wait_bounded(&ctl->empty[s], ((it / nstages) - 1) & 1)) {
+        // ------------------------------------------------------------ producer (whole warp).
+        // Lane 0 owns the barrier hand-shakes; the stage's copy requests are issued by DIFFERENT lanes.  A
+        // thread that issues a bulk copy is held for ~0.3 us whatever the size, so one lane issuing a stage's
+        // requests back to back tops out near 60-90 GB/s per SM; the same requests issued side by side from
+        // several lanes reach ~130 GB/s.  Tiled form: the stage is (2 + pieces) chunks of 18 KB, one per lane
+        // (two from the B block, the rest from the contiguous A block).  Row-major form: one lane per box.
+        if (!kTiled && lane == 0) {
+            tc::prefetch_tensormap(&P.map_a);
+            tc::prefetch_tensormap(&P.map_b);
+        }
+        const int sf_row_stride = P.k_stages * kSfSlab;   // bytes per 128-row tile of scales
+        int s = 0;
+        uint32_t empty_phase = 0;
+        bool wrapped = false;                              // the first pass over the ring finds every stage free
+        bool stop = false;
+        for (int w = blockIdx.x; w < total_items && !stop; w += gridDim.x) {
+            const int tile = w / splits;
+            const int ks0 = (w - tile * splits) * P.stages_per_split;
+            const int ks1 = min(P.k_stages, ks0 + P.stages_per_split);
+            const int m_blk = tile % P.m_blocks;
+            const int n_blk = tile / P.m_blocks;
+            for (int ks = ks0; ks < ks1; ++ks) {
+                int bad = 0;
+                if (lane == 0) {
+                    if (*abort_flag) {
+                        bad = 1;
+                    } else if (wrapped && !mbar_wait_bounded(&ctl->empty[s], empty_phase)) {
                         record_error(kErrGemmEmptyBarrierTimeout);
                         *abort_flag = 1;
-                        break;
+                        bad = 1;
+                    } else {
+                        mbar_expect_tx(&ctl->full[s], stage_sz);
                     }
-                    uint8_t* st = smem + s * stage_sz;
-                    mbar_expect_tx(&ctl->full[s], stage_sz);
-                    if (kTiled) {
-                        bulk_copy_g2s(st, P.b_image + (static_cast<size_t>(n_blk) * P.k_stages + ks) * (2 * kBlock),
-                                      2 * kBlock, &ctl->full[s]);
-                        bulk_copy_g2s(st + off_a,
-                                      P.a_image + (static_cast<size_t>(m_blk) * P.k_stages + ks) * (pieces * kBlock),
-                                      pieces * kBlock, &ctl->full[s]);
-                        continue;
+                }
+                bad = __shfl_sync(0xffffffffu, bad, 0);
+                if (bad) {
+                    stop = true;
+                    break;
+                }
+                uint8_t* st = smem + s * stage_sz;
+                if (kTiled) {
+                    if (lane < 2 + pieces) {
+                        const uint8_t* src =
+                            lane < 2 ? P.b_image + (static_cast<size_t>(n_blk) * P.k_stages + ks) * (2 * kBlock) + lane * kBlock
+                                     : P.a_image + (static_cast<size_t>(m_blk) * P.k_stages + ks) * (pieces * kBlock) +
+                                           (lane - 2) * kBlock;
+                        bulk_copy_g2s(st + lane * kBlock, src, kBlock, &ctl->full[s]);
                     }
+                } else if (lane == 0) {
                     tc::tma_load_2d(st, &P.map_b, ks * kBKBytes, n_blk * kBN, &ctl->full[s]);
+                } else if (lane == 1) {
                     bulk_copy_g2s(st + off_sfb,
                                   P.sfb + static_cast<size_t>(n_blk) * sf_row_stride + static_cast<size_t>(ks) * kSfSlab,
                                   kSfSlab, &ctl->full[s]);
-                    for (int p = 0; p < pieces; ++p) {
-                        const int a_row_tile = p * (P.a_piece_rows >> 7) + m_blk;
+                } else if (lane < 2 + 2 * pieces) {
+                    const int p = (lane - 2) >> 1;
+                    const int a_row_tile = p * (P.a_piece_rows >> 7) + m_blk;
+                    if ((lane & 1) == 0) {
                         tc::tma_load_2d(st + off_a + p * kTile, &P.map_a, ks * kBKBytes, a_row_tile * kBM, &ctl->full[s]);
+                    } else {
                         bulk_copy_g2s(st + off_sfa + p * kSfSlab,
                                       P.sfa + static_cast<size_t>(a_row_tile) * sf_row_stride +
                                           static_cast<size_t>(ks) * kSfSlab,
                                       kSfSlab, &ctl->full[s]);
                     }
+                }
+                if (++s == nstages) {
+                    s = 0;
+                    empty_phase ^= wrapped ? 1u : 0u;
+                    wrapped = true;
                 }
             }
         }
@@ -309,7 +336,18 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc = tc::make_idesc_mxf4nvf4(kBN);
-            int it = 0, tile_iter = 0;
+            // descriptor words: (stage base >> 4) + compile-time offsets; see tcgen05.cuh
+            const uint32_t stage16 = static_cast<uint32_t>(stage_sz) >> 4;
+            const uint32_t off_a16 = static_cast<uint32_t>(off_a) >> 4;
+            const uint32_t off_sfb16 = static_cast<uint32_t>(off_sfb) >> 4;
+            const uint32_t off_sfa16 = static_cast<uint32_t>(off_sfa) >> 4;
+            const uint32_t base16 = smem_u32(smem) >> 4;
+            const uint32_t t_sfa = tmem_base + kSfaCol;
+            const uint32_t t_sfb = tmem_base + kSfbCol;
+            int s = 0;
+            uint32_t full_phase = 0;
+            uint32_t lo0 = base16;                 // descriptor word of the current stage's first byte
+            int tile_iter = 0;
             for (int w = blockIdx.x; w < total_items && !*abort_flag; w += gridDim.x, ++tile_iter) {
                 const int ks0 = (w % splits) * P.stages_per_split;
                 const int ks1 = min(P.k_stages, ks0 + P.stages_per_split);
@@ -322,40 +360,52 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
                 }
                 tc::fence_after_thread_sync();
                 const uint32_t tmem_acc = tmem_base + buf * 128;
-                for (int ks = ks0; ks < ks1; ++ks, ++it) {
-                    const int s = it % nstages;
-                    if (!mbar_wait_bounded(&ctl->full[s], (it / nstages) & 1)) {
+                uint32_t accumulate = 0;           // the first MMA of the item overwrites the accumulator
+                for (int ks = ks0; ks < ks1; ++ks) {
+                    if (!mbar_wait_bounded(&ctl->full[s], full_phase)) {
                         record_error(kErrGemmTmaBarrierTimeout);
                         *abort_flag = 1;
                         break;
                     }
                     tc::fence_after_thread_sync();
-                    const uint32_t st = smem_u32(smem + s * stage_sz);
                     // B scales of K atom a sit in kSubTiles * 4 consecutive columns (4 per 128 rows)
 #pragma unroll
                     for (int a = 0; a < 4; ++a) {
 #pragma unroll
                         for (int h = 0; h < kSubTiles; ++h) {
-                            tc::cp_sf_32x128b(tmem_base + kSfbCol + 4 * (kSubTiles * a + h),
-                                              tc::make_sf_desc(st + off_sfb + h * kSfSlab + a * 512));
+                            tc::cp_sf_32x128b(t_sfb + 4 * (kSubTiles * a + h),
+                                              tc::desc_from_words(lo0 + off_sfb16 + ((h * kSfSlab + a * 512) >> 4),
+                                                                  tc::kDescHiSfAtom));
                         }
                     }
+                    uint32_t lo_a = lo0 + off_a16;         // piece p's code tile
+                    uint32_t lo_sfa = lo0 + off_sfa16;     // piece p's scale slab
+                    uint32_t t_sfa_p = t_sfa;
                     for (int p = 0; p < pieces; ++p) {
 #pragma unroll
                         for (int a = 0; a < 4; ++a) {
-                            tc::cp_sf_32x128b(tmem_base + kSfaCol + 16 * p + 4 * a,
-                                              tc::make_sf_desc(st + off_sfa + p * kSfSlab + a * 512));
+                            tc::cp_sf_32x128b(t_sfa_p + 4 * a,
+                                              tc::desc_from_words(lo_sfa + ((a * 512) >> 4), tc::kDescHiSfAtom));
                         }
 #pragma unroll
                         for (int a = 0; a < 4; ++a) {
-                            tc::mma_mxf4nvf4(tmem_acc, tc::make_kmajor_sw128_desc(st + off_a + p * kTile, a * 32),
-                                             tc::make_kmajor_sw128_desc(st, a * 32), idesc,
-                                             tmem_base + kSfaCol + 16 * p + 4 * a,
-                                             tmem_base + kSfbCol + 4 * kSubTiles * a,
-                                             ((ks - ks0) | p | a) != 0);
+                            tc::mma_mxf4nvf4(tmem_acc, tc::desc_from_words(lo_a + ((a * 32) >> 4), tc::kDescHiKmajorSw128),
+                                             tc::desc_from_words(lo0 + ((a * 32) >> 4), tc::kDescHiKmajorSw128), idesc,
+                                             t_sfa_p + 4 * a, t_sfb + 4 * kSubTiles * a, accumulate);
+                            accumulate = 1;
                         }
+                        lo_a += kTile >> 4;
+                        lo_sfa += kSfSlab >> 4;
+                        t_sfa_p += 16;
                     }
                     tc::commit(&ctl->empty[s]);   // stage s may be refilled once these MMAs have read it
+                    if (++s == nstages) {
+                        s = 0;
+                        full_phase ^= 1;
+                        lo0 = base16;
+                    } else {
+                        lo0 += stage16;
+                    }
                 }
                 tc::commit(&ctl->acc_full[buf]);  // accumulator complete
             }

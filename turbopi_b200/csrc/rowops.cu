@@ -9,7 +9,6 @@
 // the transformed row and the updated residual stream are written only when asked for.
 // One CTA per row; every thread keeps its 16-element blocks in registers (K <= 16384).
 #include <algorithm>
-#include <atomic>
 
 #include "common.cuh"
 
@@ -315,20 +314,6 @@ extern "C" int tpb200_row_transform_quantize(const tpb200_rowop_args* a, tpb200_
     P.piece_rows = a->piece_rows;
     P.kb_pad = (a->K + 255) / 256 * 16;
     P.tiled = a->layout == TPB200_OPERANDS_TILED;
-    // Ask for the largest shared-memory carve-out although this kernel needs almost none: it runs between
-    // tensor-core GEMMs that take 218 KB, and an SM that has to change its L1 / shared-memory split between
-    // two kernels sits idle while it does.
-    static std::atomic<uint64_t> configured{0};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return TPB200_ERR_CUDA;
-    const uint64_t bit = 1ull << (dev & 63);
-    if (!(configured.load(std::memory_order_relaxed) & bit)) {
-        if (cudaFuncSetAttribute(tpb::row_transform_quantize_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                 cudaSharedmemCarveoutMaxShared) != cudaSuccess) {
-            return TPB200_ERR_CUDA;
-        }
-        configured.fetch_or(bit, std::memory_order_relaxed);
-    }
     const int threads = std::min(tpb::kThreads, (P.kb_pad + 31) / 32 * 32);
     tpb::row_transform_quantize_kernel<<<a->M, threads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(P);
     return tpb_launch_status();

@@ -67,6 +67,18 @@ __device__ __forceinline__ uint64_t make_sf_desc(uint32_t atom_smem_addr) {
     return make_smem_desc(atom_smem_addr, 0, 128, kSwizzleNone);
 }
 
+// The same descriptors split into 32-bit words.  The thread that issues the MMAs spends ~60 cycles per
+// tcgen05 instruction when every descriptor is assembled with 64-bit arithmetic, and it is ONE thread: in
+// a loop of 20-30 instructions per stage that is the kernel's critical path.  The upper word of a
+// descriptor is a constant of its kind; the lower word is (shared-memory address >> 4) plus constants.
+constexpr uint32_t kDescHiKmajorSw128 = (1024u >> 4) | (1u << 14) | (static_cast<uint32_t>(kSwizzle128B) << 29);
+constexpr uint32_t kDescHiSfAtom = (128u >> 4) | (1u << 14);
+__device__ __forceinline__ uint64_t desc_from_words(uint32_t lo, uint32_t hi) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+    return d;
+}
+
 // Instruction descriptor for kind::mxf4nvf4 (e2m1 x e2m1, UE4M3 scales per 16, K = 64), M = 128:
 //   [7,10) A format = 1 (e2m1)  [10,13) B format = 1  [15],[16] K-major  [17,23) N >> 3
 //   [23] scale format 0 = UE4M3  [24,29) M >> 4  [4,6)/[29,31) scale-factor byte ids = 0
@@ -76,14 +88,14 @@ __host__ __device__ constexpr uint32_t make_idesc_mxf4nvf4(int n) {
 
 // D[tmem] (+)= A[smem] * B[smem]^T with block scales read from tensor memory
 __device__ __forceinline__ void mma_mxf4nvf4(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                             uint32_t tmem_sfa, uint32_t tmem_sfb, bool accumulate) {
+                                             uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
     asm volatile(
         "{\n"
         " .reg .pred p;\n"
         " setp.ne.b32 p, %4, 0;\n"
         " tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n"
         "}\n" ::"r"(tmem_d),
-        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(static_cast<uint32_t>(accumulate)), "r"(tmem_sfa), "r"(tmem_sfb)
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
         : "memory");
 }
 
