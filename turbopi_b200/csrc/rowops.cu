@@ -15,7 +15,7 @@
 namespace tpb {
 namespace {
 
-constexpr int kThreads = 1024;   // one 16-element block per thread: K <= 16384
+constexpr int kThreads = 512;    // up to two 16-element blocks per thread: K <= 16384
 constexpr int kMaxK = 16384;
 
 struct RowOpParams {
@@ -101,11 +101,12 @@ __device__ __forceinline__ void store16_bf16(__nv_bfloat16* p, const float (&v)[
     q[1] = make_uint4(w[4], w[5], w[6], w[7]);
 }
 
-// One CTA per row, one thread per 16-element block (32 .. 1024 threads): the block stays in registers
-// from the global load to the code store; the only shared memory is the scratch of the block-wide
-// reductions.
+// One CTA per row; thread t owns the 16-element blocks t and (for rows longer than 8192) t + T and keeps
+// them in registers from the global load to the code store; the only shared memory is the scratch of the
+// block-wide reductions.  512 threads x 2 blocks instead of 1024 x 1 for the longest rows: two CTAs fit an
+// SM's register file, so one row's reductions overlap the other's arithmetic.
+template <int NB>
 __global__ void __launch_bounds__(kThreads) row_transform_quantize_kernel(const __grid_constant__ RowOpParams P) {
-    constexpr int NB = 1;
     __shared__ float red[kThreads / 32];
     const int m = blockIdx.x;
     const int K = P.K;
@@ -315,6 +316,10 @@ extern "C" int tpb200_row_transform_quantize(const tpb200_rowop_args* a, tpb200_
     P.kb_pad = (a->K + 255) / 256 * 16;
     P.tiled = a->layout == TPB200_OPERANDS_TILED;
     const int threads = std::min(tpb::kThreads, (P.kb_pad + 31) / 32 * 32);
-    tpb::row_transform_quantize_kernel<<<a->M, threads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(P);
+    if (P.kb_pad <= tpb::kThreads) {
+        tpb::row_transform_quantize_kernel<1><<<a->M, threads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(P);
+    } else {
+        tpb::row_transform_quantize_kernel<2><<<a->M, threads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(P);
+    }
     return tpb_launch_status();
 }
