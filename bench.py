@@ -36,9 +36,9 @@ HIDDEN, INTER = 1024, 4096
 SHAPES = [(INTER, HIDDEN), (INTER, HIDDEN), (HIDDEN, INTER)]      # (N, K): gate, up, down
 BLOCK = 16
 NSETS = 4
-# dram__bytes_read.sum + dram__bytes_write.sum of one grouped launch over this workload, from the ncu
-# capture summarised in profiles/gemv_rowmajor_grouped54.md (127.46 MB read + 3.97 MB written)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 131436544
+# dram__bytes_read.sum + dram__bytes_write.sum of one grouped launch over this workload, from ncu captures of
+# the two kernels (CUDA-core: 127.46 MB read + 3.97 MB written; tensor-core: 127.68 MB + 5.53 MB)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = {"cuda": 131436544, "tc": 133206528}
 METRIC = "nvfp4_gemv_hbm_gbps"
 UNIT = "GB/s"
 
@@ -247,12 +247,15 @@ def run_ours(args):
         total_bytes = STEP_BYTES * args.steps * world
         value = total_bytes / (ms / 1e3) / 1e9
         achieved = STEP_BYTES / per_launch_s / 1e9
-        traffic = NCU_TRAFFIC_BYTES_PER_LAUNCH
+        traffic = NCU_TRAFFIC_BYTES_PER_LAUNCH[args.path]
         cpu = cpu_baseline_sample() if world == 1 else None
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": "f16 products / f32 accumulate", "data": "synthetic",
+            "vs_baseline": None,
+            "dtype": ("f16 products / f32 accumulate" if tcs is None else
+                      "e2m1 x e2m1 block-scaled tensor-core products / f32 accumulate (bf16 activations as 3 e2m1 pieces)"),
+            "data": "synthetic",
             "config": {"workload": "NVFP4 weight-only GEMV, M=1, Gemma-300M action-expert MLP, 18 layers x "
                                    "(gate,up 1024->4096; down 4096->1024) = 54 matrices per step, E4M3 block-16 "
                                    "scales + fp32 global scale, bf16 in/out",
