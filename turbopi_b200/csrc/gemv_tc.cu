@@ -50,11 +50,13 @@ __host__ __device__ constexpr int stage_bytes(int pieces) { return kWBlock + 16 
 __host__ __device__ constexpr int num_stages(int pieces) {
     return (227 * 1024 - 2048) / stage_bytes(pieces) < kMaxStages ? (227 * 1024 - 2048) / stage_bytes(pieces) : kMaxStages;
 }
-constexpr int kThreads = 192;
+constexpr int kThreads = 224;          // warps: 0 producer, 1 MMA issuer, 2..5 epilogue, 6 scale copier
 constexpr int kTmemCols = 512;
 // tensor memory: accumulator (buffer b, row half h) at column b * 128 + h * 64, then the scales
-constexpr uint32_t kSfaCol = 256;              // weights: 16 columns per row half
-constexpr uint32_t kSfbCol = kSfaCol + 32;     // activations
+// two sets of scale columns (stages alternate): 32 for the weights' two row halves + 16 for the activations
+constexpr uint32_t kSfSetCols = 48;
+constexpr uint32_t kSfaCol = 256;
+constexpr uint32_t kSfbCol = kSfaCol + 32;
 constexpr int kMaxProblems = TPB200_MAX_GROUP;
 
 struct TcProblem {
@@ -91,6 +93,8 @@ struct SharedControl {
     uint64_t empty[kMaxStages];
     uint64_t acc_full[2];
     uint64_t acc_empty[2];
+    uint64_t sf_full[2];      // scale set j copied into tensor memory (arrives through tcgen05.commit)
+    uint64_t sf_empty[2];     // the MMAs that read scale set j are done
     uint32_t tmem_base;
     int abort_flag;
     int ticket;
@@ -164,6 +168,8 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
         for (int b = 0; b < 2; ++b) {
             mbar_init(&ctl->acc_full[b], 1);
             mbar_init(&ctl->acc_empty[b], 4);
+            mbar_init(&ctl->sf_full[b], 1);
+            mbar_init(&ctl->sf_empty[b], 1);
         }
         ctl->abort_flag = 0;
         fence_mbar_init();
@@ -252,12 +258,12 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
             // descriptor words: (stage address >> 4) + constants; see tcgen05.cuh
             const uint32_t base16 = smem_u32(smem) >> 4;
             const uint32_t stage16 = static_cast<uint32_t>(kStageBytes) >> 4;
-            const uint32_t off_sfb16 = static_cast<uint32_t>(kWBlock + NB * 128) >> 4;
             const uint32_t t_sfa = tmem_base + kSfaCol;
             const uint32_t t_sfb = tmem_base + kSfbCol;
             int s = 0;
             uint32_t full_phase = 0;
             uint32_t lo0 = base16;
+            uint32_t g = 0;                        // stages issued so far; stage g uses scale set g & 1
             int unit_iter = 0, ph = 0;
             for (int u = unit_lo; u < unit_hi && !*abort_flag; ++unit_iter) {
                 const Group un = decode_group(P, u, unit_hi, ph);
@@ -278,14 +284,16 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
                         break;
                     }
                     tc::fence_after_thread_sync();
-                    // stage: [codes rows 0..127][codes rows 128..255][slab 0..127][slab 128..255][x codes][x slab]
-#pragma unroll
-                    for (int a = 0; a < 4; ++a) {
-                        tc::cp_sf_32x128b(t_sfa + 4 * a, tc::desc_from_words(lo0 + ((2 * kWTile + a * 512) >> 4), tc::kDescHiSfAtom));
-                        tc::cp_sf_32x128b(t_sfa + 16 + 4 * a,
-                                          tc::desc_from_words(lo0 + ((2 * kWTile + kSfSlab + a * 512) >> 4), tc::kDescHiSfAtom));
-                        tc::cp_sf_32x128b(t_sfb + 4 * a, tc::desc_from_words(lo0 + off_sfb16 + ((a * 512) >> 4), tc::kDescHiSfAtom));
+                    // the scale copier (warp 6) has moved this stage's scales into set g & 1
+                    const uint32_t set = g & 1u;
+                    if (!mbar_wait_bounded(&ctl->sf_full[set], (g >> 1) & 1u)) {
+                        record_error(kErrGemmTmaBarrierTimeout);
+                        *abort_flag = 1;
+                        break;
                     }
+                    tc::fence_after_thread_sync();
+                    const uint32_t sfa = t_sfa + set * kSfSetCols;
+                    const uint32_t sfb = t_sfb + set * kSfSetCols;
 #pragma unroll
                     for (int a = 0; a < 4; ++a) {
                         const uint64_t xdesc = tc::desc_from_words(lo0 + ((kWBlock + a * 32) >> 4), tc::kDescHiKmajorSw128);
@@ -293,11 +301,13 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
                         for (int h = 0; h < 2; ++h) {
                             tc::mma_mxf4nvf4(tmem_acc + h * kMaxNB,
                                              tc::desc_from_words(lo0 + ((h * kWTile + a * 32) >> 4), tc::kDescHiKmajorSw128),
-                                             xdesc, idesc, t_sfa + 16 * h + 4 * a, t_sfb + 4 * a, a == 0 ? accumulate : 1u);
+                                             xdesc, idesc, sfa + 16 * h + 4 * a, sfb + 4 * a, a == 0 ? accumulate : 1u);
                         }
                     }
                     accumulate = 1;
                     tc::commit(&ctl->empty[s]);
+                    tc::commit(&ctl->sf_empty[set]);
+                    ++g;
                     if (++s == kStages) {
                         s = 0;
                         full_phase ^= 1;
@@ -309,7 +319,56 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
                 tc::commit(&ctl->acc_full[buf]);
             }
         }
-    } else {
+    } else if (warp == 6) {
+        // ------------------------------------------------------------ scale copier.
+        // One thread issues every tcgen05 instruction it is given at ~60 cycles apiece; with the 12 scale
+        // copies of a stage on the MMA thread that thread, not the weight stream, set the pace.  Here they
+        // run one stage ahead into the other set of scale columns.  The copies do not depend on the tile, so
+        // this lane only needs the number of stages its CTA walks.
+        if (lane == 0) {
+            int total = 0;
+            {
+                int ph = 0;
+                for (int u = unit_lo; u < unit_hi; ++u) {
+                    const Unit un = decode_unit(P, u, ph);
+                    total += un.ks1 - un.ks0;
+                }
+            }
+            const uint32_t base16 = smem_u32(smem) >> 4;
+            const uint32_t stage16 = static_cast<uint32_t>(kStageBytes) >> 4;
+            const uint32_t off_sfb16 = static_cast<uint32_t>(kWBlock + NB * 128) >> 4;
+            int s = 0;
+            uint32_t full_phase = 0, lo0 = base16;
+            for (int g = 0; g < total && !*abort_flag; ++g) {
+                const uint32_t set = g & 1;
+                if (!mbar_wait_bounded(&ctl->full[s], full_phase) ||
+                    (g >= 2 && !mbar_wait_bounded(&ctl->sf_empty[set], ((g >> 1) - 1) & 1))) {
+                    record_error(kErrGemmTmaBarrierTimeout);
+                    *abort_flag = 1;
+                    break;
+                }
+                tc::fence_after_thread_sync();
+                const uint32_t sfa = tmem_base + kSfaCol + set * kSfSetCols;
+                const uint32_t sfb = tmem_base + kSfbCol + set * kSfSetCols;
+                // stage: [codes rows 0..127][codes rows 128..255][slab 0..127][slab 128..255][x codes][x slab]
+#pragma unroll
+                for (int a = 0; a < 4; ++a) {
+                    tc::cp_sf_32x128b(sfa + 4 * a, tc::desc_from_words(lo0 + ((2 * kWTile + a * 512) >> 4), tc::kDescHiSfAtom));
+                    tc::cp_sf_32x128b(sfa + 16 + 4 * a,
+                                      tc::desc_from_words(lo0 + ((2 * kWTile + kSfSlab + a * 512) >> 4), tc::kDescHiSfAtom));
+                    tc::cp_sf_32x128b(sfb + 4 * a, tc::desc_from_words(lo0 + off_sfb16 + ((a * 512) >> 4), tc::kDescHiSfAtom));
+                }
+                tc::commit(&ctl->sf_full[set]);
+                if (++s == kStages) {
+                    s = 0;
+                    full_phase ^= 1;
+                    lo0 = base16;
+                } else {
+                    lo0 += stage16;
+                }
+            }
+        }
+    } else if (warp >= 2) {
         // ------------------------------------------------------------ epilogue (warps 2..5, 128 threads)
         const int q = warp & 3;
         const int et = q * 32 + lane;            // 0..127: the weight row inside the tile
