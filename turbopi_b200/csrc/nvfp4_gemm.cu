@@ -15,7 +15,8 @@
 //   warps 2-5  epilogue: tcgen05.ld, alpha / row scale / bias / activation (or rotary embedding for
 //              the fused QKV form), conversion, 128B-swizzled staging in shared memory and TMA
 //              tile stores (full-line writes, clipped at the matrix edge by the tensor map).
-// No multicast, no cluster; every wait is bounded and reports through the device error word.
+// One CTA per SM, no clusters: no operand is shared between CTAs; every wait is bounded and reports
+// through the device error word.
 //
 // Two operand formats.  Row-major (the reference's): tiles of 128 x 128 outputs, operands fetched with
 // tiled TMA boxes.  Tiled images (kTiled): both operands pre-arranged so that everything one K stage
