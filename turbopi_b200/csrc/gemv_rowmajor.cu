@@ -77,6 +77,20 @@ struct GemvParams {
     ProblemDev prob[MAXP];
 };
 
+// Index of the problem that owns `tile`, by bisection: the table lives in the kernel's parameter space, where
+// every dependent look-up with a computed index costs ~100 cycles, so a walk from entry 0 delays the CTAs of
+// the last problems by microseconds.
+template <int MAXP>
+__device__ __forceinline__ int find_problem(const GemvParams<MAXP>& P, int tile) {
+    int lo = 0, hi = P.num_problems - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (tile >= P.prob[mid].tile_begin) lo = mid;
+        else hi = mid - 1;
+    }
+    return lo;
+}
+
 __device__ __forceinline__ __half to_half_sat(float v) {
     return __float2half_rn(fminf(fmaxf(v, -65504.0f), 65504.0f));
 }
@@ -314,7 +328,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_rowmajor_kernel(const __grid
     const int tile_hi = static_cast<int>(static_cast<long long>(blockIdx.x + 1) * total_tiles / gridDim.x);
 
     // Producer (thread 0): request tile number `it` of this CTA.  `ip` follows the problem index.
-    int ip = 0;
+    int ip = find_problem(P, tile_lo);
     auto issue = [&](int it) {
         const int tile = tile_lo + it;
         if (tile >= tile_hi) return;
@@ -343,7 +357,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_rowmajor_kernel(const __grid
     pdl_wait_prior_grids();
 
     __half2 xr[M_TILE][CPL][16];
-    int p = 0, cur_p = -1;
+    int p = find_problem(P, tile_lo), cur_p = -1;
     int KP = 1, kp = 0, rw = 0, RW = kWarps, nchunks = 0;
 
     for (int it = 0;; ++it) {
@@ -455,7 +469,7 @@ __global__ void __launch_bounds__(kWsThreads, 2) gemv_rowmajor_ws_kernel(const _
     if (warp == kWarps) {
         // ---------------- producer: one lane streams this CTA's tiles through the ring ----------------
         if (lane == 0) {
-            int ip = 0;
+            int ip = find_problem(P, tile_lo);
             for (int it = 0; tile_lo + it < tile_hi; ++it) {
                 const int tile = tile_lo + it;
                 const int s = it % kStages;
@@ -484,7 +498,7 @@ __global__ void __launch_bounds__(kWsThreads, 2) gemv_rowmajor_ws_kernel(const _
     // ---------------- consumers ----------------
     pdl_wait_prior_grids();  // activations and the output buffer belong to earlier kernels until here
     __half2 xr[M_TILE][CPL][16];
-    int p = 0, cur_p = -1, nchunks = 0;
+    int p = find_problem(P, tile_lo), cur_p = -1, nchunks = 0;
     constexpr int RG = 4 / M_TILE;
     for (int it = 0; tile_lo + it < tile_hi; ++it) {
         const int tile = tile_lo + it;

@@ -114,6 +114,19 @@ struct Unit {
     int p, rt, split, ks0, ks1;
 };
 
+// Index of the problem that owns unit u, by bisection.  The problem table sits in the kernel's parameter
+// space and every dependent look-up with a computed index costs ~100 cycles; walking the table from its
+// start made the CTAs of the last problems begin their work 8 us after the first ones.
+__device__ __forceinline__ int find_problem(const TcParams& P, int u) {
+    int lo = 0, hi = P.num_problems - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (u >= P.prob[mid].unit_begin) lo = mid;
+        else hi = mid - 1;
+    }
+    return lo;
+}
+
 __device__ __forceinline__ Unit decode_unit(const TcParams& P, int u, int& p_hint) {
     while (p_hint + 1 < P.num_problems && u >= P.prob[p_hint + 1].unit_begin) ++p_hint;
     const TcProblem& pr = P.prob[p_hint];
@@ -159,6 +172,7 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
     const int NB = 16 * P.pieces;
     const int unit_lo = static_cast<int>(static_cast<long long>(blockIdx.x) * P.total_units / gridDim.x);
     const int unit_hi = static_cast<int>(static_cast<long long>(blockIdx.x + 1) * P.total_units / gridDim.x);
+    const int p_first = find_problem(P, unit_lo);     // every role starts its table walk here
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kMaxStages; ++s) {
@@ -196,7 +210,7 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
         constexpr uint32_t kQuarter = kWBlock / 4;
         int pre = 0;
         {
-            int ph = 0;
+            int ph = p_first;
             for (int u = unit_lo; u < unit_hi && pre < kStages; ++u) {
                 const Unit un = decode_unit(P, u, ph);
                 const TcProblem& pr = P.prob[un.p];
@@ -213,7 +227,7 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
             }
         }
         pdl_wait_prior_grids();
-        int it = 0, ph = 0;
+        int it = 0, ph = p_first;
         bool stop = false;
         for (int u = unit_lo; u < unit_hi && !stop; ++u) {
             const Unit un = decode_unit(P, u, ph);
@@ -264,7 +278,7 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
             uint32_t full_phase = 0;
             uint32_t lo0 = base16;
             uint32_t g = 0;                        // stages issued so far; stage g uses scale set g & 1
-            int unit_iter = 0, ph = 0;
+            int unit_iter = 0, ph = p_first;
             for (int u = unit_lo; u < unit_hi && !*abort_flag; ++unit_iter) {
                 const Group un = decode_group(P, u, unit_hi, ph);
                 u = un.next;
@@ -328,7 +342,7 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
         if (lane == 0) {
             int total = 0;
             {
-                int ph = 0;
+                int ph = p_first;
                 for (int u = unit_lo; u < unit_hi; ++u) {
                     const Unit un = decode_unit(P, u, ph);
                     total += un.ks1 - un.ks0;
@@ -372,7 +386,7 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
         // ------------------------------------------------------------ epilogue (warps 2..5, 128 threads)
         const int q = warp & 3;
         const int et = q * 32 + lane;            // 0..127: the weight row inside the tile
-        int unit_iter = 0, ph = 0;
+        int unit_iter = 0, ph = p_first;
         pdl_wait_prior_grids();                   // the output buffer may still be read by the previous kernel
         for (int u = unit_lo; u < unit_hi && !*abort_flag; ++unit_iter) {
             const Group un = decode_group(P, u, unit_hi, ph);
