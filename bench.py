@@ -148,7 +148,7 @@ def run_ours(args):
         for s in range(NSETS):
             probs = [dict(x=x[K], weight_packed=p, weight_scales=sc, global_scale=gs, out=oo)
                      for (p, sc, gs, N, K), oo in zip(sets[s], outs[s])]
-            tcs.append(ops.TcGemv(probs, pieces=3, pdl=args.pdl))
+            tcs.append(ops.TcGemv(probs, pieces=3, pdl=not args.no_pdl))
 
     def launch_step(i):
         if tcs is not None:
@@ -211,7 +211,7 @@ def run_ours(args):
             probs.append(dict(x=x[K], weight_packed=p, weight_scales=sc, out=out_flat[s][off:off + N].view(1, N),
                               global_scale=gs))
             off += N
-        e2e_groups.append(ops.GroupedGemv(probs, BLOCK) if tcs is None else ops.TcGemv(probs, pieces=3, pdl=args.pdl))
+        e2e_groups.append(ops.GroupedGemv(probs, BLOCK) if tcs is None else ops.TcGemv(probs, pieces=3, pdl=not args.no_pdl))
     h_out = torch.empty_like(out_flat[0], device="cpu").pin_memory()
     h2d = sum(t.numel() * t.element_size() for t in hx.values())
     d2h = h_out.numel() * h_out.element_size()
@@ -560,7 +560,8 @@ def main():
                     help="GEMV kernel: CUDA-core decode (cuda) or tensor-core (tc)")
     ap.add_argument("--no-graph", action="store_true", help="launch the step's kernels directly instead of one CUDA graph")
     ap.add_argument("--no-extras", action="store_true", help="skip the per-configuration side measurements")
-    ap.add_argument("--pdl", action="store_true", help="--path tc: programmatic dependent launch between quantiser and GEMV")
+    ap.add_argument("--no-pdl", action="store_true",
+                    help="--path tc: no programmatic dependent launch between quantiser and GEMV")
     ap.add_argument("--no-clock-warmup", action="store_true",
                     help="do exactly W warm-up steps (profiling runs); by default warm-up lasts >= 0.4 s")
     args = ap.parse_args()

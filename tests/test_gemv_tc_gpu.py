@@ -90,3 +90,43 @@ def test_tc_grouped_matches_cuda_core_gemv(cuda_device):
     ops.TcGemv(probs, pieces=3, activation=0).launch()
     for p, o in zip(probs, refs):
         assert rel_err(p["out"].float().cpu().numpy(), o.float().cpu().numpy()) <= 1e-2
+
+
+def test_tc_gemv_chain_under_programmatic_dependent_launch(cuda_device):
+    """Quantiser -> GEMV -> quantiser -> GEMV ... launched with programmatic stream serialisation (the GEMV
+    requests its first weight blocks while the quantiser still runs): same bytes as the plain launches,
+    also when the chain is captured in a CUDA graph and replayed."""
+    from turbopi_b200 import _lib, ops
+    rng = np.random.default_rng(77)
+    specs = [(4096, 1024), (4096, 1024), (1024, 4096)] * 3
+    xs = {K: _dev(formats.round_to_bf16(rng.normal(size=(1, K)).astype(np.float32)), cuda_device, torch.bfloat16)
+          for K in (1024, 4096)}
+    mats = [_weights(rng, N, K) for (N, K) in specs]
+
+    def build(pdl):
+        outs = [torch.zeros((1, N), dtype=torch.bfloat16, device=cuda_device) for (N, K) in specs]
+        tc = ops.TcGemv([dict(x=xs[K], weight_packed=_dev(p, cuda_device), weight_scales=_dev(s, cuda_device),
+                              global_scale=g, out=o) for (N, K), (p, s, g), o in zip(specs, mats, outs)],
+                        pieces=3, pdl=pdl)
+        return tc, outs
+
+    plain, want = build(False)
+    plain.launch()
+    chained, got = build(True)
+    for _ in range(3):
+        chained.launch()
+    torch.cuda.synchronize()
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
+    side = torch.cuda.Stream(device=cuda_device)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        chained.launch()
+        chained.launch()
+    for o in got:
+        o.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    for a, b in zip(got, want):
+        assert torch.equal(a, b)
+    assert _lib.load().tpb200_device_error(0) == 0
