@@ -178,6 +178,10 @@ typedef struct {
      * of a_pieces * 18432 bytes = one 128-row code tile per piece in the same chunk pattern, then one scale
      * slab per piece; a_pieces <= 3.  Padding rows / K must hold zero scales. */
     int layout;
+    /* TPB200_FLAG_PDL: launch with programmatic stream serialisation.  The kernel sets itself up (barriers,
+     * tensor memory) while the previous kernel of the stream is still running and waits for it before it
+     * reads an operand or writes a result. */
+    int flags;
 } tpb200_nvfp4_gemm_args;
 enum { TPB200_OPERANDS_ROWMAJOR = 0, TPB200_OPERANDS_TILED = 1 };
 size_t tpb200_nvfp4_gemm_workspace_size(int M, int N, int K, int a_pieces, int layout);
@@ -253,6 +257,7 @@ typedef struct {
     void* y_out;
     void* packed; int pitch; void* sf; float* row_scale; int pieces; int piece_rows;
     int layout;   /* TPB200_OPERANDS_TILED: `packed` is the GEMM's tiled A image (pitch, sf, piece_rows unused) */
+    int flags;    /* TPB200_FLAG_PDL: programmatic stream serialisation, as for the GEMM */
 } tpb200_rowop_args;
 int tpb200_row_transform_quantize(const tpb200_rowop_args* args, tpb200_stream_t stream);
 

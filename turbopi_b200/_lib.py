@@ -38,7 +38,7 @@ class GemmArgs(ctypes.Structure):
                 ("qkv_q_out", c_void_p), ("qkv_ldq", c_int), ("qkv_q_dim", c_int),
                 ("qkv_k_rows", c_void_p), ("qkv_v_rows", c_void_p),
                 ("qkv_positions", c_void_p), ("qkv_rope_cos", c_void_p), ("qkv_rope_sin", c_void_p),
-                ("workspace", c_void_p), ("workspace_bytes", c_size_t), ("layout", c_int)]
+                ("workspace", c_void_p), ("workspace_bytes", c_size_t), ("layout", c_int), ("flags", c_int)]
 
 
 class GemvTcProblem(ctypes.Structure):
@@ -56,7 +56,7 @@ class RowOpArgs(ctypes.Structure):
                 ("res_in", c_void_p), ("gate", c_void_p), ("h_out", c_void_p),
                 ("w0", c_void_p), ("w1", c_void_p), ("eps", c_float), ("y_out", c_void_p),
                 ("packed", c_void_p), ("pitch", c_int), ("sf", c_void_p), ("row_scale", c_void_p),
-                ("pieces", c_int), ("piece_rows", c_int), ("layout", c_int)]
+                ("pieces", c_int), ("piece_rows", c_int), ("layout", c_int), ("flags", c_int)]
 
 
 ROW_NONE, ROW_RMSNORM, ROW_ADARMS, ROW_LAYERNORM, ROW_GELU_MUL = 0, 1, 2, 3, 4

@@ -258,6 +258,11 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
     tc::fence_after_thread_sync();
     const uint32_t tmem_base = ctl->tmem_base;
     volatile int* abort_flag = &ctl->abort_flag;
+    // Programmatic dependent launch: everything above ran while the previous kernel of the stream may still
+    // have been running.  The producer (operands) and the epilogue (row scales, bias, results, split-K
+    // scratch) touch global memory, so they wait for it here; the MMA issuer only ever sees shared memory.
+    pdl_launch_dependents();
+    if (warp != 1) pdl_wait_prior_grids();
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer (whole warp).
@@ -1177,11 +1182,22 @@ extern "C" int tpb200_nvfp4_gemm_ex(const tpb200_nvfp4_gemm_args* a, tpb200_stre
     P.v_rows = static_cast<__nv_bfloat16*>(a->qkv_v_rows);
     P.scratch = reinterpret_cast<float*>(static_cast<uint8_t*>(a->workspace) + tpb::kCounterBytes);
     const int grid = std::min(tiles * plan.splits, sms);
-    if (tiled) {
-        tpb::nvfp4_gemm_kernel<true><<<grid, tpb::kThreads, smem, reinterpret_cast<cudaStream_t>(stream)>>>(P);
-    } else {
-        tpb::nvfp4_gemm_kernel<false><<<grid, tpb::kThreads, smem, reinterpret_cast<cudaStream_t>(stream)>>>(P);
+    TPB_REQUIRE((a->flags & ~TPB200_FLAG_PDL) == 0, TPB200_ERR_ENUM);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(tpb::kThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = reinterpret_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    if (a->flags & TPB200_FLAG_PDL) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
     }
+    const cudaError_t err = tiled ? cudaLaunchKernelEx(&cfg, tpb::nvfp4_gemm_kernel<true>, P)
+                                  : cudaLaunchKernelEx(&cfg, tpb::nvfp4_gemm_kernel<false>, P);
+    if (err != cudaSuccess) return TPB200_ERR_CUDA;
     return tpb_launch_status();
 }
 

@@ -108,6 +108,9 @@ __device__ __forceinline__ void store16_bf16(__nv_bfloat16* p, const float (&v)[
 template <int NB>
 __global__ void __launch_bounds__(kThreads) row_transform_quantize_kernel(const __grid_constant__ RowOpParams P) {
     __shared__ float red[kThreads / 32];
+    // under programmatic dependent launch this kernel may start while its producer still runs
+    pdl_launch_dependents();
+    pdl_wait_prior_grids();
     const int m = blockIdx.x;
     const int K = P.K;
     const int T = blockDim.x;
@@ -316,10 +319,21 @@ extern "C" int tpb200_row_transform_quantize(const tpb200_rowop_args* a, tpb200_
     P.kb_pad = (a->K + 255) / 256 * 16;
     P.tiled = a->layout == TPB200_OPERANDS_TILED;
     const int threads = std::min(tpb::kThreads, (P.kb_pad + 31) / 32 * 32);
-    if (P.kb_pad <= tpb::kThreads) {
-        tpb::row_transform_quantize_kernel<1><<<a->M, threads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(P);
-    } else {
-        tpb::row_transform_quantize_kernel<2><<<a->M, threads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(P);
+    TPB_REQUIRE((a->flags & ~TPB200_FLAG_PDL) == 0, TPB200_ERR_ENUM);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(a->M, 1, 1);
+    cfg.blockDim = dim3(threads, 1, 1);
+    cfg.stream = reinterpret_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    if (a->flags & TPB200_FLAG_PDL) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
     }
+    const cudaError_t err = P.kb_pad <= tpb::kThreads
+                                ? cudaLaunchKernelEx(&cfg, tpb::row_transform_quantize_kernel<1>, P)
+                                : cudaLaunchKernelEx(&cfg, tpb::row_transform_quantize_kernel<2>, P);
+    if (err != cudaSuccess) return TPB200_ERR_CUDA;
     return tpb_launch_status();
 }

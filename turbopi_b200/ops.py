@@ -308,7 +308,30 @@ def nvfp4_gemm_workspace_size(M, N, K, pieces=1, layout=0):
     return int(_lib.load().tpb200_nvfp4_gemm_workspace_size(M, N, K, pieces, layout))
 
 
+# Launch flags applied to the tensor-core GEMM and the row kernel (see `launch_flags`)
+_launch_flags = FLAG_NONE
+
+
+class launch_flags:
+    """Context manager: `with ops.launch_flags(ops.FLAG_PDL): ...` launches every GEMM and row kernel inside
+    with programmatic stream serialisation, so that each kernel's set-up overlaps its predecessor's tail."""
+
+    def __init__(self, flags):
+        self.flags = int(flags)
+
+    def __enter__(self):
+        global _launch_flags
+        self.prev, _launch_flags = _launch_flags, self.flags
+        return self
+
+    def __exit__(self, *exc):
+        global _launch_flags
+        _launch_flags = self.prev
+        return False
+
+
 def _gemm_ex(args, device, workspace=None):
+    args.flags = _launch_flags
     if workspace is not None:
         _cuda(workspace)
         args.workspace = _ptr(workspace)
@@ -453,7 +476,7 @@ def rowop(mode, x, K, q=None, res_in=None, gate=None, h_out=None, w0=None, w1=No
                        packed=p(q.packed) if q is not None else 0, pitch=q.pitch if q is not None else 0,
                        sf=p(q.sf) if q is not None else 0, row_scale=p(q.row_scale) if q is not None else 0,
                        pieces=q.pieces if q is not None else 0, piece_rows=q.piece_rows if q is not None else 0,
-                       layout=q.layout if q is not None else 0)
+                       layout=q.layout if q is not None else 0, flags=_launch_flags)
     with torch.cuda.device(x.device):
         st = _lib.load().tpb200_row_transform_quantize(ctypes.byref(a), torch.cuda.current_stream(x.device).cuda_stream)
     _lib.check(st, "tpb200_row_transform_quantize")

@@ -130,8 +130,11 @@ def sinusoidal_time_embedding(t, dim, min_period=4e-3, max_period=4.0):
 class Pi05:
     """Random-init Pi0.5-shaped model; `infer(images_u8, tokens, noise, num_steps)` -> actions [50, 32]."""
 
-    def __init__(self, cfg: Pi05Config, device, seed=0, keep_raw=False):
+    def __init__(self, cfg: Pi05Config, device, seed=0, keep_raw=False, pdl=True):
         self.cfg, self.device = cfg, device
+        # programmatic dependent launch across the GEMM / row-kernel chain: each kernel's launch and set-up
+        # overlap the tail of the one before it
+        self.launch_flags = ops.FLAG_PDL if pdl else ops.FLAG_NONE
         g = torch.Generator(device=device).manual_seed(seed)
         self.keep_raw = keep_raw
 
@@ -358,9 +361,10 @@ class Pi05:
         self.actions.copy_(self.b["x_t"])
 
     def forward(self, num_steps):
-        self.vision_tower()
-        self.prefix_pass()
-        self.denoise_loop(num_steps)
+        with ops.launch_flags(self.launch_flags):
+            self.vision_tower()
+            self.prefix_pass()
+            self.denoise_loop(num_steps)
 
     # ------------------------------------------------------------------ public API
     def capture(self, num_steps):
