@@ -260,7 +260,7 @@ def run_ours(args):
                                    "(gate,up 1024->4096; down 4096->1024) = 54 matrices per step, E4M3 block-16 "
                                    "scales + fp32 global scale, bf16 in/out",
                        "launch": ("one grouped launch per step (tpb200_nvfp4_gemv_grouped)" if tcs is None else
-                                  "activation-piece quantiser + one grouped tensor-core launch per step, chained by programmatic dependent launch "
+                                  "activation-piece quantiser + one grouped tensor-core launch per step" + ("" if args.no_pdl else ", chained by programmatic dependent launch") + " "
                                   "(tpb200_nvfp4_gemv_tc)"),
                        "l2": f"{NSETS} weight sets of {STEP_BYTES / 1e6:.1f} MB rotated per step (> 126 MB L2)",
                        "graph": "each step replays one CUDA graph" if step_graphs is not None else "direct launches",
