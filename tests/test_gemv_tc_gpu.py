@@ -130,3 +130,24 @@ def test_tc_gemv_chain_under_programmatic_dependent_launch(cuda_device):
     for a, b in zip(got, want):
         assert torch.equal(a, b)
     assert _lib.load().tpb200_device_error(0) == 0
+
+
+def test_tc_gemv_reads_the_gemm_weight_image(cuda_device):
+    """One tiled weight image serves prefill and decode: the GEMV given `w_image` (what tile_weights makes for
+    the tensor-core GEMM) returns the same bytes as the GEMV that tiles the packed weights itself."""
+    from turbopi_b200 import ops
+    rng = np.random.default_rng(91)
+    N, K = 1152, 2048
+    packed, sbytes, g = _weights(rng, N, K)
+    x = _dev(formats.round_to_bf16(rng.normal(size=(2, K)).astype(np.float32)), cuda_device, torch.bfloat16)
+    b = torch.zeros((N, ops.packed_pitch(K)), dtype=torch.uint8, device=cuda_device)
+    b[:, :K // 2] = _dev(packed, cuda_device)
+    image = ops.tile_weights(b, ops.swizzle_scales(_dev(sbytes, cuda_device)), N, K)
+    y1 = torch.zeros((2, N), dtype=torch.float32, device=cuda_device)
+    y2 = torch.zeros((2, N), dtype=torch.float32, device=cuda_device)
+    ops.TcGemv([dict(x=x, w_image=image, global_scale=g, out=y1)], pieces=3).launch()
+    ops.TcGemv([dict(x=x, weight_packed=_dev(packed, cuda_device), weight_scales=_dev(sbytes, cuda_device),
+                     global_scale=g, out=y2)], pieces=3).launch()
+    assert torch.equal(y1, y2)
+    ref = nvfp4.gemv_dequant_matmul(x.float().cpu().numpy(), packed, sbytes, None, 0, 16, g, True)
+    assert rel_err(y1.cpu().numpy(), ref) <= 1e-2
