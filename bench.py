@@ -216,11 +216,32 @@ def run_ours(args):
     h2d = sum(t.numel() * t.element_size() for t in hx.values())
     d2h = h_out.numel() * h_out.element_size()
 
-    def e2e_step(i):
+    def e2e_body(sidx):
         for K in x:
-            x[K].copy_(hx[K], non_blocking=True)
-        e2e_groups[i % NSETS].launch()
-        h_out.copy_(out_flat[i % NSETS], non_blocking=True)
+            x[K].copy_(hx[K], non_blocking=True)          # pinned host -> device
+        e2e_groups[sidx].launch()
+        h_out.copy_(out_flat[sidx], non_blocking=True)    # device -> pinned host
+
+    # a caller that repeats the step captures it once (copies included) and replays it
+    e2e_graphs = None
+    if not args.no_graph:
+        side2 = torch.cuda.Stream(device=device)
+        with torch.cuda.stream(side2):
+            for sidx in range(NSETS):
+                e2e_body(sidx)
+        torch.cuda.synchronize()
+        e2e_graphs = []
+        for sidx in range(NSETS):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side2):
+                e2e_body(sidx)
+            e2e_graphs.append(g)
+
+    def e2e_step(i):
+        if e2e_graphs is not None:
+            e2e_graphs[i % NSETS].replay()
+        else:
+            e2e_body(i % NSETS)
         stream.synchronize()                      # the caller has its result on the host
 
     for i in range(max(3, min(args.warmup, 20))):
