@@ -260,9 +260,11 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
     volatile int* abort_flag = &ctl->abort_flag;
     // Programmatic dependent launch: everything above ran while the previous kernel of the stream may still
     // have been running.  The producer (operands) and the epilogue (row scales, bias, results, split-K
-    // scratch) touch global memory, so they wait for it here; the MMA issuer only ever sees shared memory.
+    // scratch) touch global memory, so they wait for it; the MMA issuer only ever sees shared memory.  The
+    // producer first requests the WEIGHT halves of its first stages (tiled form): weights never depend on the
+    // previous kernel, so their way from HBM overlaps that kernel's tail.
     pdl_launch_dependents();
-    if (warp != 1) pdl_wait_prior_grids();
+    if (warp >= 2) pdl_wait_prior_grids();
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer (whole warp).
@@ -280,17 +282,39 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
         uint32_t empty_phase = 0;
         bool wrapped = false;                              // the first pass over the ring finds every stage free
         bool stop = false;
+        int pre = 0;                                       // stages whose B half went out before the wait
+        if (kTiled) {
+            for (int w = blockIdx.x; w < total_items && pre < nstages; w += gridDim.x) {
+                const int tile = w / splits;
+                const int ks0 = (w - tile * splits) * P.stages_per_split;
+                const int ks1 = min(P.k_stages, ks0 + P.stages_per_split);
+                const int n_blk = tile / P.m_blocks;
+                for (int ks = ks0; ks < ks1 && pre < nstages; ++ks, ++pre) {
+                    if (lane == 0) mbar_expect_tx(&ctl->full[pre], stage_sz);
+                    __syncwarp();
+                    if (lane < 2) {
+                        bulk_copy_g2s(smem + pre * stage_sz + lane * kBlock,
+                                      P.b_image + (static_cast<size_t>(n_blk) * P.k_stages + ks) * (2 * kBlock) + lane * kBlock,
+                                      kBlock, &ctl->full[pre]);
+                    }
+                }
+            }
+        }
+        pdl_wait_prior_grids();
+        int it = 0;
         for (int w = blockIdx.x; w < total_items && !stop; w += gridDim.x) {
             const int tile = w / splits;
             const int ks0 = (w - tile * splits) * P.stages_per_split;
             const int ks1 = min(P.k_stages, ks0 + P.stages_per_split);
             const int m_blk = tile % P.m_blocks;
             const int n_blk = tile / P.m_blocks;
-            for (int ks = ks0; ks < ks1; ++ks) {
+            for (int ks = ks0; ks < ks1; ++ks, ++it) {
                 int bad = 0;
                 if (lane == 0) {
                     if (*abort_flag) {
                         bad = 1;
+                    } else if (it < pre) {
+                        // barrier already armed, B half already on its way
                     } else if (wrapped && !mbar_wait_bounded(&ctl->empty[s], empty_phase)) {
                         record_error(kErrGemmEmptyBarrierTimeout);
                         *abort_flag = 1;
@@ -306,7 +330,7 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
                 }
                 uint8_t* st = smem + s * stage_sz;
                 if (kTiled) {
-                    if (lane < 2 + pieces) {
+                    if (lane < 2 + pieces && (lane >= 2 || it >= pre)) {
                         const uint8_t* src =
                             lane < 2 ? P.b_image + (static_cast<size_t>(n_blk) * P.k_stages + ks) * (2 * kBlock) + lane * kBlock
                                      : P.a_image + (static_cast<size_t>(m_blk) * P.k_stages + ks) * (pieces * kBlock) +
