@@ -208,3 +208,90 @@ def test_fp8_activation_quantiser_properties():
     # values were divided by the unrounded one, so the round trip carries the scale's rounding error
     assert np.abs(deq - x).max() / np.abs(x).max() < 0.2
     assert (s[:, 32:] != 0).all()                       # every block is quantised, not only the first 32
+
+
+# ---------------------------------------------------------------- model-level oracle (a12 / a13 / a14)
+def _model_case(name):
+    from oracle import pi05
+    from pi05_fixture import load_model_fixture, oracle_cfg, oracle_weights
+    g, cfg = load_model_fixture()
+    w, ocfg = oracle_weights(g, cfg), oracle_cfg(cfg)
+    valid = torch.from_numpy(g[f"{name}.pad_mask"])
+    cos, sin = pi05.rope_tables(torch.arange(1024), cfg["head_dim"], bf16=False)
+    return pi05, g, cfg, w, ocfg, valid, cos, sin
+
+
+def test_model_oracle_masks_and_positions_match_reference():
+    """prefix_valid / prefix_positions against the masks and position ids the reference's embed_prefix,
+    compute_prefix_kv_cache and precompute_graph_tensors produced (padded prompt, missing camera)."""
+    for name, image_valid, prompt_len in (("A", [True, True], 10), ("B", [True, True], 7), ("C", [True, False], 7)):
+        pi05, g, cfg, w, ocfg, valid, cos, sin = _model_case(name)
+        ours = pi05.prefix_valid(ocfg, image_valid, prompt_len)
+        assert torch.equal(ours, valid)
+        pos, first = pi05.prefix_positions(valid)
+        ref_pos = torch.from_numpy(g[f"{name}.position_ids"])
+        assert torch.equal(pos[valid], ref_pos[valid])
+        A = cfg["action_horizon"]
+        assert np.array_equal(np.arange(first, first + A), g[f"{name}.suffix_position_ids"])
+        # the reference's additive mask: action tokens see valid prefix keys and every action token
+        key_valid = torch.cat([valid, torch.ones(A, dtype=torch.bool)])
+        assert np.array_equal(np.broadcast_to(key_valid.numpy(), (A, key_valid.numel())), g[f"{name}.attention_mask_is_zero"])
+
+
+def test_model_oracle_sinusoid_and_conditioning_match_reference():
+    pi05, g, cfg, w, ocfg, valid, cos, sin = _model_case("A")
+    s = pi05.sinusoidal(torch.from_numpy(g["sinusoid_t"]), 1024)
+    assert np.array_equal(s.numpy(), g["sinusoid_1024"])              # float64, bit-exact
+    with pi05.exact_fp32():
+        for i, t in enumerate([1.0, 1.0 - 1.0 / 3, 1.0 - 2.0 / 3]):
+            c = pi05.adarms_cond(w, torch.tensor([t], dtype=torch.float32), cfg["expert_width"])
+            assert np.allclose(c[0].numpy(), g["A.adarms_conds"][i], rtol=1e-5, atol=1e-6)
+
+
+def test_model_oracle_matches_reference_model():
+    """Vision tower + prefix pass + denoise steps of the oracle in exact-fp32 mode against what the
+    reference's own classes / PI0Pytorch methods computed on the same weights."""
+    for name in ("A", "B", "C"):
+        pi05, g, cfg, w, ocfg, valid, cos, sin = _model_case(name)
+        images = torch.from_numpy(g["images_u8"])
+        tokens = torch.from_numpy(g["tokens"])
+        noise = torch.from_numpy(g["noise"])
+        T = 2 * (cfg["image_size"] // cfg["patch"]) ** 2
+        with pi05.exact_fp32():
+            img_tokens = pi05.vision_tower(w, images, ocfg)
+            assert np.allclose(img_tokens.numpy(), g[f"{name}.prefix_embs"][:T], rtol=1e-4, atol=2e-5)
+            kv = pi05.prefix_pass(w, img_tokens, tokens, ocfg, cos, sin, valid)
+            v = valid.numpy()
+            for l in range(cfg["prefix_layers"]):
+                assert np.allclose(kv[l][0].numpy()[v], g[f"{name}.k{l}"][v], rtol=1e-4, atol=2e-5), (name, "K", l)
+                assert np.allclose(kv[l][1].numpy()[v], g[f"{name}.v{l}"][v], rtol=1e-4, atol=2e-5), (name, "V", l)
+            # the denoise steps read the REFERENCE's cache (invalid rows included: they are masked)
+            kv_ref = [(torch.from_numpy(g[f"{name}.k{l}"]), torch.from_numpy(g[f"{name}.v{l}"]))
+                      for l in range(cfg["prefix_layers"])]
+            cond = pi05.adarms_cond(w, torch.tensor([1.0]), cfg["expert_width"])
+            v0 = pi05.denoise_velocity(w, kv_ref, noise, cond, ocfg, cos, sin, valid)
+            assert np.allclose(v0.numpy(), g[f"{name}.v_step0"], rtol=1e-4, atol=2e-5), name
+            actions = pi05.denoise(w, kv, noise, 3, ocfg, cos, sin, valid)
+            assert np.allclose(actions.numpy(), g[f"{name}.actions"], rtol=1e-4, atol=5e-5), name
+    # with nothing padded the reference's unmasked cached step equals its graph-safe masked one
+    assert np.allclose(g["A.v_step0_with_cache"], g["A.v_step0"], rtol=1e-5, atol=1e-6)
+
+
+def test_model_oracle_bf16_mode_stays_close_to_fp32_reference():
+    """The bf16-rounding mode (the one the GPU pipeline is compared with) differs from the fp32 reference
+    only by bf16 noise."""
+    pi05, g, cfg, w, ocfg, valid, cos, sin = _model_case("B")
+    cos_b, sin_b = pi05.rope_tables(torch.arange(1024), cfg["head_dim"], bf16=True)
+    actions, _ = pi05.sample_actions(w, torch.from_numpy(g["images_u8"]), torch.from_numpy(g["tokens"]),
+                                     torch.from_numpy(g["noise"]), 3, ocfg, cos_b, sin_b, valid)
+    assert np.abs(actions.numpy() - g["B.actions"]).max() < 2e-2
+
+
+def test_att_2d_mask_example():
+    """make_att_2d_masks on a hand-sized case (prefix-LM blocks + padding), as stored by the reference run."""
+    from pi05_fixture import load_model_fixture
+    g, _ = load_model_fixture()
+    pad = np.array([1, 1, 0, 1, 0], dtype=bool)
+    ar = np.cumsum([0, 0, 0, 1, 0])
+    ours = (ar[None, :] <= ar[:, None]) & (pad[None, :] & pad[:, None])
+    assert np.array_equal(ours, g["att2d_example"])

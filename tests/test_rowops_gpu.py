@@ -133,3 +133,56 @@ def test_row_kernel_rowmajor_operand_equals_tiled(cuda_device):
     packed2, sf2, rs2, _ = ops.nvfp4_quantize_act_pieces(x, P)
     assert torch.equal(packed2.reshape(P, -1, qr.pitch)[:, :M], qr.packed.reshape(P, -1, qr.pitch)[:, :M])
     assert torch.equal(rs2, qr.row_scale)
+
+
+def _rowops_golden():
+    from pathlib import Path
+    return dict(np.load(Path(__file__).resolve().parent / "golden" / "pi05_rowops.npz"))
+
+
+@pytest.mark.parametrize("K", [1024, 2048])
+def test_row_kernel_matches_reference_modules(cuda_device, K):
+    """The row kernel against outputs of the reference's own GemmaRMSNorm (plain and adaptive),
+    _gated_residual and nn.LayerNorm run in bf16 (tests/golden/pi05_rowops.npz, made by
+    tests/golden/make_golden_model.py from transformers_replace/models/gemma/modeling_gemma.py:49-129,212-230)."""
+    from turbopi_b200 import _lib, ops
+    g = _rowops_golden()
+    t = lambda k: torch.from_numpy(g[k]).to(BF).to(cuda_device)
+    x, res = t(f"rms{K}.x"), t(f"rms{K}.res")
+    M = x.shape[0]
+    q = ops.QuantBuf(M, K, 3, cuda_device)
+    y = torch.empty((M, K), dtype=BF, device=cuda_device)
+    h = torch.empty((M, K), dtype=BF, device=cuda_device)
+    # plain RMSNorm after an ungated residual
+    ops.rowop(_lib.ROW_RMSNORM, x, K, q, res_in=res, h_out=h, w0=t(f"rms{K}.w"), eps=1e-6, y_out=y)
+    assert torch.equal(h.cpu(), t(f"rms{K}.h").cpu())
+    _close_bf16(y.cpu(), t(f"rms{K}.y").cpu())
+    # adaptive RMSNorm after a gated residual; scale / shift / gate are the chunks of dense(cond)
+    mod = t(f"ada{K}.mod")
+    scale, shift, gate = mod[:K].contiguous(), mod[K:2 * K].contiguous(), mod[2 * K:].contiguous()
+    assert torch.equal(gate.cpu(), t(f"ada{K}.gate").cpu())
+    ops.rowop(_lib.ROW_ADARMS, x, K, q, res_in=res, gate=t(f"ada{K}.gate_prev"), h_out=h, w0=scale, w1=shift, eps=1e-6, y_out=y)
+    assert torch.equal(h.cpu(), t(f"ada{K}.h").cpu())
+    _close_bf16(y.cpu(), t(f"ada{K}.y").cpu(), offset=shift.cpu()[None, :])
+    # LayerNorm (SigLIP) on the same residual sum
+    ops.rowop(_lib.ROW_LAYERNORM, x, K, q, res_in=res, h_out=h, w0=t(f"ln{K}.w"), w1=t(f"ln{K}.b"), eps=1e-6, y_out=y)
+    _close_bf16(y.cpu(), t(f"ln{K}.y").cpu(), min_equal=0.99, ulps=2, offset=t(f"ln{K}.b").cpu()[None, :])
+    assert _lib.load().tpb200_device_error(0) == 0
+
+
+def test_gelu_mul_matches_reference_mlp(cuda_device):
+    """GELU(gate) * up of the reference's GemmaMLP (captured at the input of its down projection) and the
+    MLP output through the weight-only GEMMs."""
+    from turbopi_b200 import _lib, ops
+    g = _rowops_golden()
+    gu = torch.from_numpy(g["mlp.gate_up"]).to(BF).to(cuda_device)
+    I = gu.shape[1] // 2
+    M = gu.shape[0]
+    q = ops.QuantBuf(M, I, 3, cuda_device)
+    y = torch.empty((M, I), dtype=BF, device=cuda_device)
+    ops.rowop(_lib.ROW_GELU_MUL, gu, I, q, y_out=y)
+    ref = torch.from_numpy(g["mlp.act"]).to(BF)
+    # torch's fp32 tanh form loses accuracy in the negative tail; bound by one bf16 step of the row maximum
+    assert (y.cpu().float() - ref.float()).abs().max().item() <= 2.0 ** -7 * ref.float().abs().max().item()
+    assert (y.cpu() == ref).float().mean().item() >= 0.95
+    assert _lib.load().tpb200_device_error(0) == 0
