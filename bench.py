@@ -449,13 +449,16 @@ def run_extras(device, sets, x):
     # with weight-only semantics; `tflops` counts the useful 2 M N K once, not the 3 pieces)
     from turbopi_b200 import _lib as tlib
     from turbopi_b200.pi05 import TcLinear
+    gemm_ws = ops.gemm_workspace(device)
     for (M, N, K, name) in ((712, 32768, 2048, "gemma2b_gate_up_M712"), (712, 2048, 16384, "gemma2b_down_M712"),
                             (712, 2560, 2048, "gemma2b_qkv_M712"), (512, 4304, 1152, "siglip_fc1_M512"),
                             (512, 1152, 4304, "siglip_fc2_M512"), (50, 8192, 1024, "expert_gate_up_M50"),
                             (50, 1024, 4096, "expert_down_M50")):
         q = ops.QuantBuf(M, K, 3, device)
         xq = torch.randn(M, K, device=device).to(torch.bfloat16)
-        lins = [TcLinear(torch.randn(N, K, device=device) * 0.02) for _ in range(2)]
+        lins = [TcLinear.from_weight(torch.randn(N, K, device=device) * 0.02) for _ in range(2)]
+        for l_ in lins:
+            l_.ws = gemm_ws
         o = torch.empty((M, N), dtype=torch.bfloat16, device=device)
         ops.rowop(tlib.ROW_NONE, xq, K, q)
         t = time_launches(lambda i: lins[i % 2](q, o), 16)

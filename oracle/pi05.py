@@ -20,6 +20,8 @@ token ever reads them).  `PI0Pytorch.denoise_step_with_cache` (:619-621) drops t
 lets action tokens attend to padded keys; the oracle follows the masked `denoise_step_graphed`.
 
 Weights are plain float32 matrices (already dequantised) in a dict; see tests/test_pi05_gpu.py.
+Every tensor follows the device of the weights, so the full-depth comparison can execute this same code
+with fp32 torch kernels on the GPU (checked against its CPU execution at reduced depth).
 """
 import contextlib
 import math
@@ -89,7 +91,7 @@ def attention(q, k, v, heads, key_valid=None):
     qh = q.view(L, heads, D).transpose(0, 1)
     mask = None
     if key_valid is not None:
-        mask = torch.where(key_valid, 0.0, MASKED)[None, None, None, :].to(q.dtype)
+        mask = torch.where(key_valid.to(q.device), 0.0, MASKED)[None, None, None, :].to(q.dtype)
     o = F.scaled_dot_product_attention(qh[None], k[None, None].expand(1, heads, -1, -1),
                                        v[None, None].expand(1, heads, -1, -1), attn_mask=mask)
     return r(o[0].transpose(0, 1).reshape(L, heads * D))
@@ -132,6 +134,7 @@ def prefix_pass(w, img_tokens, tokens, cfg, cos, sin, valid=None):
     S = h.shape[0]
     if valid is None:
         valid = torch.ones(S, dtype=torch.bool)
+    valid = valid.to(h.device)
     pos, _ = prefix_positions(valid)
     pc, ps = cos[pos], sin[pos]
     kv = []
@@ -160,7 +163,7 @@ def sinusoidal(t, dim, min_period=4e-3, max_period=4.0):
 
 def adarms_cond(w, t, ew):
     """silu(time_mlp_out(silu(time_mlp_in(sincos(t))))) (pi0_pytorch.py:817-839)."""
-    emb = r(sinusoidal(t, ew).float())
+    emb = r(sinusoidal(t.cpu(), ew).float()).to(w["time_mlp_in"].device)
     return linear(linear(emb, w["time_mlp_in"], w["time_mlp_in_b"], "silu"), w["time_mlp_out"], w["time_mlp_out_b"], "silu")
 
 
@@ -170,9 +173,10 @@ def denoise_velocity(w, kv, x_t, cond, cfg, cos, sin, valid=None):
     S = kv[0][0].shape[0]
     if valid is None:
         valid = torch.ones(S, dtype=torch.bool)
+    valid = valid.to(x_t.device)
     _, first = prefix_positions(valid)
     pos_c, pos_s = cos[first:first + A], sin[first:first + A]
-    key_valid = torch.cat([valid, torch.ones(A, dtype=torch.bool)])
+    key_valid = torch.cat([valid, torch.ones(A, dtype=torch.bool, device=valid.device)])
     mod = linear(cond, w["ada_dense"], w["ada_dense_b"]).view(-1, 3, ew)       # [n_norms, (scale, shift, gate), ew]
     h = linear(r(x_t), w["action_in"], w["action_in_b"])
     for l, L in enumerate(w["expert"]):

@@ -395,16 +395,26 @@ def rope_tables(num_positions, head_dim=256, theta=10000.0, device="cuda"):
 
 
 def fused_qkv_rope_append(x, w_packed, w_sf, q_dim, k_rows, v_rows, positions, rope_cos, rope_sin, alpha=1.0,
-                          pieces=3, q_out=None, workspace=None):
+                          pieces=3, q_out=None, workspace=None, check_positions=True):
     """q = RoPE(x Wq^T), cache K rows <- RoPE(x Wk^T), cache V rows <- x Wv^T in ONE kernel.
     x [M, H] bf16; w_packed / w_sf: tile-permuted stacked [Wq; Wk; Wv] (qkv_tile_permutation) in NVFP4;
     k_rows / v_rows: views of the cache whose row 0 is the first token's row, row stride 256 (bf16);
-    positions int32 [M].  Returns q [M, q_dim] bf16."""
+    positions int32 [M], each inside the RoPE table (`check_positions` reads them back to verify, which
+    synchronises: switch it off inside a stream capture).  Returns q [M, q_dim] bf16."""
     _cuda(x, w_packed, w_sf, k_rows, v_rows, positions, rope_cos, rope_sin)
     M, K = x.shape
     N = q_dim + 512
-    if k_rows.stride(0) != 256 or v_rows.stride(0) != 256 or k_rows.dtype != torch.bfloat16:
+    if (k_rows.stride(0) != 256 or v_rows.stride(0) != 256 or k_rows.dtype != torch.bfloat16
+            or v_rows.dtype != torch.bfloat16):
         raise TurboPiError("cache rows must be bf16 with a row stride of 256 elements")
+    if k_rows.shape[0] < M or v_rows.shape[0] < M:
+        raise TurboPiError(f"cache views hold {min(k_rows.shape[0], v_rows.shape[0])} rows, {M} tokens to append")
+    if positions.dtype != torch.int32 or positions.numel() < M:
+        raise TurboPiError("positions must be int32 with one entry per token")
+    if rope_cos.shape != rope_sin.shape or rope_cos.dtype != torch.bfloat16 or rope_cos.shape[1] != 128:
+        raise TurboPiError("RoPE tables must be bf16 [positions, 128]")
+    if check_positions and (int(positions[:M].min()) < 0 or int(positions[:M].max()) >= rope_cos.shape[0]):
+        raise TurboPiError("a position lies outside the RoPE table")
     if q_out is None:
         q_out = torch.empty((M, q_dim), dtype=torch.bfloat16, device=x.device)
     if w_sf is None:

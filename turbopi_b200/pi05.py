@@ -11,7 +11,15 @@ carried as residual e2m1 pieces); norms, residuals and GELU*up are the fused row
 write the next GEMM's operand directly; Q/K/V + RoPE + KV-cache append is the GEMM's fused
 epilogue.  Attention itself is torch's scaled_dot_product_attention for now.  All buffers are
 allocated once, so the whole inference (or just the denoise loop) replays as ONE CUDA graph.
-Weights are random-initialised (there is no checkpoint to load here).
+
+Weights come from a reference-named state dict (`Pi05.from_state_dict`, tensor names of
+`PI0Pytorch.state_dict()`), from a prepared container file (`Pi05.save` / `Pi05.from_file`,
+turbopi_b200/weights.py) or, for benchmarks, from a seeded random initialisation.
+
+Padding follows the reference: prefix tokens that do not exist (a missing camera, the padded tail of the
+prompt) are never attended to, position ids are `cumsum(valid) - 1`, and the action tokens continue at
+`sum(valid)` (pi0_pytorch.py:80-108,442,571-579,791-866).  The valid mask only changes small device
+buffers (positions, additive key bias), so one captured graph serves every mask.
 """
 import ctypes
 import math
@@ -20,8 +28,8 @@ from dataclasses import dataclass
 import torch
 import torch.nn.functional as F
 
-from . import _lib, ops
-from ._lib import ACT_GELU, ACT_NONE, ACT_SILU
+from . import _lib, ops, weights
+from ._lib import ACT_GELU, ACT_NONE, ACT_SILU, TurboPiError
 from .nvfp4_packed import quantize_nvfp4_two_level
 
 
@@ -71,32 +79,24 @@ QuantBuf, rowop = ops.QuantBuf, ops.rowop
 
 class TcLinear:
     """One NVFP4 weight matrix prepared for the tensor-core GEMM (standard NVFP4: E4M3 scale per 16 and
-    an fp32 global scale).  `raw` keeps the reference-layout codes / scale bytes for dequantisation."""
+    an fp32 global scale): the tiled operand image, the global scale, an optional fp32 bias.  `raw` keeps
+    the reference-layout codes / scale bytes for dequantisation in tests."""
 
-    def __init__(self, weight, bias=None, row_perm=None, keep_raw=False):
-        N, K = weight.shape
-        packed, scales, g = quantize_nvfp4_two_level(weight, 16)
-        self.N, self.K, self.g = N, K, g
-        if keep_raw:
-            self.raw = (packed.clone(), scales.clone(), g)
-        if row_perm is not None:
-            packed, scales = packed[row_perm], scales[row_perm]
-        pitch = ops.packed_pitch(K)
-        b = torch.zeros((N, pitch), dtype=torch.uint8, device=weight.device)
-        b[:, :K // 2] = packed
-        # the GEMM streams the tiled image; the row-major operand is only its source
-        self.b = ops.tile_weights(b, ops.swizzle_scales(scales.contiguous()), N, K)
+    def __init__(self, image, g, N, K, bias=None, raw=None):
+        self.b, self.g, self.N, self.K = image, float(g), int(N), int(K)
         self.bias = None if bias is None else bias.float().contiguous()
-
-    # split-K scratch shared by every linear of a device (the model runs them one after another)
-    _workspaces = {}
+        if raw is not None:
+            self.raw = raw
+        self.ws = None            # split-K scratch, set by the owning pipeline
 
     @classmethod
-    def workspace(cls, device):
-        key = str(device)
-        if key not in cls._workspaces:
-            cls._workspaces[key] = ops.gemm_workspace(device)
-        return cls._workspaces[key]
+    def from_weight(cls, weight, bias=None, row_perm=None, keep_raw=False):
+        N, K = weight.shape
+        packed, scales, g = quantize_nvfp4_two_level(weight, 16)
+        raw = (packed.clone(), scales.clone(), g) if keep_raw else None
+        if row_perm is not None:
+            packed, scales = packed[row_perm], scales[row_perm]
+        return cls(weights.tile_weights_host(packed, scales), g, N, K, bias, raw)
 
     def __call__(self, q, out, activation=ACT_NONE, M=None):
         M = q.M if M is None else M
@@ -105,17 +105,19 @@ class TcLinear:
                              alpha=float(self.g), bias=p(self.bias), activation=int(activation), out=p(out),
                              out_dtype=ops._dt(out), ldo=out.stride(0), M=M, N=self.N, K=self.K,
                              layout=ops.OPERANDS_TILED)
-        ops._gemm_ex(args, out.device, self.workspace(out.device))
+        ops._gemm_ex(args, out.device, self.ws)
         return out
 
     def qkv(self, q, q_out, k_rows, v_rows, positions, cos, sin, q_dim, M=None):
         M = q.M if M is None else M
+        if k_rows.shape[0] < M or v_rows.shape[0] < M or positions.numel() < M:
+            raise TurboPiError("fused QKV: cache rows / positions shorter than the token count")
         p = ops._ptr
         args = _lib.GemmArgs(a_packed=p(q.packed), a_pieces=q.pieces, a_row_scale=p(q.row_scale), b_packed=p(self.b),
                              alpha=float(self.g), M=M, N=self.N, K=self.K, layout=ops.OPERANDS_TILED,
                              qkv_q_out=p(q_out), qkv_ldq=q_out.stride(0), qkv_q_dim=q_dim, qkv_k_rows=p(k_rows),
                              qkv_v_rows=p(v_rows), qkv_positions=p(positions), qkv_rope_cos=p(cos), qkv_rope_sin=p(sin))
-        ops._gemm_ex(args, q_out.device, self.workspace(q_out.device))
+        ops._gemm_ex(args, q_out.device, self.ws)
         return q_out
 
 
@@ -128,71 +130,188 @@ def sinusoidal_time_embedding(t, dim, min_period=4e-3, max_period=4.0):
 
 
 class Pi05:
-    """Random-init Pi0.5-shaped model; `infer(images_u8, tokens, noise, num_steps)` -> actions [50, 32]."""
+    """Pi0.5-shaped model; `infer(images_u8, tokens, noise, num_steps)` -> actions [50, 32].
 
-    def __init__(self, cfg: Pi05Config, device, seed=0, keep_raw=False, pdl=True):
+    Pi05(cfg, device, seed=...)            seeded random weights (benchmarks, tests)
+    Pi05.from_state_dict(sd, cfg, device)  tensors under the reference's names (weights.reference_state_dict_names)
+    Pi05.from_file(path, device)           a container written by `save()`
+    """
+
+    def __init__(self, cfg: Pi05Config, device, seed=0, keep_raw=False, pdl=True, state_dict=None, _prepared=None):
         self.cfg, self.device = cfg, device
+        c = cfg
+        if c.prefix_len + c.action_horizon > c.max_seq:
+            raise TurboPiError(f"prefix ({c.prefix_len}) + action horizon ({c.action_horizon}) exceed the KV cache "
+                               f"({c.max_seq} rows)")
         # programmatic dependent launch across the GEMM / row-kernel chain: each kernel's launch and set-up
         # overlap the tail of the one before it
         self.launch_flags = ops.FLAG_PDL if pdl else ops.FLAG_NONE
-        g = torch.Generator(device=device).manual_seed(seed)
         self.keep_raw = keep_raw
-
-        def W(n, k, std=0.02):
-            return torch.randn(n, k, generator=g, device=device) * std
-
-        def Bv(n, std=0.02):
-            return torch.randn(n, generator=g, device=device) * std
-
-        def lin(n, k, bias=False, perm=None):
-            return TcLinear(W(n, k), Bv(n) if bias else None, perm, keep_raw)
-
-        def nw(n):   # norm parameters: small random values so that the norms are not the identity
-            return (torch.randn(n, generator=g, device=device) * 0.1).to(torch.bfloat16)
-
-        c = cfg
-        vw, pk = c.vision_width, 3 * c.patch * c.patch
-        self.patch_k = (pk + 15) // 16 * 16
-        wp = torch.zeros(vw, self.patch_k, device=device)
-        wp[:, :pk] = W(vw, pk)
-        self.patch_embed = TcLinear(wp, Bv(vw), None, keep_raw)
-        self.pos_emb = (torch.randn(c.image_tokens, vw, generator=g, device=device) * 0.02).to(torch.bfloat16)
-        self.vision = []
-        for _ in range(c.vision_layers):
-            self.vision.append(dict(
-                ln1_w=(1.0 + nw(vw).float()).to(torch.bfloat16), ln1_b=nw(vw),
-                qkv=lin(3 * vw, vw, True), out=lin(vw, vw, True),
-                ln2_w=(1.0 + nw(vw).float()).to(torch.bfloat16), ln2_b=nw(vw),
-                fc1=lin(c.vision_mlp, vw, True), fc2=lin(vw, c.vision_mlp, True)))
-        self.post_ln_w, self.post_ln_b = (1.0 + nw(vw).float()).to(torch.bfloat16), nw(vw)
-        self.projector = lin(c.width, vw, True)
-
-        perm = ops.qkv_tile_permutation(c.q_dim).to(device)
-        self.embed_tokens = (torch.randn(c.vocab, c.width, generator=g, device=device) * 0.02).to(torch.bfloat16)
-        self.prefix = []
-        for _ in range(c.prefix_layers):
-            self.prefix.append(dict(
-                in_norm=nw(c.width), qkv=lin(c.q_dim + 2 * c.head_dim, c.width, False, perm),
-                o=lin(c.width, c.q_dim), post_norm=nw(c.width),
-                gate_up=lin(2 * c.mlp, c.width), down=lin(c.width, c.mlp)))
-
-        ew = c.expert_width
-        self.action_in = lin(ew, c.action_dim, True)
-        self.action_out = lin(c.action_dim, ew, True)
-        self.time_mlp_in = lin(ew, ew, True)
-        self.time_mlp_out = lin(ew, ew, True)
+        self.patch_k = (3 * c.patch * c.patch + 15) // 16 * 16
         self.n_norms = 2 * c.expert_layers + 1
-        self.ada_dense = lin(self.n_norms * 3 * ew, ew, True)       # every adaptive norm's dense(cond), stacked
-        self.expert = []
-        for _ in range(c.expert_layers):
-            self.expert.append(dict(qkv=lin(c.q_dim + 2 * c.head_dim, ew, False, perm), o=lin(ew, c.q_dim),
-                                    gate_up=lin(2 * c.expert_mlp, ew), down=lin(ew, c.expert_mlp)))
-
+        self.workspace = ops.gemm_workspace(device)       # split-K scratch of THIS pipeline's launches
+        if _prepared is not None:
+            self._from_prepared(_prepared)
+        else:
+            self._from_tensors(self._random_source(seed) if state_dict is None else self._dict_source(state_dict))
         self.cos, self.sin = ops.rope_tables(c.max_seq, c.head_dim, device=device)
+        if self.cos.shape[0] != c.max_seq:
+            raise TurboPiError("RoPE table and KV cache disagree on the number of positions")
         self._alloc()
         self._graph = None
         self._graph_steps = None
         self._time_emb = {}
+        self.set_valid()
+
+    @classmethod
+    def from_state_dict(cls, state_dict, cfg: Pi05Config, device, **kw):
+        return cls(cfg, device, state_dict=state_dict, **kw)
+
+    @classmethod
+    def from_file(cls, path, device, **kw):
+        tensors, meta = weights.load_container(path, device)
+        if meta.get("kind") != "pi05":
+            raise TurboPiError(f"{path}: not a Pi0.5 weight container")
+        return cls(Pi05Config(**meta["config"]), device, _prepared=(tensors, meta), **kw)
+
+    # ------------------------------------------------------------------ weights
+    def _random_source(self, seed):
+        g = torch.Generator(device=self.device).manual_seed(seed)
+        shapes = weights.reference_state_dict_names(self.cfg)
+
+        def get(name):
+            shape = shapes[name]
+            norm = len(shape) == 1 and ("layernorm" in name or "layer_norm" in name)
+            # norm parameters: small random values so that the norms are not the identity
+            t = torch.randn(shape, generator=g, device=self.device) * (0.1 if norm else 0.02)
+            if norm and name.endswith(".weight") and ("layer_norm" in name or "post_layernorm" in name):
+                t = t + 1.0
+            return t
+        return get
+
+    def _dict_source(self, sd):
+        shapes = weights.reference_state_dict_names(self.cfg)
+        missing = [n for n in shapes if n not in sd]
+        if missing:
+            raise TurboPiError(f"state dict lacks {len(missing)} tensors, e.g. {missing[:3]}")
+
+        def get(name):
+            t = sd[name]
+            if tuple(t.shape) != tuple(shapes[name]):
+                raise TurboPiError(f"{name}: shape {tuple(t.shape)}, expected {tuple(shapes[name])}")
+            return t.to(self.device).float()
+        return get
+
+    def _from_tensors(self, get):
+        """Quantise, permute and tile every linear; norms, embeddings and tables go to bf16."""
+        c, kr = self.cfg, self.keep_raw
+        bf = torch.bfloat16
+        V = "paligemma_with_expert.paligemma.model.vision_tower.vision_model."
+        PG = "paligemma_with_expert.paligemma.model."
+        EX = "paligemma_with_expert.gemma_expert.model."
+
+        def lin(wname, bias=True, perm=None):
+            return TcLinear.from_weight(get(wname + ".weight"), get(wname + ".bias") if bias else None, perm, kr)
+
+        def stacked(names, bias, perm=None):
+            w = torch.cat([get(n + ".weight") for n in names], 0)
+            b = torch.cat([get(n + ".bias") for n in names], 0) if bias else None
+            return TcLinear.from_weight(w, b, perm, kr)
+
+        vw = c.vision_width
+        wp = torch.zeros(vw, self.patch_k, device=self.device)
+        wp[:, :3 * c.patch * c.patch] = get(V + "embeddings.patch_embedding.weight").reshape(vw, -1)   # (c, i, j)
+        self.patch_embed = TcLinear.from_weight(wp, get(V + "embeddings.patch_embedding.bias"), None, kr)
+        self.pos_emb = get(V + "embeddings.position_embedding.weight").to(bf)
+        self.vision = []
+        for i in range(c.vision_layers):
+            L = f"{V}encoder.layers.{i}."
+            self.vision.append(dict(
+                ln1_w=get(L + "layer_norm1.weight").to(bf), ln1_b=get(L + "layer_norm1.bias").to(bf),
+                qkv=stacked([L + "self_attn.q_proj", L + "self_attn.k_proj", L + "self_attn.v_proj"], True),
+                out=lin(L + "self_attn.out_proj"),
+                ln2_w=get(L + "layer_norm2.weight").to(bf), ln2_b=get(L + "layer_norm2.bias").to(bf),
+                fc1=lin(L + "mlp.fc1"), fc2=lin(L + "mlp.fc2")))
+        self.post_ln_w, self.post_ln_b = get(V + "post_layernorm.weight").to(bf), get(V + "post_layernorm.bias").to(bf)
+        self.projector = lin(PG + "multi_modal_projector.linear")
+
+        perm = ops.qkv_tile_permutation(c.q_dim).to(self.device)
+        self.embed_tokens = get(PG + "language_model.embed_tokens.weight").to(bf)
+
+        def decoder(prefix):
+            a = prefix + "self_attn."
+            return dict(qkv=stacked([a + "q_proj", a + "k_proj", a + "v_proj"], False, perm), o=lin(a + "o_proj", False),
+                        gate_up=stacked([prefix + "mlp.gate_proj", prefix + "mlp.up_proj"], False),
+                        down=lin(prefix + "mlp.down_proj", False))
+
+        self.prefix = []
+        for i in range(c.prefix_layers):
+            L = f"{PG}language_model.layers.{i}."
+            d = decoder(L)
+            d["in_norm"] = get(L + "input_layernorm.weight").to(bf)
+            d["post_norm"] = get(L + "post_attention_layernorm.weight").to(bf)
+            self.prefix.append(d)
+
+        self.action_in = lin("action_in_proj")
+        self.action_out = lin("action_out_proj")
+        self.time_mlp_in = lin("time_mlp_in")
+        self.time_mlp_out = lin("time_mlp_out")
+        self.expert, dense = [], []
+        for i in range(c.expert_layers):
+            L = f"{EX}layers.{i}."
+            self.expert.append(decoder(L))
+            dense += [L + "input_layernorm.dense", L + "post_attention_layernorm.dense"]
+        self.ada_dense = stacked(dense + [EX + "norm.dense"], True)    # every adaptive norm's dense(cond), stacked
+
+    _LINEAR_SLOTS = ("qkv", "out", "fc1", "fc2", "o", "gate_up", "down")
+
+    def _named_parts(self):
+        """(name, object) of everything `save()` stores: TcLinear objects and plain tensors."""
+        yield "patch_embed", self.patch_embed
+        yield "pos_emb", self.pos_emb
+        for group, layers in (("vision", self.vision), ("prefix", self.prefix), ("expert", self.expert)):
+            for i, L in enumerate(layers):
+                for k, v in L.items():
+                    yield f"{group}.{i}.{k}", v
+        for k in ("post_ln_w", "post_ln_b", "projector", "embed_tokens", "action_in", "action_out", "time_mlp_in",
+                  "time_mlp_out", "ada_dense"):
+            yield k, getattr(self, k)
+
+    def save(self, path):
+        """Write the prepared model (tiled 4-bit operand images, bf16 tables) to a container file."""
+        tensors, linears = {}, {}
+        for name, obj in self._named_parts():
+            if isinstance(obj, TcLinear):
+                tensors[name + ".image"] = obj.b
+                if obj.bias is not None:
+                    tensors[name + ".bias"] = obj.bias
+                linears[name] = {"N": obj.N, "K": obj.K, "global_scale": obj.g}
+            else:
+                tensors[name] = obj
+        cfgd = {k: getattr(self.cfg, k) for k in self.cfg.__dataclass_fields__}
+        return weights.save_container(path, tensors, {"kind": "pi05", "config": cfgd, "linears": linears})
+
+    def _from_prepared(self, prepared):
+        tensors, meta = prepared
+        lins = meta["linears"]
+
+        def part(name):
+            if name in lins:
+                e = lins[name]
+                return TcLinear(tensors[name + ".image"], e["global_scale"], e["N"], e["K"], tensors.get(name + ".bias"))
+            return tensors[name]
+
+        c = self.cfg
+        self.patch_embed, self.pos_emb = part("patch_embed"), part("pos_emb")
+        self.vision = [{k: part(f"vision.{i}.{k}") for k in ("ln1_w", "ln1_b", "qkv", "out", "ln2_w", "ln2_b", "fc1", "fc2")}
+                       for i in range(c.vision_layers)]
+        self.prefix = [{k: part(f"prefix.{i}.{k}") for k in ("qkv", "o", "gate_up", "down", "in_norm", "post_norm")}
+                       for i in range(c.prefix_layers)]
+        self.expert = [{k: part(f"expert.{i}.{k}") for k in ("qkv", "o", "gate_up", "down")}
+                       for i in range(c.expert_layers)]
+        for k in ("post_ln_w", "post_ln_b", "projector", "embed_tokens", "action_in", "action_out", "time_mlp_in",
+                  "time_mlp_out", "ada_dense"):
+            setattr(self, k, part(k))
 
     # ------------------------------------------------------------------ buffers
     def _alloc(self):
@@ -225,19 +344,47 @@ class Pi05:
             q_emlp=QuantBuf(A, c.expert_mlp, P, d), v_out=torch.empty((A, c.action_dim), dtype=torch.float32, device=d),
             pos_suffix=torch.arange(S, S + A, dtype=torch.int32, device=d),
         )
+        for _, obj in self._named_parts():
+            if isinstance(obj, TcLinear):
+                obj.ws = self.workspace
+        # additive attention bias per key (0 or the reference's mask value) over the cache rows
+        self.key_bias = torch.zeros((c.max_seq,), dtype=bf, device=d)
         self.tokens = torch.zeros((c.text_len,), dtype=torch.long, device=d)
         self.images = torch.zeros((c.num_images, c.image_size, c.image_size, 3), dtype=torch.uint8, device=d)
         self.noise = torch.zeros((A, c.action_dim), dtype=torch.float32, device=d)
         self.actions = torch.zeros((A, c.action_dim), dtype=torch.float32, device=d)
 
     # ------------------------------------------------------------------ stages
+    def set_valid(self, image_valid=None, prompt_len=None):
+        """Declare which prefix tokens exist: `image_valid[i]` per camera, and the number of prompt tokens
+        before the padding.  Updates the position ids (`cumsum(valid) - 1`; action tokens continue at
+        `sum(valid)`) and the additive key bias in place, so a captured graph picks them up on its next replay."""
+        c = self.cfg
+        image_valid = [True] * c.num_images if image_valid is None else [bool(v) for v in image_valid]
+        prompt_len = c.text_len if prompt_len is None else int(prompt_len)
+        if len(image_valid) != c.num_images or not 0 <= prompt_len <= c.text_len:
+            raise TurboPiError("set_valid: one flag per camera and 0 <= prompt_len <= text_len")
+        valid = torch.cat([torch.full((c.image_tokens,), v) for v in image_valid] + [torch.arange(c.text_len) < prompt_len])
+        if not bool(valid.any()):
+            raise TurboPiError("set_valid: at least one prefix token must be valid")
+        pos = (torch.cumsum(valid.long(), 0) - 1).clamp_min(0)
+        first = int(valid.sum())
+        S, A = c.prefix_len, c.action_horizon
+        bias = torch.zeros(c.max_seq, dtype=torch.float32)
+        bias[:S][~valid] = -2.3819763e38                      # the reference's mask value (pi0_pytorch.py:185-188)
+        self.b["pos_prefix"].copy_(pos.to(torch.int32))
+        self.b["pos_suffix"].copy_(torch.arange(first, first + A, dtype=torch.int32))
+        self.key_bias.copy_(bias.to(torch.bfloat16))
+        self.valid = valid
+
     def _attention(self, q, k, v, out):
-        """q [L, H*D] -> softmax(q k^T / sqrt(D)) v, all heads sharing one K/V head; no mask
-        (prefix tokens are mutually visible, action tokens see the whole prefix and each other)."""
+        """q [L, H*D] -> softmax(q k^T / sqrt(D) + key bias) v, all heads sharing one K/V head.  Prefix
+        tokens see every valid prefix token, action tokens see the valid prefix and each other."""
         c = self.cfg
         L = q.shape[0]
         qh = q.view(L, c.heads, c.head_dim).transpose(0, 1).unsqueeze(0)
-        o = F.scaled_dot_product_attention(qh, k[None, None], v[None, None], enable_gqa=True)
+        o = F.scaled_dot_product_attention(qh, k[None, None], v[None, None],
+                                           attn_mask=self.key_bias[None, None, None, :k.shape[0]], enable_gqa=True)
         out.view(L, c.heads, c.head_dim).copy_(o[0].transpose(0, 1))
 
     def vision_tower(self):
@@ -379,9 +526,12 @@ class Pi05:
         self._graph, self._graph_steps = g, num_steps
 
     @torch.no_grad()
-    def infer(self, images_u8, tokens, noise, num_steps=10, use_graph=True):
+    def infer(self, images_u8, tokens, noise, num_steps=10, use_graph=True, image_valid=None, prompt_len=None):
         """images_u8 [num_images, H, W, 3] uint8, tokens [text_len] int64, noise [horizon, action_dim] fp32
-        (host or device tensors).  Returns the device tensor of actions [horizon, action_dim] fp32."""
+        (host or device tensors); `image_valid` / `prompt_len` as in `set_valid` (default: everything valid).
+        Returns the device tensor of actions [horizon, action_dim] fp32."""
+        if image_valid is not None or prompt_len is not None or not bool(self.valid.all()):
+            self.set_valid(image_valid, prompt_len)
         self.images.copy_(images_u8, non_blocking=True)
         self.tokens.copy_(tokens, non_blocking=True)
         self.noise.copy_(noise, non_blocking=True)

@@ -36,7 +36,8 @@ def case_gemm(args):
     dev = torch.device("cuda:0")
     g = torch.Generator(device=dev).manual_seed(0)
     x = torch.randn(args.M, args.K, device=dev, generator=g).to(torch.bfloat16)
-    lin = TcLinear(torch.randn(args.N, args.K, device=dev, generator=g) * 0.02)
+    lin = TcLinear.from_weight(torch.randn(args.N, args.K, device=dev, generator=g) * 0.02)
+    lin.ws = ops.gemm_workspace(dev)
     q = ops.QuantBuf(args.M, args.K, args.pieces, dev)
     out = torch.empty((args.M, args.N), dtype=torch.bfloat16, device=dev)
 
