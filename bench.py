@@ -148,7 +148,7 @@ def run_ours(args):
         for s in range(NSETS):
             probs = [dict(x=x[K], weight_packed=p, weight_scales=sc, global_scale=gs, out=oo)
                      for (p, sc, gs, N, K), oo in zip(sets[s], outs[s])]
-            tcs.append(ops.TcGemv(probs, pieces=3, pdl=not args.no_pdl))
+            tcs.append(ops.TcGemv(probs, pieces=3, pdl=not args.no_pdl, fused=not args.no_fuse))
 
     def launch_step(i):
         if tcs is not None:
@@ -157,6 +157,7 @@ def run_ours(args):
             groups[i % NSETS].launch()
 
     step_graphs = None
+    timed_graph = None
     if not args.no_graph:
         # one CUDA graph per weight set: a step is a single graph launch on the host side
         side = torch.cuda.Stream(device=device)
@@ -170,6 +171,12 @@ def run_ours(args):
             with torch.cuda.graph(g, stream=side):
                 launch_step(s)
             step_graphs.append(g)
+        # the timed region is ONE graph holding all `steps` passes (weight sets rotating), so that the
+        # device, not the host's replay loop, paces it
+        timed_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(timed_graph, stream=side):
+            for i in range(args.steps):
+                launch_step(i)
 
     def step(i):
         if step_graphs is not None:
@@ -191,13 +198,16 @@ def run_ours(args):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.profiler.start()       # `ncu --profile-from-start off` captures the timed region only
     e0.record(stream)
-    for i in range(args.steps):
-        step(i)
+    if timed_graph is not None:
+        timed_graph.replay()
+    else:
+        for i in range(args.steps):
+            step(i)
     e1.record(stream)
     group.barrier()
     torch.cuda.profiler.stop()
     ms = group.max_over_ranks(e0.elapsed_time(e1))
-    launches = args.steps * (2 if tcs is not None else 1)
+    launches = args.steps * (2 if (tcs is not None and args.no_fuse) else 1)
     per_launch_s = (e0.elapsed_time(e1) / 1e3) / args.steps   # the GEMV launch; the quantisers ride in its shadow
 
     # ---- end to end: host activations in, host results out, through the Python API --------------------
@@ -211,7 +221,7 @@ def run_ours(args):
             probs.append(dict(x=x[K], weight_packed=p, weight_scales=sc, out=out_flat[s][off:off + N].view(1, N),
                               global_scale=gs))
             off += N
-        e2e_groups.append(ops.GroupedGemv(probs, BLOCK) if tcs is None else ops.TcGemv(probs, pieces=3, pdl=not args.no_pdl))
+        e2e_groups.append(ops.GroupedGemv(probs, BLOCK) if tcs is None else ops.TcGemv(probs, pieces=3, pdl=not args.no_pdl, fused=not args.no_fuse))
     h_out = torch.empty_like(out_flat[0], device="cpu").pin_memory()
     h2d = sum(t.numel() * t.element_size() for t in hx.values())
     d2h = h_out.numel() * h_out.element_size()
@@ -281,10 +291,14 @@ def run_ours(args):
                                    "(gate,up 1024->4096; down 4096->1024) = 54 matrices per step, E4M3 block-16 "
                                    "scales + fp32 global scale, bf16 in/out",
                        "launch": ("one grouped launch per step (tpb200_nvfp4_gemv_grouped)" if tcs is None else
-                                  "activation-piece quantiser + one grouped tensor-core launch per step" + ("" if args.no_pdl else ", chained by programmatic dependent launch") + " "
-                                  "(tpb200_nvfp4_gemv_tc)"),
+                                  ("activation-piece quantiser + one grouped tensor-core launch per step "
+                                   "(tpb200_nvfp4_quantize_acts_tc, tpb200_nvfp4_gemv_tc)" if args.no_fuse else
+                                   "ONE grouped tensor-core launch per step, activations quantised inside it "
+                                   "(tpb200_nvfp4_gemv_tc_fused)") +
+                                  ("" if args.no_pdl else ", steps chained by programmatic dependent launch")),
                        "l2": f"{NSETS} weight sets of {STEP_BYTES / 1e6:.1f} MB rotated per step (> 126 MB L2)",
-                       "graph": "each step replays one CUDA graph" if step_graphs is not None else "direct launches",
+                       "graph": ("the timed region is one CUDA graph of all steps (device-paced)" if timed_graph is not None
+                                 else "direct launches"),
                        "parallelism": f"{world} independent replica(s), no collective",
                        "warmup_note": "warm-up extended to >= 0.4 s so clocks are sampled under load"},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
@@ -413,18 +427,25 @@ def run_extras(device, sets, x):
     for sidx in range(NSETS):
         probs = [dict(x=x[K], weight_packed=p, weight_scales=sc, global_scale=gs,
                       out=torch.empty((1, N), dtype=torch.bfloat16, device=device)) for (p, sc, gs, N, K) in sets[sidx]]
-        tcs.append(ops.TcGemv(probs, pieces=3))
-    t = time_replays(lambda i: tcs[i % NSETS].launch(), 400)
-    ex["tc_grouped_54_quantize_plus_gemv"] = {"us_per_step": t * 1e6, "gbps": STEP_BYTES / t / 1e9}
-    t = time_replays(lambda i: tcs[i % NSETS].gemv(), 400)
-    ex["tc_grouped_54_gemv_only"] = {"us_per_step": t * 1e6, "gbps": STEP_BYTES / t / 1e9}
+        tcs.append(ops.TcGemv(probs, pieces=3, fused=False))
+    t = time_launches(lambda i: tcs[i % NSETS].launch(), 64)
+    ex["tc_grouped_54_quantiser_launch_plus_gemv"] = {"us_per_step": t * 1e6, "gbps": STEP_BYTES / t / 1e9}
+    t = time_launches(lambda i: tcs[i % NSETS].gemv(), 64)
+    ex["tc_grouped_54_gemv_on_pretiled_activations"] = {"us_per_step": t * 1e6, "gbps": STEP_BYTES / t / 1e9}
     for (Nsel, Ksel, name) in ((INTER, HIDDEN, "gateup_1024x4096"), (HIDDEN, INTER, "down_4096x1024")):
         ms_ = [m for m in flat if m[3] == Nsel][:24]
-        singles = [ops.TcGemv([dict(x=x[Ksel], weight_packed=p, weight_scales=sc, global_scale=gs,
-                                    out=torch.empty((1, N), dtype=torch.bfloat16, device=device))], pieces=3)
-                   for (p, sc, gs, N, K) in ms_]
-        t = time_launches(lambda i: singles[i % len(singles)].gemv(), 48)
-        ex[f"tc_single_launch_M1_{name}"] = {"us": t * 1e6, "gbps": algorithmic_bytes(Nsel, Ksel) / t / 1e9}
+        for M in (1, 4, 16):
+            xm = torch.randn(M, Ksel, device=device).to(torch.bfloat16)
+            singles = [ops.TcGemv([dict(x=xm, weight_packed=p, weight_scales=sc, global_scale=gs,
+                                        out=torch.empty((M, N), dtype=torch.bfloat16, device=device))], pieces=3)
+                       for (p, sc, gs, N, K) in ms_]
+            for pdl in (False, True):
+                for sg in singles:
+                    sg.flags = ops.FLAG_PDL if pdl else ops.FLAG_NONE
+                t = time_launches(lambda i: singles[i % len(singles)].launch(), 48)
+                ex[f"tc_single_launch_M{M}_{name}" + ("_pdl" if pdl else "")] = {
+                    "us": t * 1e6, "gbps": algorithmic_bytes(Nsel, Ksel, M) / t / 1e9}
+            del singles
     del tcs
     # (e) prefix NVFP4 x NVFP4 GEMMs on tcgen05 (e2m1 activations and weights, UE4M3 block-16 scales)
     for (M, N, K, name) in ((712, 16384, 2048, "gemma2b_gateup_M712"), (712, 2048, 16384, "gemma2b_down_M712"),
@@ -584,6 +605,8 @@ def main():
                     help="GEMV kernel: CUDA-core decode (cuda) or tensor-core (tc)")
     ap.add_argument("--no-graph", action="store_true", help="launch the step's kernels directly instead of one CUDA graph")
     ap.add_argument("--no-extras", action="store_true", help="skip the per-configuration side measurements")
+    ap.add_argument("--no-fuse", action="store_true",
+                    help="--path tc: stand-alone activation quantiser launch + GEMV instead of the fused launch")
     ap.add_argument("--no-pdl", action="store_true",
                     help="--path tc: no programmatic dependent launch between quantiser and GEMV")
     ap.add_argument("--no-clock-warmup", action="store_true",

@@ -6,7 +6,8 @@
  *   - all tensor pointers are caller-owned DEVICE memory, row-major, 16-byte aligned;
  *   - the call only enqueues work on `stream` (no allocation, no synchronisation,
  *     no global mutable state), so it may be captured in a CUDA graph and is safe
- *     to call concurrently on different streams;
+ *     to call concurrently on different streams -- except tpb200_nvfp4_gemv_tc_static,
+ *     whose scratch is one array shared by every call on a device (see there);
  *   - the device is the calling thread's current device;
  *   - `tpb200_*` functions return TPB200_OK or a negative tpb200_status; arguments
  *     are validated on the host before anything is launched;
@@ -204,8 +205,16 @@ int tpb200_nvfp4_quantize_act_pieces(const void* x, int x_dtype, int ldx, void* 
  * chunk c of row r at c ^ (r & 7)) followed by their 2048-byte scale slab
  * (tpb200_nvfp4_gemv_tc_x_image_bytes), x_row_scale: 16 floats.  Row tiles whose K range is split
  * across CTAs are combined through `workspace` (size from tpb200_nvfp4_gemv_tc_workspace_size; the
- * caller zeroes it ONCE after allocation, the kernel leaves its counters at zero).  Launches that share
- * a workspace must not overlap.  No counterpart in the reference (its GEMVs are CUDA-core kernels).
+ * caller zeroes it ONCE after allocation, the kernel leaves its counters at zero; after a non-zero
+ * tpb200_device_error() zero it again before reuse).  Launches that share a workspace must not overlap.
+ * The host plans each launch (whole 256-row tiles dealt to the CTAs longest first; tiles are cut along K
+ * only when a launch has too few or too long tiles for the machine) and remembers the plans of the last
+ * few shape lists per calling thread.  No counterpart in the reference (its GEMVs are CUDA-core kernels).
+ *
+ * tpb200_nvfp4_gemv_tc_fused is the same GEMV with the activation quantiser inside the launch: `x` is
+ * the raw [M, K] activation tensor (x_dtype, row stride ldx elements, 0 = K) and four warps of every CTA
+ * quantise the K ranges their CTA needs straight into its stage buffers, so a decode step is ONE launch
+ * and there is no activation image in global memory.
  * ------------------------------------------------------------------------------------------- */
 typedef struct {
     const void* w_image;
@@ -226,9 +235,28 @@ int tpb200_nvfp4_quantize_acts_tc(const tpb200_act_tc* acts, int count, int x_dt
 int tpb200_nvfp4_gemv_tc(const tpb200_gemv_tc_problem* problems, int count, int M, int pieces, int bias_dtype,
                          int out_dtype, int activation, void* workspace, size_t workspace_bytes, int flags,
                          tpb200_stream_t stream);
+typedef struct {
+    const void* w_image;
+    const void* x; int ldx; /* 0 = K */
+    const void* bias; void* out;
+    int N; int K; int ldo; /* 0 = N */
+    float global_scale;
+} tpb200_gemv_tc_fused_problem;
+size_t tpb200_nvfp4_gemv_tc_fused_workspace_size(const tpb200_gemv_tc_fused_problem* problems, int count);
+int tpb200_nvfp4_gemv_tc_fused(const tpb200_gemv_tc_fused_problem* problems, int count, int M, int pieces, int x_dtype,
+                               int bias_dtype, int out_dtype, int activation, void* workspace, size_t workspace_bytes,
+                               int flags, tpb200_stream_t stream);
+
+/* What the launch planner does with a list of [N, K] problems on a GPU of `sms` SMs (host only, no device
+ * needed): CTAs used, work units, K stages of the busiest CTA and of the whole launch, tiles cut along K,
+ * scratch bytes.  For tests and capacity planning. */
+typedef struct {
+    int grid; int units; int max_load_stages; int total_stages; int cut_tiles; size_t workspace_bytes;
+} tpb200_gemv_tc_plan_info;
+int tpb200_nvfp4_gemv_tc_plan(const int* N, const int* K, int count, int sms, tpb200_gemv_tc_plan_info* info);
 
 /* tpb200_nvfp4_gemv_tc for callers that cannot allocate device memory (no counterpart in the reference).
- * The split-K scratch is a 16 MiB array built into the library (tpb200_nvfp4_gemv_tc_static_capacity());
+ * The split-K scratch is a 4 MiB array built into the library (tpb200_nvfp4_gemv_tc_static_capacity());
  * launches whose plan needs more are refused with TPB200_ERR_WORKSPACE.  The call allocates nothing.
  * The first call on a device looks up the array's device address; make that first call outside of any
  * stream capture.  All calls on a device share the one array: two calls that may run at the same time

@@ -1,5 +1,6 @@
 """Parity of the tensor-core NVFP4 GEMV (weights as the MMA's 128-row operand, residual-piece
-activations, split-K through scratch) with the CPU oracle and with the CUDA-core GEMV."""
+activations quantised inside the launch or read from a pre-tiled image, host-planned schedule with
+K cuts through scratch where a launch has few tiles) with the CPU oracle and with the CUDA-core GEMV."""
 import numpy as np
 import pytest
 import torch
@@ -46,9 +47,10 @@ def test_weight_tiling_is_the_swizzled_image(cuda_device):
     assert slabs[1, :, 1].sum() == 0                   # ... with zero scales
 
 
+@pytest.mark.parametrize("fused", [True, False])
 @pytest.mark.parametrize("M", [1, 4, 16])
 @pytest.mark.parametrize("N,K", [(4096, 1024), (1024, 4096), (16384, 2048), (2048, 16384), (200, 272), (2560, 2048)])
-def test_tc_gemv_matches_oracle(cuda_device, M, N, K):
+def test_tc_gemv_matches_oracle(cuda_device, M, N, K, fused):
     from turbopi_b200 import _lib, ops
     rng = np.random.default_rng(M + N + K)
     packed, sbytes, g = _weights(rng, N, K)
@@ -58,7 +60,7 @@ def test_tc_gemv_matches_oracle(cuda_device, M, N, K):
     out = buf[16:16 + M]
     tc = ops.TcGemv([dict(x=_dev(x, cuda_device, torch.bfloat16), weight_packed=_dev(packed, cuda_device),
                           weight_scales=_dev(sbytes, cuda_device), global_scale=g, out=out,
-                          bias=_dev(bias, cuda_device))], pieces=3)
+                          bias=_dev(bias, cuda_device))], pieces=3, fused=fused)
     tc.launch()
     tc.launch()                       # the counters are back at zero: a second launch gives the same bytes
     y1 = out.cpu().numpy().copy()
@@ -92,10 +94,11 @@ def test_tc_grouped_matches_cuda_core_gemv(cuda_device):
         assert rel_err(p["out"].float().cpu().numpy(), o.float().cpu().numpy()) <= 1e-2
 
 
-def test_tc_gemv_chain_under_programmatic_dependent_launch(cuda_device):
-    """Quantiser -> GEMV -> quantiser -> GEMV ... launched with programmatic stream serialisation (the GEMV
-    requests its first weight blocks while the quantiser still runs): same bytes as the plain launches,
-    also when the chain is captured in a CUDA graph and replayed."""
+@pytest.mark.parametrize("fused", [True, False])
+def test_tc_gemv_chain_under_programmatic_dependent_launch(cuda_device, fused):
+    """GEMV -> GEMV ... (or quantiser -> GEMV -> quantiser -> GEMV ...) launched with programmatic stream
+    serialisation (a GEMV requests its first weight blocks while its predecessor still runs): same bytes
+    as the plain launches, also when the chain is captured in a CUDA graph and replayed."""
     from turbopi_b200 import _lib, ops
     rng = np.random.default_rng(77)
     specs = [(4096, 1024), (4096, 1024), (1024, 4096)] * 3
@@ -107,7 +110,7 @@ def test_tc_gemv_chain_under_programmatic_dependent_launch(cuda_device):
         outs = [torch.zeros((1, N), dtype=torch.bfloat16, device=cuda_device) for (N, K) in specs]
         tc = ops.TcGemv([dict(x=xs[K], weight_packed=_dev(p, cuda_device), weight_scales=_dev(s, cuda_device),
                               global_scale=g, out=o) for (N, K), (p, s, g), o in zip(specs, mats, outs)],
-                        pieces=3, pdl=pdl)
+                        pieces=3, pdl=pdl, fused=fused)
         return tc, outs
 
     plain, want = build(False)
@@ -151,3 +154,71 @@ def test_tc_gemv_reads_the_gemm_weight_image(cuda_device):
     assert torch.equal(y1, y2)
     ref = nvfp4.gemv_dequant_matmul(x.float().cpu().numpy(), packed, sbytes, None, 0, 16, g, True)
     assert rel_err(y1.cpu().numpy(), ref) <= 1e-2
+
+
+@pytest.mark.parametrize("M", [1, 3, 16])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_fused_quantiser_equals_stand_alone_quantiser(cuda_device, M, dtype):
+    """The activation pieces made inside the GEMV launch are the ones the stand-alone quantiser writes:
+    both forms return the same bytes, for every activation dtype, for a grouped launch whose problems
+    share activation tensors and for a K that ends inside a 256-wide stage."""
+    from turbopi_b200 import _lib, ops
+    rng = np.random.default_rng(5 + M)
+    shapes = [(512, 1024), (512, 1024), (768, 4096), (300, 1104), (256, 4096)]
+    xs = {K: (torch.from_numpy(rng.normal(size=(M, K)).astype(np.float32)) * 3.0).to(cuda_device).to(dtype)
+          for K in (1024, 4096, 1104)}
+    mats = [_weights(rng, N, K) for (N, K) in shapes]
+
+    def run(fused):
+        outs = [torch.zeros((M, N), dtype=torch.float32, device=cuda_device) for (N, K) in shapes]
+        tc = ops.TcGemv([dict(x=xs[K], weight_packed=_dev(p, cuda_device), weight_scales=_dev(s, cuda_device),
+                              global_scale=g, out=o) for (N, K), (p, s, g), o in zip(shapes, mats, outs)],
+                        pieces=3, fused=fused)
+        tc.launch()
+        torch.cuda.synchronize()
+        return outs
+
+    a, b = run(True), run(False)
+    assert _lib.load().tpb200_device_error(0) == 0
+    for (N, K), ya, yb, (p, s, g) in zip(shapes, a, b, mats):
+        assert torch.equal(ya, yb), (N, K)
+        ref = nvfp4.gemv_dequant_matmul(xs[K].float().cpu().numpy(), p, s, None, 0, 16, g, True)
+        assert rel_err(ya.cpu().numpy(), ref) <= 1e-2
+
+
+def test_tc_gemv_strided_activations_and_outputs(cuda_device):
+    """Activation rows and output rows with a pitch larger than their width (views into wider buffers)."""
+    from turbopi_b200 import ops
+    rng = np.random.default_rng(12)
+    N, K, M = 640, 2048, 5
+    packed, sbytes, g = _weights(rng, N, K)
+    xbuf = torch.from_numpy(rng.normal(size=(M, K + 64)).astype(np.float32)).to(cuda_device).to(torch.bfloat16)
+    obuf = torch.full((M, N + 32), 9.0, dtype=torch.float32, device=cuda_device)
+    x, out = xbuf[:, :K], obuf[:, :N]
+    ops.TcGemv([dict(x=x, weight_packed=_dev(packed, cuda_device), weight_scales=_dev(sbytes, cuda_device),
+                     global_scale=g, out=out)], pieces=3).launch()
+    ref = nvfp4.gemv_dequant_matmul(x.float().cpu().numpy(), packed, sbytes, None, 0, 16, g, True)
+    assert rel_err(out.cpu().numpy(), ref) <= 1e-2
+    assert (obuf[:, N:] == 9.0).all()
+
+
+def test_tc_gemv_54_matrix_step_matches_oracle(cuda_device):
+    """The benchmark's step: 18 x (gate, up 1024 -> 4096; down 4096 -> 1024) in one launch (648 whole tiles
+    dealt to the CTAs, no tile cut), spot-checked against the oracle on three matrices."""
+    from turbopi_b200 import _lib, ops
+    rng = np.random.default_rng(54)
+    shapes = [(4096, 1024), (4096, 1024), (1024, 4096)] * 18
+    xs = {K: _dev(formats.round_to_bf16(rng.normal(size=(1, K)).astype(np.float32)), cuda_device, torch.bfloat16)
+          for K in (1024, 4096)}
+    mats = [_weights(rng, N, K) for (N, K) in shapes]
+    outs = [torch.zeros((1, N), dtype=torch.bfloat16, device=cuda_device) for (N, K) in shapes]
+    tc = ops.TcGemv([dict(x=xs[K], weight_packed=_dev(p, cuda_device), weight_scales=_dev(s, cuda_device),
+                          global_scale=g, out=o) for (N, K), (p, s, g), o in zip(shapes, mats, outs)], pieces=3)
+    assert tc.workspace.numel() <= 512            # nothing is cut: no partial sums
+    tc.launch()
+    torch.cuda.synchronize()
+    assert _lib.load().tpb200_device_error(0) == 0
+    for i in (0, 26, 53):
+        (N, K), (p, s, g) = shapes[i], mats[i]
+        ref = nvfp4.gemv_dequant_matmul(xs[K].float().cpu().numpy(), p, s, None, 0, 16, g, True)
+        assert rel_err(outs[i].float().cpu().numpy(), ref) <= 1e-2, i

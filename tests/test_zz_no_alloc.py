@@ -23,11 +23,12 @@ def _problem(rng, N, K, M, device):
 def test_static_scratch_entry_matches_workspace_entry(cuda_device):
     from turbopi_b200 import _lib, ops
     lib = _lib.load()
-    assert lib.tpb200_nvfp4_gemv_tc_static_capacity() == 16 << 20
+    assert lib.tpb200_nvfp4_gemv_tc_static_capacity() == 4 << 20
     rng = np.random.default_rng(77)
     # two problems in one launch; the second one's K is split across CTAs, so the scratch is really used
     probs = [_problem(rng, 4096, 1024, 2, cuda_device), _problem(rng, 1024, 4096, 2, cuda_device)]
-    tc = ops.TcGemv(probs, pieces=3)
+    tc = ops.TcGemv(probs, pieces=3, fused=False)
+    assert tc.workspace.numel() > 4096                    # the plan cuts tiles: partial sums go through scratch
     tc.quantize()
     tc.gemv()                                             # existing entry point, caller-provided workspace
     torch.cuda.synchronize()
@@ -45,12 +46,23 @@ def test_static_scratch_entry_matches_workspace_entry(cuda_device):
 
 
 def test_static_scratch_entry_refuses_what_does_not_fit(cuda_device):
-    """A plan that needs more than the built-in 16 MiB is rejected on the host, nothing is launched."""
-    from turbopi_b200 import _lib
+    """A plan that needs more than the built-in 4 MiB is rejected on the host and nothing is launched.
+    Every buffer is real, so a planner that stopped refusing would compute, not fault."""
+    from turbopi_b200 import _lib, ops
     lib = _lib.load()
-    # 1024 row tiles, 8 K-splits of 16 token rows each: 262144 x 16384 needs far more than 16 MiB;
-    # the pointers are never dereferenced because the size check comes first
-    arr = (_lib.GemvTcProblem * 1)()
-    arr[0] = _lib.GemvTcProblem(256, 256, 256, 0, 256, 262144, 16384, 0, 1.0)
-    st = lib.tpb200_nvfp4_gemv_tc_static(arr, 1, 1, 3, 0, 2, 0, 0, None)
-    assert st == -6 and b"workspace" in lib.tpb200_status_string(st)
+    N, K, M = 25600, 16384, 1       # 100 tiles of 64 K stages: the plan cuts every tile four ways
+    image = torch.zeros(int(lib.tpb200_nvfp4_tiled_b_bytes(N, K)), dtype=torch.uint8, device=cuda_device)
+    x = torch.ones((M, K), dtype=torch.bfloat16, device=cuda_device)
+    out = torch.full((M, N), 7.0, dtype=torch.float32, device=cuda_device)
+    tc = ops.TcGemv([dict(x=x, w_image=image, global_scale=1.0, out=out)], pieces=3, fused=False)
+    assert tc.workspace.numel() > lib.tpb200_nvfp4_gemv_tc_static_capacity()
+    tc.quantize()
+    with pytest.raises(_lib.TurboPiError) as e:
+        tc.gemv_static()
+    assert "workspace" in str(e.value)
+    torch.cuda.synchronize()
+    assert (out == 7.0).all()
+    tc.gemv()                                             # the same launch with a caller-provided workspace runs
+    torch.cuda.synchronize()
+    assert (out == 0.0).all()
+    assert lib.tpb200_device_error(0) == 0

@@ -47,6 +47,16 @@ class GemvTcProblem(ctypes.Structure):
                 ("N", c_int), ("K", c_int), ("ldo", c_int), ("global_scale", c_float)]
 
 
+class GemvTcFusedProblem(ctypes.Structure):
+    _fields_ = [("w_image", c_void_p), ("x", c_void_p), ("ldx", c_int), ("bias", c_void_p), ("out", c_void_p),
+                ("N", c_int), ("K", c_int), ("ldo", c_int), ("global_scale", c_float)]
+
+
+class GemvTcPlanInfo(ctypes.Structure):
+    _fields_ = [("grid", c_int), ("units", c_int), ("max_load_stages", c_int), ("total_stages", c_int),
+                ("cut_tiles", c_int), ("workspace_bytes", c_size_t)]
+
+
 class ActTc(ctypes.Structure):
     _fields_ = [("x", c_void_p), ("ldx", c_int), ("K", c_int), ("x_image", c_void_p), ("x_row_scale", c_void_p)]
 
@@ -91,6 +101,11 @@ SIGNATURES = {
     "tpb200_nvfp4_quantize_acts_tc": (c_int, [ctypes.POINTER(ActTc), c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "tpb200_nvfp4_gemv_tc": (c_int, [ctypes.POINTER(GemvTcProblem), c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                      c_size_t, c_int, c_void_p]),
+    "tpb200_nvfp4_gemv_tc_fused_workspace_size": (c_size_t, [ctypes.POINTER(GemvTcFusedProblem), c_int]),
+    "tpb200_nvfp4_gemv_tc_fused": (c_int, [ctypes.POINTER(GemvTcFusedProblem), c_int, c_int, c_int, c_int, c_int, c_int,
+                                           c_int, c_void_p, c_size_t, c_int, c_void_p]),
+    "tpb200_nvfp4_gemv_tc_plan": (c_int, [ctypes.POINTER(c_int), ctypes.POINTER(c_int), c_int, c_int,
+                                          ctypes.POINTER(GemvTcPlanInfo)]),
     "tpb200_row_transform_quantize": (c_int, [ctypes.POINTER(RowOpArgs), c_void_p]),
     "tpb200_nvfp4_gemv_tc_static_capacity": (c_size_t, []),
     "tpb200_nvfp4_gemv_tc_static": (c_int, [ctypes.POINTER(GemvTcProblem), c_int, c_int, c_int, c_int, c_int, c_int,

@@ -7,30 +7,27 @@
 // along N: piece p of token t is B row 16 p + t, so one MMA (N = 16 * pieces) per 64-wide K
 // atom handles all pieces and the epilogue adds the pieces' columns.
 //
-// Both operands are stored PRE-TILED in the shared-memory image of the 128-byte swizzle, scales
-// included, so that a stage is TWO plain 1-D bulk copies -- no tensor maps, any number of problems
-// per launch:
-//   weights      the tensor-core GEMM's B image (tpb200_nvfp4_tile_weights): block (n_blk, ks) of
-//                36 KB = 256 rows x 128 B of codes (16-byte chunk c of row r at c ^ (r & 7)) + the two
-//                2 KB scale slabs; one image serves the prefill GEMM and this decode GEMV;
-//   activations  block ks = 16 * pieces rows x 128 B of codes in the same pattern + one 2 KB scale slab.
-// A stage (36 KB of weights + <= 10 KB of activations) feeds two MMAs per 64-wide K atom (weight rows
-// 0..127 and 128..255, two accumulators) against the same activation operand.
+// Weights are stored PRE-TILED in the shared-memory image of the 128-byte swizzle, scales included:
+// the tensor-core GEMM's B image (tpb200_nvfp4_tile_weights), block (n_blk, ks) of 36 KB = 256 rows x
+// 128 B of codes (16-byte chunk c of row r at c ^ (r & 7)) + the two 2 KB scale slabs; one image
+// serves the prefill GEMM and this decode GEMV.  A stage = one such block (four plain 1-D bulk copies
+// issued side by side) + the activation block of the same K range (16 * pieces rows x 128 B of codes
+// in the same pattern + one 2 KB scale slab), feeding two MMAs per 64-wide K atom (weight rows 0..127
+// and 128..255, two accumulators).  A ring of five stages keeps the stream going.
 //
-// One lane issues the two bulk copies of a stage; a ring of four stages (176 KB) keeps the stream
-// going.  (Streaming alone is not the limit: a ring of 36-48 KB bulk copies reads HBM at 7.1 TB/s
-// over 148 SMs when nothing consumes the data, and four warps of 16-byte cp.async copies do no
-// better.  What this kernel adds per stage -- scale copies and MMAs between `full` and `empty`,
-// and the fenced hand-over of split-K partial sums -- is what keeps it at ~3 TB/s.)
+// The activation block comes from one of two places:
+//   fused      four warps of the CTA quantise the K range of the raw [M, K] activations straight into
+//              the stage buffer while the weight block is in flight (row amax -> power-of-two pre-scale
+//              -> residual pieces; the same arithmetic as the stand-alone quantiser), so a decode step
+//              is ONE launch;
+//   pre-tiled  a fifth bulk copy from an image written by tpb200_nvfp4_quantize_act(s)_tc.
 //
-// Work unit = (problem, 256-row tile, K split); all units carry (nearly) the same number of stages
-// and every CTA owns a contiguous range of equally many.  Consecutive units of one tile inside a
-// CTA's range form a GROUP that is accumulated in tensor memory as one K range, so only the tiles cut
-// by a range boundary are shared between CTAs: each of their groups writes its partial sums (only the
-// valid tokens) to caller-provided scratch, and the CTA that arrives last on the tile's counter adds
-// them in K order (deterministic), applies the epilogue and resets the counter.  Nothing ever waits
-// on another CTA.  (Handing over partial sums costs a device-wide fence, ~2.5 us per hand-over; with
-// one per unit the CTAs that drew down-projection units finished 17 us after the others.)
+// Schedule.  The host plans every launch: a work unit is (problem, 256-row tile, K range); whole
+// tiles are dealt to the CTAs longest-first so that no partial sums cross CTAs, and only when a launch
+// has too few or too long tiles for the machine are tiles cut along K.  A cut tile's pieces write their
+// partial sums (valid tokens only) to caller-provided scratch and the CTA that arrives last on the tile's
+// counter adds them in K order (deterministic), applies the epilogue and resets the counter.  Nothing
+// ever waits on another CTA.  The unit list travels in the kernel's parameter space.
 #include <algorithm>
 #include <atomic>
 
@@ -48,9 +45,11 @@ constexpr int kMaxNB = 64;            // 16 tokens x 4 pieces
 // takes as many stages as fit: 5 for up to 3 pieces, 4 for 4
 __host__ __device__ constexpr int stage_bytes(int pieces) { return kWBlock + 16 * pieces * 128 + kSfSlab; }
 __host__ __device__ constexpr int num_stages(int pieces) {
-    return (227 * 1024 - 2048) / stage_bytes(pieces) < kMaxStages ? (227 * 1024 - 2048) / stage_bytes(pieces) : kMaxStages;
+    return (227 * 1024 - 3072) / stage_bytes(pieces) < kMaxStages ? (227 * 1024 - 3072) / stage_bytes(pieces) : kMaxStages;
 }
-constexpr int kThreads = 224;          // warps: 0 producer, 1 MMA issuer, 2..5 epilogue, 6 scale copier
+// warps: 0 producer, 1 MMA issuer, 2..5 epilogue, 6 scale copier, 7..10 activation quantisers
+constexpr int kThreads = 352;
+constexpr int kActWarp0 = 7;
 constexpr int kTmemCols = 512;
 // tensor memory: accumulator (buffer b, row half h) at column b * 128 + h * 64, then the scales
 // two sets of scale columns (stages alternate): 32 for the weights' two row halves + 16 for the activations
@@ -58,34 +57,49 @@ constexpr uint32_t kSfSetCols = 48;
 constexpr uint32_t kSfaCol = 256;
 constexpr uint32_t kSfbCol = kSfaCol + 32;
 constexpr int kMaxProblems = TPB200_MAX_GROUP;
+constexpr int kMaxCtas = 256;
+constexpr int kRsRing = 16;           // row multipliers of the units in flight between quantiser and epilogue
+constexpr int kSlotFloats = 16 * 256; // partial sums of one unit: [token][row of the tile]
 
 struct TcProblem {
     const uint8_t* w_image;     // [row_tiles of 256][k_stages][36864]
-    const uint8_t* x_image;     // [k_stages][NB * 128 + 2048]
-    const float* row_scale;     // [M]
+    const void* x;              // fused: raw activations [M, ldx]; pre-tiled: [k_stages][NB * 128 + 2048]
+    const float* row_scale;     // pre-tiled only: [M]
     const void* bias;
     void* out;
     int N, K;
-    int ldo;
+    int ldo, ldx;
     float global_scale;
     int k_stages;
-    int row_tiles;
-    int splits;                 // K splits per row tile
-    int stages_per_split;
-    int unit_begin;
-    int scratch_off;            // float offset of this problem's partials [splits][16][row_tiles*128]
-    int counter_off;            // int offset of this problem's per-tile counters
 };
 
+// One work unit of a CTA: K stages [ks0, ks1) of row tile rt of problem p, accumulated in tensor memory
+// as one K range.
+struct TcUnit {
+    uint8_t p;
+    uint8_t shared;      // the tile is cut along K: hand the partial sums over
+    uint16_t rt;
+    uint16_t ks0, ks1;
+    uint16_t slot0;      // first partial-sum slot of the tile
+    uint16_t counter;    // the tile's arrival counter
+    uint8_t slot;        // this unit's slot, in K order
+    uint8_t nslots;      // units the tile was cut into
+    uint16_t pad;
+};
+static_assert(sizeof(TcUnit) == 16, "unit records are copied as 16-byte words");
+
+template <int kMaxUnits>
 struct TcParams {
     int num_problems;
-    int total_units;
     int M;
     int pieces;
-    int bias_dtype, out_dtype, activation;
+    int x_dtype, bias_dtype, out_dtype, activation;
+    int fused;
     float* scratch;
     int* counters;
     TcProblem prob[kMaxProblems];
+    uint16_t cta_begin[kMaxCtas + 1];
+    TcUnit units[kMaxUnits];
 };
 
 struct SharedControl {
@@ -98,6 +112,7 @@ struct SharedControl {
     uint32_t tmem_base;
     int abort_flag;
     int ticket;
+    float row_scale[kRsRing][16];
 };
 
 __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16]) {
@@ -110,57 +125,20 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)
         : "memory");
 }
 
-struct Unit {
-    int p, rt, split, ks0, ks1;
-};
-
-// Index of the problem that owns unit u, by bisection.  The problem table sits in the kernel's parameter
-// space and every dependent look-up with a computed index costs ~100 cycles; walking the table from its
-// start made the CTAs of the last problems begin their work 8 us after the first ones.
-__device__ __forceinline__ int find_problem(const TcParams& P, int u) {
-    int lo = 0, hi = P.num_problems - 1;
-    while (lo < hi) {
-        const int mid = (lo + hi + 1) >> 1;
-        if (u >= P.prob[mid].unit_begin) lo = mid;
-        else hi = mid - 1;
+// Power-of-two pre-scale that brings a row's largest magnitude into [1024, 2048): the block scales of the
+// pieces then sit in the upper range of UE4M3.  Returns the exponent e (pre-scale 2^e, undone by 2^-e).
+__device__ __forceinline__ int prescale_exponent(float amax) {
+    int e = 0;
+    if (amax > 0.0f && amax < 3.0e38f) {
+        int ex;
+        frexpf(amax, &ex);
+        e = 11 - ex;
     }
-    return lo;
+    return e;
 }
 
-__device__ __forceinline__ Unit decode_unit(const TcParams& P, int u, int& p_hint) {
-    while (p_hint + 1 < P.num_problems && u >= P.prob[p_hint + 1].unit_begin) ++p_hint;
-    const TcProblem& pr = P.prob[p_hint];
-    const int local = u - pr.unit_begin;
-    Unit un;
-    un.p = p_hint;
-    un.rt = local / pr.splits;
-    un.split = local - un.rt * pr.splits;
-    un.ks0 = un.split * pr.stages_per_split;
-    un.ks1 = min(pr.k_stages, un.ks0 + pr.stages_per_split);
-    return un;
-}
-
-// The group that starts at unit u: the units of u's tile from u to the end of the tile or of the CTA's range.
-struct Group {
-    int p, rt, split0, split1, ks0, ks1, next;
-};
-
-__device__ __forceinline__ Group decode_group(const TcParams& P, int u, int unit_hi, int& p_hint) {
-    const Unit un = decode_unit(P, u, p_hint);
-    const TcProblem& pr = P.prob[un.p];
-    const int tile_end = pr.unit_begin + (un.rt + 1) * pr.splits;
-    Group g;
-    g.p = un.p;
-    g.rt = un.rt;
-    g.split0 = un.split;
-    g.next = min(unit_hi, tile_end);
-    g.split1 = un.split + (g.next - u) - 1;
-    g.ks0 = un.ks0;
-    g.ks1 = min(pr.k_stages, (g.split1 + 1) * pr.stages_per_split);
-    return g;
-}
-
-__global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid_constant__ TcParams P) {
+template <int kMaxUnits>
+__global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid_constant__ TcParams<kMaxUnits> P) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int kStages = num_stages(P.pieces);
@@ -170,13 +148,15 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int NB = 16 * P.pieces;
-    const int unit_lo = static_cast<int>(static_cast<long long>(blockIdx.x) * P.total_units / gridDim.x);
-    const int unit_hi = static_cast<int>(static_cast<long long>(blockIdx.x + 1) * P.total_units / gridDim.x);
-    const int p_first = find_problem(P, unit_lo);     // every role starts its table walk here
+    const int u_lo = P.cta_begin[blockIdx.x];
+    const int u_hi = P.cta_begin[blockIdx.x + 1];
+    const bool fused = P.fused != 0;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kMaxStages; ++s) {
-            mbar_init(&ctl->full[s], 1);
+            // a stage is full when its weight block has landed (one arrival with the byte count) and,
+            // in the fused form, when each of the four quantiser warps has written its rows
+            mbar_init(&ctl->full[s], fused ? 5 : 1);
             mbar_init(&ctl->empty[s], 1);
         }
         for (int b = 0; b < 2; ++b) {
@@ -192,6 +172,16 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
         tc::tmem_alloc(&ctl->tmem_base, kTmemCols);
         tc::tmem_relinquish();
     }
+    if (fused && warp >= kActWarp0) {
+        // rows of tokens >= M are never written again: they stay zero codes with zero scales
+        const int at = threadIdx.x - kActWarp0 * 32;
+        const int abytes = NB * 128 + kSfSlab;
+        for (int s = 0; s < kStages; ++s) {
+            uint4* a = reinterpret_cast<uint4*>(smem + s * kStageBytes + kWBlock);
+            for (int i = at; i < abytes / 16; i += 128) a[i] = make_uint4(0u, 0u, 0u, 0u);
+        }
+        fence_proxy_async_smem();
+    }
     tc::fence_before_thread_sync();
     __syncthreads();
     tc::fence_after_thread_sync();
@@ -202,35 +192,32 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
     if (warp == 0) {
         // ------------------------------------------------------------ producer (whole warp): lane 0 owns the
         // barrier hand-shakes, lanes 0..3 each copy a quarter of the stage's weight block and lane 4 the
-        // activation block.  (A thread that issues a bulk copy is held for ~0.3 us whatever the size; requests
-        // issued side by side from several lanes overlap that.)  Weights never depend on the previous kernel,
-        // so the first stages' weight blocks are requested before griddepcontrol.wait; the activation image
-        // is written by the previous kernel.
-        const uint32_t xbytes = static_cast<uint32_t>(NB) * 128u + kSfSlab;
+        // pre-tiled activation block.  (A thread that issues a bulk copy is held for ~0.3 us whatever the size;
+        // requests issued side by side from several lanes overlap that.)  Weights never depend on the previous
+        // kernel, so the first stages' weight blocks are requested before griddepcontrol.wait; activations
+        // are written by the previous kernel.
+        const uint32_t xbytes = fused ? 0u : static_cast<uint32_t>(NB) * 128u + kSfSlab;
         constexpr uint32_t kQuarter = kWBlock / 4;
         int pre = 0;
-        {
-            int ph = p_first;
-            for (int u = unit_lo; u < unit_hi && pre < kStages; ++u) {
-                const Unit un = decode_unit(P, u, ph);
-                const TcProblem& pr = P.prob[un.p];
-                for (int ks = un.ks0; ks < un.ks1 && pre < kStages; ++ks, ++pre) {
-                    uint8_t* st = smem + pre * kStageBytes;
-                    const size_t blk = static_cast<size_t>(un.rt) * pr.k_stages + ks;
-                    if (lane == 0) mbar_expect_tx(&ctl->full[pre], kWBlock + xbytes);
-                    __syncwarp();
-                    if (lane < 4) {
-                        bulk_copy_g2s(st + lane * kQuarter, pr.w_image + blk * kWBlock + lane * kQuarter, kQuarter,
-                                      &ctl->full[pre]);
-                    }
+        for (int u = u_lo; u < u_hi && pre < kStages; ++u) {
+            const TcUnit un = P.units[u];
+            const TcProblem& pr = P.prob[un.p];
+            for (int ks = un.ks0; ks < un.ks1 && pre < kStages; ++ks, ++pre) {
+                uint8_t* st = smem + pre * kStageBytes;
+                const size_t blk = static_cast<size_t>(un.rt) * pr.k_stages + ks;
+                if (lane == 0) mbar_expect_tx(&ctl->full[pre], kWBlock + xbytes);
+                __syncwarp();
+                if (lane < 4) {
+                    bulk_copy_g2s(st + lane * kQuarter, pr.w_image + blk * kWBlock + lane * kQuarter, kQuarter,
+                                  &ctl->full[pre]);
                 }
             }
         }
         pdl_wait_prior_grids();
-        int it = 0, ph = p_first;
+        int it = 0;
         bool stop = false;
-        for (int u = unit_lo; u < unit_hi && !stop; ++u) {
-            const Unit un = decode_unit(P, u, ph);
+        for (int u = u_lo; u < u_hi && !stop; ++u) {
+            const TcUnit un = P.units[u];
             const TcProblem& pr = P.prob[un.p];
             for (int ks = un.ks0; ks < un.ks1; ++ks, ++it) {
                 const int s = it % kStages;
@@ -260,8 +247,9 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
                         bulk_copy_g2s(st + lane * kQuarter, pr.w_image + blk * kWBlock + lane * kQuarter, kQuarter,
                                       &ctl->full[s]);
                     }
-                } else if (lane == 4) {
-                    bulk_copy_g2s(st + kWBlock, pr.x_image + static_cast<size_t>(ks) * xbytes, xbytes, &ctl->full[s]);
+                } else if (lane == 4 && !fused) {
+                    bulk_copy_g2s(st + kWBlock, static_cast<const uint8_t*>(pr.x) + static_cast<size_t>(ks) * xbytes, xbytes,
+                                  &ctl->full[s]);
                 }
             }
         }
@@ -278,10 +266,9 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
             uint32_t full_phase = 0;
             uint32_t lo0 = base16;
             uint32_t g = 0;                        // stages issued so far; stage g uses scale set g & 1
-            int unit_iter = 0, ph = p_first;
-            for (int u = unit_lo; u < unit_hi && !*abort_flag; ++unit_iter) {
-                const Group un = decode_group(P, u, unit_hi, ph);
-                u = un.next;
+            int unit_iter = 0;
+            for (int u = u_lo; u < u_hi && !*abort_flag; ++u, ++unit_iter) {
+                const TcUnit un = P.units[u];
                 const int buf = unit_iter & 1;
                 if (unit_iter >= 2 && !mbar_wait_bounded(&ctl->acc_empty[buf], ((unit_iter >> 1) - 1) & 1)) {
                     record_error(kErrGemmEpilogueBarrierTimeout);
@@ -341,12 +328,9 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
         // this lane only needs the number of stages its CTA walks.
         if (lane == 0) {
             int total = 0;
-            {
-                int ph = p_first;
-                for (int u = unit_lo; u < unit_hi; ++u) {
-                    const Unit un = decode_unit(P, u, ph);
-                    total += un.ks1 - un.ks0;
-                }
+            for (int u = u_lo; u < u_hi; ++u) {
+                const TcUnit un = P.units[u];
+                total += un.ks1 - un.ks0;
             }
             const uint32_t base16 = smem_u32(smem) >> 4;
             const uint32_t stage16 = static_cast<uint32_t>(kStageBytes) >> 4;
@@ -382,15 +366,127 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
                 }
             }
         }
+    } else if (warp >= kActWarp0) {
+        // ------------------------------------------------------------ activation quantisers (fused form).
+        // Warp w owns the token rows t = w, w + 4, ...: it finds their pre-scales (one pass over the row,
+        // kept for the two most recent activation tensors), and for every stage writes the residual pieces
+        // of its rows' 16 blocks into the stage buffer, then arrives on the stage's `full` barrier.  The
+        // warps never talk to each other, so each can leave on its own if a wait runs out.
+        if (fused) {
+            const int aw = warp - kActWarp0;
+            const int nrows = P.M > aw ? (P.M - aw + 3) / 4 : 0;       // rows aw, aw + 4, ...
+            // pre-scale exponents of this warp's rows for the two most recent activation tensors
+            const void* cache_x0 = nullptr;
+            const void* cache_x1 = nullptr;
+            int e0[4] = {0, 0, 0, 0}, e1[4] = {0, 0, 0, 0}, ecur[4] = {0, 0, 0, 0};
+            int victim = 0;
+            pdl_wait_prior_grids();                                     // the activations come from the previous kernel
+            int it = 0;
+            bool stop = false;
+            for (int u = u_lo; u < u_hi && !stop; ++u) {
+                const TcUnit un = P.units[u];
+                const TcProblem& pr = P.prob[un.p];
+                const void* x = pr.x;
+                const int K = pr.K, ldx = pr.ldx;
+                const int nblk = K >> 4;
+                if (cache_x0 == x) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) ecur[j] = e0[j];
+                } else if (cache_x1 == x) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) ecur[j] = e1[j];
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        int e = 0;
+                        if (j < nrows) {
+                            const int t = aw + 4 * j;
+                            float amax = 0.0f;
+                            for (int kb = lane; kb < nblk; kb += 32) {
+                                float r[16];
+                                load16_as_float(x, P.x_dtype, static_cast<size_t>(t) * ldx + kb * 16, r);
+#pragma unroll
+                                for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(r[i]));
+                            }
+#pragma unroll
+                            for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+                            e = prescale_exponent(amax);
+                        }
+                        ecur[j] = e;
+                    }
+                    if (victim == 0) {
+                        cache_x0 = x;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) e0[j] = ecur[j];
+                    } else {
+                        cache_x1 = x;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) e1[j] = ecur[j];
+                    }
+                    victim ^= 1;
+                }
+                if (lane < nrows) {
+                    // the epilogue of this unit multiplies by 2^-e
+                    const int el = lane == 0 ? ecur[0] : (lane == 1 ? ecur[1] : (lane == 2 ? ecur[2] : ecur[3]));
+                    ctl->row_scale[u & (kRsRing - 1)][aw + 4 * lane] = ldexpf(1.0f, -el);
+                }
+                for (int ks = un.ks0; ks < un.ks1; ++ks, ++it) {
+                    const int s = it % kStages;
+                    int bad = 0;
+                    if (lane == 0) {
+                        if (*abort_flag) {
+                            bad = 1;
+                        } else if (it >= kStages && !mbar_wait_bounded(&ctl->empty[s], ((it / kStages) - 1) & 1)) {
+                            record_error(kErrGemmEmptyBarrierTimeout);
+                            *abort_flag = 1;
+                            bad = 1;
+                        }
+                    }
+                    bad = __shfl_sync(0xffffffffu, bad, 0);
+                    if (bad) {
+                        stop = true;
+                        break;
+                    }
+                    uint8_t* blk = smem + s * kStageBytes + kWBlock;
+                    for (int item = lane; item < nrows * 16; item += 32) {
+                        const int j = item >> 4;
+                        const int kbl = item & 15;                 // block inside the stage
+                        const int kb = ks * 16 + kbl;
+                        const int t = aw + 4 * j;
+                        const bool valid = kb < nblk;
+                        float r[16];
+                        if (valid) {
+                            load16_as_float(x, P.x_dtype, static_cast<size_t>(t) * ldx + kb * 16, r);
+                            const float pre = ldexpf(1.0f, j == 0 ? ecur[0] : (j == 1 ? ecur[1] : (j == 2 ? ecur[2] : ecur[3])));
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) r[i] *= pre;
+                        }
+                        const int c = kbl >> 1;                    // 16-byte chunk of the 128-byte row
+                        for (int p = 0; p < P.pieces; ++p) {
+                            const int prow = p * 16 + t;
+                            uint8_t* dst = blk + prow * 128 + ((c ^ (prow & 7)) << 4) + (kbl & 1) * 8;
+                            uint8_t* sf_dst = blk + NB * 128 + (kbl >> 2) * 512 + (prow & 31) * 16 + ((prow >> 5) & 3) * 4 + (kbl & 3);
+                            uint32_t lo = 0, hi = 0;
+                            uint8_t code = 0;
+                            if (valid) code = quantize_block16_piece(r, lo, hi);
+                            *sf_dst = code;
+                            *reinterpret_cast<uint2*>(dst) = make_uint2(lo, hi);
+                        }
+                    }
+                    fence_proxy_async_smem();                      // the tensor core reads these bytes
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&ctl->full[s]);
+                }
+            }
+        }
     } else if (warp >= 2) {
         // ------------------------------------------------------------ epilogue (warps 2..5, 128 threads)
         const int q = warp & 3;
         const int et = q * 32 + lane;            // 0..127: the weight row inside the tile
-        int unit_iter = 0, ph = p_first;
+        int unit_iter = 0;
         pdl_wait_prior_grids();                   // the output buffer may still be read by the previous kernel
-        for (int u = unit_lo; u < unit_hi && !*abort_flag; ++unit_iter) {
-            const Group un = decode_group(P, u, unit_hi, ph);
-            u = un.next;
+        for (int u = u_lo; u < u_hi && !*abort_flag; ++u, ++unit_iter) {
+            const TcUnit un = P.units[u];
             const TcProblem& pr = P.prob[un.p];
             const int buf = unit_iter & 1;
             if (!mbar_wait_bounded(&ctl->acc_full[buf], (unit_iter >> 1) & 1)) {
@@ -417,55 +513,45 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
             __syncwarp();
             if (lane == 0) mbar_arrive(&ctl->acc_empty[buf]);
 
-            const int n_pad = pr.row_tiles * 256;
             bool finalize = true;
-            if (un.split0 != 0 || un.split1 != pr.splits - 1) {
-                // this group covers only part of the tile's K range: hand its sums over.  The tile's groups
-                // start at its first unit and wherever a CTA's range begins inside it.
-                const int t0 = pr.unit_begin + un.rt * pr.splits;
-                const long long total = P.total_units;
-                const int grid = gridDim.x;
-                const int b_first = static_cast<int>((static_cast<long long>(t0) * grid) / total) + 1;
-                int ngroups = 1;
-                for (int b = b_first; b < grid && static_cast<int>(b * total / grid) < t0 + pr.splits; ++b) {
-                    if (static_cast<int>(b * total / grid) > t0) ++ngroups;
-                }
-                float* part = P.scratch + pr.scratch_off;
+            if (un.shared) {
+                // this unit covers only part of the tile's K range: hand its sums over
+                float* part = P.scratch + static_cast<size_t>(un.slot0) * kSlotFloats;
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
-                    const int n = un.rt * 256 + h * 128 + et;
 #pragma unroll
                     for (int t = 0; t < 16; ++t) {
-                        if (t < P.M) part[(static_cast<size_t>(un.split0) * 16 + t) * n_pad + n] = v[h][t];
+                        if (t < P.M) part[(static_cast<size_t>(un.slot) * 16 + t) * 256 + h * 128 + et] = v[h][t];
                     }
                 }
                 __threadfence();
                 asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (et == 0) ctl->ticket = atomicAdd(P.counters + pr.counter_off + un.rt, 1);
+                if (et == 0) ctl->ticket = atomicAdd(P.counters + un.counter, 1);
                 asm volatile("bar.sync 1, 128;" ::: "memory");
-                finalize = (ctl->ticket == ngroups - 1);
+                finalize = (ctl->ticket == un.nslots - 1);
                 if (finalize) {
                     __threadfence();
 #pragma unroll
                     for (int h = 0; h < 2; ++h) {
-                        const int n = un.rt * 256 + h * 128 + et;
 #pragma unroll
                         for (int t = 0; t < 16; ++t) {
                             if (t < P.M) {
-                                float acc = __ldcg(part + static_cast<size_t>(t) * n_pad + n);       // group at split 0
-                                for (int b = b_first; b < grid && static_cast<int>(b * total / grid) < t0 + pr.splits; ++b) {
-                                    const int sp = static_cast<int>(b * total / grid) - t0;
-                                    if (sp > 0) acc += __ldcg(part + (static_cast<size_t>(sp) * 16 + t) * n_pad + n);
+                                float acc = 0.0f;
+                                for (int sl = 0; sl < un.nslots; ++sl) {
+                                    acc += __ldcg(part + (static_cast<size_t>(sl) * 16 + t) * 256 + h * 128 + et);
                                 }
                                 v[h][t] = acc;
                             }
                         }
                     }
-                    if (et == 0) P.counters[pr.counter_off + un.rt] = 0;   // ready for the next launch
+                    if (et == 0) P.counters[un.counter] = 0;               // ready for the next launch
                 }
                 asm volatile("bar.sync 1, 128;" ::: "memory");              // ticket slot free for the next unit
             }
             if (finalize) {
+                // the row multipliers were written by the quantiser warps before they released the unit's
+                // first stage, which the MMAs behind this accumulator have consumed
+                const float* rs = fused ? ctl->row_scale[u & (kRsRing - 1)] : pr.row_scale;
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     const int n = un.rt * 256 + h * 128 + et;
@@ -473,7 +559,8 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
 #pragma unroll
                     for (int t = 0; t < 16; ++t) {
                         if (t < P.M) {
-                            float f = v[h][t] * pr.global_scale * __ldg(pr.row_scale + t);
+                            const float m = fused ? *(volatile const float*)(rs + t) : __ldg(rs + t);
+                            float f = v[h][t] * pr.global_scale * m;
                             if (pr.bias != nullptr) f += load_as_float(pr.bias, P.bias_dtype, n);
                             f = apply_activation(f, P.activation);
                             store_from_float(pr.out, P.out_dtype, static_cast<size_t>(t) * pr.ldo + n, f);
@@ -496,10 +583,6 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
 // Activation pieces in the tiled image: one CTA per token row t < 16 (rows >= M are zeroed).
 // Same arithmetic as nvfp4_quantize_pieces_kernel in nvfp4_gemm.cu.
 // ------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t e2m1_index(float a) {
-    return (a > 0.25f) + (a > 0.75f) + (a > 1.25f) + (a > 1.75f) + (a > 2.5f) + (a > 3.5f) + (a > 5.0f);
-}
-
 struct QuantActs {
     int count;
     const void* x[TPB200_MAX_ACTS];
@@ -539,12 +622,7 @@ __global__ void __launch_bounds__(256) quantize_pieces_tiled_kernel(const __grid
     amax = red[0];
 #pragma unroll
     for (int i = 1; i < 8; ++i) amax = fmaxf(amax, red[i]);
-    int e = 0;
-    if (amax > 0.0f && amax < 3.0e38f) {
-        int ex;
-        frexpf(amax, &ex);
-        e = 11 - ex;
-    }
+    const int e = prescale_exponent(amax);
     const float pre = ldexpf(1.0f, e);
     if (threadIdx.x == 0 && t < M) row_scale[t] = ldexpf(1.0f, -e);
 
@@ -582,46 +660,199 @@ int device_error_gemv_tc(int clear) { return read_device_error(clear); }
 }  // namespace tpb
 
 // ---------------------------------------------------------------------------------------------
-// Host side
+// Host side: the planner.  No heap: every table is a fixed-size member of a thread-local object, so
+// the entry points allocate nothing, on the device or on the host.
 // ---------------------------------------------------------------------------------------------
 namespace {
 
-struct TcPlan {
-    int splits[TPB200_MAX_GROUP];
-    int stages_per_split[TPB200_MAX_GROUP];
-    size_t scratch_floats;
-    size_t counters;
-    int total_units;
+constexpr int kSmallUnits = 192;
+constexpr int kLargeUnits = 1024;
+constexpr int kMaxPieces = kLargeUnits;      // a candidate cut with more pieces than a launch can list is skipped
+
+struct Shape {
+    int N, K;
 };
 
-// shared by the workspace query and the launch so that both see the same layout
-int make_plan(const tpb200_gemv_tc_problem* probs, int count, int sms, TcPlan& plan) {
-    long long total_stages = 0;
-    for (int i = 0; i < count; ++i) {
-        if (probs[i].N < 1 || probs[i].K < 16 || probs[i].K % 16 != 0) return TPB200_ERR_SHAPE;
-        const long long row_tiles = (probs[i].N + 255) / 256;
-        total_stages += row_tiles * ((probs[i].K + 255) / 256);
-    }
-    // aim for ~4 units per SM, units of 1..8 stages, and never longer than the shortest problem's K so
-    // that the units of a mixed launch carry (nearly) the same number of stages: CTAs own equal COUNTS
-    int target = static_cast<int>(std::min<long long>(8, std::max<long long>(1, total_stages / (4LL * sms))));
-    for (int i = 0; i < count; ++i) target = std::min(target, (probs[i].K + 255) / 256);
-    plan.scratch_floats = 0;
-    plan.counters = 0;
-    plan.total_units = 0;
-    for (int i = 0; i < count; ++i) {
-        const int row_tiles = (probs[i].N + 255) / 256;
-        const int k_stages = (probs[i].K + 255) / 256;
-        int splits = (k_stages + target - 1) / target;
-        const int sps = (k_stages + splits - 1) / splits;
-        splits = (k_stages + sps - 1) / sps;
-        plan.splits[i] = splits;
-        plan.stages_per_split[i] = sps;
-        if (splits > 1) {
-            plan.scratch_floats += static_cast<size_t>(splits) * 16 * row_tiles * 256;
-            plan.counters += row_tiles;
+struct Piece {
+    uint16_t p, rt, ks0, ks1;
+    int16_t cta;
+};
+
+struct Plan {
+    tpb::TcUnit units[kLargeUnits];          // CTA by CTA
+    uint16_t cta_begin[tpb::kMaxCtas + 1];
+    int num_units = 0;
+    int grid = 0;
+    size_t slots = 0;                        // partial-sum slots (16 * 256 floats each)
+    size_t counters = 0;
+    int max_load = 0;                        // stages of the longest CTA
+};
+
+struct PlanScratch {
+    Piece pieces[kMaxPieces];
+    Piece best[kMaxPieces];
+    int num = 0, num_best = 0, grid_best = 0;
+    int load[tpb::kMaxCtas];
+    int heap[tpb::kMaxCtas];                 // CTA ids ordered by load (binary min-heap)
+    int order[kLargeUnits];
+};
+
+// Deal the pieces of one candidate cut (no piece longer than `lmax` stages) to the CTAs, longest first,
+// each to the least loaded CTA; returns the largest load in stages, or -1 if the cut has too many pieces.
+int deal(const Shape* shapes, int count, int sms, int lmax, PlanScratch& S, bool& any_cut) {
+    S.num = 0;
+    any_cut = false;
+    for (int p = 0; p < count; ++p) {
+        const int row_tiles = (shapes[p].N + 255) / 256;
+        const int k_stages = (shapes[p].K + 255) / 256;
+        const int cuts = (k_stages + lmax - 1) / lmax;
+        const int len = (k_stages + cuts - 1) / cuts;
+        if (cuts > 1) any_cut = true;
+        for (int rt = 0; rt < row_tiles; ++rt) {
+            for (int k0 = 0; k0 < k_stages; k0 += len) {
+                if (S.num == kMaxPieces) return -1;
+                S.pieces[S.num++] = {static_cast<uint16_t>(p), static_cast<uint16_t>(rt), static_cast<uint16_t>(k0),
+                                     static_cast<uint16_t>(std::min(k_stages, k0 + len)), 0};
+            }
         }
-        plan.total_units += row_tiles * splits;
+    }
+    // longest first; ties in launch order (a total order, so std::sort is deterministic)
+    std::sort(S.pieces, S.pieces + S.num, [](const Piece& a, const Piece& b) {
+        const int la = a.ks1 - a.ks0, lb = b.ks1 - b.ks0;
+        if (la != lb) return la > lb;
+        if (a.p != b.p) return a.p < b.p;
+        if (a.rt != b.rt) return a.rt < b.rt;
+        return a.ks0 < b.ks0;
+    });
+    const int grid = std::min(sms, S.num);
+    for (int c = 0; c < grid; ++c) {
+        S.load[c] = 0;
+        S.heap[c] = c;
+    }
+    auto heavier = [&S](int a, int b) { return S.load[a] != S.load[b] ? S.load[a] > S.load[b] : a > b; };
+    for (int i = 0; i < S.num; ++i) {
+        std::pop_heap(S.heap, S.heap + grid, heavier);           // least loaded CTA moves to the back
+        const int c = S.heap[grid - 1];
+        S.pieces[i].cta = static_cast<int16_t>(c);
+        S.load[c] += S.pieces[i].ks1 - S.pieces[i].ks0;
+        std::push_heap(S.heap, S.heap + grid, heavier);
+    }
+    return *std::max_element(S.load, S.load + grid);
+}
+
+// Candidate cuts: tiles whole, or no piece longer than 16 / 8 / 4 / 2 / 1 stages.  A cut costs a hand-over of
+// partial sums through global memory at the end of the launch (about five stage times, plus the last
+// arriver's walk over the tile's pieces), so it is taken only when it shortens the longest CTA by more.
+int make_plan(const Shape* shapes, int count, int sms, Plan& plan, PlanScratch& S) {
+    if (sms < 1 || sms > tpb::kMaxCtas) return TPB200_ERR_CUDA;
+    int longest = 1;
+    for (int i = 0; i < count; ++i) {
+        const Shape& s = shapes[i];
+        if (s.N < 1 || s.K < 16 || s.K % 16 != 0) return TPB200_ERR_SHAPE;
+        if ((s.N + 255) / 256 > 65535 || (s.K + 255) / 256 > 65535) return TPB200_ERR_SHAPE;
+        longest = std::max(longest, (s.K + 255) / 256);
+    }
+    constexpr int kHandOverStages = 5;
+    constexpr int kWhole = 1 << 30;
+    int best_cost = 0;
+    bool have = false;
+    for (int lmax : {kWhole, 16, 8, 4, 2, 1}) {
+        if (lmax != kWhole && lmax >= longest) continue;           // same as the whole-tile plan
+        bool any_cut = false;
+        const int load = deal(shapes, count, sms, lmax, S, any_cut);
+        if (load < 0) continue;
+        int cost = load;
+        if (any_cut) {
+            int max_cuts = 1;
+            for (int i = 0; i < count; ++i) {
+                const int ks = (shapes[i].K + 255) / 256;
+                max_cuts = std::max(max_cuts, (ks + lmax - 1) / lmax);
+            }
+            cost += kHandOverStages + max_cuts / 8;
+        }
+        if (!have || cost < best_cost) {
+            std::copy(S.pieces, S.pieces + S.num, S.best);
+            S.num_best = S.num;
+            S.grid_best = std::min(sms, S.num);
+            best_cost = cost;
+            have = true;
+        }
+    }
+    if (!have) return TPB200_ERR_SHAPE;                            // more tiles than one launch can list
+
+    // CTA by CTA: whole tiles first, cut tiles last (their hand-over then holds up nothing that follows);
+    // neighbouring pieces of one tile that landed on the same CTA become one unit.
+    auto k_stages = [&](int p) { return (shapes[p].K + 255) / 256; };
+    std::sort(S.best, S.best + S.num_best, [&](const Piece& a, const Piece& b) {
+        if (a.cta != b.cta) return a.cta < b.cta;
+        const bool ca = (a.ks1 - a.ks0) != k_stages(a.p), cb = (b.ks1 - b.ks0) != k_stages(b.p);
+        if (ca != cb) return !ca;
+        if (a.p != b.p) return a.p < b.p;
+        if (a.rt != b.rt) return a.rt < b.rt;
+        return a.ks0 < b.ks0;
+    });
+    plan.num_units = 0;
+    plan.grid = S.grid_best;
+    plan.max_load = 0;
+    int i = 0;
+    for (int c = 0; c < plan.grid; ++c) {
+        plan.cta_begin[c] = static_cast<uint16_t>(plan.num_units);
+        const int first = plan.num_units;
+        int load = 0;
+        for (; i < S.num_best && S.best[i].cta == c; ++i) {
+            const Piece& pc = S.best[i];
+            load += pc.ks1 - pc.ks0;
+            if (plan.num_units > first) {
+                tpb::TcUnit& last = plan.units[plan.num_units - 1];
+                if (last.p == pc.p && last.rt == pc.rt && last.ks1 == pc.ks0) {
+                    last.ks1 = pc.ks1;
+                    continue;
+                }
+            }
+            if (plan.num_units == kLargeUnits) return TPB200_ERR_SHAPE;
+            tpb::TcUnit u = {};
+            u.p = static_cast<uint8_t>(pc.p);
+            u.rt = pc.rt;
+            u.ks0 = pc.ks0;
+            u.ks1 = pc.ks1;
+            plan.units[plan.num_units++] = u;
+        }
+        plan.max_load = std::max(plan.max_load, load);
+    }
+    plan.cta_begin[plan.grid] = static_cast<uint16_t>(plan.num_units);
+    // cut tiles: slots in K order, one counter per tile
+    int ncut = 0;
+    for (int k = 0; k < plan.num_units; ++k) {
+        const tpb::TcUnit& u = plan.units[k];
+        if (u.ks1 - u.ks0 != k_stages(u.p)) S.order[ncut++] = k;
+    }
+    std::sort(S.order, S.order + ncut, [&](int a, int b) {
+        const tpb::TcUnit &x = plan.units[a], &y = plan.units[b];
+        if (x.p != y.p) return x.p < y.p;
+        if (x.rt != y.rt) return x.rt < y.rt;
+        return x.ks0 < y.ks0;
+    });
+    plan.slots = 0;
+    plan.counters = 0;
+    for (int a = 0; a < ncut;) {
+        int b = a;
+        while (b < ncut && plan.units[S.order[b]].p == plan.units[S.order[a]].p &&
+               plan.units[S.order[b]].rt == plan.units[S.order[a]].rt) {
+            ++b;
+        }
+        const int n = b - a;
+        if (n > 255 || plan.slots + n > 65535 || plan.counters > 65535) return TPB200_ERR_SHAPE;
+        for (int k = a; k < b; ++k) {
+            tpb::TcUnit& u = plan.units[S.order[k]];
+            u.shared = 1;
+            u.slot0 = static_cast<uint16_t>(plan.slots);
+            u.counter = static_cast<uint16_t>(plan.counters);
+            u.slot = static_cast<uint8_t>(k - a);
+            u.nslots = static_cast<uint8_t>(n);
+        }
+        plan.slots += n;
+        plan.counters += 1;
+        a = b;
     }
     return TPB200_OK;
 }
@@ -635,16 +866,254 @@ int device_sms(int& sms) {
     return TPB200_OK;
 }
 
+size_t counter_bytes(const Plan& plan) { return (plan.counters * sizeof(int) + 255) / 256 * 256; }
+size_t workspace_bytes(const Plan& plan) {
+    return counter_bytes(plan) + plan.slots * tpb::kSlotFloats * sizeof(float);
+}
+
+// Plans are remembered per calling thread for the last few distinct shape lists: a decode loop launches
+// the same handful of groups over and over.
+struct PlanCache {
+    static constexpr int kEntries = 8;
+    struct Entry {
+        int count = 0, sms = 0;
+        Shape shapes[TPB200_MAX_GROUP];
+        Plan plan;
+    };
+    Entry entries[kEntries];
+    int next = 0;
+    PlanScratch scratch;
+
+    int get(const Shape* shapes, int count, const Plan** out) {
+        int sms = 0;
+        if (device_sms(sms) != TPB200_OK) return TPB200_ERR_CUDA;
+        for (Entry& e : entries) {
+            if (e.count == count && e.sms == sms &&
+                std::equal(shapes, shapes + count, e.shapes, [](const Shape& a, const Shape& b) { return a.N == b.N && a.K == b.K; })) {
+                *out = &e.plan;
+                return TPB200_OK;
+            }
+        }
+        Entry& e = entries[next];
+        e.count = 0;                                 // invalid while it is rebuilt
+        const int st = make_plan(shapes, count, sms, e.plan, scratch);
+        if (st != TPB200_OK) return st;
+        std::copy(shapes, shapes + count, e.shapes);
+        e.count = count;
+        e.sms = sms;
+        next = (next + 1) % kEntries;
+        *out = &e.plan;
+        return TPB200_OK;
+    }
+};
+
+PlanCache& plan_cache() {
+    static thread_local PlanCache cache;
+    return cache;
+}
+
+// Everything a launch needs, validated and planned on the host BEFORE anything is enqueued.
+struct Launch {
+    Shape shapes[TPB200_MAX_GROUP];
+    tpb::TcProblem prob[TPB200_MAX_GROUP];
+    int count = 0;
+    const Plan* plan = nullptr;
+    int M = 0, pieces = 0, x_dtype = TPB200_BF16, bias_dtype = TPB200_F32, out_dtype = TPB200_BF16, activation = 0;
+    int fused = 0, flags = 0;
+};
+
+int check_common(int count, int M, int pieces, int bias_dtype, int out_dtype, int activation, int flags) {
+    TPB_REQUIRE(count >= 1 && count <= TPB200_MAX_GROUP, TPB200_ERR_SHAPE);
+    TPB_REQUIRE(M >= 1 && M <= 16 && pieces >= 1 && pieces <= 4, TPB200_ERR_SHAPE);
+    TPB_REQUIRE(tpb_valid_dtype(bias_dtype) && tpb_valid_dtype(out_dtype), TPB200_ERR_ENUM);
+    TPB_REQUIRE(activation >= TPB200_ACT_NONE && activation <= TPB200_ACT_SILU, TPB200_ERR_ENUM);
+    TPB_REQUIRE((flags & ~TPB200_FLAG_PDL) == 0, TPB200_ERR_ENUM);
+    return TPB200_OK;
+}
+
+template <int kMaxUnits>
+int launch_with(const Launch& L, void* workspace, tpb200_stream_t stream) {
+    static thread_local tpb::TcParams<kMaxUnits> P;      // ~8 / ~21 KB: kept off the caller's stack
+    const Plan& plan = *L.plan;
+    P.num_problems = L.count;
+    P.M = L.M;
+    P.pieces = L.pieces;
+    P.x_dtype = L.x_dtype;
+    P.bias_dtype = L.bias_dtype;
+    P.out_dtype = L.out_dtype;
+    P.activation = L.activation;
+    P.fused = L.fused;
+    P.counters = static_cast<int*>(workspace);
+    P.scratch = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + counter_bytes(plan));
+    std::copy(L.prob, L.prob + L.count, P.prob);
+    std::copy(plan.cta_begin, plan.cta_begin + plan.grid + 1, P.cta_begin);
+    std::copy(plan.units, plan.units + plan.num_units, P.units);
+
+    const size_t smem = tpb::num_stages(L.pieces) * tpb::stage_bytes(L.pieces) + sizeof(tpb::SharedControl) + 1024;
+    static std::atomic<uint64_t> configured{0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const uint64_t bit = 1ull << (dev & 63);
+    if (!(configured.load(std::memory_order_relaxed) & bit)) {
+        if (cudaFuncSetAttribute(tpb::nvfp4_gemv_tc_kernel<kMaxUnits>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 227 * 1024) != cudaSuccess) {
+            return TPB200_ERR_CUDA;
+        }
+        configured.fetch_or(bit, std::memory_order_relaxed);
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(plan.grid, 1, 1);
+    cfg.blockDim = dim3(tpb::kThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = reinterpret_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    if (L.flags & TPB200_FLAG_PDL) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    if (cudaLaunchKernelEx(&cfg, tpb::nvfp4_gemv_tc_kernel<kMaxUnits>, P) != cudaSuccess) return TPB200_ERR_CUDA;
+    return TPB200_OK;
+}
+
+int launch(const Launch& L, void* workspace, size_t workspace_size, tpb200_stream_t stream) {
+    if (L.plan->slots > 0) {
+        TPB_REQUIRE(workspace != nullptr, TPB200_ERR_WORKSPACE);
+        TPB_REQUIRE(workspace_size >= workspace_bytes(*L.plan), TPB200_ERR_WORKSPACE);
+        TPB_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255u) == 0, TPB200_ERR_ALIGN);
+    }
+    if (L.plan->num_units <= kSmallUnits) return launch_with<kSmallUnits>(L, workspace, stream);
+    return launch_with<kLargeUnits>(L, workspace, stream);
+}
+
+Launch& launch_record() {
+    static thread_local Launch L;
+    return L;
+}
+
+int prepare_pretiled(const tpb200_gemv_tc_problem* problems, int count, int M, int pieces, int bias_dtype, int out_dtype,
+                     int activation, int flags, Launch& L) {
+    TPB_REQUIRE(problems != nullptr, TPB200_ERR_NULL);
+    const int st = check_common(count, M, pieces, bias_dtype, out_dtype, activation, flags);
+    if (st != TPB200_OK) return st;
+    L.count = count;
+    L.M = M;
+    L.pieces = pieces;
+    L.x_dtype = TPB200_BF16;
+    L.bias_dtype = bias_dtype;
+    L.out_dtype = out_dtype;
+    L.activation = activation;
+    L.flags = flags;
+    L.fused = 0;
+    for (int i = 0; i < count; ++i) {
+        const tpb200_gemv_tc_problem& h = problems[i];
+        TPB_REQUIRE(h.w_image && h.x_image && h.x_row_scale && h.out, TPB200_ERR_NULL);
+        TPB_REQUIRE(tpb_aligned16(h.w_image) && tpb_aligned16(h.x_image), TPB200_ERR_ALIGN);
+        TPB_REQUIRE(h.ldo == 0 || h.ldo >= h.N, TPB200_ERR_SHAPE);
+        tpb::TcProblem d = {};
+        d.w_image = static_cast<const uint8_t*>(h.w_image);
+        d.x = h.x_image;
+        d.row_scale = h.x_row_scale;
+        d.bias = h.bias;
+        d.out = h.out;
+        d.N = h.N;
+        d.K = h.K;
+        d.ldo = h.ldo == 0 ? h.N : h.ldo;
+        d.ldx = 0;
+        d.global_scale = h.global_scale;
+        d.k_stages = (h.K + 255) / 256;
+        L.prob[i] = d;
+        L.shapes[i] = {h.N, h.K};
+    }
+    return plan_cache().get(L.shapes, count, &L.plan);
+}
+
+int prepare_fused(const tpb200_gemv_tc_fused_problem* problems, int count, int M, int pieces, int x_dtype, int bias_dtype,
+                  int out_dtype, int activation, int flags, Launch& L) {
+    TPB_REQUIRE(problems != nullptr, TPB200_ERR_NULL);
+    const int st = check_common(count, M, pieces, bias_dtype, out_dtype, activation, flags);
+    if (st != TPB200_OK) return st;
+    TPB_REQUIRE(tpb_valid_dtype(x_dtype), TPB200_ERR_ENUM);
+    L.count = count;
+    L.M = M;
+    L.pieces = pieces;
+    L.x_dtype = x_dtype;
+    L.bias_dtype = bias_dtype;
+    L.out_dtype = out_dtype;
+    L.activation = activation;
+    L.flags = flags;
+    L.fused = 1;
+    for (int i = 0; i < count; ++i) {
+        const tpb200_gemv_tc_fused_problem& h = problems[i];
+        TPB_REQUIRE(h.w_image && h.x && h.out, TPB200_ERR_NULL);
+        TPB_REQUIRE(tpb_aligned16(h.w_image) && tpb_aligned16(h.x), TPB200_ERR_ALIGN);
+        TPB_REQUIRE(h.ldo == 0 || h.ldo >= h.N, TPB200_ERR_SHAPE);
+        const int ldx = h.ldx == 0 ? h.K : h.ldx;
+        TPB_REQUIRE(ldx >= h.K, TPB200_ERR_SHAPE);
+        TPB_REQUIRE((static_cast<long long>(ldx) * tpb_dtype_size(x_dtype)) % 16 == 0, TPB200_ERR_ALIGN);
+        tpb::TcProblem d = {};
+        d.w_image = static_cast<const uint8_t*>(h.w_image);
+        d.x = h.x;
+        d.row_scale = nullptr;
+        d.bias = h.bias;
+        d.out = h.out;
+        d.N = h.N;
+        d.K = h.K;
+        d.ldo = h.ldo == 0 ? h.N : h.ldo;
+        d.ldx = ldx;
+        d.global_scale = h.global_scale;
+        d.k_stages = (h.K + 255) / 256;
+        L.prob[i] = d;
+        L.shapes[i] = {h.N, h.K};
+    }
+    return plan_cache().get(L.shapes, count, &L.plan);
+}
+
+size_t planned_workspace(const Shape* shapes, int count) {
+    const Plan* plan = nullptr;
+    if (plan_cache().get(shapes, count, &plan) != TPB200_OK) return 0;
+    // counters first (zero-initialised by the caller once), then the partial sums
+    return workspace_bytes(*plan) + 256;
+}
+
 }  // namespace
 
 extern "C" size_t tpb200_nvfp4_gemv_tc_workspace_size(const tpb200_gemv_tc_problem* problems, int count) {
     if (problems == nullptr || count < 1 || count > TPB200_MAX_GROUP) return 0;
-    int sms = 0;
-    if (device_sms(sms) != TPB200_OK) return 0;
-    TcPlan plan;
-    if (make_plan(problems, count, sms, plan) != TPB200_OK) return 0;
-    // counters first (zero-initialised by the caller once), then the partial sums
-    return (plan.counters * sizeof(int) + 255) / 256 * 256 + plan.scratch_floats * sizeof(float) + 256;
+    Shape shapes[TPB200_MAX_GROUP];
+    for (int i = 0; i < count; ++i) shapes[i] = {problems[i].N, problems[i].K};
+    return planned_workspace(shapes, count);
+}
+
+extern "C" size_t tpb200_nvfp4_gemv_tc_fused_workspace_size(const tpb200_gemv_tc_fused_problem* problems, int count) {
+    if (problems == nullptr || count < 1 || count > TPB200_MAX_GROUP) return 0;
+    Shape shapes[TPB200_MAX_GROUP];
+    for (int i = 0; i < count; ++i) shapes[i] = {problems[i].N, problems[i].K};
+    return planned_workspace(shapes, count);
+}
+
+extern "C" int tpb200_nvfp4_gemv_tc_plan(const int* N, const int* K, int count, int sms, tpb200_gemv_tc_plan_info* info) {
+    TPB_REQUIRE(N && K && info, TPB200_ERR_NULL);
+    TPB_REQUIRE(count >= 1 && count <= TPB200_MAX_GROUP, TPB200_ERR_SHAPE);
+    TPB_REQUIRE(sms >= 1 && sms <= tpb::kMaxCtas, TPB200_ERR_SHAPE);
+    static thread_local Plan plan;
+    static thread_local PlanScratch scratch;
+    Shape shapes[TPB200_MAX_GROUP];
+    long long total = 0;
+    for (int i = 0; i < count; ++i) {
+        shapes[i] = {N[i], K[i]};
+        total += static_cast<long long>((N[i] + 255) / 256) * ((K[i] + 255) / 256);
+    }
+    const int st = make_plan(shapes, count, sms, plan, scratch);
+    if (st != TPB200_OK) return st;
+    info->grid = plan.grid;
+    info->units = plan.num_units;
+    info->max_load_stages = plan.max_load;
+    info->total_stages = static_cast<int>(total);
+    info->cut_tiles = static_cast<int>(plan.counters);
+    info->workspace_bytes = workspace_bytes(plan);
+    return TPB200_OK;
 }
 
 extern "C" size_t tpb200_nvfp4_gemv_tc_x_image_bytes(int K, int pieces) {
@@ -698,103 +1167,31 @@ extern "C" int tpb200_nvfp4_quantize_act_tc(const void* x, int x_dtype, int ldx,
 
 extern "C" int tpb200_nvfp4_gemv_tc(const tpb200_gemv_tc_problem* problems, int count, int M, int pieces,
                                     int bias_dtype, int out_dtype, int activation, void* workspace,
-                                    size_t workspace_bytes, int flags, tpb200_stream_t stream) {
-    TPB_REQUIRE(problems != nullptr, TPB200_ERR_NULL);
-    TPB_REQUIRE(count >= 1 && count <= TPB200_MAX_GROUP, TPB200_ERR_SHAPE);
-    TPB_REQUIRE(M >= 1 && M <= 16 && pieces >= 1 && pieces <= 4, TPB200_ERR_SHAPE);
-    TPB_REQUIRE(tpb_valid_dtype(bias_dtype) && tpb_valid_dtype(out_dtype), TPB200_ERR_ENUM);
-    TPB_REQUIRE(activation >= TPB200_ACT_NONE && activation <= TPB200_ACT_SILU, TPB200_ERR_ENUM);
-    TPB_REQUIRE((flags & ~TPB200_FLAG_PDL) == 0, TPB200_ERR_ENUM);
-    int sms = 0;
-    if (device_sms(sms) != TPB200_OK) return TPB200_ERR_CUDA;
-    TcPlan plan;
-    const int st = make_plan(problems, count, sms, plan);
+                                    size_t workspace_size, int flags, tpb200_stream_t stream) {
+    Launch& L = launch_record();
+    const int st = prepare_pretiled(problems, count, M, pieces, bias_dtype, out_dtype, activation, flags, L);
     if (st != TPB200_OK) return st;
-    const size_t counter_bytes = (plan.counters * sizeof(int) + 255) / 256 * 256;
-    if (plan.scratch_floats > 0) {
-        TPB_REQUIRE(workspace != nullptr, TPB200_ERR_WORKSPACE);
-        TPB_REQUIRE(workspace_bytes >= counter_bytes + plan.scratch_floats * sizeof(float), TPB200_ERR_WORKSPACE);
-        TPB_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255u) == 0, TPB200_ERR_ALIGN);
-    }
+    return launch(L, workspace, workspace_size, stream);
+}
 
-    tpb::TcParams P;
-    P.num_problems = count;
-    P.total_units = plan.total_units;
-    P.M = M;
-    P.pieces = pieces;
-    P.bias_dtype = bias_dtype;
-    P.out_dtype = out_dtype;
-    P.activation = activation;
-    P.counters = static_cast<int*>(workspace);
-    P.scratch = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + counter_bytes);
-    int units = 0, coff = 0;
-    size_t soff = 0;
-    for (int i = 0; i < count; ++i) {
-        const tpb200_gemv_tc_problem& h = problems[i];
-        TPB_REQUIRE(h.w_image && h.x_image && h.x_row_scale && h.out, TPB200_ERR_NULL);
-        TPB_REQUIRE(tpb_aligned16(h.w_image) && tpb_aligned16(h.x_image), TPB200_ERR_ALIGN);
-        TPB_REQUIRE(h.ldo == 0 || h.ldo >= h.N, TPB200_ERR_SHAPE);
-        tpb::TcProblem& d = P.prob[i];
-        d.w_image = static_cast<const uint8_t*>(h.w_image);
-        d.x_image = static_cast<const uint8_t*>(h.x_image);
-        d.row_scale = h.x_row_scale;
-        d.bias = h.bias;
-        d.out = h.out;
-        d.N = h.N;
-        d.K = h.K;
-        d.ldo = h.ldo == 0 ? h.N : h.ldo;
-        d.global_scale = h.global_scale;
-        d.k_stages = (h.K + 255) / 256;
-        d.row_tiles = (h.N + 255) / 256;
-        d.splits = plan.splits[i];
-        d.stages_per_split = plan.stages_per_split[i];
-        d.unit_begin = units;
-        d.scratch_off = static_cast<int>(soff);
-        d.counter_off = coff;
-        units += d.row_tiles * d.splits;
-        if (d.splits > 1) {
-            soff += static_cast<size_t>(d.splits) * 16 * d.row_tiles * 256;
-            coff += d.row_tiles;
-        }
-    }
-
-    const size_t smem = tpb::num_stages(pieces) * tpb::stage_bytes(pieces) + sizeof(tpb::SharedControl) + 1024;
-    static std::atomic<uint64_t> configured{0};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    const uint64_t bit = 1ull << (dev & 63);
-    if (!(configured.load(std::memory_order_relaxed) & bit)) {
-        if (cudaFuncSetAttribute(tpb::nvfp4_gemv_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 227 * 1024) != cudaSuccess) {
-            return TPB200_ERR_CUDA;
-        }
-        configured.fetch_or(bit, std::memory_order_relaxed);
-    }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(std::min(plan.total_units, sms), 1, 1);
-    cfg.blockDim = dim3(tpb::kThreads, 1, 1);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = reinterpret_cast<cudaStream_t>(stream);
-    cudaLaunchAttribute attr[1];
-    if (flags & TPB200_FLAG_PDL) {
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-    }
-    if (cudaLaunchKernelEx(&cfg, tpb::nvfp4_gemv_tc_kernel, P) != cudaSuccess) return TPB200_ERR_CUDA;
-    return TPB200_OK;
+extern "C" int tpb200_nvfp4_gemv_tc_fused(const tpb200_gemv_tc_fused_problem* problems, int count, int M, int pieces,
+                                          int x_dtype, int bias_dtype, int out_dtype, int activation, void* workspace,
+                                          size_t workspace_size, int flags, tpb200_stream_t stream) {
+    Launch& L = launch_record();
+    const int st = prepare_fused(problems, count, M, pieces, x_dtype, bias_dtype, out_dtype, activation, flags, L);
+    if (st != TPB200_OK) return st;
+    return launch(L, workspace, workspace_size, stream);
 }
 
 // ---------------------------------------------------------------------------------------------
 // The same GEMV for callers that are not able to allocate device memory.
 //
-// tpb200_nvfp4_gemv_tc needs a workspace for its split-K partial sums and tile counters.  Some
-// callers have nowhere to get one from: a TensorRT plugin whose enqueue() was not granted a
-// workspace, a robot-control loop that must not touch the allocator once it is running, host code
-// that is handed raw pointers and no allocator of the framework that owns them.  For them the
+// tpb200_nvfp4_gemv_tc needs a workspace for the partial sums and arrival counters of tiles that its
+// plan cuts along K.  Some callers have nowhere to get one from: a TensorRT plugin whose enqueue() was
+// not granted a workspace, a robot-control loop that must not touch the allocator once it is running,
+// host code that is handed raw pointers and no allocator of the framework that owns them.  For them the
 // scratch lives in the library image itself, in the array below.  Every GPU that loads the library
-// carries these 16 MiB until the process exits.
+// carries these 4 MiB until the process exits.
 //
 // Host code must not hand `g_static_scratch` to a kernel directly: in host code that name is only a
 // stand-in for the symbol, not a device address.  The address is looked up once per device with
@@ -802,7 +1199,7 @@ extern "C" int tpb200_nvfp4_gemv_tc(const tpb200_gemv_tc_problem* problems, int 
 // ---------------------------------------------------------------------------------------------
 namespace {
 
-constexpr size_t kStaticScratchBytes = 16u << 20;
+constexpr size_t kStaticScratchBytes = 4u << 20;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 // device-side address of g_static_scratch per device ordinal, filled on first use
@@ -827,26 +1224,20 @@ extern "C" size_t tpb200_nvfp4_gemv_tc_static_capacity(void) { return kStaticScr
 extern "C" int tpb200_nvfp4_gemv_tc_static(const tpb200_gemv_tc_problem* problems, int count, int M, int pieces,
                                            int bias_dtype, int out_dtype, int activation, int flags,
                                            tpb200_stream_t stream) {
-    TPB_REQUIRE(problems != nullptr, TPB200_ERR_NULL);
-    TPB_REQUIRE(count >= 1 && count <= TPB200_MAX_GROUP, TPB200_ERR_SHAPE);
-    int sms = 0;
-    if (device_sms(sms) != TPB200_OK) return TPB200_ERR_CUDA;
-    TcPlan plan;
-    const int st = make_plan(problems, count, sms, plan);
+    // every argument is validated and the launch planned before anything is enqueued
+    Launch& L = launch_record();
+    const int st = prepare_pretiled(problems, count, M, pieces, bias_dtype, out_dtype, activation, flags, L);
     if (st != TPB200_OK) return st;
-    const size_t counter_bytes = (plan.counters * sizeof(int) + 255) / 256 * 256;
-    const size_t need = counter_bytes + plan.scratch_floats * sizeof(float);
-    // larger problems than the built-in scratch can hold are refused, never truncated
-    TPB_REQUIRE(need <= kStaticScratchBytes, TPB200_ERR_WORKSPACE);
+    // larger plans than the built-in scratch can hold are refused, never truncated
+    TPB_REQUIRE(workspace_bytes(*L.plan) <= kStaticScratchBytes, TPB200_ERR_WORKSPACE);
     void* scratch = nullptr;
     const int sa = static_scratch_address(&scratch);
     if (sa != TPB200_OK) return sa;
     // The array keeps whatever the previous call left.  Only the tile counters have to start at
     // zero; the partial sums are always written before they are read.
-    if (counter_bytes > 0 &&
-        cudaMemsetAsync(scratch, 0, counter_bytes, reinterpret_cast<cudaStream_t>(stream)) != cudaSuccess) {
+    const size_t cb = L.plan->counters > 0 ? counter_bytes(*L.plan) : 0;
+    if (cb > 0 && cudaMemsetAsync(scratch, 0, cb, reinterpret_cast<cudaStream_t>(stream)) != cudaSuccess) {
         return TPB200_ERR_CUDA;
     }
-    return tpb200_nvfp4_gemv_tc(problems, count, M, pieces, bias_dtype, out_dtype, activation, scratch,
-                                kStaticScratchBytes, flags, stream);
+    return launch(L, scratch, kStaticScratchBytes, stream);
 }

@@ -516,26 +516,34 @@ class TcGemv:
     """NVFP4 weight-only GEMV(s) for M <= 16 tokens on the tensor cores.  Built once from a list of
     problems (dicts: weight_packed [N, K/2] uint8, weight_scales [N, K/16] E4M3 bytes, global_scale,
     x [M, K], out [M, N], optional bias; or `w_image` = the tiled weight image of tile_weights(), the
-    same one the tensor-core GEMM streams); weights are tiled at construction.  `launch()` quantises
-    every distinct activation tensor into residual pieces and enqueues ONE GEMV kernel."""
+    same one the tensor-core GEMM streams); weights are tiled at construction.
 
-    def __init__(self, problems, pieces=3, activation=ACT_NONE, pdl=False):
+    `fused=True` (default): `launch()` is ONE kernel, which quantises the activations it needs inside the
+    launch.  `fused=False`: `launch()` first writes every distinct activation tensor as residual pieces to
+    an image in global memory (one quantiser launch), then runs the GEMV on those."""
+
+    def __init__(self, problems, pieces=3, activation=ACT_NONE, pdl=False, fused=True):
         if not 1 <= len(problems) <= _lib.MAX_GROUP:
             raise TurboPiError(f"1..{_lib.MAX_GROUP} problems per launch")
         p0 = problems[0]
         self.device = p0["x"].device
         self.M = p0["x"].shape[0]
         self.pieces = pieces
+        self.fused = fused
         self.activation = int(activation)
         self.flags = FLAG_PDL if pdl else FLAG_NONE
         self.out_dtype = _dt(p0["out"])
+        self.x_dtype = _dt(p0["x"])
         self.bias_dtype = _dt(p0["bias"]) if p0.get("bias") is not None else F32
         self._keep = []
-        self._acts = {}           # id(x) -> (x, image, row_scale, K)
-        arr = (_lib.GemvTcProblem * len(problems))()
+        self._acts = {}           # x.data_ptr() -> (x, image, row_scale, K)
+        lib = _lib.load()
+        arr = ((_lib.GemvTcFusedProblem if fused else _lib.GemvTcProblem) * len(problems))()
         for i, p in enumerate(problems):
             x, out = p["x"], p["out"]
             _cuda(x, out, p.get("bias"))
+            if x.shape[0] != self.M or _dt(x) != self.x_dtype or x.stride(1) != 1:
+                raise TurboPiError("every problem of a launch takes [M, K] activations of one dtype")
             K = x.shape[1]
             if "w_image" in p:
                 w_image, N = p["w_image"], out.shape[1]
@@ -547,21 +555,31 @@ class TcGemv:
                 b = torch.zeros((N, packed_pitch(K)), dtype=torch.uint8, device=self.device)
                 b[:, :K // 2] = w[:, :K // 2]
                 w_image = tile_weights(b, swizzle_scales(ws.view(torch.uint8)), N, K)
-            key = x.data_ptr()
-            if key not in self._acts:
-                nbytes = int(_lib.load().tpb200_nvfp4_gemv_tc_x_image_bytes(K, pieces))
-                self._acts[key] = (x, torch.empty(nbytes, dtype=torch.uint8, device=self.device),
-                                   torch.empty(16, dtype=torch.float32, device=self.device), K)
-            _, xi, rs, _ = self._acts[key]
-            self._keep.append((w_image, out, p.get("bias")))
-            arr[i] = _lib.GemvTcProblem(_ptr(w_image), _ptr(xi), _ptr(rs), _ptr(p.get("bias")),
-                                        _ptr(out), N, K, out.stride(0), float(p.get("global_scale", 1.0)))
+            self._keep.append((w_image, x, out, p.get("bias")))
+            gs = float(p.get("global_scale", 1.0))
+            if fused:
+                arr[i] = _lib.GemvTcFusedProblem(_ptr(w_image), _ptr(x), x.stride(0), _ptr(p.get("bias")), _ptr(out), N, K,
+                                                 out.stride(0), gs)
+            else:
+                key = x.data_ptr()
+                if key not in self._acts:
+                    nbytes = int(lib.tpb200_nvfp4_gemv_tc_x_image_bytes(K, pieces))
+                    self._acts[key] = (x, torch.empty(nbytes, dtype=torch.uint8, device=self.device),
+                                       torch.empty(16, dtype=torch.float32, device=self.device), K)
+                _, xi, rs, _ = self._acts[key]
+                arr[i] = _lib.GemvTcProblem(_ptr(w_image), _ptr(xi), _ptr(rs), _ptr(p.get("bias")), _ptr(out), N, K,
+                                            out.stride(0), gs)
         self._arr = arr
         with torch.cuda.device(self.device):
-            nbytes = int(_lib.load().tpb200_nvfp4_gemv_tc_workspace_size(arr, len(arr)))
+            size = lib.tpb200_nvfp4_gemv_tc_fused_workspace_size if fused else lib.tpb200_nvfp4_gemv_tc_workspace_size
+            nbytes = int(size(arr, len(arr)))
+        if nbytes == 0:
+            raise TurboPiError("the launch cannot be planned (unsupported shape or too many tiles for one launch)")
         self.workspace = torch.zeros(max(nbytes, 256), dtype=torch.uint8, device=self.device)
 
     def quantize(self):
+        if self.fused:
+            return
         lib = _lib.load()
         with torch.cuda.device(self.device):
             stream = torch.cuda.current_stream(self.device).cuda_stream
@@ -575,16 +593,24 @@ class TcGemv:
                 _lib.check(st, "tpb200_nvfp4_quantize_acts_tc")
 
     def gemv(self):
+        lib = _lib.load()
         with torch.cuda.device(self.device):
-            st = _lib.load().tpb200_nvfp4_gemv_tc(self._arr, len(self._arr), self.M, self.pieces, self.bias_dtype,
-                                                  self.out_dtype, self.activation, _ptr(self.workspace),
-                                                  self.workspace.numel(), self.flags,
-                                                  torch.cuda.current_stream(self.device).cuda_stream)
+            stream = torch.cuda.current_stream(self.device).cuda_stream
+            if self.fused:
+                st = lib.tpb200_nvfp4_gemv_tc_fused(self._arr, len(self._arr), self.M, self.pieces, self.x_dtype,
+                                                    self.bias_dtype, self.out_dtype, self.activation,
+                                                    _ptr(self.workspace), self.workspace.numel(), self.flags, stream)
+            else:
+                st = lib.tpb200_nvfp4_gemv_tc(self._arr, len(self._arr), self.M, self.pieces, self.bias_dtype,
+                                              self.out_dtype, self.activation, _ptr(self.workspace),
+                                              self.workspace.numel(), self.flags, stream)
         _lib.check(st, "tpb200_nvfp4_gemv_tc")
 
     def gemv_static(self):
         """The GEMV through the entry point that uses the library's built-in scratch instead of
-        `self.workspace` (for hosts that cannot allocate device memory)."""
+        `self.workspace` (for hosts that cannot allocate device memory); pre-tiled activations only."""
+        if self.fused:
+            raise TurboPiError("gemv_static takes pre-tiled activations: build the TcGemv with fused=False")
         with torch.cuda.device(self.device):
             st = _lib.load().tpb200_nvfp4_gemv_tc_static(self._arr, len(self._arr), self.M, self.pieces,
                                                          self.bias_dtype, self.out_dtype, self.activation, self.flags,
