@@ -208,8 +208,9 @@ int tpb200_nvfp4_quantize_act_pieces(const void* x, int x_dtype, int ldx, void* 
  * caller zeroes it ONCE after allocation, the kernel leaves its counters at zero; after a non-zero
  * tpb200_device_error() zero it again before reuse).  Launches that share a workspace must not overlap.
  * The host plans each launch (whole 256-row tiles dealt to the CTAs longest first; tiles are cut along K
- * only when a launch has too few or too long tiles for the machine) and remembers the plans of the last
- * few shape lists per calling thread.  No counterpart in the reference (its GEMVs are CUDA-core kernels).
+ * only when a launch has too few or too long tiles for the machine; a launch that fills the machine several
+ * times over leaves a third of its units in a pool that the CTAs draw from as they become free, through one
+ * ticket counter in the workspace) and remembers the plans of the last few shape lists per calling thread.  No counterpart in the reference (its GEMVs are CUDA-core kernels).
  *
  * tpb200_nvfp4_gemv_tc_fused is the same GEMV with the activation quantiser inside the launch: `x` is
  * the raw [M, K] activation tensor (x_dtype, row stride ldx elements, 0 = K) and four warps of every CTA
@@ -251,7 +252,8 @@ int tpb200_nvfp4_gemv_tc_fused(const tpb200_gemv_tc_fused_problem* problems, int
  * needed): CTAs used, work units, K stages of the busiest CTA and of the whole launch, tiles cut along K,
  * scratch bytes.  For tests and capacity planning. */
 typedef struct {
-    int grid; int units; int max_load_stages; int total_stages; int cut_tiles; size_t workspace_bytes;
+    int grid; int units; int max_load_stages; /* of a CTA's fixed list */ int total_stages; int cut_tiles;
+    int pool_units; /* units not tied to a CTA, drawn by whichever CTA is free */ size_t workspace_bytes;
 } tpb200_gemv_tc_plan_info;
 int tpb200_nvfp4_gemv_tc_plan(const int* N, const int* K, int count, int sms, tpb200_gemv_tc_plan_info* info);
 

@@ -4,6 +4,7 @@ There is no fallback: if the library is missing or a call returns a non-zero
 status, an exception is raised.
 """
 import ctypes
+import os
 from ctypes import c_char_p, c_float, c_int, c_size_t, c_void_p
 from pathlib import Path
 
@@ -54,7 +55,7 @@ class GemvTcFusedProblem(ctypes.Structure):
 
 class GemvTcPlanInfo(ctypes.Structure):
     _fields_ = [("grid", c_int), ("units", c_int), ("max_load_stages", c_int), ("total_stages", c_int),
-                ("cut_tiles", c_int), ("workspace_bytes", c_size_t)]
+                ("cut_tiles", c_int), ("pool_units", c_int), ("workspace_bytes", c_size_t)]
 
 
 class ActTc(ctypes.Structure):
@@ -133,11 +134,12 @@ def load():
     global _lib
     if _lib is not None:
         return _lib
-    if not LIB_PATH.exists():
+    path = Path(os.environ.get("TURBOPI_B200_LIB", LIB_PATH))    # an alternative build (e.g. a diagnostic one)
+    if not path.exists():
         raise TurboPiError(
-            f"{LIB_PATH} is missing: build it with `python -m turbopi_b200.build` "
+            f"{path} is missing: build it with `python -m turbopi_b200.build` "
             "(there is no CPU or PyTorch fallback for these kernels)")
-    lib = ctypes.CDLL(str(LIB_PATH))
+    lib = ctypes.CDLL(str(path))
     for name, (res, args) in SIGNATURES.items():
         fn = getattr(lib, name)      # AttributeError if the library does not export it
         fn.restype = res

@@ -24,6 +24,7 @@ enum DeviceErrorCode : int {
     kErrNone = 0,
     kErrGemvFullBarrierTimeout = 101,
     kErrGemvEmptyBarrierTimeout = 102,
+    kErrGemvUnitQueueTimeout = 103,
     kErrGemmTmaBarrierTimeout = 201,
     kErrGemmMmaBarrierTimeout = 202,
     kErrGemmEpilogueBarrierTimeout = 203,

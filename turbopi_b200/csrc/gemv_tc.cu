@@ -95,12 +95,18 @@ struct TcParams {
     int pieces;
     int x_dtype, bias_dtype, out_dtype, activation;
     int fused;
+    int debug_slot;             // diagnostic builds: which timeline slot this launch writes
+    int pool_begin, pool_size;  // units[pool_begin, pool_begin + pool_size) are drawn by whichever CTA is free
+    unsigned int* queue;        // the pool's ticket counter (zero between launches)
     float* scratch;
     int* counters;
     TcProblem prob[kMaxProblems];
     uint16_t cta_begin[kMaxCtas + 1];
     TcUnit units[kMaxUnits];
 };
+
+constexpr int kUnitRing = 16;         // work units in flight between the producer and the slowest role of a CTA
+constexpr uint8_t kEndOfUnits = 0xFF; // `p` of the record that closes a CTA's unit list
 
 struct SharedControl {
     uint64_t full[kMaxStages];
@@ -110,9 +116,12 @@ struct SharedControl {
     uint64_t sf_full[2];      // scale set j copied into tensor memory (arrives through tcgen05.commit)
     uint64_t sf_empty[2];     // the MMAs that read scale set j are done
     uint32_t tmem_base;
-    int abort_flag;
+    volatile int abort_flag;
     int ticket;
+    volatile int units_published;
+    TcUnit units[kUnitRing];              // the CTA's unit list as the producer publishes it
     float row_scale[kRsRing][16];
+    int act_e[4][2][16];                  // per quantiser warp: pre-scale exponents of its two cached tensors
 };
 
 __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16]) {
@@ -137,6 +146,88 @@ __device__ __forceinline__ int prescale_exponent(float amax) {
     return e;
 }
 
+// 16 consecutive elements, already in registers as loaded (two 16-byte words of 16-bit elements, or four of fp32)
+__device__ __forceinline__ void unpack16(const uint4 (&raw)[4], int dtype, float (&v)[16]) {
+    if (dtype == TPB200_F32) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            v[4 * i] = __uint_as_float(raw[i].x);
+            v[4 * i + 1] = __uint_as_float(raw[i].y);
+            v[4 * i + 2] = __uint_as_float(raw[i].z);
+            v[4 * i + 3] = __uint_as_float(raw[i].w);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const uint32_t w[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = dtype == TPB200_F16 ? __half22float2(*reinterpret_cast<const __half2*>(&w[j]))
+                                                     : __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[j]));
+                v[8 * i + 2 * j] = f.x;
+                v[8 * i + 2 * j + 1] = f.y;
+            }
+        }
+    }
+}
+
+// Unit i of this CTA's list, once the producer has published it.  False at the end of the list, after an
+// abort, or when the (bounded) wait runs out.
+__device__ __forceinline__ bool fetch_unit(SharedControl* ctl, int i, TcUnit& un) {
+    if (ctl->units_published <= i) {
+        const long long start = clock64();
+        while (ctl->units_published <= i) {
+            if (ctl->abort_flag) return false;
+            if (clock64() - start > 2000000000LL) {
+                record_error(kErrGemvUnitQueueTimeout);
+                ctl->abort_flag = 1;
+                return false;
+            }
+        }
+    }
+    uint32_t w0, w1, w2, w3;
+    asm volatile("ld.volatile.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(w0), "=r"(w1), "=r"(w2), "=r"(w3)
+                 : "r"(smem_u32(&ctl->units[i & (kUnitRing - 1)]))
+                 : "memory");
+    uint4 w = make_uint4(w0, w1, w2, w3);
+    un = *reinterpret_cast<TcUnit*>(&w);
+    return un.p != kEndOfUnits;
+}
+
+// the same for a whole warp: lane 0 waits, every lane gets the record
+__device__ __forceinline__ bool fetch_unit_warp(SharedControl* ctl, int i, int lane, TcUnit& un) {
+    uint4 w = make_uint4(0u, 0u, 0u, 0u);
+    int ok = 0;
+    if (lane == 0) {
+        TcUnit t;
+        ok = fetch_unit(ctl, i, t) ? 1 : 0;
+        w = *reinterpret_cast<uint4*>(&t);
+    }
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    w.x = __shfl_sync(0xffffffffu, w.x, 0);
+    w.y = __shfl_sync(0xffffffffu, w.y, 0);
+    w.z = __shfl_sync(0xffffffffu, w.z, 0);
+    w.w = __shfl_sync(0xffffffffu, w.w, 0);
+    un = *reinterpret_cast<TcUnit*>(&w);
+    return ok != 0;
+}
+
+#ifdef TPB_TIMELINE
+// Diagnostic build only (-DTPB_TIMELINE): every CTA of the last launches leaves globaltimer stamps of its
+// milestones here; tpb200_debug_gemv_tc_timeline() copies them out.
+constexpr int kTlSlots = 4, kTlPoints = 12;
+__device__ unsigned long long g_timeline[kTlSlots][kMaxCtas][kTlPoints];
+__device__ __forceinline__ unsigned long long tl_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define TL(point) g_timeline[P.debug_slot & (kTlSlots - 1)][blockIdx.x][point] = tl_now()
+#else
+#define TL(point) ((void)0)
+#endif
+
 template <int kMaxUnits>
 __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid_constant__ TcParams<kMaxUnits> P) {
     extern __shared__ uint8_t smem_raw[];
@@ -148,15 +239,16 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int NB = 16 * P.pieces;
-    const int u_lo = P.cta_begin[blockIdx.x];
+    const int u_lo = P.cta_begin[blockIdx.x];        // this CTA's fixed units; more may come from the shared pool
     const int u_hi = P.cta_begin[blockIdx.x + 1];
     const bool fused = P.fused != 0;
 
     if (threadIdx.x == 0) {
+        TL(0);
         for (int s = 0; s < kMaxStages; ++s) {
             // a stage is full when its weight block has landed (one arrival with the byte count) and,
-            // in the fused form, when each of the four quantiser warps has written its rows
-            mbar_init(&ctl->full[s], fused ? 5 : 1);
+            // in the fused form, when the quantiser warp that owns the stage has written the activations
+            mbar_init(&ctl->full[s], fused ? 2 : 1);
             mbar_init(&ctl->empty[s], 1);
         }
         for (int b = 0; b < 2; ++b) {
@@ -166,6 +258,7 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
             mbar_init(&ctl->sf_empty[b], 1);
         }
         ctl->abort_flag = 0;
+        ctl->units_published = 0;
         fence_mbar_init();
     }
     if (warp == 1) {
@@ -186,18 +279,36 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
     __syncthreads();
     tc::fence_after_thread_sync();
     const uint32_t tmem_base = ctl->tmem_base;
-    volatile int* abort_flag = &ctl->abort_flag;
     pdl_launch_dependents();
+    if (threadIdx.x == 0) TL(1);
 
     if (warp == 0) {
         // ------------------------------------------------------------ producer (whole warp): lane 0 owns the
-        // barrier hand-shakes, lanes 0..3 each copy a quarter of the stage's weight block and lane 4 the
-        // pre-tiled activation block.  (A thread that issues a bulk copy is held for ~0.3 us whatever the size;
-        // requests issued side by side from several lanes overlap that.)  Weights never depend on the previous
-        // kernel, so the first stages' weight blocks are requested before griddepcontrol.wait; activations
-        // are written by the previous kernel.
+        // barrier hand-shakes and the unit list, lanes 0..3 each copy a quarter of the stage's weight block and
+        // lane 4 the pre-tiled activation block.  (A thread that issues a bulk copy is held for ~0.3 us whatever
+        // the size; requests issued side by side from several lanes overlap that.)  Weights never depend on the
+        // previous kernel, so the first stages' weight blocks are requested before griddepcontrol.wait;
+        // activations are written by the previous kernel.
+        //
+        // Unit list: the CTA's fixed units first, then units drawn from the launch's shared pool (one atomic
+        // per unit on a counter that the last drawer returns to zero).  SMs do not get equal shares of the
+        // memory system; with fixed lists alone the slowest CTA finishes microseconds after the others and
+        // holds up the next kernel of the stream.  The pool is touched only after griddepcontrol.wait, when
+        // the previous launch on this workspace has left its counter at zero.
         const uint32_t xbytes = fused ? 0u : static_cast<uint32_t>(NB) * 128u + kSfSlab;
         constexpr uint32_t kQuarter = kWBlock / 4;
+        int published = 0;
+        auto publish = [&](const TcUnit& un) {
+            if (lane == 0) {
+                ctl->units[published & (kUnitRing - 1)] = un;
+                __threadfence_block();
+                ctl->units_published = published + 1;
+            }
+            ++published;
+        };
+        TcUnit end_mark = {};
+        end_mark.p = kEndOfUnits;
+
         int pre = 0;
         for (int u = u_lo; u < u_hi && pre < kStages; ++u) {
             const TcUnit un = P.units[u];
@@ -213,24 +324,59 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
                 }
             }
         }
+        int next_fixed = u_lo;
+        TcUnit cur = end_mark;
+        bool have_cur = false;
+        if (next_fixed < u_hi) {
+            cur = P.units[next_fixed++];
+            have_cur = true;
+            publish(cur);
+        }
+        if (lane == 0) TL(2);
         pdl_wait_prior_grids();
+        if (lane == 0) TL(3);
+        bool pool_open = P.pool_size > 0;
+        // one draw from the pool; the drawer of the last ticket (every CTA fails exactly once) re-arms the counter
+        auto draw = [&](TcUnit& un) -> bool {
+            unsigned int ticket = 0;
+            if (lane == 0) ticket = atomicAdd(P.queue, 1u);
+            ticket = __shfl_sync(0xffffffffu, ticket, 0);
+            if (ticket < static_cast<unsigned int>(P.pool_size)) {
+                un = P.units[P.pool_begin + ticket];
+                return true;
+            }
+            pool_open = false;
+            if (lane == 0 && ticket == static_cast<unsigned int>(P.pool_size) + gridDim.x - 1u) {
+                atomicExch(P.queue, 0u);
+            }
+            return false;
+        };
+        if (!have_cur && pool_open) {
+            have_cur = draw(cur);
+            if (have_cur) publish(cur);
+        }
         int it = 0;
         bool stop = false;
-        for (int u = u_lo; u < u_hi && !stop; ++u) {
-            const TcUnit un = P.units[u];
+        while (have_cur && !stop) {
+            const TcUnit un = cur;
             const TcProblem& pr = P.prob[un.p];
+            // the next unit is fixed, or its ticket is requested now and read after this unit's copies went out
+            const bool next_is_fixed = next_fixed < u_hi;
+            unsigned int ticket = 0;
+            const bool drawing = !next_is_fixed && pool_open;
+            if (drawing && lane == 0) ticket = atomicAdd(P.queue, 1u);
             for (int ks = un.ks0; ks < un.ks1; ++ks, ++it) {
                 const int s = it % kStages;
                 uint8_t* st = smem + s * kStageBytes;
                 const size_t blk = static_cast<size_t>(un.rt) * pr.k_stages + ks;
                 int bad = 0;
                 if (lane == 0) {
-                    if (*abort_flag) {
+                    if (ctl->abort_flag) {
                         bad = 1;
                     } else if (it >= pre) {
                         if (it >= kStages && !mbar_wait_bounded(&ctl->empty[s], ((it / kStages) - 1) & 1)) {
                             record_error(kErrGemmEmptyBarrierTimeout);
-                            *abort_flag = 1;
+                            ctl->abort_flag = 1;
                             bad = 1;
                         } else {
                             mbar_expect_tx(&ctl->full[s], kWBlock + xbytes);
@@ -252,7 +398,26 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
                                   &ctl->full[s]);
                 }
             }
+            if (stop) break;
+            have_cur = false;
+            if (next_is_fixed) {
+                cur = P.units[next_fixed++];
+                have_cur = true;
+            } else if (drawing) {
+                ticket = __shfl_sync(0xffffffffu, ticket, 0);
+                if (ticket < static_cast<unsigned int>(P.pool_size)) {
+                    cur = P.units[P.pool_begin + ticket];
+                    have_cur = true;
+                } else {
+                    pool_open = false;
+                    if (lane == 0 && ticket == static_cast<unsigned int>(P.pool_size) + gridDim.x - 1u) {
+                        atomicExch(P.queue, 0u);
+                    }
+                }
+            }
+            if (have_cur) publish(cur);
         }
+        publish(end_mark);
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
@@ -266,13 +431,12 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
             uint32_t full_phase = 0;
             uint32_t lo0 = base16;
             uint32_t g = 0;                        // stages issued so far; stage g uses scale set g & 1
-            int unit_iter = 0;
-            for (int u = u_lo; u < u_hi && !*abort_flag; ++u, ++unit_iter) {
-                const TcUnit un = P.units[u];
-                const int buf = unit_iter & 1;
-                if (unit_iter >= 2 && !mbar_wait_bounded(&ctl->acc_empty[buf], ((unit_iter >> 1) - 1) & 1)) {
+            TcUnit un;
+            for (int i = 0; !ctl->abort_flag && fetch_unit(ctl, i, un); ++i) {
+                const int buf = i & 1;
+                if (i >= 2 && !mbar_wait_bounded(&ctl->acc_empty[buf], ((i >> 1) - 1) & 1)) {
                     record_error(kErrGemmEpilogueBarrierTimeout);
-                    *abort_flag = 1;
+                    ctl->abort_flag = 1;
                     break;
                 }
                 tc::fence_after_thread_sync();
@@ -281,15 +445,16 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
                 for (int ks = un.ks0; ks < un.ks1; ++ks) {
                     if (!mbar_wait_bounded(&ctl->full[s], full_phase)) {
                         record_error(kErrGemmTmaBarrierTimeout);
-                        *abort_flag = 1;
+                        ctl->abort_flag = 1;
                         break;
                     }
                     tc::fence_after_thread_sync();
+                    if (g == 0) TL(4);
                     // the scale copier (warp 6) has moved this stage's scales into set g & 1
                     const uint32_t set = g & 1u;
                     if (!mbar_wait_bounded(&ctl->sf_full[set], (g >> 1) & 1u)) {
                         record_error(kErrGemmTmaBarrierTimeout);
-                        *abort_flag = 1;
+                        ctl->abort_flag = 1;
                         break;
                     }
                     tc::fence_after_thread_sync();
@@ -319,179 +484,204 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
                 }
                 tc::commit(&ctl->acc_full[buf]);
             }
+            TL(5);
         }
     } else if (warp == 6) {
         // ------------------------------------------------------------ scale copier.
         // One thread issues every tcgen05 instruction it is given at ~60 cycles apiece; with the 12 scale
         // copies of a stage on the MMA thread that thread, not the weight stream, set the pace.  Here they
         // run one stage ahead into the other set of scale columns.  The copies do not depend on the tile, so
-        // this lane only needs the number of stages its CTA walks.
+        // this lane only needs the number of stages of each unit.
         if (lane == 0) {
-            int total = 0;
-            for (int u = u_lo; u < u_hi; ++u) {
-                const TcUnit un = P.units[u];
-                total += un.ks1 - un.ks0;
-            }
             const uint32_t base16 = smem_u32(smem) >> 4;
             const uint32_t stage16 = static_cast<uint32_t>(kStageBytes) >> 4;
             const uint32_t off_sfb16 = static_cast<uint32_t>(kWBlock + NB * 128) >> 4;
             int s = 0;
             uint32_t full_phase = 0, lo0 = base16;
-            for (int g = 0; g < total && !*abort_flag; ++g) {
-                const uint32_t set = g & 1;
-                if (!mbar_wait_bounded(&ctl->full[s], full_phase) ||
-                    (g >= 2 && !mbar_wait_bounded(&ctl->sf_empty[set], ((g >> 1) - 1) & 1))) {
-                    record_error(kErrGemmTmaBarrierTimeout);
-                    *abort_flag = 1;
-                    break;
-                }
-                tc::fence_after_thread_sync();
-                const uint32_t sfa = tmem_base + kSfaCol + set * kSfSetCols;
-                const uint32_t sfb = tmem_base + kSfbCol + set * kSfSetCols;
-                // stage: [codes rows 0..127][codes rows 128..255][slab 0..127][slab 128..255][x codes][x slab]
+            int g = 0;
+            TcUnit un;
+            bool stop = false;
+            for (int i = 0; !stop && !ctl->abort_flag && fetch_unit(ctl, i, un); ++i) {
+                for (int ks = un.ks0; ks < un.ks1; ++ks, ++g) {
+                    const uint32_t set = g & 1;
+                    if (!mbar_wait_bounded(&ctl->full[s], full_phase) ||
+                        (g >= 2 && !mbar_wait_bounded(&ctl->sf_empty[set], ((g >> 1) - 1) & 1))) {
+                        record_error(kErrGemmTmaBarrierTimeout);
+                        ctl->abort_flag = 1;
+                        stop = true;
+                        break;
+                    }
+                    tc::fence_after_thread_sync();
+                    const uint32_t sfa = tmem_base + kSfaCol + set * kSfSetCols;
+                    const uint32_t sfb = tmem_base + kSfbCol + set * kSfSetCols;
+                    // stage: [codes rows 0..127][codes rows 128..255][slab 0..127][slab 128..255][x codes][x slab]
 #pragma unroll
-                for (int a = 0; a < 4; ++a) {
-                    tc::cp_sf_32x128b(sfa + 4 * a, tc::desc_from_words(lo0 + ((2 * kWTile + a * 512) >> 4), tc::kDescHiSfAtom));
-                    tc::cp_sf_32x128b(sfa + 16 + 4 * a,
-                                      tc::desc_from_words(lo0 + ((2 * kWTile + kSfSlab + a * 512) >> 4), tc::kDescHiSfAtom));
-                    tc::cp_sf_32x128b(sfb + 4 * a, tc::desc_from_words(lo0 + off_sfb16 + ((a * 512) >> 4), tc::kDescHiSfAtom));
-                }
-                tc::commit(&ctl->sf_full[set]);
-                if (++s == kStages) {
-                    s = 0;
-                    full_phase ^= 1;
-                    lo0 = base16;
-                } else {
-                    lo0 += stage16;
+                    for (int a = 0; a < 4; ++a) {
+                        tc::cp_sf_32x128b(sfa + 4 * a, tc::desc_from_words(lo0 + ((2 * kWTile + a * 512) >> 4), tc::kDescHiSfAtom));
+                        tc::cp_sf_32x128b(sfa + 16 + 4 * a,
+                                          tc::desc_from_words(lo0 + ((2 * kWTile + kSfSlab + a * 512) >> 4), tc::kDescHiSfAtom));
+                        tc::cp_sf_32x128b(sfb + 4 * a, tc::desc_from_words(lo0 + off_sfb16 + ((a * 512) >> 4), tc::kDescHiSfAtom));
+                    }
+                    tc::commit(&ctl->sf_full[set]);
+                    if (++s == kStages) {
+                        s = 0;
+                        full_phase ^= 1;
+                        lo0 = base16;
+                    } else {
+                        lo0 += stage16;
+                    }
                 }
             }
         }
     } else if (warp >= kActWarp0) {
         // ------------------------------------------------------------ activation quantisers (fused form).
-        // Warp w owns the token rows t = w, w + 4, ...: it finds their pre-scales (one pass over the row,
-        // kept for the two most recent activation tensors), and for every stage writes the residual pieces
-        // of its rows' 16 blocks into the stage buffer, then arrives on the stage's `full` barrier.  The
-        // warps never talk to each other, so each can leave on its own if a wait runs out.
+        // Quantiser warp w owns every fourth stage of the CTA's stage sequence (stage number % 4 == w): for
+        // such a stage it turns the 256-wide K slice of all M token rows into residual pieces inside the stage
+        // buffer and arrives on the stage's `full` barrier.  Four stages are in work at once, so the latency
+        // of the activation loads and the ~0.6 us of arithmetic per stage stay off the weight stream's
+        // pace (0.55 us per stage).  Row pre-scales come from one pass over the tensor, kept per warp for its
+        // two most recent activation tensors.  The warps never talk to each other, so each can leave on its
+        // own if a wait runs out.
         if (fused) {
             const int aw = warp - kActWarp0;
-            const int nrows = P.M > aw ? (P.M - aw + 3) / 4 : 0;       // rows aw, aw + 4, ...
-            // pre-scale exponents of this warp's rows for the two most recent activation tensors
             const void* cache_x0 = nullptr;
             const void* cache_x1 = nullptr;
-            int e0[4] = {0, 0, 0, 0}, e1[4] = {0, 0, 0, 0}, ecur[4] = {0, 0, 0, 0};
             int victim = 0;
             pdl_wait_prior_grids();                                     // the activations come from the previous kernel
-            int it = 0;
+            if (aw == 0 && lane == 0) TL(8);
+            int it = 0;                                                 // stages of the units seen so far
             bool stop = false;
-            for (int u = u_lo; u < u_hi && !stop; ++u) {
-                const TcUnit un = P.units[u];
-                const TcProblem& pr = P.prob[un.p];
-                const void* x = pr.x;
-                const int K = pr.K, ldx = pr.ldx;
-                const int nblk = K >> 4;
-                if (cache_x0 == x) {
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) ecur[j] = e0[j];
-                } else if (cache_x1 == x) {
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) ecur[j] = e1[j];
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        int e = 0;
-                        if (j < nrows) {
-                            const int t = aw + 4 * j;
+            TcUnit un;
+            for (int i = 0; !stop && fetch_unit_warp(ctl, i, lane, un); ++i) {
+                const int nst = un.ks1 - un.ks0;
+                const int first = (aw - it) & 3;                        // this warp's first stage inside the unit
+                if (first < nst) {
+                    const TcProblem& pr = P.prob[un.p];
+                    const void* x = pr.x;
+                    const int ldx = pr.ldx;
+                    const int nblk = pr.K >> 4;
+                    int slot;
+                    if (cache_x0 == x) {
+                        slot = 0;
+                    } else if (cache_x1 == x) {
+                        slot = 1;
+                    } else {
+                        slot = victim;
+                        victim ^= 1;
+                        if (slot == 0) cache_x0 = x;
+                        else cache_x1 = x;
+                        for (int t = 0; t < P.M; ++t) {
                             float amax = 0.0f;
                             for (int kb = lane; kb < nblk; kb += 32) {
                                 float r[16];
                                 load16_as_float(x, P.x_dtype, static_cast<size_t>(t) * ldx + kb * 16, r);
 #pragma unroll
-                                for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(r[i]));
+                                for (int q = 0; q < 16; ++q) amax = fmaxf(amax, fabsf(r[q]));
                             }
 #pragma unroll
                             for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-                            e = prescale_exponent(amax);
+                            if (lane == 0) ctl->act_e[aw][slot][t] = prescale_exponent(amax);
                         }
-                        ecur[j] = e;
+                        __syncwarp();
                     }
-                    if (victim == 0) {
-                        cache_x0 = x;
+                    const int* e_row = ctl->act_e[aw][slot];
+                    // the epilogue of this unit multiplies by 2^-e; written by the owner of the unit's first stage
+                    if (first == 0 && lane < P.M) ctl->row_scale[i & (kRsRing - 1)][lane] = ldexpf(1.0f, -e_row[lane]);
+                    for (int o = first; o < nst && !stop; o += 4) {
+                        const int ks = un.ks0 + o;
+                        const int git = it + o;
+                        const int s = git % kStages;
+                        uint8_t* blk = smem + s * kStageBytes + kWBlock;
+                        bool waited = false;
+                        for (int item0 = 0; item0 < P.M * 16; item0 += 64) {
+                            // up to two (row, block) items per lane and round; the loads go out first
+                            uint4 raw[2][4];
+                            bool valid[2];
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) e0[j] = ecur[j];
-                    } else {
-                        cache_x1 = x;
+                            for (int q = 0; q < 2; ++q) {
+                                const int item = item0 + lane + 32 * q;
+                                const int kb = ks * 16 + (item & 15);
+                                valid[q] = item < P.M * 16 && kb < nblk;
+                                if (valid[q]) {
+                                    const size_t e0 = static_cast<size_t>(item >> 4) * ldx + static_cast<size_t>(kb) * 16;
+                                    if (P.x_dtype == TPB200_F32) {
+                                        const uint4* gp = reinterpret_cast<const uint4*>(static_cast<const float*>(x) + e0);
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) e1[j] = ecur[j];
-                    }
-                    victim ^= 1;
-                }
-                if (lane < nrows) {
-                    // the epilogue of this unit multiplies by 2^-e
-                    const int el = lane == 0 ? ecur[0] : (lane == 1 ? ecur[1] : (lane == 2 ? ecur[2] : ecur[3]));
-                    ctl->row_scale[u & (kRsRing - 1)][aw + 4 * lane] = ldexpf(1.0f, -el);
-                }
-                for (int ks = un.ks0; ks < un.ks1; ++ks, ++it) {
-                    const int s = it % kStages;
-                    int bad = 0;
-                    if (lane == 0) {
-                        if (*abort_flag) {
-                            bad = 1;
-                        } else if (it >= kStages && !mbar_wait_bounded(&ctl->empty[s], ((it / kStages) - 1) & 1)) {
-                            record_error(kErrGemmEmptyBarrierTimeout);
-                            *abort_flag = 1;
-                            bad = 1;
-                        }
-                    }
-                    bad = __shfl_sync(0xffffffffu, bad, 0);
-                    if (bad) {
-                        stop = true;
-                        break;
-                    }
-                    uint8_t* blk = smem + s * kStageBytes + kWBlock;
-                    for (int item = lane; item < nrows * 16; item += 32) {
-                        const int j = item >> 4;
-                        const int kbl = item & 15;                 // block inside the stage
-                        const int kb = ks * 16 + kbl;
-                        const int t = aw + 4 * j;
-                        const bool valid = kb < nblk;
-                        float r[16];
-                        if (valid) {
-                            load16_as_float(x, P.x_dtype, static_cast<size_t>(t) * ldx + kb * 16, r);
-                            const float pre = ldexpf(1.0f, j == 0 ? ecur[0] : (j == 1 ? ecur[1] : (j == 2 ? ecur[2] : ecur[3])));
+                                        for (int w = 0; w < 4; ++w) raw[q][w] = __ldg(gp + w);
+                                    } else {
+                                        const uint4* gp = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(x) + e0);
+                                        raw[q][0] = __ldg(gp);
+                                        raw[q][1] = __ldg(gp + 1);
+                                    }
+                                }
+                            }
+                            if (!waited) {
+                                waited = true;
+                                int bad = 0;
+                                if (lane == 0) {
+                                    if (ctl->abort_flag) {
+                                        bad = 1;
+                                    } else if (git >= kStages && !mbar_wait_bounded(&ctl->empty[s], ((git / kStages) - 1) & 1)) {
+                                        record_error(kErrGemmEmptyBarrierTimeout);
+                                        ctl->abort_flag = 1;
+                                        bad = 1;
+                                    }
+                                }
+                                bad = __shfl_sync(0xffffffffu, bad, 0);
+                                if (bad) {
+                                    stop = true;
+                                    break;
+                                }
+                            }
 #pragma unroll
-                            for (int i = 0; i < 16; ++i) r[i] *= pre;
+                            for (int q = 0; q < 2; ++q) {
+                                const int item = item0 + lane + 32 * q;
+                                if (item >= P.M * 16) continue;
+                                const int t = item >> 4;
+                                const int kbl = item & 15;                 // block inside the stage
+                                float r[16];
+                                if (valid[q]) {
+                                    unpack16(raw[q], P.x_dtype, r);
+                                    const float pre = ldexpf(1.0f, e_row[t]);
+#pragma unroll
+                                    for (int w = 0; w < 16; ++w) r[w] *= pre;
+                                }
+                                const int c = kbl >> 1;                    // 16-byte chunk of the 128-byte row
+                                for (int pc = 0; pc < P.pieces; ++pc) {
+                                    const int prow = pc * 16 + t;
+                                    uint8_t* dst = blk + prow * 128 + ((c ^ (prow & 7)) << 4) + (kbl & 1) * 8;
+                                    uint8_t* sf_dst = blk + NB * 128 + (kbl >> 2) * 512 + (prow & 31) * 16 + ((prow >> 5) & 3) * 4 + (kbl & 3);
+                                    uint32_t lo = 0, hi = 0;
+                                    uint8_t code = 0;
+                                    if (valid[q]) code = quantize_block16_piece(r, lo, hi);
+                                    *sf_dst = code;
+                                    *reinterpret_cast<uint2*>(dst) = make_uint2(lo, hi);
+                                }
+                            }
                         }
-                        const int c = kbl >> 1;                    // 16-byte chunk of the 128-byte row
-                        for (int p = 0; p < P.pieces; ++p) {
-                            const int prow = p * 16 + t;
-                            uint8_t* dst = blk + prow * 128 + ((c ^ (prow & 7)) << 4) + (kbl & 1) * 8;
-                            uint8_t* sf_dst = blk + NB * 128 + (kbl >> 2) * 512 + (prow & 31) * 16 + ((prow >> 5) & 3) * 4 + (kbl & 3);
-                            uint32_t lo = 0, hi = 0;
-                            uint8_t code = 0;
-                            if (valid) code = quantize_block16_piece(r, lo, hi);
-                            *sf_dst = code;
-                            *reinterpret_cast<uint2*>(dst) = make_uint2(lo, hi);
-                        }
+                        if (stop) break;
+                        fence_proxy_async_smem();                      // the tensor core reads these bytes
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&ctl->full[s]);
+                        if (aw == 0 && lane == 0 && git == 0) TL(9);
                     }
-                    fence_proxy_async_smem();                      // the tensor core reads these bytes
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&ctl->full[s]);
                 }
+                it += nst;
             }
+            if (aw == 0 && lane == 0) TL(10);
         }
     } else if (warp >= 2) {
         // ------------------------------------------------------------ epilogue (warps 2..5, 128 threads)
         const int q = warp & 3;
         const int et = q * 32 + lane;            // 0..127: the weight row inside the tile
-        int unit_iter = 0;
         pdl_wait_prior_grids();                   // the output buffer may still be read by the previous kernel
-        for (int u = u_lo; u < u_hi && !*abort_flag; ++u, ++unit_iter) {
-            const TcUnit un = P.units[u];
+        TcUnit un;
+        for (int i = 0; !ctl->abort_flag && fetch_unit_warp(ctl, i, lane, un); ++i) {
             const TcProblem& pr = P.prob[un.p];
-            const int buf = unit_iter & 1;
-            if (!mbar_wait_bounded(&ctl->acc_full[buf], (unit_iter >> 1) & 1)) {
+            const int buf = i & 1;
+            if (!mbar_wait_bounded(&ctl->acc_full[buf], (i >> 1) & 1)) {
                 record_error(kErrGemmMmaBarrierTimeout);
-                *abort_flag = 1;
+                ctl->abort_flag = 1;
                 break;
             }
             tc::fence_after_thread_sync();
@@ -549,9 +739,9 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
                 asm volatile("bar.sync 1, 128;" ::: "memory");              // ticket slot free for the next unit
             }
             if (finalize) {
-                // the row multipliers were written by the quantiser warps before they released the unit's
-                // first stage, which the MMAs behind this accumulator have consumed
-                const float* rs = fused ? ctl->row_scale[u & (kRsRing - 1)] : pr.row_scale;
+                // the row multipliers were written by a quantiser warp before it released the unit's first
+                // stage, which the MMAs behind this accumulator have consumed
+                const float* rs = fused ? ctl->row_scale[i & (kRsRing - 1)] : pr.row_scale;
 #pragma unroll
                 for (int h = 0; h < 2; ++h) {
                     const int n = un.rt * 256 + h * 128 + et;
@@ -571,12 +761,14 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
         }
     }
 
+    if (warp == 2 && lane == 0) TL(6);
     tc::fence_before_thread_sync();
     __syncthreads();
     if (warp == 1) {
         tc::fence_after_thread_sync();
         tc::tmem_dealloc(tmem_base, kTmemCols);
     }
+    if (threadIdx.x == 0) TL(7);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -677,15 +869,17 @@ struct Piece {
     uint16_t p, rt, ks0, ks1;
     int16_t cta;
 };
+constexpr int16_t kPoolCta = 0x7FFF;         // sorts after every CTA
 
 struct Plan {
     tpb::TcUnit units[kLargeUnits];          // CTA by CTA
     uint16_t cta_begin[tpb::kMaxCtas + 1];
     int num_units = 0;
     int grid = 0;
+    int pool_begin = 0, pool_size = 0;       // units[pool_begin ...) are not tied to a CTA
     size_t slots = 0;                        // partial-sum slots (16 * 256 floats each)
-    size_t counters = 0;
-    int max_load = 0;                        // stages of the longest CTA
+    size_t counters = 0;                     // arrival counters of cut tiles; the pool's ticket counter follows them
+    int max_load = 0;                        // stages of the longest CTA's fixed list
 };
 
 struct PlanScratch {
@@ -699,7 +893,7 @@ struct PlanScratch {
 
 // Deal the pieces of one candidate cut (no piece longer than `lmax` stages) to the CTAs, longest first,
 // each to the least loaded CTA; returns the largest load in stages, or -1 if the cut has too many pieces.
-int deal(const Shape* shapes, int count, int sms, int lmax, PlanScratch& S, bool& any_cut) {
+int deal(const Shape* shapes, int count, int sms, int lmax, int fixed_limit, PlanScratch& S, bool& any_cut) {
     S.num = 0;
     any_cut = false;
     for (int p = 0; p < count; ++p) {
@@ -733,8 +927,13 @@ int deal(const Shape* shapes, int count, int sms, int lmax, PlanScratch& S, bool
     for (int i = 0; i < S.num; ++i) {
         std::pop_heap(S.heap, S.heap + grid, heavier);           // least loaded CTA moves to the back
         const int c = S.heap[grid - 1];
-        S.pieces[i].cta = static_cast<int16_t>(c);
-        S.load[c] += S.pieces[i].ks1 - S.pieces[i].ks0;
+        const int len = S.pieces[i].ks1 - S.pieces[i].ks0;
+        if (S.load[c] == 0 || S.load[c] + len <= fixed_limit) {
+            S.pieces[i].cta = static_cast<int16_t>(c);
+            S.load[c] += len;
+        } else {
+            S.pieces[i].cta = kPoolCta;                          // left for whichever CTA is free first
+        }
         std::push_heap(S.heap, S.heap + grid, heavier);
     }
     return *std::max_element(S.load, S.load + grid);
@@ -754,12 +953,12 @@ int make_plan(const Shape* shapes, int count, int sms, Plan& plan, PlanScratch& 
     }
     constexpr int kHandOverStages = 5;
     constexpr int kWhole = 1 << 30;
-    int best_cost = 0;
+    int best_cost = 0, best_lmax = kWhole;
     bool have = false;
     for (int lmax : {kWhole, 16, 8, 4, 2, 1}) {
         if (lmax != kWhole && lmax >= longest) continue;           // same as the whole-tile plan
         bool any_cut = false;
-        const int load = deal(shapes, count, sms, lmax, S, any_cut);
+        const int load = deal(shapes, count, sms, lmax, kWhole, S, any_cut);
         if (load < 0) continue;
         int cost = load;
         if (any_cut) {
@@ -775,16 +974,28 @@ int make_plan(const Shape* shapes, int count, int sms, Plan& plan, PlanScratch& 
             S.num_best = S.num;
             S.grid_best = std::min(sms, S.num);
             best_cost = cost;
+            best_lmax = lmax;
             have = true;
         }
     }
     if (!have) return TPB200_ERR_SHAPE;                            // more tiles than one launch can list
+    // A launch that fills the machine several times over keeps about a third of its work out of the fixed
+    // lists: SMs do not get equal shares of the memory system, and the CTAs that run ahead pick those units up.
+    if (S.grid_best == sms && S.num_best >= 2 * sms) {
+        long long total = 0;
+        for (int i = 0; i < S.num_best; ++i) total += S.best[i].ks1 - S.best[i].ks0;
+        const int fixed_limit = static_cast<int>(total * 2 / (3LL * sms));
+        bool any_cut = false;
+        deal(shapes, count, sms, best_lmax, std::max(fixed_limit, 1), S, any_cut);
+        std::copy(S.pieces, S.pieces + S.num, S.best);
+    }
 
     // CTA by CTA: whole tiles first, cut tiles last (their hand-over then holds up nothing that follows);
     // neighbouring pieces of one tile that landed on the same CTA become one unit.
     auto k_stages = [&](int p) { return (shapes[p].K + 255) / 256; };
     std::sort(S.best, S.best + S.num_best, [&](const Piece& a, const Piece& b) {
         if (a.cta != b.cta) return a.cta < b.cta;
+        if (a.cta == kPoolCta && (a.ks1 - a.ks0) != (b.ks1 - b.ks0)) return (a.ks1 - a.ks0) > (b.ks1 - b.ks0);
         const bool ca = (a.ks1 - a.ks0) != k_stages(a.p), cb = (b.ks1 - b.ks0) != k_stages(b.p);
         if (ca != cb) return !ca;
         if (a.p != b.p) return a.p < b.p;
@@ -820,6 +1031,18 @@ int make_plan(const Shape* shapes, int count, int sms, Plan& plan, PlanScratch& 
         plan.max_load = std::max(plan.max_load, load);
     }
     plan.cta_begin[plan.grid] = static_cast<uint16_t>(plan.num_units);
+    plan.pool_begin = plan.num_units;
+    for (; i < S.num_best; ++i) {                                  // the pool, longest first, nothing merged
+        const Piece& pc = S.best[i];
+        if (plan.num_units == kLargeUnits) return TPB200_ERR_SHAPE;
+        tpb::TcUnit u = {};
+        u.p = static_cast<uint8_t>(pc.p);
+        u.rt = pc.rt;
+        u.ks0 = pc.ks0;
+        u.ks1 = pc.ks1;
+        plan.units[plan.num_units++] = u;
+    }
+    plan.pool_size = plan.num_units - plan.pool_begin;
     // cut tiles: slots in K order, one counter per tile
     int ncut = 0;
     for (int k = 0; k < plan.num_units; ++k) {
@@ -866,9 +1089,11 @@ int device_sms(int& sms) {
     return TPB200_OK;
 }
 
-size_t counter_bytes(const Plan& plan) { return (plan.counters * sizeof(int) + 255) / 256 * 256; }
+// arrival counters of the cut tiles, then the pool's ticket counter
+size_t counter_bytes(const Plan& plan) { return ((plan.counters + 1) * sizeof(int) + 255) / 256 * 256; }
+bool needs_workspace(const Plan& plan) { return plan.slots > 0 || plan.pool_size > 0; }
 size_t workspace_bytes(const Plan& plan) {
-    return counter_bytes(plan) + plan.slots * tpb::kSlotFloats * sizeof(float);
+    return needs_workspace(plan) ? counter_bytes(plan) + plan.slots * tpb::kSlotFloats * sizeof(float) : 0;
 }
 
 // Plans are remembered per calling thread for the last few distinct shape lists: a decode loop launches
@@ -943,7 +1168,12 @@ int launch_with(const Launch& L, void* workspace, tpb200_stream_t stream) {
     P.out_dtype = L.out_dtype;
     P.activation = L.activation;
     P.fused = L.fused;
+    static std::atomic<int> launch_number{0};
+    P.debug_slot = launch_number.fetch_add(1, std::memory_order_relaxed);
     P.counters = static_cast<int*>(workspace);
+    P.queue = reinterpret_cast<unsigned int*>(workspace) + plan.counters;
+    P.pool_begin = plan.pool_begin;
+    P.pool_size = plan.pool_size;
     P.scratch = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + counter_bytes(plan));
     std::copy(L.prob, L.prob + L.count, P.prob);
     std::copy(plan.cta_begin, plan.cta_begin + plan.grid + 1, P.cta_begin);
@@ -978,7 +1208,7 @@ int launch_with(const Launch& L, void* workspace, tpb200_stream_t stream) {
 }
 
 int launch(const Launch& L, void* workspace, size_t workspace_size, tpb200_stream_t stream) {
-    if (L.plan->slots > 0) {
+    if (needs_workspace(*L.plan)) {
         TPB_REQUIRE(workspace != nullptr, TPB200_ERR_WORKSPACE);
         TPB_REQUIRE(workspace_size >= workspace_bytes(*L.plan), TPB200_ERR_WORKSPACE);
         TPB_REQUIRE((reinterpret_cast<uintptr_t>(workspace) & 255u) == 0, TPB200_ERR_ALIGN);
@@ -1112,9 +1342,21 @@ extern "C" int tpb200_nvfp4_gemv_tc_plan(const int* N, const int* K, int count, 
     info->max_load_stages = plan.max_load;
     info->total_stages = static_cast<int>(total);
     info->cut_tiles = static_cast<int>(plan.counters);
+    info->pool_units = plan.pool_size;
     info->workspace_bytes = workspace_bytes(plan);
     return TPB200_OK;
 }
+
+#ifdef TPB_TIMELINE
+// Diagnostic build only: copies the stamps of the last kTlSlots launches ([slot][CTA][point], nanoseconds)
+// and returns the launch number the next launch will get.
+extern "C" int tpb200_debug_gemv_tc_timeline(unsigned long long* out, size_t bytes) {
+    if (bytes > sizeof(tpb::g_timeline)) bytes = sizeof(tpb::g_timeline);
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, tpb::g_timeline, bytes);
+    return 0;
+}
+#endif
 
 extern "C" size_t tpb200_nvfp4_gemv_tc_x_image_bytes(int K, int pieces) {
     if (K < 16 || pieces < 1 || pieces > 4) return 0;
@@ -1235,7 +1477,7 @@ extern "C" int tpb200_nvfp4_gemv_tc_static(const tpb200_gemv_tc_problem* problem
     if (sa != TPB200_OK) return sa;
     // The array keeps whatever the previous call left.  Only the tile counters have to start at
     // zero; the partial sums are always written before they are read.
-    const size_t cb = L.plan->counters > 0 ? counter_bytes(*L.plan) : 0;
+    const size_t cb = needs_workspace(*L.plan) ? counter_bytes(*L.plan) : 0;
     if (cb > 0 && cudaMemsetAsync(scratch, 0, cb, reinterpret_cast<cudaStream_t>(stream)) != cudaSuccess) {
         return TPB200_ERR_CUDA;
     }
