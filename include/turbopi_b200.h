@@ -268,6 +268,33 @@ int tpb200_nvfp4_gemv_tc_static(const tpb200_gemv_tc_problem* problems, int coun
                                 int bias_dtype, int out_dtype, int activation, int flags, tpb200_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Attention softmax(scale * Q K^T + key_bias) V on the tensor cores, bf16 in / bf16 out, fp32 softmax.
+ * Replaces the scaled_dot_product_attention calls of the reference model
+ * (openpi/src/openpi/models_pytorch/pi0_pytorch.py:476-501 prefix, :608-627 / :723-727 action expert;
+ * eager forms: transformers_replace/models/gemma/modeling_gemma.py:222-245, .../siglip/modeling_siglip.py:325-345).
+ *   q [n_rows, head_dim] (row stride ldq), k / v [n_keys, head_dim], out [n_rows, head_dim]; head_dim a
+ *   multiple of 8, <= 256.  Gemma's 8 query heads on one key/value head are passed as n_rows = tokens * 8
+ *   rows of the [tokens, 8 * 256] projection (ldq = 256).  groups_outer x groups_inner independent problems
+ *   (SigLIP: images x heads) start at base + a * stride[0] + b * stride[1] elements.
+ *   key_bias: bf16 [n_keys] added to every row's scores (0, or the mask value for a key that must not be
+ *   attended to), NULL = none.
+ * Keys are split in tiles of 128 across CTAs; with more than one tile the partial results pass through
+ * `workspace` (tpb200_attention_workspace_size bytes, no initialisation needed) and a second small kernel.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct {
+    const void* q; const void* k; const void* v; void* out; const void* key_bias;
+    int n_rows; int n_keys; int head_dim;
+    int ldq; int ldk; int ldv; int ldo;
+    int groups_outer; int groups_inner;
+    long long q_stride[2]; long long k_stride[2]; long long v_stride[2]; long long o_stride[2];
+    float scale;
+    void* workspace; size_t workspace_bytes;
+    int flags;
+} tpb200_attention_args;
+size_t tpb200_attention_workspace_size(int n_rows, int n_keys, int head_dim, int groups);
+int tpb200_attention(const tpb200_attention_args* args, tpb200_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Row-wise glue between two linears, fused with the activation quantiser of the tensor-core GEMM:
  *   h = res_in + x * gate (optional)  ->  RMSNorm (1 + w0) | adaptive RMSNorm (1 + w0) + w1 | LayerNorm w0, w1
  *   or  GELU_tanh(x[:, :K]) * x[:, K:2K]

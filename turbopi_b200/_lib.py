@@ -58,6 +58,16 @@ class GemvTcPlanInfo(ctypes.Structure):
                 ("cut_tiles", c_int), ("pool_units", c_int), ("workspace_bytes", c_size_t)]
 
 
+class AttentionArgs(ctypes.Structure):
+    _fields_ = [("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("out", c_void_p), ("key_bias", c_void_p),
+                ("n_rows", c_int), ("n_keys", c_int), ("head_dim", c_int),
+                ("ldq", c_int), ("ldk", c_int), ("ldv", c_int), ("ldo", c_int),
+                ("groups_outer", c_int), ("groups_inner", c_int),
+                ("q_stride", ctypes.c_longlong * 2), ("k_stride", ctypes.c_longlong * 2),
+                ("v_stride", ctypes.c_longlong * 2), ("o_stride", ctypes.c_longlong * 2),
+                ("scale", c_float), ("workspace", c_void_p), ("workspace_bytes", c_size_t), ("flags", c_int)]
+
+
 class ActTc(ctypes.Structure):
     _fields_ = [("x", c_void_p), ("ldx", c_int), ("K", c_int), ("x_image", c_void_p), ("x_row_scale", c_void_p)]
 
@@ -107,6 +117,8 @@ SIGNATURES = {
                                            c_int, c_void_p, c_size_t, c_int, c_void_p]),
     "tpb200_nvfp4_gemv_tc_plan": (c_int, [ctypes.POINTER(c_int), ctypes.POINTER(c_int), c_int, c_int,
                                           ctypes.POINTER(GemvTcPlanInfo)]),
+    "tpb200_attention_workspace_size": (c_size_t, [c_int, c_int, c_int, c_int]),
+    "tpb200_attention": (c_int, [ctypes.POINTER(AttentionArgs), c_void_p]),
     "tpb200_row_transform_quantize": (c_int, [ctypes.POINTER(RowOpArgs), c_void_p]),
     "tpb200_nvfp4_gemv_tc_static_capacity": (c_size_t, []),
     "tpb200_nvfp4_gemv_tc_static": (c_int, [ctypes.POINTER(GemvTcProblem), c_int, c_int, c_int, c_int, c_int, c_int,

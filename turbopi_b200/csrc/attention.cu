@@ -1,0 +1,466 @@
+// Attention for the Pi0.5 shapes on the tensor cores (tcgen05 kind::f16, bf16 operands, fp32 accumulators
+// in tensor memory):
+//
+//   Gemma prefix / action expert   8 query heads on ONE key/value head, head_dim 256: the (token, head)
+//                                  pairs are just rows of a [tokens * 8, 256] matrix that all attend to the
+//                                  same keys, so the call is single-head attention over that matrix
+//                                  (712 x 8 rows on 712 keys; 50 x 8 rows on 762 keys), with an additive
+//                                  bias per key for padded prompt tokens / a missing camera;
+//   SigLIP                         2 images x 16 heads, 256 tokens, head_dim 72 (padded to 128 in shared memory).
+//
+// Every problem is far too small to fill the machine with one CTA per 128 query rows running over all
+// keys (the action expert has 4 such tiles), so the keys are split too: CTA (row tile, key tile of 128,
+// group) computes S = Q K^T (16 MMAs of K = 16), the softmax of its 128 x 128 block relative to the block's
+// own row maxima, and O = P V (8 MMAs), and leaves O, the row maxima and the row sums in scratch; a second
+// small kernel combines the key tiles' partial results (the usual log-sum-exp merge).  With a single key
+// tile the first kernel writes the final rows itself.
+//
+// Operands in shared memory, all in the 128-byte-swizzle image (rows of 128 B = 64 bf16, 16-byte chunk c of
+// row r at c ^ (r & 7), 8-row groups 1024 B apart, one 16 KB block per 64 columns of head_dim):
+//   Q [128 rows][D], K [128 keys][D]      K-major operands of S = Q K^T
+//   P [128 rows][128 keys]                K-major A operand of O = P V, written by the softmax threads over Q
+//   V [128 keys][D]                       the SAME image read as an MN-major B operand (the 128-byte direction
+//                                         is head_dim = N, the rows are keys = K): no transposed copy of V.
+// Loads are plain 16-byte cp.async with zero fill past the end of a matrix; nothing here waits on another CTA.
+#include <algorithm>
+#include <atomic>
+
+#include "tcgen05.cuh"
+
+namespace tpb {
+namespace {
+
+constexpr int kRows = 128;              // query rows per CTA
+constexpr int kKeys = 128;              // keys per CTA
+constexpr int kChunkBytes = kRows * 128;   // one 64-column block of an operand
+constexpr int kThreadsAttn = 128;
+constexpr float kMasked = -2.3819763e38f;   // the reference's additive mask value (pi0_pytorch.py:185-188)
+constexpr uint32_t kTmemColsAttn = 512;
+constexpr uint32_t kColS = 0, kColO = 128;
+
+struct AttnParams {
+    const __nv_bfloat16* q;
+    const __nv_bfloat16* k;
+    const __nv_bfloat16* v;
+    __nv_bfloat16* out;
+    const __nv_bfloat16* key_bias;
+    int n_rows, n_keys, head_dim, dpad;         // dpad: head_dim rounded up to 64
+    int ldq, ldk, ldv, ldo;
+    int groups_inner;
+    long long q_stride[2], k_stride[2], v_stride[2], o_stride[2];
+    float scale;
+    int row_tiles, key_tiles;
+    float* part_o;                              // [group][row tile][key tile][128][dv]
+    float* part_ml;                             // [group][row tile][key tile][128][2]
+    int dv;                                     // head_dim rounded up to 16: N of the second MMA
+};
+
+struct AttnControl {
+    uint64_t bar_s, bar_o;
+    uint32_t tmem_base;
+    int abort_flag;
+    float bias[kKeys];
+};
+
+// Instruction descriptor for kind::f16 with bf16 operands and an fp32 accumulator, M = 128:
+//   [4,6) D format = 1 (f32)  [7,10) A format = 1 (bf16)  [10,13) B format = 1  [15] A major  [16] B major
+//   (0 = K-major, 1 = MN-major)  [17,23) N >> 3  [24,29) M >> 4
+__host__ __device__ constexpr uint32_t make_idesc_bf16(int n, int b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(b_mn_major) << 16) |
+           (static_cast<uint32_t>(n >> 3) << 17) | ((128u >> 4) << 24);
+}
+
+__device__ __forceinline__ void mma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                         uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        " .reg .pred p;\n"
+        " setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "}\n" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, bool valid) {
+    const uint32_t n = valid ? 16u : 0u;       // 0 source bytes: the 16 destination bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+// rows [row0, row0 + 128) of a [n, d] bf16 matrix (row stride ld elements) -> the swizzled image at `dst`
+__device__ __forceinline__ void load_tile(uint8_t* dst, const __nv_bfloat16* src, int ld, int row0, int n, int d, int dpad) {
+    const int cpr = dpad >> 3;                  // 16-byte chunks per row
+    for (int idx = threadIdx.x; idx < kRows * cpr; idx += kThreadsAttn) {
+        const int r = idx / cpr;
+        const int c = idx - r * cpr;
+        const bool valid = (row0 + r < n) && (c * 8 < d);
+        const __nv_bfloat16* g = valid ? src + static_cast<size_t>(row0 + r) * ld + c * 8 : src;
+        uint8_t* s = dst + (c >> 3) * kChunkBytes + r * 128 + (((c & 7) ^ (r & 7)) << 4);
+        cp_async16(s, g, valid);
+    }
+}
+
+__global__ void __launch_bounds__(kThreadsAttn, 1) attention_partial_kernel(const __grid_constant__ AttnParams P) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int nchunk = P.dpad >> 6;
+    uint8_t* sQ = smem;                                   // later P
+    uint8_t* sK = sQ + max(nchunk, 2) * kChunkBytes;      // P needs two 64-key blocks
+    uint8_t* sV = sK + nchunk * kChunkBytes;
+    AttnControl* ctl = reinterpret_cast<AttnControl*>(sV + nchunk * kChunkBytes);
+
+    const int rt = blockIdx.x, kt = blockIdx.y, g = blockIdx.z;
+    const int ga = g / P.groups_inner, gb = g - ga * P.groups_inner;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&ctl->bar_s, 1);
+        mbar_init(&ctl->bar_o, 1);
+        ctl->abort_flag = 0;
+        fence_mbar_init();
+    }
+    if (warp == 0) {
+        tc::tmem_alloc(&ctl->tmem_base, kTmemColsAttn);
+        tc::tmem_relinquish();
+    }
+    pdl_launch_dependents();
+    pdl_wait_prior_grids();                               // q, k, v come from the previous kernel
+
+    const __nv_bfloat16* q = P.q + ga * P.q_stride[0] + gb * P.q_stride[1];
+    const __nv_bfloat16* k = P.k + ga * P.k_stride[0] + gb * P.k_stride[1];
+    const __nv_bfloat16* v = P.v + ga * P.v_stride[0] + gb * P.v_stride[1];
+    load_tile(sQ, q, P.ldq, rt * kRows, P.n_rows, P.head_dim, P.dpad);
+    load_tile(sK, k, P.ldk, kt * kKeys, P.n_keys, P.head_dim, P.dpad);
+    load_tile(sV, v, P.ldv, kt * kKeys, P.n_keys, P.head_dim, P.dpad);
+    {
+        const int key = kt * kKeys + threadIdx.x;
+        float b = kMasked;                                // keys past the end never count
+        if (key < P.n_keys) b = P.key_bias != nullptr ? __bfloat162float(P.key_bias[key]) : 0.0f;
+        ctl->bias[threadIdx.x] = b;
+    }
+    cp_async_wait_all();
+    fence_proxy_async_smem();
+    tc::fence_before_thread_sync();
+    __syncthreads();
+    tc::fence_after_thread_sync();
+    const uint32_t tmem = ctl->tmem_base;
+
+    // ---------------------------------------------------------------- S = Q K^T
+    if (threadIdx.x == 0) {
+        const uint32_t idesc = make_idesc_bf16(kKeys, 0);
+        const uint32_t q16 = smem_u32(sQ) >> 4, k16 = smem_u32(sK) >> 4;
+        const int ksteps = (P.head_dim + 15) >> 4;        // 16 columns of head_dim per MMA
+        for (int kk = 0; kk < ksteps; ++kk) {
+            const uint32_t off = static_cast<uint32_t>((kk >> 2) * kChunkBytes + (kk & 3) * 32) >> 4;
+            mma_bf16(tmem + kColS, tc::desc_from_words(q16 + off, tc::kDescHiKmajorSw128),
+                     tc::desc_from_words(k16 + off, tc::kDescHiKmajorSw128), idesc, kk > 0 ? 1u : 0u);
+        }
+        tc::commit(&ctl->bar_s);
+    }
+    bool ok = mbar_wait_bounded(&ctl->bar_s, 0);
+    if (!ok) {
+        record_error(kErrAttnBarrierTimeout);
+        ctl->abort_flag = 1;
+    }
+    tc::fence_after_thread_sync();
+
+    // ---------------------------------------------------------------- softmax of this block, P -> shared memory
+    const int row = threadIdx.x;                          // tensor-memory lane = query row of the tile
+    const uint32_t lane_addr = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+    float m = -3.0e38f;
+    float l = 0.0f;
+    if (ok) {
+        // pass 1: row maximum of scale * s + bias
+#pragma unroll
+        for (int c0 = 0; c0 < kKeys; c0 += 32) {
+            uint32_t r[32];
+            tc::tmem_ld_32x32b_x32(lane_addr + kColS + c0, r);
+            tc::tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) m = fmaxf(m, fmaf(__uint_as_float(r[j]), P.scale, ctl->bias[c0 + j]));
+        }
+        // pass 2: p = exp(t - m) rounded to bf16 (what the PyTorch path feeds its second matmul), row sum of
+        // the rounded values, 16-byte stores into the K-major image of P
+        uint8_t* sP = sQ;
+#pragma unroll
+        for (int c0 = 0; c0 < kKeys; c0 += 32) {
+            uint32_t r[32];
+            tc::tmem_ld_32x32b_x32(lane_addr + kColS + c0, r);
+            tc::tmem_ld_wait();
+#pragma unroll
+            for (int j8 = 0; j8 < 4; ++j8) {
+                uint32_t w[4];
+#pragma unroll
+                for (int j2 = 0; j2 < 4; ++j2) {
+                    const int j = j8 * 8 + j2 * 2;
+                    const float t0 = fmaf(__uint_as_float(r[j]), P.scale, ctl->bias[c0 + j]);
+                    const float t1 = fmaf(__uint_as_float(r[j + 1]), P.scale, ctl->bias[c0 + j + 1]);
+                    const __nv_bfloat162 pb = __floats2bfloat162_rn(__expf(t0 - m), __expf(t1 - m));
+                    l += __bfloat162float(pb.x) + __bfloat162float(pb.y);
+                    w[j2] = *reinterpret_cast<const uint32_t*>(&pb);
+                }
+                const int c = (c0 >> 3) + j8;             // 16-byte chunk of the 128-key row: 0..15
+                uint8_t* dst = sP + (c >> 3) * kChunkBytes + row * 128 + (((c & 7) ^ (row & 7)) << 4);
+                *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        }
+    }
+    fence_proxy_async_smem();
+    tc::fence_before_thread_sync();
+    __syncthreads();
+    tc::fence_after_thread_sync();
+
+    // ---------------------------------------------------------------- O = P V
+    if (threadIdx.x == 0 && !ctl->abort_flag) {
+        const uint32_t idesc = make_idesc_bf16(P.dv, 1);  // B = V read MN-major
+        const uint32_t p16 = smem_u32(sQ) >> 4, v16 = smem_u32(sV) >> 4;
+        // MN-major, 128-byte swizzle: 64 columns of head_dim are contiguous, 8-key groups 1024 B apart
+        // (stride offset), the next 64 columns one 16 KB block further (leading offset)
+        constexpr uint32_t kDescHiMnSw128 = (1024u >> 4) | (1u << 14) | (static_cast<uint32_t>(tc::kSwizzle128B) << 29);
+        constexpr uint32_t kLboField = (static_cast<uint32_t>(kChunkBytes) >> 4) << 16;
+        for (int kk = 0; kk < kKeys / 16; ++kk) {
+            const uint32_t a_off = static_cast<uint32_t>((kk >> 2) * kChunkBytes + (kk & 3) * 32) >> 4;
+            const uint32_t b_off = static_cast<uint32_t>(kk * 2048) >> 4;
+            mma_bf16(tmem + kColO, tc::desc_from_words(p16 + a_off, tc::kDescHiKmajorSw128),
+                     tc::desc_from_words((v16 + b_off) | kLboField, kDescHiMnSw128), idesc, kk > 0 ? 1u : 0u);
+        }
+        tc::commit(&ctl->bar_o);
+    }
+    if (ok && !ctl->abort_flag) {
+        if (!mbar_wait_bounded(&ctl->bar_o, 0)) {
+            record_error(kErrAttnBarrierTimeout);
+            ok = false;
+        }
+    } else {
+        ok = false;
+    }
+    tc::fence_after_thread_sync();
+
+    // ---------------------------------------------------------------- write the rows
+    const int grow = rt * kRows + row;
+    if (ok && grow < P.n_rows) {
+        if (P.key_tiles == 1) {
+            __nv_bfloat16* o = P.out + ga * P.o_stride[0] + gb * P.o_stride[1] + static_cast<size_t>(grow) * P.ldo;
+            const float inv = 1.0f / l;
+            for (int c0 = 0; c0 < P.dv; c0 += 16) {
+                uint32_t r[16];
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+                    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                      "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                    : "r"(lane_addr + kColO + c0)
+                    : "memory");
+                tc::tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; j += 8) {
+                    if (c0 + j < P.head_dim) {            // head_dim is a multiple of 8
+                        uint32_t w[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(r[j + 2 * e]) * inv,
+                                                                           __uint_as_float(r[j + 2 * e + 1]) * inv);
+                            w[e] = *reinterpret_cast<const uint32_t*>(&b);
+                        }
+                        *reinterpret_cast<uint4*>(o + c0 + j) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+            }
+        } else {
+            const size_t tile = (static_cast<size_t>(g) * P.row_tiles + rt) * P.key_tiles + kt;
+            float* po = P.part_o + (tile * kRows + row) * P.dv;
+            float* pml = P.part_ml + (tile * kRows + row) * 2;
+            pml[0] = m;
+            pml[1] = l;
+            for (int c0 = 0; c0 < P.dv; c0 += 16) {
+                uint32_t r[16];
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+                    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                      "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                    : "r"(lane_addr + kColO + c0)
+                    : "memory");
+                tc::tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; j += 4) {
+                    *reinterpret_cast<uint4*>(po + c0 + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+                }
+            }
+        }
+    }
+    tc::fence_before_thread_sync();
+    __syncthreads();
+    if (warp == 0) {
+        tc::fence_after_thread_sync();
+        tc::tmem_dealloc(tmem, kTmemColsAttn);
+    }
+}
+
+// out[row] = sum_j w_j O_j / sum_j w_j l_j with w_j = exp(m_j - max_j m_j): one thread per 8 output columns
+__global__ void __launch_bounds__(256) attention_combine_kernel(const __grid_constant__ AttnParams P, int groups) {
+    pdl_launch_dependents();
+    pdl_wait_prior_grids();
+    const int c8 = P.head_dim >> 3;
+    const long long total = static_cast<long long>(groups) * P.n_rows * c8;
+    const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int c = static_cast<int>(idx % c8);
+    const long long gr = idx / c8;
+    const int grow = static_cast<int>(gr % P.n_rows);
+    const int g = static_cast<int>(gr / P.n_rows);
+    const int ga = g / P.groups_inner, gb = g - ga * P.groups_inner;
+    const int rt = grow / kRows, row = grow - rt * kRows;
+    const size_t tile0 = (static_cast<size_t>(g) * P.row_tiles + rt) * P.key_tiles;
+    float mmax = -3.0e38f;
+    for (int j = 0; j < P.key_tiles; ++j) mmax = fmaxf(mmax, P.part_ml[((tile0 + j) * kRows + row) * 2]);
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    float lsum = 0.0f;
+    for (int j = 0; j < P.key_tiles; ++j) {
+        const float* ml = P.part_ml + ((tile0 + j) * kRows + row) * 2;
+        const float w = __expf(ml[0] - mmax);
+        lsum = fmaf(w, ml[1], lsum);
+        const float4* po = reinterpret_cast<const float4*>(P.part_o + ((tile0 + j) * kRows + row) * P.dv + c * 8);
+        const float4 a = po[0], b = po[1];
+        acc[0] = fmaf(w, a.x, acc[0]); acc[1] = fmaf(w, a.y, acc[1]); acc[2] = fmaf(w, a.z, acc[2]); acc[3] = fmaf(w, a.w, acc[3]);
+        acc[4] = fmaf(w, b.x, acc[4]); acc[5] = fmaf(w, b.y, acc[5]); acc[6] = fmaf(w, b.z, acc[6]); acc[7] = fmaf(w, b.w, acc[7]);
+    }
+    const float inv = 1.0f / lsum;
+    uint32_t w[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const __nv_bfloat162 b = __floats2bfloat162_rn(acc[2 * e] * inv, acc[2 * e + 1] * inv);
+        w[e] = *reinterpret_cast<const uint32_t*>(&b);
+    }
+    __nv_bfloat16* o = P.out + ga * P.o_stride[0] + gb * P.o_stride[1] + static_cast<size_t>(grow) * P.ldo + c * 8;
+    *reinterpret_cast<uint4*>(o) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+}  // namespace
+
+int device_error_attention(int clear) { return read_device_error(clear); }
+
+}  // namespace tpb
+
+namespace {
+
+struct AttnDims {
+    int row_tiles, key_tiles, dpad, dv, groups;
+    size_t part_o_floats, part_ml_floats;
+};
+
+int attn_dims(int n_rows, int n_keys, int head_dim, int groups, AttnDims& d) {
+    TPB_REQUIRE(n_rows >= 1 && n_keys >= 1 && groups >= 1, TPB200_ERR_SHAPE);
+    TPB_REQUIRE(head_dim >= 8 && head_dim <= 256 && head_dim % 8 == 0, TPB200_ERR_SHAPE);
+    d.row_tiles = (n_rows + 127) / 128;
+    d.key_tiles = (n_keys + 127) / 128;
+    d.dpad = (head_dim + 63) / 64 * 64;
+    d.dv = (head_dim + 15) / 16 * 16;
+    d.groups = groups;
+    TPB_REQUIRE(d.key_tiles <= 65535 && groups <= 65535, TPB200_ERR_SHAPE);
+    const size_t tiles = static_cast<size_t>(groups) * d.row_tiles * d.key_tiles;
+    d.part_o_floats = d.key_tiles > 1 ? tiles * 128 * d.dv : 0;
+    d.part_ml_floats = d.key_tiles > 1 ? tiles * 128 * 2 : 0;
+    return TPB200_OK;
+}
+
+}  // namespace
+
+extern "C" size_t tpb200_attention_workspace_size(int n_rows, int n_keys, int head_dim, int groups) {
+    AttnDims d;
+    if (attn_dims(n_rows, n_keys, head_dim, groups, d) != TPB200_OK) return 0;
+    return (d.part_o_floats + d.part_ml_floats) * sizeof(float) + 256;
+}
+
+extern "C" int tpb200_attention(const tpb200_attention_args* a, tpb200_stream_t stream) {
+    TPB_REQUIRE(a != nullptr, TPB200_ERR_NULL);
+    TPB_REQUIRE(a->q && a->k && a->v && a->out, TPB200_ERR_NULL);
+    TPB_REQUIRE((a->flags & ~TPB200_FLAG_PDL) == 0, TPB200_ERR_ENUM);
+    TPB_REQUIRE(a->groups_outer >= 1 && a->groups_inner >= 1, TPB200_ERR_SHAPE);
+    AttnDims d;
+    const int st = attn_dims(a->n_rows, a->n_keys, a->head_dim, a->groups_outer * a->groups_inner, d);
+    if (st != TPB200_OK) return st;
+    TPB_REQUIRE(a->ldq >= a->head_dim && a->ldk >= a->head_dim && a->ldv >= a->head_dim && a->ldo >= a->head_dim,
+                TPB200_ERR_SHAPE);
+    // every row and every group offset must keep 16-byte alignment (8 bf16)
+    TPB_REQUIRE(tpb_aligned16(a->q) && tpb_aligned16(a->k) && tpb_aligned16(a->v) && tpb_aligned16(a->out), TPB200_ERR_ALIGN);
+    TPB_REQUIRE(a->ldq % 8 == 0 && a->ldk % 8 == 0 && a->ldv % 8 == 0 && a->ldo % 8 == 0, TPB200_ERR_ALIGN);
+    for (int i = 0; i < 2; ++i) {
+        TPB_REQUIRE(a->q_stride[i] % 8 == 0 && a->k_stride[i] % 8 == 0 && a->v_stride[i] % 8 == 0 && a->o_stride[i] % 8 == 0,
+                    TPB200_ERR_ALIGN);
+    }
+    const size_t need = (d.part_o_floats + d.part_ml_floats) * sizeof(float);
+    if (need > 0) {
+        TPB_REQUIRE(a->workspace != nullptr && a->workspace_bytes >= need, TPB200_ERR_WORKSPACE);
+        TPB_REQUIRE((reinterpret_cast<uintptr_t>(a->workspace) & 255u) == 0, TPB200_ERR_ALIGN);
+    }
+
+    tpb::AttnParams P = {};
+    P.q = static_cast<const __nv_bfloat16*>(a->q);
+    P.k = static_cast<const __nv_bfloat16*>(a->k);
+    P.v = static_cast<const __nv_bfloat16*>(a->v);
+    P.out = static_cast<__nv_bfloat16*>(a->out);
+    P.key_bias = static_cast<const __nv_bfloat16*>(a->key_bias);
+    P.n_rows = a->n_rows;
+    P.n_keys = a->n_keys;
+    P.head_dim = a->head_dim;
+    P.dpad = d.dpad;
+    P.dv = d.dv;
+    P.ldq = a->ldq;
+    P.ldk = a->ldk;
+    P.ldv = a->ldv;
+    P.ldo = a->ldo;
+    P.groups_inner = a->groups_inner;
+    for (int i = 0; i < 2; ++i) {
+        P.q_stride[i] = a->q_stride[i];
+        P.k_stride[i] = a->k_stride[i];
+        P.v_stride[i] = a->v_stride[i];
+        P.o_stride[i] = a->o_stride[i];
+    }
+    P.scale = a->scale;
+    P.row_tiles = d.row_tiles;
+    P.key_tiles = d.key_tiles;
+    P.part_o = static_cast<float*>(a->workspace);
+    P.part_ml = P.part_o + d.part_o_floats;
+
+    const int nchunk = d.dpad / 64;
+    const size_t smem = static_cast<size_t>(std::max(nchunk, 2) + 2 * nchunk) * tpb::kChunkBytes + sizeof(tpb::AttnControl) + 1024;
+    static std::atomic<uint64_t> configured{0};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const uint64_t bit = 1ull << (dev & 63);
+    if (!(configured.load(std::memory_order_relaxed) & bit)) {
+        if (cudaFuncSetAttribute(tpb::attention_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) !=
+            cudaSuccess) {
+            return TPB200_ERR_CUDA;
+        }
+        configured.fetch_or(bit, std::memory_order_relaxed);
+    }
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(d.row_tiles, d.key_tiles, d.groups);
+    cfg.blockDim = dim3(tpb::kThreadsAttn, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = reinterpret_cast<cudaStream_t>(stream);
+    if (a->flags & TPB200_FLAG_PDL) {
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    if (cudaLaunchKernelEx(&cfg, tpb::attention_partial_kernel, P) != cudaSuccess) return TPB200_ERR_CUDA;
+    if (d.key_tiles > 1) {
+        const long long threads = static_cast<long long>(d.groups) * a->n_rows * (a->head_dim / 8);
+        cudaLaunchConfig_t c2 = {};
+        c2.gridDim = dim3(static_cast<unsigned>((threads + 255) / 256), 1, 1);
+        c2.blockDim = dim3(256, 1, 1);
+        c2.stream = reinterpret_cast<cudaStream_t>(stream);
+        if (a->flags & TPB200_FLAG_PDL) {
+            c2.attrs = attr;
+            c2.numAttrs = 1;
+        }
+        if (cudaLaunchKernelEx(&c2, tpb::attention_combine_kernel, P, d.groups) != cudaSuccess) return TPB200_ERR_CUDA;
+    }
+    return TPB200_OK;
+}

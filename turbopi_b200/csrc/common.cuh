@@ -30,6 +30,7 @@ enum DeviceErrorCode : int {
     kErrGemmEpilogueBarrierTimeout = 203,
     kErrGemmEmptyBarrierTimeout = 204,
     kErrGemmSplitTimeout = 205,
+    kErrAttnBarrierTimeout = 301,
 };
 
 __device__ __forceinline__ void record_error(int code) { atomicCAS(&g_device_error, 0, code); }

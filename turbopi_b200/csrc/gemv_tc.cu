@@ -309,20 +309,21 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
         TcUnit end_mark = {};
         end_mark.p = kEndOfUnits;
 
+        // the ring's first fill goes out in ONE round: lane l requests quarter l % 4 of stage l / 4
         int pre = 0;
+        const uint8_t* my_src = nullptr;
         for (int u = u_lo; u < u_hi && pre < kStages; ++u) {
             const TcUnit un = P.units[u];
             const TcProblem& pr = P.prob[un.p];
             for (int ks = un.ks0; ks < un.ks1 && pre < kStages; ++ks, ++pre) {
-                uint8_t* st = smem + pre * kStageBytes;
                 const size_t blk = static_cast<size_t>(un.rt) * pr.k_stages + ks;
-                if (lane == 0) mbar_expect_tx(&ctl->full[pre], kWBlock + xbytes);
-                __syncwarp();
-                if (lane < 4) {
-                    bulk_copy_g2s(st + lane * kQuarter, pr.w_image + blk * kWBlock + lane * kQuarter, kQuarter,
-                                  &ctl->full[pre]);
-                }
+                if ((lane >> 2) == pre) my_src = pr.w_image + blk * kWBlock + (lane & 3) * kQuarter;
             }
+        }
+        if (lane < pre) mbar_expect_tx(&ctl->full[lane], kWBlock + xbytes);
+        __syncwarp();
+        if (my_src != nullptr) {
+            bulk_copy_g2s(smem + (lane >> 2) * kStageBytes + (lane & 3) * kQuarter, my_src, kQuarter, &ctl->full[lane >> 2]);
         }
         int next_fixed = u_lo;
         TcUnit cur = end_mark;
@@ -360,11 +361,6 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
         while (have_cur && !stop) {
             const TcUnit un = cur;
             const TcProblem& pr = P.prob[un.p];
-            // the next unit is fixed, or its ticket is requested now and read after this unit's copies went out
-            const bool next_is_fixed = next_fixed < u_hi;
-            unsigned int ticket = 0;
-            const bool drawing = !next_is_fixed && pool_open;
-            if (drawing && lane == 0) ticket = atomicAdd(P.queue, 1u);
             for (int ks = un.ks0; ks < un.ks1; ++ks, ++it) {
                 const int s = it % kStages;
                 uint8_t* st = smem + s * kStageBytes;
@@ -399,21 +395,14 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
                 }
             }
             if (stop) break;
+            // The next unit is drawn only now, not ahead of time: the ticket's round trip passes while the ring
+            // (five stages deep) still feeds the MMAs, and a slow CTA holds one unit less when the pool runs dry.
             have_cur = false;
-            if (next_is_fixed) {
+            if (next_fixed < u_hi) {
                 cur = P.units[next_fixed++];
                 have_cur = true;
-            } else if (drawing) {
-                ticket = __shfl_sync(0xffffffffu, ticket, 0);
-                if (ticket < static_cast<unsigned int>(P.pool_size)) {
-                    cur = P.units[P.pool_begin + ticket];
-                    have_cur = true;
-                } else {
-                    pool_open = false;
-                    if (lane == 0 && ticket == static_cast<unsigned int>(P.pool_size) + gridDim.x - 1u) {
-                        atomicExch(P.queue, 0u);
-                    }
-                }
+            } else if (pool_open) {
+                have_cur = draw(cur);
             }
             if (have_cur) publish(cur);
         }
@@ -571,12 +560,36 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
                         if (slot == 0) cache_x0 = x;
                         else cache_x1 = x;
                         for (int t = 0; t < P.M; ++t) {
+                            // four blocks per lane and round, all requested before the first is used: the pass
+                            // costs one memory latency per 2048 elements, not one per block
                             float amax = 0.0f;
-                            for (int kb = lane; kb < nblk; kb += 32) {
-                                float r[16];
-                                load16_as_float(x, P.x_dtype, static_cast<size_t>(t) * ldx + kb * 16, r);
+                            for (int kb0 = 0; kb0 < nblk; kb0 += 128) {
+                                uint4 raw[4][4];
 #pragma unroll
-                                for (int q = 0; q < 16; ++q) amax = fmaxf(amax, fabsf(r[q]));
+                                for (int j = 0; j < 4; ++j) {
+                                    const int kb = kb0 + lane + 32 * j;
+                                    if (kb < nblk) {
+                                        const size_t e0 = static_cast<size_t>(t) * ldx + static_cast<size_t>(kb) * 16;
+                                        if (P.x_dtype == TPB200_F32) {
+                                            const uint4* gp = reinterpret_cast<const uint4*>(static_cast<const float*>(x) + e0);
+#pragma unroll
+                                            for (int w = 0; w < 4; ++w) raw[j][w] = __ldg(gp + w);
+                                        } else {
+                                            const uint4* gp = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(x) + e0);
+                                            raw[j][0] = __ldg(gp);
+                                            raw[j][1] = __ldg(gp + 1);
+                                        }
+                                    }
+                                }
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    if (kb0 + lane + 32 * j < nblk) {
+                                        float r[16];
+                                        unpack16(raw[j], P.x_dtype, r);
+#pragma unroll
+                                        for (int q = 0; q < 16; ++q) amax = fmaxf(amax, fabsf(r[q]));
+                                    }
+                                }
                             }
 #pragma unroll
                             for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
@@ -689,14 +702,22 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
             float v[2][16];
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
+                // all pieces of a row half are requested before the one wait (a tensor-memory load takes a few
+                // hundred nanoseconds; one after the other they cost more than the unit's MMAs)
+                uint32_t r[4][16];
 #pragma unroll
-                for (int t = 0; t < 16; ++t) v[h][t] = 0.0f;
-                for (int pc = 0; pc < P.pieces; ++pc) {
-                    uint32_t r[16];
-                    tmem_ld_32x32b_x16(taddr + h * kMaxNB + pc * 16, r);
-                    tc::tmem_ld_wait();
+                for (int pc = 0; pc < 4; ++pc) {
+                    if (pc < P.pieces) tmem_ld_32x32b_x16(taddr + h * kMaxNB + pc * 16, r[pc]);
+                }
+                tc::tmem_ld_wait();
 #pragma unroll
-                    for (int t = 0; t < 16; ++t) v[h][t] += __uint_as_float(r[t]);
+                for (int t = 0; t < 16; ++t) {
+                    float acc = __uint_as_float(r[0][t]);
+#pragma unroll
+                    for (int pc = 1; pc < 4; ++pc) {
+                        if (pc < P.pieces) acc += __uint_as_float(r[pc][t]);
+                    }
+                    v[h][t] = acc;
                 }
             }
             tc::fence_before_thread_sync();

@@ -9,7 +9,7 @@ transformers_replace/models/gemma/modeling_gemma.py:49-129,212-230).
 Every linear layer runs as NVFP4 weights x bf16 activations on the tcgen05 GEMM (activations
 carried as residual e2m1 pieces); norms, residuals and GELU*up are the fused row kernels that
 write the next GEMM's operand directly; Q/K/V + RoPE + KV-cache append is the GEMM's fused
-epilogue.  Attention itself is torch's scaled_dot_product_attention for now.  All buffers are
+epilogue; attention is the tensor-core kernel of csrc/attention.cu (`ops.attention`).  All buffers are
 allocated once, so the whole inference (or just the denoise loop) replays as ONE CUDA graph.
 
 Weights come from a reference-named state dict (`Pi05.from_state_dict`, tensor names of
@@ -26,7 +26,6 @@ import math
 from dataclasses import dataclass
 
 import torch
-import torch.nn.functional as F
 
 from . import _lib, ops, weights
 from ._lib import ACT_GELU, ACT_NONE, ACT_SILU, TurboPiError
@@ -349,6 +348,13 @@ class Pi05:
                 obj.ws = self.workspace
         # additive attention bias per key (0 or the reference's mask value) over the cache rows
         self.key_bias = torch.zeros((c.max_seq,), dtype=bf, device=d)
+        # scratch of the attention kernel (partial results of the key tiles), sized for the largest call
+        lib = _lib.load()
+        hd_v = c.vision_width // c.vision_heads
+        need = max(lib.tpb200_attention_workspace_size(S * c.heads, S, c.head_dim, 1),
+                   lib.tpb200_attention_workspace_size(A * c.heads, S + A, c.head_dim, 1),
+                   lib.tpb200_attention_workspace_size(c.image_tokens, c.image_tokens, hd_v, c.num_images * c.vision_heads))
+        self.attn_ws = torch.empty(int(need), dtype=torch.uint8, device=d)
         self.tokens = torch.zeros((c.text_len,), dtype=torch.long, device=d)
         self.images = torch.zeros((c.num_images, c.image_size, c.image_size, 3), dtype=torch.uint8, device=d)
         self.noise = torch.zeros((A, c.action_dim), dtype=torch.float32, device=d)
@@ -379,13 +385,12 @@ class Pi05:
 
     def _attention(self, q, k, v, out):
         """q [L, H*D] -> softmax(q k^T / sqrt(D) + key bias) v, all heads sharing one K/V head.  Prefix
-        tokens see every valid prefix token, action tokens see the valid prefix and each other."""
+        tokens see every valid prefix token, action tokens see the valid prefix and each other.  The
+        (token, head) pairs are rows of one [L * H, D] problem for the tensor-core kernel."""
         c = self.cfg
         L = q.shape[0]
-        qh = q.view(L, c.heads, c.head_dim).transpose(0, 1).unsqueeze(0)
-        o = F.scaled_dot_product_attention(qh, k[None, None], v[None, None],
-                                           attn_mask=self.key_bias[None, None, None, :k.shape[0]], enable_gqa=True)
-        out.view(L, c.heads, c.head_dim).copy_(o[0].transpose(0, 1))
+        ops.attention(q.view(L * c.heads, c.head_dim), k, v, out.view(L * c.heads, c.head_dim), c.head_dim ** -0.5,
+                      self.key_bias, self.attn_ws)
 
     def vision_tower(self):
         c, b = self.cfg, self.b
@@ -408,8 +413,9 @@ class Pi05:
                       w1=L["ln1_b"], eps=c.eps)
             L["qkv"](b["q_v"], b["v_qkv"])
             qkv = b["v_qkv"].view(c.num_images, c.image_tokens, 3, c.vision_heads, hd).permute(2, 0, 3, 1, 4)
-            o = F.scaled_dot_product_attention(qkv[0], qkv[1], qkv[2])
-            b["v_attn"].view(c.num_images, c.image_tokens, c.vision_heads, hd).copy_(o.transpose(1, 2))
+            ops.attention(qkv[0], qkv[1], qkv[2],
+                          b["v_attn"].view(c.num_images, c.image_tokens, c.vision_heads, hd).permute(0, 2, 1, 3),
+                          hd ** -0.5, None, self.attn_ws)
             rowop(_lib.ROW_NONE, b["v_attn"], vw, b["q_v"])
             L["out"](b["q_v"], b["vy"])
             rowop(_lib.ROW_LAYERNORM, b["vy"], vw, b["q_v"], res_in=b["vh"], h_out=b["vh"], w0=L["ln2_w"], w1=L["ln2_b"],
