@@ -297,7 +297,7 @@ int tpb200_attention(const tpb200_attention_args* args, tpb200_stream_t stream);
 /* ---------------------------------------------------------------------------------------------
  * Row-wise glue between two linears, fused with the activation quantiser of the tensor-core GEMM:
  *   h = res_in + x * gate (optional)  ->  RMSNorm (1 + w0) | adaptive RMSNorm (1 + w0) + w1 | LayerNorm w0, w1
- *   or  GELU_tanh(x[:, :K]) * x[:, K:2K]
+ *   or  GELU_tanh(x[:, :K]) * x[:, K:2K]  |  SiLU(x[:, :K]) * x[:, K:2K]   (gated MLPs)
  * with the roundings of the PyTorch modules (GemmaRMSNorm, _gated_residual, GemmaMLP:
  * openpi/src/openpi/models_pytorch/transformers_replace/models/gemma/modeling_gemma.py:49-129,212-230),
  * written as residual e2m1 pieces + swizzled UE4M3 scales + row multipliers (the A operand of
@@ -305,7 +305,7 @@ int tpb200_attention(const tpb200_attention_args* args, tpb200_stream_t stream);
  * All tensors bf16, K % 16 == 0, K <= 16384.
  * ------------------------------------------------------------------------------------------- */
 enum { TPB200_ROW_NONE = 0, TPB200_ROW_RMSNORM = 1, TPB200_ROW_ADARMS = 2, TPB200_ROW_LAYERNORM = 3,
-       TPB200_ROW_GELU_MUL = 4 };
+       TPB200_ROW_GELU_MUL = 4, TPB200_ROW_SILU_MUL = 5 };
 typedef struct {
     int mode; int M; int K;
     const void* x; int ldx;

@@ -1,5 +1,5 @@
 #!/usr/bin/env python3
-"""Regenerate tests/golden/pi05_model.npz and pi05_rowops.npz by running the reference's own model code.
+"""Regenerate tests/golden/pi05_model.npz, pi05_rowops.npz and policy.npz by running the reference's own code.
 
 The reference model cannot be constructed here (its constructor wants a patched `transformers`
 4.53.2 install and a checkpoint), but the classes and methods that define the arithmetic depend on
@@ -306,6 +306,61 @@ def rowops_fixture(G):
     np.savez_compressed(OUT / "pi05_rowops.npz", **out)
 
 
+def policy_fixture(ref):
+    """Pre / post-processing of `PyTorchBackend` (openpi/src/openpi/inference/unified_policy.py:179-296): its own
+    _normalize_state, _unnormalize_actions and _preprocess, run with a stand-in tokenizer and norm statistics."""
+    text = (ref / "openpi" / "src" / "openpi" / "inference" / "unified_policy.py").read_text().splitlines()
+    import json, logging
+    from abc import ABC, abstractmethod
+    from dataclasses import dataclass
+    from typing import Any, Dict, List, Optional
+    ns = dict(torch=torch, np=np, json=json, logging=logging, ABC=ABC, abstractmethod=abstractmethod, dataclass=dataclass,
+              Dict=Dict, List=List, Optional=Optional, Any=Any, Path=Path, logger=logging.getLogger("ref"))
+    exec(FUTURE + _between(text, "@dataclass", "class PyTorchPipelinedBackend"), ns)
+    # `_preprocess` imports the model's Observation container: give it an attribute bag under that module name
+    fake = types.ModuleType("openpi.models_pytorch.pi0_pytorch")
+    fake.Observation = lambda **kw: NS(**kw)
+    for name in ("openpi", "openpi.models_pytorch"):
+        sys.modules.setdefault(name, types.ModuleType(name))
+    sys.modules["openpi.models_pytorch.pi0_pytorch"] = fake
+
+    class Tok:                      # deterministic stand-in for the SentencePiece model: BOS = 2, one id per character
+        def Encode(self, prompt, add_bos=True):
+            return ([2] if add_bos else []) + [10 + (ord(ch) % 200) for ch in prompt]
+
+    gen = np.random.default_rng(5)
+    stats_q = {"state": {"q01": (gen.normal(size=8) - 2).tolist(), "q99": (gen.normal(size=8) + 2).tolist()},
+               "actions": {"q01": (gen.normal(size=7) - 1).tolist(), "q99": (gen.normal(size=7) + 1).tolist()}}
+    stats_z = {"state": {"mean": gen.normal(size=8).tolist(), "std": (np.abs(gen.normal(size=8)) + 0.1).tolist()},
+               "actions": {"mean": gen.normal(size=7).tolist(), "std": (np.abs(gen.normal(size=7)) + 0.1).tolist()}}
+    be = ns["PyTorchBackend"].__new__(ns["PyTorchBackend"])
+    be.config = ns["PolicyConfig"](checkpoint_dir=".")
+    be.device, be.dtype, be.tokenizer = torch.device("cpu"), torch.float32, Tok()
+    state = gen.normal(size=8).astype(np.float32)
+    actions = gen.normal(size=(50, 32)).astype(np.float32)
+    img = gen.integers(0, 256, (224, 224, 3), dtype=np.uint8)
+    out = {"state": state, "actions": actions, "image": img,
+           "stats_q": np.frombuffer(json.dumps(stats_q).encode(), dtype=np.uint8),
+           "stats_z": np.frombuffer(json.dumps(stats_z).encode(), dtype=np.uint8)}
+    for tag, st in (("q", stats_q), ("z", stats_z), ("none", None)):
+        be.norm_stats = st
+        out[f"{tag}.state_norm"] = be._normalize_state(state)
+        out[f"{tag}.actions_unnorm"] = be._unnormalize_actions(actions)
+    be.norm_stats = stats_q
+    long_prompt = "pick up the black bowl and place it on the plate " * 6       # longer than 200 tokens with BOS
+    for tag, prompt, wrist in (("short", "pick up the black bowl", img[::-1].copy()), ("long", long_prompt, None)):
+        obs = be._preprocess({"observation/image": img, "observation/wrist_image": wrist, "observation/state": state,
+                              "prompt": prompt})
+        out[f"{tag}.prompt"] = np.frombuffer(prompt.encode(), dtype=np.uint8)
+        out[f"{tag}.tokens"] = obs.tokenized_prompt[0].numpy()
+        out[f"{tag}.token_mask"] = obs.tokenized_prompt_mask[0].numpy()
+        out[f"{tag}.state"] = obs.state[0].numpy()
+        out[f"{tag}.base_image"] = obs.images["base_0_rgb"][0].numpy()[:, ::16, ::16].copy()          # subsampled
+        out[f"{tag}.wrist_image"] = obs.images["left_wrist_0_rgb"][0].numpy()[:, ::16, ::16].copy()
+        out[f"{tag}.image_masks"] = np.array([bool(obs.image_masks[k][0]) for k in ("base_0_rgb", "left_wrist_0_rgb", "right_wrist_0_rgb")])
+    np.savez_compressed(OUT / "policy.npz", **out)
+
+
 def main():
     ref = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ["TURBOPI_REFERENCE"])
     torch.set_grad_enabled(False)
@@ -313,7 +368,8 @@ def main():
     G, S, P = load_reference(ref)
     model_fixture(G, S, P)
     rowops_fixture(G)
-    for n in ("pi05_model.npz", "pi05_rowops.npz"):
+    policy_fixture(ref)
+    for n in ("pi05_model.npz", "pi05_rowops.npz", "policy.npz"):
         print(n, (OUT / n).stat().st_size, "bytes")
 
 

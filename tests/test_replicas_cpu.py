@@ -57,3 +57,56 @@ def test_single_process_needs_no_group():
     assert rate == pytest.approx(10000.0) and ms == 5.0
     g.barrier()
     g.close()
+
+
+def _serve_main(rank, world, port, q, leave_after):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                      MASTER_PORT=str(port))
+    from turbopi_b200.replicas import ReplicaGroup, RequestDispatcher
+    g = ReplicaGroup.from_env(backend="gloo")
+    served = []
+
+    def infer(req):                      # a stand-in replica: the "actions" are a function of the request
+        served.append(req)
+        return torch.full((2,), float(req) * 10.0)
+
+    d = RequestDispatcher(g, infer, timeout_s=3.0)
+    results, stats = d.serve(list(range(8)), leave_after=leave_after if rank == 1 else None)
+    q.put((rank, None if results is None else [float(r[0]) for r in results], stats["done"], stats["requeued"], served))
+    if leave_after is None:
+        g.barrier()
+    g.close() if leave_after is None else None
+
+
+@pytest.mark.timeout(120)
+@pytest.mark.parametrize("leave_after", [None, 1])
+def test_dispatcher_splits_a_batch_and_requeues_what_a_lost_replica_left(leave_after):
+    """8 requests on 2 replicas: contiguous chunks of 4, results in request order on rank 0.  With rank 1 leaving
+    after its first request, rank 0 runs the three requests that never arrived."""
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_serve_main, args=(r, world, port, q, leave_after)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = {}
+    for _ in range(world):
+        rank, results, done, requeued, served = q.get(timeout=100)
+        got[rank] = (results, done, requeued, served)
+    for p in procs:
+        p.join(timeout=30)
+    results, done0, requeued, served0 = got[0]
+    assert results == [float(i) * 10.0 for i in range(8)]
+    assert got[1][0] is None
+    if leave_after is None:
+        assert requeued == [] and served0 == [0, 1, 2, 3] and got[1][3] == [4, 5, 6, 7]
+    else:
+        assert requeued == [5, 6, 7] and got[1][3] == [4] and served0 == [0, 1, 2, 3, 5, 6, 7]
+
+
+def test_split_requests_is_contiguous_and_even():
+    from turbopi_b200.replicas import split_requests
+    assert split_requests(64, 8) == [(8 * r, 8 * r + 8) for r in range(8)]
+    assert split_requests(8, 1) == [(0, 8)]
+    assert split_requests(10, 4) == [(0, 3), (3, 6), (6, 8), (8, 10)]
+    assert split_requests(2, 4) == [(0, 1), (1, 2), (2, 2), (2, 2)]

@@ -80,7 +80,7 @@ class RowOpArgs(ctypes.Structure):
                 ("pieces", c_int), ("piece_rows", c_int), ("layout", c_int), ("flags", c_int)]
 
 
-ROW_NONE, ROW_RMSNORM, ROW_ADARMS, ROW_LAYERNORM, ROW_GELU_MUL = 0, 1, 2, 3, 4
+ROW_NONE, ROW_RMSNORM, ROW_ADARMS, ROW_LAYERNORM, ROW_GELU_MUL, ROW_SILU_MUL = 0, 1, 2, 3, 4, 5
 
 # name -> (restype, argtypes); every symbol include/turbopi_b200.h declares
 SIGNATURES = {

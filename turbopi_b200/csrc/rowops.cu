@@ -21,7 +21,7 @@ constexpr int kMaxK = 16384;
 struct RowOpParams {
     int mode;
     int M, K;
-    const __nv_bfloat16* x;        // main input [M, ldx] (GELU_MUL: [M, 2K] = gate | up)
+    const __nv_bfloat16* x;        // main input [M, ldx] (GELU_MUL / SILU_MUL: [M, 2K] = gate | up)
     int ldx;
     // residual:  h = res_in + x * gate   (gate optional, [K]);  h_out optional
     const __nv_bfloat16* res_in;
@@ -128,12 +128,17 @@ __global__ void __launch_bounds__(kThreads) row_transform_quantize_kernel(const 
             continue;
         }
         const int k = kb << 4;
-        if (P.mode == TPB200_ROW_GELU_MUL) {
+        if (P.mode == TPB200_ROW_GELU_MUL || P.mode == TPB200_ROW_SILU_MUL) {
             float g[16], u[16];
             load16_bf16(P.x + static_cast<size_t>(m) * P.ldx + k, g);
             load16_bf16(P.x + static_cast<size_t>(m) * P.ldx + K + k, u);
+            if (P.mode == TPB200_ROW_GELU_MUL) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) v[j][i] = bf16r(bf16r(gelu_tanh_hw(g[i])) * u[i]);
+                for (int i = 0; i < 16; ++i) v[j][i] = bf16r(bf16r(gelu_tanh_hw(g[i])) * u[i]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 16; ++i) v[j][i] = bf16r(bf16r(__fdividef(g[i], 1.0f + __expf(-g[i]))) * u[i]);
+            }
         } else {
             load16_bf16(P.x + static_cast<size_t>(m) * P.ldx + k, v[j]);
             if (P.res_in != nullptr) {
@@ -275,9 +280,9 @@ __global__ void __launch_bounds__(kThreads) row_transform_quantize_kernel(const 
 
 extern "C" int tpb200_row_transform_quantize(const tpb200_rowop_args* a, tpb200_stream_t stream) {
     TPB_REQUIRE(a != nullptr && a->x != nullptr, TPB200_ERR_NULL);
-    TPB_REQUIRE(a->mode >= TPB200_ROW_NONE && a->mode <= TPB200_ROW_GELU_MUL, TPB200_ERR_ENUM);
+    TPB_REQUIRE(a->mode >= TPB200_ROW_NONE && a->mode <= TPB200_ROW_SILU_MUL, TPB200_ERR_ENUM);
     TPB_REQUIRE(a->M >= 1 && a->K >= 16 && a->K % 16 == 0 && a->K <= tpb::kMaxK, TPB200_ERR_SHAPE);
-    TPB_REQUIRE(a->ldx >= (a->mode == TPB200_ROW_GELU_MUL ? 2 * a->K : a->K) && a->ldx % 8 == 0, TPB200_ERR_SHAPE);
+    TPB_REQUIRE(a->ldx >= (a->mode >= TPB200_ROW_GELU_MUL ? 2 * a->K : a->K) && a->ldx % 8 == 0, TPB200_ERR_SHAPE);
     TPB_REQUIRE(tpb_aligned16(a->x) && tpb_aligned16(a->res_in) && tpb_aligned16(a->gate) && tpb_aligned16(a->h_out) &&
                     tpb_aligned16(a->w0) && tpb_aligned16(a->w1) && tpb_aligned16(a->y_out),
                 TPB200_ERR_ALIGN);

@@ -85,8 +85,16 @@ class NVFP4PackedLinear(nn.Module):
 
     Buffers follow the reference: weight_packed [N, K/2] uint8 and weight_scales
     [N, K/block] (fp32 for the "ref" format, uint8 E4M3 bytes + `global_scale` for
-    "nvfp4").  forward() accepts any leading shape; rows go through the kernel 16
-    at a time.  There is no dequantise-and-matmul path.
+    "nvfp4").  forward() accepts any leading shape and dispatches on the token count:
+
+      "nvfp4" weights   <= 16 tokens: ONE tensor-core GEMV launch (activations quantised in the launch
+                        for <= 4 tokens); more tokens: the tcgen05 block-scaled GEMM on the tiled weight
+                        image (bf16 activations as three residual e2m1 pieces).  The tiled image is built
+                        once, on the first forward, and serves both kernels.
+      "ref" weights     fp32 scales per 32 are not an operand format of the block-scaled tensor cores:
+                        rows go through the CUDA-core GEMV 16 at a time, exactly as stored.
+
+    There is no dequantise-and-matmul path.
     """
 
     def __init__(self, in_features: int, out_features: int, bias: bool = False, block_size: int = BLOCK_SIZE,
@@ -125,6 +133,37 @@ class NVFP4PackedLinear(nn.Module):
                 layer.bias.copy_(linear.bias)
         return layer.to(linear.weight.device)
 
+    # ------------------------------------------------------------------ tensor-core path ("nvfp4" format)
+    def tensor_core_ready(self) -> bool:
+        """True if the weights are standard NVFP4 (E4M3 scale per 16 + global scale) on a CUDA device."""
+        return (self.block_size == 16 and self.weight_scales is not None and self.weight_scales.dtype == torch.uint8
+                and self.weight_packed.is_cuda and self.in_features % 16 == 0)
+
+    def _tc_state(self):
+        """(tiled weight image, GEMV scratch, GEMM scratch), built on first use and whenever the packed
+        weights were replaced (load_state_dict, .to(device))."""
+        key = (self.weight_packed.data_ptr(), self.weight_scales.data_ptr(), str(self.weight_packed.device))
+        st = getattr(self, "_tc", None)
+        if st is None or st[0] != key:
+            N, K = self.out_features, self.in_features
+            dev = self.weight_packed.device
+            b = torch.zeros((N, ops.packed_pitch(K)), dtype=torch.uint8, device=dev)
+            b[:, :K // 2] = self.weight_packed
+            image = ops.tile_weights(b, ops.swizzle_scales(self.weight_scales.contiguous()), N, K)
+            st = (key, image, ops.tc_gemv_workspace(N, K, dev), ops.gemm_workspace(dev, 8 << 20))
+            self._tc = st
+        return st[1], st[2], st[3]
+
+    def _forward_tensor_cores(self, x2, act, bias):
+        T = x2.shape[0]
+        image, gemv_ws, gemm_ws = self._tc_state()
+        out = torch.empty((T, self.out_features), dtype=x2.dtype, device=x2.device)
+        if T <= 16:
+            return ops.tc_gemv(x2, image, self.out_features, out, self.global_scale, bias, act, 3, gemv_ws)
+        xb = x2 if x2.dtype == torch.bfloat16 else x2.to(torch.bfloat16)
+        return ops.nvfp4_gemm_w4a16_tiled(xb, image, self.out_features, alpha=self.global_scale, bias=bias, activation=act,
+                                          pieces=3, out=out, workspace=gemm_ws)
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         batch_shape = x.shape[:-1]
         x2 = x.reshape(-1, self.in_features)
@@ -132,9 +171,11 @@ class NVFP4PackedLinear(nn.Module):
             x2 = x2.float()
         x2 = x2.contiguous()
         T = x2.shape[0]
-        out = torch.empty((T, self.out_features), dtype=x2.dtype, device=x2.device)
         act = ACTIVATIONS.get(self.activation, 0)
         bias = None if self.bias is None else self.bias.detach().float().contiguous()
+        if self.tensor_core_ready():
+            return self._forward_tensor_cores(x2, act, bias).reshape(*batch_shape, self.out_features).to(x.dtype)
+        out = torch.empty((T, self.out_features), dtype=x2.dtype, device=x2.device)
         for t0 in range(0, T, 16):
             t1 = min(T, t0 + 16)
             ops.nvfp4_gemv_out(x2[t0:t1], self.weight_packed, self.weight_scales, out[t0:t1], bias, act,
@@ -153,7 +194,12 @@ class NVFP4PackedLinear(nn.Module):
 
 class NVFP4PackedMLP(nn.Module):
     """Gated MLP down(act(gate(x)) * up(x)).  `gate_activation` defaults to the
-    reference module's 'silu'; Gemma's own MLP uses 'gelu' (tanh form)."""
+    reference module's 'silu'; Gemma's own MLP uses 'gelu' (tanh form).
+
+    With "nvfp4" weights the forward is three or four launches whatever the token count: gate and up run as
+    ONE stacked [2I, K] matrix (one GEMV launch for <= 16 tokens, one tensor-core GEMM otherwise), the row
+    kernel applies act(gate) * up with the module's roundings (and, for the GEMM, writes the down
+    projection's operand), then the down projection."""
 
     def __init__(self, hidden_size: int, intermediate_size: int, block_size: int = BLOCK_SIZE,
                  gate_activation: str = "silu"):
@@ -172,16 +218,79 @@ class NVFP4PackedMLP(nn.Module):
         layer.gate_proj = NVFP4PackedLinear.from_linear(mlp.gate_proj, block_size, gate_activation, fmt)
         layer.up_proj = NVFP4PackedLinear.from_linear(mlp.up_proj, block_size, "none", fmt)
         layer.down_proj = NVFP4PackedLinear.from_linear(mlp.down_proj, block_size, "none", fmt)
+        if fmt == "nvfp4":
+            # gate and up are quantised as ONE [2I, K] matrix (a common global scale), so that they can run as one launch
+            with torch.no_grad():
+                w = torch.cat([mlp.gate_proj.weight.data, mlp.up_proj.weight.data], 0)
+                packed, scales, gs = quantize_nvfp4_two_level(w, 16)
+                I = mlp.gate_proj.out_features
+                dev = mlp.gate_proj.weight.device
+                for lin, sl in ((layer.gate_proj, slice(0, I)), (layer.up_proj, slice(I, 2 * I))):
+                    lin.weight_packed, lin.weight_scales, lin.global_scale = packed[sl].contiguous().to(dev), scales[sl].contiguous().to(dev), gs
         return layer
 
+    def _stacked_gate_up(self):
+        """Tiled image of [W_gate; W_up] under ONE global scale, or None if the projections do not share one
+        (each was quantised on its own: the stacked launch needs a common fp32 multiplier)."""
+        g, u = self.gate_proj, self.up_proj
+        key = (g.weight_packed.data_ptr(), u.weight_packed.data_ptr())
+        st = getattr(self, "_gu", None)
+        if st is None or st[0] != key:
+            if g.global_scale != u.global_scale:
+                st = (key, None)
+            else:
+                dev = g.weight_packed.device
+                N, K = 2 * self.intermediate_size, self.hidden_size
+                b = torch.zeros((N, ops.packed_pitch(K)), dtype=torch.uint8, device=dev)
+                b[:, :K // 2] = torch.cat([g.weight_packed, u.weight_packed], 0)
+                sc = torch.cat([g.weight_scales, u.weight_scales], 0).contiguous()
+                st = (key, ops.tile_weights(b, ops.swizzle_scales(sc), N, K), ops.tc_gemv_workspace(N, K, dev),
+                      ops.gemm_workspace(dev, 8 << 20))
+            self._gu = st
+        return st
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.down_proj(self.gate_proj(x) * self.up_proj(x))
+        g, u, d = self.gate_proj, self.up_proj, self.down_proj
+        fast = (g.tensor_core_ready() and u.tensor_core_ready() and d.tensor_core_ready() and g.bias is None
+                and u.bias is None and g.activation in ("gelu", "silu") and self.intermediate_size % 16 == 0)
+        st = self._stacked_gate_up() if fast else None
+        if st is None or st[1] is None:
+            return self.down_proj(self.gate_proj(x) * self.up_proj(x))
+        from . import _lib
+        _, gu_image, gu_gemv_ws, gu_gemm_ws = st
+        batch_shape = x.shape[:-1]
+        x2 = x.reshape(-1, self.hidden_size).contiguous()
+        if x2.dtype != torch.bfloat16:
+            x2 = x2.to(torch.bfloat16)
+        T, I = x2.shape[0], self.intermediate_size
+        gu = torch.empty((T, 2 * I), dtype=torch.bfloat16, device=x2.device)
+        mode = _lib.ROW_GELU_MUL if g.activation == "gelu" else _lib.ROW_SILU_MUL
+        d_image, d_gemv_ws, d_gemm_ws = d._tc_state()
+        d_bias = None if d.bias is None else d.bias.detach().float().contiguous()
+        out = torch.empty((T, self.hidden_size), dtype=torch.bfloat16, device=x2.device)
+        if T <= 16:
+            ops.tc_gemv(x2, gu_image, 2 * I, gu, g.global_scale, None, 0, 3, gu_gemv_ws)
+            h = torch.empty((T, I), dtype=torch.bfloat16, device=x2.device)
+            ops.rowop(mode, gu, I, None, y_out=h, M=T)
+            ops.tc_gemv(h, d_image, self.hidden_size, out, d.global_scale, d_bias, 0, 3, d_gemv_ws)
+        else:
+            ops.nvfp4_gemm_w4a16_tiled(x2, gu_image, 2 * I, alpha=g.global_scale, pieces=3, out=gu, workspace=gu_gemm_ws)
+            q = ops.QuantBuf(T, I, 3, x2.device)
+            ops.rowop(mode, gu, I, q, M=T)
+            args = _lib.GemmArgs(a_packed=ops._ptr(q.packed), a_pieces=3, a_row_scale=ops._ptr(q.row_scale),
+                                 b_packed=ops._ptr(d_image), alpha=float(d.global_scale), bias=ops._ptr(d_bias),
+                                 out=ops._ptr(out), out_dtype=ops._dt(out), ldo=out.stride(0), M=T, N=self.hidden_size, K=I,
+                                 layout=ops.OPERANDS_TILED)
+            ops._gemm_ex(args, x2.device, d_gemm_ws)
+        return out.reshape(*batch_shape, self.hidden_size).to(x.dtype)
 
 
 def replace_mlp_with_nvfp4_packed(model, block_size: int = BLOCK_SIZE, target_layers: Optional[list] = None,
-                                  gate_activation: str = "silu") -> int:
+                                  gate_activation: str = "silu", fmt: str = "nvfp4") -> int:
     """Swap every `layer.mlp` of model.paligemma_with_expert.paligemma.language_model for an
-    NVFP4PackedMLP; returns the number replaced."""
+    NVFP4PackedMLP; returns the number replaced.  `fmt="nvfp4"` (default) stores standard NVFP4, which the
+    tensor-core kernels consume; `fmt="ref"` keeps the reference's block-32 fp32-scale buffers (CUDA-core
+    GEMV only)."""
     try:
         lm = model.paligemma_with_expert.paligemma.language_model
     except AttributeError:
@@ -192,6 +301,6 @@ def replace_mlp_with_nvfp4_packed(model, block_size: int = BLOCK_SIZE, target_la
             continue
         if getattr(layer, "mlp", None) is not None:
             device = next(layer.mlp.parameters()).device
-            layer.mlp = NVFP4PackedMLP.from_gemma_mlp(layer.mlp, block_size, gate_activation).to(device)
+            layer.mlp = NVFP4PackedMLP.from_gemma_mlp(layer.mlp, block_size, gate_activation, fmt).to(device)
             count += 1
     return count

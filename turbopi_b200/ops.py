@@ -662,3 +662,51 @@ class TcGemv:
     def launch(self):
         self.quantize()
         self.gemv()
+
+
+def tc_gemv(x, w_image, N, out, global_scale=1.0, bias=None, activation=ACT_NONE, pieces=3, workspace=None, pdl=False):
+    """One tensor-core GEMV launch without a prepared problem table: out[M, N] = act(gs * x @ W^T + bias)
+    for M <= 16 rows, W given as its tiled image.  M <= 4 quantises the activations inside the launch; larger
+    M goes through the stand-alone quantiser first (the in-launch quantiser keeps pace with the weight stream
+    only for a few rows).  `workspace`: zeroed scratch of tc_gemv_workspace() bytes, reusable across calls
+    that do not overlap; allocated here when omitted."""
+    _cuda(x, w_image, out, bias, workspace)
+    M, K = x.shape
+    if not 1 <= M <= 16 or x.stride(1) != 1:
+        raise TurboPiError("tc_gemv: 1..16 rows with a contiguous last dimension")
+    lib = _lib.load()
+    flags = FLAG_PDL if pdl else FLAG_NONE
+    bias_dtype = _dt(bias) if bias is not None else F32
+    with torch.cuda.device(x.device):
+        stream = torch.cuda.current_stream(x.device).cuda_stream
+        if M <= 4:
+            arr = (_lib.GemvTcFusedProblem * 1)(_lib.GemvTcFusedProblem(_ptr(w_image), _ptr(x), x.stride(0), _ptr(bias), _ptr(out),
+                                                                          N, K, out.stride(0), float(global_scale)))
+            if workspace is None:
+                workspace = torch.zeros(int(lib.tpb200_nvfp4_gemv_tc_fused_workspace_size(arr, 1)), dtype=torch.uint8,
+                                        device=x.device)
+            st = lib.tpb200_nvfp4_gemv_tc_fused(arr, 1, M, pieces, _dt(x), bias_dtype, _dt(out), int(activation),
+                                                _ptr(workspace), workspace.numel(), flags, stream)
+            _lib.check(st, "tpb200_nvfp4_gemv_tc_fused")
+        else:
+            xi = torch.empty(int(lib.tpb200_nvfp4_gemv_tc_x_image_bytes(K, pieces)), dtype=torch.uint8, device=x.device)
+            rs = torch.empty(16, dtype=torch.float32, device=x.device)
+            st = lib.tpb200_nvfp4_quantize_act_tc(_ptr(x), _dt(x), x.stride(0), _ptr(xi), _ptr(rs), M, K, pieces, flags, stream)
+            _lib.check(st, "tpb200_nvfp4_quantize_act_tc")
+            arr = (_lib.GemvTcProblem * 1)(_lib.GemvTcProblem(_ptr(w_image), _ptr(xi), _ptr(rs), _ptr(bias), _ptr(out), N, K,
+                                                              out.stride(0), float(global_scale)))
+            if workspace is None:
+                workspace = torch.zeros(int(lib.tpb200_nvfp4_gemv_tc_workspace_size(arr, 1)), dtype=torch.uint8,
+                                        device=x.device)
+            st = lib.tpb200_nvfp4_gemv_tc(arr, 1, M, pieces, bias_dtype, _dt(out), int(activation), _ptr(workspace),
+                                          workspace.numel(), flags, stream)
+            _lib.check(st, "tpb200_nvfp4_gemv_tc")
+    return out
+
+
+def tc_gemv_workspace(N, K, device):
+    """Zeroed scratch for tc_gemv() on an [N, K] weight (the plan does not depend on the row count)."""
+    arr = (_lib.GemvTcFusedProblem * 1)(_lib.GemvTcFusedProblem(0, 0, 0, 0, 0, N, K, 0, 1.0))
+    with torch.cuda.device(device):
+        n = int(_lib.load().tpb200_nvfp4_gemv_tc_fused_workspace_size(arr, 1))
+    return torch.zeros(max(n, 256), dtype=torch.uint8, device=device)
