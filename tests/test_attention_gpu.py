@@ -93,5 +93,8 @@ def test_attention_refuses_bad_arguments(cuda_device):
         ops.attention(q.float(), q, q, q, 1.0)                        # not bf16
     with pytest.raises(TurboPiError):
         ops.attention(q, q[:, :128], q, q, 1.0)                       # head_dim mismatch
+    wide = torch.zeros((16, 264), dtype=BF, device=cuda_device)
     with pytest.raises(TurboPiError):
-        ops.attention(q[:, :260], q[:, :260], q[:, :260], q[:, :260], 1.0)   # head_dim > 256
+        ops.attention(wide, wide, wide, wide, 1.0)                    # head_dim > 256
+    with pytest.raises(TurboPiError):
+        ops.attention(q[:, :12], q[:, :12], q[:, :12], q[:, :12], 1.0)   # head_dim not a multiple of 8

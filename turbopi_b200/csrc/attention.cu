@@ -37,6 +37,7 @@ constexpr int kThreadsAttn = 128;
 constexpr float kMasked = -2.3819763e38f;   // the reference's additive mask value (pi0_pytorch.py:185-188)
 constexpr uint32_t kTmemColsAttn = 512;
 constexpr uint32_t kColS = 0, kColO = 128;
+constexpr long long kWaitCycles = 200000000LL;   // ~0.1 s: bound of each wait for the tensor cores
 
 struct AttnParams {
     const __nv_bfloat16* q;
@@ -58,7 +59,6 @@ struct AttnParams {
 struct AttnControl {
     uint64_t bar_s, bar_o;
     uint32_t tmem_base;
-    int abort_flag;
     float bias[kKeys];
 };
 
@@ -117,10 +117,11 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) attention_partial_kernel(cons
     if (threadIdx.x == 0) {
         mbar_init(&ctl->bar_s, 1);
         mbar_init(&ctl->bar_o, 1);
-        ctl->abort_flag = 0;
         fence_mbar_init();
     }
-    if (warp == 0) {
+    if (warp == 1) {
+        // a whole, converged warp (not the one whose lane 0 just ran the barrier set-up on its own)
+        __syncwarp();
         tc::tmem_alloc(&ctl->tmem_base, kTmemColsAttn);
         tc::tmem_relinquish();
     }
@@ -158,11 +159,11 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) attention_partial_kernel(cons
         }
         tc::commit(&ctl->bar_s);
     }
-    bool ok = mbar_wait_bounded(&ctl->bar_s, 0);
-    if (!ok) {
-        record_error(kErrAttnBarrierTimeout);
-        ctl->abort_flag = 1;
-    }
+    // every wait is short (the MMAs behind it take microseconds) and its outcome is made uniform over the CTA:
+    // the tensor-memory loads below are warp-collective
+    bool ok = mbar_wait_bounded(&ctl->bar_s, 0, kWaitCycles);
+    if (!ok) record_error(kErrAttnBarrierTimeout);
+    ok = __syncthreads_and(ok);
     tc::fence_after_thread_sync();
 
     // ---------------------------------------------------------------- softmax of this block, P -> shared memory
@@ -212,7 +213,7 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) attention_partial_kernel(cons
     tc::fence_after_thread_sync();
 
     // ---------------------------------------------------------------- O = P V
-    if (threadIdx.x == 0 && !ctl->abort_flag) {
+    if (threadIdx.x == 0 && ok) {
         const uint32_t idesc = make_idesc_bf16(P.dv, 1);  // B = V read MN-major
         const uint32_t p16 = smem_u32(sQ) >> 4, v16 = smem_u32(sV) >> 4;
         // MN-major, 128-byte swizzle: 64 columns of head_dim are contiguous, 8-key groups 1024 B apart
@@ -227,62 +228,55 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) attention_partial_kernel(cons
         }
         tc::commit(&ctl->bar_o);
     }
-    if (ok && !ctl->abort_flag) {
-        if (!mbar_wait_bounded(&ctl->bar_o, 0)) {
-            record_error(kErrAttnBarrierTimeout);
-            ok = false;
-        }
-    } else {
-        ok = false;
+    if (ok) {
+        ok = mbar_wait_bounded(&ctl->bar_o, 0, kWaitCycles);
+        if (!ok) record_error(kErrAttnBarrierTimeout);
     }
+    ok = __syncthreads_and(ok);
     tc::fence_after_thread_sync();
 
     // ---------------------------------------------------------------- write the rows
+    // The tensor-memory loads are warp-collective: every lane executes them, rows past the end of the matrix
+    // only skip the stores.
     const int grow = rt * kRows + row;
-    if (ok && grow < P.n_rows) {
-        if (P.key_tiles == 1) {
-            __nv_bfloat16* o = P.out + ga * P.o_stride[0] + gb * P.o_stride[1] + static_cast<size_t>(grow) * P.ldo;
-            const float inv = 1.0f / l;
-            for (int c0 = 0; c0 < P.dv; c0 += 16) {
-                uint32_t r[16];
-                asm volatile(
-                    "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-                    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
-                    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                      "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                    : "r"(lane_addr + kColO + c0)
-                    : "memory");
-                tc::tmem_ld_wait();
+    const bool store = grow < P.n_rows;
+    if (ok) {
+        const bool final_rows = P.key_tiles == 1;
+        __nv_bfloat16* o = P.out + ga * P.o_stride[0] + gb * P.o_stride[1] + static_cast<size_t>(store ? grow : 0) * P.ldo;
+        const size_t tile = (static_cast<size_t>(g) * P.row_tiles + rt) * P.key_tiles + kt;
+        float* po = P.part_o + (tile * kRows + row) * P.dv;
+        if (!final_rows && store) {
+            float* pml = P.part_ml + (tile * kRows + row) * 2;
+            pml[0] = m;
+            pml[1] = l;
+        }
+        const float inv = 1.0f / l;
+        for (int c0 = 0; c0 < P.dv; c0 += 16) {
+            uint32_t r[16];
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                  "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                : "r"(lane_addr + kColO + c0)
+                : "memory");
+            tc::tmem_ld_wait();
+            if (!store) continue;
+            if (final_rows) {
 #pragma unroll
                 for (int j = 0; j < 16; j += 8) {
                     if (c0 + j < P.head_dim) {            // head_dim is a multiple of 8
                         uint32_t w[4];
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            const __nv_bfloat162 b = __floats2bfloat162_rn(__uint_as_float(r[j + 2 * e]) * inv,
-                                                                           __uint_as_float(r[j + 2 * e + 1]) * inv);
-                            w[e] = *reinterpret_cast<const uint32_t*>(&b);
+                            const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(r[j + 2 * e]) * inv,
+                                                                            __uint_as_float(r[j + 2 * e + 1]) * inv);
+                            w[e] = *reinterpret_cast<const uint32_t*>(&b2);
                         }
                         *reinterpret_cast<uint4*>(o + c0 + j) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
                 }
-            }
-        } else {
-            const size_t tile = (static_cast<size_t>(g) * P.row_tiles + rt) * P.key_tiles + kt;
-            float* po = P.part_o + (tile * kRows + row) * P.dv;
-            float* pml = P.part_ml + (tile * kRows + row) * 2;
-            pml[0] = m;
-            pml[1] = l;
-            for (int c0 = 0; c0 < P.dv; c0 += 16) {
-                uint32_t r[16];
-                asm volatile(
-                    "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-                    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
-                    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                      "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                    : "r"(lane_addr + kColO + c0)
-                    : "memory");
-                tc::tmem_ld_wait();
+            } else {
 #pragma unroll
                 for (int j = 0; j < 16; j += 4) {
                     *reinterpret_cast<uint4*>(po + c0 + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
@@ -292,7 +286,7 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) attention_partial_kernel(cons
     }
     tc::fence_before_thread_sync();
     __syncthreads();
-    if (warp == 0) {
+    if (warp == 1) {
         tc::fence_after_thread_sync();
         tc::tmem_dealloc(tmem, kTmemColsAttn);
     }

@@ -79,7 +79,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 
 // Wait for a phase with a wall-clock bound (about a second at any SM clock).
 // Returns false when the bound ran out; the caller records an error and leaves.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, long long limit_cycles = 2000000000LL) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long start = clock64();
     while (true) {
@@ -87,7 +87,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
         for (int i = 0; i < 64; ++i) {
             if (mbar_try_wait(bar, parity)) return true;
         }
-        if (clock64() - start > 2000000000LL) return false;
+        if (clock64() - start > limit_cycles) return false;
     }
 }
 
