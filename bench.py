@@ -15,6 +15,13 @@ every step streams its weights from HBM, never from the 126 MB L2.
 `e2e` times the same pass through the Python API with HOST activations and results
 (pinned H2D / D2H copies inside the timed region).  N > 1 runs one independent replica per
 GPU (no collective on the data path); the barrier and max-over-ranks use NCCL.
+
+Besides the headline the JSON line carries `config1_int4_gemv` (the reference's own benchmark shape),
+`pi05_latency_ms` (1 / 3 / 10 denoise steps, host to host) and `serving` (a batch of independent requests
+split over the replicas), and `extras` with per-shape figures next to cuBLAS bf16 on the same shapes.
+
+`--case NAME` runs one bounded kernel case instead (what the ncu commands in profiles/ execute):
+gemm | gemm-nvfp4 | rowop | attention | pi05, with --iters launches inside cudaProfilerStart/Stop.
 """
 import argparse
 import json
@@ -271,6 +278,12 @@ def run_ours(args):
     extras = {}
     if rank == 0 and not args.no_extras:
         extras = run_extras(device, sets, x)
+    serving = None
+    if not args.no_extras and not args.no_serving:
+        try:
+            serving = run_serving(group, device)          # every rank takes part; rank 0 gets the figures
+        except Exception as e:                            # the headline must not depend on the side measurement
+            serving = {"error": f"{type(e).__name__}: {e}"}
     dev_err = _lib.load().tpb200_device_error(0)
 
     if rank == 0:
@@ -311,6 +324,10 @@ def run_ours(args):
             "gpu_launches": launches,
             "clocks": clocks,
             "device_error": dev_err,
+            "config1_int4_gemv": extras.get("w4a16_int4_rowmajor_g128_16384x2048"),
+            "pi05_latency_ms": {k.split("_")[2]: v["ms_median"] for k, v in extras.items()
+                                if k.startswith("pi05_e2e_") and isinstance(v, dict)} or None,
+            "serving": serving,
             "extras": extras,
         }
         print(json.dumps(line))
@@ -460,7 +477,12 @@ def run_extras(device, sets, x):
         t = time_launches(lambda i: ops.nvfp4_gemm(a, a_sf, bs[i % nb], b_sf[i % nb], M, N, K, alpha=1e-4, out=o), 16)
         flops = 2.0 * M * N * K
         bytes_ = M * K // 2 + M * K // 16 + N * K // 2 + N * K // 16 + M * N * 2
-        ex[f"nvfp4_gemm_{name}"] = {"us": t * 1e6, "tflops": flops / t / 1e12, "gbps": bytes_ / t / 1e9}
+        xb_ = torch.randn(M, K, device=device).to(torch.bfloat16)
+        wb_ = [(torch.randn(N, K, device=device) * 0.02).to(torch.bfloat16) for _ in range(2)]
+        tb = time_launches(lambda i: torch.nn.functional.linear(xb_, wb_[i % 2]), 16)
+        ex[f"nvfp4_gemm_{name}"] = {"us": t * 1e6, "tflops": flops / t / 1e12, "gbps": bytes_ / t / 1e9,
+                                    "cublas_bf16_us": tb * 1e6, "cublas_bf16_tflops": flops / tb / 1e12}
+        del wb_
         xq = torch.randn(M, K, device=device).to(torch.bfloat16)
         pk, sf = ops.nvfp4_quantize_act(xq)
         t = time_launches(lambda i: ops.nvfp4_quantize_act(xq, pk, sf), 16)
@@ -484,10 +506,49 @@ def run_extras(device, sets, x):
         ops.rowop(tlib.ROW_NONE, xq, K, q)
         t = time_launches(lambda i: lins[i % 2](q, o), 16)
         tq = time_launches(lambda i: ops.rowop(tlib.ROW_NONE, xq, K, q), 16)
+        # the library comparator on the same shape: torch F.linear in bf16 (cuBLAS), weights rotating too
+        wb = [(torch.randn(N, K, device=device) * 0.02).to(torch.bfloat16) for _ in range(2)]
+        tb = time_launches(lambda i: torch.nn.functional.linear(xq, wb[i % 2]), 16)
         ex[f"w4a16_tc_linear_{name}"] = {"gemm_us": t * 1e6, "quantise_us": tq * 1e6,
                                          "tflops": 2.0 * M * N * K / t / 1e12,
-                                         "tensor_tflops": 3 * 2.0 * M * N * K / t / 1e12}
-        del lins
+                                         "tensor_tflops": 3 * 2.0 * M * N * K / t / 1e12,
+                                         "cublas_bf16_us": tb * 1e6, "cublas_bf16_tflops": 2.0 * M * N * K / tb / 1e12}
+        del lins, wb
+    # (g2) attention on the tensor cores next to torch's scaled_dot_product_attention (library kernels)
+    import torch.nn.functional as F
+    for (rows, keys, name) in ((712 * 8, 712, "prefix_712x8_on_712"), (50 * 8, 762, "expert_50x8_on_762")):
+        qm = torch.randn(rows, 256, device=device).to(torch.bfloat16)
+        km = torch.randn(keys, 256, device=device).to(torch.bfloat16)
+        vm = torch.randn(keys, 256, device=device).to(torch.bfloat16)
+        om = torch.empty_like(qm)
+        ws = ops.attention_workspace(rows, keys, 256, 1, device)
+        t = time_launches(lambda i: ops.attention(qm, km, vm, om, 1 / 16, None, ws), 16)
+        q4 = qm.view(rows // 8, 8, 256).transpose(0, 1)[None]
+        ts = time_launches(lambda i: F.scaled_dot_product_attention(q4, km[None, None], vm[None, None], enable_gqa=True), 16)
+        ex[f"attention_{name}"] = {"us": t * 1e6, "torch_sdpa_us": ts * 1e6,
+                                   "tflops": 4.0 * rows * keys * 256 / t / 1e12}
+    # (g3) the drop-in module surface: NVFP4PackedMLP.forward on Gemma-2B's MLP, decode and prefix token counts
+    from turbopi_b200.nvfp4_packed import NVFP4PackedMLP
+
+    class _Mlp(torch.nn.Module):
+        def __init__(self, h, i):
+            super().__init__()
+            self.gate_proj = torch.nn.Linear(h, i, bias=False)
+            self.up_proj = torch.nn.Linear(h, i, bias=False)
+            self.down_proj = torch.nn.Linear(i, h, bias=False)
+
+    src = _Mlp(2048, 16384).to(device)
+    for prm in src.parameters():
+        prm.data.normal_(0, 0.02)
+    mlp = NVFP4PackedMLP.from_gemma_mlp(src, gate_activation="gelu", fmt="nvfp4")
+    del src
+    for T in (1, 712):
+        xm = torch.randn(T, 2048, device=device).to(torch.bfloat16)
+        with torch.no_grad():
+            t = time_launches(lambda i: mlp(xm), 8)
+        ex[f"nvfp4_packed_mlp_forward_gemma2b_M{T}"] = {"us": t * 1e6, "weight_bytes": 3 * 2048 * 16384 * 9 // 16,
+                                                        "gbps": 3 * 2048 * 16384 * 9 / 16 / t / 1e9}
+    del mlp
     # (h) the whole Pi0.5-shaped inference (SigLIP-So400m/14 on 2 images, 712-token Gemma-2B prefix with the
     # fused QKV + RoPE + KV-cache append, Gemma-300M action expert, Euler steps) as ONE CUDA graph:
     # pinned host images / tokens / noise in, actions back on the host, random-init weights
@@ -517,6 +578,112 @@ def run_extras(device, sets, x):
                            "(its published figures, other hardware): 83.5 ms / 1 step, 102.8 ms / 3 steps, 171.4 ms / 10 steps")
     del model
     return ex
+
+
+# ------------------------------------------------------------------------------------------ serving
+def run_serving(group, device, steps=10):
+    """Batches of 8 and 64 independent Pi0.5 requests split over the replicas (contiguous chunks, one
+    captured graph per GPU, results gathered on the host of rank 0; no collective on the data path):
+    requests/s and p50 / p99 request latency."""
+    from turbopi_b200.pi05 import Pi05, Pi05Config
+    from turbopi_b200.policy import Pi05Policy
+    from turbopi_b200.replicas import RequestDispatcher
+    cfg = Pi05Config()
+    policy = Pi05Policy(Pi05(cfg, device, seed=0), None, None, num_denoising_steps=steps)
+    rng = np.random.default_rng(3)
+
+    def request(i):
+        return {"observation/image": rng.integers(0, 256, (cfg.image_size, cfg.image_size, 3), dtype=np.uint8),
+                "observation/wrist_image": rng.integers(0, 256, (cfg.image_size, cfg.image_size, 3), dtype=np.uint8),
+                "observation/state": rng.normal(size=8).astype(np.float32),
+                "prompt": [2] + rng.integers(3, cfg.vocab, 12 + i % 20).tolist(), "noise": None}
+
+    policy.warmup(2)
+    disp = RequestDispatcher(group, lambda r: policy.infer(r)["actions"], timeout_s=120.0)
+    out = {"denoise_steps": steps, "replicas": group.world}
+    for batch in (8, 64):
+        reqs = [request(i) for i in range(batch)]
+        group.barrier()
+        results, stats = disp.serve(reqs)
+        group.barrier()
+        if group.rank == 0:
+            out[f"batch_{batch}"] = {"requests_per_s": stats["requests_per_s"], "p50_ms": stats["p50_ms"],
+                                     "p99_ms": stats["p99_ms"], "wall_s": stats["wall_s"], "requeued": len(stats["requeued"]),
+                                     "finite": bool(all(np.isfinite(r).all() for r in results))}
+    del policy
+    return out if group.rank == 0 else None
+
+
+# ------------------------------------------------------------------------------------------ profiling cases
+def run_case(args):
+    """One bounded kernel case for ncu (`--profile-from-start off` sees exactly the --iters launches)."""
+    from turbopi_b200 import _lib as tlib, ops
+    from turbopi_b200.pi05 import Pi05, Pi05Config, TcLinear
+    dev = torch.device("cuda:0")
+    g = torch.Generator(device=dev).manual_seed(0)
+
+    def timed(fn, iters, warm=2):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.profiler.start()
+        a.record()
+        for _ in range(iters):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        return a.elapsed_time(b) / iters
+
+    M, N, K = args.M, args.N, args.K
+    if args.case == "gemm":            # weight-only linear: activation-piece quantiser + tiled tcgen05 GEMM
+        x = torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16)
+        lin = TcLinear.from_weight(torch.randn(N, K, device=dev, generator=g) * 0.02)
+        lin.ws = ops.gemm_workspace(dev)
+        q = ops.QuantBuf(M, K, args.pieces, dev)
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+
+        def step():
+            ops.rowop(tlib.ROW_NONE, x, K, q)
+            lin(q, out)
+        ms = timed(step, args.iters)
+        print(f"gemm M={M} N={N} K={K} pieces={args.pieces}: {ms * 1e3:.1f} us per quantise+GEMM, "
+              f"{2.0 * M * N * K / (ms * 1e-3) / 1e12:.0f} TFLOP/s useful")
+    elif args.case == "gemm-nvfp4":    # e2m1 x e2m1, row-major operands
+        pitch = ops.packed_pitch(K)
+        a = torch.randint(0, 256, (M, pitch), device=dev, dtype=torch.uint8)
+        a_sf = torch.randint(40, 120, (ops.nvfp4_sf_bytes(M, K),), device=dev, dtype=torch.uint8)
+        b = torch.randint(0, 256, (N, pitch), device=dev, dtype=torch.uint8)
+        b_sf = torch.randint(40, 120, (ops.nvfp4_sf_bytes(N, K),), device=dev, dtype=torch.uint8)
+        o = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+        ms = timed(lambda: ops.nvfp4_gemm(a, a_sf, b, b_sf, M, N, K, alpha=1e-4, out=o), args.iters)
+        print(f"gemm-nvfp4 M={M} N={N} K={K}: {ms * 1e3:.1f} us, {2.0 * M * N * K / (ms * 1e-3) / 1e12:.0f} TFLOP/s")
+    elif args.case == "rowop":
+        x = torch.randn(M, 2 * K, device=dev, generator=g).to(torch.bfloat16)
+        q = ops.QuantBuf(M, K, args.pieces, dev)
+        ms = timed(lambda: ops.rowop(tlib.ROW_GELU_MUL, x, K, q), args.iters)
+        print(f"rowop GELU*up + 3-piece quantiser M={M} K={K}: {ms * 1e3:.1f} us")
+    elif args.case == "attention":
+        rows, keys = args.M, args.N
+        qm = torch.randn(rows, 256, device=dev, generator=g).to(torch.bfloat16)
+        km = torch.randn(keys, 256, device=dev, generator=g).to(torch.bfloat16)
+        vm = torch.randn(keys, 256, device=dev, generator=g).to(torch.bfloat16)
+        o = torch.empty_like(qm)
+        ws = ops.attention_workspace(rows, keys, 256, 1, dev)
+        ms = timed(lambda: ops.attention(qm, km, vm, o, 1 / 16, None, ws), args.iters)
+        print(f"attention rows={rows} keys={keys} d=256: {ms * 1e3:.1f} us per call (partial + combine)")
+    elif args.case == "pi05":
+        cfg = Pi05Config()
+        model = Pi05(cfg, dev, seed=0)
+        gen = torch.Generator().manual_seed(1)
+        images = torch.randint(0, 256, (cfg.num_images, cfg.image_size, cfg.image_size, 3), generator=gen, dtype=torch.uint8)
+        tokens = torch.randint(0, cfg.vocab, (cfg.text_len,), generator=gen)
+        noise = torch.randn(cfg.action_horizon, cfg.action_dim, generator=gen)
+        with torch.no_grad():
+            ms = timed(lambda: model.infer(images, tokens, noise, args.denoise_steps, use_graph=False), args.iters, warm=1)
+        print(f"pi05 {args.denoise_steps} denoise step(s), eager launches: {ms:.2f} ms per inference")
+    print("device_error", tlib.load().tpb200_device_error(0))
 
 
 # ------------------------------------------------------------------------------------------ CPU arms
@@ -568,7 +735,7 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    n_layers = 2
+    n_layers = LAYERS                 # the same 54 matrices per step as the GPU arm
     bytes_ = n_layers * sum(algorithmic_bytes(n, k) for n, k in SHAPES)
     cpu_time_layers(n_layers, max(1, min(args.warmup, 3)))
     steps = args.steps
@@ -583,13 +750,15 @@ def run_reference(args):
     total = float(sum(times))
     value = bytes_ * done / total / 1e9
     cpu = {"value": value, "unit": UNIT, "cores": os.cpu_count(), "kind": "port",
-           "sample": f"each step = {n_layers} of 18 layers (6 matrices) of the same workload; torch CPU restatement "
-                     "of NVFP4PackedLinear._forward_dequant_gemm, all host threads"}
+           "sample": f"each step = all {n_layers} layers (54 matrices) of the same workload, as many of the requested steps "
+                     f"as fit {budget_s:.0f} s; torch CPU restatement of NVFP4PackedLinear._forward_dequant_gemm "
+                     "(dequantise per call + F.linear, fp32), all host threads"}
     line = {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": int(args.gpus),
             "steps": done, "steps_requested": steps, "warmup": args.warmup, "ms_per_step": total / done * 1e3,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "NVFP4 weight-only GEMV, M=1, Gemma-300M action-expert MLP (bounded sample: "
-                                   f"{n_layers} layers per step)", "parallelism": "host CPU, rank 0 only"},
+            "config": {"workload": "NVFP4 weight-only GEMV, M=1, Gemma-300M action-expert MLP, 18 layers x "
+                                   "(gate,up 1024->4096; down 4096->1024) = 54 matrices per step, E4M3 block-16 "
+                                   "scales + fp32 global scale", "parallelism": "host CPU, rank 0 only"},
             "cpu_baseline": cpu,
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
@@ -609,6 +778,15 @@ def main():
                     help="--path tc: stand-alone activation quantiser launch + GEMV instead of the fused launch")
     ap.add_argument("--no-pdl", action="store_true",
                     help="--path tc: no programmatic dependent launch between quantiser and GEMV")
+    ap.add_argument("--no-serving", action="store_true", help="skip the request-serving measurement (builds a full model)")
+    ap.add_argument("--case", default=None, choices=["gemm", "gemm-nvfp4", "rowop", "attention", "pi05"],
+                    help="run one bounded kernel case (for ncu) instead of the benchmark")
+    ap.add_argument("--M", type=int, default=712)
+    ap.add_argument("--N", type=int, default=32768)
+    ap.add_argument("--K", type=int, default=2048)
+    ap.add_argument("--pieces", type=int, default=3)
+    ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--denoise-steps", type=int, default=1)
     ap.add_argument("--no-clock-warmup", action="store_true",
                     help="do exactly W warm-up steps (profiling runs); by default warm-up lasts >= 0.4 s")
     args = ap.parse_args()
@@ -617,7 +795,10 @@ def main():
     else:
         if not torch.cuda.is_available():
             raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU fallback")
-        run_ours(args)
+        if args.case is not None:
+            run_case(args)
+        else:
+            run_ours(args)
 
 
 if __name__ == "__main__":

@@ -1,0 +1,59 @@
+#!/usr/bin/env python3
+"""Compile the reference's own plugin kernels, from the sources where they lie, into oracle/_ref/.
+
+    python oracle/build_ref.py <reference-root>      (default: $TURBOPI_REFERENCE, else /root/reference)
+
+Test infrastructure: the shared objects are used only by the `-m gpu` parity tests, as the checker for the
+plugin quantisers (quantizeWeightToINT4 / dequantizeINT4ToBF16 of openpi/w4a16_plugin/src/w4a16_gemm_kernel.cu,
+quantizeActivationToFP8 / quantizeWeightToNVFP4 of openpi/w4a8_plugin/src/w4a8_gemm_kernel.cu).  Each file is one
+translation unit built with nvcc against the CUTLASS headers the reference vendors
+(openpi/external/cutlass_nvfp4_build/include); nothing of the reference's own build system runs and no source
+is copied.  Only the plain-CUDA quantiser entry points are ever called: the files' CUTLASS GEMMs use thread-block
+clusters tuned for another chip and stay untouched.  Outputs are git-ignored; an up-to-date output is kept.
+"""
+import os
+import shutil
+import subprocess
+import sys
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+OUT = HERE / "_ref"
+UNITS = {
+    "libref_w4a16.so": "openpi/w4a16_plugin/src/w4a16_gemm_kernel.cu",
+    "libref_w4a8.so": "openpi/w4a8_plugin/src/w4a8_gemm_kernel.cu",
+}
+
+
+def build(ref_root=None, verbose=True):
+    ref = Path(ref_root or os.environ.get("TURBOPI_REFERENCE", "/root/reference"))
+    if not ref.exists():
+        if verbose:
+            print(f"[oracle/build_ref] {ref} not present: keeping whatever oracle/_ref/ already holds")
+        return []
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    inc = ref / "openpi" / "external" / "cutlass_nvfp4_build"
+    OUT.mkdir(exist_ok=True)
+    built = []
+    for name, rel in UNITS.items():
+        src, dst = ref / rel, OUT / name
+        if dst.exists() and dst.stat().st_mtime > src.stat().st_mtime:
+            built.append(dst)
+            continue
+        cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O2", "-std=c++17", "-Xcompiler", "-fPIC",
+               "--expt-relaxed-constexpr", "-shared", "-cudart", "shared", "-I", str(inc / "include"),
+               "-I", str(inc / "tools" / "util" / "include"), "-o", str(dst), str(src)]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        (OUT / (name + ".log")).write_text(r.stdout + r.stderr)
+        if r.returncode != 0:
+            if verbose:
+                print(f"[oracle/build_ref] {rel} does not build here (see oracle/_ref/{name}.log); its quantisers stay unpinned")
+            continue
+        built.append(dst)
+        if verbose:
+            print(f"[oracle/build_ref] built {dst}")
+    return built
+
+
+if __name__ == "__main__":
+    build(sys.argv[1] if len(sys.argv) > 1 else None)

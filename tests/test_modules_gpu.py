@@ -33,6 +33,7 @@ def _dequant(layer):
                           float(layer.global_scale), scale_is_e4m3=True)
 
 
+@torch.no_grad()
 @pytest.mark.parametrize("T", [1, 4, 16, 50, 712])
 @pytest.mark.parametrize("act", ["none", "gelu"])
 def test_nvfp4_packed_linear_dispatches_to_tensor_cores(cuda_device, T, act):
@@ -81,6 +82,7 @@ def _mlp_reference(mlp, x, act):
     return r(r(r(a) * up) @ wd.t())
 
 
+@torch.no_grad()
 @pytest.mark.parametrize("T", [1, 16, 712])
 @pytest.mark.parametrize("act", ["gelu", "silu"])
 def test_nvfp4_packed_mlp_runs_gate_and_up_as_one_launch(cuda_device, T, act):
@@ -104,6 +106,7 @@ def test_nvfp4_packed_mlp_runs_gate_and_up_as_one_launch(cuda_device, T, act):
         assert len(weight_passes) == 2, names                         # gate+up together, then down
 
 
+@torch.no_grad()
 def test_replace_mlp_with_nvfp4_packed_on_a_gemma_shaped_model(cuda_device):
     """The drop-in call of the reference: every layer's MLP replaced, outputs close to the fp32 module."""
     from turbopi_b200.nvfp4_packed import NVFP4PackedMLP, replace_mlp_with_nvfp4_packed

@@ -172,37 +172,37 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) attention_partial_kernel(cons
     float m = -3.0e38f;
     float l = 0.0f;
     if (ok) {
-        // pass 1: row maximum of scale * s + bias
+        // the row's 128 scores: four tensor-memory loads in flight, one wait
+        uint32_t r[4][32];
 #pragma unroll
-        for (int c0 = 0; c0 < kKeys; c0 += 32) {
-            uint32_t r[32];
-            tc::tmem_ld_32x32b_x32(lane_addr + kColS + c0, r);
-            tc::tmem_ld_wait();
+        for (int c = 0; c < 4; ++c) tc::tmem_ld_32x32b_x32(lane_addr + kColS + c * 32, r[c]);
+        tc::tmem_ld_wait();
+        float t[4][32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) m = fmaxf(m, fmaf(__uint_as_float(r[j]), P.scale, ctl->bias[c0 + j]));
+        for (int c = 0; c < 4; ++c) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+                t[c][j] = fmaf(__uint_as_float(r[c][j]), P.scale, ctl->bias[c * 32 + j]);
+                m = fmaxf(m, t[c][j]);
+            }
         }
-        // pass 2: p = exp(t - m) rounded to bf16 (what the PyTorch path feeds its second matmul), row sum of
-        // the rounded values, 16-byte stores into the K-major image of P
+        // p = exp(t - m) rounded to bf16 (what the PyTorch path feeds its second matmul), row sum of the
+        // rounded values, 16-byte stores into the K-major image of P
         uint8_t* sP = sQ;
 #pragma unroll
-        for (int c0 = 0; c0 < kKeys; c0 += 32) {
-            uint32_t r[32];
-            tc::tmem_ld_32x32b_x32(lane_addr + kColS + c0, r);
-            tc::tmem_ld_wait();
+        for (int c = 0; c < 4; ++c) {
 #pragma unroll
             for (int j8 = 0; j8 < 4; ++j8) {
                 uint32_t w[4];
 #pragma unroll
                 for (int j2 = 0; j2 < 4; ++j2) {
                     const int j = j8 * 8 + j2 * 2;
-                    const float t0 = fmaf(__uint_as_float(r[j]), P.scale, ctl->bias[c0 + j]);
-                    const float t1 = fmaf(__uint_as_float(r[j + 1]), P.scale, ctl->bias[c0 + j + 1]);
-                    const __nv_bfloat162 pb = __floats2bfloat162_rn(__expf(t0 - m), __expf(t1 - m));
+                    const __nv_bfloat162 pb = __floats2bfloat162_rn(__expf(t[c][j] - m), __expf(t[c][j + 1] - m));
                     l += __bfloat162float(pb.x) + __bfloat162float(pb.y);
                     w[j2] = *reinterpret_cast<const uint32_t*>(&pb);
                 }
-                const int c = (c0 >> 3) + j8;             // 16-byte chunk of the 128-key row: 0..15
-                uint8_t* dst = sP + (c >> 3) * kChunkBytes + row * 128 + (((c & 7) ^ (row & 7)) << 4);
+                const int ch = c * 4 + j8;                // 16-byte chunk of the 128-key row: 0..15
+                uint8_t* dst = sP + (ch >> 3) * kChunkBytes + row * 128 + (((ch & 7) ^ (row & 7)) << 4);
                 *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
             }
         }
@@ -251,35 +251,48 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) attention_partial_kernel(cons
             pml[1] = l;
         }
         const float inv = 1.0f / l;
-        for (int c0 = 0; c0 < P.dv; c0 += 16) {
-            uint32_t r[16];
-            asm volatile(
-                "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
-                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                  "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                : "r"(lane_addr + kColO + c0)
-                : "memory");
+        for (int c64 = 0; c64 < P.dv; c64 += 64) {
+            // up to four 16-column loads in flight, one wait
+            uint32_t r4[4][16];
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+                if (c64 + q4 * 16 < P.dv) {
+                    asm volatile(
+                        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+                        : "=r"(r4[q4][0]), "=r"(r4[q4][1]), "=r"(r4[q4][2]), "=r"(r4[q4][3]), "=r"(r4[q4][4]), "=r"(r4[q4][5]),
+                          "=r"(r4[q4][6]), "=r"(r4[q4][7]), "=r"(r4[q4][8]), "=r"(r4[q4][9]), "=r"(r4[q4][10]),
+                          "=r"(r4[q4][11]), "=r"(r4[q4][12]), "=r"(r4[q4][13]), "=r"(r4[q4][14]), "=r"(r4[q4][15])
+                        : "r"(lane_addr + kColO + c64 + q4 * 16)
+                        : "memory");
+                }
+            }
             tc::tmem_ld_wait();
             if (!store) continue;
-            if (final_rows) {
 #pragma unroll
-                for (int j = 0; j < 16; j += 8) {
-                    if (c0 + j < P.head_dim) {            // head_dim is a multiple of 8
-                        uint32_t w[4];
+            for (int q4 = 0; q4 < 4; ++q4) {
+                const int c0 = c64 + q4 * 16;
+                if (c0 >= P.dv) continue;
+                const uint32_t(&r)[16] = r4[q4];
+                if (final_rows) {
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(r[j + 2 * e]) * inv,
-                                                                            __uint_as_float(r[j + 2 * e + 1]) * inv);
-                            w[e] = *reinterpret_cast<const uint32_t*>(&b2);
+                    for (int j = 0; j < 16; j += 8) {
+                        if (c0 + j < P.head_dim) {            // head_dim is a multiple of 8
+                            uint32_t w[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(r[j + 2 * e]) * inv,
+                                                                                __uint_as_float(r[j + 2 * e + 1]) * inv);
+                                w[e] = *reinterpret_cast<const uint32_t*>(&b2);
+                            }
+                            *reinterpret_cast<uint4*>(o + c0 + j) = make_uint4(w[0], w[1], w[2], w[3]);
                         }
-                        *reinterpret_cast<uint4*>(o + c0 + j) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
-                }
-            } else {
+                } else {
 #pragma unroll
-                for (int j = 0; j < 16; j += 4) {
-                    *reinterpret_cast<uint4*>(po + c0 + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+                    for (int j = 0; j < 16; j += 4) {
+                        *reinterpret_cast<uint4*>(po + c0 + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+                    }
                 }
             }
         }
