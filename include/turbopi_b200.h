@@ -59,7 +59,8 @@ enum { TPB200_SCALE_F32 = 0, TPB200_SCALE_E4M3 = 1, TPB200_SCALE_F16 = 2, TPB200
 enum {
     TPB200_INT4_KBLOCK = 0,  /* (K/32, N, 4) int32 + (K/32, N) fp16 scales: W4A16Packer's order,
                                 openpi/src/openpi/utils/w4a16_packer.py:129-174 */
-    TPB200_INT4_ROWMAJOR = 1 /* (N, K/8) int32 + (N, K/group) scales, 8 codes per word along K */
+    TPB200_INT4_ROWMAJOR = 1, /* (N, K/8) int32 + (N, K/group) scales, 8 codes per word along K */
+    TPB200_INT4_PLUGIN = 2    /* signed nibbles [N, K/2] bytes + bf16 scale / optional zero per 128: the w4a16 plugin's format */
 };
 
 /* launch flags */
@@ -90,6 +91,18 @@ int tpb200_device_error(int clear);
 int tpb200_w4a16_gemv(const void* x, int x_dtype, const void* weight_packed, const void* scales,
                       int scale_dtype, const void* bias, int bias_dtype, void* out, int out_dtype, int M,
                       int N, int K, int group_size, int layout, int flags, tpb200_stream_t stream);
+
+/* W4A16 GEMM for more than 16 tokens on the tensor cores: INT4 weights are dequantised to bf16 on their way
+ * into shared memory (once per CTA and K stage, shared by up to 384 token rows) and multiplied by tcgen05.mma
+ * kind::f16; fp32 accumulation.  out = alpha * x @ dequant(W)^T + bias + beta * out.
+ *   layout TPB200_INT4_PLUGIN: w = q * scale + zero, the operands of w4a16GemmForward
+ *          (openpi/w4a16_plugin/src/w4a16_gemm_kernel.cu:54-153,336-406 is the reference's mixed-input GEMM);
+ *   layout TPB200_INT4_KBLOCK: W4A16Linear's buffers, w = (q - 8) * scale (fp16, per 32; `zeros` must be NULL),
+ *          replacing its dequantise + F.linear branch (openpi/src/openpi/modules/w4a16_linear.py:256-268).
+ * x bf16 [M, K] contiguous, K % 128 == 0, N % 8 == 0, ldo = row stride of out in elements (0 = N). */
+int tpb200_w4a16_gemm(const void* x, const void* weight, const void* scales, const void* zeros, const void* bias,
+                      int bias_dtype, void* out, int out_dtype, int M, int N, int K, int ldo, int layout, float alpha,
+                      float beta, int flags, tpb200_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------
  * NVFP4 weight-only GEMV/GEMM for decode shapes (M <= 16).
@@ -337,8 +350,9 @@ void dequantizeINT4ToBF16(const int8_t* input_packed, const void* scales_bf16, c
                           void* output_bf16, int N, int K, int group_size, tpb200_stream_t stream);
 
 /* openpi/w4a16_plugin/src/w4a16_gemm_plugin.h:41-59: out bf16 [M,N] = alpha * act bf16 [M,K] @ dequant(W)^T + beta * out,
- * W signed int4 [N, K/2], bf16 scales and optional zero points [N, K/128] (q * scale + zero).  Any M (the
- * decode kernel runs 16 rows per launch).  The workspace is only used with zero points or beta != 0. */
+ * W signed int4 [N, K/2], bf16 scales and optional zero points [N, K/128] (q * scale + zero).  Up to 16 rows run
+ * on the decode GEMV (workspace only with zero points or beta != 0), more rows on the tensor-core GEMM of
+ * tpb200_w4a16_gemm (no workspace). */
 void w4a16GemmForward(const void* activation, const void* weight_packed, const void* weight_scale,
                       const void* weight_zero, void* output, int M, int N, int K, float alpha, float beta,
                       void* workspace, size_t workspaceSize, tpb200_stream_t stream);

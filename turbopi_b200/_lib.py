@@ -13,7 +13,7 @@ LIB_PATH = Path(__file__).resolve().parent / "lib" / "libturbopi_b200.so"
 F32, F16, BF16 = 0, 1, 2
 ACT_NONE, ACT_GELU, ACT_SILU, ACT_GEGLU = 0, 1, 2, 3
 SCALE_F32, SCALE_E4M3, SCALE_F16, SCALE_BF16 = 0, 1, 2, 3
-INT4_KBLOCK, INT4_ROWMAJOR = 0, 1
+INT4_KBLOCK, INT4_ROWMAJOR, INT4_PLUGIN = 0, 1, 2
 FLAG_NONE, FLAG_PDL = 0, 1
 MAX_GROUP = 64
 
@@ -119,6 +119,8 @@ SIGNATURES = {
                                           ctypes.POINTER(GemvTcPlanInfo)]),
     "tpb200_attention_workspace_size": (c_size_t, [c_int, c_int, c_int, c_int]),
     "tpb200_attention": (c_int, [ctypes.POINTER(AttentionArgs), c_void_p]),
+    "tpb200_w4a16_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int,
+                                  c_int, c_int, c_int, c_float, c_float, c_int, c_void_p]),
     "tpb200_row_transform_quantize": (c_int, [ctypes.POINTER(RowOpArgs), c_void_p]),
     "tpb200_nvfp4_gemv_tc_static_capacity": (c_size_t, []),
     "tpb200_nvfp4_gemv_tc_static": (c_int, [ctypes.POINTER(GemvTcProblem), c_int, c_int, c_int, c_int, c_int, c_int,

@@ -8,6 +8,12 @@
 #include "common.cuh"
 
 namespace tpb {
+int w4a16_gemm_tc_launch(int format, const void* x, const void* w, const void* scale, const void* zero, const void* bias,
+                         int bias_dtype, void* out, int out_dtype, int M, int N, int K, int ldo, float alpha, float beta,
+                         int flags, cudaStream_t stream);
+}
+
+namespace tpb {
 
 int gemv_rowmajor_single(int fmt_is_u4, const void* x, int x_dtype, const void* x_scales, const void* w,
                          const void* scales, int scale_dtype, int group, float global_scale, const void* bias,
@@ -64,6 +70,13 @@ extern "C" void w4a16GemmForward(const void* activation, const void* weight_pack
     const int G = K / tpb::kW4A16Group;
     if (!activation || !weight_packed || !weight_scale || !output) return tpb::set_last_error(TPB200_ERR_NULL);
     if (M < 1 || N < 1 || K < tpb::kW4A16Group || K % tpb::kW4A16Group != 0) return tpb::set_last_error(TPB200_ERR_SHAPE);
+    if (M > 16) {
+        // prefill-sized: one tensor-core launch (zero points, alpha and beta in its epilogue; no workspace)
+        const int st = tpb::w4a16_gemm_tc_launch(0, activation, weight_packed, weight_scale, weight_zero, nullptr, TPB200_F32,
+                                                 output, TPB200_BF16, M, N, K, N, alpha, beta, TPB200_FLAG_NONE, stream);
+        tpb::set_last_error(st);
+        return;
+    }
     const bool extra = (weight_zero != nullptr) || (beta != 0.0f);
     float* acc = nullptr;
     float* xsum = nullptr;

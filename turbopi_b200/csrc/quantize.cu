@@ -167,6 +167,7 @@ int device_error_w4a16_kblock(int clear);
 int device_error_nvfp4_gemm(int clear);
 int device_error_gemv_tc(int clear);
 int device_error_attention(int clear);
+int device_error_w4a16_gemm_tc(int clear);
 
 }  // namespace tpb
 
@@ -198,7 +199,7 @@ int tpb200_device_error(int clear) {
     if (cudaDeviceSynchronize() != cudaSuccess) return TPB200_ERR_CUDA;
     int (*const readers[])(int) = {tpb::device_error_gemv_rowmajor, tpb::device_error_w4a16_kblock,
                                      tpb::device_error_nvfp4_gemm, tpb::device_error_gemv_tc,
-                                     tpb::device_error_attention};
+                                     tpb::device_error_attention, tpb::device_error_w4a16_gemm_tc};
     int first = 0;
     for (auto r : readers) {
         const int v = r(clear);

@@ -15,7 +15,7 @@ import ctypes
 import torch
 
 from . import _lib
-from ._lib import (ACT_NONE, BF16, F16, F32, FLAG_NONE, FLAG_PDL, INT4_KBLOCK, INT4_ROWMAJOR, SCALE_E4M3,
+from ._lib import (ACT_NONE, BF16, F16, F32, FLAG_NONE, FLAG_PDL, INT4_KBLOCK, INT4_PLUGIN, INT4_ROWMAJOR, SCALE_E4M3,
                    SCALE_F16, SCALE_BF16, SCALE_F32, TurboPiError)
 
 _DTYPES = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}
@@ -82,6 +82,27 @@ def w4a16_gemv(input, weight_packed, scales):
         raise TurboPiError(f"shape mismatch: input {tuple(input.shape)}, weight_packed {tuple(weight_packed.shape)}")
     out = torch.empty((input.size(0), N), dtype=torch.float32, device=input.device)
     return w4a16_gemv_out(input.contiguous(), weight_packed.contiguous(), scales.contiguous(), out)
+
+
+def w4a16_gemm(x, weight, scales, zeros=None, bias=None, out=None, layout=INT4_KBLOCK, alpha=1.0, beta=0.0,
+               out_dtype=torch.bfloat16):
+    """out[M, N] = alpha * x @ dequant(W)^T + bias + beta * out for any M on the tensor cores (INT4 weights
+    dequantised to bf16 inside the kernel).  layout INT4_KBLOCK: weight (K/32, N, 4) int32 + fp16 scales
+    (K/32, N); INT4_PLUGIN: weight [N, K/2] int8 + bf16 scales / zeros [N, K/128].  x is converted to bf16."""
+    _cuda(x, weight, scales, zeros, bias, out)
+    M, K = x.shape
+    N = weight.shape[1] if layout == INT4_KBLOCK else weight.shape[0]
+    xb = x.to(torch.bfloat16).contiguous()
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    if bias is not None:
+        bias = bias.float().contiguous()
+    with torch.cuda.device(x.device):
+        st = _lib.load().tpb200_w4a16_gemm(_ptr(xb), _ptr(weight), _ptr(scales), _ptr(zeros), _ptr(bias), F32, _ptr(out),
+                                           _dt(out), M, N, K, out.stride(0), int(layout), float(alpha), float(beta),
+                                           _launch_flags, _stream(x))
+    _lib.check(st, "tpb200_w4a16_gemm")
+    return out
 
 
 # ------------------------------------------------------------------------------------- NVFP4

@@ -120,8 +120,11 @@ class W4A16Linear(nn.Module):
     """nn.Linear replacement with INT4 weights.
 
     Buffers: weight_packed (K/32, N, 4) int32, scales (K/32, N) fp16 -- the reference's state-dict
-    format.  forward() runs the INT4 kernel for any number of tokens (16 per launch); unlike the
-    reference there is no dequantise-and-F.linear path, so a CUDA device is required.
+    format.  forward() dispatches on the token count: up to 16 tokens run on the decode GEMV, more on
+    the tensor-core GEMM that dequantises the same buffers to bf16 inside the kernel (one launch for any
+    number of tokens; needs in_features % 128 == 0 and out_features % 8 == 0, otherwise the GEMV runs 16
+    rows at a time).  Unlike the reference there is no dequantise-and-F.linear path, so a CUDA device
+    is required.
     """
 
     __constants__ = ["in_features", "out_features"]
@@ -161,6 +164,9 @@ class W4A16Linear(nn.Module):
         bias = None if self.bias is None else self.bias.detach().contiguous()
         if bias is not None and bias.dtype not in (torch.float16, torch.bfloat16, torch.float32):
             bias = bias.float()
+        if T > 16 and K % 128 == 0 and self.out_features % 8 == 0:
+            ops.w4a16_gemm(x, self.weight_packed, self.scales, None, bias, out, INT4_KBLOCK)
+            return out.reshape(*batch_dims, self.out_features)
         for t0 in range(0, T, 16):
             t1 = min(T, t0 + 16)
             ops.w4a16_gemv_out(x[t0:t1], self.weight_packed, self.scales, out[t0:t1], bias, 32, INT4_KBLOCK)
