@@ -514,6 +514,19 @@ def run_extras(device, sets, x):
                                          "tensor_tflops": 3 * 2.0 * M * N * K / t / 1e12,
                                          "cublas_bf16_us": tb * 1e6, "cublas_bf16_tflops": 2.0 * M * N * K / tb / 1e12}
         del lins, wb
+    # (g1) INT4 x bf16 GEMM on the tensor cores (w4a16GemmForward's operands) at the prefix shape, next to cuBLAS bf16
+    for (M, N, K, name) in ((712, 16384, 2048, "gemma2b_gateup_M712"), (712, 2048, 16384, "gemma2b_down_M712"),
+                            (64, 16384, 2048, "gemma2b_gateup_M64")):
+        xq = torch.randn(M, K, device=device).to(torch.bfloat16)
+        wq = [torch.randint(-128, 128, (N, K // 2), device=device, dtype=torch.int8) for _ in range(2)]
+        sq = (torch.rand(N, K // 128, device=device) * 0.01 + 0.002).to(torch.bfloat16)
+        o = torch.empty((M, N), dtype=torch.bfloat16, device=device)
+        t = time_launches(lambda i: ops.w4a16_gemm(xq, wq[i % 2], sq, None, None, o, tlib.INT4_PLUGIN), 16)
+        wb = [(torch.randn(N, K, device=device) * 0.02).to(torch.bfloat16) for _ in range(2)]
+        tb = time_launches(lambda i: torch.nn.functional.linear(xq, wb[i % 2]), 16)
+        ex[f"w4a16_int4_tc_gemm_{name}"] = {"us": t * 1e6, "tflops": 2.0 * M * N * K / t / 1e12, "cublas_bf16_us": tb * 1e6,
+                                            "cublas_bf16_tflops": 2.0 * M * N * K / tb / 1e12}
+        del wq, wb
     # (g2) attention on the tensor cores next to torch's scaled_dot_product_attention (library kernels)
     import torch.nn.functional as F
     for (rows, keys, name) in ((712 * 8, 712, "prefix_712x8_on_712"), (50 * 8, 762, "expert_50x8_on_762")):

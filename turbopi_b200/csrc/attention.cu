@@ -90,9 +90,11 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wai
 
 // rows [row0, row0 + 128) of a [n, d] bf16 matrix (row stride ld elements) -> the swizzled image at `dst`
 __device__ __forceinline__ void load_tile(uint8_t* dst, const __nv_bfloat16* src, int ld, int row0, int n, int d, int dpad) {
-    const int cpr = dpad >> 3;                  // 16-byte chunks per row
+    const int cpr = dpad >> 3;                  // 16-byte chunks per row: 8, 16, 24 or 32
+    const int sh = dpad == 64 ? 3 : (dpad == 128 ? 4 : 5);
+    const bool pow2 = dpad != 192;
     for (int idx = threadIdx.x; idx < kRows * cpr; idx += kThreadsAttn) {
-        const int r = idx / cpr;
+        const int r = pow2 ? (idx >> sh) : idx / cpr;
         const int c = idx - r * cpr;
         const bool valid = (row0 + r < n) && (c * 8 < d);
         const __nv_bfloat16* g = valid ? src + static_cast<size_t>(row0 + r) * ld + c * 8 : src;
@@ -463,10 +465,10 @@ extern "C" int tpb200_attention(const tpb200_attention_args* a, tpb200_stream_t 
         c2.gridDim = dim3(static_cast<unsigned>((threads + 255) / 256), 1, 1);
         c2.blockDim = dim3(256, 1, 1);
         c2.stream = reinterpret_cast<cudaStream_t>(stream);
-        if (a->flags & TPB200_FLAG_PDL) {
-            c2.attrs = attr;
-            c2.numAttrs = 1;
-        }
+        // the merge kernel may start while the partial kernel still runs (it waits for it in griddepcontrol.wait):
+        // its launch latency hides behind the tiles' work
+        c2.attrs = attr;
+        c2.numAttrs = 1;
         if (cudaLaunchKernelEx(&c2, tpb::attention_combine_kernel, P, d.groups) != cudaSuccess) return TPB200_ERR_CUDA;
     }
     return TPB200_OK;

@@ -550,6 +550,7 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
                     const int ldx = pr.ldx;
                     const int nblk = pr.K >> 4;
                     int slot;
+                    bool need_amax = false;
                     if (cache_x0 == x) {
                         slot = 0;
                     } else if (cache_x1 == x) {
@@ -559,47 +560,10 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
                         victim ^= 1;
                         if (slot == 0) cache_x0 = x;
                         else cache_x1 = x;
-                        for (int t = 0; t < P.M; ++t) {
-                            // four blocks per lane and round, all requested before the first is used: the pass
-                            // costs one memory latency per 2048 elements, not one per block
-                            float amax = 0.0f;
-                            for (int kb0 = 0; kb0 < nblk; kb0 += 128) {
-                                uint4 raw[4][4];
-#pragma unroll
-                                for (int j = 0; j < 4; ++j) {
-                                    const int kb = kb0 + lane + 32 * j;
-                                    if (kb < nblk) {
-                                        const size_t e0 = static_cast<size_t>(t) * ldx + static_cast<size_t>(kb) * 16;
-                                        if (P.x_dtype == TPB200_F32) {
-                                            const uint4* gp = reinterpret_cast<const uint4*>(static_cast<const float*>(x) + e0);
-#pragma unroll
-                                            for (int w = 0; w < 4; ++w) raw[j][w] = __ldg(gp + w);
-                                        } else {
-                                            const uint4* gp = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(x) + e0);
-                                            raw[j][0] = __ldg(gp);
-                                            raw[j][1] = __ldg(gp + 1);
-                                        }
-                                    }
-                                }
-#pragma unroll
-                                for (int j = 0; j < 4; ++j) {
-                                    if (kb0 + lane + 32 * j < nblk) {
-                                        float r[16];
-                                        unpack16(raw[j], P.x_dtype, r);
-#pragma unroll
-                                        for (int q = 0; q < 16; ++q) amax = fmaxf(amax, fabsf(r[q]));
-                                    }
-                                }
-                            }
-#pragma unroll
-                            for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-                            if (lane == 0) ctl->act_e[aw][slot][t] = prescale_exponent(amax);
-                        }
-                        __syncwarp();
+                        need_amax = true;          // done below, behind the first stage's loads
                     }
                     const int* e_row = ctl->act_e[aw][slot];
-                    // the epilogue of this unit multiplies by 2^-e; written by the owner of the unit's first stage
-                    if (first == 0 && lane < P.M) ctl->row_scale[i & (kRsRing - 1)][lane] = ldexpf(1.0f, -e_row[lane]);
+                    bool scale_pending = first == 0;   // the owner of the unit's first stage publishes the row multipliers
                     for (int o = first; o < nst && !stop; o += 4) {
                         const int ks = un.ks0 + o;
                         const int git = it + o;
@@ -627,6 +591,52 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
                                         raw[q][1] = __ldg(gp + 1);
                                     }
                                 }
+                            }
+                            if (need_amax) {
+                                // a new activation tensor: its row maxima, with the stage's loads already in flight
+                                need_amax = false;
+                                for (int t = 0; t < P.M; ++t) {
+                                    // four blocks per lane and round, all requested before the first is used: the pass
+                                    // costs one memory latency per 2048 elements, not one per block
+                                    float amax = 0.0f;
+                                    for (int kb0 = 0; kb0 < nblk; kb0 += 128) {
+                                        uint4 araw[4][4];
+#pragma unroll
+                                        for (int j = 0; j < 4; ++j) {
+                                            const int kb = kb0 + lane + 32 * j;
+                                            if (kb < nblk) {
+                                                const size_t e0 = static_cast<size_t>(t) * ldx + static_cast<size_t>(kb) * 16;
+                                                if (P.x_dtype == TPB200_F32) {
+                                                    const uint4* gp = reinterpret_cast<const uint4*>(static_cast<const float*>(x) + e0);
+#pragma unroll
+                                                    for (int w = 0; w < 4; ++w) araw[j][w] = __ldg(gp + w);
+                                                } else {
+                                                    const uint4* gp = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(x) + e0);
+                                                    araw[j][0] = __ldg(gp);
+                                                    araw[j][1] = __ldg(gp + 1);
+                                                }
+                                            }
+                                        }
+#pragma unroll
+                                        for (int j = 0; j < 4; ++j) {
+                                            if (kb0 + lane + 32 * j < nblk) {
+                                                float r[16];
+                                                unpack16(araw[j], P.x_dtype, r);
+#pragma unroll
+                                                for (int q = 0; q < 16; ++q) amax = fmaxf(amax, fabsf(r[q]));
+                                            }
+                                        }
+                                    }
+#pragma unroll
+                                    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+                                    if (lane == 0) ctl->act_e[aw][slot][t] = prescale_exponent(amax);
+                                }
+                                __syncwarp();
+                            }
+                            if (scale_pending) {
+                                // the epilogue of this unit multiplies by 2^-e
+                                scale_pending = false;
+                                if (lane < P.M) ctl->row_scale[i & (kRsRing - 1)][lane] = ldexpf(1.0f, -e_row[lane]);
                             }
                             if (!waited) {
                                 waited = true;
