@@ -596,32 +596,45 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
                                 // a new activation tensor: its row maxima, with the stage's loads already in flight
                                 need_amax = false;
                                 for (int t = 0; t < P.M; ++t) {
-                                    // four blocks per lane and round, all requested before the first is used: the pass
-                                    // costs one memory latency per 2048 elements, not one per block
+                                    // every block of a lane's share is requested before the first is used (eight
+                                    // blocks per lane and round for 16-bit activations, four for fp32): a row of up
+                                    // to 4096 elements costs ONE memory latency, at a time when the memory system
+                                    // is saturated by the weight stream and a round trip takes well over a microsecond
                                     float amax = 0.0f;
-                                    for (int kb0 = 0; kb0 < nblk; kb0 += 128) {
-                                        uint4 araw[4][4];
+                                    const bool wide = P.x_dtype == TPB200_F32;
+                                    const int per_round = wide ? 4 : 8;
+                                    for (int kb0 = 0; kb0 < nblk; kb0 += 32 * per_round) {
+                                        uint4 araw[16];
 #pragma unroll
-                                        for (int j = 0; j < 4; ++j) {
+                                        for (int j = 0; j < 8; ++j) {
                                             const int kb = kb0 + lane + 32 * j;
-                                            if (kb < nblk) {
+                                            if (j < per_round && kb < nblk) {
                                                 const size_t e0 = static_cast<size_t>(t) * ldx + static_cast<size_t>(kb) * 16;
-                                                if (P.x_dtype == TPB200_F32) {
+                                                if (wide) {
                                                     const uint4* gp = reinterpret_cast<const uint4*>(static_cast<const float*>(x) + e0);
 #pragma unroll
-                                                    for (int w = 0; w < 4; ++w) araw[j][w] = __ldg(gp + w);
+                                                    for (int w = 0; w < 4; ++w) araw[(4 * j + w) & 15] = __ldg(gp + w);
                                                 } else {
                                                     const uint4* gp = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(x) + e0);
-                                                    araw[j][0] = __ldg(gp);
-                                                    araw[j][1] = __ldg(gp + 1);
+                                                    araw[2 * j] = __ldg(gp);
+                                                    araw[2 * j + 1] = __ldg(gp + 1);
                                                 }
                                             }
                                         }
 #pragma unroll
-                                        for (int j = 0; j < 4; ++j) {
-                                            if (kb0 + lane + 32 * j < nblk) {
+                                        for (int j = 0; j < 8; ++j) {
+                                            if (j < per_round && kb0 + lane + 32 * j < nblk) {
+                                                uint4 blk4[4];
+                                                if (wide) {
+#pragma unroll
+                                                    for (int w = 0; w < 4; ++w) blk4[w] = araw[(4 * j + w) & 15];
+                                                } else {
+                                                    blk4[0] = araw[2 * j];
+                                                    blk4[1] = araw[2 * j + 1];
+                                                    blk4[2] = blk4[3] = make_uint4(0u, 0u, 0u, 0u);
+                                                }
                                                 float r[16];
-                                                unpack16(araw[j], P.x_dtype, r);
+                                                unpack16(blk4, P.x_dtype, r);
 #pragma unroll
                                                 for (int q = 0; q < 16; ++q) amax = fmaxf(amax, fabsf(r[q]));
                                             }
@@ -708,6 +721,7 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
                 break;
             }
             tc::fence_after_thread_sync();
+            if (warp == 2 && lane == 0) TL(11);
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * 128;
             float v[2][16];
 #pragma unroll
@@ -722,6 +736,7 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
                 tc::tmem_ld_wait();
 #pragma unroll
                 for (int t = 0; t < 16; ++t) {
+                    if (t >= P.M) break;
                     float acc = __uint_as_float(r[0][t]);
 #pragma unroll
                     for (int pc = 1; pc < 4; ++pc) {
@@ -777,15 +792,13 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
                 for (int h = 0; h < 2; ++h) {
                     const int n = un.rt * 256 + h * 128 + et;
                     if (n >= pr.N) continue;
+                    const float bias = pr.bias != nullptr ? load_as_float(pr.bias, P.bias_dtype, n) : 0.0f;
 #pragma unroll
                     for (int t = 0; t < 16; ++t) {
-                        if (t < P.M) {
-                            const float m = fused ? *(volatile const float*)(rs + t) : __ldg(rs + t);
-                            float f = v[h][t] * pr.global_scale * m;
-                            if (pr.bias != nullptr) f += load_as_float(pr.bias, P.bias_dtype, n);
-                            f = apply_activation(f, P.activation);
-                            store_from_float(pr.out, P.out_dtype, static_cast<size_t>(t) * pr.ldo + n, f);
-                        }
+                        if (t >= P.M) break;
+                        const float m = fused ? *(volatile const float*)(rs + t) : __ldg(rs + t);
+                        const float f = apply_activation(fmaf(v[h][t] * pr.global_scale, m, bias), P.activation);
+                        store_from_float(pr.out, P.out_dtype, static_cast<size_t>(t) * pr.ldo + n, f);
                     }
                 }
             }
@@ -924,7 +937,7 @@ struct PlanScratch {
 
 // Deal the pieces of one candidate cut (no piece longer than `lmax` stages) to the CTAs, longest first,
 // each to the least loaded CTA; returns the largest load in stages, or -1 if the cut has too many pieces.
-int deal(const Shape* shapes, int count, int sms, int lmax, int fixed_limit, PlanScratch& S, bool& any_cut) {
+int deal(const Shape* shapes, int count, int sms, int lmax, PlanScratch& S, bool& any_cut) {
     S.num = 0;
     any_cut = false;
     for (int p = 0; p < count; ++p) {
@@ -958,13 +971,8 @@ int deal(const Shape* shapes, int count, int sms, int lmax, int fixed_limit, Pla
     for (int i = 0; i < S.num; ++i) {
         std::pop_heap(S.heap, S.heap + grid, heavier);           // least loaded CTA moves to the back
         const int c = S.heap[grid - 1];
-        const int len = S.pieces[i].ks1 - S.pieces[i].ks0;
-        if (S.load[c] == 0 || S.load[c] + len <= fixed_limit) {
-            S.pieces[i].cta = static_cast<int16_t>(c);
-            S.load[c] += len;
-        } else {
-            S.pieces[i].cta = kPoolCta;                          // left for whichever CTA is free first
-        }
+        S.pieces[i].cta = static_cast<int16_t>(c);
+        S.load[c] += S.pieces[i].ks1 - S.pieces[i].ks0;
         std::push_heap(S.heap, S.heap + grid, heavier);
     }
     return *std::max_element(S.load, S.load + grid);
@@ -984,12 +992,12 @@ int make_plan(const Shape* shapes, int count, int sms, Plan& plan, PlanScratch& 
     }
     constexpr int kHandOverStages = 5;
     constexpr int kWhole = 1 << 30;
-    int best_cost = 0, best_lmax = kWhole;
+    int best_cost = 0;
     bool have = false;
     for (int lmax : {kWhole, 16, 8, 4, 2, 1}) {
         if (lmax != kWhole && lmax >= longest) continue;           // same as the whole-tile plan
         bool any_cut = false;
-        const int load = deal(shapes, count, sms, lmax, kWhole, S, any_cut);
+        const int load = deal(shapes, count, sms, lmax, S, any_cut);
         if (load < 0) continue;
         int cost = load;
         if (any_cut) {
@@ -1005,20 +1013,19 @@ int make_plan(const Shape* shapes, int count, int sms, Plan& plan, PlanScratch& 
             S.num_best = S.num;
             S.grid_best = std::min(sms, S.num);
             best_cost = cost;
-            best_lmax = lmax;
             have = true;
         }
     }
     if (!have) return TPB200_ERR_SHAPE;                            // more tiles than one launch can list
-    // A launch that fills the machine several times over keeps about a third of its work out of the fixed
-    // lists: SMs do not get equal shares of the memory system, and the CTAs that run ahead pick those units up.
+    // A launch that fills the machine several times over ties only ONE unit to each CTA (the smallest ones:
+    // they are what the CTAs request before griddepcontrol.wait) and leaves the rest in the pool, longest
+    // first.  SMs do not get equal shares of the memory system -- a CTA can need 40 % longer per stage than
+    // its neighbour -- and a long unit tied to a slow CTA would be the last thing the launch waits for.
     if (S.grid_best == sms && S.num_best >= 2 * sms) {
-        long long total = 0;
-        for (int i = 0; i < S.num_best; ++i) total += S.best[i].ks1 - S.best[i].ks0;
-        const int fixed_limit = static_cast<int>(total * 2 / (3LL * sms));
-        bool any_cut = false;
-        deal(shapes, count, sms, best_lmax, std::max(fixed_limit, 1), S, any_cut);
-        std::copy(S.pieces, S.pieces + S.num, S.best);
+        for (int i = 0; i < S.num_best; ++i) {
+            const int from_end = S.num_best - 1 - i;               // the list is sorted longest first
+            S.best[i].cta = from_end < sms ? static_cast<int16_t>(from_end) : kPoolCta;
+        }
     }
 
     // CTA by CTA: whole tiles first, cut tiles last (their hand-over then holds up nothing that follows);

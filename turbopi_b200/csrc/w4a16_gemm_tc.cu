@@ -3,8 +3,10 @@
 //   out[M, N] = alpha * x[M, K] @ dequant(W)[N, K]^T (+ beta * out)
 //
 // INT4 x bf16 is not an operand pair of the tensor cores, so the weights are dequantised to bf16 on the way
-// into shared memory -- once per CTA and K stage, then used by the MMAs of up to three 128-row tiles of
-// tokens (B-stationary: 384 tokens x 128 output columns per CTA, three fp32 accumulators in tensor memory).
+// into shared memory -- once per CTA and K stage, then used by the MMAs of up to two 128-row tiles of
+// tokens (256 tokens x 256 output columns per CTA, two fp32 accumulators filling tensor memory).  The tile is
+// as large as tensor memory allows because the activations are re-read once per 256 output columns: with
+// 128-column tiles those reads (373 MB through L2 for 712 x 16384 x 2048) cost more than the MMAs.
 // Two weight formats:
 //   plugin   signed nibbles [N, K/2] bytes (low nibble = even k), bf16 scale and optional bf16 zero point per
 //            128 along K: w = q * scale + zero          (openpi/w4a16_plugin/src/w4a16_gemm_plugin.h:41-59)
@@ -12,9 +14,9 @@
 //            fp16 scale per 32, zero point 8: w = (q - 8) * scale
 //            (openpi/src/openpi/utils/w4a16_packer.py:311-368, modules/w4a16_linear.py:174-199)
 //
-// Roles (192 threads): warps 0..3 turn one weight row each (64 K values per stage: 32 bytes -> one 128-byte
-// swizzled row of bf16) and later run the epilogue; warp 4 lane 0 requests the activation tiles by TMA
-// (128 rows x 128 bytes, 128-byte swizzle, rows past M read as zero); warp 5 allocates tensor memory and its
+// Roles (320 threads): warps 0..7 turn one weight row each (64 K values per stage: 32 bytes -> one 128-byte
+// swizzled row of bf16) and later run the epilogue; warp 8 lane 0 requests the activation tiles by TMA
+// (128 rows x 128 bytes, 128-byte swizzle, rows past M read as zero); warp 9 allocates tensor memory and its
 // lane 0 issues tcgen05.mma kind::f16.  The MMAs of stage k run while the threads dequantise stage k + 1.
 // Every wait is bounded; nothing waits on another CTA.
 #include <algorithm>
@@ -29,13 +31,16 @@ bool make_tensor_map_bytes_sw128(CUtensorMap* map, const void* base, uint64_t ro
 
 namespace {
 
-constexpr int kTileN = 128;            // output columns per CTA
+constexpr int kTileN = 256;            // output columns per CTA
 constexpr int kTileM = 128;            // token rows per accumulator
-constexpr int kMaxMt = 3;              // accumulators per CTA
+constexpr int kMaxMt = 2;              // accumulators per CTA
 constexpr int kStageK = 64;            // K values per stage: one 128-byte row of bf16
 constexpr int kChunk = 128 * 128;      // bytes of one 128-row operand tile of a stage
+constexpr int kBTile = kTileN * 128;   // bytes of the dequantised weight tile of a stage
 constexpr int kAStages = 3, kBStages = 2;
-constexpr int kThreadsW4 = 192;
+constexpr int kDequantThreads = kTileN;
+constexpr int kThreadsW4 = kDequantThreads + 64;
+constexpr int kTmaWarp = kDequantThreads / 32, kMmaWarp = kTmaWarp + 1;
 constexpr long long kWaitW4 = 400000000LL;   // ~0.2 s
 
 struct W4Params {
@@ -48,7 +53,7 @@ struct W4Params {
     int bias_dtype, out_dtype;
     int M, N, K, ldo;
     float alpha, beta;
-    int m_groups;                      // ceil(m_tiles / 3)
+    int mt_per_cta;                    // 1 or 2 token tiles per CTA
     int m_tiles;
 };
 
@@ -101,13 +106,13 @@ __global__ void __launch_bounds__(kThreadsW4, 1) w4a16_gemm_tc_kernel(const __gr
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* sA = smem;                                            // [kAStages][kMaxMt][16 KB]
-    uint8_t* sB = sA + kAStages * kMaxMt * kChunk;                 // [kBStages][16 KB]
-    W4Control* ctl = reinterpret_cast<W4Control*>(sB + kBStages * kChunk);
+    uint8_t* sB = sA + kAStages * kMaxMt * kChunk;                 // [kBStages][32 KB]
+    W4Control* ctl = reinterpret_cast<W4Control*>(sB + kBStages * kBTile);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * kTileN;
-    const int mt0 = blockIdx.y * kMaxMt;
-    const int nmt = min(kMaxMt, P.m_tiles - mt0);
+    const int mt0 = blockIdx.y * P.mt_per_cta;
+    const int nmt = min(P.mt_per_cta, P.m_tiles - mt0);
     const int nks = P.K / kStageK;
 
     if (threadIdx.x == 0) {
@@ -116,18 +121,18 @@ __global__ void __launch_bounds__(kThreadsW4, 1) w4a16_gemm_tc_kernel(const __gr
             mbar_init(&ctl->a_empty[s], 1);
         }
         for (int s = 0; s < kBStages; ++s) {
-            mbar_init(&ctl->b_full[s], 128);
+            mbar_init(&ctl->b_full[s], kDequantThreads);
             mbar_init(&ctl->b_empty[s], 1);
         }
         mbar_init(&ctl->acc_full, 1);
         fence_mbar_init();
     }
-    if (warp == 5) {
+    if (warp == kMmaWarp) {
         __syncwarp();
         tc::tmem_alloc(&ctl->tmem_base, 512);
         tc::tmem_relinquish();
     }
-    if (warp == 4 && lane == 0) tc::prefetch_tensormap(&P.map_x);
+    if (warp == kTmaWarp && lane == 0) tc::prefetch_tensormap(&P.map_x);
     tc::fence_before_thread_sync();
     __syncthreads();
     tc::fence_after_thread_sync();
@@ -135,7 +140,7 @@ __global__ void __launch_bounds__(kThreadsW4, 1) w4a16_gemm_tc_kernel(const __gr
     pdl_launch_dependents();
 
     bool ok = true;
-    if (warp == 4) {
+    if (warp == kTmaWarp) {
         // ------------------------------------------------------------ activation tiles by TMA
         if (lane == 0) {
             pdl_wait_prior_grids();
@@ -151,7 +156,7 @@ __global__ void __launch_bounds__(kThreadsW4, 1) w4a16_gemm_tc_kernel(const __gr
                 }
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == kMmaWarp) {
         // ------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             const uint32_t idesc = idesc_bf16_kmajor(kTileN);
@@ -166,7 +171,7 @@ __global__ void __launch_bounds__(kThreadsW4, 1) w4a16_gemm_tc_kernel(const __gr
                 tc::fence_after_thread_sync();
 #pragma unroll
                 for (int kk = 0; kk < kStageK / 16; ++kk) {
-                    const uint64_t bdesc = tc::desc_from_words(b16 + ((sb * kChunk + kk * 32) >> 4), tc::kDescHiKmajorSw128);
+                    const uint64_t bdesc = tc::desc_from_words(b16 + ((sb * kBTile + kk * 32) >> 4), tc::kDescHiKmajorSw128);
                     for (int t = 0; t < nmt; ++t) {
                         mma_bf16_ss(tmem + t * kTileN,
                                     tc::desc_from_words(a16 + (((sa * kMaxMt + t) * kChunk + kk * 32) >> 4), tc::kDescHiKmajorSw128),
@@ -180,11 +185,14 @@ __global__ void __launch_bounds__(kThreadsW4, 1) w4a16_gemm_tc_kernel(const __gr
         }
     } else {
         // ------------------------------------------------------------ weight rows: dequantise into shared memory
-        const int r = threadIdx.x;                       // 0..127: row of the tile = output column n0 + r
+        const int r = threadIdx.x;                       // 0..255: row of the weight tile = output column n0 + r
         const int n = n0 + r;
         const bool row_ok = n < P.N;
         const uint32_t flip = kPacker ? 0u : 0x88888888u;
         uint4 raw[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+        float nsc[2] = {0.0f, 0.0f}, nzp[2] = {0.0f, 0.0f};
+        // codes AND scales of a stage are requested one stage ahead: a scale fetched at the moment it is needed
+        // costs a memory round trip per stage, more than the stage's arithmetic
         auto load_raw = [&](int ks) {
             if (!row_ok) return;
             if (kPacker) {
@@ -192,28 +200,22 @@ __global__ void __launch_bounds__(kThreadsW4, 1) w4a16_gemm_tc_kernel(const __gr
                 const uint4* w = reinterpret_cast<const uint4*>(P.w);
                 raw[0] = __ldg(w + static_cast<size_t>(2 * ks) * P.N + n);
                 raw[1] = __ldg(w + static_cast<size_t>(2 * ks + 1) * P.N + n);
+                const __half* sp = static_cast<const __half*>(P.scale);
+                nsc[0] = __half2float(__ldg(sp + static_cast<size_t>(2 * ks) * P.N + n));
+                nsc[1] = __half2float(__ldg(sp + static_cast<size_t>(2 * ks + 1) * P.N + n));
             } else {
                 const uint4* w = reinterpret_cast<const uint4*>(P.w + static_cast<size_t>(n) * (P.K / 2) + ks * 32);
                 raw[0] = __ldg(w);
                 raw[1] = __ldg(w + 1);
+                const size_t gi = static_cast<size_t>(n) * (P.K / 128) + (ks >> 1);      // 128 along K = two stages
+                nsc[0] = nsc[1] = __bfloat162float(__ldg(static_cast<const __nv_bfloat16*>(P.scale) + gi));
+                if (P.zero != nullptr) nzp[0] = nzp[1] = __bfloat162float(__ldg(P.zero + gi));
             }
         };
         load_raw(0);
         for (int ks = 0; ks < nks && ok; ++ks) {
             const int sb = ks % kBStages;
-            float sc[2] = {0.0f, 0.0f}, zp[2] = {0.0f, 0.0f};
-            if (row_ok) {
-                if (kPacker) {
-                    const __half* s = static_cast<const __half*>(P.scale);
-                    sc[0] = __half2float(s[static_cast<size_t>(2 * ks) * P.N + n]);
-                    sc[1] = __half2float(s[static_cast<size_t>(2 * ks + 1) * P.N + n]);
-                } else {
-                    const int g = ks >> 1;               // 128 along K = two stages
-                    const size_t gi = static_cast<size_t>(n) * (P.K / 128) + g;
-                    sc[0] = sc[1] = __bfloat162float(static_cast<const __nv_bfloat16*>(P.scale)[gi]);
-                    if (P.zero != nullptr) zp[0] = zp[1] = __bfloat162float(P.zero[gi]);
-                }
-            }
+            const float sc[2] = {nsc[0], nsc[1]}, zp[2] = {nzp[0], nzp[1]};
             const uint32_t w[8] = {raw[0].x, raw[0].y, raw[0].z, raw[0].w, raw[1].x, raw[1].y, raw[1].z, raw[1].w};
             if (ks + 1 < nks) load_raw(ks + 1);          // the next stage's bytes travel during this stage's arithmetic
             if (ks >= kBStages && !mbar_wait_bounded(&ctl->b_empty[sb], ((ks / kBStages) - 1) & 1, kWaitW4)) {
@@ -221,7 +223,7 @@ __global__ void __launch_bounds__(kThreadsW4, 1) w4a16_gemm_tc_kernel(const __gr
                 ok = false;
                 break;
             }
-            uint8_t* row = sB + sb * kChunk + r * 128;
+            uint8_t* row = sB + sb * kBTile + r * 128;
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
                 const uint4 v = dequant8(w[c], flip, sc[c >> 2], zp[c >> 2]);
@@ -238,11 +240,15 @@ __global__ void __launch_bounds__(kThreadsW4, 1) w4a16_gemm_tc_kernel(const __gr
         ok = __all_sync(0xffffffffu, ok);                // the tensor-memory loads are warp-collective
         tc::fence_after_thread_sync();
         if (ok) {
-            const uint32_t lane_addr = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+            // warps 0..3 take the accumulators' columns [0, 128), warps 4..7 columns [128, 256); the warp's
+            // quarter of the 128 token rows (tensor-memory lanes) is warp % 4
+            const int tr = threadIdx.x & 127;
+            const int col_half = threadIdx.x >> 7;
+            const uint32_t lane_addr = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
             for (int t = 0; t < nmt; ++t) {
-                const int m = (mt0 + t) * kTileM + r;
+                const int m = (mt0 + t) * kTileM + tr;
                 const bool store = m < P.M;
-                for (int c0 = 0; c0 < kTileN; c0 += 32) {
+                for (int c0 = col_half * 128; c0 < col_half * 128 + 128; c0 += 32) {
                     uint32_t v[32];
                     tc::tmem_ld_32x32b_x32(lane_addr + t * kTileN + c0, v);
                     tc::tmem_ld_wait();
@@ -292,7 +298,7 @@ __global__ void __launch_bounds__(kThreadsW4, 1) w4a16_gemm_tc_kernel(const __gr
 
     tc::fence_before_thread_sync();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == kMmaWarp) {
         tc::fence_after_thread_sync();
         tc::tmem_dealloc(tmem, 512);
     }
@@ -330,8 +336,18 @@ int w4a16_gemm_tc_launch(int format, const void* x, const void* w, const void* s
     P.alpha = alpha;
     P.beta = beta;
     P.m_tiles = (M + kTileM - 1) / kTileM;
-    P.m_groups = (P.m_tiles + kMaxMt - 1) / kMaxMt;
-    const size_t smem = static_cast<size_t>(kAStages * kMaxMt + kBStages) * kChunk + sizeof(W4Control) + 1024;
+    // two token tiles per CTA halve the weight reads and dequantisations; with too few CTAs for the machine
+    // one tile per CTA doubles the CTAs instead
+    int sms = 148;
+    {
+        int dev_ = 0;
+        if (cudaGetDevice(&dev_) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev_);
+    }
+    const int n_tiles = (N + kTileN - 1) / kTileN;
+    P.mt_per_cta = (P.m_tiles > 1 && n_tiles * ((P.m_tiles + 1) / 2) >= sms) ? 2 : 1;
+    const int m_groups = (P.m_tiles + P.mt_per_cta - 1) / P.mt_per_cta;
+    const size_t smem = static_cast<size_t>(kAStages * kMaxMt) * kChunk + static_cast<size_t>(kBStages) * kBTile +
+                        sizeof(W4Control) + 1024;
     auto kernel = format == 1 ? w4a16_gemm_tc_kernel<true> : w4a16_gemm_tc_kernel<false>;
     static std::atomic<uint64_t> configured[2] = {{0}, {0}};
     int dev = 0;
@@ -344,7 +360,7 @@ int w4a16_gemm_tc_launch(int format, const void* x, const void* w, const void* s
         configured[format].fetch_or(bit, std::memory_order_relaxed);
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((N + kTileN - 1) / kTileN, P.m_groups, 1);
+    cfg.gridDim = dim3(n_tiles, m_groups, 1);
     cfg.blockDim = dim3(kThreadsW4, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
