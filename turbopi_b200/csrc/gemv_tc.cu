@@ -216,7 +216,7 @@ __device__ __forceinline__ bool fetch_unit_warp(SharedControl* ctl, int i, int l
 #ifdef TPB_TIMELINE
 // Diagnostic build only (-DTPB_TIMELINE): every CTA of the last launches leaves globaltimer stamps of its
 // milestones here; tpb200_debug_gemv_tc_timeline() copies them out.
-constexpr int kTlSlots = 4, kTlPoints = 12;
+constexpr int kTlSlots = 4, kTlPoints = 16;
 __device__ unsigned long long g_timeline[kTlSlots][kMaxCtas][kTlPoints];
 __device__ __forceinline__ unsigned long long tl_now() {
     unsigned long long t;
@@ -309,6 +309,16 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
         TcUnit end_mark = {};
         end_mark.p = kEndOfUnits;
 
+        // The first unit is announced before anything else: the other roles (the quantiser warps above all) start
+        // on it while this warp is still held by the copy requests below.
+        int next_fixed = u_lo;
+        TcUnit cur = end_mark;
+        bool have_cur = false;
+        if (next_fixed < u_hi) {
+            cur = P.units[next_fixed++];
+            have_cur = true;
+            publish(cur);
+        }
         // the ring's first fill goes out in ONE round: lane l requests quarter l % 4 of stage l / 4
         int pre = 0;
         const uint8_t* my_src = nullptr;
@@ -324,14 +334,6 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
         __syncwarp();
         if (my_src != nullptr) {
             bulk_copy_g2s(smem + (lane >> 2) * kStageBytes + (lane & 3) * kQuarter, my_src, kQuarter, &ctl->full[lane >> 2]);
-        }
-        int next_fixed = u_lo;
-        TcUnit cur = end_mark;
-        bool have_cur = false;
-        if (next_fixed < u_hi) {
-            cur = P.units[next_fixed++];
-            have_cur = true;
-            publish(cur);
         }
         if (lane == 0) TL(2);
         pdl_wait_prior_grids();
@@ -536,12 +538,29 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
             const void* cache_x0 = nullptr;
             const void* cache_x1 = nullptr;
             int victim = 0;
-            pdl_wait_prior_grids();                                     // the activations come from the previous kernel
+            // The activations come from the previous kernel, so they may only be READ after griddepcontrol.wait.
+            // Asking the L2 for their lines before that is harmless (the L2 is the point of coherence: a line
+            // written later is simply updated) and takes the DRAM round trip -- two microseconds while the weight
+            // streams of two launches saturate the memory system -- out of the path to the first MMA.
+            if (u_lo < u_hi) {
+                const TcUnit first_unit = P.units[u_lo];
+                const TcProblem& fp = P.prob[first_unit.p];
+                const int row_bytes = fp.K * (P.x_dtype == TPB200_F32 ? 4 : 2);
+                const int lines = (row_bytes + 127) >> 7;
+                for (int t = 0; t < P.M; ++t) {
+                    const char* row = static_cast<const char*>(fp.x) + static_cast<size_t>(t) * fp.ldx * (P.x_dtype == TPB200_F32 ? 4 : 2);
+                    for (int ln = aw * 32 + lane; ln < lines; ln += 128) {
+                        asm volatile("prefetch.global.L2 [%0];" ::"l"(row + (static_cast<size_t>(ln) << 7)));
+                    }
+                }
+            }
+            pdl_wait_prior_grids();
             if (aw == 0 && lane == 0) TL(8);
             int it = 0;                                                 // stages of the units seen so far
             bool stop = false;
             TcUnit un;
             for (int i = 0; !stop && fetch_unit_warp(ctl, i, lane, un); ++i) {
+                if (aw == 0 && lane == 0 && i == 0) TL(12);
                 const int nst = un.ks1 - un.ks0;
                 const int first = (aw - it) & 3;                        // this warp's first stage inside the unit
                 if (first < nst) {
@@ -646,6 +665,7 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
                                 }
                                 __syncwarp();
                             }
+                            if (aw == 0 && lane == 0 && git == 0) TL(13);
                             if (scale_pending) {
                                 // the epilogue of this unit multiplies by 2^-e
                                 scale_pending = false;
@@ -696,6 +716,7 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
                             }
                         }
                         if (stop) break;
+                        if (aw == 0 && lane == 0 && git == 0) TL(14);
                         fence_proxy_async_smem();                      // the tensor core reads these bytes
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&ctl->full[s]);
