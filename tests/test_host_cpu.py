@@ -133,3 +133,42 @@ def test_weight_row_permutations_are_permutations():
     assert sorted(g.tolist()) == list(range(2048))
     b = g.reshape(-1, 2, 128)                            # every 256-row block: 128 gate rows, their up rows
     assert (b[:, 1] == b[:, 0] + 1024).all() and (b[:, 0, 0] == torch.arange(8) * 128).all()
+
+
+def _gemv_tc_plan(shapes, sms=148):
+    n = len(shapes)
+    N = (ctypes.c_int * n)(*[s[0] for s in shapes])
+    K = (ctypes.c_int * n)(*[s[1] for s in shapes])
+    info = _lib.GemvTcPlanInfo()
+    status = _lib.load().tpb200_nvfp4_gemv_tc_plan(N, K, n, sms, ctypes.byref(info))
+    return status, info
+
+
+def test_gemv_tc_planner_covers_every_stage_and_fits_the_gpu():
+    """The tensor-core GEMV's launch planner runs on the host alone: every 256-row x 256-column stage of every
+    matrix is planned exactly once, the grid never exceeds the SM count, and scratch is asked for only when tiles
+    are cut along K or units are pooled."""
+    stages = lambda shapes: sum(-(-n // 256) * (k // 256) for n, k in shapes)
+    expert = [(4096, 1024), (4096, 1024), (1024, 4096)] * 18          # the 54 MLP matrices of the action expert
+    status, info = _gemv_tc_plan(expert)
+    assert status == 0
+    assert info.grid == 148 and info.total_stages == stages(expert) == 3456
+    assert info.pool_units > 0 and info.pool_units + info.grid == info.units    # one fixed unit per CTA, rest pooled
+    assert info.max_load_stages * info.grid < info.total_stages                  # the pool carries most of the work
+    assert info.workspace_bytes >= 4                                             # the pool's ticket counter
+
+    for shapes in ([(4096, 1024)], [(16384, 2048)], [(256, 256)], [(100, 256)]):
+        status, info = _gemv_tc_plan(shapes)
+        assert status == 0 and info.total_stages == stages(shapes)
+        assert 1 <= info.grid <= 148 and info.cut_tiles == 0 and info.workspace_bytes == 0
+
+    status, info = _gemv_tc_plan([(1024, 4096)])          # 4 row tiles of 16 stages: cut along K to fill more SMs
+    assert status == 0 and info.cut_tiles == 4 and info.grid > 4 and info.workspace_bytes > 0
+    assert info.total_stages == 64
+
+    status, info = _gemv_tc_plan([(4096, 1024)] * 3, sms=8)
+    assert status == 0 and info.grid == 8 and info.total_stages == 192
+
+    for bad in ([(4096, 1000)], [(0, 1024)], []):          # K not a multiple of the stage, empty problems
+        status, _ = _gemv_tc_plan(bad) if bad else (_lib.load().tpb200_nvfp4_gemv_tc_plan(None, None, 0, 148, None), None)
+        assert status != 0
