@@ -686,6 +686,24 @@ def run_case(args):
         ws = ops.attention_workspace(rows, keys, 256, 1, dev)
         ms = timed(lambda: ops.attention(qm, km, vm, o, 1 / 16, None, ws), args.iters)
         print(f"attention rows={rows} keys={keys} d=256: {ms * 1e3:.1f} us per call (partial + combine)")
+    elif args.case == "int4-gemm":     # bf16 x int4 (plugin layout, group 128) on the tensor cores
+        x = torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16)
+        w = torch.randint(-128, 128, (N, K // 2), device=dev, dtype=torch.int8)
+        sc = (torch.rand(N, K // 128, device=dev) * 0.01 + 0.002).to(torch.bfloat16)
+        o = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+        ms = timed(lambda: ops.w4a16_gemm(x, w, sc, None, None, o, tlib.INT4_PLUGIN), args.iters)
+        print(f"int4-gemm M={M} N={N} K={K}: {ms * 1e3:.1f} us, {2.0 * M * N * K / (ms * 1e-3) / 1e12:.0f} TFLOP/s")
+    elif args.case == "int4-gemv":     # the reference's (K/32, N, 4) layout, one fp16 row
+        x = torch.randn(1, K, device=dev, generator=g).to(torch.float16)
+        w = torch.randint(-2 ** 31, 2 ** 31 - 1, (K // 32, N, 4), device=dev, dtype=torch.int32)
+        sc = (torch.rand(K // 32, N, device=dev) * 0.015 + 0.005).to(torch.float16)
+        ms = timed(lambda: ops.w4a16_gemv(x, w, sc), args.iters)
+        print(f"int4-gemv N={N} K={K} (k-block layout, group 32): {ms * 1e3:.1f} us per call")
+    elif args.case == "quantize":      # bf16 activations -> e2m1 codes + swizzled UE4M3 scales
+        x = torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16)
+        packed, sf = ops.nvfp4_quantize_act(x)
+        ms = timed(lambda: ops.nvfp4_quantize_act(x, packed, sf), args.iters)
+        print(f"quantize M={M} K={K}: {ms * 1e3:.1f} us per call")
     elif args.case == "pi05":
         cfg = Pi05Config()
         model = Pi05(cfg, dev, seed=0)
@@ -792,7 +810,7 @@ def main():
     ap.add_argument("--no-pdl", action="store_true",
                     help="--path tc: no programmatic dependent launch between quantiser and GEMV")
     ap.add_argument("--no-serving", action="store_true", help="skip the request-serving measurement (builds a full model)")
-    ap.add_argument("--case", default=None, choices=["gemm", "gemm-nvfp4", "rowop", "attention", "pi05"],
+    ap.add_argument("--case", default=None, choices=["gemm", "gemm-nvfp4", "rowop", "attention", "pi05", "int4-gemm", "int4-gemv", "quantize"],
                     help="run one bounded kernel case (for ncu) instead of the benchmark")
     ap.add_argument("--M", type=int, default=712)
     ap.add_argument("--N", type=int, default=32768)

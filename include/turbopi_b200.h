@@ -291,8 +291,9 @@ int tpb200_nvfp4_gemv_tc_static(const tpb200_gemv_tc_problem* problems, int coun
  *   (SigLIP: images x heads) start at base + a * stride[0] + b * stride[1] elements.
  *   key_bias: bf16 [n_keys] added to every row's scores (0, or the mask value for a key that must not be
  *   attended to), NULL = none.
- * Keys are split in tiles of 128 across CTAs; with more than one tile the partial results pass through
+ * Keys are split in tiles of 256 across CTAs; with more than one tile the partial results pass through
  * `workspace` (tpb200_attention_workspace_size bytes, no initialisation needed) and a second small kernel.
+ * Group strides are >= 0; a stride of 0 lets every group read the same rows (shared keys / values).
  * ------------------------------------------------------------------------------------------- */
 typedef struct {
     const void* q; const void* k; const void* v; void* out; const void* key_bias;

@@ -32,7 +32,8 @@ def _gemma_case(cuda_device, L, S, valid, seed, heads=8, D=256):
     return out.float().cpu().numpy(), ref.numpy()
 
 
-@pytest.mark.parametrize("L,S", [(712, 712), (50, 762), (5, 3), (128, 128), (129, 129), (1, 300), (300, 1)])
+@pytest.mark.parametrize("L,S", [(712, 712), (50, 762), (5, 3), (128, 128), (129, 129), (1, 300), (300, 1), (40, 256),
+                                 (40, 257), (200, 384), (17, 385), (130, 1030)])
 def test_gemma_attention_matches_oracle(cuda_device, L, S):
     got, ref = _gemma_case(cuda_device, L, S, None, L * 1000 + S)
     assert rel_err(got, ref) <= 1e-2
@@ -80,6 +81,28 @@ def test_siglip_attention_matches_torch(cuda_device):
     assert _lib.load().tpb200_device_error(0) == 0
     r = qkv.float().view(NI, T, 3, H, D).permute(2, 0, 3, 1, 4)
     ref = F.scaled_dot_product_attention(r[0], r[1], r[2]).transpose(1, 2).reshape(NI * T, H * D)
+    got = out.float().cpu()
+    assert rel_err(got.numpy(), ref.numpy()) <= 1e-2
+    assert cosine(got.numpy(), ref.numpy()) >= 0.9999
+
+
+@pytest.mark.parametrize("D", [8, 64, 72, 128, 136, 200])
+@pytest.mark.parametrize("S", [100, 300])
+def test_other_head_dims_and_shared_keys(cuda_device, D, S):
+    """Head dims that fill the 64-column blocks partly, and 3 x 2 groups of queries that all read the SAME keys
+    and values (group strides 0)."""
+    from turbopi_b200 import _lib, ops
+    g = torch.Generator().manual_seed(D * 7 + S)
+    A, B, R = 3, 2, 70
+    q = torch.randn(A, B, R, D, generator=g).to(BF)
+    k = torch.randn(S, D, generator=g).to(BF)
+    v = torch.randn(S, D, generator=g).to(BF)
+    out = torch.full((A, B, R, D), 5.0, dtype=BF, device=cuda_device)
+    kd, vd = k.to(cuda_device), v.to(cuda_device)
+    ops.attention(q.to(cuda_device), kd.expand(A, B, S, D), vd.expand(A, B, S, D), out, D ** -0.5)
+    torch.cuda.synchronize()
+    assert _lib.load().tpb200_device_error(0) == 0
+    ref = F.scaled_dot_product_attention(q.float(), k.float().expand(A, B, S, D), v.float().expand(A, B, S, D))
     got = out.float().cpu()
     assert rel_err(got.numpy(), ref.numpy()) <= 1e-2
     assert cosine(got.numpy(), ref.numpy()) >= 0.9999

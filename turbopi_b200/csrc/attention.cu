@@ -9,19 +9,23 @@
 //   SigLIP                         2 images x 16 heads, 256 tokens, head_dim 72 (padded to 128 in shared memory).
 //
 // Every problem is far too small to fill the machine with one CTA per 128 query rows running over all
-// keys (the action expert has 4 such tiles), so the keys are split too: CTA (row tile, key tile of 128,
-// group) computes S = Q K^T (16 MMAs of K = 16), the softmax of its 128 x 128 block relative to the block's
-// own row maxima, and O = P V (8 MMAs), and leaves O, the row maxima and the row sums in scratch; a second
+// keys (the action expert has 4 such tiles), so the keys are split too: CTA (row tile, key tile of 256,
+// group) computes S = Q K^T as two 128-key tiles side by side in tensor memory (2 x 16 MMAs of K = 16), the
+// softmax of its 128 x 256 block relative to the block's own row maxima (base-2 exponentials, 256 threads:
+// two per row), and O = P V (16 MMAs), and leaves O, the row maxima and the row sums in scratch; a second
 // small kernel combines the key tiles' partial results (the usual log-sum-exp merge).  With a single key
 // tile the first kernel writes the final rows itself.
 //
 // Operands in shared memory, all in the 128-byte-swizzle image (rows of 128 B = 64 bf16, 16-byte chunk c of
 // row r at c ^ (r & 7), 8-row groups 1024 B apart, one 16 KB block per 64 columns of head_dim):
-//   Q [128 rows][D], K [128 keys][D]      K-major operands of S = Q K^T
-//   P [128 rows][128 keys]                K-major A operand of O = P V, written by the softmax threads over Q
-//   V [128 keys][D]                       the SAME image read as an MN-major B operand (the 128-byte direction
-//                                         is head_dim = N, the rows are keys = K): no transposed copy of V.
-// Loads are plain 16-byte cp.async with zero fill past the end of a matrix; nothing here waits on another CTA.
+//   Q [128 rows][D], K [2 x 128 keys][D]  K-major operands of S = Q K^T
+//   P [128 rows][256 keys]                K-major A operand of O = P V, written by the softmax threads over Q
+//   V [2 x 128 keys][D]                   loaded where K was once the S MMAs are done; the SAME image is read as an
+//                                         MN-major B operand (the 128-byte direction is head_dim = N, the rows
+//                                         are keys = K): no transposed copy of V.
+// Loads are TMA tile copies through 4-dimensional tensor maps (head_dim, rows, groups; zero fill past the end
+// of a matrix), issued by one thread; the partial O of a CTA is staged where V was and leaves as one bulk
+// copy.  Nothing here waits on another CTA; every wait is bounded and reports through the device error word.
 #include <algorithm>
 #include <atomic>
 
@@ -31,35 +35,48 @@ namespace tpb {
 namespace {
 
 constexpr int kRows = 128;              // query rows per CTA
-constexpr int kKeys = 128;              // keys per CTA
+constexpr int kKeyTile = 128;           // keys per S tile (one MMA's N)
+constexpr int kKeysCta = 256;           // keys per CTA: two S tiles side by side in tensor memory
 constexpr int kChunkBytes = kRows * 128;   // one 64-column block of an operand
-constexpr int kThreadsAttn = 128;
+constexpr int kThreadsAttn = 256;           // two warps per 32-lane quarter of tensor memory: each takes half the columns
 constexpr float kMasked = -2.3819763e38f;   // the reference's additive mask value (pi0_pytorch.py:185-188)
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kFloor2 = -3.0e38f;         // lowest score in the base-2 domain (the mask value times log2 e overflows)
 constexpr uint32_t kTmemColsAttn = 512;
-constexpr uint32_t kColS = 0, kColO = 128;
-constexpr long long kWaitCycles = 200000000LL;   // ~0.1 s: bound of each wait for the tensor cores
+constexpr uint32_t kColS = 0, kColO = 256;
+constexpr long long kWaitCycles = 200000000LL;   // ~0.1 s: bound of each wait for copies / tensor cores
+
+// One operand (q, k or v) as a 4-dimensional tensor map: dimension 0 is head_dim, the other three are the
+// rows and the two group indices ordered by ascending stride; slot[i] is the coordinate position (1..3)
+// of rows / inner group / outer group, mul[i] is 0 for a broadcast (stride 0) group dimension.
+struct AttnOperand {
+    CUtensorMap map;
+    int slot[3];
+    int mul[3];
+};
 
 struct AttnParams {
-    const __nv_bfloat16* q;
-    const __nv_bfloat16* k;
-    const __nv_bfloat16* v;
+    AttnOperand q, k, v;
     __nv_bfloat16* out;
     const __nv_bfloat16* key_bias;
     int n_rows, n_keys, head_dim, dpad;         // dpad: head_dim rounded up to 64
-    int ldq, ldk, ldv, ldo;
+    int ldo;
     int groups_inner;
-    long long q_stride[2], k_stride[2], v_stride[2], o_stride[2];
-    float scale;
+    long long o_stride[2];
+    float scale2;                               // scale * log2(e): the softmax runs in base 2
     int row_tiles, key_tiles;
-    float* part_o;                              // [group][row tile][key tile][128][dv]
+    float* part_o;                              // [group][row tile][key tile] images of 128 rows x dvp floats
     float* part_ml;                             // [group][row tile][key tile][128][2]
     int dv;                                     // head_dim rounded up to 16: N of the second MMA
+    int dvp;                                    // head_dim rounded up to 32: row pitch of a partial image
 };
 
 struct AttnControl {
-    uint64_t bar_s, bar_o;
+    uint64_t bar_k0, bar_k1, bar_s, bar_v, bar_o;
     uint32_t tmem_base;
-    float bias[kKeys];
+    float bias2[kKeysCta];
+    float half_max[2][kRows];                   // row maxima / row sums of the two column halves
+    float half_sum[2][kRows];
 };
 
 // Instruction descriptor for kind::f16 with bf16 operands and an fp32 accumulator, M = 128:
@@ -82,44 +99,57 @@ __device__ __forceinline__ void mma_bf16(uint32_t tmem_d, uint64_t desc_a, uint6
         : "memory");
 }
 
-__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, bool valid) {
-    const uint32_t n = valid ? 16u : 0u;       // 0 source bytes: the 16 destination bytes are zero-filled
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(n) : "memory");
-}
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
-
-// rows [row0, row0 + 128) of a [n, d] bf16 matrix (row stride ld elements) -> the swizzled image at `dst`
-__device__ __forceinline__ void load_tile(uint8_t* dst, const __nv_bfloat16* src, int ld, int row0, int n, int d, int dpad) {
-    const int cpr = dpad >> 3;                  // 16-byte chunks per row: 8, 16, 24 or 32
-    const int sh = dpad == 64 ? 3 : (dpad == 128 ? 4 : 5);
-    const bool pow2 = dpad != 192;
-    for (int idx = threadIdx.x; idx < kRows * cpr; idx += kThreadsAttn) {
-        const int r = pow2 ? (idx >> sh) : idx / cpr;
-        const int c = idx - r * cpr;
-        const bool valid = (row0 + r < n) && (c * 8 < d);
-        const __nv_bfloat16* g = valid ? src + static_cast<size_t>(row0 + r) * ld + c * 8 : src;
-        uint8_t* s = dst + (c >> 3) * kChunkBytes + r * 128 + (((c & 7) ^ (r & 7)) << 4);
-        cp_async16(s, g, valid);
+// 128 rows starting at `row0` of group (ga, gb): one 64-column box per 16 KB block of the swizzled image
+__device__ __forceinline__ void load_rows(uint8_t* dst, const AttnOperand& op, int row0, int ga, int gb, int nchunk,
+                                          uint64_t* bar) {
+    const int v[3] = {row0 * op.mul[0], gb * op.mul[1], ga * op.mul[2]};
+    int c1 = 0, c2 = 0, c3 = 0;
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+        c1 = op.slot[i] == 1 ? v[i] : c1;
+        c2 = op.slot[i] == 2 ? v[i] : c2;
+        c3 = op.slot[i] == 3 ? v[i] : c3;
     }
+    for (int c = 0; c < nchunk; ++c) tc::tma_load_4d(dst + c * kChunkBytes, &op.map, c * 64, c1, c2, c3, bar);
+}
+
+__device__ __forceinline__ void bulk_store_s2g(void* gdst, const void* smem_src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(smem_src)),
+                 "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 
 __global__ void __launch_bounds__(kThreadsAttn, 1) attention_partial_kernel(const __grid_constant__ AttnParams P) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int nchunk = P.dpad >> 6;
-    uint8_t* sQ = smem;                                   // later P
-    uint8_t* sK = sQ + max(nchunk, 2) * kChunkBytes;      // P needs two 64-key blocks
-    uint8_t* sV = sK + nchunk * kChunkBytes;
-    AttnControl* ctl = reinterpret_cast<AttnControl*>(sV + nchunk * kChunkBytes);
+    uint8_t* sQ = smem;                                   // later P: 128 rows x 256 keys = four 64-key blocks
+    uint8_t* sKV = sQ + max(nchunk, 4) * kChunkBytes;     // two key tiles: K first, then V, then the staged partial O
+    const uint32_t tile_bytes = static_cast<uint32_t>(nchunk) * kChunkBytes;
+    AttnControl* ctl = reinterpret_cast<AttnControl*>(sKV + 2 * tile_bytes);
 
     const int rt = blockIdx.x, kt = blockIdx.y, g = blockIdx.z;
     const int ga = g / P.groups_inner, gb = g - ga * P.groups_inner;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int key0 = kt * kKeysCta;
+    const int nt = (P.n_keys - key0 > kKeyTile) ? 2 : 1;  // S tiles of this CTA
 
     if (threadIdx.x == 0) {
+        mbar_init(&ctl->bar_k0, 1);
+        mbar_init(&ctl->bar_k1, 1);
         mbar_init(&ctl->bar_s, 1);
+        mbar_init(&ctl->bar_v, 1);
         mbar_init(&ctl->bar_o, 1);
         fence_mbar_init();
+        tc::prefetch_tensormap(&P.q.map);
+        tc::prefetch_tensormap(&P.k.map);
+        tc::prefetch_tensormap(&P.v.map);
     }
     if (warp == 1) {
         // a whole, converged warp (not the one whose lane 0 just ran the barrier set-up on its own)
@@ -128,110 +158,152 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) attention_partial_kernel(cons
         tc::tmem_relinquish();
     }
     pdl_launch_dependents();
-    pdl_wait_prior_grids();                               // q, k, v come from the previous kernel
-
-    const __nv_bfloat16* q = P.q + ga * P.q_stride[0] + gb * P.q_stride[1];
-    const __nv_bfloat16* k = P.k + ga * P.k_stride[0] + gb * P.k_stride[1];
-    const __nv_bfloat16* v = P.v + ga * P.v_stride[0] + gb * P.v_stride[1];
-    load_tile(sQ, q, P.ldq, rt * kRows, P.n_rows, P.head_dim, P.dpad);
-    load_tile(sK, k, P.ldk, kt * kKeys, P.n_keys, P.head_dim, P.dpad);
-    load_tile(sV, v, P.ldv, kt * kKeys, P.n_keys, P.head_dim, P.dpad);
-    {
-        const int key = kt * kKeys + threadIdx.x;
-        float b = kMasked;                                // keys past the end never count
-        if (key < P.n_keys) b = P.key_bias != nullptr ? __bfloat162float(P.key_bias[key]) : 0.0f;
-        ctl->bias[threadIdx.x] = b;
-    }
-    cp_async_wait_all();
-    fence_proxy_async_smem();
     tc::fence_before_thread_sync();
     __syncthreads();
     tc::fence_after_thread_sync();
     const uint32_t tmem = ctl->tmem_base;
+    pdl_wait_prior_grids();                               // q, k, v (and the bias) may come from the previous kernel
 
-    // ---------------------------------------------------------------- S = Q K^T
-    if (threadIdx.x == 0) {
-        const uint32_t idesc = make_idesc_bf16(kKeys, 0);
-        const uint32_t q16 = smem_u32(sQ) >> 4, k16 = smem_u32(sK) >> 4;
-        const int ksteps = (P.head_dim + 15) >> 4;        // 16 columns of head_dim per MMA
-        for (int kk = 0; kk < ksteps; ++kk) {
-            const uint32_t off = static_cast<uint32_t>((kk >> 2) * kChunkBytes + (kk & 3) * 32) >> 4;
-            mma_bf16(tmem + kColS, tc::desc_from_words(q16 + off, tc::kDescHiKmajorSw128),
-                     tc::desc_from_words(k16 + off, tc::kDescHiKmajorSw128), idesc, kk > 0 ? 1u : 0u);
+    // warps 1..7: the keys' additive bias in the base-2 domain (visible to all after the barrier behind the S wait)
+    for (int i = threadIdx.x - 32; i >= 0 && i < kKeysCta; i += kThreadsAttn - 32) {
+        const int key = key0 + i;
+        float b = kFloor2;                                // keys past the end never count
+        if (key < P.n_keys) {
+            b = P.key_bias != nullptr ? fmaxf(__bfloat162float(P.key_bias[key]) * kLog2e, kFloor2) : 0.0f;
         }
-        tc::commit(&ctl->bar_s);
+        ctl->bias2[i] = b;
     }
-    // every wait is short (the MMAs behind it take microseconds) and its outcome is made uniform over the CTA:
+
+    // ---------------------------------------------------------------- loads, S = Q K^T (two key tiles)
+    if (threadIdx.x == 0) {
+        mbar_expect_tx(&ctl->bar_k0, 2 * tile_bytes);
+        load_rows(sQ, P.q, rt * kRows, ga, gb, nchunk, &ctl->bar_k0);
+        load_rows(sKV, P.k, key0, ga, gb, nchunk, &ctl->bar_k0);
+        if (nt == 2) {
+            mbar_expect_tx(&ctl->bar_k1, tile_bytes);
+            load_rows(sKV + tile_bytes, P.k, key0 + kKeyTile, ga, gb, nchunk, &ctl->bar_k1);
+        }
+        const uint32_t idesc = make_idesc_bf16(kKeyTile, 0);
+        const uint32_t q16 = smem_u32(sQ) >> 4;
+        const int ksteps = (P.head_dim + 15) >> 4;        // 16 columns of head_dim per MMA
+        bool loaded = true;
+        for (int t = 0; t < nt && loaded; ++t) {
+            loaded = mbar_wait_bounded(t == 0 ? &ctl->bar_k0 : &ctl->bar_k1, 0, kWaitCycles);
+            if (!loaded) {
+                record_error(kErrAttnBarrierTimeout);
+                break;
+            }
+            tc::fence_after_thread_sync();
+            const uint32_t k16 = (smem_u32(sKV) + t * tile_bytes) >> 4;
+            for (int kk = 0; kk < ksteps; ++kk) {
+                const uint32_t off = static_cast<uint32_t>((kk >> 2) * kChunkBytes + (kk & 3) * 32) >> 4;
+                mma_bf16(tmem + kColS + t * kKeyTile, tc::desc_from_words(q16 + off, tc::kDescHiKmajorSw128),
+                         tc::desc_from_words(k16 + off, tc::kDescHiKmajorSw128), idesc, kk > 0 ? 1u : 0u);
+            }
+        }
+        if (loaded) tc::commit(&ctl->bar_s);              // otherwise the wait below runs out for the whole CTA
+    }
+    // every wait is short (the work behind it takes microseconds) and its outcome is made uniform over the CTA:
     // the tensor-memory loads below are warp-collective
-    bool ok = mbar_wait_bounded(&ctl->bar_s, 0, kWaitCycles);
+    bool ok = mbar_wait_bounded(&ctl->bar_s, 0, 2 * kWaitCycles);
     if (!ok) record_error(kErrAttnBarrierTimeout);
     ok = __syncthreads_and(ok);
     tc::fence_after_thread_sync();
 
+    // the S MMAs have read K: V takes its place while the softmax runs
+    if (threadIdx.x == 0 && ok) {
+        mbar_expect_tx(&ctl->bar_v, nt * tile_bytes);
+        load_rows(sKV, P.v, key0, ga, gb, nchunk, &ctl->bar_v);
+        if (nt == 2) load_rows(sKV + tile_bytes, P.v, key0 + kKeyTile, ga, gb, nchunk, &ctl->bar_v);
+    }
+
     // ---------------------------------------------------------------- softmax of this block, P -> shared memory
-    const int row = threadIdx.x;                          // tensor-memory lane = query row of the tile
-    const uint32_t lane_addr = tmem + (static_cast<uint32_t>(warp * 32) << 16);
-    float m = -3.0e38f;
+    // Thread (half, row): the row's scores in columns [64 * half, 64 * half + 64) of each S tile.
+    const int row = threadIdx.x & (kRows - 1);            // tensor-memory lane = query row of the tile
+    const int half = threadIdx.x >> 7;
+    const uint32_t lane_addr = tmem + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+    float m = kFloor2;
     float l = 0.0f;
     if (ok) {
-        // the row's 128 scores: four tensor-memory loads in flight, one wait
-        uint32_t r[4][32];
+        // pass 1: the maximum over this thread's up to 128 scores (base-2 domain), all loads in flight at once
+        for (int t = 0; t < nt; ++t) {
+            uint32_t r[2][32];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) tc::tmem_ld_32x32b_x32(lane_addr + kColS + c * 32, r[c]);
-        tc::tmem_ld_wait();
-        float t[4][32];
+            for (int c = 0; c < 2; ++c) tc::tmem_ld_32x32b_x32(lane_addr + kColS + t * kKeyTile + half * 64 + c * 32, r[c]);
+            tc::tmem_ld_wait();
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                t[c][j] = fmaf(__uint_as_float(r[c][j]), P.scale, ctl->bias[c * 32 + j]);
-                m = fmaxf(m, t[c][j]);
+                for (int j = 0; j < 32; ++j) {
+                    m = fmaxf(m, fmaf(__uint_as_float(r[c][j]), P.scale2, ctl->bias2[t * kKeyTile + half * 64 + c * 32 + j]));
+                }
             }
         }
-        // p = exp(t - m) rounded to bf16 (what the PyTorch path feeds its second matmul), row sum of the
+        ctl->half_max[half][row] = m;
+    }
+    __syncthreads();
+    if (ok) {
+        m = fmaxf(m, ctl->half_max[half ^ 1][row]);
+        // pass 2: p = 2^(t - m) rounded to bf16 (what the PyTorch path feeds its second matmul), row sum of the
         // rounded values, 16-byte stores into the K-major image of P
         uint8_t* sP = sQ;
+        for (int t = 0; t < nt; ++t) {
+            uint32_t r[2][32];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) tc::tmem_ld_32x32b_x32(lane_addr + kColS + t * kKeyTile + half * 64 + c * 32, r[c]);
+            tc::tmem_ld_wait();
 #pragma unroll
-            for (int j8 = 0; j8 < 4; ++j8) {
-                uint32_t w[4];
+            for (int c = 0; c < 2; ++c) {
 #pragma unroll
-                for (int j2 = 0; j2 < 4; ++j2) {
-                    const int j = j8 * 8 + j2 * 2;
-                    const __nv_bfloat162 pb = __floats2bfloat162_rn(__expf(t[c][j] - m), __expf(t[c][j + 1] - m));
-                    l += __bfloat162float(pb.x) + __bfloat162float(pb.y);
-                    w[j2] = *reinterpret_cast<const uint32_t*>(&pb);
+                for (int j8 = 0; j8 < 4; ++j8) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int j2 = 0; j2 < 4; ++j2) {
+                        const int j = j8 * 8 + j2 * 2;
+                        const float* b2 = &ctl->bias2[t * kKeyTile + half * 64 + c * 32 + j];
+                        const float x0 = fmaf(__uint_as_float(r[c][j]), P.scale2, b2[0]) - m;
+                        const float x1 = fmaf(__uint_as_float(r[c][j + 1]), P.scale2, b2[1]) - m;
+                        const __nv_bfloat162 pb = __floats2bfloat162_rn(ex2(x0), ex2(x1));
+                        l += __bfloat162float(pb.x) + __bfloat162float(pb.y);
+                        w[j2] = *reinterpret_cast<const uint32_t*>(&pb);
+                    }
+                    const int ch = t * 16 + half * 8 + c * 4 + j8;   // 16-byte chunk of the 256-key row: 0..31
+                    uint8_t* dst = sP + (ch >> 3) * kChunkBytes + row * 128 + (((ch & 7) ^ (row & 7)) << 4);
+                    *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
-                const int ch = c * 4 + j8;                // 16-byte chunk of the 128-key row: 0..15
-                uint8_t* dst = sP + (ch >> 3) * kChunkBytes + row * 128 + (((ch & 7) ^ (row & 7)) << 4);
-                *reinterpret_cast<uint4*>(dst) = make_uint4(w[0], w[1], w[2], w[3]);
             }
         }
+        ctl->half_sum[half][row] = l;
     }
     fence_proxy_async_smem();
     tc::fence_before_thread_sync();
     __syncthreads();
     tc::fence_after_thread_sync();
+    if (ok) l += ctl->half_sum[half ^ 1][row];
 
     // ---------------------------------------------------------------- O = P V
     if (threadIdx.x == 0 && ok) {
-        const uint32_t idesc = make_idesc_bf16(P.dv, 1);  // B = V read MN-major
-        const uint32_t p16 = smem_u32(sQ) >> 4, v16 = smem_u32(sV) >> 4;
-        // MN-major, 128-byte swizzle: 64 columns of head_dim are contiguous, 8-key groups 1024 B apart
-        // (stride offset), the next 64 columns one 16 KB block further (leading offset)
-        constexpr uint32_t kDescHiMnSw128 = (1024u >> 4) | (1u << 14) | (static_cast<uint32_t>(tc::kSwizzle128B) << 29);
-        constexpr uint32_t kLboField = (static_cast<uint32_t>(kChunkBytes) >> 4) << 16;
-        for (int kk = 0; kk < kKeys / 16; ++kk) {
-            const uint32_t a_off = static_cast<uint32_t>((kk >> 2) * kChunkBytes + (kk & 3) * 32) >> 4;
-            const uint32_t b_off = static_cast<uint32_t>(kk * 2048) >> 4;
-            mma_bf16(tmem + kColO, tc::desc_from_words(p16 + a_off, tc::kDescHiKmajorSw128),
-                     tc::desc_from_words((v16 + b_off) | kLboField, kDescHiMnSw128), idesc, kk > 0 ? 1u : 0u);
+        if (mbar_wait_bounded(&ctl->bar_v, 0, kWaitCycles)) {
+            tc::fence_after_thread_sync();
+            const uint32_t idesc = make_idesc_bf16(P.dv, 1);  // B = V read MN-major
+            const uint32_t p16 = smem_u32(sQ) >> 4;
+            // MN-major, 128-byte swizzle: 64 columns of head_dim are contiguous, 8-key groups 1024 B apart
+            // (stride offset), the next 64 columns one 16 KB block further (leading offset)
+            constexpr uint32_t kDescHiMnSw128 = (1024u >> 4) | (1u << 14) | (static_cast<uint32_t>(tc::kSwizzle128B) << 29);
+            constexpr uint32_t kLboField = (static_cast<uint32_t>(kChunkBytes) >> 4) << 16;
+            for (int kk = 0; kk < nt * (kKeyTile / 16); ++kk) {
+                const uint32_t a_off = static_cast<uint32_t>((kk >> 2) * kChunkBytes + (kk & 3) * 32) >> 4;
+                const uint32_t v16 = (smem_u32(sKV) + (kk >> 3) * tile_bytes + (kk & 7) * 2048) >> 4;
+                mma_bf16(tmem + kColO, tc::desc_from_words(p16 + a_off, tc::kDescHiKmajorSw128),
+                         tc::desc_from_words(v16 | kLboField, kDescHiMnSw128), idesc, kk > 0 ? 1u : 0u);
+            }
+            tc::commit(&ctl->bar_o);
+        } else {
+            record_error(kErrAttnBarrierTimeout);         // the wait below runs out for the whole CTA
         }
-        tc::commit(&ctl->bar_o);
     }
     if (ok) {
-        ok = mbar_wait_bounded(&ctl->bar_o, 0, kWaitCycles);
+        ok = mbar_wait_bounded(&ctl->bar_o, 0, 2 * kWaitCycles);
         if (!ok) record_error(kErrAttnBarrierTimeout);
     }
     ok = __syncthreads_and(ok);
@@ -239,21 +311,23 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) attention_partial_kernel(cons
 
     // ---------------------------------------------------------------- write the rows
     // The tensor-memory loads are warp-collective: every lane executes them, rows past the end of the matrix
-    // only skip the stores.
+    // only skip the stores.  With a single key tile the rows are final (bf16, normalised); otherwise the
+    // unnormalised fp32 rows are staged in shared memory where V was (chunk c of row r at c ^ (r & 7), so the
+    // stores of a quarter warp spread over all banks) and leave as ONE bulk copy, image and all.
     const int grow = rt * kRows + row;
     const bool store = grow < P.n_rows;
+    const bool final_rows = P.key_tiles == 1;
+    const size_t tile = (static_cast<size_t>(g) * P.row_tiles + rt) * P.key_tiles + kt;
     if (ok) {
-        const bool final_rows = P.key_tiles == 1;
         __nv_bfloat16* o = P.out + ga * P.o_stride[0] + gb * P.o_stride[1] + static_cast<size_t>(store ? grow : 0) * P.ldo;
-        const size_t tile = (static_cast<size_t>(g) * P.row_tiles + rt) * P.key_tiles + kt;
-        float* po = P.part_o + (tile * kRows + row) * P.dv;
-        if (!final_rows && store) {
+        uint8_t* srow = sKV + static_cast<size_t>(row) * P.dvp * 4;
+        if (!final_rows && store && half == 0) {
             float* pml = P.part_ml + (tile * kRows + row) * 2;
             pml[0] = m;
             pml[1] = l;
         }
         const float inv = 1.0f / l;
-        for (int c64 = 0; c64 < P.dv; c64 += 64) {
+        for (int c64 = half * 64; c64 < P.dv; c64 += 128) {   // the halves take alternate 64-column batches
             // up to four 16-column loads in flight, one wait
             uint32_t r4[4][16];
 #pragma unroll
@@ -270,13 +344,13 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) attention_partial_kernel(cons
                 }
             }
             tc::tmem_ld_wait();
-            if (!store) continue;
 #pragma unroll
             for (int q4 = 0; q4 < 4; ++q4) {
                 const int c0 = c64 + q4 * 16;
                 if (c0 >= P.dv) continue;
                 const uint32_t(&r)[16] = r4[q4];
                 if (final_rows) {
+                    if (!store) continue;
 #pragma unroll
                     for (int j = 0; j < 16; j += 8) {
                         if (c0 + j < P.head_dim) {            // head_dim is a multiple of 8
@@ -293,21 +367,29 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) attention_partial_kernel(cons
                 } else {
 #pragma unroll
                     for (int j = 0; j < 16; j += 4) {
-                        *reinterpret_cast<uint4*>(po + c0 + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+                        const int ch = (c0 + j) >> 2;
+                        *reinterpret_cast<uint4*>(srow + ((ch ^ (row & 7)) << 4)) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
                     }
                 }
             }
         }
     }
+    fence_proxy_async_smem();
     tc::fence_before_thread_sync();
     __syncthreads();
+    if (threadIdx.x == 0 && ok && !final_rows) {
+        const uint32_t bytes = static_cast<uint32_t>(kRows) * P.dvp * 4;
+        bulk_store_s2g(P.part_o + tile * kRows * P.dvp, sKV, bytes);
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // shared memory stays valid until the copy is done
+    }
     if (warp == 1) {
         tc::fence_after_thread_sync();
         tc::tmem_dealloc(tmem, kTmemColsAttn);
     }
 }
 
-// out[row] = sum_j w_j O_j / sum_j w_j l_j with w_j = exp(m_j - max_j m_j): one thread per 8 output columns
+// out[row] = sum_j w_j O_j / sum_j w_j l_j with w_j = 2^(m_j - max_j m_j): one thread per 8 output columns
 __global__ void __launch_bounds__(256) attention_combine_kernel(const __grid_constant__ AttnParams P, int groups) {
     pdl_launch_dependents();
     pdl_wait_prior_grids();
@@ -322,16 +404,17 @@ __global__ void __launch_bounds__(256) attention_combine_kernel(const __grid_con
     const int ga = g / P.groups_inner, gb = g - ga * P.groups_inner;
     const int rt = grow / kRows, row = grow - rt * kRows;
     const size_t tile0 = (static_cast<size_t>(g) * P.row_tiles + rt) * P.key_tiles;
-    float mmax = -3.0e38f;
+    float mmax = kFloor2;
     for (int j = 0; j < P.key_tiles; ++j) mmax = fmaxf(mmax, P.part_ml[((tile0 + j) * kRows + row) * 2]);
     float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
     float lsum = 0.0f;
+    const int sw = row & 7;
     for (int j = 0; j < P.key_tiles; ++j) {
         const float* ml = P.part_ml + ((tile0 + j) * kRows + row) * 2;
-        const float w = __expf(ml[0] - mmax);
+        const float w = ex2(ml[0] - mmax);
         lsum = fmaf(w, ml[1], lsum);
-        const float4* po = reinterpret_cast<const float4*>(P.part_o + ((tile0 + j) * kRows + row) * P.dv + c * 8);
-        const float4 a = po[0], b = po[1];
+        const float4* po = reinterpret_cast<const float4*>(P.part_o + ((tile0 + j) * kRows + row) * P.dvp);
+        const float4 a = po[(2 * c) ^ sw], b = po[(2 * c + 1) ^ sw];
         acc[0] = fmaf(w, a.x, acc[0]); acc[1] = fmaf(w, a.y, acc[1]); acc[2] = fmaf(w, a.z, acc[2]); acc[3] = fmaf(w, a.w, acc[3]);
         acc[4] = fmaf(w, b.x, acc[4]); acc[5] = fmaf(w, b.y, acc[5]); acc[6] = fmaf(w, b.z, acc[6]); acc[7] = fmaf(w, b.w, acc[7]);
     }
@@ -355,7 +438,7 @@ int device_error_attention(int clear) { return read_device_error(clear); }
 namespace {
 
 struct AttnDims {
-    int row_tiles, key_tiles, dpad, dv, groups;
+    int row_tiles, key_tiles, dpad, dv, dvp, groups;
     size_t part_o_floats, part_ml_floats;
 };
 
@@ -363,15 +446,58 @@ int attn_dims(int n_rows, int n_keys, int head_dim, int groups, AttnDims& d) {
     TPB_REQUIRE(n_rows >= 1 && n_keys >= 1 && groups >= 1, TPB200_ERR_SHAPE);
     TPB_REQUIRE(head_dim >= 8 && head_dim <= 256 && head_dim % 8 == 0, TPB200_ERR_SHAPE);
     d.row_tiles = (n_rows + 127) / 128;
-    d.key_tiles = (n_keys + 127) / 128;
+    d.key_tiles = (n_keys + 255) / 256;
     d.dpad = (head_dim + 63) / 64 * 64;
     d.dv = (head_dim + 15) / 16 * 16;
+    d.dvp = (head_dim + 31) / 32 * 32;
     d.groups = groups;
     TPB_REQUIRE(d.key_tiles <= 65535 && groups <= 65535, TPB200_ERR_SHAPE);
     const size_t tiles = static_cast<size_t>(groups) * d.row_tiles * d.key_tiles;
-    d.part_o_floats = d.key_tiles > 1 ? tiles * 128 * d.dv : 0;
+    d.part_o_floats = d.key_tiles > 1 ? tiles * 128 * d.dvp : 0;
     d.part_ml_floats = d.key_tiles > 1 ? tiles * 128 * 2 : 0;
     return TPB200_OK;
+}
+
+// Tensor map of one operand: [outer groups][inner groups][rows][head_dim] with element strides (stride[0],
+// stride[1], ld, 1).  The three outer dimensions go into the map by ascending stride; a group dimension
+// with stride 0 (every group reads the same rows) becomes a dimension of size 1 whose coordinate stays 0.
+bool attn_operand(tpb::AttnOperand& op, const void* base, int head_dim, int rows, long long ld, int groups_inner,
+                  long long stride_inner, int groups_outer, long long stride_outer) {
+    struct Dim { uint64_t size, stride_bytes; int role; };
+    Dim dims[3] = {{static_cast<uint64_t>(rows), static_cast<uint64_t>(ld) * 2, 0},
+                   {static_cast<uint64_t>(groups_inner), static_cast<uint64_t>(stride_inner) * 2, 1},
+                   {static_cast<uint64_t>(groups_outer), static_cast<uint64_t>(stride_outer) * 2, 2}};
+    for (int i = 0; i < 3; ++i) op.mul[i] = 1;
+    for (int i = 1; i < 3; ++i) {
+        if (dims[i].size == 1 || dims[i].stride_bytes == 0) {
+            dims[i].size = 1;
+            dims[i].stride_bytes = 0;                    // placed last, stride chosen below
+            op.mul[i] = 0;
+        }
+    }
+    // order: real dimensions by ascending stride, then the size-1 ones
+    int order[3] = {0, 1, 2};
+    std::sort(order, order + 3, [&](int a, int b) {
+        const bool ua = dims[a].stride_bytes == 0, ub = dims[b].stride_bytes == 0;
+        if (ua != ub) return ub;
+        if (dims[a].stride_bytes != dims[b].stride_bytes) return dims[a].stride_bytes < dims[b].stride_bytes;
+        return a < b;
+    });
+    uint64_t gdims[4] = {static_cast<uint64_t>(head_dim), 0, 0, 0};
+    uint64_t strides[3];
+    uint32_t box[4] = {64, 1, 1, 1};
+    uint64_t span = 0;
+    for (int pos = 0; pos < 3; ++pos) {
+        const Dim& dm = dims[order[pos]];
+        uint64_t st = dm.stride_bytes;
+        if (st == 0) st = std::max<uint64_t>(span, 16);
+        gdims[pos + 1] = dm.size;
+        strides[pos] = st;
+        span = std::max(span, (st * dm.size + 15) / 16 * 16);
+        op.slot[dm.role] = pos + 1;
+        if (dm.role == 0) box[pos + 1] = 128;
+    }
+    return tpb::make_tensor_map_bf16_nd_sw128(&op.map, base, 4, gdims, strides, box);
 }
 
 }  // namespace
@@ -398,6 +524,7 @@ extern "C" int tpb200_attention(const tpb200_attention_args* a, tpb200_stream_t 
     for (int i = 0; i < 2; ++i) {
         TPB_REQUIRE(a->q_stride[i] % 8 == 0 && a->k_stride[i] % 8 == 0 && a->v_stride[i] % 8 == 0 && a->o_stride[i] % 8 == 0,
                     TPB200_ERR_ALIGN);
+        TPB_REQUIRE(a->q_stride[i] >= 0 && a->k_stride[i] >= 0 && a->v_stride[i] >= 0 && a->o_stride[i] >= 0, TPB200_ERR_SHAPE);
     }
     const size_t need = (d.part_o_floats + d.part_ml_floats) * sizeof(float);
     if (need > 0) {
@@ -406,9 +533,14 @@ extern "C" int tpb200_attention(const tpb200_attention_args* a, tpb200_stream_t 
     }
 
     tpb::AttnParams P = {};
-    P.q = static_cast<const __nv_bfloat16*>(a->q);
-    P.k = static_cast<const __nv_bfloat16*>(a->k);
-    P.v = static_cast<const __nv_bfloat16*>(a->v);
+    if (!attn_operand(P.q, a->q, a->head_dim, a->n_rows, a->ldq, a->groups_inner, a->q_stride[1], a->groups_outer,
+                      a->q_stride[0]) ||
+        !attn_operand(P.k, a->k, a->head_dim, a->n_keys, a->ldk, a->groups_inner, a->k_stride[1], a->groups_outer,
+                      a->k_stride[0]) ||
+        !attn_operand(P.v, a->v, a->head_dim, a->n_keys, a->ldv, a->groups_inner, a->v_stride[1], a->groups_outer,
+                      a->v_stride[0])) {
+        return TPB200_ERR_SHAPE;
+    }
     P.out = static_cast<__nv_bfloat16*>(a->out);
     P.key_bias = static_cast<const __nv_bfloat16*>(a->key_bias);
     P.n_rows = a->n_rows;
@@ -416,25 +548,18 @@ extern "C" int tpb200_attention(const tpb200_attention_args* a, tpb200_stream_t 
     P.head_dim = a->head_dim;
     P.dpad = d.dpad;
     P.dv = d.dv;
-    P.ldq = a->ldq;
-    P.ldk = a->ldk;
-    P.ldv = a->ldv;
+    P.dvp = d.dvp;
     P.ldo = a->ldo;
     P.groups_inner = a->groups_inner;
-    for (int i = 0; i < 2; ++i) {
-        P.q_stride[i] = a->q_stride[i];
-        P.k_stride[i] = a->k_stride[i];
-        P.v_stride[i] = a->v_stride[i];
-        P.o_stride[i] = a->o_stride[i];
-    }
-    P.scale = a->scale;
+    for (int i = 0; i < 2; ++i) P.o_stride[i] = a->o_stride[i];
+    P.scale2 = a->scale * 1.4426950408889634f;
     P.row_tiles = d.row_tiles;
     P.key_tiles = d.key_tiles;
     P.part_o = static_cast<float*>(a->workspace);
     P.part_ml = P.part_o + d.part_o_floats;
 
     const int nchunk = d.dpad / 64;
-    const size_t smem = static_cast<size_t>(std::max(nchunk, 2) + 2 * nchunk) * tpb::kChunkBytes + sizeof(tpb::AttnControl) + 1024;
+    const size_t smem = static_cast<size_t>(std::max(nchunk, 4) + 2 * nchunk) * tpb::kChunkBytes + sizeof(tpb::AttnControl) + 1024;
     static std::atomic<uint64_t> configured{0};
     int dev = 0;
     cudaGetDevice(&dev);

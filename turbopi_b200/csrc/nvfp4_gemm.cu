@@ -954,6 +954,25 @@ bool make_tensor_map_bytes_sw128(CUtensorMap* map, const void* base, uint64_t ro
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// bf16 tensor of `rank` (2..5) dimensions, dims[0] contiguous, strides_bytes[i] = byte stride of dims[i + 1];
+// box[0] <= 64 elements (one 128-byte swizzle row), elements past the end of a dimension read as zero.
+bool make_tensor_map_bf16_nd_sw128(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
+                                   const uint64_t* strides_bytes, const uint32_t* box) {
+    EncodeFn fn = get_encode_fn();
+    if (fn == nullptr || rank < 2 || rank > 5) return false;
+    cuuint64_t d[5], st[4];
+    cuuint32_t b[5], es[5];
+    for (int i = 0; i < rank; ++i) {
+        d[i] = dims[i];
+        b[i] = box[i];
+        es[i] = 1;
+        if (i + 1 < rank) st[i] = strides_bytes[i];
+    }
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, static_cast<cuuint32_t>(rank), const_cast<void*>(base), d, st, b, es,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 // Output matrix [rows, cols] of bf16 / fp32 elements, box = 128 rows x 128 bytes, 128-byte swizzle.
 bool make_tensor_map_out_sw128(CUtensorMap* map, void* base, int dtype, uint64_t cols, uint64_t rows,
                                uint64_t pitch_bytes) {

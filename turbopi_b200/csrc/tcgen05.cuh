@@ -128,6 +128,14 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
         "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
         : "memory");
 }
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* map, int c0, int c1, int c2, int c3,
+                                            uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], "
+        "[%6];" ::"r"(smem_u32(smem_dst)),
+        "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(smem_u32(bar))
+        : "memory");
+}
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -151,5 +159,10 @@ __device__ __forceinline__ bool elect_one() {
 // Returns false if the driver entry point is unavailable or refuses the shape.
 bool make_tensor_map_bytes_sw128(CUtensorMap* map, const void* base, uint64_t row_bytes, uint64_t rows,
                                  uint64_t pitch_bytes, uint32_t box_rows);
+
+// bf16 tensor of 2..5 dimensions (dims[0] contiguous, strides_bytes[i] = byte stride of dims[i + 1], multiples of
+// 16), box[0] <= 64 elements, 128-byte swizzle, zero fill past the end of every dimension.
+bool make_tensor_map_bf16_nd_sw128(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
+                                   const uint64_t* strides_bytes, const uint32_t* box);
 
 }  // namespace tpb
