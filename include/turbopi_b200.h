@@ -68,7 +68,12 @@ enum {
     TPB200_FLAG_NONE = 0,
     TPB200_FLAG_PDL = 1 /* launch with programmatic stream serialisation: the kernel prefetches its
                            weights while the previous kernel in the stream is still running, and
-                           waits for that kernel before it reads activations or writes outputs */
+                           waits for that kernel before it reads activations or writes outputs.
+                           Requirement on the caller: weight images, scales and bias must be COMPLETE
+                           before a launch with this flag is enqueued -- a kernel that prepares them
+                           (tpb200_nvfp4_tile_weights, quantizeWeightToNVFP4, ...) must not be the
+                           launch's immediate predecessor in the stream; put a stream or event
+                           synchronisation, or any launch without the flag, in between. */
 };
 
 int tpb200_version(void);
@@ -76,7 +81,10 @@ const char* tpb200_status_string(int status);
 /* last non-OK status produced on this host thread by a void-returning entry point (and clears it) */
 int tpb200_last_error(void);
 /* code recorded by a kernel whose bounded wait ran out on the current device, 0 if none; synchronises
- * the device.  `clear` != 0 resets the word. */
+ * the device.  `clear` != 0 resets the word.
+ * Recovery: a kernel that gave up may have left its split-K counters non-zero.  After a non-zero code
+ * every workspace that was passed to a GEMM / GEMV / attention launch since the last check must be set
+ * to zero again (cudaMemsetAsync) before it is reused; results of the failed launch are undefined. */
 int tpb200_device_error(int clear);
 
 /* ---------------------------------------------------------------------------------------------

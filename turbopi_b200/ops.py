@@ -470,6 +470,9 @@ def tile_weights(b_packed, b_sf, N, K):
         st = _lib.load().tpb200_nvfp4_tile_weights(_ptr(b_packed), b_packed.stride(0), _ptr(b_sf), _ptr(image), N, K,
                                                    _stream(b_packed))
     _lib.check(st, "tpb200_nvfp4_tile_weights")
+    # weight preparation is a one-off: finish it here, so that a following launch with FLAG_PDL (which reads
+    # weights before it waits for its predecessor) can never start on an incomplete image
+    torch.cuda.current_stream(b_packed.device).synchronize()
     return image
 
 
