@@ -312,6 +312,13 @@ typedef struct {
     float scale;
     void* workspace; size_t workspace_bytes;
     int flags;
+    /* Optional fused hand-over to the next linear (single problem only, groups 1 x 1): when quant_image is not
+     * NULL, every token (= quant_rows_per_token consecutive rows, K = quant_rows_per_token * head_dim, a
+     * multiple of 256, <= 8192) is also written as a row of the tiled A image of tpb200_nvfp4_gemm_ex
+     * (quant_pieces residual pieces, quant_row_scale[token] = the row multiplier), exactly as
+     * tpb200_row_transform_quantize in plain mode would produce from `out`; `out` may then be NULL.  Needs the
+     * workspace whatever the key count. */
+    void* quant_image; float* quant_row_scale; int quant_pieces; int quant_rows_per_token;
 } tpb200_attention_args;
 size_t tpb200_attention_workspace_size(int n_rows, int n_keys, int head_dim, int groups);
 int tpb200_attention(const tpb200_attention_args* args, tpb200_stream_t stream);

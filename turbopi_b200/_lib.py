@@ -65,7 +65,9 @@ class AttentionArgs(ctypes.Structure):
                 ("groups_outer", c_int), ("groups_inner", c_int),
                 ("q_stride", ctypes.c_longlong * 2), ("k_stride", ctypes.c_longlong * 2),
                 ("v_stride", ctypes.c_longlong * 2), ("o_stride", ctypes.c_longlong * 2),
-                ("scale", c_float), ("workspace", c_void_p), ("workspace_bytes", c_size_t), ("flags", c_int)]
+                ("scale", c_float), ("workspace", c_void_p), ("workspace_bytes", c_size_t), ("flags", c_int),
+                ("quant_image", c_void_p), ("quant_row_scale", c_void_p), ("quant_pieces", c_int),
+                ("quant_rows_per_token", c_int)]
 
 
 class ActTc(ctypes.Structure):

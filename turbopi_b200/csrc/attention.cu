@@ -69,6 +69,12 @@ struct AttnParams {
     float* part_ml;                             // [group][row tile][key tile][128][2]
     int dv;                                     // head_dim rounded up to 16: N of the second MMA
     int dvp;                                    // head_dim rounded up to 32: row pitch of a partial image
+    // optional: the merged rows also leave as the tiled A image of the tensor-core GEMM that follows
+    // (token = rows_per_token consecutive rows = one row of the image, K = rows_per_token * head_dim)
+    uint8_t* qa_image;
+    float* qa_row_scale;
+    int qa_pieces;
+    int qa_rows_per_token;
 };
 
 struct AttnControl {
@@ -316,7 +322,7 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) attention_partial_kernel(cons
     // stores of a quarter warp spread over all banks) and leave as ONE bulk copy, image and all.
     const int grow = rt * kRows + row;
     const bool store = grow < P.n_rows;
-    const bool final_rows = P.key_tiles == 1;
+    const bool final_rows = P.key_tiles == 1 && P.qa_image == nullptr;
     const size_t tile = (static_cast<size_t>(g) * P.row_tiles + rt) * P.key_tiles + kt;
     if (ok) {
         __nv_bfloat16* o = P.out + ga * P.o_stride[0] + gb * P.o_stride[1] + static_cast<size_t>(store ? grow : 0) * P.ldo;
@@ -429,6 +435,78 @@ __global__ void __launch_bounds__(256) attention_combine_kernel(const __grid_con
     *reinterpret_cast<uint4*>(o) = make_uint4(w[0], w[1], w[2], w[3]);
 }
 
+// The merge of attention_combine_kernel for ONE token per CTA (rows_per_token consecutive rows, one thread per
+// 8 output columns), followed by what the row kernel's plain mode would do with that token's row of
+// K = rows_per_token * head_dim bf16 values: row maximum -> power-of-two pre-scale into [1024, 2048) -> residual
+// e2m1 pieces with UE4M3 block scales, written into the tiled A image of the next GEMM.  A 16-element block is
+// shared by two adjacent threads.  Same arithmetic, bit for bit, as merge + bf16 store + row kernel.
+__global__ void __launch_bounds__(1024) attention_combine_quant_kernel(const __grid_constant__ AttnParams P) {
+    __shared__ float red[32];
+    pdl_launch_dependents();
+    pdl_wait_prior_grids();
+    const int c8 = P.head_dim >> 3;
+    const int token = blockIdx.x;
+    const int rin = threadIdx.x / c8, c = threadIdx.x - rin * c8;
+    const int grow = token * P.qa_rows_per_token + rin;
+    const int rt = grow / kRows, row = grow - rt * kRows;
+    const size_t tile0 = static_cast<size_t>(rt) * P.key_tiles;
+    float mmax = kFloor2;
+    for (int j = 0; j < P.key_tiles; ++j) mmax = fmaxf(mmax, P.part_ml[((tile0 + j) * kRows + row) * 2]);
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    float lsum = 0.0f;
+    const int sw = row & 7;
+    for (int j = 0; j < P.key_tiles; ++j) {
+        const float* ml = P.part_ml + ((tile0 + j) * kRows + row) * 2;
+        const float w = ex2(ml[0] - mmax);
+        lsum = fmaf(w, ml[1], lsum);
+        const float4* po = reinterpret_cast<const float4*>(P.part_o + ((tile0 + j) * kRows + row) * P.dvp);
+        const float4 a = po[(2 * c) ^ sw], b = po[(2 * c + 1) ^ sw];
+        acc[0] = fmaf(w, a.x, acc[0]); acc[1] = fmaf(w, a.y, acc[1]); acc[2] = fmaf(w, a.z, acc[2]); acc[3] = fmaf(w, a.w, acc[3]);
+        acc[4] = fmaf(w, b.x, acc[4]); acc[5] = fmaf(w, b.y, acc[5]); acc[6] = fmaf(w, b.z, acc[6]); acc[7] = fmaf(w, b.w, acc[7]);
+    }
+    const float inv = 1.0f / lsum;
+    uint32_t w[4];
+    float r[8];
+    float amax = 0.0f;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const __nv_bfloat162 b = __floats2bfloat162_rn(acc[2 * e] * inv, acc[2 * e + 1] * inv);
+        w[e] = *reinterpret_cast<const uint32_t*>(&b);
+        r[2 * e] = __bfloat162float(b.x);            // the quantiser sees the bf16 values a reader of `out` would
+        r[2 * e + 1] = __bfloat162float(b.y);
+        amax = fmaxf(amax, fmaxf(fabsf(r[2 * e]), fabsf(r[2 * e + 1])));
+    }
+    if (P.out != nullptr) {
+        __nv_bfloat16* o = P.out + static_cast<size_t>(grow) * P.ldo + c * 8;
+        *reinterpret_cast<uint4*>(o) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    // the token's maximum over the whole CTA
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = 0.0f;
+    for (int i = 0; i < static_cast<int>(blockDim.x >> 5); ++i) amax = fmaxf(amax, red[i]);
+    const int e = prescale_exponent(amax);
+    const float pre = ldexpf(1.0f, e);
+    if (threadIdx.x == 0) P.qa_row_scale[token] = ldexpf(1.0f, -e);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) r[i] *= pre;
+    // block (token / 128, kb / 16) of the image: [piece][128 rows][128 B, 16-byte chunks XOR-swizzled by row & 7],
+    // then [piece][4 atoms of 512 B]; this thread holds half `hb` of 16-element block kb of the token's row
+    const int kb = threadIdx.x >> 1, hb = threadIdx.x & 1;
+    const int kb_blocks = (P.qa_rows_per_token * P.head_dim) >> 8;       // 256-wide K stages of the row
+    const int rr = token & 127, jj = kb & 15;
+    uint8_t* blk = P.qa_image + (static_cast<size_t>(token >> 7) * kb_blocks + (kb >> 4)) * (static_cast<size_t>(P.qa_pieces) * 18432);
+    for (int p = 0; p < P.qa_pieces; ++p) {
+        uint32_t word;
+        const uint8_t code = quantize_half8_piece(r, word);
+        uint8_t* code_dst = blk + p * 16384 + rr * 128 + (((jj >> 1) ^ (rr & 7)) << 4) + (jj & 1) * 8 + hb * 4;
+        *reinterpret_cast<uint32_t*>(code_dst) = word;
+        if (hb == 0) blk[P.qa_pieces * 16384 + p * 2048 + (jj >> 2) * 512 + (rr & 31) * 16 + (rr >> 5) * 4 + (jj & 3)] = code;
+    }
+}
+
 }  // namespace
 
 int device_error_attention(int clear) { return read_device_error(clear); }
@@ -453,8 +531,8 @@ int attn_dims(int n_rows, int n_keys, int head_dim, int groups, AttnDims& d) {
     d.groups = groups;
     TPB_REQUIRE(d.key_tiles <= 65535 && groups <= 65535, TPB200_ERR_SHAPE);
     const size_t tiles = static_cast<size_t>(groups) * d.row_tiles * d.key_tiles;
-    d.part_o_floats = d.key_tiles > 1 ? tiles * 128 * d.dvp : 0;
-    d.part_ml_floats = d.key_tiles > 1 ? tiles * 128 * 2 : 0;
+    d.part_o_floats = tiles * 128 * d.dvp;      // unused by a launch with one key tile and no fused quantiser
+    d.part_ml_floats = tiles * 128 * 2;
     return TPB200_OK;
 }
 
@@ -510,7 +588,9 @@ extern "C" size_t tpb200_attention_workspace_size(int n_rows, int n_keys, int he
 
 extern "C" int tpb200_attention(const tpb200_attention_args* a, tpb200_stream_t stream) {
     TPB_REQUIRE(a != nullptr, TPB200_ERR_NULL);
-    TPB_REQUIRE(a->q && a->k && a->v && a->out, TPB200_ERR_NULL);
+    TPB_REQUIRE(a->q && a->k && a->v, TPB200_ERR_NULL);
+    const bool quant = a->quant_image != nullptr;
+    TPB_REQUIRE(a->out != nullptr || quant, TPB200_ERR_NULL);
     TPB_REQUIRE((a->flags & ~TPB200_FLAG_PDL) == 0, TPB200_ERR_ENUM);
     TPB_REQUIRE(a->groups_outer >= 1 && a->groups_inner >= 1, TPB200_ERR_SHAPE);
     AttnDims d;
@@ -526,7 +606,17 @@ extern "C" int tpb200_attention(const tpb200_attention_args* a, tpb200_stream_t 
                     TPB200_ERR_ALIGN);
         TPB_REQUIRE(a->q_stride[i] >= 0 && a->k_stride[i] >= 0 && a->v_stride[i] >= 0 && a->o_stride[i] >= 0, TPB200_ERR_SHAPE);
     }
-    const size_t need = (d.part_o_floats + d.part_ml_floats) * sizeof(float);
+    if (quant) {
+        // one token = rows_per_token consecutive rows = one row of the GEMM operand, K = rows_per_token * head_dim
+        TPB_REQUIRE(a->groups_outer == 1 && a->groups_inner == 1, TPB200_ERR_SHAPE);
+        TPB_REQUIRE(a->quant_row_scale != nullptr, TPB200_ERR_NULL);
+        TPB_REQUIRE(a->quant_pieces >= 1 && a->quant_pieces <= 3, TPB200_ERR_SHAPE);
+        TPB_REQUIRE(a->quant_rows_per_token >= 1 && a->n_rows % a->quant_rows_per_token == 0, TPB200_ERR_SHAPE);
+        const long long K = static_cast<long long>(a->quant_rows_per_token) * a->head_dim;
+        TPB_REQUIRE(K % 256 == 0 && K / 8 <= 1024, TPB200_ERR_SHAPE);
+        TPB_REQUIRE(tpb_aligned16(a->quant_image), TPB200_ERR_ALIGN);
+    }
+    const size_t need = (d.key_tiles > 1 || quant) ? (d.part_o_floats + d.part_ml_floats) * sizeof(float) : 0;
     if (need > 0) {
         TPB_REQUIRE(a->workspace != nullptr && a->workspace_bytes >= need, TPB200_ERR_WORKSPACE);
         TPB_REQUIRE((reinterpret_cast<uintptr_t>(a->workspace) & 255u) == 0, TPB200_ERR_ALIGN);
@@ -557,6 +647,10 @@ extern "C" int tpb200_attention(const tpb200_attention_args* a, tpb200_stream_t 
     P.key_tiles = d.key_tiles;
     P.part_o = static_cast<float*>(a->workspace);
     P.part_ml = P.part_o + d.part_o_floats;
+    P.qa_image = static_cast<uint8_t*>(a->quant_image);
+    P.qa_row_scale = a->quant_row_scale;
+    P.qa_pieces = a->quant_pieces;
+    P.qa_rows_per_token = a->quant_rows_per_token;
 
     const int nchunk = d.dpad / 64;
     const size_t smem = static_cast<size_t>(std::max(nchunk, 4) + 2 * nchunk) * tpb::kChunkBytes + sizeof(tpb::AttnControl) + 1024;
@@ -584,7 +678,15 @@ extern "C" int tpb200_attention(const tpb200_attention_args* a, tpb200_stream_t 
         cfg.numAttrs = 1;
     }
     if (cudaLaunchKernelEx(&cfg, tpb::attention_partial_kernel, P) != cudaSuccess) return TPB200_ERR_CUDA;
-    if (d.key_tiles > 1) {
+    if (quant) {
+        cudaLaunchConfig_t c2 = {};
+        c2.gridDim = dim3(static_cast<unsigned>(a->n_rows / a->quant_rows_per_token), 1, 1);
+        c2.blockDim = dim3(static_cast<unsigned>(a->quant_rows_per_token * a->head_dim / 8), 1, 1);
+        c2.stream = reinterpret_cast<cudaStream_t>(stream);
+        c2.attrs = attr;
+        c2.numAttrs = 1;
+        if (cudaLaunchKernelEx(&c2, tpb::attention_combine_quant_kernel, P) != cudaSuccess) return TPB200_ERR_CUDA;
+    } else if (d.key_tiles > 1) {
         const long long threads = static_cast<long long>(d.groups) * a->n_rows * (a->head_dim / 8);
         cudaLaunchConfig_t c2 = {};
         c2.gridDim = dim3(static_cast<unsigned>((threads + 255) / 256), 1, 1);

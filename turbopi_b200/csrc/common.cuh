@@ -222,6 +222,46 @@ __device__ __forceinline__ uint8_t quantize_block16_piece(float (&r)[16], uint32
     return code;
 }
 
+// The same piece for a 16-element block held by TWO adjacent lanes (eight elements each, the even lane the
+// first eight): the block maximum crosses the pair with one shuffle, both lanes derive the same scale, each
+// returns the 32-bit word of its own eight codes.  Bit-identical to quantize_block16_piece.  All 32 lanes of
+// the warp must call it together.
+__device__ __forceinline__ uint8_t quantize_half8_piece(float (&r)[8], uint32_t& word) {
+    float bmax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) bmax = fmaxf(bmax, fabsf(r[i]));
+    bmax = fmaxf(bmax, __shfl_xor_sync(0xffffffffu, bmax, 1));
+    const float want = bmax * (1.0f / 6.0f);
+    uint8_t code = encode_e4m3(want);
+    float s = decode_e4m3(code);
+    if (s < want && code < 0x7E) {
+        code += 1;
+        s = decode_e4m3(code);
+    }
+    const float inv = s > 0.0f ? 1.0f / s : 0.0f;
+    word = 0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t byte = encode_e2m1x2(r[2 * i] * inv, r[2 * i + 1] * inv);
+        const float2 q = decode_e2m1x2(byte);
+        r[2 * i] = fmaf(-q.x, s, r[2 * i]);
+        r[2 * i + 1] = fmaf(-q.y, s, r[2 * i + 1]);
+        word |= byte << (8 * i);
+    }
+    return code;
+}
+
+// Exponent e of the row pre-scale 2^e that brings a row's largest magnitude into [1024, 2048)
+__device__ __forceinline__ int prescale_exponent(float amax) {
+    int e = 0;
+    if (amax > 0.0f && amax < 3.0e38f) {
+        int ex;
+        frexpf(amax, &ex);
+        e = 11 - ex;
+    }
+    return e;
+}
+
 // ---------------------------------------------------------------------------
 // Scalars of a run-time dtype
 // ---------------------------------------------------------------------------

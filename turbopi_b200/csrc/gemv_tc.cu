@@ -136,16 +136,6 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)
 
 // Power-of-two pre-scale that brings a row's largest magnitude into [1024, 2048): the block scales of the
 // pieces then sit in the upper range of UE4M3.  Returns the exponent e (pre-scale 2^e, undone by 2^-e).
-__device__ __forceinline__ int prescale_exponent(float amax) {
-    int e = 0;
-    if (amax > 0.0f && amax < 3.0e38f) {
-        int ex;
-        frexpf(amax, &ex);
-        e = 11 - ex;
-    }
-    return e;
-}
-
 // 16 consecutive elements, already in registers as loaded (two 16-byte words of 16-bit elements, or four of fp32)
 __device__ __forceinline__ void unpack16(const uint4 (&raw)[4], int dtype, float (&v)[16]) {
     if (dtype == TPB200_F32) {

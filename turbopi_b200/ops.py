@@ -544,33 +544,46 @@ def attention_workspace(n_rows, n_keys, head_dim, groups, device):
     return torch.empty(n, dtype=torch.uint8, device=device)
 
 
-def attention(q, k, v, out, scale, key_bias=None, workspace=None):
+def attention(q, k, v, out, scale, key_bias=None, workspace=None, quant=None, rows_per_token=1):
     """out = softmax(scale * q k^T + key_bias) v on the tensor cores; bf16 tensors.
     q / out: [rows, D] or [A, B, rows, D] views (any strides with a unit last stride); k / v: [keys, D] or
-    [A, B, keys, D].  Gemma's grouped heads: pass q as the [tokens * heads, 256] view of the projection."""
+    [A, B, keys, D].  Gemma's grouped heads: pass q as the [tokens * heads, 256] view of the projection.
+    `quant` (a tiled QuantBuf of [rows / rows_per_token, rows_per_token * D]): the result is also, or with
+    out=None only, written as the operand of the next tensor-core GEMM -- what rowop(ROW_NONE, out, ...) would
+    produce, without that launch (2-D problems only)."""
     _cuda(q, k, v, out, key_bias, workspace)
     if q.dim() == 2:
-        q, k, v, out = q[None, None], k[None, None], v[None, None], out[None, None]
-    if not (q.dim() == k.dim() == v.dim() == out.dim() == 4):
+        q, k, v = q[None, None], k[None, None], v[None, None]
+        out = None if out is None else out[None, None]
+    if out is None and quant is None:
+        raise TurboPiError("attention: neither out nor quant given")
+    if not (q.dim() == k.dim() == v.dim() == 4 and (out is None or out.dim() == 4)):
         raise TurboPiError("attention: q, k, v, out must all be 2-D or all 4-D")
     for t in (q, k, v, out):
-        if t.dtype != torch.bfloat16 or t.stride(3) != 1:
+        if t is not None and (t.dtype != torch.bfloat16 or t.stride(3) != 1):
             raise TurboPiError("attention: bf16 tensors with a contiguous last dimension")
     A, B, R, D = q.shape
     S = k.shape[2]
-    if tuple(k.shape) != (A, B, S, D) or tuple(v.shape) != (A, B, S, D) or tuple(out.shape) != (A, B, R, D):
+    if tuple(k.shape) != (A, B, S, D) or tuple(v.shape) != (A, B, S, D) or (out is not None and tuple(out.shape) != (A, B, R, D)):
         raise TurboPiError("attention: shapes of q, k, v, out do not agree")
     if key_bias is not None and (key_bias.dtype != torch.bfloat16 or key_bias.numel() < S or not key_bias.is_contiguous()):
         raise TurboPiError("attention: key_bias must be a contiguous bf16 vector with one entry per key")
+    if quant is not None:
+        if A * B != 1 or R % rows_per_token or not quant.tiled or quant.M != R // rows_per_token or quant.K != rows_per_token * D:
+            raise TurboPiError("attention: quant must be a tiled QuantBuf of [rows / rows_per_token, rows_per_token * D]")
     if workspace is None:
         workspace = attention_workspace(R, S, D, A * B, q.device)
     two = ctypes.c_longlong * 2
+    o = q if out is None else out          # strides only; the pointer stays NULL without `out`
     args = _lib.AttentionArgs(q=_ptr(q), k=_ptr(k), v=_ptr(v), out=_ptr(out), key_bias=_ptr(key_bias), n_rows=R, n_keys=S,
-                              head_dim=D, ldq=q.stride(2), ldk=k.stride(2), ldv=v.stride(2), ldo=out.stride(2),
+                              head_dim=D, ldq=q.stride(2), ldk=k.stride(2), ldv=v.stride(2), ldo=o.stride(2),
                               groups_outer=A, groups_inner=B, q_stride=two(q.stride(0), q.stride(1)),
                               k_stride=two(k.stride(0), k.stride(1)), v_stride=two(v.stride(0), v.stride(1)),
-                              o_stride=two(out.stride(0), out.stride(1)), scale=float(scale), workspace=_ptr(workspace),
-                              workspace_bytes=workspace.numel(), flags=_launch_flags)
+                              o_stride=two(o.stride(0), o.stride(1)), scale=float(scale), workspace=_ptr(workspace),
+                              workspace_bytes=workspace.numel(), flags=_launch_flags,
+                              quant_image=_ptr(quant.packed) if quant is not None else None,
+                              quant_row_scale=_ptr(quant.row_scale) if quant is not None else None,
+                              quant_pieces=quant.pieces if quant is not None else 0, quant_rows_per_token=rows_per_token)
     with torch.cuda.device(q.device):
         st = _lib.load().tpb200_attention(ctypes.byref(args), torch.cuda.current_stream(q.device).cuda_stream)
     _lib.check(st, "tpb200_attention")

@@ -392,6 +392,14 @@ class Pi05:
         ops.attention(q.view(L * c.heads, c.head_dim), k, v, out.view(L * c.heads, c.head_dim), c.head_dim ** -0.5,
                       self.key_bias, self.attn_ws)
 
+    def _attention_to_operand(self, q, k, v, quant):
+        """The same attention, its result written only as the operand of the output projection that follows
+        (the merge kernel quantises each token's H * D row itself: no bf16 round trip, no row-kernel launch)."""
+        c = self.cfg
+        L = q.shape[0]
+        ops.attention(q.view(L * c.heads, c.head_dim), k, v, None, c.head_dim ** -0.5, self.key_bias, self.attn_ws,
+                      quant=quant, rows_per_token=c.heads)
+
     def vision_tower(self):
         c, b = self.cfg, self.b
         T, vw = c.num_images * c.image_tokens, c.vision_width
@@ -441,8 +449,7 @@ class Pi05:
                       eps=c.eps)
             L["qkv"].qkv(b["q_p"], b["p_q"], self.cache[l, 0], self.cache[l, 1], b["pos_prefix"], self.cos, self.sin,
                          c.q_dim)
-            self._attention(b["p_q"], self.cache[l, 0, :S], self.cache[l, 1, :S], b["p_q"])
-            rowop(_lib.ROW_NONE, b["p_q"], c.q_dim, b["q_pattn"])
+            self._attention_to_operand(b["p_q"], self.cache[l, 0, :S], self.cache[l, 1, :S], b["q_pattn"])
             L["o"](b["q_pattn"], b["py"])
             rowop(_lib.ROW_RMSNORM, b["py"], c.width, b["q_p"], res_in=b["ph"], h_out=b["ph"], w0=L["post_norm"],
                   eps=c.eps)
@@ -490,8 +497,7 @@ class Pi05:
                       w1=m_in[1], eps=c.eps)
             L["qkv"].qkv(b["q_e"], b["e_q"], self.cache[l, 0, S:], self.cache[l, 1, S:], b["pos_suffix"], self.cos,
                          self.sin, c.q_dim)
-            self._attention(b["e_q"], self.cache[l, 0, :S + A], self.cache[l, 1, :S + A], b["e_q"])
-            rowop(_lib.ROW_NONE, b["e_q"], c.q_dim, b["q_eattn"])
+            self._attention_to_operand(b["e_q"], self.cache[l, 0, :S + A], self.cache[l, 1, :S + A], b["q_eattn"])
             L["o"](b["q_eattn"], b["ey"])
             rowop(_lib.ROW_ADARMS, b["ey"], ew, b["q_e"], res_in=b["eh"], gate=m_in[2], h_out=b["eh"], w0=m_post[0],
                   w1=m_post[1], eps=c.eps)
