@@ -234,7 +234,7 @@ def test_fused_qkv_split_k_matches_unsplit(cuda_device):
     split over CTAs gives the same bf16 values as the unsplit launch."""
     from turbopi_b200 import ops
     rng = np.random.default_rng(13)
-    S, H, QD = 50, 1024, 2048
+    S, H, QD = 50, 2048, 2048
     x = _dev(formats.round_to_bf16(rng.normal(size=(S, H)).astype(np.float32)), cuda_device, torch.bfloat16)
     w = (rng.normal(size=(QD + 512, H)) * 0.02).astype(np.float32)
     packed, sbytes, g = nvfp4.quantize_two_level(w, 16)
@@ -260,7 +260,7 @@ def test_fused_qkv_split_k_matches_unsplit(cuda_device):
 # ---------------------------------------------------------------------------- tiled operand images
 @pytest.mark.parametrize("M,N,K,act,split", [(128, 256, 256, 0, False), (200, 384, 2048, 1, False),
                                              (712, 2048, 2048, 0, False), (50, 1024, 4096, 2, True),
-                                             (300, 1152, 1152, 0, True), (5, 8, 16, 0, False),
+                                             (300, 1152, 4304, 0, True), (300, 1152, 1152, 0, False), (5, 8, 16, 0, False),
                                              (130, 4304, 1152, 1, False), (712, 2048, 16384, 0, True)])
 def test_tiled_operands_match_oracle_and_rowmajor(cuda_device, M, N, K, act, split):
     """The fast path (pre-tiled operand images, 128 x 256 output tiles, bulk-copy producer) against the

@@ -43,7 +43,7 @@ constexpr int kMaxPieces = 4;
 constexpr int kTile = 128 * kBKBytes;    // 16 KB operand tile
 constexpr int kSfSlab = 4 * 512;         // 4 K-atoms of one 128-row tile
 constexpr int kOutBuf = 128 * 128;       // one staged output box: 128 rows x 128 bytes
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;           // warps: 0 producer, 1 MMA issuer, 2..5 and 6..9 two epilogue groups
 constexpr int kTmemCols = 512;
 // tensor memory: columns [0, 256) hold two 128-column accumulators (row-major form) or one of 256
 // columns (tiled form); then the B scales (4 columns per K atom and 128 rows) and 16 columns per A piece
@@ -101,6 +101,7 @@ struct alignas(64) GemmParams {
     int ldo;                   // elements
     __nv_bfloat16* k_rows;
     __nv_bfloat16* v_rows;
+    int debug_slot;            // diagnostic builds: which timeline slot this launch writes
 };
 constexpr int kCounterSlots = 2048;
 
@@ -109,6 +110,7 @@ enum { kEpiPlain = 0, kEpiQkvRope = 1 };
 struct SharedControl {
     uint64_t full[kMaxStages];
     uint64_t empty[kMaxStages];
+    alignas(16) float bias_s[2][128];  // the bias of the columns each epilogue group is working on
     uint64_t acc_full[2];
     uint64_t acc_empty[2];
     uint32_t tmem_base;
@@ -135,6 +137,7 @@ __device__ __forceinline__ void bulk_wait_group_read() {
 }
 __device__ __forceinline__ void bulk_wait_group_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void epilogue_barrier() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+__device__ __forceinline__ void epilogue_group_barrier(int grp) { asm volatile("bar.sync %0, 128;" ::"r"(1 + grp) : "memory"); }
 
 // 16-byte chunk c of row r in a staged 128-byte-row box (the layout a 128B-swizzled TMA store reads)
 __device__ __forceinline__ uint8_t* staged_chunk(uint8_t* buf, int r, int c) {
@@ -152,6 +155,26 @@ __device__ __forceinline__ void finish_plain32(float* v, float rs, const float* 
         }
     }
     // one uniform branch per chunk: the transcendental code stays out of the plain path
+    if (activation == TPB200_ACT_GELU) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = gelu_tanh_fast(v[i]);
+    } else if (activation == TPB200_ACT_SILU) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = silu_fast(v[i]);
+    }
+}
+
+// the same with the 32 bias values already in shared memory (zeros past the end of the matrix, or no bias)
+__device__ __forceinline__ void finish_plain32_staged(float* v, float rs, const float* bias_s, bool has_bias, int activation) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] *= rs;
+    if (has_bias) {
+#pragma unroll
+        for (int i = 0; i < 32; i += 4) {
+            const float4 b = *reinterpret_cast<const float4*>(bias_s + i);
+            v[i] += b.x; v[i + 1] += b.y; v[i + 2] += b.z; v[i + 3] += b.w;
+        }
+    }
     if (activation == TPB200_ACT_GELU) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = gelu_tanh_fast(v[i]);
@@ -213,6 +236,21 @@ __device__ __forceinline__ void rope_pair32(const float* lo, const float* hi, fl
     }
 }
 
+#ifdef TPB_TIMELINE
+// Diagnostic build only (-DTPB_TIMELINE): every CTA of the last launches leaves globaltimer stamps of its
+// milestones here; tpb200_debug_gemm_timeline() copies them out.
+constexpr int kTlSlots = 4, kTlPoints = 16, kTlCtas = 160;
+__device__ unsigned long long g_gemm_timeline[kTlSlots][kTlCtas][kTlPoints];
+__device__ __forceinline__ unsigned long long tl_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define TL(point) g_gemm_timeline[P.debug_slot & (kTlSlots - 1)][blockIdx.x][point] = tl_now()
+#else
+#define TL(point) ((void)0)
+#endif
+
 template <bool kTiled>
 __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_constant__ GemmParams P) {
     extern __shared__ uint8_t smem_raw[];
@@ -236,15 +274,20 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
     const int lane = threadIdx.x & 31;
     const int splits = P.splits;
     const int total_items = P.m_blocks * P.n_blocks * splits;
+    // Unsplit launches with the plain epilogue drain an accumulator with both epilogue groups (alternate
+    // 128-byte boxes): the MMA thread waits for that drain before every tile, the accumulator being single.
+    // The split-K hand-over and the fused QKV epilogue stay on group 0.
+    const bool two_groups = P.epilogue == kEpiPlain && splits == 1;
 
     if (threadIdx.x == 0) {
+        TL(0);
         for (int s = 0; s < kMaxStages; ++s) {
             mbar_init(&ctl->full[s], 1);
             mbar_init(&ctl->empty[s], 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&ctl->acc_full[b], 1);
-            mbar_init(&ctl->acc_empty[b], 4);   // one arrival per epilogue warp
+            mbar_init(&ctl->acc_empty[b], two_groups ? 8 : 4);   // one arrival per epilogue warp at work
         }
         ctl->abort_flag = 0;
         fence_mbar_init();
@@ -258,6 +301,7 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
     tc::fence_after_thread_sync();
     const uint32_t tmem_base = ctl->tmem_base;
     volatile int* abort_flag = &ctl->abort_flag;
+    if (threadIdx.x == 0) TL(1);
     // Programmatic dependent launch: everything above ran while the previous kernel of the stream may still
     // have been running.  The producer (operands) and the epilogue (row scales, bias, results, split-K
     // scratch) touch global memory, so they wait for it; the MMA issuer only ever sees shared memory.  The
@@ -301,6 +345,7 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
             }
         }
         pdl_wait_prior_grids();
+        if (lane == 0) TL(2);
         int it = 0;
         for (int w = blockIdx.x; w < total_items && !stop; w += gridDim.x) {
             const int tile = w / splits;
@@ -361,6 +406,7 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
                     wrapped = true;
                 }
             }
+            if (lane == 0 && w == blockIdx.x) TL(3);
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------ MMA issuer
@@ -398,6 +444,7 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
                         break;
                     }
                     tc::fence_after_thread_sync();
+                    if (tile_iter == 0 && ks == ks0) TL(4);
                     // B scales of K atom a sit in kSubTiles * 4 consecutive columns (4 per 128 rows)
 #pragma unroll
                     for (int a = 0; a < 4; ++a) {
@@ -438,18 +485,21 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
                     }
                 }
                 tc::commit(&ctl->acc_full[buf]);  // accumulator complete
+                if (tile_iter == 0) TL(5);
             }
         }
     } else {
         // ------------------------------------------------------------ epilogue (warps 2..5, 128 threads)
         const int q = warp & 3;                       // tensor-memory lane quarter this warp may read
         const int row = q * 32 + lane;                // row of the tile this thread owns
-        const int etid = threadIdx.x - 64;            // 0..127
-        const bool issuer = (etid == 0);              // first epilogue thread issues the TMA stores
+        const int grp = (warp - 2) >> 2;              // epilogue group 0 (warps 2..5) or 1 (warps 6..9)
+        const int etid = (threadIdx.x - 64) & 127;    // 0..127 inside the group
+        const bool issuer = (etid == 0);              // the group's first thread issues its TMA stores
+        const bool at_work = grp == 0 || two_groups;
         const int n_heads_q = P.q_dim >> 8;
         int tile_iter = 0;
         uint32_t nstore = 0;                          // staged boxes so far (buffer = nstore & 1)
-        for (int w = blockIdx.x; w < total_items && !*abort_flag; w += gridDim.x, ++tile_iter) {
+        for (int w = blockIdx.x; at_work && w < total_items && !*abort_flag; w += gridDim.x, ++tile_iter) {
             const int tile = w / splits;
             const int m_blk = tile % P.m_blocks;
             const int n_blk = tile / P.m_blocks;
@@ -460,6 +510,7 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
                 break;
             }
             tc::fence_after_thread_sync();
+            if (issuer && tile_iter == 0) TL(6);
             const int m = m_blk * kBM + row;
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + buf * 128;
             const float rs = (P.row_scale != nullptr && m < P.M) ? P.alpha * __ldg(P.row_scale + m) : P.alpha;
@@ -474,17 +525,23 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
                 float4* scratch4 = reinterpret_cast<float4*>(P.scratch);
                 if (q * 32 < rows_valid) {     // whole warps only: the tensor-memory load is warp-collective
                     float4* dst = scratch4 + static_cast<size_t>(w) * kItemFloat4 + row;
+                    // four tensor-memory loads in flight per wait: the parking pass is on every split launch's
+                    // critical path (all CTAs of the tile wait for the slowest one to finish it)
 #pragma unroll 1
-                    for (int c = 0; c < kBN / 32; ++c) {
-                        uint32_t r[32];
-                        tc::tmem_ld_32x32b_x32(taddr + c * 32, r);
+                    for (int c4 = 0; c4 < kBN / 128; ++c4) {
+                        uint32_t r[4][32];
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) tc::tmem_ld_32x32b_x32(taddr + (c4 * 4 + c) * 32, r[c]);
                         tc::tmem_ld_wait();
                         if (row < rows_valid) {
 #pragma unroll
-                            for (int g = 0; g < 8; ++g) {
-                                dst[(c * 8 + g) * 128] =
-                                    make_float4(__uint_as_float(r[4 * g]), __uint_as_float(r[4 * g + 1]),
-                                                __uint_as_float(r[4 * g + 2]), __uint_as_float(r[4 * g + 3]));
+                            for (int c = 0; c < 4; ++c) {
+#pragma unroll
+                                for (int g = 0; g < 8; ++g) {
+                                    dst[((c4 * 4 + c) * 8 + g) * 128] =
+                                        make_float4(__uint_as_float(r[c][4 * g]), __uint_as_float(r[c][4 * g + 1]),
+                                                    __uint_as_float(r[c][4 * g + 2]), __uint_as_float(r[c][4 * g + 3]));
+                                }
                             }
                         }
                     }
@@ -496,6 +553,7 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
                 epilogue_barrier();
                 if (issuer) {
                     atomicAdd(P.counters + tile, 1u);
+                    if (tile_iter == 0) TL(7);
                     const long long t0 = clock64();
                     while (true) {
                         unsigned int seen;
@@ -511,6 +569,7 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
                 epilogue_barrier();
                 if (*abort_flag) break;
                 __threadfence();
+                if (issuer && tile_iter == 0) TL(8);
                 const int split = w - tile * splits;
                 const int per = (rows_valid + splits - 1) / splits;
                 const int r0 = split * per;
@@ -600,6 +659,7 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
                 }
                 // the last CTA to leave the tile puts both counters back to zero for the next launch
                 epilogue_barrier();
+                if (issuer && tile_iter == 0) TL(9);
                 if (issuer) {
                     const unsigned int t = atomicAdd(P.counters + kCounterSlots + tile, 1u);
                     if (t == static_cast<unsigned int>(splits - 1)) {
@@ -619,12 +679,65 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
                 const int n_out = geglu ? P.N >> 1 : P.N;
                 const int cols_per_box = P.out_dtype == TPB200_BF16 ? 64 : 32;
                 const int nboxes = out_cols / cols_per_box;
+                uint8_t* ob = out_stage + grp * kOutBuf;      // one staging buffer per group
+                float* bias_s = ctl->bias_s[grp];
+                const bool has_bias = P.bias != nullptr;
+                if (P.out_dtype == TPB200_BF16 && !geglu && nboxes == 4) {
+                    // bf16, 256-column tile: the group's two boxes (columns [64 g, 64 g + 64) and 128 further on)
+                    // are converted straight out of tensor memory into 64 packed registers, and the accumulator
+                    // is handed back to the MMA thread BEFORE anything is staged or stored: the single
+                    // accumulator is free again after four loads instead of after the whole epilogue.
+                    if (has_bias) {
+                        const int nb = n_blk * kBN + (etid >> 6) * 128 + grp * 64 + (etid & 63);
+                        bias_s[etid] = nb < P.N ? __ldg(P.bias + nb) : 0.0f;
+                    }
+                    epilogue_group_barrier(grp);
+                    uint32_t pk[4][16];
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t raw[32];
+                        tc::tmem_ld_32x32b_x32(taddr + (c >> 1) * 128 + grp * 64 + (c & 1) * 32, raw);
+                        tc::tmem_ld_wait();
+                        float v[32];
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[i]);
+                        finish_plain32_staged(v, rs, bias_s + c * 32, has_bias, P.activation);
+                        pack_bf16x32(v, pk[c]);
+                    }
+                    tc::fence_before_thread_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&ctl->acc_empty[buf]);
+#pragma unroll
+                    for (int b2 = 0; b2 < 2; ++b2) {
+                        const int n0 = n_blk * kBN + b2 * 128 + grp * 64;
+                        if (issuer) bulk_wait_group_read<0>();    // the group's previous store has read the buffer
+                        epilogue_group_barrier(grp);
+#pragma unroll
+                        for (int c = 0; c < 2; ++c) {
+#pragma unroll
+                            for (int g = 0; g < 4; ++g) {
+                                *reinterpret_cast<uint4*>(staged_chunk(ob, row, c * 4 + g)) =
+                                    make_uint4(pk[b2 * 2 + c][4 * g], pk[b2 * 2 + c][4 * g + 1], pk[b2 * 2 + c][4 * g + 2],
+                                               pk[b2 * 2 + c][4 * g + 3]);
+                            }
+                        }
+                        fence_proxy_async_smem();
+                        epilogue_group_barrier(grp);
+                        if (issuer) {
+                            if (n0 < n_out) tma_store_2d(&P.map_out, ob, n0, m_blk * kBM);
+                            bulk_commit_group();
+                        }
+                    }
+                    continue;
+                }
 #pragma unroll 1
-                for (int bx = 0; bx < nboxes; ++bx, ++nstore) {
-                    uint8_t* ob = out_stage + (nstore & 1) * kOutBuf;
-                    if (issuer) bulk_wait_group_read<1>();    // the store that last used this buffer has read it
-                    epilogue_barrier();
+                for (int bx = grp; bx < nboxes; bx += 2) {
                     const int n0 = n_blk * out_cols + bx * cols_per_box;
+                    if (has_bias && !geglu && etid < cols_per_box) {
+                        bias_s[etid] = n0 + etid < P.N ? __ldg(P.bias + n0 + etid) : 0.0f;
+                    }
+                    if (issuer) bulk_wait_group_read<0>();    // the group's previous store has read the buffer
+                    epilogue_group_barrier(grp);
 #pragma unroll 1
                     for (int c = 0; c < cols_per_box / 32; ++c) {
                         uint32_t raw[32];
@@ -641,7 +754,7 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
                             for (int i = 0; i < 32; ++i) up[i] = __uint_as_float(raw[i]);
                             finish_geglu32(v, up, rs);
                         } else {
-                            finish_plain32(v, rs, P.bias, n0 + c * 32, P.N, P.activation);
+                            finish_plain32_staged(v, rs, bias_s + c * 32, has_bias, P.activation);
                         }
                         if (P.out_dtype == TPB200_BF16) {
                             uint32_t pk[16];
@@ -659,14 +772,14 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
                             }
                         }
                     }
-                    if (bx == nboxes - 1) {
+                    if (bx + 2 >= nboxes) {
                         // everything this warp needs from the accumulator is in registers / shared memory
                         tc::fence_before_thread_sync();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&ctl->acc_empty[buf]);
                     }
                     fence_proxy_async_smem();
-                    epilogue_barrier();
+                    epilogue_group_barrier(grp);
                     if (issuer) {
                         if (n0 < n_out) tma_store_2d(&P.map_out, ob, n0, m_blk * kBM);
                         bulk_commit_group();
@@ -729,6 +842,7 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
             }
         }
         if (issuer) bulk_wait_group_all();   // every output tile has landed before the CTA goes away
+        if (issuer) TL(10);
     }
 
     tc::fence_before_thread_sync();
@@ -997,20 +1111,22 @@ int device_error_nvfp4_gemm(int clear) { return read_device_error(clear); }
 constexpr size_t kCounterBytes = 16384;            // 4096 tile counters in front of the partial sums
 struct SplitPlan { int splits; int stages_per_split; size_t bytes; };
 
-SplitPlan plan_splits(int tiles, int k_stages, int pieces, bool tiled, int sms, size_t workspace_bytes) {
+SplitPlan plan_splits(int tiles, int k_stages, int pieces, bool tiled, int sms, size_t workspace_bytes, int rows) {
     SplitPlan best{1, k_stages, 0};
     if (2 * tiles > sms || tiles > kCounterSlots || k_stages < 2) return best;
     const size_t item_bytes = static_cast<size_t>(128) * tile_n(tiled) * 4;   // one partial accumulator
-    // a stage costs its bytes over what one SM takes in with two stages in flight (KB per microsecond);
-    // a split launch adds parking the sums, the wait for the slowest CTA and the slice pass
-    const float t_stage = stage_bytes(pieces, tiled) / 1024.0f / (tiled ? 50.0f : 60.0f);
+    // Device timestamps of this kernel (three pieces, tiled): a stage takes 1.4 us (two stages of 90 KB in
+    // flight per SM); a split launch adds parking the sums (1.8 us for 50 valid rows, 3.4 for 128), the wait for
+    // the slowest partner (1-1.5 us) and the slice pass (1.7 / 4.4 us) where an unsplit tile has a 2 us epilogue.
+    const float t_stage = stage_bytes(pieces, tiled) / 1024.0f / (tiled ? 64.0f : 70.0f);
+    const float t_split = 1.0f + 0.05f * static_cast<float>(std::min(rows, 128));
     float best_cost = k_stages * t_stage;
     for (int s = 2; s <= std::min(k_stages, sms / tiles); ++s) {    // one wave: every CTA is resident
         const int sps = (k_stages + s - 1) / s;
         const int s_eff = (k_stages + sps - 1) / sps;
         const size_t bytes = kCounterBytes + static_cast<size_t>(tiles) * s_eff * item_bytes;
         if (bytes > workspace_bytes) continue;
-        const float c = sps * t_stage + 2.5f;
+        const float c = sps * t_stage + t_split;
         if (c < best_cost * 0.95f) {
             best_cost = c;
             best = SplitPlan{s_eff, sps, bytes};
@@ -1102,7 +1218,7 @@ extern "C" size_t tpb200_nvfp4_gemm_workspace_size(int M, int N, int K, int a_pi
         return 0;
     }
     const int tiles = ((M + tpb::kBM - 1) / tpb::kBM) * ((N + bn - 1) / bn);
-    return tpb::plan_splits(tiles, (K + 255) / 256, a_pieces <= 0 ? 1 : a_pieces, tiled, sms, ~size_t(0)).bytes;
+    return tpb::plan_splits(tiles, (K + 255) / 256, a_pieces <= 0 ? 1 : a_pieces, tiled, sms, ~size_t(0), M).bytes;
 }
 
 extern "C" int tpb200_nvfp4_gemm_ex(const tpb200_nvfp4_gemm_args* a, tpb200_stream_t stream) {
@@ -1214,7 +1330,7 @@ extern "C" int tpb200_nvfp4_gemm_ex(const tpb200_nvfp4_gemm_args* a, tpb200_stre
     tpb::SplitPlan plan{1, P.k_stages, 0};
     if (a->workspace != nullptr) {
         TPB_REQUIRE(tpb_aligned16(a->workspace), TPB200_ERR_ALIGN);
-        plan = tpb::plan_splits(tiles, P.k_stages, pieces, tiled, sms, a->workspace_bytes);
+        plan = tpb::plan_splits(tiles, P.k_stages, pieces, tiled, sms, a->workspace_bytes, M);
     }
     P.splits = plan.splits;
     P.stages_per_split = plan.stages_per_split;
@@ -1238,6 +1354,10 @@ extern "C" int tpb200_nvfp4_gemm_ex(const tpb200_nvfp4_gemm_args* a, tpb200_stre
         cfg.attrs = attr;
         cfg.numAttrs = 1;
     }
+#ifdef TPB_TIMELINE
+    static std::atomic<int> launch_no{0};
+    P.debug_slot = launch_no.fetch_add(1);
+#endif
     const cudaError_t err = tiled ? cudaLaunchKernelEx(&cfg, tpb::nvfp4_gemm_kernel<true>, P)
                                   : cudaLaunchKernelEx(&cfg, tpb::nvfp4_gemm_kernel<false>, P);
     if (err != cudaSuccess) return TPB200_ERR_CUDA;
@@ -1257,3 +1377,13 @@ extern "C" int tpb200_nvfp4_gemm(const void* a_packed, int a_pitch, const void* 
     a.M = M; a.N = N; a.K = K;
     return tpb200_nvfp4_gemm_ex(&a, stream);
 }
+
+#ifdef TPB_TIMELINE
+// Diagnostic build only: the stamps of the last launches ([slot][CTA][point], nanoseconds).
+extern "C" int tpb200_debug_gemm_timeline(unsigned long long* out, size_t bytes) {
+    if (bytes > sizeof(tpb::g_gemm_timeline)) bytes = sizeof(tpb::g_gemm_timeline);
+    cudaDeviceSynchronize();
+    cudaMemcpyFromSymbol(out, tpb::g_gemm_timeline, bytes);
+    return 0;
+}
+#endif
