@@ -514,6 +514,25 @@ def run_extras(device, sets, x):
                                          "tensor_tflops": 3 * 2.0 * M * N * K / t / 1e12,
                                          "cublas_bf16_us": tb * 1e6, "cublas_bf16_tflops": 2.0 * M * N * K / tb / 1e12}
         del lins, wb
+    # (g0) this GPU's own e2m1 block-scaled MMA rate: back-to-back 128 x 256 x 64 MMAs on resident operands, one
+    # CTA per SM -- the measured denominator for the GEMM rates above (the nominal dense FP4 figure is 9 PFLOP/s)
+    lib = tlib.load()
+    sms = torch.cuda.get_device_properties(device).multi_processor_count
+    stream_h = torch.cuda.current_stream(device).cuda_stream
+    for mmas in (2000, 20000):
+        tlib.check(lib.tpb200_measure_fp4_mma_rate(mmas, stream_h), "fp4 mma rate")     # the first call also warms up
+    torch.cuda.synchronize()
+    rates = []
+    for _ in range(5):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        tlib.check(lib.tpb200_measure_fp4_mma_rate(20000, stream_h), "fp4 mma rate")
+        b.record()
+        torch.cuda.synchronize()
+        rates.append(sms * 20000 * 4194304.0 / (a.elapsed_time(b) * 1e-3) / 1e12)
+    rates.sort()
+    ex["fp4_mma_rate_measured"] = {"tflops": rates[len(rates) // 2], "mma": "tcgen05.mma kind::mxf4nvf4 128x256x64, no loads",
+                                   "nominal_tflops": 9000.0}
     # (g1) INT4 x bf16 GEMM on the tensor cores (w4a16GemmForward's operands) at the prefix shape, next to cuBLAS bf16
     for (M, N, K, name) in ((712, 16384, 2048, "gemma2b_gateup_M712"), (712, 2048, 16384, "gemma2b_down_M712"),
                             (64, 16384, 2048, "gemma2b_gateup_M64")):

@@ -209,6 +209,12 @@ enum { TPB200_OPERANDS_ROWMAJOR = 0, TPB200_OPERANDS_TILED = 1 };
 size_t tpb200_nvfp4_gemm_workspace_size(int M, int N, int K, int a_pieces, int layout);
 size_t tpb200_nvfp4_tiled_a_bytes(int M, int K, int pieces);
 size_t tpb200_nvfp4_tiled_b_bytes(int N, int K);
+
+/* Measurement utility (no counterpart in the reference): one CTA per SM issues `mmas_per_cta` block-scaled e2m1
+ * MMAs of 128 x 256 x 64 (4,194,304 flops each) back to back on operands resident in shared memory -- no loads, no
+ * epilogue.  Time the launch with events: SMs * mmas_per_cta * 4194304 / time is this GPU's FP4 tensor rate at the
+ * clocks it runs at, the denominator the GEMM's rates are quoted against next to the nominal figure. */
+int tpb200_measure_fp4_mma_rate(int mmas_per_cta, tpb200_stream_t stream);
 int tpb200_nvfp4_tile_weights(const void* b_packed, int b_pitch, const void* b_sf, void* image, int N, int K,
                               tpb200_stream_t stream);
 int tpb200_nvfp4_gemm_ex(const tpb200_nvfp4_gemm_args* args, tpb200_stream_t stream);

@@ -100,6 +100,7 @@ SIGNATURES = {
     "tpb200_nvfp4_gemm_workspace_size": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "tpb200_nvfp4_tiled_a_bytes": (c_size_t, [c_int, c_int, c_int]),
     "tpb200_nvfp4_tiled_b_bytes": (c_size_t, [c_int, c_int]),
+    "tpb200_measure_fp4_mma_rate": (c_int, [c_int, c_void_p]),
     "tpb200_nvfp4_tile_weights": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "tpb200_nvfp4_quantize_act": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]),
     "tpb200_nvfp4_gemm": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_float, c_void_p, c_int,

@@ -578,6 +578,7 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
                 auto sum32 = [&](int r, int col, float* v) {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = 0.0f;
+#pragma unroll 2
                     for (int sp = 0; sp < splits; ++sp) {
                         const float4* src = part + static_cast<size_t>(sp) * kItemFloat4 + (col >> 2) * 128 + r;
 #pragma unroll
@@ -587,7 +588,59 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
                         }
                     }
                 };
-                if (P.epilogue == kEpiPlain) {
+                if (P.epilogue == kEpiPlain && nrows * (kBN / 32) <= 32 &&
+                    !(kTiled && P.activation == TPB200_ACT_GEGLU)) {
+                    // Few rows per CTA (the 50-token launches cut 8 or 16 ways): units of 8 columns instead of 32
+                    // put all 128 threads to work and leave each with 2 loads per split instead of 8 -- the pass
+                    // is a chain of L2 round trips, and this is the tail of a latency-bound launch.
+                    const int units = nrows * (kBN / 8);
+                    for (int u = etid; u < units; u += 128) {
+                        const int r = r0 + u % nrows;
+                        const int c8 = u / nrows;
+                        const int n = n_blk * kBN + c8 * 8;
+                        if (n >= P.N) continue;
+                        const int mm = m_blk * kBM + r;
+                        const float rs_mm = P.row_scale != nullptr ? P.alpha * __ldg(P.row_scale + mm) : P.alpha;
+                        float v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                        const float4* src = part + (c8 * 2) * 128 + r;
+#pragma unroll 4
+                        for (int sp = 0; sp < splits; ++sp) {
+                            const float4 t0 = __ldcg(src + static_cast<size_t>(sp) * kItemFloat4);
+                            const float4 t1 = __ldcg(src + static_cast<size_t>(sp) * kItemFloat4 + 128);
+                            v[0] += t0.x; v[1] += t0.y; v[2] += t0.z; v[3] += t0.w;
+                            v[4] += t1.x; v[5] += t1.y; v[6] += t1.z; v[7] += t1.w;
+                        }
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            v[i] *= rs_mm;
+                            if (P.bias != nullptr && n + i < P.N) v[i] += __ldg(P.bias + n + i);
+                            if (P.activation == TPB200_ACT_GELU) v[i] = gelu_tanh_fast(v[i]);
+                            else if (P.activation == TPB200_ACT_SILU) v[i] = silu_fast(v[i]);
+                        }
+                        if (P.out_dtype == TPB200_BF16) {
+                            uint32_t pk[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const __nv_bfloat162 b2 = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                                pk[i] = *reinterpret_cast<const uint32_t*>(&b2);
+                            }
+                            __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(P.out) + static_cast<size_t>(mm) * P.ldo + n;
+                            if (n + 8 <= P.N) {
+                                *reinterpret_cast<uint4*>(dst) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                            } else {
+                                for (int i = 0; n + i < P.N; ++i) dst[i] = __float2bfloat16_rn(v[i]);
+                            }
+                        } else {
+                            float* dst = static_cast<float*>(P.out) + static_cast<size_t>(mm) * P.ldo + n;
+                            if (n + 8 <= P.N) {
+                                reinterpret_cast<float4*>(dst)[0] = make_float4(v[0], v[1], v[2], v[3]);
+                                reinterpret_cast<float4*>(dst)[1] = make_float4(v[4], v[5], v[6], v[7]);
+                            } else {
+                                for (int i = 0; n + i < P.N; ++i) dst[i] = v[i];
+                            }
+                        }
+                    }
+                } else if (P.epilogue == kEpiPlain) {
                     const bool geglu = kTiled && P.activation == TPB200_ACT_GEGLU;
                     const int out_cols = geglu ? 128 : kBN;          // output columns of this tile
                     const int n_out = geglu ? P.N >> 1 : P.N;
@@ -848,6 +901,67 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
     tc::fence_before_thread_sync();
     __syncthreads();
     if (warp == 1) {
+        tc::fence_after_thread_sync();
+        tc::tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Measurement utility: the e2m1 block-scaled MMA rate of this GPU with nothing else in the way.  One CTA per
+// SM issues `mmas` MMAs of 128 x 256 x 64 back to back on operands that already sit in shared memory (no
+// loads, no epilogue), so FLOPs / time is the tensor pipe's own pace at the clocks the run gets.
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(64, 1) fp4_mma_rate_kernel(int mmas) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // [B 256 rows x 128 B][A 128 rows x 128 B][B scale slabs 2 x 2 KB][A scale slab 2 KB][barrier, tmem address]
+    uint8_t* sB = smem;
+    uint8_t* sA = sB + 2 * kTile;
+    uint8_t* sSfb = sA + kTile;
+    uint8_t* sSfa = sSfb + 2 * kSfSlab;
+    uint64_t* bar = reinterpret_cast<uint64_t*>(sSfa + kSfSlab);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bar + 1);
+    for (int i = threadIdx.x; i < 3 * kTile / 4; i += 64) reinterpret_cast<uint32_t*>(smem)[i] = 0x2A2A2A2Au;   // codes 1.0 / -1.0
+    for (int i = threadIdx.x; i < 3 * kSfSlab / 4; i += 64) reinterpret_cast<uint32_t*>(sSfb)[i] = 0x38383838u; // UE4M3 1.0
+    if (threadIdx.x == 0) {
+        mbar_init(bar, 1);
+        fence_mbar_init();
+    }
+    fence_proxy_async_smem();
+    if (threadIdx.x >= 32) {
+        __syncwarp();
+        tc::tmem_alloc(tmem_slot, kTmemCols);
+        tc::tmem_relinquish();
+    }
+    tc::fence_before_thread_sync();
+    __syncthreads();
+    tc::fence_after_thread_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) {
+        constexpr uint32_t idesc = tc::make_idesc_mxf4nvf4(256);
+        const uint32_t b16 = smem_u32(sB) >> 4, a16 = smem_u32(sA) >> 4;
+        const uint32_t sfb16 = smem_u32(sSfb) >> 4, sfa16 = smem_u32(sSfa) >> 4;
+        const uint32_t t_sfb = tmem_base + kSfbCol, t_sfa = tmem_base + kSfaCol;
+        for (int a = 0; a < 4; ++a) {
+            for (int h = 0; h < 2; ++h) {
+                tc::cp_sf_32x128b(t_sfb + 4 * (2 * a + h), tc::desc_from_words(sfb16 + ((h * kSfSlab + a * 512) >> 4), tc::kDescHiSfAtom));
+            }
+            tc::cp_sf_32x128b(t_sfa + 4 * a, tc::desc_from_words(sfa16 + ((a * 512) >> 4), tc::kDescHiSfAtom));
+        }
+        uint32_t accumulate = 0;
+        for (int i = 0; i < mmas; ++i) {
+            const int a = i & 3;
+            tc::mma_mxf4nvf4(tmem_base, tc::desc_from_words(a16 + ((a * 32) >> 4), tc::kDescHiKmajorSw128),
+                             tc::desc_from_words(b16 + ((a * 32) >> 4), tc::kDescHiKmajorSw128), idesc, t_sfa + 4 * a,
+                             t_sfb + 8 * a, accumulate);
+            accumulate = 1;
+        }
+        tc::commit(bar);
+        if (!mbar_wait_bounded(bar, 0)) record_error(kErrGemmMmaBarrierTimeout);
+    }
+    tc::fence_before_thread_sync();
+    __syncthreads();
+    if (threadIdx.x >= 32) {
         tc::fence_after_thread_sync();
         tc::tmem_dealloc(tmem_base, kTmemCols);
     }
@@ -1344,7 +1458,9 @@ extern "C" int tpb200_nvfp4_gemm_ex(const tpb200_nvfp4_gemm_args* a, tpb200_stre
     TPB_REQUIRE((a->flags & ~TPB200_FLAG_PDL) == 0, TPB200_ERR_ENUM);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid, 1, 1);
-    cfg.blockDim = dim3(tpb::kThreads, 1, 1);
+    // the second epilogue group (warps 6..9) only has work in unsplit launches with the plain epilogue
+    const bool two_groups = P.epilogue == tpb::kEpiPlain && P.splits == 1;
+    cfg.blockDim = dim3(two_groups ? tpb::kThreads : tpb::kThreads - 128, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = reinterpret_cast<cudaStream_t>(stream);
     cudaLaunchAttribute attr[1];
@@ -1387,3 +1503,18 @@ extern "C" int tpb200_debug_gemm_timeline(unsigned long long* out, size_t bytes)
     return 0;
 }
 #endif
+
+extern "C" int tpb200_measure_fp4_mma_rate(int mmas_per_cta, tpb200_stream_t stream) {
+    TPB_REQUIRE(mmas_per_cta >= 1 && mmas_per_cta <= (1 << 22), TPB200_ERR_SHAPE);
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+        return TPB200_ERR_CUDA;
+    }
+    const int smem = 3 * tpb::kTile + 3 * tpb::kSfSlab + 64 + 1024;
+    if (cudaFuncSetAttribute(tpb::fp4_mma_rate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
+        return TPB200_ERR_CUDA;
+    }
+    tpb::fp4_mma_rate_kernel<<<sms, 64, smem, reinterpret_cast<cudaStream_t>(stream)>>>(mmas_per_cta);
+    return tpb_launch_status();
+}
