@@ -65,6 +65,7 @@ struct AttnParams {
     long long o_stride[2];
     float scale2;                               // scale * log2(e): the softmax runs in base 2
     int row_tiles, key_tiles;
+    int keys_per_cta;                           // 256 (two S tiles), or 128 when the problem has few CTAs
     float* part_o;                              // [group][row tile][key tile] images of 128 rows x dvp floats
     float* part_ml;                             // [group][row tile][key tile][128][2]
     int dv;                                     // head_dim rounded up to 16: N of the second MMA
@@ -143,8 +144,8 @@ __global__ void __launch_bounds__(kThreadsAttn, 1) attention_partial_kernel(cons
     const int rt = blockIdx.x, kt = blockIdx.y, g = blockIdx.z;
     const int ga = g / P.groups_inner, gb = g - ga * P.groups_inner;
     const int warp = threadIdx.x >> 5;
-    const int key0 = kt * kKeysCta;
-    const int nt = (P.n_keys - key0 > kKeyTile) ? 2 : 1;  // S tiles of this CTA
+    const int key0 = kt * P.keys_per_cta;
+    const int nt = (P.keys_per_cta > kKeyTile && P.n_keys - key0 > kKeyTile) ? 2 : 1;  // S tiles of this CTA
 
     if (threadIdx.x == 0) {
         mbar_init(&ctl->bar_k0, 1);
@@ -516,7 +517,7 @@ int device_error_attention(int clear) { return read_device_error(clear); }
 namespace {
 
 struct AttnDims {
-    int row_tiles, key_tiles, dpad, dv, dvp, groups;
+    int row_tiles, key_tiles, keys_per_cta, dpad, dv, dvp, groups;
     size_t part_o_floats, part_ml_floats;
 };
 
@@ -524,7 +525,11 @@ int attn_dims(int n_rows, int n_keys, int head_dim, int groups, AttnDims& d) {
     TPB_REQUIRE(n_rows >= 1 && n_keys >= 1 && groups >= 1, TPB200_ERR_SHAPE);
     TPB_REQUIRE(head_dim >= 8 && head_dim <= 256 && head_dim % 8 == 0, TPB200_ERR_SHAPE);
     d.row_tiles = (n_rows + 127) / 128;
-    d.key_tiles = (n_keys + 255) / 256;
+    // 256 keys per CTA halve the partial results; a problem with few row tiles (the action expert: 4) is a
+    // chain of latencies instead, and a CTA that loads Q + 128 keys of K and V (192 KB through its SM's L2
+    // port) is done sooner than one that loads Q + 256 (320 KB)
+    d.keys_per_cta = (static_cast<long long>(groups) * d.row_tiles * ((n_keys + 255) / 256) < 64 && n_keys > 128) ? 128 : 256;
+    d.key_tiles = (n_keys + d.keys_per_cta - 1) / d.keys_per_cta;
     d.dpad = (head_dim + 63) / 64 * 64;
     d.dv = (head_dim + 15) / 16 * 16;
     d.dvp = (head_dim + 31) / 32 * 32;
@@ -645,6 +650,7 @@ extern "C" int tpb200_attention(const tpb200_attention_args* a, tpb200_stream_t 
     P.scale2 = a->scale * 1.4426950408889634f;
     P.row_tiles = d.row_tiles;
     P.key_tiles = d.key_tiles;
+    P.keys_per_cta = d.keys_per_cta;
     P.part_o = static_cast<float*>(a->workspace);
     P.part_ml = P.part_o + d.part_o_floats;
     P.qa_image = static_cast<uint8_t*>(a->quant_image);
