@@ -783,6 +783,53 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
                     }
                     continue;
                 }
+                if (P.out_dtype == TPB200_BF16 && geglu) {
+                    // Gated GELU, bf16: the group's 64 gate columns and their 64 up columns leave tensor memory as
+                    // bf16 pairs (the module rounds both projections to bf16 before the activation anyway), the
+                    // accumulator goes back to the MMA thread, and only then comes the GELU arithmetic.
+                    uint32_t gpk[2][16], upk[2][16];
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t raw[32];
+                        tc::tmem_ld_32x32b_x32(taddr + (c >> 1) * 128 + grp * 64 + (c & 1) * 32, raw);
+                        tc::tmem_ld_wait();
+                        float v[32];
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(raw[i]) * rs;
+                        pack_bf16x32(v, c < 2 ? gpk[c & 1] : upk[c & 1]);
+                    }
+                    tc::fence_before_thread_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&ctl->acc_empty[buf]);
+                    const int n0 = n_blk * 128 + grp * 64;
+                    if (issuer) bulk_wait_group_read<0>();    // the group's previous store has read the buffer
+                    epilogue_group_barrier(grp);
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        uint32_t o[16];
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const float2 gb = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gpk[c][i]));
+                            const float2 ub = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&upk[c][i]));
+                            const float a0 = __bfloat162float(__float2bfloat16_rn(gelu_tanh_fast(gb.x))) * ub.x;
+                            const float a1 = __bfloat162float(__float2bfloat16_rn(gelu_tanh_fast(gb.y))) * ub.y;
+                            const __nv_bfloat162 r2 = __floats2bfloat162_rn(a0, a1);
+                            o[i] = *reinterpret_cast<const uint32_t*>(&r2);
+                        }
+#pragma unroll
+                        for (int g = 0; g < 4; ++g) {
+                            *reinterpret_cast<uint4*>(staged_chunk(ob, row, c * 4 + g)) =
+                                make_uint4(o[4 * g], o[4 * g + 1], o[4 * g + 2], o[4 * g + 3]);
+                        }
+                    }
+                    fence_proxy_async_smem();
+                    epilogue_group_barrier(grp);
+                    if (issuer) {
+                        if (n0 < n_out) tma_store_2d(&P.map_out, ob, n0, m_blk * kBM);
+                        bulk_commit_group();
+                    }
+                    continue;
+                }
 #pragma unroll 1
                 for (int bx = grp; bx < nboxes; bx += 2) {
                     const int n0 = n_blk * out_cols + bx * cols_per_box;
