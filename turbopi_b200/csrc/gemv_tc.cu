@@ -579,26 +579,22 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
                         const int s = git % kStages;
                         uint8_t* blk = smem + s * kStageBytes + kWBlock;
                         bool waited = false;
-                        for (int item0 = 0; item0 < P.M * 16; item0 += 64) {
-                            // up to two (row, block) items per lane and round; the loads go out first
-                            uint4 raw[2][4];
-                            bool valid[2];
-#pragma unroll
-                            for (int q = 0; q < 2; ++q) {
-                                const int item = item0 + lane + 32 * q;
-                                const int kb = ks * 16 + (item & 15);
-                                valid[q] = item < P.M * 16 && kb < nblk;
-                                if (valid[q]) {
-                                    const size_t e0 = static_cast<size_t>(item >> 4) * ldx + static_cast<size_t>(kb) * 16;
-                                    if (P.x_dtype == TPB200_F32) {
-                                        const uint4* gp = reinterpret_cast<const uint4*>(static_cast<const float*>(x) + e0);
-#pragma unroll
-                                        for (int w = 0; w < 4; ++w) raw[q][w] = __ldg(gp + w);
-                                    } else {
-                                        const uint4* gp = reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(x) + e0);
-                                        raw[q][0] = __ldg(gp);
-                                        raw[q][1] = __ldg(gp + 1);
-                                    }
+                        // one round per token row: lane = (16-element block of the stage, half of that block); the two
+                        // lanes of a block share its maximum through one shuffle, so a block's three residual pieces are
+                        // a chain of 8-element steps instead of 16-element ones
+                        const int kbl = lane >> 1, hb = lane & 1;          // block inside the stage, half of the block
+                        for (int t = 0; t < P.M; ++t) {
+                            uint4 raw[2];
+                            const int kb = ks * 16 + kbl;
+                            const bool valid = kb < nblk;
+                            if (valid) {
+                                const size_t e0 = static_cast<size_t>(t) * ldx + static_cast<size_t>(kb) * 16 + hb * 8;
+                                if (P.x_dtype == TPB200_F32) {
+                                    const uint4* gp = reinterpret_cast<const uint4*>(static_cast<const float*>(x) + e0);
+                                    raw[0] = __ldg(gp);
+                                    raw[1] = __ldg(gp + 1);
+                                } else {
+                                    raw[0] = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(x) + e0));
                                 }
                             }
                             if (need_amax) {
@@ -679,30 +675,39 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
                                     break;
                                 }
                             }
+                            float r[8];
 #pragma unroll
-                            for (int q = 0; q < 2; ++q) {
-                                const int item = item0 + lane + 32 * q;
-                                if (item >= P.M * 16) continue;
-                                const int t = item >> 4;
-                                const int kbl = item & 15;                 // block inside the stage
-                                float r[16];
-                                if (valid[q]) {
-                                    unpack16(raw[q], P.x_dtype, r);
-                                    const float pre = ldexpf(1.0f, e_row[t]);
+                            for (int w = 0; w < 8; ++w) r[w] = 0.0f;
+                            if (valid) {
+                                if (P.x_dtype == TPB200_F32) {
+                                    r[0] = __uint_as_float(raw[0].x); r[1] = __uint_as_float(raw[0].y);
+                                    r[2] = __uint_as_float(raw[0].z); r[3] = __uint_as_float(raw[0].w);
+                                    r[4] = __uint_as_float(raw[1].x); r[5] = __uint_as_float(raw[1].y);
+                                    r[6] = __uint_as_float(raw[1].z); r[7] = __uint_as_float(raw[1].w);
+                                } else {
+                                    const uint32_t w4[4] = {raw[0].x, raw[0].y, raw[0].z, raw[0].w};
 #pragma unroll
-                                    for (int w = 0; w < 16; ++w) r[w] *= pre;
+                                    for (int j = 0; j < 4; ++j) {
+                                        const float2 f = P.x_dtype == TPB200_F16
+                                                             ? __half22float2(*reinterpret_cast<const __half2*>(&w4[j]))
+                                                             : __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w4[j]));
+                                        r[2 * j] = f.x;
+                                        r[2 * j + 1] = f.y;
+                                    }
                                 }
-                                const int c = kbl >> 1;                    // 16-byte chunk of the 128-byte row
-                                for (int pc = 0; pc < P.pieces; ++pc) {
-                                    const int prow = pc * 16 + t;
-                                    uint8_t* dst = blk + prow * 128 + ((c ^ (prow & 7)) << 4) + (kbl & 1) * 8;
-                                    uint8_t* sf_dst = blk + NB * 128 + (kbl >> 2) * 512 + (prow & 31) * 16 + ((prow >> 5) & 3) * 4 + (kbl & 3);
-                                    uint32_t lo = 0, hi = 0;
-                                    uint8_t code = 0;
-                                    if (valid[q]) code = quantize_block16_piece(r, lo, hi);
-                                    *sf_dst = code;
-                                    *reinterpret_cast<uint2*>(dst) = make_uint2(lo, hi);
-                                }
+                                const float pre = ldexpf(1.0f, e_row[t]);
+#pragma unroll
+                                for (int w = 0; w < 8; ++w) r[w] *= pre;
+                            }
+                            const int c = kbl >> 1;                    // 16-byte chunk of the 128-byte row
+                            for (int pc = 0; pc < P.pieces; ++pc) {
+                                const int prow = pc * 16 + t;
+                                uint8_t* dst = blk + prow * 128 + ((c ^ (prow & 7)) << 4) + (kbl & 1) * 8 + hb * 4;
+                                uint8_t* sf_dst = blk + NB * 128 + (kbl >> 2) * 512 + (prow & 31) * 16 + ((prow >> 5) & 3) * 4 + (kbl & 3);
+                                uint32_t word;
+                                const uint8_t code = quantize_half8_piece(r, word);   // zeros in, zero code and scale out
+                                if (hb == 0) *sf_dst = code;
+                                *reinterpret_cast<uint32_t*>(dst) = word;
                             }
                         }
                         if (stop) break;
