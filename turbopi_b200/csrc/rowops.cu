@@ -74,10 +74,12 @@ __device__ __forceinline__ float gelu_tanh_hw(float x) {
     return __fdividef(x, 1.0f + __expf(-z2));
 }
 
-__device__ __forceinline__ void load16_bf16(const __nv_bfloat16* p, float (&v)[16]) {
+// E = 8 or 16 consecutive bf16 (16-byte aligned) <-> floats
+template <int E>
+__device__ __forceinline__ void load_bf16(const __nv_bfloat16* p, float (&v)[E]) {
     const uint4* q = reinterpret_cast<const uint4*>(p);
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < E / 8; ++i) {
         const uint4 u = __ldg(q + i);
         const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
@@ -89,23 +91,24 @@ __device__ __forceinline__ void load16_bf16(const __nv_bfloat16* p, float (&v)[1
     }
 }
 
-__device__ __forceinline__ void store16_bf16(__nv_bfloat16* p, const float (&v)[16]) {
-    uint32_t w[8];
+template <int E>
+__device__ __forceinline__ void store_bf16(__nv_bfloat16* p, const float (&v)[E]) {
+    uint32_t w[E / 2];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
+    for (int i = 0; i < E / 2; ++i) {
         __nv_bfloat162 b = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
         w[i] = *reinterpret_cast<uint32_t*>(&b);
     }
     uint4* q = reinterpret_cast<uint4*>(p);
-    q[0] = make_uint4(w[0], w[1], w[2], w[3]);
-    q[1] = make_uint4(w[4], w[5], w[6], w[7]);
+#pragma unroll
+    for (int i = 0; i < E / 8; ++i) q[i] = make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]);
 }
 
 // One CTA per row; thread t owns the 16-element blocks t and (for rows longer than 8192) t + T and keeps
 // them in registers from the global load to the code store; the only shared memory is the scratch of the
 // block-wide reductions.  512 threads x 2 blocks instead of 1024 x 1 for the longest rows: two CTAs fit an
 // SM's register file, so one row's reductions overlap the other's arithmetic.
-template <int NB>
+template <int NB, int E>
 __global__ void __launch_bounds__(kThreads) row_transform_quantize_kernel(const __grid_constant__ RowOpParams P) {
     __shared__ float red[kThreads / 32];
     // under programmatic dependent launch this kernel may start while its producer still runs
@@ -116,43 +119,44 @@ __global__ void __launch_bounds__(kThreads) row_transform_quantize_kernel(const 
     const int T = blockDim.x;
     const int tid = threadIdx.x;
     const int nblk = K >> 4;
-    float v[NB][16];
+    const int nunit = K / E;                    // units of E elements: whole 16-element blocks (E = 16) or halves (E = 8)
+    float v[NB][E];
 
     // ---- load (+ residual) ------------------------------------------------------------------
 #pragma unroll
     for (int j = 0; j < NB; ++j) {
-        const int kb = tid + j * T;
-        if (kb >= nblk) {
+        const int u = tid + j * T;
+        if (u >= nunit) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) v[j][i] = 0.0f;
+            for (int i = 0; i < E; ++i) v[j][i] = 0.0f;
             continue;
         }
-        const int k = kb << 4;
+        const int k = u * E;
         if (P.mode == TPB200_ROW_GELU_MUL || P.mode == TPB200_ROW_SILU_MUL) {
-            float g[16], u[16];
-            load16_bf16(P.x + static_cast<size_t>(m) * P.ldx + k, g);
-            load16_bf16(P.x + static_cast<size_t>(m) * P.ldx + K + k, u);
+            float g[E], up[E];
+            load_bf16<E>(P.x + static_cast<size_t>(m) * P.ldx + k, g);
+            load_bf16<E>(P.x + static_cast<size_t>(m) * P.ldx + K + k, up);
             if (P.mode == TPB200_ROW_GELU_MUL) {
 #pragma unroll
-                for (int i = 0; i < 16; ++i) v[j][i] = bf16r(bf16r(gelu_tanh_hw(g[i])) * u[i]);
+                for (int i = 0; i < E; ++i) v[j][i] = bf16r(bf16r(gelu_tanh_hw(g[i])) * up[i]);
             } else {
 #pragma unroll
-                for (int i = 0; i < 16; ++i) v[j][i] = bf16r(bf16r(__fdividef(g[i], 1.0f + __expf(-g[i]))) * u[i]);
+                for (int i = 0; i < E; ++i) v[j][i] = bf16r(bf16r(__fdividef(g[i], 1.0f + __expf(-g[i]))) * up[i]);
             }
         } else {
-            load16_bf16(P.x + static_cast<size_t>(m) * P.ldx + k, v[j]);
+            load_bf16<E>(P.x + static_cast<size_t>(m) * P.ldx + k, v[j]);
             if (P.res_in != nullptr) {
-                float h[16];
-                load16_bf16(P.res_in + static_cast<size_t>(m) * K + k, h);
+                float h[E];
+                load_bf16<E>(P.res_in + static_cast<size_t>(m) * K + k, h);
                 if (P.gate != nullptr) {
-                    float gt[16];
-                    load16_bf16(P.gate + k, gt);
+                    float gt[E];
+                    load_bf16<E>(P.gate + k, gt);
 #pragma unroll
-                    for (int i = 0; i < 16; ++i) v[j][i] = bf16r(v[j][i] * gt[i]);
+                    for (int i = 0; i < E; ++i) v[j][i] = bf16r(v[j][i] * gt[i]);
                 }
 #pragma unroll
-                for (int i = 0; i < 16; ++i) v[j][i] = bf16r(h[i] + v[j][i]);
-                if (P.h_out != nullptr) store16_bf16(P.h_out + static_cast<size_t>(m) * K + k, v[j]);
+                for (int i = 0; i < E; ++i) v[j][i] = bf16r(h[i] + v[j][i]);
+                if (P.h_out != nullptr) store_bf16<E>(P.h_out + static_cast<size_t>(m) * K + k, v[j]);
             }
         }
     }
@@ -163,24 +167,24 @@ __global__ void __launch_bounds__(kThreads) row_transform_quantize_kernel(const 
 #pragma unroll
         for (int j = 0; j < NB; ++j) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) ss += v[j][i] * v[j][i];
+            for (int i = 0; i < E; ++i) ss += v[j][i] * v[j][i];
         }
         ss = block_sum(ss, red);
         const float r = rsqrtf(ss / static_cast<float>(K) + P.eps);
 #pragma unroll
         for (int j = 0; j < NB; ++j) {
-            const int kb = tid + j * T;
-            if (kb >= nblk) continue;
-            float w0[16];
-            load16_bf16(P.w0 + (kb << 4), w0);
+            const int u = tid + j * T;
+            if (u >= nunit) continue;
+            float w0[E];
+            load_bf16<E>(P.w0 + u * E, w0);
             if (P.mode == TPB200_ROW_RMSNORM) {
 #pragma unroll
-                for (int i = 0; i < 16; ++i) v[j][i] = bf16r(v[j][i] * r * (1.0f + w0[i]));
+                for (int i = 0; i < E; ++i) v[j][i] = bf16r(v[j][i] * r * (1.0f + w0[i]));
             } else {
-                float w1[16];
-                load16_bf16(P.w1 + (kb << 4), w1);
+                float w1[E];
+                load_bf16<E>(P.w1 + u * E, w1);
 #pragma unroll
-                for (int i = 0; i < 16; ++i) v[j][i] = bf16r(v[j][i] * r * (1.0f + w0[i]) + w1[i]);
+                for (int i = 0; i < E; ++i) v[j][i] = bf16r(v[j][i] * r * (1.0f + w0[i]) + w1[i]);
             }
         }
     } else if (P.mode == TPB200_ROW_LAYERNORM) {
@@ -188,15 +192,15 @@ __global__ void __launch_bounds__(kThreads) row_transform_quantize_kernel(const 
 #pragma unroll
         for (int j = 0; j < NB; ++j) {
 #pragma unroll
-            for (int i = 0; i < 16; ++i) sm += v[j][i];
+            for (int i = 0; i < E; ++i) sm += v[j][i];
         }
         const float mean = block_sum(sm, red) / static_cast<float>(K);
         float ss = 0.0f;
 #pragma unroll
         for (int j = 0; j < NB; ++j) {
-            if (tid + j * T >= nblk) continue;
+            if (tid + j * T >= nunit) continue;
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
+            for (int i = 0; i < E; ++i) {
                 const float d = v[j][i] - mean;
                 ss += d * d;
             }
@@ -204,21 +208,21 @@ __global__ void __launch_bounds__(kThreads) row_transform_quantize_kernel(const 
         const float r = rsqrtf(block_sum(ss, red) / static_cast<float>(K) + P.eps);
 #pragma unroll
         for (int j = 0; j < NB; ++j) {
-            const int kb = tid + j * T;
-            if (kb >= nblk) continue;
-            float w0[16], w1[16];
-            load16_bf16(P.w0 + (kb << 4), w0);
-            load16_bf16(P.w1 + (kb << 4), w1);
+            const int u = tid + j * T;
+            if (u >= nunit) continue;
+            float w0[E], w1[E];
+            load_bf16<E>(P.w0 + u * E, w0);
+            load_bf16<E>(P.w1 + u * E, w1);
 #pragma unroll
-            for (int i = 0; i < 16; ++i) v[j][i] = bf16r((v[j][i] - mean) * r * w0[i] + w1[i]);
+            for (int i = 0; i < E; ++i) v[j][i] = bf16r((v[j][i] - mean) * r * w0[i] + w1[i]);
         }
     }
 
     if (P.y_out != nullptr) {
 #pragma unroll
         for (int j = 0; j < NB; ++j) {
-            const int kb = tid + j * T;
-            if (kb < nblk) store16_bf16(P.y_out + static_cast<size_t>(m) * K + (kb << 4), v[j]);
+            const int u = tid + j * T;
+            if (u < nunit) store_bf16<E>(P.y_out + static_cast<size_t>(m) * K + u * E, v[j]);
         }
     }
     if (P.packed == nullptr) return;
@@ -228,7 +232,7 @@ __global__ void __launch_bounds__(kThreads) row_transform_quantize_kernel(const 
 #pragma unroll
     for (int j = 0; j < NB; ++j) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[j][i]));
+        for (int i = 0; i < E; ++i) amax = fmaxf(amax, fabsf(v[j][i]));
     }
     amax = block_max(amax, red);
     int e = 0;
@@ -241,11 +245,16 @@ __global__ void __launch_bounds__(kThreads) row_transform_quantize_kernel(const 
     if (tid == 0) P.row_scale[m] = ldexpf(1.0f, -e);
 #pragma unroll
     for (int j = 0; j < NB; ++j) {
-        const int kb = tid + j * T;
-        if (kb >= P.kb_pad) continue;
+        // E = 16: this thread's whole block kb.  E = 8: half hb of block kb; the two lanes of a block derive the
+        // same scale (one shuffle for the block maximum), so every thread of the warp takes part (the launch has
+        // 2 * kb_pad threads, a multiple of 32: no thread is past the padded row)
+        const int u = tid + j * T;
+        const int kb = E == 16 ? u : u >> 1;
+        const int hb = E == 16 ? 0 : u & 1;
+        if (E == 16 && kb >= P.kb_pad) continue;
         const bool valid = kb < nblk;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) v[j][i] *= pre;
+        for (int i = 0; i < E; ++i) v[j][i] = valid ? v[j][i] * pre : 0.0f;
         for (int p = 0; p < P.pieces; ++p) {
             uint8_t* sf_dst;
             uint8_t* code_dst;
@@ -264,13 +273,20 @@ __global__ void __launch_bounds__(kThreads) row_transform_quantize_kernel(const 
                          (prow & 31) * 16 + ((prow >> 5) & 3) * 4 + (kb & 3);
                 code_dst = P.packed + static_cast<size_t>(prow) * P.pitch + kb * 8;
             }
-            if (!valid) {
-                *sf_dst = 0;
-                continue;
+            if constexpr (E == 16) {
+                if (!valid) {
+                    *sf_dst = 0;
+                    continue;
+                }
+                uint32_t lo, hi;
+                *sf_dst = quantize_block16_piece(v[j], lo, hi);
+                *reinterpret_cast<uint2*>(code_dst) = make_uint2(lo, hi);
+            } else {
+                uint32_t word;
+                const uint8_t code = quantize_half8_piece(v[j], word);   // zeros in: zero scale, zero codes
+                if (hb == 0) *sf_dst = code;
+                if (valid) *reinterpret_cast<uint32_t*>(code_dst + hb * 4) = word;
             }
-            uint32_t lo, hi;
-            *sf_dst = quantize_block16_piece(v[j], lo, hi);
-            *reinterpret_cast<uint2*>(code_dst) = make_uint2(lo, hi);
         }
     }
 }
@@ -323,7 +339,10 @@ extern "C" int tpb200_row_transform_quantize(const tpb200_rowop_args* a, tpb200_
     P.piece_rows = a->piece_rows;
     P.kb_pad = (a->K + 255) / 256 * 16;
     P.tiled = a->layout == TPB200_OPERANDS_TILED;
-    const int threads = std::min(tpb::kThreads, (P.kb_pad + 31) / 32 * 32);
+    // rows of up to 4096 elements: two threads per 16-element block (the three residual pieces are a dependent
+    // chain per block; halving it is what a latency-bound launch gains from); longer rows: one or two blocks per thread
+    const bool halves = a->packed != nullptr && P.kb_pad <= tpb::kThreads / 2;
+    const int threads = halves ? 2 * P.kb_pad : std::min(tpb::kThreads, (P.kb_pad + 31) / 32 * 32);
     TPB_REQUIRE((a->flags & ~TPB200_FLAG_PDL) == 0, TPB200_ERR_ENUM);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(a->M, 1, 1);
@@ -336,9 +355,10 @@ extern "C" int tpb200_row_transform_quantize(const tpb200_rowop_args* a, tpb200_
         cfg.attrs = attr;
         cfg.numAttrs = 1;
     }
-    const cudaError_t err = P.kb_pad <= tpb::kThreads
-                                ? cudaLaunchKernelEx(&cfg, tpb::row_transform_quantize_kernel<1>, P)
-                                : cudaLaunchKernelEx(&cfg, tpb::row_transform_quantize_kernel<2>, P);
+    const cudaError_t err = halves ? cudaLaunchKernelEx(&cfg, tpb::row_transform_quantize_kernel<1, 8>, P)
+                            : P.kb_pad <= tpb::kThreads
+                                ? cudaLaunchKernelEx(&cfg, tpb::row_transform_quantize_kernel<1, 16>, P)
+                                : cudaLaunchKernelEx(&cfg, tpb::row_transform_quantize_kernel<2, 16>, P);
     if (err != cudaSuccess) return TPB200_ERR_CUDA;
     return tpb_launch_status();
 }
