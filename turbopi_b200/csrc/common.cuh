@@ -100,6 +100,21 @@ __device__ __forceinline__ void bulk_copy_g2s(void* dst, const void* src, uint32
                  : "memory");
 }
 
+// The same copy with an L2 eviction hint: data that is read exactly once (a weight stream) should not push
+// small, reused data (activations, scratch, the next kernel's inputs) out of L2.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t policy;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(policy));
+    return policy;
+}
+__device__ __forceinline__ void bulk_copy_g2s_hint(void* dst, const void* src, uint32_t bytes, uint64_t* bar, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
+            smem_u32(dst)),
+        "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+        : "memory");
+}
+
 // Programmatic dependent launch: let the next kernel in the stream start its
 // independent prologue (weight prefetch) while this one is still running, and
 // wait for the previous kernel's results before touching dependent data.

@@ -322,8 +322,10 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
         }
         if (lane < pre) mbar_expect_tx(&ctl->full[lane], kWBlock + xbytes);
         __syncwarp();
+        const uint64_t stream_once = l2_policy_evict_first();   // weights pass through L2 once
         if (my_src != nullptr) {
-            bulk_copy_g2s(smem + (lane >> 2) * kStageBytes + (lane & 3) * kQuarter, my_src, kQuarter, &ctl->full[lane >> 2]);
+            bulk_copy_g2s_hint(smem + (lane >> 2) * kStageBytes + (lane & 3) * kQuarter, my_src, kQuarter,
+                               &ctl->full[lane >> 2], stream_once);
         }
         if (lane == 0) TL(2);
         pdl_wait_prior_grids();
@@ -378,8 +380,8 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
                 }
                 if (lane < 4) {
                     if (it >= pre) {
-                        bulk_copy_g2s(st + lane * kQuarter, pr.w_image + blk * kWBlock + lane * kQuarter, kQuarter,
-                                      &ctl->full[s]);
+                        bulk_copy_g2s_hint(st + lane * kQuarter, pr.w_image + blk * kWBlock + lane * kQuarter, kQuarter,
+                                           &ctl->full[s], stream_once);
                     }
                 } else if (lane == 4 && !fused) {
                     bulk_copy_g2s(st + kWBlock, static_cast<const uint8_t*>(pr.x) + static_cast<size_t>(ks) * xbytes, xbytes,
