@@ -341,7 +341,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_rowmajor_kernel(const __grid
         const uint32_t wbytes = static_cast<uint32_t>(rows) * row_bytes;
         const uint32_t sbytes = pr.scales_by_tma ? static_cast<uint32_t>(rows) * pr.scale_row_bytes : 0u;
         mbar_expect_tx(&full[s], wbytes + sbytes);
-        bulk_copy_g2s(wst + s * kWStage, pr.w + static_cast<size_t>(row0) * row_bytes, wbytes, &full[s]);
+        bulk_copy_g2s_hint(wst + s * kWStage, pr.w + static_cast<size_t>(row0) * row_bytes, wbytes, &full[s], l2_policy_evict_first());
         if (sbytes) {
             bulk_copy_g2s(sst + s * kSStage, pr.scales + static_cast<size_t>(row0) * pr.scale_row_bytes, sbytes,
                           &full[s]);
@@ -485,7 +485,7 @@ __global__ void __launch_bounds__(kWsThreads, 2) gemv_rowmajor_ws_kernel(const _
                 const uint32_t wbytes = static_cast<uint32_t>(rows) * row_bytes;
                 const uint32_t sbytes = pr.scales_by_tma ? static_cast<uint32_t>(rows) * pr.scale_row_bytes : 0u;
                 mbar_expect_tx(&full[s], wbytes + sbytes);
-                bulk_copy_g2s(wst + s * kWStage, pr.w + static_cast<size_t>(row0) * row_bytes, wbytes, &full[s]);
+                bulk_copy_g2s_hint(wst + s * kWStage, pr.w + static_cast<size_t>(row0) * row_bytes, wbytes, &full[s], l2_policy_evict_first());
                 if (sbytes) {
                     bulk_copy_g2s(sst + s * kSStage, pr.scales + static_cast<size_t>(row0) * pr.scale_row_bytes,
                                   sbytes, &full[s]);

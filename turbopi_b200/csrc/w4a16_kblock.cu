@@ -80,7 +80,7 @@ __global__ void __launch_bounds__(kThreads, 2) w4a16_kblock_kernel(const __grid_
         mbar_expect_tx(&full[s], static_cast<uint32_t>(qv) * (wb + sb));
         for (int q = 0; q < qv; ++q) {
             const size_t e = static_cast<size_t>(q0 + q) * N + n0;
-            bulk_copy_g2s(wst + s * kWStage + q * (kNT * 16), P.w + e * 16, wb, &full[s]);
+            bulk_copy_g2s_hint(wst + s * kWStage + q * (kNT * 16), P.w + e * 16, wb, &full[s], l2_policy_evict_first());
             if (sb) bulk_copy_g2s(sst + s * kSStage + q * (kNT * 2), P.scales + e, sb, &full[s]);
         }
     };
