@@ -327,6 +327,9 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
         bool wrapped = false;                              // the first pass over the ring finds every stage free
         bool stop = false;
         int pre = 0;                                       // stages whose B half went out before the wait
+        // weights are read once per inference (2.8 GB in all): they should not push the activations that the
+        // next kernel reads out of L2
+        const uint64_t weights_policy = l2_policy_evict_first();
         if (kTiled) {
             for (int w = blockIdx.x; w < total_items && pre < nstages; w += gridDim.x) {
                 const int tile = w / splits;
@@ -337,9 +340,9 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
                     if (lane == 0) mbar_expect_tx(&ctl->full[pre], stage_sz);
                     __syncwarp();
                     if (lane < 2) {
-                        bulk_copy_g2s(smem + pre * stage_sz + lane * kBlock,
-                                      P.b_image + (static_cast<size_t>(n_blk) * P.k_stages + ks) * (2 * kBlock) + lane * kBlock,
-                                      kBlock, &ctl->full[pre]);
+                        bulk_copy_g2s_hint(smem + pre * stage_sz + lane * kBlock,
+                                           P.b_image + (static_cast<size_t>(n_blk) * P.k_stages + ks) * (2 * kBlock) + lane * kBlock,
+                                           kBlock, &ctl->full[pre], weights_policy);
                     }
                 }
             }
@@ -380,7 +383,8 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemm_kernel(const __grid_co
                             lane < 2 ? P.b_image + (static_cast<size_t>(n_blk) * P.k_stages + ks) * (2 * kBlock) + lane * kBlock
                                      : P.a_image + (static_cast<size_t>(m_blk) * P.k_stages + ks) * (pieces * kBlock) +
                                            (lane - 2) * kBlock;
-                        bulk_copy_g2s(st + lane * kBlock, src, kBlock, &ctl->full[s]);
+                        if (lane < 2) bulk_copy_g2s_hint(st + lane * kBlock, src, kBlock, &ctl->full[s], weights_policy);
+                        else bulk_copy_g2s(st + lane * kBlock, src, kBlock, &ctl->full[s]);
                     }
                 } else if (lane == 0) {
                     tc::tma_load_2d(st, &P.map_b, ks * kBKBytes, n_blk * kBN, &ctl->full[s]);
