@@ -515,6 +515,19 @@ def run_extras(device, sets, x):
                                          "tensor_tflops": 3 * 2.0 * M * N * K / t / 1e12,
                                          "cublas_bf16_us": tb * 1e6, "cublas_bf16_tflops": 2.0 * M * N * K / tb / 1e12}
         del lins, wb
+    # (e2) the same NVFP4 x NVFP4 products on the tiled operand images (one e2m1 activation piece, 128 x 256 tiles):
+    # the form the prefix would run with e2m1 activations
+    for (M, N, K, name) in ((712, 16384, 2048, "gemma2b_gateup_M712"), (712, 2048, 16384, "gemma2b_down_M712")):
+        q1 = ops.QuantBuf(M, K, 1, device)
+        xq = torch.randn(M, K, device=device).to(torch.bfloat16)
+        lins = [TcLinear.from_weight(torch.randn(N, K, device=device) * 0.02) for _ in range(2)]
+        for l_ in lins:
+            l_.ws = gemm_ws
+        o = torch.empty((M, N), dtype=torch.bfloat16, device=device)
+        ops.rowop(tlib.ROW_NONE, xq, K, q1)
+        t = time_launches(lambda i: lins[i % 2](q1, o), 16)
+        ex[f"nvfp4_gemm_tiled_1piece_{name}"] = {"us": t * 1e6, "tflops": 2.0 * M * N * K / t / 1e12}
+        del lins
     # (g0) this GPU's own e2m1 block-scaled MMA rate: back-to-back 128 x 256 x 64 MMAs on resident operands, one
     # CTA per SM -- the measured denominator for the GEMM rates above (the nominal dense FP4 figure is 9 PFLOP/s)
     lib = tlib.load()

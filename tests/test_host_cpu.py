@@ -172,3 +172,36 @@ def test_gemv_tc_planner_covers_every_stage_and_fits_the_gpu():
     for bad in ([(4096, 1000)], [(0, 1024)], []):          # K not a multiple of the stage, empty problems
         status, _ = _gemv_tc_plan(bad) if bad else (_lib.load().tpb200_nvfp4_gemv_tc_plan(None, None, 0, 148, None), None)
         assert status != 0
+
+
+def test_attention_arguments_are_validated_on_the_host():
+    """tpb200_attention refuses bad shapes / strides / hand-over requests before any CUDA call (fake 16-byte
+    aligned pointers, no device needed)."""
+    lib = _lib.load()
+    two = ctypes.c_longlong * 2
+
+    def args(**kw):
+        a = dict(q=256, k=256, v=256, out=256, key_bias=None, n_rows=64, n_keys=300, head_dim=256, ldq=256, ldk=256,
+                 ldv=256, ldo=256, groups_outer=1, groups_inner=1, q_stride=two(0, 0), k_stride=two(0, 0),
+                 v_stride=two(0, 0), o_stride=two(0, 0), scale=1.0, workspace=None, workspace_bytes=0, flags=0,
+                 quant_image=None, quant_row_scale=None, quant_pieces=0, quant_rows_per_token=1)
+        a.update(kw)
+        return _lib.AttentionArgs(**a)
+
+    call = lambda **kw: lib.tpb200_attention(ctypes.byref(args(**kw)), None)
+    assert call(q=None) == -1
+    assert call(head_dim=264) == -2 and call(head_dim=12) == -2 and call(n_keys=0) == -2
+    assert call(ldq=128) == -2                         # row stride shorter than a row
+    assert call(q=264) == -3 and call(ldk=260) == -3    # not 16-byte aligned
+    assert call(flags=8) == -4
+    assert call() == -6                                 # two key tiles need the workspace
+    # fused hand-over to the next linear: one problem only, whole tokens, K a multiple of 256, 1..3 pieces
+    q = dict(quant_image=256, quant_row_scale=256, quant_pieces=3, quant_rows_per_token=8, workspace=256,
+             workspace_bytes=1 << 30)
+    assert call(**{**q, "groups_inner": 2}) == -2
+    assert call(**{**q, "quant_row_scale": None}) == -1
+    assert call(**{**q, "quant_pieces": 4}) == -2
+    assert call(**{**q, "n_rows": 60}) == -2            # 60 rows are not whole tokens of 8
+    assert call(**{**q, "quant_rows_per_token": 2, "head_dim": 72, "ldq": 72, "ldk": 72, "ldv": 72, "ldo": 72}) == -2
+    assert lib.tpb200_attention_workspace_size(400, 762, 256, 1) >= 4 * 6 * 128 * (256 + 2) * 4
+    assert lib.tpb200_attention_workspace_size(64, 300, 300, 1) == 0
