@@ -5,7 +5,8 @@
 
 Test infrastructure: the shared objects are used only by the `-m gpu` parity tests, as the checker for the
 plugin quantisers (quantizeWeightToINT4 / dequantizeINT4ToBF16 of openpi/w4a16_plugin/src/w4a16_gemm_kernel.cu,
-quantizeActivationToFP8 / quantizeWeightToNVFP4 of openpi/w4a8_plugin/src/w4a8_gemm_kernel.cu).  Each file is one
+quantizeActivationToFP8 / quantizeWeightToNVFP4 of openpi/w4a8_plugin/src/w4a8_gemm_kernel.cu) and for the NVFP4 GEMV
+(nvfp4_gemv_forward of openpi/nvfp4_packed_plugin/src/nvfp4_packed_kernel.cu).  Each file is one
 translation unit built with nvcc against the CUTLASS headers the reference vendors
 (openpi/external/cutlass_nvfp4_build/include); nothing of the reference's own build system runs and no source
 is copied.  Only the plain-CUDA quantiser entry points are ever called: the files' CUTLASS GEMMs use thread-block
@@ -22,6 +23,8 @@ OUT = HERE / "_ref"
 UNITS = {
     "libref_w4a16.so": "openpi/w4a16_plugin/src/w4a16_gemm_kernel.cu",
     "libref_w4a8.so": "openpi/w4a8_plugin/src/w4a8_gemm_kernel.cu",
+    # plain CUDA (no CUTLASS): the plugin's GEMV launcher nvfp4_gemv_forward and its kernels
+    "libref_nvfp4_packed.so": "openpi/nvfp4_packed_plugin/src/nvfp4_packed_kernel.cu",
 }
 
 

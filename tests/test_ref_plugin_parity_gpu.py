@@ -98,3 +98,46 @@ def test_nvfp4_weight_quantiser_equals_reference_cuda(cuda_device, N, K):
         got[tag] = (packed.cpu(), sc.cpu())
     assert torch.equal(got["ref"][1], got["ours"][1]), "scales"
     assert torch.equal(got["ref"][0], got["ours"][0]), "codes"
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 512, 1024), (3, 4096, 1024), (2, 1024, 4096)])
+@pytest.mark.parametrize("act,with_bias", [(0, False), (0, True), (1, True), (2, True)])
+def test_nvfp4_gemv_forward_equals_reference_cuda(cuda_device, M, N, K, act, with_bias):
+    """nvfp4_gemv_forward (the TensorRT plugin's launcher, fp32 tensors, fp32 block-32 scales on weights AND
+    activations, optional bias + GELU / SiLU) against the reference's own kernels
+    (openpi/nvfp4_packed_plugin/src/nvfp4_packed_kernel.cu, compiled unmodified).  The reference multiplies in
+    fp32; the kernel here carries scaled activations as fp16 pairs (relative rounding 2^-11 per product, fp32
+    sums), so the outputs agree to a few 1e-4 of the largest output -- far inside the 1e-2 bound of the
+    specification, but not bit for bit.  Prints both kernels' device times on this GPU."""
+    from oracle import nvfp4
+    from turbopi_b200 import _lib
+    ref, ours = _ref("libref_nvfp4_packed.so"), _lib.load()
+    rng = np.random.default_rng(M * 7 + N + K + act)
+    q, s = nvfp4.quantize_to_nvfp4((rng.normal(size=(N, K)) * 0.02).astype(np.float32), 32)
+    packed = torch.from_numpy(nvfp4.pack_nvfp4(q)).to(cuda_device)
+    sw = torch.from_numpy(s).to(cuda_device)
+    xq, xs = nvfp4.quantize_to_nvfp4(rng.normal(size=(M, K)).astype(np.float32), 32)
+    a, sa = torch.from_numpy(xq).to(cuda_device), torch.from_numpy(xs).to(cuda_device)
+    bias = torch.from_numpy(rng.normal(size=(N,)).astype(np.float32)).to(cuda_device) if with_bias else None
+    stream = torch.cuda.current_stream().cuda_stream
+    outs, times = {}, {}
+    for tag, lib in (("ref", ref), ("ours", ours)):
+        f = lib.nvfp4_gemv_forward
+        f.restype = None
+        f.argtypes = [P, P, P, P, P, P, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int, P]
+        out = torch.zeros((M, N), dtype=torch.float32, device=cuda_device)
+        call = lambda: f(a.data_ptr(), packed.data_ptr(), sa.data_ptr(), sw.data_ptr(),
+                         bias.data_ptr() if bias is not None else None, out.data_ptr(), M, N, K, act, 0, stream)
+        call()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(20):
+            call()
+        e1.record()
+        torch.cuda.synchronize()
+        outs[tag], times[tag] = out.cpu().numpy(), e0.elapsed_time(e1) / 20 * 1e3
+    assert ours.tpb200_last_error() == 0 and ours.tpb200_device_error(0) == 0
+    scale = np.abs(outs["ref"]).max()
+    assert np.abs(outs["ours"] - outs["ref"]).max() <= 2e-3 * scale
+    print(f"nvfp4_gemv_forward M={M} N={N} K={K} act={act}: reference kernel {times['ref']:.1f} us, ours {times['ours']:.1f} us")
