@@ -58,5 +58,59 @@ def build(ref_root=None, verbose=True):
     return built
 
 
+# The reference's torch extensions (pybind modules): its production GEMV (nvfp4_gemv_v5 / v6) and the fused QKV
+# projection with in-place cache write.  Built with torch.utils.cpp_extension from the sources where they lie, with the
+# flag the reference's own loader passes (--use_fast_math, openpi/nvfp4_packed_plugin/python/nvfp4_packed.py:58),
+# into oracle/_ref/<name>/; the tests import the finished .so directly (load_torch_ext), no reference checkout needed.
+TORCH_EXTS = {
+    "ref_nvfp4_gemv_v5": "openpi/nvfp4_packed_plugin/src/nvfp4_gemv_v5.cu",
+    "ref_fused_qkv_fp4": "openpi/kv_fuse_plugin/src/fused_qkv_fp4.cu",
+}
+
+
+def build_torch_exts(ref_root=None, verbose=True):
+    ref = Path(ref_root or os.environ.get("TURBOPI_REFERENCE", "/root/reference"))
+    if not ref.exists():
+        return []
+    from torch.utils import cpp_extension
+    OUT.mkdir(exist_ok=True)
+    built = []
+    for name, rel in TORCH_EXTS.items():
+        src, bdir = ref / rel, OUT / name
+        so = bdir / f"{name}.so"
+        if so.exists() and so.stat().st_mtime > src.stat().st_mtime:
+            built.append(so)
+            continue
+        bdir.mkdir(exist_ok=True)
+        try:
+            cpp_extension.load(name=name, sources=[str(src)], build_directory=str(bdir), verbose=False,
+                               extra_cuda_cflags=["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "--use_fast_math"],
+                               is_python_module=False)
+        except Exception as e:                           # a checker that does not build leaves its row to the Python pins
+            (OUT / (name + ".log")).write_text(str(e))
+            if verbose:
+                print(f"[oracle/build_ref] {rel} does not build here (see oracle/_ref/{name}.log)")
+            continue
+        built.append(so)
+        if verbose:
+            print(f"[oracle/build_ref] built {so}")
+    return built
+
+
+def load_torch_ext(name):
+    """Import oracle/_ref/<name>/<name>.so (built by build_torch_exts) as a module, or return None."""
+    import importlib.util
+    import torch  # noqa: F401  (the extension links against libtorch)
+    so = OUT / name / f"{name}.so"
+    if not so.exists():
+        return None
+    spec = importlib.util.spec_from_file_location(name, so)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
 if __name__ == "__main__":
-    build(sys.argv[1] if len(sys.argv) > 1 else None)
+    root = sys.argv[1] if len(sys.argv) > 1 else None
+    build(root)
+    build_torch_exts(root)

@@ -141,3 +141,63 @@ def test_nvfp4_gemv_forward_equals_reference_cuda(cuda_device, M, N, K, act, wit
     scale = np.abs(outs["ref"]).max()
     assert np.abs(outs["ours"] - outs["ref"]).max() <= 2e-3 * scale
     print(f"nvfp4_gemv_forward M={M} N={N} K={K} act={act}: reference kernel {times['ref']:.1f} us, ours {times['ours']:.1f} us")
+
+
+def _ref_ext(name):
+    from oracle import build_ref
+    mod = build_ref.load_torch_ext(name)
+    if mod is None:
+        pytest.skip(f"oracle/_ref/{name} not built (oracle/build_ref.py needs the reference checkout)")
+    return mod
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 4096, 1024), (1, 1024, 4096), (4, 512, 2048), (16, 256, 1024)])
+@pytest.mark.parametrize("act", [0, 1, 2])
+def test_nvfp4_gemv_v6_equals_reference_extension(cuda_device, M, N, K, act):
+    """ops.nvfp4_gemv_v6 against the reference's production GEMV (nvfp4_gemv_v6 of
+    openpi/nvfp4_packed_plugin/src/nvfp4_gemv_v5.cu, built unmodified with its --use_fast_math): same argument
+    list, same fp32 [M, N] result to a few 1e-4 of the largest output (fp16 activation pairs here, fp32 there)."""
+    from oracle import nvfp4
+    from turbopi_b200 import _lib, ops
+    ext = _ref_ext("ref_nvfp4_gemv_v5")
+    rng = np.random.default_rng(M + N + K + act)
+    q, s = nvfp4.quantize_to_nvfp4((rng.normal(size=(N, K)) * 0.02).astype(np.float32), 32)
+    packed = torch.from_numpy(nvfp4.pack_nvfp4(q)).to(cuda_device)
+    sw = torch.from_numpy(s).to(cuda_device)
+    x = torch.from_numpy(rng.normal(size=(M, K)).astype(np.float32)).to(cuda_device)
+    bias = torch.from_numpy(rng.normal(size=(N,)).astype(np.float32)).to(cuda_device)
+    want = ext.nvfp4_gemv_v6(x, packed, sw, bias, M, N, K, act)
+    got = ops.nvfp4_gemv_v6(x, packed, sw, bias, M, N, K, act)
+    torch.cuda.synchronize()
+    assert _lib.load().tpb200_device_error(0) == 0
+    assert got.shape == want.shape and got.dtype == want.dtype == torch.float32
+    assert (got - want).abs().max().item() <= 2e-3 * want.abs().max().item()
+
+
+@pytest.mark.parametrize("hidden", [2048, 1024])
+def test_fused_qkv_fp4_equals_reference_extension(cuda_device, hidden):
+    """kv_fuse.fused_qkv_fp4 (Q returned, K / V rows written in place at cache[b, cache_pos, 0, :], no RoPE, fp32)
+    against the reference's kernel (openpi/kv_fuse_plugin/src/fused_qkv_fp4.cu, built unmodified): Q and the
+    caches agree, and nothing but the addressed cache rows changes."""
+    from turbopi_b200 import kv_fuse
+    ext = _ref_ext("ref_fused_qkv_fp4")
+    B, H, KVH, D, S, pos = 2, 8, 1, 256, 16, 5
+    g = torch.Generator().manual_seed(hidden)
+    ws = []
+    for n in (H * D, KVH * D, KVH * D):
+        packed, sc = kv_fuse.quantize_to_fp4(torch.randn(n, hidden, generator=g) * 0.02)
+        ws += [packed.to(cuda_device), sc.to(cuda_device)]
+    x = torch.randn(B, hidden, generator=g).to(cuda_device)
+    res = {}
+    for tag, fn in (("ref", ext.fused_qkv_fp4), ("ours", kv_fuse.fused_qkv_fp4)):
+        kc = torch.full((B, S, KVH, D), -7.0, device=cuda_device)
+        vc = torch.full((B, S, KVH, D), -7.0, device=cuda_device)
+        qo = fn(x, *ws, kc, vc, hidden, H, KVH, D, pos)
+        torch.cuda.synchronize()
+        res[tag] = (qo.float().cpu(), kc.cpu(), vc.cpu())
+    for a, b in zip(res["ref"], res["ours"]):
+        assert (a - b).abs().max().item() <= 2e-3 * a.abs().max().item()
+    for t in res["ours"][1:]:
+        mask = torch.ones_like(t, dtype=torch.bool)
+        mask[:, pos] = False
+        assert (t[mask] == -7.0).all()
