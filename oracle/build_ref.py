@@ -65,6 +65,7 @@ def build(ref_root=None, verbose=True):
 TORCH_EXTS = {
     "ref_nvfp4_gemv_v5": "openpi/nvfp4_packed_plugin/src/nvfp4_gemv_v5.cu",
     "ref_fused_qkv_fp4": "openpi/kv_fuse_plugin/src/fused_qkv_fp4.cu",
+    "ref_nvfp4_packed_torch": "openpi/nvfp4_packed_plugin/src/nvfp4_packed_torch.cu",
 }
 
 

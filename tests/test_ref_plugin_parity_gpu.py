@@ -201,3 +201,27 @@ def test_fused_qkv_fp4_equals_reference_extension(cuda_device, hidden):
         mask = torch.ones_like(t, dtype=torch.bool)
         mask[:, pos] = False
         assert (t[mask] == -7.0).all()
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 2048, 1024), (3, 512, 4096)])
+@pytest.mark.parametrize("act", [0, 1, 2])
+def test_nvfp4_gemv_torch_variants_equal_reference_extension(cuda_device, M, N, K, act):
+    """ops.nvfp4_gemv (per-block activation scales) and ops.nvfp4_gemv_w4a16 against the reference's
+    nvfp4_packed_torch.cu extension (openpi/nvfp4_packed_plugin/src/nvfp4_packed_torch.cu:173-290), built unmodified."""
+    from oracle import nvfp4
+    from turbopi_b200 import ops
+    ext = _ref_ext("ref_nvfp4_packed_torch")
+    rng = np.random.default_rng(M * 31 + N + K + act)
+    q, s = nvfp4.quantize_to_nvfp4((rng.normal(size=(N, K)) * 0.02).astype(np.float32), 32)
+    packed = torch.from_numpy(nvfp4.pack_nvfp4(q)).to(cuda_device)
+    sw = torch.from_numpy(s).to(cuda_device)
+    bias = torch.from_numpy(rng.normal(size=(N,)).astype(np.float32)).to(cuda_device)
+    x = torch.from_numpy(rng.normal(size=(M, K)).astype(np.float32)).to(cuda_device)
+    xq, xs = nvfp4.quantize_to_nvfp4(rng.normal(size=(M, K)).astype(np.float32), 32)
+    a, sa = torch.from_numpy(xq).to(cuda_device), torch.from_numpy(xs).to(cuda_device)
+    pairs = [(ext.nvfp4_gemv_w4a16(x, packed, sw, bias, M, N, K, act), ops.nvfp4_gemv_w4a16(x, packed, sw, bias, M, N, K, act)),
+             (ext.nvfp4_gemv(a, packed, sa, sw, bias, M, N, K, act), ops.nvfp4_gemv(a, packed, sa, sw, bias, M, N, K, act))]
+    torch.cuda.synchronize()
+    for want, got in pairs:
+        assert got.shape == want.shape
+        assert (got.float() - want.float()).abs().max().item() <= 2e-3 * want.float().abs().max().item()
