@@ -1,7 +1,7 @@
 #!/usr/bin/env python3
 """Compile the reference's own plugin kernels, from the sources where they lie, into oracle/_ref/.
 
-    python oracle/build_ref.py <reference-root>      (default: $TURBOPI_REFERENCE, else /root/reference)
+    python oracle/build_ref.py <reference-root>      (default: $TURBOPI_REFERENCE, else the checkout beside this build)
 
 Test infrastructure: the shared objects are used only by the `-m gpu` parity tests, as the checker for the
 plugin quantisers (quantizeWeightToINT4 / dequantizeINT4ToBF16 of openpi/w4a16_plugin/src/w4a16_gemm_kernel.cu,
@@ -19,6 +19,7 @@ import sys
 from pathlib import Path
 
 HERE = Path(__file__).resolve().parent
+DEFAULT_REFERENCE = "/root/reference"
 OUT = HERE / "_ref"
 UNITS = {
     "libref_w4a16.so": "openpi/w4a16_plugin/src/w4a16_gemm_kernel.cu",
@@ -29,7 +30,7 @@ UNITS = {
 
 
 def build(ref_root=None, verbose=True):
-    ref = Path(ref_root or os.environ.get("TURBOPI_REFERENCE", "/root/reference"))
+    ref = Path(ref_root or os.environ.get("TURBOPI_REFERENCE", DEFAULT_REFERENCE))
     if not ref.exists():
         if verbose:
             print(f"[oracle/build_ref] {ref} not present: keeping whatever oracle/_ref/ already holds")
@@ -70,7 +71,7 @@ TORCH_EXTS = {
 
 
 def build_torch_exts(ref_root=None, verbose=True):
-    ref = Path(ref_root or os.environ.get("TURBOPI_REFERENCE", "/root/reference"))
+    ref = Path(ref_root or os.environ.get("TURBOPI_REFERENCE", DEFAULT_REFERENCE))
     if not ref.exists():
         return []
     from torch.utils import cpp_extension
