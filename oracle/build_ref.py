@@ -29,34 +29,38 @@ UNITS = {
 }
 
 
+def _reference(ref_root):
+    return Path(ref_root or os.environ.get("TURBOPI_REFERENCE", DEFAULT_REFERENCE))
+
+
+def _build_unit(ref, name, rel, verbose):
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    inc = ref / "openpi" / "external" / "cutlass_nvfp4_build"
+    src, dst = ref / rel, OUT / name
+    if dst.exists() and dst.stat().st_mtime > src.stat().st_mtime:
+        return dst
+    cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O2", "-std=c++17", "-Xcompiler", "-fPIC",
+           "--expt-relaxed-constexpr", "-shared", "-cudart", "shared", "-I", str(inc / "include"),
+           "-I", str(inc / "tools" / "util" / "include"), "-o", str(dst), str(src)]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    (OUT / (name + ".log")).write_text(r.stdout + r.stderr)
+    if r.returncode != 0:
+        if verbose:
+            print(f"[oracle/build_ref] {rel} does not build here (see oracle/_ref/{name}.log); its entry points stay unpinned")
+        return None
+    if verbose:
+        print(f"[oracle/build_ref] built {dst}")
+    return dst
+
+
 def build(ref_root=None, verbose=True):
-    ref = Path(ref_root or os.environ.get("TURBOPI_REFERENCE", DEFAULT_REFERENCE))
+    ref = _reference(ref_root)
     if not ref.exists():
         if verbose:
             print(f"[oracle/build_ref] {ref} not present: keeping whatever oracle/_ref/ already holds")
         return []
-    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
-    inc = ref / "openpi" / "external" / "cutlass_nvfp4_build"
     OUT.mkdir(exist_ok=True)
-    built = []
-    for name, rel in UNITS.items():
-        src, dst = ref / rel, OUT / name
-        if dst.exists() and dst.stat().st_mtime > src.stat().st_mtime:
-            built.append(dst)
-            continue
-        cmd = [nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O2", "-std=c++17", "-Xcompiler", "-fPIC",
-               "--expt-relaxed-constexpr", "-shared", "-cudart", "shared", "-I", str(inc / "include"),
-               "-I", str(inc / "tools" / "util" / "include"), "-o", str(dst), str(src)]
-        r = subprocess.run(cmd, capture_output=True, text=True)
-        (OUT / (name + ".log")).write_text(r.stdout + r.stderr)
-        if r.returncode != 0:
-            if verbose:
-                print(f"[oracle/build_ref] {rel} does not build here (see oracle/_ref/{name}.log); its quantisers stay unpinned")
-            continue
-        built.append(dst)
-        if verbose:
-            print(f"[oracle/build_ref] built {dst}")
-    return built
+    return [d for d in (_build_unit(ref, n, r, verbose) for n, r in UNITS.items()) if d is not None]
 
 
 # The reference's torch extensions (pybind modules): its production GEMV (nvfp4_gemv_v5 / v6) and the fused QKV
@@ -70,33 +74,49 @@ TORCH_EXTS = {
 }
 
 
+def _build_ext(ref, name, rel, verbose):
+    from torch.utils import cpp_extension
+    src, bdir = ref / rel, OUT / name
+    so = bdir / f"{name}.so"
+    if so.exists() and so.stat().st_mtime > src.stat().st_mtime:
+        return so
+    bdir.mkdir(exist_ok=True)
+    try:
+        cpp_extension.load(name=name, sources=[str(src)], build_directory=str(bdir), verbose=False,
+                           extra_cuda_cflags=["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "--use_fast_math"],
+                           is_python_module=False)
+    except Exception as e:                           # a checker that does not build leaves its row to the Python pins
+        (OUT / (name + ".log")).write_text(str(e))
+        if verbose:
+            print(f"[oracle/build_ref] {rel} does not build here (see oracle/_ref/{name}.log)")
+        return None
+    if verbose:
+        print(f"[oracle/build_ref] built {so}")
+    return so
+
+
 def build_torch_exts(ref_root=None, verbose=True):
-    ref = Path(ref_root or os.environ.get("TURBOPI_REFERENCE", DEFAULT_REFERENCE))
+    ref = _reference(ref_root)
     if not ref.exists():
         return []
-    from torch.utils import cpp_extension
     OUT.mkdir(exist_ok=True)
-    built = []
-    for name, rel in TORCH_EXTS.items():
-        src, bdir = ref / rel, OUT / name
-        so = bdir / f"{name}.so"
-        if so.exists() and so.stat().st_mtime > src.stat().st_mtime:
-            built.append(so)
-            continue
-        bdir.mkdir(exist_ok=True)
-        try:
-            cpp_extension.load(name=name, sources=[str(src)], build_directory=str(bdir), verbose=False,
-                               extra_cuda_cflags=["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "--use_fast_math"],
-                               is_python_module=False)
-        except Exception as e:                           # a checker that does not build leaves its row to the Python pins
-            (OUT / (name + ".log")).write_text(str(e))
-            if verbose:
-                print(f"[oracle/build_ref] {rel} does not build here (see oracle/_ref/{name}.log)")
-            continue
-        built.append(so)
+    return [d for d in (_build_ext(ref, n, r, verbose) for n, r in TORCH_EXTS.items()) if d is not None]
+
+
+def build_all(ref_root=None, verbose=True):
+    """Every checker, the translation units side by side (each is one compiler run of minutes; nothing is rebuilt
+    while its output is newer than its source)."""
+    from concurrent.futures import ThreadPoolExecutor
+    ref = _reference(ref_root)
+    if not ref.exists():
         if verbose:
-            print(f"[oracle/build_ref] built {so}")
-    return built
+            print(f"[oracle/build_ref] {ref} not present: keeping whatever oracle/_ref/ already holds")
+        return []
+    OUT.mkdir(exist_ok=True)
+    jobs = [(_build_unit, n, r) for n, r in UNITS.items()] + [(_build_ext, n, r) for n, r in TORCH_EXTS.items()]
+    with ThreadPoolExecutor(max_workers=len(jobs)) as pool:
+        done = list(pool.map(lambda j: j[0](ref, j[1], j[2], verbose), jobs))
+    return [d for d in done if d is not None]
 
 
 def load_torch_ext(name):
@@ -113,6 +133,4 @@ def load_torch_ext(name):
 
 
 if __name__ == "__main__":
-    root = sys.argv[1] if len(sys.argv) > 1 else None
-    build(root)
-    build_torch_exts(root)
+    build_all(sys.argv[1] if len(sys.argv) > 1 else None)
