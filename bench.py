@@ -420,8 +420,12 @@ def run_extras(device, sets, x):
     xi = torch.randn(1, K, device=device).to(torch.bfloat16)
     oi = torch.empty((1, N), dtype=torch.bfloat16, device=device)
     nbytes = N * K // 2 + N * (K // G) * 2 + K * 2 + N * 2
-    t = time_launches(lambda i: ops.w4a16_gemv_out(xi, ws[i % 16], sc[i % 16], oi, group_size=G, layout=1), 64)
-    ex["w4a16_int4_rowmajor_g128_16384x2048"] = {"us": t * 1e6, "gbps": nbytes / t / 1e9, "bytes": nbytes}
+    t = time_launches(lambda i: ops.w4a16_gemv_out(xi, ws[i % 16], sc[i % 16], oi, group_size=G, layout=1, pdl=True), 64)
+    t_plain = time_launches(lambda i: ops.w4a16_gemv_out(xi, ws[i % 16], sc[i % 16], oi, group_size=G, layout=1), 64)
+    ex["w4a16_int4_rowmajor_g128_16384x2048"] = {"us": t * 1e6, "gbps": nbytes / t / 1e9, "bytes": nbytes,
+                                                 "launch": "64 launches in one graph, chained by programmatic dependent launch "
+                                                           "(as the headline's steps are)",
+                                                 "us_without_pdl": t_plain * 1e6}
     # reference layout (K/32, N, 4) g=32, fp16 in / fp32 out
     wk = [torch.randint(-2 ** 31, 2 ** 31 - 1, (K // 32, N, 4), device=device, dtype=torch.int32) for _ in range(16)]
     sk = [(torch.rand(K // 32, N, device=device) * 0.015 + 0.005).to(torch.float16) for _ in range(16)]

@@ -103,6 +103,36 @@ def test_w4a16_benchmark_config_rowmajor_g128(cuda_device):
     assert _canary_ok(buf)
 
 
+@pytest.mark.parametrize("N,K,G", [(256, 2048, 128), (4096, 1024, 32), (48, 4096, 64), (1600, 2048, 2048), (16, 1024, 128)])
+@pytest.mark.parametrize("xdt,sdt,with_bias", [(torch.bfloat16, np.float16, False), (torch.float16, np.float16, True),
+                                               (torch.float32, "bf16", True)])
+def test_w4a16_one_token_rowmajor_kernel(cuda_device, N, K, G, xdt, sdt, with_bias):
+    """The single-token row-major kernel (K of 1024 / 2048 / 4096, any group that is a multiple of 32, fp16 or bf16
+    scales, every activation dtype, optional bias, PDL flag) against the dequantise-then-matmul oracle; the words past
+    the output stay untouched."""
+    from turbopi_b200 import ops
+    rng = np.random.default_rng(N + K + G)
+    codes = rng.integers(0, 16, size=(N, K), dtype=np.uint8)
+    words = int4._pack_words(codes, "rowmajor")
+    scales = rng.uniform(0.005, 0.02, size=(N, K // G)).astype(np.float32)
+    if sdt == "bf16":
+        scales = _bf16(scales)
+        sc_dev = _dev(scales, cuda_device, torch.bfloat16)
+    else:
+        scales = scales.astype(np.float16)
+        sc_dev = _dev(scales, cuda_device)
+    x = rng.normal(size=(1, K)).astype(np.float32)
+    x = _bf16(x) if xdt == torch.bfloat16 else x.astype(np.float16).astype(np.float32) if xdt == torch.float16 else x
+    bias = rng.normal(size=(N,)).astype(np.float32) if with_bias else None
+    ref = int4.gemv_dequant_matmul(x, words, scales.astype(np.float32), "rowmajor", G, bias)
+    for pdl in (False, True):
+        buf, out = _canary_out(1, N, torch.bfloat16, cuda_device)
+        ops.w4a16_gemv_out(_dev(x, cuda_device, xdt), _dev(words, cuda_device), sc_dev, out,
+                           bias=_dev(bias, cuda_device) if with_bias else None, group_size=G, layout=1, pdl=pdl)
+        _check(out.float().cpu().numpy(), ref)
+        assert _canary_ok(buf)
+
+
 @pytest.mark.parametrize("N,K", [(16384, 2048), (2048, 16384), (100, 64), (64, 32), (1000, 4096)])
 def test_w4a16_reference_layout_kblock(cuda_device, N, K):
     """The reference op's contract: fp16 (1,K) x (K/32,N,4) int32 + (K/32,N) fp16 -> fp32 (1,N)."""

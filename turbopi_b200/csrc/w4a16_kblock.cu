@@ -227,11 +227,26 @@ int device_error_w4a16_kblock(int clear) { return read_device_error(clear); }
 
 }  // namespace tpb
 
+namespace tpb {
+int w4a16_rowmajor_lean(const void* x, int x_dtype, const void* weight_packed, const void* scales, int scale_dtype,
+                        const void* bias, int bias_dtype, void* out, int out_dtype, int M, int N, int K, int group_size,
+                        int flags, cudaStream_t stream);
+}
+
 extern "C" int tpb200_w4a16_gemv(const void* x, int x_dtype, const void* weight_packed, const void* scales,
                                  int scale_dtype, const void* bias, int bias_dtype, void* out, int out_dtype, int M,
                                  int N, int K, int group_size, int layout, int flags, tpb200_stream_t stream_) {
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
     if (layout == TPB200_INT4_ROWMAJOR) {
+        // one token, K of 1024 / 2048 / 4096: the kernel written for that class (benchmark config 1); every other
+        // shape, and every argument that needs refusing, goes to the general decode kernel and its checks
+        if (x && weight_packed && scales && out && tpb_valid_dtype(x_dtype) && tpb_valid_dtype(out_dtype) &&
+            tpb_valid_dtype(bias_dtype) && (flags & ~TPB200_FLAG_PDL) == 0 && tpb_aligned16(x) &&
+            tpb_aligned16(weight_packed) && tpb_aligned16(scales) && tpb_aligned16(out) && N >= 1) {
+            const int st = tpb::w4a16_rowmajor_lean(x, x_dtype, weight_packed, scales, scale_dtype, bias, bias_dtype, out,
+                                                    out_dtype, M, N, K, group_size, flags, stream);
+            if (st <= 0) return st;
+        }
         return tpb::gemv_rowmajor_single(1, x, x_dtype, nullptr, weight_packed, scales, scale_dtype, group_size, 1.0f,
                                          bias, bias_dtype, out, out_dtype, M, N, K, TPB200_ACT_NONE, flags, stream);
     }
