@@ -34,7 +34,7 @@ def _dequant(layer):
 
 
 @torch.no_grad()
-@pytest.mark.parametrize("T", [1, 4, 16, 50, 712])
+@pytest.mark.parametrize("T", [1, 4, 5, 16, 50, 712])
 @pytest.mark.parametrize("act", ["none", "gelu"])
 def test_nvfp4_packed_linear_dispatches_to_tensor_cores(cuda_device, T, act):
     from turbopi_b200 import _lib
@@ -57,8 +57,10 @@ def test_nvfp4_packed_linear_dispatches_to_tensor_cores(cuda_device, T, act):
     if names is not None:
         gemm = [n for n in names if "nvfp4_gemm_kernel" in n]
         gemv = [n for n in names if "nvfp4_gemv_tc_kernel" in n]
-        assert len(gemm) + len(gemv) == 1, names                      # ONE weight pass, whatever the token count
-        assert (len(gemv) == 1) == (T <= 16)
+        cuda_core = [n for n in names if "gemv_rowmajor" in n]
+        assert len(gemm) + len(gemv) + len(cuda_core) == 1, names     # ONE weight pass, whatever the token count
+        assert (len(cuda_core) == 1) == (T <= 4)                      # a few tokens: the packed rows as stored
+        assert (len(gemv) == 1) == (4 < T <= 16)
     # leading dimensions are kept
     y3 = layer(x.to(cuda_device).reshape(1, T, 1024))
     assert y3.shape == (1, T, 768) and torch.equal(y3[0], y)
@@ -102,7 +104,7 @@ def test_nvfp4_packed_mlp_runs_gate_and_up_as_one_launch(cuda_device, T, act):
     assert cosine(y.float().cpu().numpy(), ref.numpy()) >= 0.999
     names = _kernel_names(lambda: mlp(x.to(cuda_device)))
     if names is not None:
-        weight_passes = [n for n in names if "nvfp4_gemm_kernel" in n or "nvfp4_gemv_tc_kernel" in n]
+        weight_passes = [n for n in names if "nvfp4_gemm_kernel" in n or "nvfp4_gemv_tc_kernel" in n or "gemv_rowmajor" in n]
         assert len(weight_passes) == 2, names                         # gate+up together, then down
 
 

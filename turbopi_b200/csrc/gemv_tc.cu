@@ -785,16 +785,32 @@ __global__ void __launch_bounds__(kThreads, 1) nvfp4_gemv_tc_kernel(const __grid
                 finalize = (ctl->ticket == un.nslots - 1);
                 if (finalize) {
                     __threadfence();
+                    if (P.M == 1) {
 #pragma unroll
-                    for (int h = 0; h < 2; ++h) {
+                        for (int h = 0; h < 2; ++h) {
+                            float acc = 0.0f;
+                            for (int sl = 0; sl < un.nslots; ++sl) {
+                                acc += __ldcg(part + static_cast<size_t>(sl) * kSlotFloats + h * 128 + et);
+                            }
+                            v[h][0] = acc;
+                        }
+                    } else {
+                        // several tokens: slot by slot (the sum keeps its K order) with all of a slot's loads in
+                        // flight together -- token by token the walk is a chain of M * slots L2 round trips
 #pragma unroll
-                        for (int t = 0; t < 16; ++t) {
-                            if (t < P.M) {
-                                float acc = 0.0f;
-                                for (int sl = 0; sl < un.nslots; ++sl) {
-                                    acc += __ldcg(part + (static_cast<size_t>(sl) * 16 + t) * 256 + h * 128 + et);
+                        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                            for (int t = 0; t < 16; ++t) v[h][t] = 0.0f;
+                        }
+#pragma unroll 2
+                        for (int sl = 0; sl < un.nslots; ++sl) {
+                            const float* src = part + static_cast<size_t>(sl) * kSlotFloats + et;
+#pragma unroll
+                            for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                                for (int t = 0; t < 16; ++t) {
+                                    if (t < P.M) v[h][t] += __ldcg(src + t * 256 + h * 128);
                                 }
-                                v[h][t] = acc;
                             }
                         }
                     }

@@ -87,10 +87,11 @@ class NVFP4PackedLinear(nn.Module):
     [N, K/block] (fp32 for the "ref" format, uint8 E4M3 bytes + `global_scale` for
     "nvfp4").  forward() accepts any leading shape and dispatches on the token count:
 
-      "nvfp4" weights   <= 16 tokens: ONE tensor-core GEMV launch (activations quantised in the launch
-                        for <= 4 tokens); more tokens: the tcgen05 block-scaled GEMM on the tiled weight
-                        image (bf16 activations as three residual e2m1 pieces).  The tiled image is built
-                        once, on the first forward, and serves both kernels.
+      "nvfp4" weights   <= 4 tokens: the CUDA-core GEMV on the packed rows as stored; 5..16 tokens: one
+                        tensor-core GEMV launch behind a quantiser launch; more tokens: the tcgen05
+                        block-scaled GEMM on the tiled weight image (bf16 activations as three residual
+                        e2m1 pieces).  The tiled image is built once, on the first forward that needs it,
+                        and serves both tensor-core kernels.
       "ref" weights     fp32 scales per 32 are not an operand format of the block-scaled tensor cores:
                         rows go through the CUDA-core GEMV 16 at a time, exactly as stored.
 
@@ -156,8 +157,13 @@ class NVFP4PackedLinear(nn.Module):
 
     def _forward_tensor_cores(self, x2, act, bias):
         T = x2.shape[0]
-        image, gemv_ws, gemm_ws = self._tc_state()
         out = torch.empty((T, self.out_features), dtype=x2.dtype, device=x2.device)
+        if T <= 4 and self.in_features % 32 == 0 and self.weight_packed.is_contiguous():
+            # one matrix, a few tokens: the CUDA-core GEMV streams the packed rows as stored and has no
+            # split-K hand-over at the end (4.5-12 us against 9-27 us for the tensor-core kernel, whose
+            # ground is many matrices per launch)
+            return ops.nvfp4_gemv_out(x2, self.weight_packed, self.weight_scales, out, bias, act, 16, self.global_scale)
+        image, gemv_ws, gemm_ws = self._tc_state()
         if T <= 16:
             return ops.tc_gemv(x2, image, self.out_features, out, self.global_scale, bias, act, 3, gemv_ws)
         xb = x2 if x2.dtype == torch.bfloat16 else x2.to(torch.bfloat16)
@@ -272,7 +278,10 @@ class NVFP4PackedMLP(nn.Module):
             ops.tc_gemv(x2, gu_image, 2 * I, gu, g.global_scale, None, 0, 3, gu_gemv_ws)
             h = torch.empty((T, I), dtype=torch.bfloat16, device=x2.device)
             ops.rowop(mode, gu, I, None, y_out=h, M=T)
-            ops.tc_gemv(h, d_image, self.hidden_size, out, d.global_scale, d_bias, 0, 3, d_gemv_ws)
+            if T <= 4 and d.in_features % 32 == 0 and d.weight_packed.is_contiguous():
+                ops.nvfp4_gemv_out(h, d.weight_packed, d.weight_scales, out, d_bias, 0, 16, d.global_scale)
+            else:
+                ops.tc_gemv(h, d_image, self.hidden_size, out, d.global_scale, d_bias, 0, 3, d_gemv_ws)
         else:
             ops.nvfp4_gemm_w4a16_tiled(x2, gu_image, 2 * I, alpha=g.global_scale, pieces=3, out=gu, workspace=gu_gemm_ws)
             q = ops.QuantBuf(T, I, 3, x2.device)
