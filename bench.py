@@ -736,6 +736,18 @@ def run_case(args):
         sc = (torch.rand(K // 32, N, device=dev) * 0.015 + 0.005).to(torch.float16)
         ms = timed(lambda: ops.w4a16_gemv(x, w, sc), args.iters)
         print(f"int4-gemv N={N} K={K} (k-block layout, group 32): {ms * 1e3:.1f} us per call")
+    elif args.case == "int4-gemv-rowmajor":   # benchmark config 1: row-major [N, K/8] words, group 128, one bf16 row
+        x = torch.randn(1, K, device=dev, generator=g).to(torch.bfloat16)
+        ws = [torch.randint(-2 ** 31, 2 ** 31 - 1, (N, K // 8), device=dev, dtype=torch.int32) for _ in range(8)]
+        sc = (torch.rand(N, K // 128, device=dev) * 0.015 + 0.005).to(torch.float16)
+        o = torch.empty((1, N), dtype=torch.bfloat16, device=dev)
+        it = [0]
+
+        def step():                    # eight weight matrices in turn: 8 x N x K / 2 bytes, more than the L2 holds at config 1
+            it[0] += 1
+            ops.w4a16_gemv_out(x, ws[it[0] % 8], sc, o, group_size=128, layout=1)
+        ms = timed(step, args.iters)
+        print(f"int4-gemv N={N} K={K} (row-major layout, group 128): {ms * 1e3:.1f} us per call")
     elif args.case == "quantize":      # bf16 activations -> e2m1 codes + swizzled UE4M3 scales
         x = torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16)
         packed, sf = ops.nvfp4_quantize_act(x)
@@ -847,7 +859,7 @@ def main():
     ap.add_argument("--no-pdl", action="store_true",
                     help="--path tc: no programmatic dependent launch between quantiser and GEMV")
     ap.add_argument("--no-serving", action="store_true", help="skip the request-serving measurement (builds a full model)")
-    ap.add_argument("--case", default=None, choices=["gemm", "gemm-nvfp4", "rowop", "attention", "pi05", "int4-gemm", "int4-gemv", "quantize"],
+    ap.add_argument("--case", default=None, choices=["gemm", "gemm-nvfp4", "rowop", "attention", "pi05", "int4-gemm", "int4-gemv", "int4-gemv-rowmajor", "quantize"],
                     help="run one bounded kernel case (for ncu) instead of the benchmark")
     ap.add_argument("--M", type=int, default=712)
     ap.add_argument("--N", type=int, default=32768)

@@ -134,7 +134,10 @@ __global__ void __launch_bounds__(kLeanThreads, 2) w4a16_rowmajor_lean_kernel(co
 
     const uint32_t k1032 = 0x64086408u;
     const __half2 h1032 = *reinterpret_cast<const __half2*>(&k1032);
-    const int chunks_per_group = P.group >> 5;
+    // the scale group of each of this lane's chunks: the same for every row, so the division is done once
+    int grp[CH];
+#pragma unroll
+    for (int c = 0; c < CH; ++c) grp[c] = (lane + 32 * c) / (P.group >> 5);
     bool ok = true;
     for (int i = 0; i < ntile && ok; ++i) {
         const int s = i % kLeanStages;
@@ -172,10 +175,9 @@ __global__ void __launch_bounds__(kLeanThreads, 2) w4a16_rowmajor_lean_kernel(co
                 }
                 const __half2 sum2 = __hadd2(__hadd2(acc[0], acc[1]), __hadd2(acc[2], acc[3]));
                 const float2 f = __half22float2(sum2);
-                const int g = chunk / chunks_per_group;
                 const float sc = P.scale_dtype == TPB200_SCALE_F16
-                                     ? __half2float(reinterpret_cast<const __half*>(st)[r * groups + g])
-                                     : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(st)[r * groups + g]);
+                                     ? __half2float(reinterpret_cast<const __half*>(st)[r * groups + grp[c]])
+                                     : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(st)[r * groups + grp[c]]);
                 total = fmaf(f.x + f.y, sc, total);
             }
 #pragma unroll
