@@ -103,7 +103,8 @@ def test_w4a16_benchmark_config_rowmajor_g128(cuda_device):
     assert _canary_ok(buf)
 
 
-@pytest.mark.parametrize("N,K,G", [(256, 2048, 128), (4096, 1024, 32), (48, 4096, 64), (1600, 2048, 2048), (16, 1024, 128)])
+@pytest.mark.parametrize("N,K,G", [(256, 2048, 128), (4096, 1024, 32), (48, 4096, 64), (1600, 2048, 2048), (16, 1024, 128),
+                                   (9600, 1024, 64), (9488, 2048, 128)])     # the last two: several tiles per CTA
 @pytest.mark.parametrize("xdt,sdt,with_bias", [(torch.bfloat16, np.float16, False), (torch.float16, np.float16, True),
                                                (torch.float32, "bf16", True)])
 def test_w4a16_one_token_rowmajor_kernel(cuda_device, N, K, G, xdt, sdt, with_bias):
