@@ -205,3 +205,23 @@ def test_attention_arguments_are_validated_on_the_host():
     assert call(**{**q, "quant_rows_per_token": 2, "head_dim": 72, "ldq": 72, "ldk": 72, "ldv": 72, "ldo": 72}) == -2
     assert lib.tpb200_attention_workspace_size(400, 762, 256, 1) >= 4 * 6 * 128 * (256 + 2) * 4
     assert lib.tpb200_attention_workspace_size(64, 300, 300, 1) == 0
+
+
+def test_bench_reference_arm_prints_the_contract_line():
+    """`bench.py --impl reference` needs no GPU: one JSON line with the own arm's metric, unit and config, the CPU
+    baseline it timed (`kind`, `cores`, `sample`) and an `e2e` that repeats the value with no copies."""
+    import json
+    import subprocess
+    import sys
+    out = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "0"],
+                         capture_output=True, text=True, timeout=600, cwd=str(ROOT))
+    assert out.returncode == 0, out.stderr[-2000:]
+    lines = [ln for ln in out.stdout.splitlines() if ln.startswith("{")]
+    assert len(lines) == 1
+    d = json.loads(lines[0])
+    assert d["impl"] == "reference" and d["metric"] == "nvfp4_gemv_hbm_gbps" and d["unit"] == "GB/s"
+    assert d["higher_is_better"] is True and d["n_gpus"] == 1 and d["value"] > 0
+    assert d["cpu_baseline"]["kind"] in ("port", "reference") and d["cpu_baseline"]["cores"] >= 1
+    assert d["cpu_baseline"]["value"] == d["value"] and d["cpu_baseline"]["sample"]
+    assert d["e2e"] == {"value": d["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    assert "workload" in d["config"]
