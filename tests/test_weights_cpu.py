@@ -81,6 +81,8 @@ def test_state_dict_to_file_to_model_is_byte_identical(tmp_path):
         assert na == nb
         if isinstance(a, TcLinear):
             assert torch.equal(a.b, b.b) and torch.equal(a.b, c.b)
+            assert a.rowmajor == b.rowmajor == c.rowmajor           # the operand form travels with the file
+            assert not a.rowmajor or (torch.equal(a.sf, b.sf) and torch.equal(a.sf, c.sf))
             assert a.g == b.g and (a.N, a.K) == (b.N, b.K)
             assert (a.bias is None) == (b.bias is None) and (a.bias is None or torch.equal(a.bias, b.bias))
             n += 1
@@ -90,6 +92,9 @@ def test_state_dict_to_file_to_model_is_byte_identical(tmp_path):
     # fused tensors: q / k / v stacked and tile-permuted, gate / up stacked, adaptive norms stacked
     assert m1.prefix[0]["qkv"].N == cfg.q_dim + 2 * cfg.head_dim and m1.prefix[0]["gate_up"].N == 2 * cfg.mlp
     assert m1.ada_dense.N == m1.n_norms * 3 * cfg.expert_width
+    # large prefix MLP matrices and the output projections behind the attention kernel: tiled images; the rest row-major
+    assert not m1.prefix[0]["gate_up"].rowmajor and not m1.prefix[0]["o"].rowmajor and not m1.expert[0]["o"].rowmajor
+    assert m1.prefix[0]["qkv"].rowmajor and m1.expert[0]["down"].rowmajor and m1.vision[0]["fc1"].rowmajor
 
 
 def test_state_dict_errors():

@@ -78,32 +78,54 @@ QuantBuf, rowop = ops.QuantBuf, ops.rowop
 
 class TcLinear:
     """One NVFP4 weight matrix prepared for the tensor-core GEMM (standard NVFP4: E4M3 scale per 16 and
-    an fp32 global scale): the tiled operand image, the global scale, an optional fp32 bias.  `raw` keeps
-    the reference-layout codes / scale bytes for dequantisation in tests."""
+    an fp32 global scale), the global scale, an optional fp32 bias, in one of the GEMM's two operand forms:
+    the tiled image (`sf is None`; 128 x 256 output tiles, one contiguous block per K stage: the form for the
+    large prefix MLP matrices, and the one the attention kernel's fused quantiser writes activations for), or
+    row-major codes [N, pitch] + swizzled scale atoms (128 x 128 tiles, a three-stage ring: ~2 us less per launch
+    on the small, latency-bound linears of the vision tower and the action expert).  The activation operand
+    (`QuantBuf`) must be in the same form.  `raw` keeps the reference-layout codes / scale bytes for
+    dequantisation in tests."""
 
-    def __init__(self, image, g, N, K, bias=None, raw=None):
-        self.b, self.g, self.N, self.K = image, float(g), int(N), int(K)
+    def __init__(self, image, g, N, K, bias=None, raw=None, sf=None):
+        self.b, self.sf, self.g, self.N, self.K = image, sf, float(g), int(N), int(K)
         self.bias = None if bias is None else bias.float().contiguous()
         if raw is not None:
             self.raw = raw
         self.ws = None            # split-K scratch, set by the owning pipeline
 
+    @property
+    def rowmajor(self):
+        return self.sf is not None
+
     @classmethod
-    def from_weight(cls, weight, bias=None, row_perm=None, keep_raw=False):
+    def from_weight(cls, weight, bias=None, row_perm=None, keep_raw=False, rowmajor=False):
         N, K = weight.shape
         packed, scales, g = quantize_nvfp4_two_level(weight, 16)
         raw = (packed.clone(), scales.clone(), g) if keep_raw else None
         if row_perm is not None:
             packed, scales = packed[row_perm], scales[row_perm]
+        if rowmajor:
+            b = torch.zeros((N, ops.packed_pitch(K)), dtype=torch.uint8, device=packed.device)
+            b[:, :K // 2] = packed
+            return cls(b, g, N, K, bias, raw, sf=ops.swizzle_scales(scales.contiguous()))
         return cls(weights.tile_weights_host(packed, scales), g, N, K, bias, raw)
 
-    def __call__(self, q, out, activation=ACT_NONE, M=None):
-        M = q.M if M is None else M
+    def _args(self, q, M):
+        if q.tiled == self.rowmajor:
+            raise TurboPiError("activation operand and weight are in different operand forms")
         p = ops._ptr
-        args = _lib.GemmArgs(a_packed=p(q.packed), a_pieces=q.pieces, a_row_scale=p(q.row_scale), b_packed=p(self.b),
-                             alpha=float(self.g), bias=p(self.bias), activation=int(activation), out=p(out),
-                             out_dtype=ops._dt(out), ldo=out.stride(0), M=M, N=self.N, K=self.K,
-                             layout=ops.OPERANDS_TILED)
+        if self.rowmajor:
+            return _lib.GemmArgs(a_packed=p(q.packed), a_pitch=q.pitch, a_sf=p(q.sf), a_pieces=q.pieces,
+                                 a_piece_rows=q.piece_rows, a_row_scale=p(q.row_scale), b_packed=p(self.b),
+                                 b_pitch=self.b.stride(0), b_sf=p(self.sf), alpha=float(self.g), M=M, N=self.N, K=self.K,
+                                 layout=ops.OPERANDS_ROWMAJOR)
+        return _lib.GemmArgs(a_packed=p(q.packed), a_pieces=q.pieces, a_row_scale=p(q.row_scale), b_packed=p(self.b),
+                             alpha=float(self.g), M=M, N=self.N, K=self.K, layout=ops.OPERANDS_TILED)
+
+    def __call__(self, q, out, activation=ACT_NONE, M=None):
+        args = self._args(q, q.M if M is None else M)
+        args.bias, args.activation = ops._ptr(self.bias), int(activation)
+        args.out, args.out_dtype, args.ldo = ops._ptr(out), ops._dt(out), out.stride(0)
         ops._gemm_ex(args, out.device, self.ws)
         return out
 
@@ -112,10 +134,10 @@ class TcLinear:
         if k_rows.shape[0] < M or v_rows.shape[0] < M or positions.numel() < M:
             raise TurboPiError("fused QKV: cache rows / positions shorter than the token count")
         p = ops._ptr
-        args = _lib.GemmArgs(a_packed=p(q.packed), a_pieces=q.pieces, a_row_scale=p(q.row_scale), b_packed=p(self.b),
-                             alpha=float(self.g), M=M, N=self.N, K=self.K, layout=ops.OPERANDS_TILED,
-                             qkv_q_out=p(q_out), qkv_ldq=q_out.stride(0), qkv_q_dim=q_dim, qkv_k_rows=p(k_rows),
-                             qkv_v_rows=p(v_rows), qkv_positions=p(positions), qkv_rope_cos=p(cos), qkv_rope_sin=p(sin))
+        args = self._args(q, M)
+        args.qkv_q_out, args.qkv_ldq, args.qkv_q_dim = p(q_out), q_out.stride(0), q_dim
+        args.qkv_k_rows, args.qkv_v_rows, args.qkv_positions = p(k_rows), p(v_rows), p(positions)
+        args.qkv_rope_cos, args.qkv_rope_sin = p(cos), p(sin)
         ops._gemm_ex(args, q_out.device, self.ws)
         return q_out
 
@@ -209,18 +231,21 @@ class Pi05:
         PG = "paligemma_with_expert.paligemma.model."
         EX = "paligemma_with_expert.gemma_expert.model."
 
-        def lin(wname, bias=True, perm=None):
-            return TcLinear.from_weight(get(wname + ".weight"), get(wname + ".bias") if bias else None, perm, kr)
+        # Operand form per linear: the tiled image for the large prefix MLP matrices and for the two output
+        # projections whose activations the attention kernel quantises itself; row-major for everything else
+        # (the vision tower, the fused QKV projections, the action expert's MLP and the small projections).
+        def lin(wname, bias=True, perm=None, rm=True):
+            return TcLinear.from_weight(get(wname + ".weight"), get(wname + ".bias") if bias else None, perm, kr, rm)
 
-        def stacked(names, bias, perm=None):
+        def stacked(names, bias, perm=None, rm=True):
             w = torch.cat([get(n + ".weight") for n in names], 0)
             b = torch.cat([get(n + ".bias") for n in names], 0) if bias else None
-            return TcLinear.from_weight(w, b, perm, kr)
+            return TcLinear.from_weight(w, b, perm, kr, rm)
 
         vw = c.vision_width
         wp = torch.zeros(vw, self.patch_k, device=self.device)
         wp[:, :3 * c.patch * c.patch] = get(V + "embeddings.patch_embedding.weight").reshape(vw, -1)   # (c, i, j)
-        self.patch_embed = TcLinear.from_weight(wp, get(V + "embeddings.patch_embedding.bias"), None, kr)
+        self.patch_embed = TcLinear.from_weight(wp, get(V + "embeddings.patch_embedding.bias"), None, kr, True)
         self.pos_emb = get(V + "embeddings.position_embedding.weight").to(bf)
         self.vision = []
         for i in range(c.vision_layers):
@@ -237,16 +262,17 @@ class Pi05:
         perm = ops.qkv_tile_permutation(c.q_dim).to(self.device)
         self.embed_tokens = get(PG + "language_model.embed_tokens.weight").to(bf)
 
-        def decoder(prefix):
+        def decoder(prefix, mlp_rm):
             a = prefix + "self_attn."
-            return dict(qkv=stacked([a + "q_proj", a + "k_proj", a + "v_proj"], False, perm), o=lin(a + "o_proj", False),
-                        gate_up=stacked([prefix + "mlp.gate_proj", prefix + "mlp.up_proj"], False),
-                        down=lin(prefix + "mlp.down_proj", False))
+            return dict(qkv=stacked([a + "q_proj", a + "k_proj", a + "v_proj"], False, perm),
+                        o=lin(a + "o_proj", False, rm=False),
+                        gate_up=stacked([prefix + "mlp.gate_proj", prefix + "mlp.up_proj"], False, rm=mlp_rm),
+                        down=lin(prefix + "mlp.down_proj", False, rm=mlp_rm))
 
         self.prefix = []
         for i in range(c.prefix_layers):
             L = f"{PG}language_model.layers.{i}."
-            d = decoder(L)
+            d = decoder(L, False)
             d["in_norm"] = get(L + "input_layernorm.weight").to(bf)
             d["post_norm"] = get(L + "post_attention_layernorm.weight").to(bf)
             self.prefix.append(d)
@@ -258,7 +284,7 @@ class Pi05:
         self.expert, dense = [], []
         for i in range(c.expert_layers):
             L = f"{EX}layers.{i}."
-            self.expert.append(decoder(L))
+            self.expert.append(decoder(L, True))
             dense += [L + "input_layernorm.dense", L + "post_attention_layernorm.dense"]
         self.ada_dense = stacked(dense + [EX + "norm.dense"], True)    # every adaptive norm's dense(cond), stacked
 
@@ -277,14 +303,19 @@ class Pi05:
             yield k, getattr(self, k)
 
     def save(self, path):
-        """Write the prepared model (tiled 4-bit operand images, bf16 tables) to a container file."""
+        """Write the prepared model (4-bit operands in the form each linear runs in, bf16 tables) to a container file."""
         tensors, linears = {}, {}
         for name, obj in self._named_parts():
             if isinstance(obj, TcLinear):
-                tensors[name + ".image"] = obj.b
+                if obj.rowmajor:
+                    tensors[name + ".codes"] = obj.b
+                    tensors[name + ".scale_atoms"] = obj.sf
+                else:
+                    tensors[name + ".image"] = obj.b
                 if obj.bias is not None:
                     tensors[name + ".bias"] = obj.bias
-                linears[name] = {"N": obj.N, "K": obj.K, "global_scale": obj.g}
+                linears[name] = {"N": obj.N, "K": obj.K, "global_scale": obj.g,
+                                 "form": "rowmajor" if obj.rowmajor else "tiled"}
             else:
                 tensors[name] = obj
         cfgd = {k: getattr(self.cfg, k) for k in self.cfg.__dataclass_fields__}
@@ -297,6 +328,9 @@ class Pi05:
         def part(name):
             if name in lins:
                 e = lins[name]
+                if e.get("form", "tiled") == "rowmajor":
+                    return TcLinear(tensors[name + ".codes"], e["global_scale"], e["N"], e["K"], tensors.get(name + ".bias"),
+                                    sf=tensors[name + ".scale_atoms"])
                 return TcLinear(tensors[name + ".image"], e["global_scale"], e["N"], e["K"], tensors.get(name + ".bias"))
             return tensors[name]
 
@@ -324,23 +358,23 @@ class Pi05:
         self.cache = torch.zeros((c.prefix_layers, 2, c.max_seq, c.head_dim), dtype=bf, device=d)
         self.b = dict(
             # vision
-            patches=torch.zeros((T, self.patch_k), dtype=bf, device=d), q_patch=QuantBuf(T, self.patch_k, P, d),
+            patches=torch.zeros((T, self.patch_k), dtype=bf, device=d), q_patch=QuantBuf(T, self.patch_k, P, d, tiled=False),
             vh=torch.empty((T, vw), dtype=bf, device=d), vy=torch.empty((T, vw), dtype=bf, device=d),
-            q_v=QuantBuf(T, vw, P, d), v_qkv=torch.empty((T, 3 * vw), dtype=bf, device=d),
+            q_v=QuantBuf(T, vw, P, d, tiled=False), v_qkv=torch.empty((T, 3 * vw), dtype=bf, device=d),
             v_attn=torch.empty((T, vw), dtype=bf, device=d),
-            v_fc1=torch.empty((T, c.vision_mlp), dtype=bf, device=d), q_vmlp=QuantBuf(T, c.vision_mlp, P, d),
+            v_fc1=torch.empty((T, c.vision_mlp), dtype=bf, device=d), q_vmlp=QuantBuf(T, c.vision_mlp, P, d, tiled=False),
             # prefix
             ph=torch.empty((S, c.width), dtype=bf, device=d), py=torch.empty((S, c.width), dtype=bf, device=d),
-            q_p=QuantBuf(S, c.width, P, d), p_q=torch.empty((S, c.q_dim), dtype=bf, device=d),
+            q_p=QuantBuf(S, c.width, P, d), q_pqkv=QuantBuf(S, c.width, P, d, tiled=False), p_q=torch.empty((S, c.q_dim), dtype=bf, device=d),
             q_pattn=QuantBuf(S, c.q_dim, P, d), p_gu=torch.empty((S, 2 * c.mlp), dtype=bf, device=d),
             q_pmlp=QuantBuf(S, c.mlp, P, d), pos_prefix=torch.arange(S, dtype=torch.int32, device=d),
             # expert
             x_t=torch.zeros((A, c.action_dim), dtype=torch.float32, device=d),
-            x_bf=torch.zeros((A, c.action_dim), dtype=bf, device=d), q_act=QuantBuf(A, c.action_dim, P, d),
+            x_bf=torch.zeros((A, c.action_dim), dtype=bf, device=d), q_act=QuantBuf(A, c.action_dim, P, d, tiled=False),
             eh=torch.empty((A, ew), dtype=bf, device=d), ey=torch.empty((A, ew), dtype=bf, device=d),
-            q_e=QuantBuf(A, ew, P, d), e_q=torch.empty((A, c.q_dim), dtype=bf, device=d),
+            q_e=QuantBuf(A, ew, P, d, tiled=False), e_q=torch.empty((A, c.q_dim), dtype=bf, device=d),
             q_eattn=QuantBuf(A, c.q_dim, P, d), e_gu=torch.empty((A, 2 * c.expert_mlp), dtype=bf, device=d),
-            q_emlp=QuantBuf(A, c.expert_mlp, P, d), v_out=torch.empty((A, c.action_dim), dtype=torch.float32, device=d),
+            q_emlp=QuantBuf(A, c.expert_mlp, P, d, tiled=False), v_out=torch.empty((A, c.action_dim), dtype=torch.float32, device=d),
             pos_suffix=torch.arange(S, S + A, dtype=torch.int32, device=d),
         )
         for _, obj in self._named_parts():
@@ -442,12 +476,12 @@ class Pi05:
         first = True
         for l, L in enumerate(self.prefix):
             if first:
-                rowop(_lib.ROW_RMSNORM, b["ph"], c.width, b["q_p"], w0=L["in_norm"], eps=c.eps)
+                rowop(_lib.ROW_RMSNORM, b["ph"], c.width, b["q_pqkv"], w0=L["in_norm"], eps=c.eps)
                 first = False
             else:
-                rowop(_lib.ROW_RMSNORM, b["py"], c.width, b["q_p"], res_in=b["ph"], h_out=b["ph"], w0=L["in_norm"],
+                rowop(_lib.ROW_RMSNORM, b["py"], c.width, b["q_pqkv"], res_in=b["ph"], h_out=b["ph"], w0=L["in_norm"],
                       eps=c.eps)
-            L["qkv"].qkv(b["q_p"], b["p_q"], self.cache[l, 0], self.cache[l, 1], b["pos_prefix"], self.cos, self.sin,
+            L["qkv"].qkv(b["q_pqkv"], b["p_q"], self.cache[l, 0], self.cache[l, 1], b["pos_prefix"], self.cos, self.sin,
                          c.q_dim)
             self._attention_to_operand(b["p_q"], self.cache[l, 0, :S], self.cache[l, 1, :S], b["q_pattn"])
             L["o"](b["q_pattn"], b["py"])
@@ -469,7 +503,7 @@ class Pi05:
             ts = torch.tensor([1.0 + i * dt for i in range(num_steps)], dtype=torch.float32)
             self._time_emb[num_steps] = sinusoidal_time_embedding(ts, ew).to(torch.bfloat16).to(d)
         emb = self._time_emb[num_steps]
-        qb = QuantBuf(num_steps, ew, c.pieces, d)
+        qb = QuantBuf(num_steps, ew, c.pieces, d, tiled=False)
         t1 = torch.empty((num_steps, ew), dtype=torch.bfloat16, device=d)
         rowop(_lib.ROW_NONE, emb, ew, qb)
         self.time_mlp_in(qb, t1, ACT_SILU)
