@@ -329,8 +329,13 @@ typedef struct {
      * multiple of 256, <= 8192) is also written as a row of the tiled A image of tpb200_nvfp4_gemm_ex
      * (quant_pieces residual pieces, quant_row_scale[token] = the row multiplier), exactly as
      * tpb200_row_transform_quantize in plain mode would produce from `out`; `out` may then be NULL.  Needs the
-     * workspace whatever the key count. */
+     * workspace whatever the key count.
+     * quant_sf != NULL selects the GEMM's row-major operand form instead: quant_image = the codes
+     * [quant_pieces * quant_piece_rows, quant_pitch] bytes (piece p of token t at row p * quant_piece_rows + t,
+     * quant_piece_rows a multiple of 128, quant_pitch >= K / 2 and a multiple of 16), quant_sf = their swizzled
+     * scale atoms. */
     void* quant_image; float* quant_row_scale; int quant_pieces; int quant_rows_per_token;
+    void* quant_sf; int quant_pitch; int quant_piece_rows;
 } tpb200_attention_args;
 size_t tpb200_attention_workspace_size(int n_rows, int n_keys, int head_dim, int groups);
 int tpb200_attention(const tpb200_attention_args* args, tpb200_stream_t stream);

@@ -108,10 +108,11 @@ def test_other_head_dims_and_shared_keys(cuda_device, D, S):
     assert cosine(got.numpy(), ref.numpy()) >= 0.9999
 
 
+@pytest.mark.parametrize("tiled", [True, False])
 @pytest.mark.parametrize("L,S,heads", [(50, 762, 8), (712, 712, 8), (130, 200, 8), (9, 300, 2)])
-def test_fused_operand_output_equals_attention_then_row_kernel(cuda_device, L, S, heads):
-    """attention(..., quant=) writes the next GEMM's operand itself: the image, scales and row multipliers are
-    byte for byte what attention followed by the row kernel's plain mode produces."""
+def test_fused_operand_output_equals_attention_then_row_kernel(cuda_device, L, S, heads, tiled):
+    """attention(..., quant=) writes the next GEMM's operand itself, in either operand form: the codes, scales and
+    row multipliers are byte for byte what attention followed by the row kernel's plain mode produces."""
     from turbopi_b200 import _lib, ops
     g = torch.Generator().manual_seed(L + S)
     D = 256
@@ -123,18 +124,19 @@ def test_fused_operand_output_equals_attention_then_row_kernel(cuda_device, L, S
     bias = torch.where(valid, 0.0, opi.MASKED).to(BF).to(cuda_device)
     out = torch.empty_like(q)
     ops.attention(q.view(L * heads, D), k, v, out.view(L * heads, D), D ** -0.5, bias)
-    two_step = ops.QuantBuf(L, heads * D, 3, cuda_device)
+    two_step = ops.QuantBuf(L, heads * D, 3, cuda_device, tiled=tiled)
     ops.rowop(_lib.ROW_NONE, out, heads * D, two_step)
-    fused = ops.QuantBuf(L, heads * D, 3, cuda_device)
+    fused = ops.QuantBuf(L, heads * D, 3, cuda_device, tiled=tiled)
     out2 = torch.empty_like(q)
     ops.attention(q.view(L * heads, D), k, v, out2.view(L * heads, D), D ** -0.5, bias, quant=fused, rows_per_token=heads)
-    only = ops.QuantBuf(L, heads * D, 3, cuda_device)
+    only = ops.QuantBuf(L, heads * D, 3, cuda_device, tiled=tiled)
     ops.attention(q.view(L * heads, D), k, v, None, D ** -0.5, bias, quant=only, rows_per_token=heads)
     torch.cuda.synchronize()
     assert _lib.load().tpb200_device_error(0) == 0
     assert torch.equal(out, out2)
     for got in (fused, only):
         assert torch.equal(got.packed, two_step.packed)
+        assert tiled or torch.equal(got.sf, two_step.sf)
         assert torch.equal(got.row_scale, two_step.row_scale)
 
 

@@ -92,9 +92,10 @@ def test_state_dict_to_file_to_model_is_byte_identical(tmp_path):
     # fused tensors: q / k / v stacked and tile-permuted, gate / up stacked, adaptive norms stacked
     assert m1.prefix[0]["qkv"].N == cfg.q_dim + 2 * cfg.head_dim and m1.prefix[0]["gate_up"].N == 2 * cfg.mlp
     assert m1.ada_dense.N == m1.n_norms * 3 * cfg.expert_width
-    # large prefix MLP matrices and the output projections behind the attention kernel: tiled images; the rest row-major
-    assert not m1.prefix[0]["gate_up"].rowmajor and not m1.prefix[0]["o"].rowmajor and not m1.expert[0]["o"].rowmajor
-    assert m1.prefix[0]["qkv"].rowmajor and m1.expert[0]["down"].rowmajor and m1.vision[0]["fc1"].rowmajor
+    # the large prefix MLP matrices are tiled images, the rest row-major
+    assert not m1.prefix[0]["gate_up"].rowmajor and not m1.prefix[0]["down"].rowmajor
+    assert m1.prefix[0]["qkv"].rowmajor and m1.prefix[0]["o"].rowmajor and m1.expert[0]["down"].rowmajor
+    assert m1.expert[0]["o"].rowmajor and m1.vision[0]["fc1"].rowmajor
 
 
 def test_state_dict_errors():

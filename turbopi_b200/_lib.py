@@ -67,7 +67,8 @@ class AttentionArgs(ctypes.Structure):
                 ("v_stride", ctypes.c_longlong * 2), ("o_stride", ctypes.c_longlong * 2),
                 ("scale", c_float), ("workspace", c_void_p), ("workspace_bytes", c_size_t), ("flags", c_int),
                 ("quant_image", c_void_p), ("quant_row_scale", c_void_p), ("quant_pieces", c_int),
-                ("quant_rows_per_token", c_int)]
+                ("quant_rows_per_token", c_int),
+                ("quant_sf", c_void_p), ("quant_pitch", c_int), ("quant_piece_rows", c_int)]
 
 
 class ActTc(ctypes.Structure):

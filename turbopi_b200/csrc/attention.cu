@@ -76,6 +76,8 @@ struct AttnParams {
     float* qa_row_scale;
     int qa_pieces;
     int qa_rows_per_token;
+    uint8_t* qa_sf;          // not null: the row-major operand form (codes [pieces * piece_rows, pitch] + scale atoms)
+    int qa_pitch, qa_piece_rows;
 };
 
 struct AttnControl {
@@ -502,6 +504,16 @@ __global__ void __launch_bounds__(1024) attention_combine_quant_kernel(const __g
     for (int p = 0; p < P.qa_pieces; ++p) {
         uint32_t word;
         const uint8_t code = quantize_half8_piece(r, word);
+        if (P.qa_sf != nullptr) {
+            // row-major form: piece p of the token is row p * piece_rows + token; atoms of 128 rows x 4 blocks
+            const int prow = p * P.qa_piece_rows + token;
+            *reinterpret_cast<uint32_t*>(P.qa_image + static_cast<size_t>(prow) * P.qa_pitch + kb * 8 + hb * 4) = word;
+            if (hb == 0) {
+                P.qa_sf[(static_cast<size_t>(prow >> 7) * (kb_blocks * 4) + (kb >> 2)) * 512 + (prow & 31) * 16 +
+                        ((prow >> 5) & 3) * 4 + (kb & 3)] = code;
+            }
+            continue;
+        }
         uint8_t* code_dst = blk + p * 16384 + rr * 128 + (((jj >> 1) ^ (rr & 7)) << 4) + (jj & 1) * 8 + hb * 4;
         *reinterpret_cast<uint32_t*>(code_dst) = word;
         if (hb == 0) blk[P.qa_pieces * 16384 + p * 2048 + (jj >> 2) * 512 + (rr & 31) * 16 + (rr >> 5) * 4 + (jj & 3)] = code;
@@ -620,6 +632,11 @@ extern "C" int tpb200_attention(const tpb200_attention_args* a, tpb200_stream_t 
         const long long K = static_cast<long long>(a->quant_rows_per_token) * a->head_dim;
         TPB_REQUIRE(K % 256 == 0 && K / 8 <= 1024, TPB200_ERR_SHAPE);
         TPB_REQUIRE(tpb_aligned16(a->quant_image), TPB200_ERR_ALIGN);
+        if (a->quant_sf != nullptr) {
+            TPB_REQUIRE(a->quant_pitch >= K / 2 && a->quant_pitch % 16 == 0 && tpb_aligned16(a->quant_sf), TPB200_ERR_ALIGN);
+            TPB_REQUIRE(a->quant_piece_rows % 128 == 0 && a->quant_piece_rows >= a->n_rows / a->quant_rows_per_token,
+                        TPB200_ERR_SHAPE);
+        }
     }
     const size_t need = (d.key_tiles > 1 || quant) ? (d.part_o_floats + d.part_ml_floats) * sizeof(float) : 0;
     if (need > 0) {
@@ -657,6 +674,9 @@ extern "C" int tpb200_attention(const tpb200_attention_args* a, tpb200_stream_t 
     P.qa_row_scale = a->quant_row_scale;
     P.qa_pieces = a->quant_pieces;
     P.qa_rows_per_token = a->quant_rows_per_token;
+    P.qa_sf = static_cast<uint8_t*>(a->quant_sf);
+    P.qa_pitch = a->quant_pitch;
+    P.qa_piece_rows = a->quant_piece_rows;
 
     const int nchunk = d.dpad / 64;
     const size_t smem = static_cast<size_t>(std::max(nchunk, 4) + 2 * nchunk) * tpb::kChunkBytes + sizeof(tpb::AttnControl) + 1024;

@@ -569,8 +569,8 @@ def attention(q, k, v, out, scale, key_bias=None, workspace=None, quant=None, ro
     if key_bias is not None and (key_bias.dtype != torch.bfloat16 or key_bias.numel() < S or not key_bias.is_contiguous()):
         raise TurboPiError("attention: key_bias must be a contiguous bf16 vector with one entry per key")
     if quant is not None:
-        if A * B != 1 or R % rows_per_token or not quant.tiled or quant.M != R // rows_per_token or quant.K != rows_per_token * D:
-            raise TurboPiError("attention: quant must be a tiled QuantBuf of [rows / rows_per_token, rows_per_token * D]")
+        if A * B != 1 or R % rows_per_token or quant.M != R // rows_per_token or quant.K != rows_per_token * D:
+            raise TurboPiError("attention: quant must be a QuantBuf of [rows / rows_per_token, rows_per_token * D]")
     if workspace is None:
         workspace = attention_workspace(R, S, D, A * B, q.device)
     two = ctypes.c_longlong * 2
@@ -583,7 +583,10 @@ def attention(q, k, v, out, scale, key_bias=None, workspace=None, quant=None, ro
                               workspace_bytes=workspace.numel(), flags=_launch_flags,
                               quant_image=_ptr(quant.packed) if quant is not None else None,
                               quant_row_scale=_ptr(quant.row_scale) if quant is not None else None,
-                              quant_pieces=quant.pieces if quant is not None else 0, quant_rows_per_token=rows_per_token)
+                              quant_pieces=quant.pieces if quant is not None else 0, quant_rows_per_token=rows_per_token,
+                              quant_sf=_ptr(quant.sf) if quant is not None and not quant.tiled else None,
+                              quant_pitch=quant.pitch if quant is not None else 0,
+                              quant_piece_rows=quant.piece_rows if quant is not None else 0)
     with torch.cuda.device(q.device):
         st = _lib.load().tpb200_attention(ctypes.byref(args), torch.cuda.current_stream(q.device).cuda_stream)
     _lib.check(st, "tpb200_attention")

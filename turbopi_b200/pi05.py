@@ -80,7 +80,7 @@ class TcLinear:
     """One NVFP4 weight matrix prepared for the tensor-core GEMM (standard NVFP4: E4M3 scale per 16 and
     an fp32 global scale), the global scale, an optional fp32 bias, in one of the GEMM's two operand forms:
     the tiled image (`sf is None`; 128 x 256 output tiles, one contiguous block per K stage: the form for the
-    large prefix MLP matrices, and the one the attention kernel's fused quantiser writes activations for), or
+    large prefix MLP matrices), or
     row-major codes [N, pitch] + swizzled scale atoms (128 x 128 tiles, a three-stage ring: ~2 us less per launch
     on the small, latency-bound linears of the vision tower and the action expert).  The activation operand
     (`QuantBuf`) must be in the same form.  `raw` keeps the reference-layout codes / scale bytes for
@@ -231,9 +231,8 @@ class Pi05:
         PG = "paligemma_with_expert.paligemma.model."
         EX = "paligemma_with_expert.gemma_expert.model."
 
-        # Operand form per linear: the tiled image for the large prefix MLP matrices and for the two output
-        # projections whose activations the attention kernel quantises itself; row-major for everything else
-        # (the vision tower, the fused QKV projections, the action expert's MLP and the small projections).
+        # Operand form per linear: the tiled image for the large prefix MLP matrices (gate_up, down), row-major
+        # for everything else (the vision tower, the attention projections, the action expert, the small projections).
         def lin(wname, bias=True, perm=None, rm=True):
             return TcLinear.from_weight(get(wname + ".weight"), get(wname + ".bias") if bias else None, perm, kr, rm)
 
@@ -265,7 +264,7 @@ class Pi05:
         def decoder(prefix, mlp_rm):
             a = prefix + "self_attn."
             return dict(qkv=stacked([a + "q_proj", a + "k_proj", a + "v_proj"], False, perm),
-                        o=lin(a + "o_proj", False, rm=False),
+                        o=lin(a + "o_proj", False),
                         gate_up=stacked([prefix + "mlp.gate_proj", prefix + "mlp.up_proj"], False, rm=mlp_rm),
                         down=lin(prefix + "mlp.down_proj", False, rm=mlp_rm))
 
@@ -366,14 +365,14 @@ class Pi05:
             # prefix
             ph=torch.empty((S, c.width), dtype=bf, device=d), py=torch.empty((S, c.width), dtype=bf, device=d),
             q_p=QuantBuf(S, c.width, P, d), q_pqkv=QuantBuf(S, c.width, P, d, tiled=False), p_q=torch.empty((S, c.q_dim), dtype=bf, device=d),
-            q_pattn=QuantBuf(S, c.q_dim, P, d), p_gu=torch.empty((S, 2 * c.mlp), dtype=bf, device=d),
+            q_pattn=QuantBuf(S, c.q_dim, P, d, tiled=False), p_gu=torch.empty((S, 2 * c.mlp), dtype=bf, device=d),
             q_pmlp=QuantBuf(S, c.mlp, P, d), pos_prefix=torch.arange(S, dtype=torch.int32, device=d),
             # expert
             x_t=torch.zeros((A, c.action_dim), dtype=torch.float32, device=d),
             x_bf=torch.zeros((A, c.action_dim), dtype=bf, device=d), q_act=QuantBuf(A, c.action_dim, P, d, tiled=False),
             eh=torch.empty((A, ew), dtype=bf, device=d), ey=torch.empty((A, ew), dtype=bf, device=d),
             q_e=QuantBuf(A, ew, P, d, tiled=False), e_q=torch.empty((A, c.q_dim), dtype=bf, device=d),
-            q_eattn=QuantBuf(A, c.q_dim, P, d), e_gu=torch.empty((A, 2 * c.expert_mlp), dtype=bf, device=d),
+            q_eattn=QuantBuf(A, c.q_dim, P, d, tiled=False), e_gu=torch.empty((A, 2 * c.expert_mlp), dtype=bf, device=d),
             q_emlp=QuantBuf(A, c.expert_mlp, P, d, tiled=False), v_out=torch.empty((A, c.action_dim), dtype=torch.float32, device=d),
             pos_suffix=torch.arange(S, S + A, dtype=torch.int32, device=d),
         )
