@@ -182,6 +182,7 @@ class Pi05:
         self._graph = None
         self._graph_steps = None
         self._time_emb = {}
+        self._mod = {}            # per step count: the adaptive norms' modulation table
         self.set_valid()
 
     @classmethod
@@ -544,8 +545,20 @@ class Pi05:
         self.action_out(b["q_e"], b["v_out"])
         b["x_t"].add_(b["v_out"], alpha=dt)
 
+    def _modulation(self, num_steps):
+        """The adaptive norms' (scale, shift, gate) for every step of an `num_steps` schedule.  They depend on
+        the schedule and the weights only, not on the observation (the reference precomputes the per-step
+        conditioning vectors for its graphs too: pi0_pytorch.py:770-839), so they are computed once per schedule -- by
+        the warm-up pass that precedes a capture -- and stay out of the per-inference graph."""
+        mod = self._mod.get(num_steps)
+        if mod is None:
+            if torch.cuda.is_current_stream_capturing():
+                raise TurboPiError("the modulation table of a new schedule must be built before the capture")
+            mod = self._mod[num_steps] = self._ada_modulation(num_steps)
+        return mod
+
     def denoise_loop(self, num_steps):
-        mod = self._ada_modulation(num_steps)
+        mod = self._modulation(num_steps)
         self.b["x_t"].copy_(self.noise)
         dt = -1.0 / num_steps
         for i in range(num_steps):
