@@ -14,7 +14,7 @@ from typing import Optional, Tuple
 import torch
 import torch.nn as nn
 
-from . import ops
+from . import _lib, ops
 from ._lib import ACTIVATIONS
 
 BLOCK_SIZE = 32
@@ -80,6 +80,33 @@ def quantize_nvfp4_two_level(weight: torch.Tensor, block_size: int = 16):
     return packed, s8.view(torch.uint8), g
 
 
+def _operand_buffer(module, T, K, device):
+    """The tiled A operand of `module`'s GEMM for T tokens, kept on the module: allocating (and zero-filling) 3 x T x K / 2
+    bytes per call costs more than the quantiser that fills them.  Padding rows and columns are never written, so
+    they stay zero from one call to the next.  (Calls on one module are expected in stream order, as with any
+    module that owns scratch.)"""
+    cache = module.__dict__.setdefault("_operands", {})
+    key = (int(T), int(K), str(device))
+    q = cache.get(key)
+    if q is None:
+        if len(cache) >= 4:
+            cache.clear()
+        q = cache[key] = ops.QuantBuf(T, K, 3, device)
+    return q
+
+
+def _split_k_scratch(module, T, N, K, device):
+    """Zeroed split-K scratch of `module`'s GEMM, as large as the launch planner wants for T tokens (a scratch
+    that is too small makes the planner cut K less and leaves SMs idle: 712 x 2048 x 16384 runs on 48 CTAs
+    without it).  Grown when a larger token count arrives; owned by the module, so calls on different modules
+    never share counters."""
+    need = ops.nvfp4_gemm_workspace_size(T, N, K, 3, ops.OPERANDS_TILED)
+    ws = module.__dict__.get("_gemm_ws")
+    if ws is None or ws.numel() < need or ws.device != torch.device(device):
+        ws = module.__dict__["_gemm_ws"] = ops.gemm_workspace(device, max(int(need), 1 << 20))
+    return ws
+
+
 class NVFP4PackedLinear(nn.Module):
     """Linear layer over packed e2m1 weights with fused bias + GELU-tanh / SiLU.
 
@@ -141,7 +168,7 @@ class NVFP4PackedLinear(nn.Module):
                 and self.weight_packed.is_cuda and self.in_features % 16 == 0)
 
     def _tc_state(self):
-        """(tiled weight image, GEMV scratch, GEMM scratch), built on first use and whenever the packed
+        """(tiled weight image, GEMV scratch), built on first use and whenever the packed
         weights were replaced (load_state_dict, .to(device))."""
         key = (self.weight_packed.data_ptr(), self.weight_scales.data_ptr(), str(self.weight_packed.device))
         st = getattr(self, "_tc", None)
@@ -151,9 +178,9 @@ class NVFP4PackedLinear(nn.Module):
             b = torch.zeros((N, ops.packed_pitch(K)), dtype=torch.uint8, device=dev)
             b[:, :K // 2] = self.weight_packed
             image = ops.tile_weights(b, ops.swizzle_scales(self.weight_scales.contiguous()), N, K)
-            st = (key, image, ops.tc_gemv_workspace(N, K, dev), ops.gemm_workspace(dev, 8 << 20))
+            st = (key, image, ops.tc_gemv_workspace(N, K, dev))
             self._tc = st
-        return st[1], st[2], st[3]
+        return st[1], st[2]
 
     def _forward_tensor_cores(self, x2, act, bias):
         T = x2.shape[0]
@@ -163,12 +190,21 @@ class NVFP4PackedLinear(nn.Module):
             # split-K hand-over at the end (4.5-12 us against 9-27 us for the tensor-core kernel, whose
             # ground is many matrices per launch)
             return ops.nvfp4_gemv_out(x2, self.weight_packed, self.weight_scales, out, bias, act, 16, self.global_scale)
-        image, gemv_ws, gemm_ws = self._tc_state()
+        image, gemv_ws = self._tc_state()
         if T <= 16:
             return ops.tc_gemv(x2, image, self.out_features, out, self.global_scale, bias, act, 3, gemv_ws)
         xb = x2 if x2.dtype == torch.bfloat16 else x2.to(torch.bfloat16)
-        return ops.nvfp4_gemm_w4a16_tiled(xb, image, self.out_features, alpha=self.global_scale, bias=bias, activation=act,
-                                          pieces=3, out=out, workspace=gemm_ws)
+        q = _operand_buffer(self, T, self.in_features, x2.device)
+        # the quantiser and the GEMM are chained by programmatic dependent launch: the weights are static, so
+        # the GEMM may fetch them while the quantiser still runs
+        with ops.launch_flags(ops.FLAG_PDL):
+            ops.rowop(_lib.ROW_NONE, xb, self.in_features, q)
+            args = _lib.GemmArgs(a_packed=ops._ptr(q.packed), a_pieces=3, a_row_scale=ops._ptr(q.row_scale),
+                                 b_packed=ops._ptr(image), alpha=float(self.global_scale), bias=ops._ptr(bias),
+                                 activation=int(act), out=ops._ptr(out), out_dtype=ops._dt(out), ldo=out.stride(0), M=T,
+                                 N=self.out_features, K=self.in_features, layout=ops.OPERANDS_TILED)
+            ops._gemm_ex(args, x2.device, _split_k_scratch(self, T, self.out_features, self.in_features, x2.device))
+        return out
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         batch_shape = x.shape[:-1]
@@ -250,8 +286,7 @@ class NVFP4PackedMLP(nn.Module):
                 b = torch.zeros((N, ops.packed_pitch(K)), dtype=torch.uint8, device=dev)
                 b[:, :K // 2] = torch.cat([g.weight_packed, u.weight_packed], 0)
                 sc = torch.cat([g.weight_scales, u.weight_scales], 0).contiguous()
-                st = (key, ops.tile_weights(b, ops.swizzle_scales(sc), N, K), ops.tc_gemv_workspace(N, K, dev),
-                      ops.gemm_workspace(dev, 8 << 20))
+                st = (key, ops.tile_weights(b, ops.swizzle_scales(sc), N, K), ops.tc_gemv_workspace(N, K, dev))
             self._gu = st
         return st
 
@@ -263,7 +298,7 @@ class NVFP4PackedMLP(nn.Module):
         if st is None or st[1] is None:
             return self.down_proj(self.gate_proj(x) * self.up_proj(x))
         from . import _lib
-        _, gu_image, gu_gemv_ws, gu_gemm_ws = st
+        _, gu_image, gu_gemv_ws = st
         batch_shape = x.shape[:-1]
         x2 = x.reshape(-1, self.hidden_size).contiguous()
         if x2.dtype != torch.bfloat16:
@@ -271,7 +306,7 @@ class NVFP4PackedMLP(nn.Module):
         T, I = x2.shape[0], self.intermediate_size
         gu = torch.empty((T, 2 * I), dtype=torch.bfloat16, device=x2.device)
         mode = _lib.ROW_GELU_MUL if g.activation == "gelu" else _lib.ROW_SILU_MUL
-        d_image, d_gemv_ws, d_gemm_ws = d._tc_state()
+        d_image, d_gemv_ws = d._tc_state()
         d_bias = None if d.bias is None else d.bias.detach().float().contiguous()
         out = torch.empty((T, self.hidden_size), dtype=torch.bfloat16, device=x2.device)
         if T <= 16:
@@ -283,14 +318,21 @@ class NVFP4PackedMLP(nn.Module):
             else:
                 ops.tc_gemv(h, d_image, self.hidden_size, out, d.global_scale, d_bias, 0, 3, d_gemv_ws)
         else:
-            ops.nvfp4_gemm_w4a16_tiled(x2, gu_image, 2 * I, alpha=g.global_scale, pieces=3, out=gu, workspace=gu_gemm_ws)
-            q = ops.QuantBuf(T, I, 3, x2.device)
-            ops.rowop(mode, gu, I, q, M=T)
-            args = _lib.GemmArgs(a_packed=ops._ptr(q.packed), a_pieces=3, a_row_scale=ops._ptr(q.row_scale),
-                                 b_packed=ops._ptr(d_image), alpha=float(d.global_scale), bias=ops._ptr(d_bias),
-                                 out=ops._ptr(out), out_dtype=ops._dt(out), ldo=out.stride(0), M=T, N=self.hidden_size, K=I,
-                                 layout=ops.OPERANDS_TILED)
-            ops._gemm_ex(args, x2.device, d_gemm_ws)
+            qx = _operand_buffer(g, T, self.hidden_size, x2.device)
+            q = _operand_buffer(d, T, I, x2.device)
+            with ops.launch_flags(ops.FLAG_PDL):     # four launches chained by programmatic dependent launch
+                ops.rowop(_lib.ROW_NONE, x2, self.hidden_size, qx)
+                args = _lib.GemmArgs(a_packed=ops._ptr(qx.packed), a_pieces=3, a_row_scale=ops._ptr(qx.row_scale),
+                                     b_packed=ops._ptr(gu_image), alpha=float(g.global_scale), out=ops._ptr(gu),
+                                     out_dtype=ops._dt(gu), ldo=gu.stride(0), M=T, N=2 * I, K=self.hidden_size,
+                                     layout=ops.OPERANDS_TILED)
+                ops._gemm_ex(args, x2.device, _split_k_scratch(g, T, 2 * I, self.hidden_size, x2.device))
+                ops.rowop(mode, gu, I, q, M=T)
+                args = _lib.GemmArgs(a_packed=ops._ptr(q.packed), a_pieces=3, a_row_scale=ops._ptr(q.row_scale),
+                                     b_packed=ops._ptr(d_image), alpha=float(d.global_scale), bias=ops._ptr(d_bias),
+                                     out=ops._ptr(out), out_dtype=ops._dt(out), ldo=out.stride(0), M=T, N=self.hidden_size,
+                                     K=I, layout=ops.OPERANDS_TILED)
+                ops._gemm_ex(args, x2.device, _split_k_scratch(d, T, self.hidden_size, I, x2.device))
         return out.reshape(*batch_shape, self.hidden_size).to(x.dtype)
 
 
