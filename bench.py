@@ -492,9 +492,11 @@ def run_extras(device, sets, x):
         pk, sf = ops.nvfp4_quantize_act(xq)
         t = time_launches(lambda i: ops.nvfp4_quantize_act(xq, pk, sf), 16)
         ex[f"nvfp4_quantize_act_{M}x{K}"] = {"us": t * 1e6, "gbps": (M * K * 2 + M * K // 2 + M * K // 16) / t / 1e9}
-    # (g) the model's linears as they run in the pipeline: bf16 activations -> 3 residual e2m1 pieces in the
-    # tiled A image (row kernel), NVFP4 weights as tiled images, 128 x 256 output tiles (benchmark config 4
-    # with weight-only semantics; `tflops` counts the useful 2 M N K once, not the 3 pieces)
+    # (g) the model's linears as they run in the pipeline: bf16 activations -> 3 residual e2m1 pieces (row
+    # kernel), NVFP4 weights; the two large prefix MLP matrices on the tiled images (128 x 256 output tiles), the
+    # other shapes in the row-major operand form (128 x 128 tiles), chained by programmatic dependent launch as
+    # in the pipeline (benchmark config 4 with weight-only semantics; `tflops` counts the useful 2 M N K once,
+    # not the 3 pieces; `tiled_gemm_us`: the same shape on the tiled images)
     from turbopi_b200 import _lib as tlib
     from turbopi_b200.pi05 import TcLinear
     gemm_ws = ops.gemm_workspace(device)
@@ -502,23 +504,34 @@ def run_extras(device, sets, x):
                             (712, 2560, 2048, "gemma2b_qkv_M712"), (512, 4304, 1152, "siglip_fc1_M512"),
                             (512, 1152, 4304, "siglip_fc2_M512"), (50, 8192, 1024, "expert_gate_up_M50"),
                             (50, 1024, 4096, "expert_down_M50")):
-        q = ops.QuantBuf(M, K, 3, device)
+        rowmajor = N * K < (1 << 25)            # the pipeline's rule: everything but the prefix gate_up / down
         xq = torch.randn(M, K, device=device).to(torch.bfloat16)
-        lins = [TcLinear.from_weight(torch.randn(N, K, device=device) * 0.02) for _ in range(2)]
-        for l_ in lins:
-            l_.ws = gemm_ws
         o = torch.empty((M, N), dtype=torch.bfloat16, device=device)
-        ops.rowop(tlib.ROW_NONE, xq, K, q)
-        t = time_launches(lambda i: lins[i % 2](q, o), 16)
-        tq = time_launches(lambda i: ops.rowop(tlib.ROW_NONE, xq, K, q), 16)
+        weights_ = [torch.randn(N, K, device=device) * 0.02 for _ in range(2)]
+        times = {}
+        for form in ((False, True) if rowmajor else (False,)):
+            q = ops.QuantBuf(M, K, 3, device, tiled=not form)
+            lins = [TcLinear.from_weight(w_, rowmajor=form) for w_ in weights_]
+            for l_ in lins:
+                l_.ws = gemm_ws
+            ops.rowop(tlib.ROW_NONE, xq, K, q)
+            with ops.launch_flags(ops.FLAG_PDL):
+                times[form] = (time_launches(lambda i: lins[i % 2](q, o), 16),
+                               time_launches(lambda i: ops.rowop(tlib.ROW_NONE, xq, K, q), 16))
+            del lins
+        del weights_
+        t, tq = times[rowmajor]
         # the library comparator on the same shape: torch F.linear in bf16 (cuBLAS), weights rotating too
         wb = [(torch.randn(N, K, device=device) * 0.02).to(torch.bfloat16) for _ in range(2)]
         tb = time_launches(lambda i: torch.nn.functional.linear(xq, wb[i % 2]), 16)
         ex[f"w4a16_tc_linear_{name}"] = {"gemm_us": t * 1e6, "quantise_us": tq * 1e6,
+                                         "form": "row-major operands, 128x128 tiles" if rowmajor else "tiled images, 128x256 tiles",
                                          "tflops": 2.0 * M * N * K / t / 1e12,
                                          "tensor_tflops": 3 * 2.0 * M * N * K / t / 1e12,
                                          "cublas_bf16_us": tb * 1e6, "cublas_bf16_tflops": 2.0 * M * N * K / tb / 1e12}
-        del lins, wb
+        if rowmajor:
+            ex[f"w4a16_tc_linear_{name}"]["tiled_gemm_us"] = times[False][0] * 1e6
+        del wb
     # (e2) the same NVFP4 x NVFP4 products on the tiled operand images (one e2m1 activation piece, 128 x 256 tiles):
     # the form the prefix would run with e2m1 activations
     for (M, N, K, name) in ((712, 16384, 2048, "gemma2b_gateup_M712"), (712, 2048, 16384, "gemma2b_down_M712")):
