@@ -702,9 +702,9 @@ def run_case(args):
     M, N, K = args.M, args.N, args.K
     if args.case == "gemm":            # weight-only linear: activation-piece quantiser + tiled tcgen05 GEMM
         x = torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16)
-        lin = TcLinear.from_weight(torch.randn(N, K, device=dev, generator=g) * 0.02)
+        lin = TcLinear.from_weight(torch.randn(N, K, device=dev, generator=g) * 0.02, rowmajor=args.rowmajor)
         lin.ws = ops.gemm_workspace(dev)
-        q = ops.QuantBuf(M, K, args.pieces, dev)
+        q = ops.QuantBuf(M, K, args.pieces, dev, tiled=not args.rowmajor)
         out = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
 
         def step():
@@ -878,6 +878,8 @@ def main():
     ap.add_argument("--N", type=int, default=32768)
     ap.add_argument("--K", type=int, default=2048)
     ap.add_argument("--pieces", type=int, default=3)
+    ap.add_argument("--rowmajor", action="store_true",
+                    help="--case gemm: the row-major operand form (128 x 128 tiles) instead of the tiled images")
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--denoise-steps", type=int, default=1)
     ap.add_argument("--no-clock-warmup", action="store_true",
