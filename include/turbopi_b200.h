@@ -7,8 +7,8 @@
  *   - the call only enqueues work on `stream` (no allocation, no synchronisation,
  *     no global mutable state), so it may be captured in a CUDA graph and is safe
  *     to call concurrently on different streams -- except tpb200_nvfp4_gemv_tc_static,
- *     whose scratch is one array shared by every call on a device, and tensor-core GEMM launches
- *     that were given a split-K workspace (see both there);
+ *     whose scratch is one array shared by every call on a device (see there); launches that may
+ *     overlap must not share a workspace;
  *   - the device is the calling thread's current device;
  *   - `tpb200_*` functions return TPB200_OK or a negative tpb200_status; arguments
  *     are validated on the host before anything is launched;
@@ -190,11 +190,9 @@ typedef struct {
      * (a smaller one limits the split; NULL = never split).  Zero it ONCE after allocation: the kernel
      * leaves its counters at zero.  Launches that share a workspace must not overlap.  The partial sums
      * are added in a fixed order, so results do not depend on timing.
-     * A split launch is the one exception to "safe to call concurrently on different streams": its CTAs wait
-     * (bounded, ~1 s) for the partner CTAs of their tile, which is safe only while the whole grid is resident.
-     * Another kernel that holds SMs at the same time (a second split launch on another stream, whatever its
-     * workspace) can keep partners off the GPU until the wait gives up (TPB200_ERR_DEVICE through
-     * tpb200_device_error).  Run split launches of one GPU on one stream, or pass workspace = NULL. */
+     * In a split launch the CTAs of a tile wait (bounded, ~1 s) for each other; the launch is a cooperative
+     * launch, which the GPU places only when the whole grid fits, so launches on other streams cannot keep
+     * partners out.  Each of two launches that may overlap needs a workspace of its own. */
     void* workspace; size_t workspace_bytes;
     /* Operand format.  TPB200_OPERANDS_ROWMAJOR (0): as described above.  TPB200_OPERANDS_TILED: a_packed and
      * b_packed point at pre-tiled images that carry their scales (a_sf, b_sf, pitches and a_piece_rows are

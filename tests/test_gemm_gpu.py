@@ -377,3 +377,38 @@ def test_gated_gelu_epilogue_matches_module_arithmetic(cuda_device, M, inter, K,
     mask = torch.ones_like(canvas, dtype=torch.bool)
     mask[1:M + 1, 8:8 + inter] = False
     assert (canvas[mask] == 7.0).all()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rowmajor", [True, False])
+def test_split_k_launches_on_two_streams(cuda_device, rowmajor):
+    """Two split-K launches (each with a workspace of its own) issued on two streams over and over: the CTAs of a
+    tile wait for each other, so each launch is a cooperative launch and the other stream's launch cannot keep
+    partners off the SMs.  Results equal the launches run one after the other; no device error."""
+    from turbopi_b200 import _lib, ops
+    from turbopi_b200.pi05 import TcLinear
+    M, N, K = 50, 1024, 4096                       # 8 or 4 output tiles: the planner cuts K
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(cuda_device)
+    lins, qs, outs, streams = [], [], [], []
+    for i in range(2):
+        lin = TcLinear.from_weight((torch.randn(N, K, generator=g) * 0.02).to(cuda_device), rowmajor=rowmajor)
+        lin.ws = ops.gemm_workspace(cuda_device)
+        q = ops.QuantBuf(M, K, 3, cuda_device, tiled=not rowmajor)
+        ops.rowop(_lib.ROW_NONE, x, K, q)
+        lins.append(lin)
+        qs.append(q)
+        outs.append(torch.empty((M, N), dtype=torch.bfloat16, device=cuda_device))
+        streams.append(torch.cuda.Stream(device=cuda_device))
+    assert ops.nvfp4_gemm_workspace_size(M, N, K, 3, 0 if rowmajor else 1) > 0      # i.e. these launches do split
+    torch.cuda.synchronize()
+    ref = [lins[i](qs[i], torch.empty_like(outs[i])) for i in range(2)]
+    torch.cuda.synchronize()
+    for _ in range(300):
+        for i in range(2):
+            with torch.cuda.stream(streams[i]):
+                lins[i](qs[i], outs[i])
+    torch.cuda.synchronize()
+    assert _lib.load().tpb200_device_error(0) == 0
+    for i in range(2):
+        assert torch.equal(outs[i], ref[i])

@@ -1514,12 +1514,24 @@ extern "C" int tpb200_nvfp4_gemm_ex(const tpb200_nvfp4_gemm_args* a, tpb200_stre
     cfg.blockDim = dim3(two_groups ? tpb::kThreads : tpb::kThreads - 128, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = reinterpret_cast<cudaStream_t>(stream);
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
+    int nattr = 0;
     if (a->flags & TPB200_FLAG_PDL) {
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        attr[nattr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[nattr].val.programmaticStreamSerializationAllowed = 1;
+        ++nattr;
+    }
+    // A split launch's CTAs wait for the partner CTAs of their tile, so all of them must be resident together.
+    // The grid never exceeds one CTA per SM, but another kernel holding SMs at the same time (a launch on another
+    // stream) could keep partners out: a cooperative launch is placed only when the whole grid fits.
+    if (plan.splits > 1) {
+        attr[nattr].id = cudaLaunchAttributeCooperative;
+        attr[nattr].val.cooperative = 1;
+        ++nattr;
+    }
+    if (nattr > 0) {
         cfg.attrs = attr;
-        cfg.numAttrs = 1;
+        cfg.numAttrs = nattr;
     }
 #ifdef TPB_TIMELINE
     static std::atomic<int> launch_no{0};
