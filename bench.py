@@ -652,7 +652,14 @@ def run_serving(group, device, steps=10):
     from turbopi_b200.policy import Pi05Policy
     from turbopi_b200.replicas import RequestDispatcher
     cfg = Pi05Config()
-    policy = Pi05Policy(Pi05(cfg, device, seed=0), None, None, num_denoising_steps=steps)
+    # three pipelines over ONE set of weights per replica, each with buffers, KV cache and scratch of its own: an
+    # inference is a chain of ~600 short dependent launches that leaves most SMs idle, three chains side by side
+    # (one host thread + one stream each) fill them.  `one_in_flight` is the same batch through one pipeline.
+    lanes = 3
+    first = Pi05(cfg, device, seed=0)
+    policies = [Pi05Policy(first if k == 0 else Pi05.sharing_weights(first), None, None, num_denoising_steps=steps)
+                for k in range(lanes)]
+    policy = policies[0]
     rng = np.random.default_rng(3)
 
     def request(i):
@@ -661,19 +668,28 @@ def run_serving(group, device, steps=10):
                 "observation/state": rng.normal(size=8).astype(np.float32),
                 "prompt": [2] + rng.integers(3, cfg.vocab, 12 + i % 20).tolist(), "noise": None}
 
-    policy.warmup(2)
-    disp = RequestDispatcher(group, lambda r: policy.infer(r)["actions"], timeout_s=120.0)
-    out = {"denoise_steps": steps, "replicas": group.world}
-    for batch in (8, 64):
+    for p_ in policies:
+        p_.warmup(2)
+    infer_fns = [(lambda r, p_=p_: p_.infer(r)["actions"]) for p_ in policies]
+    disp = RequestDispatcher(group, infer_fns, timeout_s=120.0)
+    single = RequestDispatcher(group, infer_fns[0], port=int(os.environ.get("MASTER_PORT", "29500")) + 18, timeout_s=120.0)
+    out = {"denoise_steps": steps, "replicas": group.world, "pipelines_in_flight_per_replica": lanes}
+
+    def run(d, batch):
         reqs = [request(i) for i in range(batch)]
         group.barrier()
-        results, stats = disp.serve(reqs)
+        results, stats = d.serve(reqs)
         group.barrier()
-        if group.rank == 0:
-            out[f"batch_{batch}"] = {"requests_per_s": stats["requests_per_s"], "p50_ms": stats["p50_ms"],
-                                     "p99_ms": stats["p99_ms"], "wall_s": stats["wall_s"], "requeued": len(stats["requeued"]),
-                                     "finite": bool(all(np.isfinite(r).all() for r in results))}
-    del policy
+        if group.rank != 0:
+            return None
+        return {"requests_per_s": stats["requests_per_s"], "p50_ms": stats["p50_ms"], "p99_ms": stats["p99_ms"],
+                "wall_s": stats["wall_s"], "requeued": len(stats["requeued"]),
+                "finite": bool(all(np.isfinite(r).all() for r in results))}
+
+    for batch in (8, 64):
+        out[f"batch_{batch}"] = run(disp, batch)
+    out["one_in_flight"] = {"batch_64": run(single, 64)}
+    del policies, policy
     return out if group.rank == 0 else None
 
 

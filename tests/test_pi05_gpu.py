@@ -220,3 +220,32 @@ def test_full_width_error_vs_depth(cuda_device, depth):
           f"max |actions| = {ref.abs().max().item():.3f}")
     assert err <= 2e-2, err
     assert cosine(got.numpy(), ref.numpy()) >= 0.999
+
+
+def test_two_pipelines_over_one_set_of_weights_on_two_streams(cuda_device):
+    """`Pi05.sharing_weights`: a second pipeline over the same weight tensors (no copy) with buffers and scratch of
+    its own.  Both replay their graphs on two streams at the same time, over and over; each returns what it
+    returns alone (their split-K launches are cooperative launches, their scratch is per pipeline)."""
+    from turbopi_b200 import _lib
+    from turbopi_b200.pi05 import Pi05, Pi05Config
+    cfg = Pi05Config(image_size=56, patch=14, vision_layers=2, vision_width=128, vision_mlp=272, vision_heads=2,
+                     prefix_layers=2, width=256, mlp=512, text_len=24, vocab=500, expert_layers=2, expert_width=128,
+                     expert_mlp=256, action_horizon=50, action_dim=32, max_seq=256)
+    a = Pi05(cfg, cuda_device, seed=4)
+    b = Pi05.sharing_weights(a)
+    assert b.prefix[0]["gate_up"].b.data_ptr() == a.prefix[0]["gate_up"].b.data_ptr()
+    assert b.workspace.data_ptr() != a.workspace.data_ptr() and b.cache.data_ptr() != a.cache.data_ptr()
+    g = torch.Generator().manual_seed(8)
+    inputs = [(torch.randint(0, 256, (2, 56, 56, 3), generator=g, dtype=torch.uint8), torch.randint(0, 500, (24,), generator=g),
+               torch.randn(50, 32, generator=g)) for _ in range(2)]
+    alone = [a.infer(*inputs[0], num_steps=3).clone(), a.infer(*inputs[1], num_steps=3).clone()]
+    b.infer(*inputs[1], num_steps=3)                      # captures b's graph
+    torch.cuda.synchronize()
+    streams = [torch.cuda.Stream(device=cuda_device) for _ in range(2)]
+    for _ in range(20):
+        for m, s, inp in ((a, streams[0], inputs[0]), (b, streams[1], inputs[1])):
+            with torch.cuda.stream(s):
+                m.infer(*inp, num_steps=3)
+    torch.cuda.synchronize()
+    assert _lib.load().tpb200_device_error(0) == 0
+    assert torch.equal(a.actions, alone[0]) and torch.equal(b.actions, alone[1])

@@ -110,3 +110,37 @@ def test_split_requests_is_contiguous_and_even():
     assert split_requests(8, 1) == [(0, 8)]
     assert split_requests(10, 4) == [(0, 3), (3, 6), (6, 8), (8, 10)]
     assert split_requests(2, 4) == [(0, 1), (1, 2), (2, 2), (2, 2)]
+
+
+def test_dispatcher_keeps_several_requests_in_flight_per_replica():
+    """`infer` given as a list of callables (pipelines of one replica): the chunk is served by one host thread per
+    pipeline, every request exactly once, results in request order."""
+    import threading
+    import time
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        os.environ.pop(k, None)
+    from turbopi_b200.replicas import ReplicaGroup, RequestDispatcher
+    g = ReplicaGroup.from_env(backend="gloo")
+    served = [[], [], []]
+    running, peak = [0], [0]
+    lock = threading.Lock()
+
+    def lane(k):
+        def infer(req):
+            with lock:
+                running[0] += 1
+                peak[0] = max(peak[0], running[0])
+            time.sleep(0.02)
+            served[k].append(req)
+            with lock:
+                running[0] -= 1
+            return torch.full((2,), float(req))
+        return infer
+
+    d = RequestDispatcher(g, [lane(0), lane(1), lane(2)], timeout_s=5.0)
+    results, stats = d.serve(list(range(12)))
+    assert [float(r[0]) for r in results] == [float(i) for i in range(12)]
+    assert sorted(served[0] + served[1] + served[2]) == list(range(12))
+    assert peak[0] >= 2 and all(len(s) >= 1 for s in served)          # the lanes did overlap
+    assert stats["done"] == 12 and stats["requeued"] == [] and len(stats["latencies_ms"]) == 12
+    g.close()

@@ -302,8 +302,9 @@ class Pi05:
                   "time_mlp_out", "ada_dense"):
             yield k, getattr(self, k)
 
-    def save(self, path):
-        """Write the prepared model (4-bit operands in the form each linear runs in, bf16 tables) to a container file."""
+    def _export(self):
+        """(tensors, meta) of the prepared model: what `save` writes and `_from_prepared` reads.  The tensors are
+        the model's own, not copies."""
         tensors, linears = {}, {}
         for name, obj in self._named_parts():
             if isinstance(obj, TcLinear):
@@ -319,7 +320,20 @@ class Pi05:
             else:
                 tensors[name] = obj
         cfgd = {k: getattr(self.cfg, k) for k in self.cfg.__dataclass_fields__}
-        return weights.save_container(path, tensors, {"kind": "pi05", "config": cfgd, "linears": linears})
+        return tensors, {"kind": "pi05", "config": cfgd, "linears": linears}
+
+    def save(self, path):
+        """Write the prepared model (4-bit operands in the form each linear runs in, bf16 tables) to a container file."""
+        tensors, meta = self._export()
+        return weights.save_container(path, tensors, meta)
+
+    @classmethod
+    def sharing_weights(cls, other, **kw):
+        """A second pipeline over `other`'s weights (the same device tensors, no copy) with buffers, KV cache,
+        split-K and attention scratch of its own: two such pipelines can run at the same time on two streams of
+        one GPU (every kernel's scratch is per pipeline, split-K launches are cooperative launches)."""
+        kw.setdefault("pdl", other.launch_flags == ops.FLAG_PDL)
+        return cls(other.cfg, other.device, _prepared=other._export(), **kw)
 
     def _from_prepared(self, prepared):
         tensors, meta = prepared

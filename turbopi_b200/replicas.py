@@ -15,6 +15,7 @@ runs those requests itself.
 """
 import os
 import pickle
+import threading
 import time
 from datetime import timedelta
 
@@ -104,7 +105,15 @@ class RequestDispatcher:
     """
 
     def __init__(self, group, infer, port=None, timeout_s=30.0):
-        self.group, self.infer, self.timeout_s = group, infer, float(timeout_s)
+        # `infer` may be a list of callables: that many requests of this rank's chunk are in flight at a time,
+        # one host thread and (on a GPU) one CUDA stream per callable, each callable being a pipeline of its own
+        # (its own buffers and scratch).  A Pi0.5 inference is a chain of ~600 short dependent launches that
+        # leaves most SMs idle most of the time; two or three chains side by side fill them.
+        self.lanes = list(infer) if isinstance(infer, (list, tuple)) else [infer]
+        self.group, self.infer, self.timeout_s = group, self.lanes[0], float(timeout_s)
+        self._streams = None
+        if len(self.lanes) > 1 and group.device.type == "cuda":
+            self._streams = [torch.cuda.Stream(device=group.device) for _ in self.lanes]
         self.batch_id = 0
         self.store = None
         if group.world > 1:
@@ -114,11 +123,16 @@ class RequestDispatcher:
             self.store = dist.TCPStore(host, port, world_size=group.world, is_master=(group.rank == 0),
                                        timeout=timedelta(seconds=max(60.0, 4 * self.timeout_s)), wait_for_workers=True)
 
-    def _run(self, request):
+    def _run(self, request, lane=0):
         t0 = time.perf_counter()
-        result = self.infer(request)
-        if self.group.device.type == "cuda":
-            torch.cuda.synchronize(self.group.device)
+        if self._streams is not None:
+            with torch.cuda.stream(self._streams[lane]):
+                result = self.lanes[lane](request)
+                self._streams[lane].synchronize()
+        else:
+            result = self.lanes[lane](request)
+            if self.group.device.type == "cuda":
+                torch.cuda.current_stream(self.group.device).synchronize()
         return result, (time.perf_counter() - t0) * 1e3
 
     def serve(self, requests, leave_after=None):
@@ -130,15 +144,32 @@ class RequestDispatcher:
         lo, hi = split_requests(n, g.world)[g.rank]
         t_start = time.perf_counter()
         mine, lat = {}, []
-        for k, i in enumerate(range(lo, hi)):
-            if leave_after is not None and k >= leave_after:
-                break
-            result, ms = self._run(requests[i])
-            lat.append(ms)
-            if g.rank == 0:
-                mine[i] = result
-            else:
-                self.store.set(f"b{self.batch_id}/r{i}", pickle.dumps((result, ms)))
+        todo = iter(enumerate(range(lo, hi)))
+        lock = threading.Lock()
+
+        def work(lane):
+            while True:
+                with lock:
+                    nxt = next(todo, None)
+                if nxt is None or (leave_after is not None and nxt[0] >= leave_after):
+                    return
+                i = nxt[1]
+                result, ms = self._run(requests[i], lane)
+                with lock:
+                    lat.append(ms)
+                    if g.rank == 0:
+                        mine[i] = result
+                    else:
+                        self.store.set(f"b{self.batch_id}/r{i}", pickle.dumps((result, ms)))
+
+        if len(self.lanes) == 1:
+            work(0)
+        else:
+            threads = [threading.Thread(target=work, args=(lane,)) for lane in range(len(self.lanes))]
+            for t in threads:
+                t.start()
+            for t in threads:
+                t.join()
         stats = {"rank": g.rank, "chunk": (lo, hi), "done": len(lat), "latencies_ms": lat, "requeued": []}
         if g.rank != 0:
             return None, stats
