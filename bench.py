@@ -652,10 +652,10 @@ def run_serving(group, device, steps=10):
     from turbopi_b200.policy import Pi05Policy
     from turbopi_b200.replicas import RequestDispatcher
     cfg = Pi05Config()
-    # three pipelines over ONE set of weights per replica, each with buffers, KV cache and scratch of its own: an
-    # inference is a chain of ~600 short dependent launches that leaves most SMs idle, three chains side by side
+    # four pipelines over ONE set of weights per replica, each with buffers, KV cache and scratch of its own: an
+    # inference is a chain of ~600 short dependent launches that leaves most SMs idle, four chains side by side
     # (one host thread + one stream each) fill them.  `one_in_flight` is the same batch through one pipeline.
-    lanes = 3
+    lanes = 4
     first = Pi05(cfg, device, seed=0)
     policies = [Pi05Policy(first if k == 0 else Pi05.sharing_weights(first), None, None, num_denoising_steps=steps)
                 for k in range(lanes)]
