@@ -130,3 +130,22 @@ def test_valid_mask_buffers():
     assert (m.key_bias[S:] == 0).all()
     m.set_valid()
     assert torch.equal(m.b["pos_prefix"].long(), torch.arange(S)) and (m.key_bias == 0).all()
+
+
+def test_a_second_pipeline_shares_the_weights_and_nothing_else():
+    """`Pi05.sharing_weights`: the same weight tensors (no copy), separate linear objects, buffers, KV cache and
+    scratch: what two pipelines need to run side by side on one GPU."""
+    cfg = Pi05Config(**SMALL)
+    a = Pi05.from_state_dict(weights.random_state_dict(cfg, seed=5), cfg, "cpu")
+    b = Pi05.sharing_weights(a)
+    assert b.cfg == a.cfg and b.launch_flags == a.launch_flags
+    for (na, x), (nb, y) in zip(a._named_parts(), b._named_parts()):
+        assert na == nb
+        if isinstance(x, TcLinear):
+            assert x is not y and x.b.data_ptr() == y.b.data_ptr() and x.rowmajor == y.rowmajor
+            assert (x.N, x.K, x.g) == (y.N, y.K, y.g)
+            assert x.ws.data_ptr() != y.ws.data_ptr()            # split-K scratch per pipeline
+        else:
+            assert x.data_ptr() == y.data_ptr()
+    assert a.cache.data_ptr() != b.cache.data_ptr() and a.attn_ws.data_ptr() != b.attn_ws.data_ptr()
+    assert a.b["ph"].data_ptr() != b.b["ph"].data_ptr() and a.actions.data_ptr() != b.actions.data_ptr()
