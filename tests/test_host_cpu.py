@@ -225,3 +225,20 @@ def test_bench_reference_arm_prints_the_contract_line():
     assert d["cpu_baseline"]["value"] == d["value"] and d["cpu_baseline"]["sample"]
     assert d["e2e"] == {"value": d["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
     assert "workload" in d["config"]
+
+
+def test_ctypes_structures_follow_the_header_field_by_field():
+    """Every argument struct of include/turbopi_b200.h has a ctypes mirror in turbopi_b200/_lib.py with the same
+    fields in the same order (a field added on one side only would shift everything behind it)."""
+    header = (ROOT / "include" / "turbopi_b200.h").read_text()
+    mirrors = {"tpb200_gemv_problem": _lib.GemvProblem, "tpb200_nvfp4_gemm_args": _lib.GemmArgs,
+               "tpb200_gemv_tc_problem": _lib.GemvTcProblem, "tpb200_gemv_tc_fused_problem": _lib.GemvTcFusedProblem,
+               "tpb200_gemv_tc_plan_info": _lib.GemvTcPlanInfo, "tpb200_attention_args": _lib.AttentionArgs,
+               "tpb200_rowop_args": _lib.RowOpArgs}
+    for name, mirror in mirrors.items():
+        m = re.search(r"typedef struct(?:\s+\w+)?\s*\{([^}]*)\}\s*" + name + r"\s*;", header, re.S)
+        assert m, name
+        body = re.sub(r"/\*.*?\*/", "", m.group(1), flags=re.S)
+        fields = [part.strip().split()[-1].split("[")[0].lstrip("*")          # "int M, N, K" declares three
+                  for d in body.split(";") if d.strip() for part in d.split(",")]
+        assert fields == [f[0] for f in mirror._fields_], name
