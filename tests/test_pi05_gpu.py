@@ -3,6 +3,7 @@ reference's own model code by tests/test_oracle_golden.py): a reduced model agai
 (padded prompt / missing camera included), then the FULL widths and head geometry at growing depth, up
 to the full 27 + 18 + 18 layers, where the same oracle code is executed in fp32 on the GPU (after a check
 that its GPU execution agrees with its CPU execution)."""
+import os
 import numpy as np
 import pytest
 import torch
@@ -249,3 +250,37 @@ def test_two_pipelines_over_one_set_of_weights_on_two_streams(cuda_device):
     torch.cuda.synchronize()
     assert _lib.load().tpb200_device_error(0) == 0
     assert torch.equal(a.actions, alone[0]) and torch.equal(b.actions, alone[1])
+
+
+def test_dispatcher_with_two_pipelines_in_flight_returns_what_one_returns(cuda_device):
+    """`RequestDispatcher` over two `Pi05Policy` pipelines that share their weights (one host thread and one stream
+    each): every request's actions equal those of the same request served by a single pipeline."""
+    import numpy as np
+    from turbopi_b200 import _lib
+    from turbopi_b200.pi05 import Pi05, Pi05Config
+    from turbopi_b200.policy import Pi05Policy
+    from turbopi_b200.replicas import ReplicaGroup, RequestDispatcher
+    cfg = Pi05Config(image_size=56, patch=14, vision_layers=2, vision_width=128, vision_mlp=272, vision_heads=2,
+                     prefix_layers=2, width=256, mlp=512, text_len=24, vocab=500, expert_layers=2, expert_width=128,
+                     expert_mlp=256, action_horizon=50, action_dim=32, max_seq=256)
+    first = Pi05(cfg, cuda_device, seed=9)
+    policies = [Pi05Policy(first, None, None, num_denoising_steps=3),
+                Pi05Policy(Pi05.sharing_weights(first), None, None, num_denoising_steps=3)]
+    rng = np.random.default_rng(2)
+    noise = rng.normal(size=(50, 32)).astype(np.float32)
+    reqs = [{"observation/image": rng.integers(0, 256, (56, 56, 3), dtype=np.uint8),
+             "observation/wrist_image": rng.integers(0, 256, (56, 56, 3), dtype=np.uint8),
+             "observation/state": rng.normal(size=8).astype(np.float32),
+             "prompt": [2] + rng.integers(3, 500, 5 + i % 7).tolist(), "noise": noise} for i in range(10)]
+    for p in policies:
+        p.warmup(1)
+    alone = [policies[0].infer(r)["actions"] for r in reqs]
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        os.environ.pop(k, None)
+    group = ReplicaGroup(0, 1, 0, cuda_device)
+    disp = RequestDispatcher(group, [lambda r, p=p: p.infer(r)["actions"] for p in policies], timeout_s=60.0)
+    results, stats = disp.serve(reqs)
+    assert _lib.load().tpb200_device_error(0) == 0
+    assert stats["done"] == 10 and stats["requeued"] == []
+    for got, ref in zip(results, alone):
+        assert np.array_equal(got, ref)
