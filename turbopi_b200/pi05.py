@@ -418,6 +418,9 @@ class Pi05:
         prompt_len = c.text_len if prompt_len is None else int(prompt_len)
         if len(image_valid) != c.num_images or not 0 <= prompt_len <= c.text_len:
             raise TurboPiError("set_valid: one flag per camera and 0 <= prompt_len <= text_len")
+        key = (tuple(image_valid), prompt_len)
+        if getattr(self, "_valid_key", None) == key:       # the same mask as last time: the device tables stand
+            return
         valid = torch.cat([torch.full((c.image_tokens,), v) for v in image_valid] + [torch.arange(c.text_len) < prompt_len])
         if not bool(valid.any()):
             raise TurboPiError("set_valid: at least one prefix token must be valid")
@@ -430,6 +433,7 @@ class Pi05:
         self.b["pos_suffix"].copy_(torch.arange(first, first + A, dtype=torch.int32))
         self.key_bias.copy_(bias.to(torch.bfloat16))
         self.valid = valid
+        self._valid_key = key
 
     def _attention(self, q, k, v, out):
         """q [L, H*D] -> softmax(q k^T / sqrt(D) + key bias) v, all heads sharing one K/V head.  Prefix
