@@ -144,3 +144,23 @@ def test_dispatcher_keeps_several_requests_in_flight_per_replica():
     assert peak[0] >= 2 and all(len(s) >= 1 for s in served)          # the lanes did overlap
     assert stats["done"] == 12 and stats["requeued"] == [] and len(stats["latencies_ms"]) == 12
     g.close()
+
+
+def test_a_failing_pipeline_fails_the_batch_loudly():
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"):
+        os.environ.pop(k, None)
+    from turbopi_b200.replicas import ReplicaGroup, RequestDispatcher
+    g = ReplicaGroup.from_env(backend="gloo")
+
+    def good(req):
+        import time
+        time.sleep(0.05)                 # long enough for the other lane to draw a request
+        return torch.zeros(1)
+
+    def bad(req):
+        raise RuntimeError("pipeline broke")
+
+    for lanes in ([bad], [good, bad]):
+        with pytest.raises(RuntimeError, match="pipeline broke"):
+            RequestDispatcher(g, lanes, timeout_s=1.0).serve(list(range(6)))
+    g.close()

@@ -146,6 +146,7 @@ class RequestDispatcher:
         mine, lat = {}, []
         todo = iter(enumerate(range(lo, hi)))
         lock = threading.Lock()
+        errors = []
 
         def work(lane):
             while True:
@@ -154,7 +155,12 @@ class RequestDispatcher:
                 if nxt is None or (leave_after is not None and nxt[0] >= leave_after):
                     return
                 i = nxt[1]
-                result, ms = self._run(requests[i], lane)
+                try:
+                    result, ms = self._run(requests[i], lane)
+                except BaseException as exc:           # a worker thread must not swallow its pipeline's error
+                    with lock:
+                        errors.append(exc)
+                    return
                 with lock:
                     lat.append(ms)
                     if g.rank == 0:
@@ -170,6 +176,8 @@ class RequestDispatcher:
                 t.start()
             for t in threads:
                 t.join()
+        if errors:
+            raise errors[0]
         stats = {"rank": g.rank, "chunk": (lo, hi), "done": len(lat), "latencies_ms": lat, "requeued": []}
         if g.rank != 0:
             return None, stats
