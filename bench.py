@@ -655,7 +655,8 @@ def run_serving(group, device, steps=10):
     # four pipelines over ONE set of weights per replica, each with buffers, KV cache and scratch of its own: an
     # inference is a chain of ~600 short dependent launches that leaves most SMs idle, four chains side by side
     # (one host thread + one stream each) fill them.  `one_in_flight` is the same batch through one pipeline.
-    lanes = 4
+    # one spinning host thread per pipeline: no more of them than the host has cores for all replicas
+    lanes = max(1, min(4, (os.cpu_count() or 1) // max(1, group.world)))
     first = Pi05(cfg, device, seed=0)
     policies = [Pi05Policy(first if k == 0 else Pi05.sharing_weights(first), None, None, num_denoising_steps=steps)
                 for k in range(lanes)]
